@@ -1,0 +1,186 @@
+/*
+ * C ABI of the B200 decoder megakernel (libmegabake_b200.so).
+ *
+ * One handle owns the launch state for one decoder shape on one GPU.  Every
+ * entry point returns an mk_error code, never throws, never allocates device
+ * memory (the caller passes the workspace) and never synchronises unless its
+ * comment says so.  Pointers are raw device addresses unless marked "host".
+ * Streams are cudaStream_t passed as void*.
+ *
+ * Each entry point names the reference interface it stands in for, by path
+ * inside the reference project.
+ */
+#ifndef MEGABAKE_B200_H
+#define MEGABAKE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MK_MAX_LAYERS 96
+#define MK_TOKEN_TILE 16
+
+typedef enum mk_error {
+  MK_OK = 0,
+  MK_ERR_INVALID = 1,      /* bad argument (null, negative, inconsistent sizes)       */
+  MK_ERR_UNSUPPORTED = 2,  /* shape outside what the kernel covers (see mk_last_error) */
+  MK_ERR_CUDA = 3,         /* a CUDA runtime/driver call failed                         */
+  MK_ERR_ALIGNMENT = 4,    /* a tensor base is not 16-byte aligned                      */
+  MK_ERR_WORKSPACE = 5,    /* workspace too small                                       */
+  MK_ERR_UNBOUND = 6,      /* launch before mk_bind_weights                             */
+  MK_ERR_DEVICE_STATUS = 7 /* the device status word is not MK_STATUS_OK                */
+} mk_error;
+
+/* Device status word written by the kernel instead of trapping
+ * (the reference traps: src/megabake/bodies/attention.py:540-543,
+ *  src/megabake/bodies/generic.py:1159-1174). */
+typedef enum mk_device_status {
+  MK_STATUS_OK = 0,
+  MK_STATUS_KV_OVERFLOW = 1, /* valid_length < 0 or valid_length + 1 > capacity */
+  MK_STATUS_BAD_INDEX = 2,   /* token id or position out of range              */
+  MK_STATUS_TIMEOUT = 3      /* a bounded device wait ran out                   */
+} mk_device_status;
+
+enum { MK_ROPE_HF = 0, MK_ROPE_HALF_SWAP = 1 };
+enum { MK_ENGINE_TCGEN05 = 0, MK_ENGINE_SIMT = 1 };
+
+/* Decoder shape.  Mirrors the facts the reference reads off the captured graph
+ * (src/megabake/lowering.py:1851-1870 for the attention contract,
+ *  src/megabake/bodies/gemm.py:1887-1890 for the multiple-of-64 rule). */
+typedef struct mk_config {
+  int32_t hidden;
+  int32_t layers;
+  int32_t q_heads;
+  int32_t kv_heads;
+  int32_t head_dim;      /* 64 or 128 */
+  int32_t intermediate;
+  int32_t vocab;
+  float rms_eps;
+  int32_t qkv_bias;      /* 1: q/k/v projections carry a bias (addmm epilogue) */
+  int32_t rope_style;    /* MK_ROPE_* */
+  int32_t max_tokens;    /* largest batch (decode) or batch*sequence (prefill) per launch */
+  int32_t max_positions; /* rows of the cos/sin tables */
+  int32_t engine;        /* MK_ENGINE_*; SIMT is a bring-up/diagnostic engine */
+  int32_t sm_limit;      /* 0: one CTA per SM on the whole GPU; >0: use this many CTAs */
+} mk_config;
+
+typedef struct mk_layer_weights {
+  const void* input_norm;  /* bf16 [hidden] */
+  const void* q;           /* bf16 [q_heads*head_dim, hidden], row-major (nn.Linear.weight) */
+  const void* k;           /* bf16 [kv_heads*head_dim, hidden] */
+  const void* v;
+  const void* q_bias;      /* bf16 [rows] or NULL */
+  const void* k_bias;
+  const void* v_bias;
+  const void* o;           /* bf16 [hidden, q_heads*head_dim] */
+  const void* post_norm;   /* bf16 [hidden] */
+  const void* gate;        /* bf16 [intermediate, hidden] */
+  const void* up;
+  const void* down;        /* bf16 [hidden, intermediate] */
+} mk_layer_weights;
+
+typedef struct mk_weights {
+  const void* embed;       /* bf16 [vocab, hidden] */
+  const void* final_norm;  /* bf16 [hidden] */
+  const void* lm_head;     /* bf16 [vocab, hidden]; equals embed when tied */
+  const void* rope_cos;    /* bf16 [max_positions, head_dim] */
+  const void* rope_sin;
+  const mk_layer_weights* layers; /* host array of config.layers entries */
+} mk_weights;
+
+typedef struct mk_status_info {
+  int32_t status;   /* mk_device_status */
+  int32_t where;    /* kernel-internal wait/site id of the first failure */
+  int32_t cta;
+  int32_t detail;
+} mk_status_info;
+
+typedef struct mk_handle_s* mk_handle;
+
+/* Bytes of device workspace mk_create needs for this shape on `device`.
+ * Reference: the runtime-owned workspace of src/megabake/compiler.py:1979-1981. */
+size_t mk_workspace_bytes(const mk_config* config, int device);
+
+/* Create launch state.  `workspace` is device memory of at least
+ * mk_workspace_bytes, 256-byte aligned, owned by the caller and kept alive
+ * until mk_destroy; it is zeroed on `stream`.
+ * Reference: compile_plan + _RuntimeState construction,
+ * src/megabake/compiler.py:702-873, 1877-1981. */
+int mk_create(const mk_config* config, void* workspace, size_t workspace_bytes, int device,
+              void* stream, mk_handle* out);
+
+/* Bind (or re-bind after the caller replaced a tensor) every parameter by
+ * pointer; encodes the TMA descriptors and uploads the phase table on `stream`.
+ * Reference: parameter rebinding in bind_callable / _fast_table_rebind,
+ * src/megabake/compiler.py:980-997, 2216-2270, and build_table_descriptors,
+ * src/megabake/bodies/gemm.py:1809-1843. */
+int mk_bind_weights(mk_handle handle, const mk_weights* weights, void* stream);
+
+/* One decode step for `batch` sequences: one cooperative launch, no sync.
+ * ids/positions: int64 [batch].  key_caches/value_caches: host arrays of
+ * config.layers device pointers, each bf16 [batch, capacity, kv_heads,
+ * head_dim] contiguous.  valid_lengths: host array of config.layers device
+ * pointers to int32 [1]; read, used as the append row, and advanced by one.
+ * logits: bf16 [batch, vocab].
+ * Reference: the bound callable's warm call, src/megabake/compiler.py:964-1081,
+ * running the decode graph of tests/fixtures.py:247-312 whose attention is
+ * megabake::kv_attention (src/megabake/lowering.py:211-247). */
+int mk_decode(mk_handle handle, const int64_t* ids, const int64_t* positions, int batch,
+              void* const* key_caches, void* const* value_caches, int32_t* const* valid_lengths,
+              int capacity, void* logits, void* stream);
+
+/* Stateless prompt pass over [batch, sequence] tokens with causal or additive
+ * attention mask (bf16 [batch, 1, sequence, sequence], NULL = causal).
+ * logits: bf16 [batch, sequence, vocab].
+ * Reference: the mode="prefill" graph whose attention is megabake::attention
+ * (src/megabake/lowering.py:273-300, src/megabake/fx_handler/hf_attention.py:28-61). */
+int mk_prefill(mk_handle handle, const int64_t* ids, const int64_t* positions, const void* mask,
+               int batch, int sequence, void* logits, void* stream);
+
+/* y[M,N] = x[M,K] . W[N,K]^T (+ bias[N]), bf16 in/out, fp32 accumulate, one
+ * rounding after the bias.  Runs the megakernel's projection engine on one
+ * phase.  `handle` supplies workspace and engine; N, K multiples of 64,
+ * M <= config.max_tokens, K <= 2048 or N*K/64 small enough per CTA (see
+ * mk_last_error).  Synchronous set-up (encodes one TMA descriptor), async launch.
+ * Reference: the projection body, src/megabake/bodies/gemm.py:629-1114 with
+ * its bias epilogue :1223-1251. */
+int mk_linear(mk_handle handle, const void* x, const void* weight, const void* bias, void* y,
+              int m, int n, int k, void* stream);
+
+/* megabake::kv_attention on caller tensors (shapes as in mk_decode, one layer):
+ * query bf16 [batch, 1, q_heads, head_dim], key/value bf16 [batch, 1, kv_heads,
+ * head_dim] (already rotated), output bf16 [batch*q_heads, 1, head_dim].
+ * Appends, attends, advances valid_length.
+ * Reference: src/megabake/lowering.py:211-247. */
+int mk_kv_attention(mk_handle handle, const void* query, const void* key, const void* value,
+                    void* key_cache, void* value_cache, int32_t* valid_length, int batch,
+                    int capacity, void* output, void* stream);
+
+/* megabake::attention: query bf16 [batch, q_len, q_heads, head_dim], key/value
+ * bf16 [batch, k_len, kv_heads, head_dim], mask bf16 additive [batch, 1, q_len,
+ * k_len] or NULL, output bf16 [batch*q_heads, q_len, head_dim].
+ * Reference: src/megabake/lowering.py:273-300. */
+int mk_attention(mk_handle handle, const void* query, const void* key, const void* value,
+                 const void* mask, float scale, int batch, int q_len, int k_len, void* output,
+                 void* stream);
+
+/* Synchronises `stream`, reads the device status word, and, if it is not OK,
+ * resets the barrier/exchange counters so the handle can launch again.
+ * Reference: none (the reference traps and loses the context). */
+int mk_status(mk_handle handle, void* stream, mk_status_info* out);
+
+/* Number of CTAs each launch uses, bytes of dynamic shared memory, kernels launched so far. */
+int mk_launch_info(mk_handle handle, int32_t* ctas, int32_t* smem_bytes, int64_t* launches);
+
+/* Last error text for this thread (host string, valid until the next call). */
+const char* mk_last_error(void);
+
+int mk_destroy(mk_handle handle);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MEGABAKE_B200_H */

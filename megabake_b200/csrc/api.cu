@@ -1,0 +1,556 @@
+// Host side of the C ABI declared in include/megabake_b200.h: workspace carving,
+// TMA descriptor encoding, the per-launch parameter block and the cooperative
+// launch of the megakernel.  No device memory is allocated here.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <vector>
+
+#include "decoder_kernel.cuh"
+
+using namespace mk;
+
+namespace {
+
+thread_local char g_error[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define MK_CUDA(call)                                                                       \
+  do {                                                                                      \
+    cudaError_t e_ = (call);                                                                \
+    if (e_ != cudaSuccess) return fail(MK_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e_)); \
+  } while (0)
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct Carve {
+  size_t ctrl, tmaps, phases, hidden, qkv, attn, act, partials, tile_ctr, att_max, att_sum, att_part, att_ctr, total;
+  int max_tiles;
+};
+
+int qkv_width(const mk_config& c) { return (c.q_heads + 2 * c.kv_heads) * c.head_dim; }
+
+Carve carve(const mk_config& c, int grid) {
+  Carve v{};
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    const size_t at = off;
+    off = align_up(off + bytes, 256);
+    return at;
+  };
+  const size_t m = static_cast<size_t>(c.max_tokens);
+  int max_tiles = (c.vocab + kTileRows - 1) / kTileRows;
+  const int inter_tiles = (c.intermediate + kTileRows - 1) / kTileRows;
+  const int qkv_tiles = (c.q_heads * c.head_dim + kTileRows - 1) / kTileRows +
+                        2 * ((c.kv_heads * c.head_dim + kTileRows - 1) / kTileRows);
+  if (inter_tiles > max_tiles) max_tiles = inter_tiles;
+  if (qkv_tiles > max_tiles) max_tiles = qkv_tiles;
+  v.max_tiles = max_tiles;
+  v.ctrl = take(sizeof(Control));
+  v.tmaps = take(sizeof(CUtensorMap) * (7 * static_cast<size_t>(c.layers) + 2));
+  v.phases = take(sizeof(GemmPhase) * (4 * static_cast<size_t>(c.layers) + 2));
+  v.hidden = take(m * c.hidden * 2);
+  v.qkv = take(m * qkv_width(c) * 2);
+  v.attn = take(m * c.q_heads * c.head_dim * 2);
+  v.act = take(m * c.intermediate * 2);
+  v.partials = take(static_cast<size_t>(grid) * 2 * kPartialFloats * 4);
+  v.tile_ctr = take(static_cast<size_t>(max_tiles) * 4);
+  v.att_max = take(m * c.kv_heads * kMaxChunks * 8 * 4);
+  v.att_sum = take(m * c.kv_heads * kMaxChunks * 8 * 4);
+  v.att_part = take(m * c.q_heads * kMaxChunks * c.head_dim * 4);
+  v.att_ctr = take(m * c.kv_heads * 4 * 4);
+  v.total = off;
+  return v;
+}
+
+int check_config(const mk_config& c) {
+  if (c.hidden <= 0 || c.layers <= 0 || c.q_heads <= 0 || c.kv_heads <= 0 || c.intermediate <= 0 || c.vocab <= 0 ||
+      c.max_tokens <= 0 || c.max_positions <= 0)
+    return fail(MK_ERR_INVALID, "config: every size must be positive");
+  if (c.layers > MK_MAX_LAYERS) return fail(MK_ERR_UNSUPPORTED, "config: at most %d layers", MK_MAX_LAYERS);
+  if (c.head_dim != 64 && c.head_dim != 128) return fail(MK_ERR_UNSUPPORTED, "config: head_dim must be 64 or 128");
+  if (c.q_heads % c.kv_heads) return fail(MK_ERR_INVALID, "config: q_heads must be a multiple of kv_heads");
+  if (c.q_heads / c.kv_heads > 8) return fail(MK_ERR_UNSUPPORTED, "config: at most 8 query heads per kv head");
+  if (c.hidden % 64 || c.intermediate % 64)
+    return fail(MK_ERR_UNSUPPORTED, "config: hidden and intermediate must be multiples of 64");
+  if (c.engine != MK_ENGINE_TCGEN05 && c.engine != MK_ENGINE_SIMT) return fail(MK_ERR_INVALID, "config: engine");
+  if (c.rope_style != MK_ROPE_HF && c.rope_style != MK_ROPE_HALF_SWAP) return fail(MK_ERR_INVALID, "config: rope_style");
+  return MK_OK;
+}
+
+int device_grid(const mk_config& c, int device, int* grid) {
+  int sms = 0;
+  MK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  *grid = (c.sm_limit > 0 && c.sm_limit < sms) ? c.sm_limit : sms;
+  return MK_OK;
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(sym);
+  });
+  return fn;
+}
+
+// bf16 [rows, k] row-major -> boxes of 128 rows x 64 columns, 128-byte swizzle.
+int encode_weight_map(CUtensorMap* out, const void* base, int rows, int k) {
+  if (reinterpret_cast<uintptr_t>(base) % 16) return fail(MK_ERR_ALIGNMENT, "weight base %p is not 16-byte aligned", base);
+  auto fn = encode_fn();
+  if (!fn) return fail(MK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
+  const cuuint32_t box[2] = {kChunkK, kTileRows};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MK_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (rows %d, k %d)", (int)r, rows, k);
+  return MK_OK;
+}
+
+}  // namespace
+
+struct mk_handle_s {
+  mk_config cfg;
+  int device, grid;
+  uint8_t* ws;
+  Carve cv;
+  bool bound;
+  mk_weights weights;
+  std::vector<mk_layer_weights> layers;
+  uint32_t epoch;
+  int64_t launches;
+  long long timeout_cycles;
+  float att_scale;
+  std::mutex lock;
+};
+
+namespace {
+
+template <typename T>
+T* at(mk_handle h, size_t off) { return reinterpret_cast<T*>(h->ws + off); }
+
+void finish_phase(GemmPhase& ph) {
+  ph.kc = ph.k / kChunkK;
+  ph.tc = ph.kc * ph.nacc;
+  ph.ntiles = ph.tile_start[ph.nseg];
+  ph.total = static_cast<long long>(ph.ntiles) * ph.tc;
+}
+
+// The activation slots hold 32 K-chunks: a phase fits if its whole K does, or
+// if no CTA's share of the phase spans more than 32 K-steps.
+int check_phase_fits(const GemmPhase& ph, int grid, const char* what) {
+  if (ph.kc <= kBSlots) return MK_OK;
+  const int geff = ph.total < grid ? static_cast<int>(ph.total) : grid;
+  const long long per_cta = (ph.total + geff - 1) / geff + 1;
+  const long long ksteps = (per_cta + ph.nacc - 1) / ph.nacc + 1;
+  if (ksteps <= kBSlots) return MK_OK;
+  return fail(MK_ERR_UNSUPPORTED,
+              "%s: K=%d needs %lld activation chunks per CTA on %d CTAs; the kernel holds %d", what, ph.k, ksteps, grid,
+              kBSlots);
+}
+
+void base_params(mk_handle h, KParams& p) {
+  memset(&p, 0, sizeof(p));
+  const mk_config& c = h->cfg;
+  p.hidden = c.hidden; p.layers = c.layers; p.q_heads = c.q_heads; p.kv_heads = c.kv_heads;
+  p.head_dim = c.head_dim; p.inter = c.intermediate; p.vocab = c.vocab; p.eps = c.rms_eps;
+  p.rope_style = c.rope_style; p.prefill_rope_style = MK_ROPE_HF;
+  p.att_scale = h->att_scale;
+  p.engine = c.engine;
+  p.epoch = h->epoch;
+  p.qkv_ld = qkv_width(c);
+  p.max_positions = c.max_positions;
+  p.timeout_cycles = h->timeout_cycles;
+  if (const char* env = getenv("MEGABAKE_DEBUG_STOP")) p.debug_stop = atoi(env);
+  p.phases = at<GemmPhase>(h, h->cv.phases);
+  p.hidden_buf = at<bf16>(h, h->cv.hidden);
+  p.qkv = at<bf16>(h, h->cv.qkv);
+  p.attn = at<bf16>(h, h->cv.attn);
+  p.act = at<bf16>(h, h->cv.act);
+  p.partials = at<float>(h, h->cv.partials);
+  p.tile_ctr = at<uint32_t>(h, h->cv.tile_ctr);
+  p.att_max = at<float>(h, h->cv.att_max);
+  p.att_sum = at<float>(h, h->cv.att_sum);
+  p.att_part = at<float>(h, h->cv.att_part);
+  p.att_ctr = at<uint32_t>(h, h->cv.att_ctr);
+  p.ctrl = at<Control>(h, h->cv.ctrl);
+  p.embed = static_cast<const bf16*>(h->weights.embed);
+  p.cos_t = static_cast<const bf16*>(h->weights.rope_cos);
+  p.sin_t = static_cast<const bf16*>(h->weights.rope_sin);
+}
+
+int launch(mk_handle h, KParams& p, void* stream) {
+  void* args[] = {&p};
+  MK_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(&megakernel), dim3(h->grid), dim3(kThreads), args,
+                                      kSmemBytes, static_cast<cudaStream_t>(stream)));
+  h->epoch += static_cast<uint32_t>(p.nbar) * static_cast<uint32_t>(h->grid);
+  h->launches += 1;
+  return MK_OK;
+}
+
+int token_tiles(int m) { return (m + kTok - 1) / kTok; }
+
+// Grid barriers between the token tiles of each projection phase (tcgen05 engine only).
+int tile_barriers(mk_handle h, int m, int n_gemm) {
+  return h->cfg.engine == MK_ENGINE_TCGEN05 ? (token_tiles(m) - 1) * n_gemm : 0;
+}
+
+int attention_fits(mk_handle h, int keys, const char* what) {
+  const int gs = h->cfg.q_heads / h->cfg.kv_heads;
+  const int max_len = (kScoreBytes / 4 / gs) & ~7;
+  const int need = (keys + max_len - 1) / max_len;
+  if (need > kMaxChunks || need > h->grid)
+    return fail(MK_ERR_UNSUPPORTED, "%s: %d keys exceed %d chunks of %d", what, keys, kMaxChunks, max_len);
+  return MK_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* mk_last_error(void) { return g_error; }
+
+size_t mk_workspace_bytes(const mk_config* config, int device) {
+  if (!config || check_config(*config) != MK_OK) return 0;
+  int grid = 0;
+  if (device_grid(*config, device, &grid) != MK_OK) return 0;
+  return carve(*config, grid).total;
+}
+
+int mk_create(const mk_config* config, void* workspace, size_t workspace_bytes, int device, void* stream,
+              mk_handle* out) {
+  if (!config || !workspace || !out) return fail(MK_ERR_INVALID, "mk_create: null argument");
+  if (int e = check_config(*config)) return e;
+  if (reinterpret_cast<uintptr_t>(workspace) % 256) return fail(MK_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
+  MK_CUDA(cudaSetDevice(device));
+  int grid = 0;
+  if (int e = device_grid(*config, device, &grid)) return e;
+  const Carve cv = carve(*config, grid);
+  if (workspace_bytes < cv.total)
+    return fail(MK_ERR_WORKSPACE, "workspace has %zu bytes, %zu needed", workspace_bytes, cv.total);
+  int major = 0, coop = 0, khz = 0;
+  MK_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+  MK_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device));
+  MK_CUDA(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, device));
+  if (major != 10) return fail(MK_ERR_UNSUPPORTED, "device %d is sm_%d0; this library is built for sm_100a only", device, major);
+  if (!coop) return fail(MK_ERR_UNSUPPORTED, "device %d does not support cooperative launch", device);
+  MK_CUDA(cudaFuncSetAttribute(megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+  int per_sm = 0;
+  MK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, megakernel, kThreads, kSmemBytes));
+  if (per_sm < 1) return fail(MK_ERR_UNSUPPORTED, "the megakernel does not fit on an SM of device %d", device);
+  mk_handle h = new (std::nothrow) mk_handle_s();
+  if (!h) return fail(MK_ERR_INVALID, "out of host memory");
+  h->cfg = *config;
+  h->device = device;
+  h->grid = grid;
+  h->ws = static_cast<uint8_t*>(workspace);
+  h->cv = cv;
+  h->bound = false;
+  h->epoch = 0;
+  h->launches = 0;
+  double ms = 2000.0;
+  if (const char* env = getenv("MEGABAKE_WAIT_LIMIT_MS")) ms = atof(env) > 0 ? atof(env) : ms;
+  h->timeout_cycles = static_cast<long long>(ms * static_cast<double>(khz));
+  h->att_scale = static_cast<float>(std::pow(static_cast<double>(config->head_dim), -0.5));
+  memset(&h->weights, 0, sizeof(h->weights));
+  cudaError_t e = cudaMemsetAsync(workspace, 0, cv.total, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) {
+    delete h;
+    return fail(MK_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+  }
+  *out = h;
+  return MK_OK;
+}
+
+int mk_destroy(mk_handle h) {
+  delete h;
+  return MK_OK;
+}
+
+int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
+  if (!h || !w || !w->layers) return fail(MK_ERR_INVALID, "mk_bind_weights: null argument");
+  std::lock_guard<std::mutex> guard(h->lock);
+  const mk_config& c = h->cfg;
+  if (!w->embed || !w->final_norm || !w->lm_head || !w->rope_cos || !w->rope_sin)
+    return fail(MK_ERR_INVALID, "mk_bind_weights: embed, final_norm, lm_head and the rope tables are required");
+  const int L = c.layers;
+  const int q_size = c.q_heads * c.head_dim, kv_size = c.kv_heads * c.head_dim;
+  std::vector<CUtensorMap> maps(7 * static_cast<size_t>(L) + 1);
+  std::vector<GemmPhase> phases(4 * static_cast<size_t>(L) + 1);
+  CUtensorMap* dmaps = at<CUtensorMap>(h, h->cv.tmaps);
+  bf16* hidden = at<bf16>(h, h->cv.hidden);
+  bf16* qkv = at<bf16>(h, h->cv.qkv);
+  bf16* attn = at<bf16>(h, h->cv.attn);
+  bf16* act = at<bf16>(h, h->cv.act);
+  auto tiles = [](int rows) { return (rows + kTileRows - 1) / kTileRows; };
+  for (int l = 0; l < L; ++l) {
+    const mk_layer_weights& lw = w->layers[l];
+    if (!lw.input_norm || !lw.q || !lw.k || !lw.v || !lw.o || !lw.post_norm || !lw.gate || !lw.up || !lw.down)
+      return fail(MK_ERR_INVALID, "mk_bind_weights: layer %d has a null weight", l);
+    if (c.qkv_bias && (!lw.q_bias || !lw.k_bias || !lw.v_bias))
+      return fail(MK_ERR_INVALID, "mk_bind_weights: layer %d lacks a q/k/v bias", l);
+    const void* mats[7] = {lw.q, lw.k, lw.v, lw.o, lw.gate, lw.up, lw.down};
+    const int rows[7] = {q_size, kv_size, kv_size, c.hidden, c.intermediate, c.intermediate, c.hidden};
+    const int ks[7] = {c.hidden, c.hidden, c.hidden, q_size, c.hidden, c.hidden, c.intermediate};
+    for (int i = 0; i < 7; ++i)
+      if (int e = encode_weight_map(&maps[7 * l + i], mats[i], rows[i], ks[i])) return e;
+    GemmPhase* ph = &phases[4 * l];
+    memset(ph, 0, sizeof(GemmPhase) * 4);
+    // q, k, v
+    ph[0].nseg = 3; ph[0].nacc = 1; ph[0].k = c.hidden;
+    const int seg_rows[3] = {q_size, kv_size, kv_size};
+    const void* biases[3] = {lw.q_bias, lw.k_bias, lw.v_bias};
+    int tile = 0, col = 0;
+    for (int s = 0; s < 3; ++s) {
+      ph[0].tmap[s] = dmaps + 7 * l + s;
+      ph[0].w[s] = static_cast<const bf16*>(mats[s]);
+      ph[0].bias[s] = c.qkv_bias ? static_cast<const bf16*>(biases[s]) : nullptr;
+      ph[0].n[s] = seg_rows[s];
+      ph[0].tile_start[s] = tile;
+      ph[0].out_col[s] = col;
+      tile += tiles(seg_rows[s]);
+      col += seg_rows[s];
+    }
+    ph[0].tile_start[3] = tile;
+    ph[0].epi = EPI_STORE; ph[0].bmode = B_NORM; ph[0].gather = (l == 0);
+    ph[0].normw = static_cast<const bf16*>(lw.input_norm);
+    ph[0].src = hidden; ph[0].src_ld = c.hidden; ph[0].dst = qkv; ph[0].dst_ld = qkv_width(c);
+    // o_proj + residual
+    ph[1].nseg = 1; ph[1].nacc = 1; ph[1].k = q_size;
+    ph[1].tmap[0] = dmaps + 7 * l + 3; ph[1].w[0] = static_cast<const bf16*>(lw.o);
+    ph[1].n[0] = c.hidden; ph[1].tile_start[1] = tiles(c.hidden);
+    ph[1].epi = EPI_RESIDUAL; ph[1].bmode = B_PLAIN;
+    ph[1].src = attn; ph[1].src_ld = q_size; ph[1].dst = hidden; ph[1].dst_ld = c.hidden;
+    // gate, up -> silu(gate) * up
+    ph[2].nseg = 1; ph[2].nacc = 2; ph[2].k = c.hidden;
+    ph[2].tmap[0] = dmaps + 7 * l + 4; ph[2].tmap[1] = dmaps + 7 * l + 5;
+    ph[2].w[0] = static_cast<const bf16*>(lw.gate); ph[2].w[1] = static_cast<const bf16*>(lw.up);
+    ph[2].n[0] = c.intermediate; ph[2].n[1] = c.intermediate; ph[2].tile_start[1] = tiles(c.intermediate);
+    ph[2].epi = EPI_SILU; ph[2].bmode = B_NORM; ph[2].normw = static_cast<const bf16*>(lw.post_norm);
+    ph[2].src = hidden; ph[2].src_ld = c.hidden; ph[2].dst = act; ph[2].dst_ld = c.intermediate;
+    // down + residual
+    ph[3].nseg = 1; ph[3].nacc = 1; ph[3].k = c.intermediate;
+    ph[3].tmap[0] = dmaps + 7 * l + 6; ph[3].w[0] = static_cast<const bf16*>(lw.down);
+    ph[3].n[0] = c.hidden; ph[3].tile_start[1] = tiles(c.hidden);
+    ph[3].epi = EPI_RESIDUAL; ph[3].bmode = B_PLAIN;
+    ph[3].src = act; ph[3].src_ld = c.intermediate; ph[3].dst = hidden; ph[3].dst_ld = c.hidden;
+    for (int i = 0; i < 4; ++i) {
+      finish_phase(ph[i]);
+      static const char* names[4] = {"q/k/v projection", "o projection", "gate/up projection", "down projection"};
+      if (int e = check_phase_fits(ph[i], h->grid, names[i])) return e;
+    }
+  }
+  if (int e = encode_weight_map(&maps[7 * L], w->lm_head, c.vocab, c.hidden)) return e;
+  GemmPhase& head = phases[4 * L];
+  memset(&head, 0, sizeof(head));
+  head.nseg = 1; head.nacc = 1; head.k = c.hidden;
+  head.tmap[0] = dmaps + 7 * L; head.w[0] = static_cast<const bf16*>(w->lm_head);
+  head.n[0] = c.vocab; head.tile_start[1] = tiles(c.vocab);
+  head.epi = EPI_STORE; head.bmode = B_NORM; head.normw = static_cast<const bf16*>(w->final_norm);
+  head.src = hidden; head.src_ld = c.hidden; head.to_logits = 1; head.dst_ld = c.vocab;
+  finish_phase(head);
+  if (int e = check_phase_fits(head, h->grid, "lm_head")) return e;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  MK_CUDA(cudaMemcpyAsync(dmaps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, s));
+  MK_CUDA(cudaMemcpyAsync(at<GemmPhase>(h, h->cv.phases), phases.data(), phases.size() * sizeof(GemmPhase),
+                          cudaMemcpyHostToDevice, s));
+  // The source vectors die at return: make sure the copies have read them.
+  MK_CUDA(cudaStreamSynchronize(s));
+  h->layers.assign(w->layers, w->layers + L);
+  h->weights = *w;
+  h->weights.layers = h->layers.data();
+  h->bound = true;
+  return MK_OK;
+}
+
+int mk_decode(mk_handle h, const int64_t* ids, const int64_t* positions, int batch, void* const* key_caches,
+              void* const* value_caches, int32_t* const* valid_lengths, int capacity, void* logits, void* stream) {
+  if (!h || !ids || !positions || !key_caches || !value_caches || !valid_lengths || !logits)
+    return fail(MK_ERR_INVALID, "mk_decode: null argument");
+  std::lock_guard<std::mutex> guard(h->lock);
+  if (!h->bound) return fail(MK_ERR_UNBOUND, "mk_decode before mk_bind_weights");
+  if (batch < 1 || batch > h->cfg.max_tokens) return fail(MK_ERR_INVALID, "mk_decode: batch %d outside [1, %d]", batch, h->cfg.max_tokens);
+  if (capacity < 1) return fail(MK_ERR_INVALID, "mk_decode: capacity %d", capacity);
+  if (int e = attention_fits(h, capacity, "mk_decode")) return e;
+  KParams p;
+  base_params(h, p);
+  const int L = h->cfg.layers;
+  for (int l = 0; l < L; ++l) {
+    if (!key_caches[l] || !value_caches[l] || !valid_lengths[l]) return fail(MK_ERR_INVALID, "mk_decode: layer %d state is null", l);
+    if (reinterpret_cast<uintptr_t>(key_caches[l]) % 16 || reinterpret_cast<uintptr_t>(value_caches[l]) % 16)
+      return fail(MK_ERR_ALIGNMENT, "mk_decode: layer %d cache is not 16-byte aligned", l);
+    p.kc[l] = key_caches[l];
+    p.vc[l] = value_caches[l];
+    p.len[l] = valid_lengths[l];
+  }
+  const int ntt = token_tiles(batch);
+  p.mode = MODE_DECODE; p.m = batch; p.batch = batch; p.seq = 1; p.capacity = capacity;
+  p.n_gemm = 4 * L + 1;
+  p.nbar = 5 * L + tile_barriers(h, batch, 4 * L + 1);
+  p.stream_once = (ntt == 1);
+  p.ids = reinterpret_cast<const long long*>(ids);
+  p.pos = reinterpret_cast<const long long*>(positions);
+  p.logits = static_cast<bf16*>(logits);
+  return launch(h, p, stream);
+}
+
+int mk_prefill(mk_handle h, const int64_t* ids, const int64_t* positions, const void* mask, int batch, int sequence,
+               void* logits, void* stream) {
+  if (!h || !ids || !positions || !logits) return fail(MK_ERR_INVALID, "mk_prefill: null argument");
+  std::lock_guard<std::mutex> guard(h->lock);
+  if (!h->bound) return fail(MK_ERR_UNBOUND, "mk_prefill before mk_bind_weights");
+  const long long m = static_cast<long long>(batch) * sequence;
+  if (batch < 1 || sequence < 1 || m > h->cfg.max_tokens)
+    return fail(MK_ERR_INVALID, "mk_prefill: %d x %d tokens outside [1, %d]", batch, sequence, h->cfg.max_tokens);
+  if (int e = attention_fits(h, sequence, "mk_prefill")) return e;
+  const int gs = h->cfg.q_heads / h->cfg.kv_heads;
+  if (sequence > ((kScoreBytes / 4 / gs) & ~7))
+    return fail(MK_ERR_UNSUPPORTED, "mk_prefill: sequence %d exceeds the per-row score buffer", sequence);
+  KParams p;
+  base_params(h, p);
+  const int L = h->cfg.layers;
+  const int ntt = token_tiles(static_cast<int>(m));
+  p.mode = MODE_PREFILL; p.m = static_cast<int>(m); p.batch = batch; p.seq = sequence; p.capacity = 0;
+  p.n_gemm = 4 * L + 1;
+  p.nbar = 6 * L + tile_barriers(h, static_cast<int>(m), 4 * L + 1);
+  p.stream_once = (ntt == 1);
+  p.ids = reinterpret_cast<const long long*>(ids);
+  p.pos = reinterpret_cast<const long long*>(positions);
+  p.mask = static_cast<const bf16*>(mask);
+  p.logits = static_cast<bf16*>(logits);
+  return launch(h, p, stream);
+}
+
+int mk_linear(mk_handle h, const void* x, const void* weight, const void* bias, void* y, int m, int n, int k,
+              void* stream) {
+  if (!h || !x || !weight || !y) return fail(MK_ERR_INVALID, "mk_linear: null argument");
+  std::lock_guard<std::mutex> guard(h->lock);
+  if (m < 1 || m > h->cfg.max_tokens) return fail(MK_ERR_INVALID, "mk_linear: m %d outside [1, %d]", m, h->cfg.max_tokens);
+  if (n < 1 || k < 64 || k % 64) return fail(MK_ERR_UNSUPPORTED, "mk_linear: k must be a positive multiple of 64");
+  if ((n + kTileRows - 1) / kTileRows > h->cv.max_tiles)
+    return fail(MK_ERR_UNSUPPORTED, "mk_linear: n %d exceeds the %d tiles this handle's workspace covers", n, h->cv.max_tiles);
+  if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(y) % 2)
+    return fail(MK_ERR_ALIGNMENT, "mk_linear: x must be 16-byte aligned");
+  const size_t L = static_cast<size_t>(h->cfg.layers);
+  CUtensorMap map;
+  if (int e = encode_weight_map(&map, weight, n, k)) return e;
+  CUtensorMap* dmap = at<CUtensorMap>(h, h->cv.tmaps) + 7 * L + 1;
+  GemmPhase* dphase = at<GemmPhase>(h, h->cv.phases) + 4 * L + 1;
+  GemmPhase ph;
+  memset(&ph, 0, sizeof(ph));
+  ph.nseg = 1; ph.nacc = 1; ph.k = k;
+  ph.tmap[0] = dmap; ph.w[0] = static_cast<const bf16*>(weight); ph.bias[0] = static_cast<const bf16*>(bias);
+  ph.n[0] = n; ph.tile_start[1] = (n + kTileRows - 1) / kTileRows;
+  ph.epi = EPI_STORE; ph.bmode = B_PLAIN;
+  ph.src = static_cast<const bf16*>(x); ph.src_ld = k;
+  ph.dst = static_cast<bf16*>(y); ph.dst_ld = n;
+  finish_phase(ph);
+  if (int e = check_phase_fits(ph, h->grid, "mk_linear")) return e;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  MK_CUDA(cudaMemcpyAsync(dmap, &map, sizeof(map), cudaMemcpyHostToDevice, s));
+  MK_CUDA(cudaMemcpyAsync(dphase, &ph, sizeof(ph), cudaMemcpyHostToDevice, s));
+  MK_CUDA(cudaStreamSynchronize(s));
+  KParams p;
+  base_params(h, p);
+  const int ntt = token_tiles(m);
+  p.phases = dphase;
+  p.mode = MODE_LINEAR; p.m = m; p.batch = m; p.seq = 1;
+  p.n_gemm = 1;
+  p.nbar = tile_barriers(h, m, 1);
+  p.stream_once = (ntt == 1);
+  return launch(h, p, stream);
+}
+
+int mk_kv_attention(mk_handle h, const void* query, const void* key, const void* value, void* key_cache,
+                    void* value_cache, int32_t* valid_length, int batch, int capacity, void* output, void* stream) {
+  if (!h || !query || !key || !value || !key_cache || !value_cache || !valid_length || !output)
+    return fail(MK_ERR_INVALID, "mk_kv_attention: null argument");
+  std::lock_guard<std::mutex> guard(h->lock);
+  if (batch < 1 || batch > h->cfg.max_tokens) return fail(MK_ERR_INVALID, "mk_kv_attention: batch %d outside [1, %d]", batch, h->cfg.max_tokens);
+  if (int e = attention_fits(h, capacity, "mk_kv_attention")) return e;
+  if (reinterpret_cast<uintptr_t>(key_cache) % 16 || reinterpret_cast<uintptr_t>(value_cache) % 16)
+    return fail(MK_ERR_ALIGNMENT, "mk_kv_attention: caches must be 16-byte aligned");
+  KParams p;
+  base_params(h, p);
+  p.mode = MODE_KVATT; p.m = batch; p.batch = batch; p.seq = 1; p.capacity = capacity;
+  p.n_gemm = 0; p.nbar = 1;
+  p.op_q = static_cast<const bf16*>(query); p.op_k = static_cast<const bf16*>(key); p.op_v = static_cast<const bf16*>(value);
+  p.op_out = static_cast<bf16*>(output);
+  p.kc[0] = key_cache; p.vc[0] = value_cache; p.len[0] = valid_length;
+  return launch(h, p, stream);
+}
+
+int mk_attention(mk_handle h, const void* query, const void* key, const void* value, const void* mask, float scale,
+                 int batch, int q_len, int k_len, void* output, void* stream) {
+  if (!h || !query || !key || !value || !output) return fail(MK_ERR_INVALID, "mk_attention: null argument");
+  std::lock_guard<std::mutex> guard(h->lock);
+  if (batch < 1 || q_len < 1 || k_len < 1) return fail(MK_ERR_INVALID, "mk_attention: sizes must be positive");
+  const int gs = h->cfg.q_heads / h->cfg.kv_heads;
+  if (k_len > ((kScoreBytes / 4 / gs) & ~7))
+    return fail(MK_ERR_UNSUPPORTED, "mk_attention: %d keys exceed the per-row score buffer", k_len);
+  if (reinterpret_cast<uintptr_t>(key) % 16 || reinterpret_cast<uintptr_t>(value) % 16)
+    return fail(MK_ERR_ALIGNMENT, "mk_attention: key/value must be 16-byte aligned");
+  KParams p;
+  base_params(h, p);
+  p.mode = MODE_ATT; p.m = batch * q_len; p.batch = batch; p.seq = q_len;
+  p.n_gemm = 0; p.nbar = 0;
+  p.att_scale = scale;
+  p.op_q = static_cast<const bf16*>(query); p.op_k = static_cast<const bf16*>(key); p.op_v = static_cast<const bf16*>(value);
+  p.op_out = static_cast<bf16*>(output);
+  p.mask = static_cast<const bf16*>(mask);
+  p.op_qlen = q_len; p.op_klen = k_len;
+  return launch(h, p, stream);
+}
+
+int mk_status(mk_handle h, void* stream, mk_status_info* out) {
+  if (!h) return fail(MK_ERR_INVALID, "mk_status: null handle");
+  std::lock_guard<std::mutex> guard(h->lock);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  MK_CUDA(cudaStreamSynchronize(s));
+  Control c;
+  MK_CUDA(cudaMemcpy(&c, at<Control>(h, h->cv.ctrl), sizeof(c), cudaMemcpyDeviceToHost));
+  if (out) {
+    out->status = c.status; out->where = c.where; out->cta = c.cta; out->detail = c.detail;
+  }
+  if (c.status != MK_STATUS_OK || c.abort) {
+    // Counters are in an unknown state after an aborted launch: start over.
+    MK_CUDA(cudaMemset(at<Control>(h, h->cv.ctrl), 0, sizeof(Control)));
+    MK_CUDA(cudaMemset(at<uint32_t>(h, h->cv.tile_ctr), 0, static_cast<size_t>(h->cv.max_tiles) * 4));
+    MK_CUDA(cudaMemset(at<uint32_t>(h, h->cv.att_ctr), 0, static_cast<size_t>(h->cfg.max_tokens) * h->cfg.kv_heads * 16));
+    h->epoch = 0;
+    return fail(MK_ERR_DEVICE_STATUS, "device status %d at site %d (cta %d, detail %d)", c.status, c.where, c.cta, c.detail);
+  }
+  return MK_OK;
+}
+
+int mk_launch_info(mk_handle h, int32_t* ctas, int32_t* smem_bytes, int64_t* launches) {
+  if (!h) return fail(MK_ERR_INVALID, "mk_launch_info: null handle");
+  if (ctas) *ctas = h->grid;
+  if (smem_bytes) *smem_bytes = kSmemBytes;
+  if (launches) *launches = h->launches;
+  return MK_OK;
+}
+
+}  // extern "C"

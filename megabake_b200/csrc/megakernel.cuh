@@ -1,0 +1,111 @@
+// Device-side data structures shared by the megakernel and its host launcher.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include "../../include/megabake_b200.h"
+
+namespace mk {
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int kThreads = 192;            // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: workers
+constexpr int kWorkers = 128;
+constexpr int kWorkerWarps = 4;
+constexpr int kStages = 9;               // weight ring depth
+constexpr int kTileRows = 128;           // weight rows per MMA (UMMA M)
+constexpr int kChunkK = 64;              // K elements per ring stage (128 B of bf16 = one swizzle row)
+constexpr int kStageBytes = kTileRows * kChunkK * 2;  // 16 KiB
+constexpr int kTok = MK_TOKEN_TILE;      // tokens per MMA (UMMA N)
+constexpr int kBSlots = 32;              // activation K-chunks resident per CTA
+constexpr int kBSlotBytes = kTok * 128;  // 2 KiB
+constexpr int kBBytes = kBSlots * kBSlotBytes;
+constexpr int kTmemCols = 64;            // 2 buffers x 2 accumulators x 16 columns
+constexpr int kMiscBytes = 1024;
+constexpr int kSmemBytes = 1024 /*alignment slack*/ + kStages * kStageBytes + kBBytes + kMiscBytes;
+constexpr int kMaxChunks = 16;           // split-context chunks per (sequence, kv head)
+constexpr int kScoreBytes = 40960;       // fp32 scores of one attention unit (inside the B region)
+constexpr int kPartialFloats = 2 * kTok * kTileRows;  // one split-K partial: [acc][token][row]
+
+static_assert(kSmemBytes <= 232448, "dynamic shared memory exceeds 227 KiB");
+
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU = 2 };
+enum { B_PLAIN = 0, B_NORM = 1 };
+enum { MODE_DECODE = 0, MODE_PREFILL = 1, MODE_LINEAR = 2, MODE_KVATT = 3, MODE_ATT = 4 };
+enum {
+  SITE_PRODUCER_EMPTY = 1, SITE_MMA_FULL = 2, SITE_MMA_B = 3, SITE_MMA_ACC = 4, SITE_EPI_ACC = 5,
+  SITE_GRID_BARRIER = 6, SITE_ATT_EXCHANGE = 7, SITE_DRAIN = 8, SITE_PROLOGUE = 9
+};
+
+// One projection phase: up to three weight matrices sharing the same activation
+// operand (q,k,v), or a gate/up pair accumulated side by side (nacc == 2).
+struct GemmPhase {
+  const CUtensorMap* tmap[3];  // device copies of the TMA descriptors
+  const bf16* w[3];            // raw weight pointers [N, K]
+  const bf16* bias[3];
+  int n[3];                    // rows of each matrix
+  int tile_start[4];           // first 128-row tile of each matrix, then the total
+  int out_col[3];              // column of each matrix's rows in the output buffer
+  int nseg, nacc;
+  int k, kc;                   // reduction length, in elements and in 64-element chunks
+  int tc;                      // chunks per tile = kc * nacc
+  int ntiles;
+  long long total;             // chunks in the phase = ntiles * tc
+  int epi, bmode;
+  int gather;                  // 1: activation rows are embedding rows selected by the token ids
+  int to_logits;               // 1: output goes to the caller's logits buffer
+  const bf16* normw;
+  const bf16* src; int src_ld;
+  bf16* dst; int dst_ld;
+};
+
+struct Control {
+  uint32_t barrier;   // monotonic grid-barrier counter
+  uint32_t abort;     // set once by whoever gives up a wait; every wait polls it
+  int status;         // mk_device_status
+  int where, cta, detail;
+  uint32_t pad[2];
+};
+
+struct KParams {
+  int hidden, layers, q_heads, kv_heads, head_dim, inter, vocab;
+  float eps;
+  int rope_style, prefill_rope_style;
+  float att_scale;    // head_dim ** -0.5 rounded to fp32 on the host
+  int mode;
+  int m;              // tokens in this launch
+  int batch, seq;
+  int capacity;
+  int engine;
+  int n_gemm;         // projection phases in this launch
+  int nbar;           // grid barriers a CTA passes in this launch
+  uint32_t epoch;     // barrier counter value when this launch starts
+  int qkv_ld;
+  int max_positions;
+  int stream_once;    // 1: weights are read once per launch (L2 evict-first)
+  int debug_stop;     // bring-up aid: leave the schedule after this many steps (0 = run everything)
+  long long timeout_cycles;
+  const GemmPhase* phases;
+  bf16 *hidden_buf, *qkv, *attn, *act;
+  float* partials;
+  uint32_t* tile_ctr;
+  float *att_max, *att_sum, *att_part;
+  uint32_t* att_ctr;
+  Control* ctrl;
+  const long long* ids;
+  const long long* pos;
+  const bf16* mask;
+  const bf16 *embed, *cos_t, *sin_t;
+  bf16* logits;
+  // stand-alone attention ops
+  const bf16 *op_q, *op_k, *op_v;
+  bf16* op_out;
+  float op_scale;
+  int op_qlen, op_klen;
+  void* kc[MK_MAX_LAYERS];
+  void* vc[MK_MAX_LAYERS];
+  int* len[MK_MAX_LAYERS];
+};
+
+}  // namespace mk
