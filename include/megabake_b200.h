@@ -172,6 +172,15 @@ int mk_attention(mk_handle handle, const void* query, const void* key, const voi
  * Reference: none (the reference traps and loses the context). */
 int mk_status(mk_handle handle, void* stream, mk_status_info* out);
 
+/* Event trace for the next launches: `buffer` is device memory of
+ * ctas * events_per_cta * 8 bytes (NULL turns tracing off).  Worker thread 0 of
+ * every CTA appends (event code << 56) | globaltimer-ns at phase entry, operand
+ * staged, first accumulator ready, phase done, barrier passed, attention done;
+ * a launch restarts each CTA's list at 0.
+ * Reference: MEGABAKE_PHASE_TIMER stamps, src/megabake/runtime.py:27-46 and
+ * src/megabake/codegen.py:1723-1751. */
+int mk_set_trace(mk_handle handle, void* buffer, int events_per_cta);
+
 /* Number of CTAs each launch uses, bytes of dynamic shared memory, kernels launched so far. */
 int mk_launch_info(mk_handle handle, int32_t* ctas, int32_t* smem_bytes, int64_t* launches);
 

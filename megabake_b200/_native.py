@@ -27,7 +27,7 @@ ENGINES = {"tcgen05": 0, "simt": 1}
 
 EXPORTS = (
     "mk_workspace_bytes", "mk_create", "mk_bind_weights", "mk_decode", "mk_prefill", "mk_linear",
-    "mk_kv_attention", "mk_attention", "mk_status", "mk_launch_info", "mk_last_error", "mk_destroy",
+    "mk_kv_attention", "mk_attention", "mk_status", "mk_set_trace", "mk_launch_info", "mk_last_error", "mk_destroy",
 )
 
 
@@ -103,6 +103,8 @@ def load() -> ctypes.CDLL:
     ]
     lib.mk_status.restype = c_int
     lib.mk_status.argtypes = [c_void_p, c_void_p, POINTER(MkStatusInfo)]
+    lib.mk_set_trace.restype = c_int
+    lib.mk_set_trace.argtypes = [c_void_p, c_void_p, c_int]
     lib.mk_launch_info.restype = c_int
     lib.mk_launch_info.argtypes = [c_void_p, POINTER(c_int32), POINTER(c_int32), POINTER(c_int64)]
     lib.mk_last_error.restype = c_char_p

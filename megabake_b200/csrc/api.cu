@@ -143,6 +143,8 @@ struct mk_handle_s {
   int64_t launches;
   long long timeout_cycles;
   float att_scale;
+  unsigned long long* trace;
+  int trace_cap;
   std::mutex lock;
 };
 
@@ -184,6 +186,8 @@ void base_params(mk_handle h, KParams& p) {
   p.max_positions = c.max_positions;
   p.timeout_cycles = h->timeout_cycles;
   if (const char* env = getenv("MEGABAKE_DEBUG_STOP")) p.debug_stop = atoi(env);
+  p.trace = h->trace;
+  p.trace_cap = h->trace ? h->trace_cap : 0;
   p.phases = at<GemmPhase>(h, h->cv.phases);
   p.hidden_buf = at<bf16>(h, h->cv.hidden);
   p.qkv = at<bf16>(h, h->cv.qkv);
@@ -270,6 +274,8 @@ int mk_create(const mk_config* config, void* workspace, size_t workspace_bytes, 
   h->bound = false;
   h->epoch = 0;
   h->launches = 0;
+  h->trace = nullptr;
+  h->trace_cap = 0;
   double ms = 2000.0;
   if (const char* env = getenv("MEGABAKE_WAIT_LIMIT_MS")) ms = atof(env) > 0 ? atof(env) : ms;
   h->timeout_cycles = static_cast<long long>(ms * static_cast<double>(khz));
@@ -542,6 +548,15 @@ int mk_status(mk_handle h, void* stream, mk_status_info* out) {
     h->epoch = 0;
     return fail(MK_ERR_DEVICE_STATUS, "device status %d at site %d (cta %d, detail %d)", c.status, c.where, c.cta, c.detail);
   }
+  return MK_OK;
+}
+
+int mk_set_trace(mk_handle h, void* buffer, int events_per_cta) {
+  if (!h) return fail(MK_ERR_INVALID, "mk_set_trace: null handle");
+  if (buffer && events_per_cta < 1) return fail(MK_ERR_INVALID, "mk_set_trace: events_per_cta must be positive");
+  std::lock_guard<std::mutex> guard(h->lock);
+  h->trace = static_cast<unsigned long long*>(buffer);
+  h->trace_cap = buffer ? events_per_cta : 0;
   return MK_OK;
 }
 

@@ -40,7 +40,7 @@ struct SmemMisc {
   int bad;     // prologue validation result
   int flag;    // "this CTA reduces / finishes" decisions taken by worker thread 0
   float rinv[kTok];
-  float xch[16];
+  int trace_n;  // events this CTA has recorded
 };
 static_assert(sizeof(SmemMisc) <= kMiscBytes, "misc shared block too large");
 
@@ -77,6 +77,19 @@ __device__ __noinline__ bool give_up(const Ctx& cx, int site, int detail) {
   return false;
 }
 
+// Optional per-CTA event trace (worker thread 0 only): what the reference's
+// MEGABAKE_PHASE_TIMER stamps give (src/megabake/runtime.py:27-46).
+__device__ __forceinline__ void trace_event(const Ctx& cx, int wtid, int code) {
+  if (cx.p->trace_cap == 0 || wtid != 0) return;
+  const int n = cx.misc->trace_n;
+  if (n >= cx.p->trace_cap) return;
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  cx.p->trace[static_cast<size_t>(cx.cta) * cx.p->trace_cap + n] =
+      (static_cast<unsigned long long>(code) << 56) | (t & 0x00FFFFFFFFFFFFFFull);
+  cx.misc->trace_n = n + 1;
+}
+
 __device__ __forceinline__ bool wait_mbar(const Ctx& cx, uint32_t bar, uint32_t parity, int site, int detail) {
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
@@ -92,23 +105,25 @@ __device__ __forceinline__ bool workers_ok(const Ctx& cx, bool ok) {
   return *reinterpret_cast<volatile int*>(&cx.misc->wabort) == 0;
 }
 
-// Monotonic-counter grid barrier over the worker warps of every CTA.
+// Monotonic-counter grid barrier over the worker warps of every CTA: one
+// release-add to arrive, relaxed polling, one fence once the count is reached.
 __device__ bool grid_barrier(const Ctx& cx, uint32_t& passed, int wtid) {
   named_bar_sync(1, kWorkers);
   passed += 1;
   if (wtid == 0) {
-    __threadfence();
     red_release_add_u32(&cx.ctrl->barrier, 1u);
     const uint32_t target = cx.p->epoch + passed * static_cast<uint32_t>(cx.grid);
     uint32_t spins = 0;
-    while (static_cast<int32_t>(ld_acquire_u32(&cx.ctrl->barrier) - target) < 0) {
-      if ((++spins & 63u) == 0 && give_up(cx, SITE_GRID_BARRIER, static_cast<int>(passed))) {
+    while (static_cast<int32_t>(ld_relaxed_u32(&cx.ctrl->barrier) - target) < 0) {
+      if ((++spins & 255u) == 0 && give_up(cx, SITE_GRID_BARRIER, static_cast<int>(passed))) {
         cx.misc->wabort = 1;
         break;
       }
     }
+    __threadfence();
   }
   named_bar_sync(1, kWorkers);
+  trace_event(cx, wtid, EV_BARRIER_DONE);
   return *reinterpret_cast<volatile int*>(&cx.misc->wabort) == 0;
 }
 
@@ -141,7 +156,7 @@ __device__ __forceinline__ int segment_of_tile(const GemmPhase* ph, int tile) {
 // ---------------------------------------------------------------------------
 // warp 0: weight producer
 
-__device__ void producer_loop(const Ctx& cx) {
+__device__ __noinline__ void producer_loop(const Ctx& cx) {
   const KParams& p = *cx.p;
   const uint64_t policy = p.stream_once ? l2_policy_evict_first() : l2_policy_evict_normal();
   const int ntt = (p.m + kTok - 1) / kTok;
@@ -198,7 +213,7 @@ __device__ void producer_loop(const Ctx& cx) {
 // ---------------------------------------------------------------------------
 // warp 1: MMA issuer
 
-__device__ void mma_loop(const Ctx& cx) {
+__device__ __noinline__ void mma_loop(const Ctx& cx) {
   const KParams& p = *cx.p;
   const int ntt = (p.m + kTok - 1) / kTok;
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&cx.misc->tmem_base);
@@ -276,35 +291,44 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
-__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 t = __bfloat1622float2(h[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
-  }
+// bf16 -> fp32 is a 16-bit shift; keeping it in integer registers avoids taking addresses.
+__device__ __forceinline__ void unpack8(const uint4 u, float* f) {
+  f[0] = __uint_as_float(u.x << 16); f[1] = __uint_as_float(u.x & 0xFFFF0000u);
+  f[2] = __uint_as_float(u.y << 16); f[3] = __uint_as_float(u.y & 0xFFFF0000u);
+  f[4] = __uint_as_float(u.z << 16); f[5] = __uint_as_float(u.z & 0xFFFF0000u);
+  f[6] = __uint_as_float(u.w << 16); f[7] = __uint_as_float(u.w & 0xFFFF0000u);
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return static_cast<uint32_t>(__bfloat16_as_ushort(h.x)) | (static_cast<uint32_t>(__bfloat16_as_ushort(h.y)) << 16);
 }
 __device__ __forceinline__ uint4 pack8(const float* f) {
-  uint4 u;
-  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-  return u;
+  return make_uint4(pack2(f[0], f[1]), pack2(f[2], f[3]), pack2(f[4], f[5]), pack2(f[6], f[7]));
 }
 
 // RMSNorm statistics of the rows of one token tile: rinv[t] = 1/sqrt(mean(x^2)+eps).
-__device__ void norm_stats(const Ctx& cx, const GemmPhase* ph, int t0, int mt, int wtid) {
+// One warp per token; eight 16-byte loads are in flight per lane before any is used.
+__device__ __noinline__ void norm_stats(const Ctx& cx, const GemmPhase* ph, int t0, int mt, int wtid) {
   const KParams& p = *cx.p;
   const int warp = wtid >> 5, lane = wtid & 31;
+  const int nvec = p.hidden / 8;
   for (int t = warp; t < mt; t += kWorkerWarps) {
     const uint4* row = reinterpret_cast<const uint4*>(activation_row(p, ph, t0 + t));
     float sum = 0.f;
-    for (int v = lane; v < p.hidden / 8; v += 32) {
-      float f[8];
-      unpack8(__ldcg(row + v), f);
+    for (int v0 = 0; v0 < nvec; v0 += 32 * 8) {
+      uint4 u[8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) sum = fmaf(f[e], f[e], sum);
+      for (int i = 0; i < 8; ++i) {
+        const int v = v0 + i * 32 + lane;
+        u[i] = v < nvec ? __ldcg(row + v) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float f[8];
+        unpack8(u[i], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sum = fmaf(f[e], f[e], sum);
+      }
     }
     sum = warp_sum(sum);
     if (lane == 0) cx.misc->rinv[t] = 1.0f / sqrtf(sum / static_cast<float>(p.hidden) + p.eps);
@@ -312,40 +336,65 @@ __device__ void norm_stats(const Ctx& cx, const GemmPhase* ph, int t0, int mt, i
   named_bar_sync(1, kWorkers);
 }
 
-// One 8-element vector of the activation operand (normalised if the phase asks).
-__device__ __forceinline__ uint4 activation_vec(const Ctx& cx, const GemmPhase* ph, const bf16* row, int t, int col) {
-  uint4 u = __ldcg(reinterpret_cast<const uint4*>(row + col));
-  if (ph->bmode == B_NORM) {
-    float x[8], w[8];
-    unpack8(u, x);
-    unpack8(__ldg(reinterpret_cast<const uint4*>(ph->normw + col)), w);
-    const float r = cx.misc->rinv[t];
+// Normalise one 8-element vector: w * bf16(x * rinv), the two roundings of the
+// Hugging Face RMSNorm.
+__device__ __forceinline__ uint4 normalise_vec(const uint4& xu, const uint4& wu, float r) {
+  float x[8], w[8];
+  unpack8(xu, x);
+  unpack8(wu, w);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) x[e] = w[e] * bf16_round(x[e] * r);
-    u = pack8(x);
-  }
-  return u;
+  for (int e = 0; e < 8; ++e) x[e] = w[e] * bf16_round(x[e] * r);
+  return pack8(x);
 }
 
-// Fill the swizzled (SWIZZLE_128B, K-major) activation slots this CTA's chunk range needs.
-__device__ void stage_b(const Ctx& cx, const GemmPhase* ph, const Range& r, int t0, int mt, int wtid) {
+// One 8-element vector of the activation operand (normalised if the phase asks).
+__device__ __forceinline__ uint4 activation_vec(const Ctx& cx, const GemmPhase* ph, const bf16* row, int t, int col) {
+  const uint4 u = __ldcg(reinterpret_cast<const uint4*>(row + col));
+  if (ph->bmode != B_NORM) return u;
+  return normalise_vec(u, __ldg(reinterpret_cast<const uint4*>(ph->normw + col)), cx.misc->rinv[t]);
+}
+
+// Fill the swizzled (SWIZZLE_128B, K-major) activation slots this CTA's chunk
+// range needs.  Loads are issued four at a time per thread before any is used.
+__device__ __noinline__ void stage_b(const Ctx& cx, const GemmPhase* ph, const Range& r, int t0, int mt, int wtid) {
   const KParams& p = *cx.p;
-  if (ph->bmode == B_NORM) norm_stats(cx, ph, t0, mt, wtid);
+  const bool norm = ph->bmode == B_NORM;
+  if (norm) norm_stats(cx, ph, t0, mt, wtid);
   const int nacc = ph->nacc, kc = ph->kc;
   const long long ks0 = r.c0 / nacc;
   const long long ks1 = (r.c1 + nacc - 1) / nacc;
   const bool all_k = (ks1 - ks0) >= kc;
   const int nk = all_k ? kc : static_cast<int>(ks1 - ks0);
   const int per_slot = mt * 8;
-  for (int item = wtid; item < nk * per_slot; item += kWorkers) {
-    const int slot = item / per_slot;
-    const int rem = item - slot * per_slot;
-    const int t = rem >> 3, v = rem & 7;
-    const int kidx = all_k ? slot : static_cast<int>((ks0 + slot) % kc);
-    const bf16* row = activation_row(p, ph, t0 + t);
-    const uint4 u = activation_vec(cx, ph, row, t, kidx * kChunkK + v * 8);
-    uint8_t* dst = cx.smem_b + slot * kBSlotBytes + (t >> 3) * 1024 + (t & 7) * 128 + ((v ^ (t & 7)) << 4);
-    *reinterpret_cast<uint4*>(dst) = u;
+  const int items = nk * per_slot;
+  const bf16* normw = ph->normw;
+  for (int item0 = wtid; item0 < items; item0 += kWorkers * 4) {
+    uint4 xu[4], wu[4];
+    int slot[4], tok[4], vec[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int item = item0 + i * kWorkers;
+      if (item < items) {
+        slot[i] = item / per_slot;
+        const int rem = item - slot[i] * per_slot;
+        tok[i] = rem >> 3;
+        vec[i] = rem & 7;
+        const int kidx = all_k ? slot[i] : static_cast<int>((ks0 + slot[i]) % kc);
+        const int col = kidx * kChunkK + vec[i] * 8;
+        xu[i] = __ldcg(reinterpret_cast<const uint4*>(activation_row(p, ph, t0 + tok[i]) + col));
+        if (norm) wu[i] = __ldg(reinterpret_cast<const uint4*>(normw + col));
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int item = item0 + i * kWorkers;
+      if (item < items) {
+        const uint4 u = norm ? normalise_vec(xu[i], wu[i], cx.misc->rinv[tok[i]]) : xu[i];
+        uint8_t* dst = cx.smem_b + slot[i] * kBSlotBytes + (tok[i] >> 3) * 1024 + (tok[i] & 7) * 128 +
+                       ((vec[i] ^ (tok[i] & 7)) << 4);
+        *reinterpret_cast<uint4*>(dst) = u;
+      }
+    }
   }
   fence_proxy_async_smem();
   mbar_arrive(smem_u32(&cx.misc->bfull));
@@ -389,38 +438,67 @@ __device__ void apply_epilogue(const Ctx& cx, const GemmPhase* ph, int tile, int
   }
 }
 
-// Split-K completion for one tile segment: store this CTA's partial, count the
-// arrival, and let the last arriver sum every partial in CTA order.
-__device__ void finish_split(const Ctx& cx, const GemmPhase* ph, const Range& r, int tile, int rloc,
+// Split-K completion for one tile segment.  The CTA that holds the tile's first
+// chunk reduces: for it the tile is the last segment of its range, so by then
+// the other contributors (for which the tile comes first) have published their
+// fp32 partials.  Contributors store, fence, count themselves and move on; the
+// reducer waits (bounded) for the count, then adds the partials to its own
+// accumulators in CTA order, which fixes the summation order.
+__device__ __noinline__ bool finish_split(const Ctx& cx, const GemmPhase* ph, const Range& r, int tile, int rloc,
                              float (*v)[kTok], int t0, int mt, int wtid) {
   const KParams& p = *cx.p;
   const int tc = ph->tc, nacc = ph->nacc;
-  const int slot = (static_cast<int>(r.c0 / tc) == tile) ? 0 : 1;
-  float* mine = p.partials + static_cast<size_t>(cx.cta * 2 + slot) * kPartialFloats;
-  for (int a = 0; a < nacc; ++a)
-    for (int t = 0; t < mt; ++t) __stcg(mine + (a * kTok + t) * kTileRows + rloc, v[a][t]);
-  __threadfence();
-  named_bar_sync(1, kWorkers);
-  const int first = cta_of_chunk(static_cast<long long>(tile) * tc, ph->total, r.geff);
-  const int last = cta_of_chunk(static_cast<long long>(tile + 1) * tc - 1, ph->total, r.geff);
+  const long long total = ph->total;
+  const int first = cta_of_chunk(static_cast<long long>(tile) * tc, total, r.geff);
+  const int last = cta_of_chunk(static_cast<long long>(tile + 1) * tc - 1, total, r.geff);
+  if (cx.cta != first) {
+    const int slot = (static_cast<int>(r.c0 / tc) == tile) ? 0 : 1;
+    float* mine = p.partials + static_cast<size_t>(cx.cta * 2 + slot) * kPartialFloats;
+    for (int a = 0; a < nacc; ++a)
+      for (int t = 0; t < mt; ++t) __stcg(mine + (a * kTok + t) * kTileRows + rloc, v[a][t]);
+    __threadfence();
+    named_bar_sync(1, kWorkers);
+    if (wtid == 0) red_release_add_u32(&p.tile_ctr[tile], 1u);
+    return true;
+  }
   if (wtid == 0) {
-    const uint32_t old = atomicAdd(&p.tile_ctr[tile], 1u);
-    const int is_last = (old == static_cast<uint32_t>(last - first));
-    if (is_last) p.tile_ctr[tile] = 0;  // next use is behind a grid barrier
-    cx.misc->flag = is_last;
+    const uint32_t expected = static_cast<uint32_t>(last - first);
+    uint32_t spins = 0;
+    while (ld_relaxed_u32(&p.tile_ctr[tile]) < expected) {
+      if ((++spins & 255u) == 0 && give_up(cx, SITE_SPLIT_REDUCE, tile)) {
+        cx.misc->wabort = 1;
+        break;
+      }
+    }
+    p.tile_ctr[tile] = 0;  // the next use is behind a grid barrier
+    __threadfence();
   }
   named_bar_sync(1, kWorkers);
-  if (*reinterpret_cast<volatile int*>(&cx.misc->flag) == 0) return;
-  __threadfence();
-  for (int a = 0; a < nacc; ++a)
-    for (int t = 0; t < mt; ++t) v[a][t] = 0.f;
-  for (int g = first; g <= last; ++g) {
-    const int gslot = (static_cast<int>((g * ph->total / r.geff) / tc) == tile) ? 0 : 1;
-    const float* theirs = p.partials + static_cast<size_t>(g * 2 + gslot) * kPartialFloats;
-    for (int a = 0; a < nacc; ++a)
-      for (int t = 0; t < mt; ++t) v[a][t] += __ldcg(theirs + (a * kTok + t) * kTileRows + rloc);
+  if (*reinterpret_cast<volatile int*>(&cx.misc->wabort)) return false;
+  for (int g0 = first + 1; g0 <= last; g0 += 4) {
+    float part[4][2];
+    for (int t = 0; t < mt; ++t) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int g = g0 + i;
+        if (g <= last) {
+          const int gslot = (static_cast<int>((g * total / r.geff) / tc) == tile) ? 0 : 1;
+          const float* theirs = p.partials + static_cast<size_t>(g * 2 + gslot) * kPartialFloats;
+          part[i][0] = __ldcg(theirs + t * kTileRows + rloc);
+          if (nacc == 2) part[i][1] = __ldcg(theirs + (kTok + t) * kTileRows + rloc);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (g0 + i <= last) {
+          v[0][t] += part[i][0];
+          if (nacc == 2) v[1][t] += part[i][1];
+        }
+      }
+    }
   }
   apply_epilogue(cx, ph, tile, rloc, v, t0, mt);
+  return true;
 }
 
 // Projection phase on the tcgen05 engine, worker side.
@@ -439,7 +517,9 @@ __device__ bool worker_gemm_tc(const Ctx& cx, int gp, uint32_t& q, uint32_t& pas
     if (r.c1 <= r.c0) continue;
     const int t0 = tt * kTok;
     const int mt = min(kTok, p.m - t0);
+    trace_event(cx, wtid, EV_PHASE_ENTER);
     stage_b(cx, ph, r, t0, mt, wtid);
+    trace_event(cx, wtid, EV_B_STAGED);
     long long c = r.c0;
     while (c < r.c1) {
       const int tile = static_cast<int>(c / tc);
@@ -450,6 +530,7 @@ __device__ bool worker_gemm_tc(const Ctx& cx, int gp, uint32_t& q, uint32_t& pas
       const uint32_t buf = q & 1u;
       bool ok = wait_mbar(cx, smem_u32(&cx.misc->accfull[buf]), (q >> 1) & 1u, SITE_EPI_ACC, gp);
       ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below needs the whole warp
+      if (c == r.c0) trace_event(cx, wtid, EV_FIRST_ACC);
       tc_fence_after();
       float v[2][kTok];
       if (ok) {
@@ -470,17 +551,18 @@ __device__ bool worker_gemm_tc(const Ctx& cx, int gp, uint32_t& q, uint32_t& pas
       if (complete) {
         apply_epilogue(cx, ph, tile, rloc, v, t0, mt);
       } else {
-        finish_split(cx, ph, r, tile, rloc, v, t0, mt, wtid);
+        if (!finish_split(cx, ph, r, tile, rloc, v, t0, mt, wtid)) return false;
       }
       c = seg_end;
     }
+    trace_event(cx, wtid, EV_PHASE_DONE);
   }
   return true;
 }
 
 // Projection phase on the SIMT engine (bring-up / diagnostics): every worker
 // warp of the grid takes output rows round-robin and does plain dot products.
-__device__ bool worker_gemm_simt(const Ctx& cx, int gp, uint32_t& passed, int wtid) {
+__device__ __noinline__ bool worker_gemm_simt(const Ctx& cx, int gp, uint32_t& passed, int wtid) {
   const KParams& p = *cx.p;
   const GemmPhase* ph = p.phases + gp;
   const int warp = wtid >> 5, lane = wtid & 31;
@@ -568,15 +650,15 @@ __device__ bool attn_exchange(const Ctx& cx, float* slots, uint32_t* counter, in
   if (wtid == 0) {
     red_release_add_u32(counter, 1u);
     uint32_t spins = 0;
-    while (ld_acquire_u32(counter) < static_cast<uint32_t>(nch)) {
-      if ((++spins & 63u) == 0 && give_up(cx, SITE_ATT_EXCHANGE, rowg)) {
+    while (ld_relaxed_u32(counter) < static_cast<uint32_t>(nch)) {
+      if ((++spins & 255u) == 0 && give_up(cx, SITE_ATT_EXCHANGE, rowg)) {
         cx.misc->wabort = 1;
         break;
       }
     }
+    __threadfence();
   }
   named_bar_sync(1, kWorkers);
-  __threadfence();
   return *reinterpret_cast<volatile int*>(&cx.misc->wabort) == 0;
 }
 
@@ -603,7 +685,7 @@ __device__ __forceinline__ float ldcg_bf16(const bf16* ptr) {
 //   decode  (kv_attention): score = bf16(q.k) * scale in fp32
 //   prefill (attention):    score = bf16(bf16(q.k) * scale) (+ mask, rounded again)
 // then fp32 softmax, probability rounded to bf16, fp32 value sum rounded once.
-__device__ bool attention_phase(const Ctx& cx, const AttnArgs& A, int wtid) {
+__device__ __noinline__ bool attention_phase(const Ctx& cx, const AttnArgs& A, int wtid) {
   const KParams& p = *cx.p;
   const int hd = p.head_dim, half = hd / 2;
   const int gs = p.q_heads / p.kv_heads;
@@ -690,29 +772,40 @@ __device__ bool attention_phase(const Ctx& cx, const AttnArgs& A, int wtid) {
     }
     const bf16* mrow = A.mask ? A.mask + (static_cast<long long>(b) * A.sq + qi) * A.klen : nullptr;
 
-    // --- scores
-    for (int base = j0 + warp * kpw; base < j1; base += kWorkerWarps * kpw) {
-      const int j = base + sub;
-      uint4 ku = make_uint4(0, 0, 0, 0);
-      if (j < j1) {
-        if (j == newpos) ku = *reinterpret_cast<const uint4*>(kn + dg * 8);
-        else ku = __ldcg(reinterpret_cast<const uint4*>(kbase + static_cast<long long>(j) * A.kv_ld) + dg);
-      }
-      float kf[8];
-      unpack8(ku, kf);
-      for (int g = 0; g < gs; ++g) {
-        const float* qv = qs + g * hd + dg * 8;
-        float dot = 0.f;
+    // --- scores: eight keys per thread are loaded before any is used
+    constexpr int kU = 8;
+    const int pass = kWorkerWarps * kpw;
+    for (int base = j0 + warp * kpw; base < j1; base += pass * kU) {
+      uint4 ku[kU];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) dot = fmaf(qv[e], kf[e], dot);
-        for (int o = 1; o < lpk; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        if (dg == 0 && j < j1) {
-          float s = bf16_round(dot) * A.scale;
-          if (!A.decode) {
-            s = bf16_round(s);
-            if (mrow) s = bf16_round(s + ldg_bf16(mrow + j));
+      for (int u8 = 0; u8 < kU; ++u8) {
+        const int j = base + u8 * pass + sub;
+        ku[u8] = make_uint4(0, 0, 0, 0);
+        if (j < j1) {
+          if (j == newpos) ku[u8] = *reinterpret_cast<const uint4*>(kn + dg * 8);
+          else ku[u8] = __ldcg(reinterpret_cast<const uint4*>(kbase + static_cast<long long>(j) * A.kv_ld) + dg);
+        }
+      }
+#pragma unroll
+      for (int u8 = 0; u8 < kU; ++u8) {
+        if (base + u8 * pass >= j1) break;  // warp-uniform
+        const int j = base + u8 * pass + sub;
+        float kf[8];
+        unpack8(ku[u8], kf);
+        for (int g = 0; g < gs; ++g) {
+          const float* qv = qs + g * hd + dg * 8;
+          float dot = 0.f;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) dot = fmaf(qv[e], kf[e], dot);
+          for (int o = 1; o < lpk; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+          if (dg == 0 && j < j1) {
+            float sv = bf16_round(dot) * A.scale;
+            if (!A.decode) {
+              sv = bf16_round(sv);
+              if (mrow) sv = bf16_round(sv + ldg_bf16(mrow + j));
+            }
+            sc[g * chunk + (j - j0)] = sv;
           }
-          sc[g * chunk + (j - j0)] = s;
         }
       }
     }
@@ -774,17 +867,27 @@ __device__ bool attention_phase(const Ctx& cx, const AttnArgs& A, int wtid) {
       float acc[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-      for (int base = j0 + warp * kpw; base < j1; base += kWorkerWarps * kpw) {
-        const int j = base + sub;
-        if (j < j1) {
-          uint4 vu;
-          if (j == newpos) vu = *reinterpret_cast<const uint4*>(vn + dg * 8);
-          else vu = __ldcg(reinterpret_cast<const uint4*>(vbase + static_cast<long long>(j) * A.kv_ld) + dg);
-          float vf[8];
-          unpack8(vu, vf);
-          const float pr = sc[g * chunk + (j - j0)];
+      for (int base = j0 + warp * kpw; base < j1; base += pass * kU) {
+        uint4 vu[kU];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) acc[e] = fmaf(pr, vf[e], acc[e]);
+        for (int u8 = 0; u8 < kU; ++u8) {
+          const int j = base + u8 * pass + sub;
+          vu[u8] = make_uint4(0, 0, 0, 0);
+          if (j < j1) {
+            if (j == newpos) vu[u8] = *reinterpret_cast<const uint4*>(vn + dg * 8);
+            else vu[u8] = __ldcg(reinterpret_cast<const uint4*>(vbase + static_cast<long long>(j) * A.kv_ld) + dg);
+          }
+        }
+#pragma unroll
+        for (int u8 = 0; u8 < kU; ++u8) {
+          const int j = base + u8 * pass + sub;
+          if (j < j1) {
+            float vf[8];
+            unpack8(vu[u8], vf);
+            const float pr = sc[g * chunk + (j - j0)];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] = fmaf(pr, vf[e], acc[e]);
+          }
         }
       }
       for (int o = lpk; o < 32; o <<= 1) {
@@ -840,7 +943,7 @@ __device__ bool attention_phase(const Ctx& cx, const AttnArgs& A, int wtid) {
 }
 
 // Prefill: rotate q and k of every token in place in the qkv buffer.
-__device__ void rope_phase(const Ctx& cx, int wtid) {
+__device__ __noinline__ void rope_phase(const Ctx& cx, int wtid) {
   const KParams& p = *cx.p;
   const int hd = p.head_dim, half = hd / 2;
   const int heads = p.q_heads + p.kv_heads;  // q heads then k heads are contiguous in a qkv row
@@ -939,6 +1042,7 @@ __device__ void worker_loop(const Ctx& cx, int wtid) {
       A.mask = p.mask; A.sq = p.seq; A.klen = p.seq; A.causal = (p.mask == nullptr);
     }
     if (!attention_phase(cx, A, wtid)) return;              // [RoPE] attention (+ KV append)
+    trace_event(cx, wtid, EV_ATTENTION_DONE);
     MK_DEBUG_STEP();
     if (!grid_barrier(cx, passed, wtid)) return;
     if (decode && cx.cta == 0 && wtid == 0) *p.len[layer] = A.len + 1;  // publish after the interval closes
@@ -988,6 +1092,7 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
     cx.misc->wabort = 0;
     cx.misc->bad = 0;
     cx.misc->flag = 0;
+    cx.misc->trace_n = 0;
     mbar_fence_init();
   }
   // Token rows a launch does not fill must not hold NaN patterns from earlier kernels.

@@ -33,9 +33,10 @@ static_assert(kSmemBytes <= 232448, "dynamic shared memory exceeds 227 KiB");
 enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU = 2 };
 enum { B_PLAIN = 0, B_NORM = 1 };
 enum { MODE_DECODE = 0, MODE_PREFILL = 1, MODE_LINEAR = 2, MODE_KVATT = 3, MODE_ATT = 4 };
+enum { EV_PHASE_ENTER = 1, EV_B_STAGED = 2, EV_FIRST_ACC = 3, EV_PHASE_DONE = 4, EV_BARRIER_DONE = 5, EV_ATTENTION_DONE = 6 };
 enum {
   SITE_PRODUCER_EMPTY = 1, SITE_MMA_FULL = 2, SITE_MMA_B = 3, SITE_MMA_ACC = 4, SITE_EPI_ACC = 5,
-  SITE_GRID_BARRIER = 6, SITE_ATT_EXCHANGE = 7, SITE_DRAIN = 8, SITE_PROLOGUE = 9
+  SITE_GRID_BARRIER = 6, SITE_ATT_EXCHANGE = 7, SITE_DRAIN = 8, SITE_PROLOGUE = 9, SITE_SPLIT_REDUCE = 10
 };
 
 // One projection phase: up to three weight matrices sharing the same activation
@@ -85,6 +86,8 @@ struct KParams {
   int max_positions;
   int stream_once;    // 1: weights are read once per launch (L2 evict-first)
   int debug_stop;     // bring-up aid: leave the schedule after this many steps (0 = run everything)
+  int trace_cap;      // events per CTA in `trace` (0 = tracing off)
+  unsigned long long* trace;  // [grid][trace_cap] (event code << 56) | %globaltimer ns
   long long timeout_cycles;
   const GemmPhase* phases;
   bf16 *hidden_buf, *qkv, *attn, *act;

@@ -39,6 +39,18 @@ def _require(tensor: torch.Tensor, name: str, *, dtype, device, shape=None) -> N
             "input-binding", f"{name} has shape {tuple(tensor.shape)}, expected {tuple(shape)}"))
 
 
+EVENT_NAMES = {1: "phase_enter", 2: "operand_staged", 3: "first_accumulator", 4: "phase_done",
+               5: "barrier_done", 6: "attention_done"}
+
+
+def decode_trace(buffer: torch.Tensor):
+    """Split a trace buffer into (codes, nanoseconds) int64 arrays [ctas, events]; code 0 = unused slot."""
+    raw = buffer.cpu()
+    codes = (raw >> 56) & 0xFF
+    times = raw & ((1 << 56) - 1)
+    return codes, times
+
+
 class DecoderKernel:
     """One persistent-kernel decoder bound to a set of weights.
 
@@ -315,6 +327,18 @@ class DecoderKernel:
                 "state-capacity", "KV cache valid length plus one token exceeds capacity"))
         if result["status"] != "OK":
             raise RuntimeError(f"megakernel device status {result}")
+
+    def set_trace(self, events_per_cta: int = 0) -> torch.Tensor | None:
+        """Turn the per-CTA event trace on (returns the int64 [ctas, events] buffer the
+        next launches fill; decode with :func:`decode_trace`) or off (0)."""
+        if events_per_cta <= 0:
+            self._trace = None
+            self._call("mk_set_trace", self.lib.mk_set_trace(self._handle, None, 0))
+            return None
+        ctas = self.launch_info()["ctas"]
+        self._trace = torch.zeros((ctas, events_per_cta), dtype=torch.int64, device=self.device)
+        self._call("mk_set_trace", self.lib.mk_set_trace(self._handle, self._trace.data_ptr(), events_per_cta))
+        return self._trace
 
     def launch_info(self) -> dict:
         ctas, smem, launches = ctypes.c_int32(), ctypes.c_int32(), ctypes.c_int64()
