@@ -39,13 +39,14 @@ int fail(int code, const char* fmt, ...) {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct Carve {
-  size_t ctrl, tmaps, phases, hidden, qkv, attn, act, partials, tile_ctr, att_max, att_sum, att_part, att_ctr, total;
-  int max_tiles;
+  size_t ctrl, tmaps, phases, hidden, hidden2, qkv, attn, act, partial, att_xch, att_part, total;
 };
 
 int qkv_width(const mk_config& c) { return (c.q_heads + 2 * c.kv_heads) * c.head_dim; }
+size_t maps_per_table(const mk_config& c) { return 7 * static_cast<size_t>(c.layers) + 1; }
+size_t phases_per_table(const mk_config& c) { return 4 * static_cast<size_t>(c.layers) + 1; }
 
-Carve carve(const mk_config& c, int grid) {
+Carve carve(const mk_config& c) {
   Carve v{};
   size_t off = 0;
   auto take = [&](size_t bytes) {
@@ -54,26 +55,17 @@ Carve carve(const mk_config& c, int grid) {
     return at;
   };
   const size_t m = static_cast<size_t>(c.max_tokens);
-  int max_tiles = (c.vocab + kTileRows - 1) / kTileRows;
-  const int inter_tiles = (c.intermediate + kTileRows - 1) / kTileRows;
-  const int qkv_tiles = (c.q_heads * c.head_dim + kTileRows - 1) / kTileRows +
-                        2 * ((c.kv_heads * c.head_dim + kTileRows - 1) / kTileRows);
-  if (inter_tiles > max_tiles) max_tiles = inter_tiles;
-  if (qkv_tiles > max_tiles) max_tiles = qkv_tiles;
-  v.max_tiles = max_tiles;
   v.ctrl = take(sizeof(Control));
-  v.tmaps = take(sizeof(CUtensorMap) * (7 * static_cast<size_t>(c.layers) + 2));
-  v.phases = take(sizeof(GemmPhase) * (4 * static_cast<size_t>(c.layers) + 2));
+  v.tmaps = take(sizeof(CUtensorMap) * (2 * maps_per_table(c) + 1));    // split table, plain table, mk_linear
+  v.phases = take(sizeof(GemmPhase) * (2 * phases_per_table(c) + 1));
   v.hidden = take(m * c.hidden * 2);
+  v.hidden2 = take(static_cast<size_t>(kSplitTokens) * c.hidden * 2);
   v.qkv = take(m * qkv_width(c) * 2);
   v.attn = take(m * c.q_heads * c.head_dim * 2);
   v.act = take(m * c.intermediate * 2);
-  v.partials = take(static_cast<size_t>(grid) * 2 * kPartialFloats * 4);
-  v.tile_ctr = take(static_cast<size_t>(max_tiles) * 4);
-  v.att_max = take(m * c.kv_heads * kMaxChunks * 8 * 4);
-  v.att_sum = take(m * c.kv_heads * kMaxChunks * 8 * 4);
+  v.partial = take(static_cast<size_t>(kMaxSplit) * kSplitTokens * c.hidden * 4);
+  v.att_xch = take(m * c.kv_heads * kMaxChunks * kExchangeFloats * 4);
   v.att_part = take(m * c.q_heads * kMaxChunks * c.head_dim * 4);
-  v.att_ctr = take(m * c.kv_heads * 4 * 4);
   v.total = off;
   return v;
 }
@@ -113,14 +105,14 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   return fn;
 }
 
-// bf16 [rows, k] row-major -> boxes of 128 rows x 64 columns, 128-byte swizzle.
-int encode_weight_map(CUtensorMap* out, const void* base, int rows, int k) {
+// bf16 [rows, k] row-major -> boxes of box_rows rows x 64 columns, 128-byte swizzle.
+int encode_weight_map(CUtensorMap* out, const void* base, int rows, int k, int box_rows) {
   if (reinterpret_cast<uintptr_t>(base) % 16) return fail(MK_ERR_ALIGNMENT, "weight base %p is not 16-byte aligned", base);
   auto fn = encode_fn();
   if (!fn) return fail(MK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
-  const cuuint32_t box[2] = {kChunkK, kTileRows};
+  const cuuint32_t box[2] = {kChunkK, static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t elem[2] = {1, 1};
   const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -139,7 +131,7 @@ struct mk_handle_s {
   bool bound;
   mk_weights weights;
   std::vector<mk_layer_weights> layers;
-  uint32_t epoch;
+  uint32_t epoch, att_epoch;
   int64_t launches;
   long long timeout_cycles;
   float att_scale;
@@ -153,25 +145,61 @@ namespace {
 template <typename T>
 T* at(mk_handle h, size_t off) { return reinterpret_cast<T*>(h->ws + off); }
 
-void finish_phase(GemmPhase& ph) {
-  ph.kc = ph.k / kChunkK;
-  ph.tc = ph.kc * ph.nacc;
-  ph.ntiles = ph.tile_start[ph.nseg];
-  ph.total = static_cast<long long>(ph.ntiles) * ph.tc;
+// Rows per tile: the smallest height for which the phase's row tiles fit in the
+// fewest possible rounds over `slots` CTAs (each round gives every CTA one unit).
+int choose_rows(const GemmPhase& ph, int slots) {
+  const int nseg = ph.nacc == 2 ? 1 : ph.nseg;
+  long long total = 0;
+  for (int s = 0; s < nseg; ++s) total += ph.n[s];
+  if (slots < 1) slots = 1;
+  for (long long rounds = (total + static_cast<long long>(kTileRows) * slots - 1) / (static_cast<long long>(kTileRows) * slots);;
+       ++rounds) {
+    for (int rows = static_cast<int>((total + rounds * slots - 1) / (rounds * slots)); rows <= kTileRows; ++rows) {
+      long long tiles = 0;
+      for (int s = 0; s < nseg; ++s) tiles += (ph.n[s] + rows - 1) / rows;
+      if (tiles <= rounds * slots) return rows;
+    }
+  }
 }
 
-// The activation slots hold 32 K-chunks: a phase fits if its whole K does, or
-// if no CTA's share of the phase spans more than 32 K-steps.
-int check_phase_fits(const GemmPhase& ph, int grid, const char* what) {
-  if (ph.kc <= kBSlots) return MK_OK;
-  const int geff = ph.total < grid ? static_cast<int>(ph.total) : grid;
-  const long long per_cta = (ph.total + geff - 1) / geff + 1;
-  const long long ksteps = (per_cta + ph.nacc - 1) / ph.nacc + 1;
-  if (ksteps <= kBSlots) return MK_OK;
-  return fail(MK_ERR_UNSUPPORTED,
-              "%s: K=%d needs %lld activation chunks per CTA on %d CTAs; the kernel holds %d", what, ph.k, ksteps, grid,
-              kBSlots);
+// A TMA box of fewer than ~40 rows (5 KB) cannot keep an SM's share of HBM
+// bandwidth busy (the copy engine retires roughly one box per 0.1 us), so a
+// projection with few output rows per CTA is cut along K as well.
+constexpr int kGoodBoxRows = 40;
+
+void finish_phase(GemmPhase& ph, int grid, bool allow_split) {
+  ph.kc = ph.k / kChunkK;
+  int best_split = 1, best_rows = choose_rows(ph, grid);
+  if (allow_split && best_rows < kGoodBoxRows) {
+    static const int candidates[] = {2, 3, 4};
+    for (int split : candidates) {
+      if (ph.kc % split || ph.kc / split < 2 || grid / split < 1) continue;
+      const int rows = choose_rows(ph, grid / split);
+      if (rows > best_rows) {
+        best_rows = rows;
+        best_split = split;
+      }
+      if (rows >= kGoodBoxRows) break;
+    }
+  }
+  ph.ksplit = best_split;
+  ph.kslice = ph.kc / best_split;
+  ph.rows = best_rows;
+  ph.gran = (ph.rows * 128 + kGranule - 1) / kGranule;
+  const int nseg = ph.nacc == 2 ? 1 : ph.nseg;
+  int tile = 0;
+  for (int s = 0; s < nseg; ++s) {
+    ph.tile_start[s] = tile;
+    tile += (ph.n[s] + ph.rows - 1) / ph.rows;
+  }
+  ph.tile_start[nseg] = tile;
+  ph.ntiles = tile;
+  ph.nunits = tile * best_split;
 }
+
+// Can launches of at most kSplitTokens tokens use the split-K table?  Its
+// consumer-side residual update keeps a whole hidden row in the activation slots.
+bool split_table_ok(const mk_config& c) { return c.hidden / kChunkK <= kBSlots; }
 
 void base_params(mk_handle h, KParams& p) {
   memset(&p, 0, sizeof(p));
@@ -182,6 +210,7 @@ void base_params(mk_handle h, KParams& p) {
   p.att_scale = h->att_scale;
   p.engine = c.engine;
   p.epoch = h->epoch;
+  p.att_epoch = h->att_epoch;
   p.qkv_ld = qkv_width(c);
   p.max_positions = c.max_positions;
   p.timeout_cycles = h->timeout_cycles;
@@ -193,33 +222,25 @@ void base_params(mk_handle h, KParams& p) {
   p.qkv = at<bf16>(h, h->cv.qkv);
   p.attn = at<bf16>(h, h->cv.attn);
   p.act = at<bf16>(h, h->cv.act);
-  p.partials = at<float>(h, h->cv.partials);
-  p.tile_ctr = at<uint32_t>(h, h->cv.tile_ctr);
-  p.att_max = at<float>(h, h->cv.att_max);
-  p.att_sum = at<float>(h, h->cv.att_sum);
+  p.att_xch = at<float>(h, h->cv.att_xch);
   p.att_part = at<float>(h, h->cv.att_part);
-  p.att_ctr = at<uint32_t>(h, h->cv.att_ctr);
   p.ctrl = at<Control>(h, h->cv.ctrl);
   p.embed = static_cast<const bf16*>(h->weights.embed);
   p.cos_t = static_cast<const bf16*>(h->weights.rope_cos);
   p.sin_t = static_cast<const bf16*>(h->weights.rope_sin);
 }
 
-int launch(mk_handle h, KParams& p, void* stream) {
+int launch(mk_handle h, KParams& p, void* stream, int attention_phases = 0) {
   void* args[] = {&p};
   MK_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(&megakernel), dim3(h->grid), dim3(kThreads), args,
                                       kSmemBytes, static_cast<cudaStream_t>(stream)));
   h->epoch += static_cast<uint32_t>(p.nbar) * static_cast<uint32_t>(h->grid);
+  h->att_epoch += static_cast<uint32_t>(attention_phases);
   h->launches += 1;
   return MK_OK;
 }
 
 int token_tiles(int m) { return (m + kTok - 1) / kTok; }
-
-// Grid barriers between the token tiles of each projection phase (tcgen05 engine only).
-int tile_barriers(mk_handle h, int m, int n_gemm) {
-  return h->cfg.engine == MK_ENGINE_TCGEN05 ? (token_tiles(m) - 1) * n_gemm : 0;
-}
 
 int attention_fits(mk_handle h, int keys, const char* what) {
   const int gs = h->cfg.q_heads / h->cfg.kv_heads;
@@ -240,7 +261,7 @@ size_t mk_workspace_bytes(const mk_config* config, int device) {
   if (!config || check_config(*config) != MK_OK) return 0;
   int grid = 0;
   if (device_grid(*config, device, &grid) != MK_OK) return 0;
-  return carve(*config, grid).total;
+  return carve(*config).total;
 }
 
 int mk_create(const mk_config* config, void* workspace, size_t workspace_bytes, int device, void* stream,
@@ -251,7 +272,7 @@ int mk_create(const mk_config* config, void* workspace, size_t workspace_bytes, 
   MK_CUDA(cudaSetDevice(device));
   int grid = 0;
   if (int e = device_grid(*config, device, &grid)) return e;
-  const Carve cv = carve(*config, grid);
+  const Carve cv = carve(*config);
   if (workspace_bytes < cv.total)
     return fail(MK_ERR_WORKSPACE, "workspace has %zu bytes, %zu needed", workspace_bytes, cv.total);
   int major = 0, coop = 0, khz = 0;
@@ -273,6 +294,7 @@ int mk_create(const mk_config* config, void* workspace, size_t workspace_bytes, 
   h->cv = cv;
   h->bound = false;
   h->epoch = 0;
+  h->att_epoch = 0;
   h->launches = 0;
   h->trace = nullptr;
   h->trace_cap = 0;
@@ -303,81 +325,104 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
     return fail(MK_ERR_INVALID, "mk_bind_weights: embed, final_norm, lm_head and the rope tables are required");
   const int L = c.layers;
   const int q_size = c.q_heads * c.head_dim, kv_size = c.kv_heads * c.head_dim;
-  std::vector<CUtensorMap> maps(7 * static_cast<size_t>(L) + 1);
-  std::vector<GemmPhase> phases(4 * static_cast<size_t>(L) + 1);
+  const size_t nmaps = maps_per_table(c), nphases = phases_per_table(c);
+  std::vector<CUtensorMap> maps(2 * nmaps);
+  std::vector<GemmPhase> phases(2 * nphases);
   CUtensorMap* dmaps = at<CUtensorMap>(h, h->cv.tmaps);
-  bf16* hidden = at<bf16>(h, h->cv.hidden);
+  bf16* hidden_a = at<bf16>(h, h->cv.hidden);
+  bf16* hidden_b = at<bf16>(h, h->cv.hidden2);
   bf16* qkv = at<bf16>(h, h->cv.qkv);
   bf16* attn = at<bf16>(h, h->cv.attn);
   bf16* act = at<bf16>(h, h->cv.act);
-  auto tiles = [](int rows) { return (rows + kTileRows - 1) / kTileRows; };
+  float* partial = at<float>(h, h->cv.partial);
   for (int l = 0; l < L; ++l) {
     const mk_layer_weights& lw = w->layers[l];
     if (!lw.input_norm || !lw.q || !lw.k || !lw.v || !lw.o || !lw.post_norm || !lw.gate || !lw.up || !lw.down)
       return fail(MK_ERR_INVALID, "mk_bind_weights: layer %d has a null weight", l);
     if (c.qkv_bias && (!lw.q_bias || !lw.k_bias || !lw.v_bias))
       return fail(MK_ERR_INVALID, "mk_bind_weights: layer %d lacks a q/k/v bias", l);
-    const void* mats[7] = {lw.q, lw.k, lw.v, lw.o, lw.gate, lw.up, lw.down};
-    const int rows[7] = {q_size, kv_size, kv_size, c.hidden, c.intermediate, c.intermediate, c.hidden};
-    const int ks[7] = {c.hidden, c.hidden, c.hidden, q_size, c.hidden, c.hidden, c.intermediate};
-    for (int i = 0; i < 7; ++i)
-      if (int e = encode_weight_map(&maps[7 * l + i], mats[i], rows[i], ks[i])) return e;
-    GemmPhase* ph = &phases[4 * l];
-    memset(ph, 0, sizeof(GemmPhase) * 4);
-    // q, k, v
-    ph[0].nseg = 3; ph[0].nacc = 1; ph[0].k = c.hidden;
-    const int seg_rows[3] = {q_size, kv_size, kv_size};
-    const void* biases[3] = {lw.q_bias, lw.k_bias, lw.v_bias};
-    int tile = 0, col = 0;
-    for (int s = 0; s < 3; ++s) {
-      ph[0].tmap[s] = dmaps + 7 * l + s;
-      ph[0].w[s] = static_cast<const bf16*>(mats[s]);
-      ph[0].bias[s] = c.qkv_bias ? static_cast<const bf16*>(biases[s]) : nullptr;
-      ph[0].n[s] = seg_rows[s];
-      ph[0].tile_start[s] = tile;
-      ph[0].out_col[s] = col;
-      tile += tiles(seg_rows[s]);
-      col += seg_rows[s];
-    }
-    ph[0].tile_start[3] = tile;
-    ph[0].epi = EPI_STORE; ph[0].bmode = B_NORM; ph[0].gather = (l == 0);
-    ph[0].normw = static_cast<const bf16*>(lw.input_norm);
-    ph[0].src = hidden; ph[0].src_ld = c.hidden; ph[0].dst = qkv; ph[0].dst_ld = qkv_width(c);
-    // o_proj + residual
-    ph[1].nseg = 1; ph[1].nacc = 1; ph[1].k = q_size;
-    ph[1].tmap[0] = dmaps + 7 * l + 3; ph[1].w[0] = static_cast<const bf16*>(lw.o);
-    ph[1].n[0] = c.hidden; ph[1].tile_start[1] = tiles(c.hidden);
-    ph[1].epi = EPI_RESIDUAL; ph[1].bmode = B_PLAIN;
-    ph[1].src = attn; ph[1].src_ld = q_size; ph[1].dst = hidden; ph[1].dst_ld = c.hidden;
-    // gate, up -> silu(gate) * up
-    ph[2].nseg = 1; ph[2].nacc = 2; ph[2].k = c.hidden;
-    ph[2].tmap[0] = dmaps + 7 * l + 4; ph[2].tmap[1] = dmaps + 7 * l + 5;
-    ph[2].w[0] = static_cast<const bf16*>(lw.gate); ph[2].w[1] = static_cast<const bf16*>(lw.up);
-    ph[2].n[0] = c.intermediate; ph[2].n[1] = c.intermediate; ph[2].tile_start[1] = tiles(c.intermediate);
-    ph[2].epi = EPI_SILU; ph[2].bmode = B_NORM; ph[2].normw = static_cast<const bf16*>(lw.post_norm);
-    ph[2].src = hidden; ph[2].src_ld = c.hidden; ph[2].dst = act; ph[2].dst_ld = c.intermediate;
-    // down + residual
-    ph[3].nseg = 1; ph[3].nacc = 1; ph[3].k = c.intermediate;
-    ph[3].tmap[0] = dmaps + 7 * l + 6; ph[3].w[0] = static_cast<const bf16*>(lw.down);
-    ph[3].n[0] = c.hidden; ph[3].tile_start[1] = tiles(c.hidden);
-    ph[3].epi = EPI_RESIDUAL; ph[3].bmode = B_PLAIN;
-    ph[3].src = act; ph[3].src_ld = c.intermediate; ph[3].dst = hidden; ph[3].dst_ld = c.hidden;
-    for (int i = 0; i < 4; ++i) {
-      finish_phase(ph[i]);
-      static const char* names[4] = {"q/k/v projection", "o projection", "gate/up projection", "down projection"};
-      if (int e = check_phase_fits(ph[i], h->grid, names[i])) return e;
-    }
   }
-  if (int e = encode_weight_map(&maps[7 * L], w->lm_head, c.vocab, c.hidden)) return e;
-  GemmPhase& head = phases[4 * L];
-  memset(&head, 0, sizeof(head));
-  head.nseg = 1; head.nacc = 1; head.k = c.hidden;
-  head.tmap[0] = dmaps + 7 * L; head.w[0] = static_cast<const bf16*>(w->lm_head);
-  head.n[0] = c.vocab; head.tile_start[1] = tiles(c.vocab);
-  head.epi = EPI_STORE; head.bmode = B_NORM; head.normw = static_cast<const bf16*>(w->final_norm);
-  head.src = hidden; head.src_ld = c.hidden; head.to_logits = 1; head.dst_ld = c.vocab;
-  finish_phase(head);
-  if (int e = check_phase_fits(head, h->grid, "lm_head")) return e;
+  // Table 0: split-K (small launches): o and down store K-slice partials; the next
+  // normalising phase adds them to the residual stream, which ping-pongs between
+  // hidden_b (after attention) and hidden_a (after the MLP).  Table 1: plain.
+  for (int table = 0; table < 2; ++table) {
+    const bool split = (table == 0);
+    if (split && !split_table_ok(c)) continue;
+    GemmPhase* tp = phases.data() + table * nphases;
+    CUtensorMap* tmaps_host = maps.data() + table * nmaps;
+    CUtensorMap* tmaps_dev = dmaps + table * nmaps;
+    int prev_parts = 0;  // K slices of the projection whose partials the next normalising phase adds
+    for (int l = 0; l < L; ++l) {
+      const mk_layer_weights& lw = w->layers[l];
+      GemmPhase* ph = tp + 4 * l;
+      memset(ph, 0, sizeof(GemmPhase) * 4);
+      // q, k, v
+      ph[0].nseg = 3; ph[0].nacc = 1; ph[0].k = c.hidden;
+      const void* qkv_mats[3] = {lw.q, lw.k, lw.v};
+      const int seg_rows[3] = {q_size, kv_size, kv_size};
+      const void* biases[3] = {lw.q_bias, lw.k_bias, lw.v_bias};
+      int col = 0;
+      for (int s = 0; s < 3; ++s) {
+        ph[0].tmap[s] = tmaps_dev + 7 * l + s;
+        ph[0].w[s] = static_cast<const bf16*>(qkv_mats[s]);
+        ph[0].bias[s] = c.qkv_bias ? static_cast<const bf16*>(biases[s]) : nullptr;
+        ph[0].n[s] = seg_rows[s];
+        ph[0].out_col[s] = col;
+        col += seg_rows[s];
+      }
+      ph[0].epi = EPI_STORE; ph[0].bmode = B_NORM; ph[0].gather = (l == 0);
+      ph[0].normw = static_cast<const bf16*>(lw.input_norm);
+      ph[0].src = hidden_a; ph[0].src_ld = c.hidden; ph[0].dst = qkv; ph[0].dst_ld = qkv_width(c);
+      if (split) {
+        ph[0].add_parts = prev_parts; ph[0].partial = partial; ph[0].h_out = hidden_b;
+      }
+      // o_proj; its activation operand is the attention output (bf16 or chunk partials)
+      ph[1].nseg = 1; ph[1].nacc = 1; ph[1].k = q_size;
+      ph[1].tmap[0] = tmaps_dev + 7 * l + 3; ph[1].w[0] = static_cast<const bf16*>(lw.o);
+      ph[1].n[0] = c.hidden;
+      ph[1].epi = split ? EPI_PARTIAL : EPI_RESIDUAL; ph[1].bmode = B_ATTN;
+      ph[1].src = attn; ph[1].src_ld = q_size; ph[1].dst = hidden_a; ph[1].dst_ld = c.hidden;
+      ph[1].partial = partial;
+      // gate, up -> silu(gate) * up
+      ph[2].nseg = 1; ph[2].nacc = 2; ph[2].k = c.hidden;
+      ph[2].tmap[0] = tmaps_dev + 7 * l + 4; ph[2].tmap[1] = tmaps_dev + 7 * l + 5;
+      ph[2].w[0] = static_cast<const bf16*>(lw.gate); ph[2].w[1] = static_cast<const bf16*>(lw.up);
+      ph[2].n[0] = c.intermediate; ph[2].n[1] = c.intermediate;
+      ph[2].epi = EPI_SILU; ph[2].bmode = B_NORM; ph[2].normw = static_cast<const bf16*>(lw.post_norm);
+      ph[2].src = split ? hidden_b : hidden_a; ph[2].src_ld = c.hidden; ph[2].dst = act; ph[2].dst_ld = c.intermediate;
+      // down
+      ph[3].nseg = 1; ph[3].nacc = 1; ph[3].k = c.intermediate;
+      ph[3].tmap[0] = tmaps_dev + 7 * l + 6; ph[3].w[0] = static_cast<const bf16*>(lw.down);
+      ph[3].n[0] = c.hidden;
+      ph[3].epi = split ? EPI_PARTIAL : EPI_RESIDUAL; ph[3].bmode = B_PLAIN;
+      ph[3].src = act; ph[3].src_ld = c.intermediate; ph[3].dst = hidden_a; ph[3].dst_ld = c.hidden;
+      ph[3].partial = partial;
+      for (int i = 0; i < 4; ++i) finish_phase(ph[i], h->grid, split && ph[i].epi == EPI_PARTIAL);
+      if (split) {
+        ph[2].add_parts = ph[1].ksplit; ph[2].partial = partial; ph[2].h_out = hidden_a;
+        prev_parts = ph[3].ksplit;
+      }
+      // One TMA descriptor per matrix, boxed to the tile height its phase chose.
+      const void* mats[7] = {lw.q, lw.k, lw.v, lw.o, lw.gate, lw.up, lw.down};
+      const int rows[7] = {q_size, kv_size, kv_size, c.hidden, c.intermediate, c.intermediate, c.hidden};
+      const int ks[7] = {c.hidden, c.hidden, c.hidden, q_size, c.hidden, c.hidden, c.intermediate};
+      const int box[7] = {ph[0].rows, ph[0].rows, ph[0].rows, ph[1].rows, ph[2].rows, ph[2].rows, ph[3].rows};
+      for (int i = 0; i < 7; ++i)
+        if (int e = encode_weight_map(&tmaps_host[7 * l + i], mats[i], rows[i], ks[i], box[i])) return e;
+    }
+    GemmPhase& head = tp[4 * L];
+    memset(&head, 0, sizeof(head));
+    head.nseg = 1; head.nacc = 1; head.k = c.hidden;
+    head.tmap[0] = tmaps_dev + 7 * L; head.w[0] = static_cast<const bf16*>(w->lm_head);
+    head.n[0] = c.vocab;
+    head.epi = EPI_STORE; head.bmode = B_NORM; head.normw = static_cast<const bf16*>(w->final_norm);
+    head.src = hidden_a; head.src_ld = c.hidden; head.to_logits = 1; head.dst_ld = c.vocab;
+    if (split) {
+      head.add_parts = prev_parts; head.partial = partial;
+    }
+    finish_phase(head, h->grid, false);
+    if (int e = encode_weight_map(&tmaps_host[7 * L], w->lm_head, c.vocab, c.hidden, head.rows)) return e;
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   MK_CUDA(cudaMemcpyAsync(dmaps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, s));
   MK_CUDA(cudaMemcpyAsync(at<GemmPhase>(h, h->cv.phases), phases.data(), phases.size() * sizeof(GemmPhase),
@@ -413,13 +458,15 @@ int mk_decode(mk_handle h, const int64_t* ids, const int64_t* positions, int bat
   }
   const int ntt = token_tiles(batch);
   p.mode = MODE_DECODE; p.m = batch; p.batch = batch; p.seq = 1; p.capacity = capacity;
+  p.split = (batch <= kSplitTokens && split_table_ok(h->cfg)) ? 1 : 0;
+  p.phases = at<GemmPhase>(h, h->cv.phases) + (p.split ? 0 : phases_per_table(h->cfg));
   p.n_gemm = 4 * L + 1;
-  p.nbar = 5 * L + tile_barriers(h, batch, 4 * L + 1);
+  p.nbar = 5 * L;
   p.stream_once = (ntt == 1);
   p.ids = reinterpret_cast<const long long*>(ids);
   p.pos = reinterpret_cast<const long long*>(positions);
   p.logits = static_cast<bf16*>(logits);
-  return launch(h, p, stream);
+  return launch(h, p, stream, L);
 }
 
 int mk_prefill(mk_handle h, const int64_t* ids, const int64_t* positions, const void* mask, int batch, int sequence,
@@ -439,8 +486,10 @@ int mk_prefill(mk_handle h, const int64_t* ids, const int64_t* positions, const 
   const int L = h->cfg.layers;
   const int ntt = token_tiles(static_cast<int>(m));
   p.mode = MODE_PREFILL; p.m = static_cast<int>(m); p.batch = batch; p.seq = sequence; p.capacity = 0;
+  p.split = (m <= kSplitTokens && split_table_ok(h->cfg)) ? 1 : 0;
+  p.phases = at<GemmPhase>(h, h->cv.phases) + (p.split ? 0 : phases_per_table(h->cfg));
   p.n_gemm = 4 * L + 1;
-  p.nbar = 6 * L + tile_barriers(h, static_cast<int>(m), 4 * L + 1);
+  p.nbar = 6 * L;
   p.stream_once = (ntt == 1);
   p.ids = reinterpret_cast<const long long*>(ids);
   p.pos = reinterpret_cast<const long long*>(positions);
@@ -455,37 +504,32 @@ int mk_linear(mk_handle h, const void* x, const void* weight, const void* bias, 
   std::lock_guard<std::mutex> guard(h->lock);
   if (m < 1 || m > h->cfg.max_tokens) return fail(MK_ERR_INVALID, "mk_linear: m %d outside [1, %d]", m, h->cfg.max_tokens);
   if (n < 1 || k < 64 || k % 64) return fail(MK_ERR_UNSUPPORTED, "mk_linear: k must be a positive multiple of 64");
-  if ((n + kTileRows - 1) / kTileRows > h->cv.max_tiles)
-    return fail(MK_ERR_UNSUPPORTED, "mk_linear: n %d exceeds the %d tiles this handle's workspace covers", n, h->cv.max_tiles);
   if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(y) % 2)
     return fail(MK_ERR_ALIGNMENT, "mk_linear: x must be 16-byte aligned");
-  const size_t L = static_cast<size_t>(h->cfg.layers);
-  CUtensorMap map;
-  if (int e = encode_weight_map(&map, weight, n, k)) return e;
-  CUtensorMap* dmap = at<CUtensorMap>(h, h->cv.tmaps) + 7 * L + 1;
-  GemmPhase* dphase = at<GemmPhase>(h, h->cv.phases) + 4 * L + 1;
+  CUtensorMap* dmap = at<CUtensorMap>(h, h->cv.tmaps) + 2 * maps_per_table(h->cfg);
+  GemmPhase* dphase = at<GemmPhase>(h, h->cv.phases) + 2 * phases_per_table(h->cfg);
   GemmPhase ph;
   memset(&ph, 0, sizeof(ph));
   ph.nseg = 1; ph.nacc = 1; ph.k = k;
   ph.tmap[0] = dmap; ph.w[0] = static_cast<const bf16*>(weight); ph.bias[0] = static_cast<const bf16*>(bias);
-  ph.n[0] = n; ph.tile_start[1] = (n + kTileRows - 1) / kTileRows;
+  ph.n[0] = n;
   ph.epi = EPI_STORE; ph.bmode = B_PLAIN;
   ph.src = static_cast<const bf16*>(x); ph.src_ld = k;
   ph.dst = static_cast<bf16*>(y); ph.dst_ld = n;
-  finish_phase(ph);
-  if (int e = check_phase_fits(ph, h->grid, "mk_linear")) return e;
+  finish_phase(ph, h->grid, false);
+  CUtensorMap map;
+  if (int e = encode_weight_map(&map, weight, n, k, ph.rows)) return e;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   MK_CUDA(cudaMemcpyAsync(dmap, &map, sizeof(map), cudaMemcpyHostToDevice, s));
   MK_CUDA(cudaMemcpyAsync(dphase, &ph, sizeof(ph), cudaMemcpyHostToDevice, s));
   MK_CUDA(cudaStreamSynchronize(s));
   KParams p;
   base_params(h, p);
-  const int ntt = token_tiles(m);
   p.phases = dphase;
   p.mode = MODE_LINEAR; p.m = m; p.batch = m; p.seq = 1;
   p.n_gemm = 1;
-  p.nbar = tile_barriers(h, m, 1);
-  p.stream_once = (ntt == 1);
+  p.nbar = 0;
+  p.stream_once = (token_tiles(m) == 1);
   return launch(h, p, stream);
 }
 
@@ -505,7 +549,7 @@ int mk_kv_attention(mk_handle h, const void* query, const void* key, const void*
   p.op_q = static_cast<const bf16*>(query); p.op_k = static_cast<const bf16*>(key); p.op_v = static_cast<const bf16*>(value);
   p.op_out = static_cast<bf16*>(output);
   p.kc[0] = key_cache; p.vc[0] = value_cache; p.len[0] = valid_length;
-  return launch(h, p, stream);
+  return launch(h, p, stream, 1);
 }
 
 int mk_attention(mk_handle h, const void* query, const void* key, const void* value, const void* mask, float scale,
@@ -543,8 +587,6 @@ int mk_status(mk_handle h, void* stream, mk_status_info* out) {
   if (c.status != MK_STATUS_OK || c.abort) {
     // Counters are in an unknown state after an aborted launch: start over.
     MK_CUDA(cudaMemset(at<Control>(h, h->cv.ctrl), 0, sizeof(Control)));
-    MK_CUDA(cudaMemset(at<uint32_t>(h, h->cv.tile_ctr), 0, static_cast<size_t>(h->cv.max_tiles) * 4));
-    MK_CUDA(cudaMemset(at<uint32_t>(h, h->cv.att_ctr), 0, static_cast<size_t>(h->cfg.max_tokens) * h->cfg.kv_heads * 16));
     h->epoch = 0;
     return fail(MK_ERR_DEVICE_STATUS, "device status %d at site %d (cta %d, detail %d)", c.status, c.where, c.cta, c.detail);
   }

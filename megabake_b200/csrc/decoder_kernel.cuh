@@ -3,22 +3,24 @@
 //
 // Roles inside each CTA (one CTA per SM):
 //   warp 0      weight producer: walks the static schedule of every projection
-//               phase of the launch and streams this CTA's share of the weights
-//               through a ring of TMA stages.  Weights never depend on a
-//               barrier, so the stream runs ahead across phases and layers.
-//   warp 1      MMA issuer: tcgen05.mma with the weight tile as the M=128
-//               operand and the token activations as the N=16 operand
-//               (the "swapAB" orientation), fp32 accumulators in TMEM.
+//               phase of the launch and streams this CTA's weight tiles through
+//               a ring of TMA-filled shared-memory slots.  Weights never depend
+//               on a barrier, so the stream runs ahead across phases and layers.
+//   warp 1      MMA issuer: tcgen05.mma with the weight tile as the M operand
+//               and the token activations as the N=16 operand (the "swapAB"
+//               orientation), fp32 accumulators in TMEM.
 //   warps 2-5   workers: build the activation operand in shared memory
 //               (RMSNorm fused here), run the epilogues out of TMEM (bias,
 //               residual add, SiLU*up), the attention phase (RoPE, KV append,
 //               split-context softmax attention) and the grid barriers.
 //
-// Work split: each projection phase is flattened to 16 KiB weight chunks
-// (128 rows x 64 K) in tile-major order and cut into equal contiguous ranges,
-// one per CTA.  A tile whose K range spans several CTAs is finished by the
-// last CTA to arrive, which sums the fp32 partials in CTA order (fixed order,
-// so results do not depend on timing).
+// Work split: the output rows of a projection phase are cut into tiles of
+// `rows` rows, chosen on the host so the tile count is just under a multiple of
+// the CTA count.  A CTA runs each of its tiles over the whole reduction length
+// into one TMEM accumulator: a single fp32 chain per output, no partial sums
+// cross CTAs, results do not depend on timing.  Only `rows` rows of the 128-row
+// MMA tile hold weights; the tensor core computes the rest on stale bytes and
+// the epilogue ignores them.
 //
 // Every device wait is bounded: a wait that runs out records where in the
 // status block, raises the abort flag that all other waits poll, and the CTA
@@ -30,19 +32,25 @@
 namespace mk {
 
 struct SmemMisc {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[kChunkBars];
+  uint64_t empty[kChunkBars];
   uint64_t accfull[2];
   uint64_t accempty[2];
-  uint64_t bfull;
+  uint64_t bfull[2];
+  uint64_t bempty[2];
   uint32_t tmem_base;
-  int wabort;  // sticky: a worker thread gave up a wait
-  int bad;     // prologue validation result
-  int flag;    // "this CTA reduces / finishes" decisions taken by worker thread 0
-  float rinv[kTok];
+  int wabort;   // sticky: a worker thread gave up a wait
+  int bad;      // prologue validation result
+  int flag;
   int trace_n;  // events this CTA has recorded
+  float rinv[kTok];
+  float red4[4];           // cross-warp sums of the block-wide RMSNorm
+  uint8_t qstart[kChunkBars];  // producer: first ring granule of each chunk in flight (by sequence % kChunkBars)
+  uint8_t qgran[kChunkBars];   // producer: granules of that chunk
+  GemmPhase phase[2];  // worker-side copies of the current / next projection phase
 };
 static_assert(sizeof(SmemMisc) <= kMiscBytes, "misc shared block too large");
+static_assert(kRingGranules < 256, "ring positions are kept in bytes");
 
 struct Ctx {
   const KParams* p;
@@ -54,9 +62,12 @@ struct Ctx {
   int cta, grid;
 };
 
-struct Range {
-  long long c0, c1;
-  int geff;
+// Worker-side running state across the phases of one launch.
+struct WorkerState {
+  uint32_t tiles;        // accumulator buffers consumed so far
+  uint32_t passed;       // grid barriers passed
+  uint32_t be_cnt[2];    // bempty completions consumed per half
+  bool outstanding[2];   // a streamed batch on this half still awaits its bempty
 };
 
 // ---------------------------------------------------------------------------
@@ -107,15 +118,15 @@ __device__ __forceinline__ bool workers_ok(const Ctx& cx, bool ok) {
 
 // Monotonic-counter grid barrier over the worker warps of every CTA: one
 // release-add to arrive, relaxed polling, one fence once the count is reached.
-__device__ bool grid_barrier(const Ctx& cx, uint32_t& passed, int wtid) {
+__device__ bool grid_barrier(const Ctx& cx, WorkerState& ws, int wtid) {
   named_bar_sync(1, kWorkers);
-  passed += 1;
+  ws.passed += 1;
   if (wtid == 0) {
     red_release_add_u32(&cx.ctrl->barrier, 1u);
-    const uint32_t target = cx.p->epoch + passed * static_cast<uint32_t>(cx.grid);
+    const uint32_t target = cx.p->epoch + ws.passed * static_cast<uint32_t>(cx.grid);
     uint32_t spins = 0;
     while (static_cast<int32_t>(ld_relaxed_u32(&cx.ctrl->barrier) - target) < 0) {
-      if ((++spins & 255u) == 0 && give_up(cx, SITE_GRID_BARRIER, static_cast<int>(passed))) {
+      if ((++spins & 255u) == 0 && give_up(cx, SITE_GRID_BARRIER, static_cast<int>(ws.passed))) {
         cx.misc->wabort = 1;
         break;
       }
@@ -128,29 +139,33 @@ __device__ bool grid_barrier(const Ctx& cx, uint32_t& passed, int wtid) {
 }
 
 // ---------------------------------------------------------------------------
-// work split
+// schedule helpers shared by the three roles
 
-__device__ __forceinline__ Range cta_range(const GemmPhase* ph, int cta, int grid) {
-  Range r;
-  const long long total = ph->total;
-  r.geff = total < grid ? static_cast<int>(total) : grid;
-  if (cta >= r.geff) {
-    r.c0 = r.c1 = 0;
-    return r;
+__device__ __forceinline__ void tile_origin(const GemmPhase* ph, int tile, int& seg, int& row0) {
+  seg = 0;
+  if (ph->nacc == 1) {
+    while (seg + 1 < ph->nseg && tile >= ph->tile_start[seg + 1]) ++seg;
   }
-  r.c0 = cta * total / r.geff;
-  r.c1 = (cta + 1) * total / r.geff;
-  return r;
+  row0 = (tile - ph->tile_start[seg]) * ph->rows;
 }
 
-__device__ __forceinline__ int cta_of_chunk(long long chunk, long long total, int geff) {
-  return static_cast<int>(((chunk + 1) * geff + total - 1) / total) - 1;
+// Every CTA walks its K slice from a different starting chunk (and wraps), so
+// that at any moment the grid's loads spread over all of a weight row's
+// 128-byte columns.  Slices whose activation operand is streamed in batches of
+// kBHalf chunks rotate by whole batches.
+__device__ __forceinline__ int k_rotation(int cta, int grid, int kslice) {
+  if (kslice <= kBSlots) return static_cast<int>((static_cast<long long>(cta) * kslice) / grid);
+  const int batches = (kslice + kBHalf - 1) / kBHalf;
+  return static_cast<int>((static_cast<long long>(cta) * batches) / grid);  // in batches
 }
 
-__device__ __forceinline__ int segment_of_tile(const GemmPhase* ph, int tile) {
-  int seg = 0;
-  while (seg + 1 < ph->nseg && tile >= ph->tile_start[seg + 1]) ++seg;
-  return seg;
+// The weight ring hands out runs of 1 KiB granules in FIFO order; a run never
+// wraps.  Producer and MMA issuer replay the same sequence.
+__device__ __forceinline__ int ring_alloc(int& head, int granules) {
+  if (head + granules > kRingGranules) head = 0;
+  const int start = head;
+  head += granules;
+  return start;
 }
 
 // ---------------------------------------------------------------------------
@@ -160,51 +175,82 @@ __device__ __noinline__ void producer_loop(const Ctx& cx) {
   const KParams& p = *cx.p;
   const uint64_t policy = p.stream_once ? l2_policy_evict_first() : l2_policy_evict_normal();
   const int ntt = (p.m + kTok - 1) / kTok;
-  uint32_t it = 0;
+  SmemMisc* misc = cx.misc;
+  // Chunks are consumed in issue order, so ring space is reclaimed by retiring
+  // the oldest chunk in flight until the wanted granules are free.
+  int head = 0, seq = 0, oldest = 0;
   bool ok = true;
+  auto retire_oldest = [&](int gp) -> bool {
+    const bool done = wait_mbar(cx, smem_u32(&misc->empty[oldest % kChunkBars]), (oldest / kChunkBars) & 1,
+                                SITE_PRODUCER_EMPTY, gp);
+    ++oldest;
+    return done;
+  };
+  auto reclaim = [&](int start, int end, int gp) -> bool {  // free [start, end) of the ring
+    while (oldest < seq) {
+      const int os = misc->qstart[oldest % kChunkBars], oe = os + misc->qgran[oldest % kChunkBars];
+      if (!(os < end && start < oe)) break;
+      if (!retire_oldest(gp)) return false;
+    }
+    return true;
+  };
   for (int gp = 0; gp < p.n_gemm && ok; ++gp) {
     const GemmPhase* ph = p.phases + gp;
-    const Range r = cta_range(ph, cx.cta, cx.grid);
-    if (r.c1 <= r.c0) continue;
-    const int tc = ph->tc, nacc = ph->nacc;
+    const int nacc = ph->nacc, gran = ph->gran, nunits = ph->nunits, ksplit = ph->ksplit, kslice = ph->kslice;
+    const uint32_t bytes = static_cast<uint32_t>(ph->rows) * 128u;
+    const int rot = k_rotation(cx.cta, cx.grid, kslice);
+    const bool streamed = kslice > kBSlots;
+    const int batches = (kslice + kBHalf - 1) / kBHalf;
+    const CUtensorMap* map_a1 = ph->tmap[1];
     for (int tt = 0; tt < ntt && ok; ++tt) {
-      long long c = r.c0;
-      while (c < r.c1 && ok) {
-        const int tile = static_cast<int>(c / tc);
-        long long seg_end = static_cast<long long>(tile + 1) * tc;
-        if (seg_end > r.c1) seg_end = r.c1;
-        const CUtensorMap* map0 = ph->tmap[0];
-        int row0 = tile * kTileRows;
-        if (nacc == 1) {
-          const int seg = segment_of_tile(ph, tile);
-          map0 = ph->tmap[seg];
-          row0 = (tile - ph->tile_start[seg]) * kTileRows;
-        }
-        for (; c < seg_end; ++c) {
-          const int j = static_cast<int>(c - static_cast<long long>(tile) * tc);
-          const int kidx = j / nacc;
-          const CUtensorMap* map = (nacc == 2) ? ph->tmap[j % nacc] : map0;
-          const uint32_t stage = it % kStages;
-          const uint32_t parity = (it / kStages) & 1u;
-          if (!wait_mbar(cx, smem_u32(&cx.misc->empty[stage]), parity ^ 1u, SITE_PRODUCER_EMPTY, gp)) {
-            ok = false;
-            break;
+      for (int unit = cx.cta; unit < nunits && ok; unit += cx.grid) {
+        const int tile = unit / ksplit, slice = unit - tile * ksplit;
+        int seg, row0;
+        tile_origin(ph, tile, seg, row0);
+        const CUtensorMap* map_a0 = ph->tmap[nacc == 2 ? 0 : seg];
+        const int kbase = slice * kslice;
+        // visiting order: rotated within the slice (whole batches when the operand is streamed)
+        int k = streamed ? rot * kBHalf : rot;
+        int batch = rot, left_in_batch = streamed ? min(kBHalf, kslice - rot * kBHalf) : kslice;
+        for (int i = 0; i < kslice && ok; ++i) {
+          for (int a = 0; a < nacc; ++a) {
+            if (head + gran > kRingGranules) {  // the tail fragment is skipped: free it too, then wrap
+              if (!reclaim(head, kRingGranules, gp)) { ok = false; break; }
+              head = 0;
+            }
+            const int start = head;
+            head += gran;
+            if (!reclaim(start, start + gran, gp)) { ok = false; break; }
+            if (seq - oldest >= kChunkBars && !retire_oldest(gp)) { ok = false; break; }  // barrier pair reuse
+            misc->qstart[seq % kChunkBars] = static_cast<uint8_t>(start);
+            misc->qgran[seq % kChunkBars] = static_cast<uint8_t>(gran);
+            const uint32_t full = smem_u32(&misc->full[seq % kChunkBars]);
+            mbar_expect_tx(full, bytes);
+            tma_load_2d(smem_u32(cx.smem_a + start * kGranule), a ? map_a1 : map_a0, (kbase + k) * kChunkK, row0, full,
+                        policy);
+            ++seq;
           }
-          const uint32_t full = smem_u32(&cx.misc->full[stage]);
-          mbar_expect_tx(full, kStageBytes);
-          tma_load_2d(smem_u32(cx.smem_a + stage * kStageBytes), map, kidx * kChunkK, row0, full, policy);
-          ++it;
+          // next chunk of the slice in visiting order
+          ++k;
+          if (streamed) {
+            if (--left_in_batch == 0) {
+              batch = (batch + 1 == batches) ? 0 : batch + 1;
+              k = batch * kBHalf;
+              left_in_batch = min(kBHalf, kslice - k);
+            }
+          } else if (k == kslice) {
+            k = 0;
+          }
         }
       }
     }
   }
   if (!ok) {
     // Leaving early: every copy already issued must land before the CTA exits.
-    const uint32_t first = it > kStages ? it - kStages : 0;
-    for (uint32_t i = first; i < it; ++i) {
-      const uint32_t bar = smem_u32(&cx.misc->full[i % kStages]);
+    for (int i = max(0, seq - kChunkBars); i < seq; ++i) {
+      const uint32_t bar = smem_u32(&misc->full[i % kChunkBars]);
       for (uint32_t spins = 0; spins < (1u << 22); ++spins) {
-        if (mbar_try_wait(bar, (i / kStages) & 1u)) break;
+        if (mbar_try_wait(bar, (i / kChunkBars) & 1)) break;
       }
     }
   }
@@ -218,48 +264,65 @@ __device__ __noinline__ void mma_loop(const Ctx& cx) {
   const int ntt = (p.m + kTok - 1) / kTok;
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&cx.misc->tmem_base);
   constexpr uint32_t idesc = umma_idesc_bf16(kTileRows, kTok);
-  uint32_t it = 0, q = 0, bcount = 0;
+  const uint64_t desc_base = umma_desc_sw128(0);
+  const uint32_t ring_base = smem_u32(cx.smem_a), b_region = smem_u32(cx.smem_b);
+  int head = 0, seq = 0;
+  uint32_t q = 0, bf_cnt[2] = {0, 0};
   for (int gp = 0; gp < p.n_gemm; ++gp) {
     const GemmPhase* ph = p.phases + gp;
-    const Range r = cta_range(ph, cx.cta, cx.grid);
-    if (r.c1 <= r.c0) continue;
-    const int tc = ph->tc, nacc = ph->nacc, kc = ph->kc;
-    const long long ks0 = r.c0 / nacc;
-    const long long ks1 = (r.c1 + nacc - 1) / nacc;
-    const bool all_k = (ks1 - ks0) >= kc;
+    const int nacc = ph->nacc, gran = ph->gran, nunits = ph->nunits, kslice = ph->kslice;
+    const bool per_unit = ph->ksplit > 1;      // the operand differs from unit to unit
+    const bool streamed = kslice > kBSlots;    // the operand does not fit: batches ping-pong through two halves
+    const int rot = k_rotation(cx.cta, cx.grid, kslice);
+    const int batches = streamed ? (kslice + kBHalf - 1) / kBHalf : 1;
+    if (cx.cta >= nunits) continue;
     for (int tt = 0; tt < ntt; ++tt) {
-      if (!wait_mbar(cx, smem_u32(&cx.misc->bfull), bcount & 1u, SITE_MMA_B, gp)) return;
-      ++bcount;
-      tc_fence_after();
-      long long c = r.c0;
-      while (c < r.c1) {
-        const int tile = static_cast<int>(c / tc);
-        long long seg_end = static_cast<long long>(tile + 1) * tc;
-        if (seg_end > r.c1) seg_end = r.c1;
+      for (int unit = cx.cta; unit < nunits; unit += cx.grid) {
+        if (!streamed && (per_unit || unit == cx.cta)) {
+          for (int h = 0; h < (kslice > kBHalf ? 2 : 1); ++h) {
+            if (!wait_mbar(cx, smem_u32(&cx.misc->bfull[h]), bf_cnt[h] & 1u, SITE_MMA_B, gp)) return;
+            ++bf_cnt[h];
+          }
+          tc_fence_after();
+        }
         const uint32_t buf = q & 1u;
         if (!wait_mbar(cx, smem_u32(&cx.misc->accempty[buf]), ((q >> 1) & 1u) ^ 1u, SITE_MMA_ACC, gp)) return;
         tc_fence_after();
-        uint32_t started0 = 0, started1 = 0;
-        for (; c < seg_end; ++c) {
-          const int j = static_cast<int>(c - static_cast<long long>(tile) * tc);
-          const int kidx = j / nacc;
-          const int acc = j - kidx * nacc;
-          const int slot = all_k ? kidx : static_cast<int>(c / nacc - ks0);
-          const uint32_t stage = it % kStages;
-          if (!wait_mbar(cx, smem_u32(&cx.misc->full[stage]), (it / kStages) & 1u, SITE_MMA_FULL, gp)) return;
-          tc_fence_after();
-          const uint32_t a_base = smem_u32(cx.smem_a + stage * kStageBytes);
-          const uint32_t b_base = smem_u32(cx.smem_b + slot * kBSlotBytes);
-          const uint32_t d = tmem + (buf * 2u + static_cast<uint32_t>(acc)) * kTok;
-          uint32_t started = acc ? started1 : started0;
-#pragma unroll
-          for (int kk = 0; kk < kChunkK / 16; ++kk) {
-            umma_bf16(d, umma_desc_sw128(a_base + kk * 32), umma_desc_sw128(b_base + kk * 32), idesc,
-                      started | static_cast<uint32_t>(kk > 0));
+        uint32_t accumulate = 0;
+        for (int vb = 0; vb < batches; ++vb) {
+          int b = rot + vb;
+          if (b >= batches) b -= batches;
+          const int h = vb & 1;
+          const int len = streamed ? min(kBHalf, kslice - b * kBHalf) : kslice;
+          if (streamed) {
+            if (!wait_mbar(cx, smem_u32(&cx.misc->bfull[h]), bf_cnt[h] & 1u, SITE_MMA_B, gp)) return;
+            ++bf_cnt[h];
+            tc_fence_after();
           }
-          if (acc) started1 = 1; else started0 = 1;
-          umma_commit(smem_u32(&cx.misc->empty[stage]));
-          ++it;
+          int slot = streamed ? h * kBHalf : rot;
+          for (int j = 0; j < len; ++j) {
+            const uint64_t b_desc = desc_base + ((b_region + slot * kBSlotBytes) >> 4);
+            for (int a = 0; a < nacc; ++a) {
+              if (head + gran > kRingGranules) head = 0;
+              const uint32_t a_addr = ring_base + head * kGranule;
+              head += gran;
+              if (!wait_mbar(cx, smem_u32(&cx.misc->full[seq % kChunkBars]), (seq / kChunkBars) & 1, SITE_MMA_FULL, gp))
+                return;
+              tc_fence_after();
+              const uint64_t a_desc = desc_base + (a_addr >> 4);
+              const uint32_t d = tmem + (buf * 2u + static_cast<uint32_t>(a)) * kTok;
+              umma_bf16(d, a_desc, b_desc, idesc, accumulate);
+              umma_bf16(d, a_desc + 2, b_desc + 2, idesc, 1u);
+              umma_bf16(d, a_desc + 4, b_desc + 4, idesc, 1u);
+              umma_bf16(d, a_desc + 6, b_desc + 6, idesc, 1u);
+              umma_commit(smem_u32(&cx.misc->empty[seq % kChunkBars]));
+              ++seq;
+            }
+            accumulate = 1u;
+            ++slot;
+            if (!streamed && slot == kslice) slot = 0;
+          }
+          if (streamed) umma_commit(smem_u32(&cx.misc->bempty[h]));
         }
         umma_commit(smem_u32(&cx.misc->accfull[buf]));
         ++q;
@@ -306,12 +369,28 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
   return make_uint4(pack2(f[0], f[1]), pack2(f[2], f[3]), pack2(f[4], f[5]), pack2(f[6], f[7]));
 }
 
+// Swizzled (SWIZZLE_128B, K-major) address of 8 elements: slot = K chunk, t = token row, vec = 16-byte column.
+__device__ __forceinline__ uint8_t* b_slot_addr(const Ctx& cx, int slot, int t, int vec) {
+  return cx.smem_b + slot * kBSlotBytes + (t >> 3) * 1024 + (t & 7) * 128 + ((vec ^ (t & 7)) << 4);
+}
+
+// Normalise one 8-element vector: w * bf16(x * rinv), the two roundings of the
+// Hugging Face RMSNorm.
+__device__ __forceinline__ uint4 normalise_vec(const uint4 xu, const uint4 wu, float r) {
+  float x[8], w[8];
+  unpack8(xu, x);
+  unpack8(wu, w);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) x[e] = w[e] * bf16_round(x[e] * r);
+  return pack8(x);
+}
+
 // RMSNorm statistics of the rows of one token tile: rinv[t] = 1/sqrt(mean(x^2)+eps).
 // One warp per token; eight 16-byte loads are in flight per lane before any is used.
 __device__ __noinline__ void norm_stats(const Ctx& cx, const GemmPhase* ph, int t0, int mt, int wtid) {
   const KParams& p = *cx.p;
   const int warp = wtid >> 5, lane = wtid & 31;
-  const int nvec = p.hidden / 8;
+  const int nvec = ph->k / 8;
   for (int t = warp; t < mt; t += kWorkerWarps) {
     const uint4* row = reinterpret_cast<const uint4*>(activation_row(p, ph, t0 + t));
     float sum = 0.f;
@@ -331,73 +410,202 @@ __device__ __noinline__ void norm_stats(const Ctx& cx, const GemmPhase* ph, int 
       }
     }
     sum = warp_sum(sum);
-    if (lane == 0) cx.misc->rinv[t] = 1.0f / sqrtf(sum / static_cast<float>(p.hidden) + p.eps);
+    if (lane == 0) cx.misc->rinv[t] = 1.0f / sqrtf(sum / static_cast<float>(ph->k) + p.eps);
   }
   named_bar_sync(1, kWorkers);
 }
 
-// Normalise one 8-element vector: w * bf16(x * rinv), the two roundings of the
-// Hugging Face RMSNorm.
-__device__ __forceinline__ uint4 normalise_vec(const uint4& xu, const uint4& wu, float r) {
-  float x[8], w[8];
-  unpack8(xu, x);
-  unpack8(wu, w);
+// RMSNorm fused with staging for a reduction length that fits the activation
+// slots (K <= 2048): one warp per token keeps the row in registers between the
+// statistics and the normalised store, so the row is read once.
+__device__ __noinline__ void stage_norm_resident(const Ctx& cx, const GemmPhase* ph, int t0, int mt, int wtid) {
+  const KParams& p = *cx.p;
+  const int warp = wtid >> 5, lane = wtid & 31;
+  const int nvec = ph->k / 8;  // <= 256
+  const uint4* wrow = reinterpret_cast<const uint4*>(ph->normw);
+  for (int t = warp; t < mt; t += kWorkerWarps) {
+    const uint4* row = reinterpret_cast<const uint4*>(activation_row(p, ph, t0 + t));
+    uint4 x[8], w[8];
 #pragma unroll
-  for (int e = 0; e < 8; ++e) x[e] = w[e] * bf16_round(x[e] * r);
-  return pack8(x);
+    for (int i = 0; i < 8; ++i) {
+      const int v = i * 32 + lane;
+      x[i] = make_uint4(0, 0, 0, 0);
+      w[i] = x[i];
+      if (v < nvec) {
+        x[i] = __ldcg(row + v);
+        w[i] = __ldg(wrow + v);
+      }
+    }
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float f[8];
+      unpack8(x[i], f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sum = fmaf(f[e], f[e], sum);
+    }
+    sum = warp_sum(sum);
+    const float r = 1.0f / sqrtf(sum / static_cast<float>(ph->k) + p.eps);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int v = i * 32 + lane;
+      if (v < nvec) *reinterpret_cast<uint4*>(b_slot_addr(cx, v >> 3, t, v & 7)) = normalise_vec(x[i], w[i], r);
+    }
+  }
 }
 
-// One 8-element vector of the activation operand (normalised if the phase asks).
-__device__ __forceinline__ uint4 activation_vec(const Ctx& cx, const GemmPhase* ph, const bf16* row, int t, int col) {
-  const uint4 u = __ldcg(reinterpret_cast<const uint4*>(row + col));
+// RMSNorm fused with staging, one token at a time over the whole worker block
+// (two 8-element vectors per thread, K <= 2048).  This variant also applies the
+// pending residual update: x = residual + bf16(sum of the previous projection's
+// fp32 K-slice partials, in slice order), writes this CTA's share of x back as
+// the new residual stream, and normalises x.  Every load of a token is issued
+// before the first is used.
+__device__ __noinline__ void stage_norm_block(const Ctx& cx, const GemmPhase* ph, int t0, int mt, int wtid) {
+  const KParams& p = *cx.p;
+  const int warp = wtid >> 5, lane = wtid & 31;
+  const int nvec = ph->k / 8;  // <= 256
+  const int parts = ph->add_parts;
+  const int writers = min(cx.grid, ph->nunits);  // only CTAs that have a unit in this phase get here
+  const uint4* wrow = reinterpret_cast<const uint4*>(ph->normw);
+  for (int t = 0; t < mt; ++t) {
+    const uint4* row = reinterpret_cast<const uint4*>(activation_row(p, ph, t0 + t));
+    uint4 x[2], w[2];
+    float4 lo[2][kMaxSplit], hi[2][kMaxSplit];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int v = i * kWorkers + wtid;
+      x[i] = make_uint4(0, 0, 0, 0);
+      w[i] = x[i];
+      if (v < nvec) {
+        x[i] = __ldcg(row + v);
+        w[i] = __ldg(wrow + v);
+#pragma unroll
+        for (int s8 = 0; s8 < kMaxSplit; ++s8) {
+          if (s8 < parts) {
+            const float4* part = reinterpret_cast<const float4*>(
+                ph->partial + (static_cast<size_t>(s8) * p.m + (t0 + t)) * ph->k) + v * 2;
+            lo[i][s8] = __ldcg(part);
+            hi[i][s8] = __ldcg(part + 1);
+          }
+        }
+      }
+    }
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int v = i * kWorkers + wtid;
+      float f[8];
+      unpack8(x[i], f);
+      if (parts > 0 && v < nvec) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int s8 = 0; s8 < kMaxSplit; ++s8) {
+          if (s8 < parts) {
+            acc[0] += lo[i][s8].x; acc[1] += lo[i][s8].y; acc[2] += lo[i][s8].z; acc[3] += lo[i][s8].w;
+            acc[4] += hi[i][s8].x; acc[5] += hi[i][s8].y; acc[6] += hi[i][s8].z; acc[7] += hi[i][s8].w;
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = bf16_round(f[e] + bf16_round(acc[e]));
+        x[i] = pack8(f);
+      }
+      if (ph->h_out && v < nvec && (v * writers) / nvec == cx.cta)
+        __stcg(reinterpret_cast<uint4*>(ph->h_out + static_cast<size_t>(t0 + t) * ph->k) + v, x[i]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sum = fmaf(f[e], f[e], sum);
+    }
+    sum = warp_sum(sum);
+    named_bar_sync(1, kWorkers);  // red4 of the previous token has been read
+    if (lane == 0) cx.misc->red4[warp] = sum;
+    named_bar_sync(1, kWorkers);
+    const float total = ((cx.misc->red4[0] + cx.misc->red4[1]) + cx.misc->red4[2]) + cx.misc->red4[3];
+    const float r = 1.0f / sqrtf(total / static_cast<float>(ph->k) + p.eps);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int v = i * kWorkers + wtid;
+      if (v < nvec) *reinterpret_cast<uint4*>(b_slot_addr(cx, v >> 3, t, v & 7)) = normalise_vec(x[i], w[i], r);
+    }
+  }
+}
+
+// Attention output for 8 consecutive columns of one token: the bf16 buffer when
+// the context was not split, else the chunk partials summed in chunk order and
+// rounded once.
+__device__ __forceinline__ uint4 attention_vec(const KParams& p, int token, int col, int nch) {
+  if (nch <= 1) return __ldcg(reinterpret_cast<const uint4*>(p.attn + static_cast<size_t>(token) * p.q_heads * p.head_dim + col));
+  const int head = col / p.head_dim, d = col - head * p.head_dim;
+  const float4* part = reinterpret_cast<const float4*>(
+      p.att_part + (static_cast<size_t>(token) * p.q_heads + head) * kMaxChunks * p.head_dim + d);
+  const int stride = p.head_dim / 4;  // float4s per chunk
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  for (int c0 = 0; c0 < nch; c0 += 4) {
+    float4 lo[4], hi[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (c0 + i < nch) {
+        lo[i] = __ldcg(part + (c0 + i) * stride);
+        hi[i] = __ldcg(part + (c0 + i) * stride + 1);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (c0 + i < nch) {
+        acc[0] += lo[i].x; acc[1] += lo[i].y; acc[2] += lo[i].z; acc[3] += lo[i].w;
+        acc[4] += hi[i].x; acc[5] += hi[i].y; acc[6] += hi[i].z; acc[7] += hi[i].w;
+      }
+    }
+  }
+  return pack8(acc);
+}
+
+// One 8-element vector of the activation operand for (token, column).
+__device__ __forceinline__ uint4 activation_vec(const Ctx& cx, const GemmPhase* ph, int token, int t, int col,
+                                                int nch) {
+  const KParams& p = *cx.p;
+  if (ph->bmode == B_ATTN) return attention_vec(p, token, col, nch);
+  const uint4 u = __ldcg(reinterpret_cast<const uint4*>(activation_row(p, ph, token) + col));
   if (ph->bmode != B_NORM) return u;
   return normalise_vec(u, __ldg(reinterpret_cast<const uint4*>(ph->normw + col)), cx.misc->rinv[t]);
 }
 
-// Fill the swizzled (SWIZZLE_128B, K-major) activation slots this CTA's chunk
-// range needs.  Loads are issued four at a time per thread before any is used.
-__device__ __noinline__ void stage_b(const Ctx& cx, const GemmPhase* ph, const Range& r, int t0, int mt, int wtid) {
+// Stage K chunks [k0, k1) of the token tile into slots slot0, slot0+1, ...
+// (B_NORM expects rinv to be ready).  Plain loads go four at a time per thread.
+__device__ __noinline__ void stage_chunks(const Ctx& cx, const GemmPhase* ph, int k0, int k1, int slot0, int t0, int mt,
+                                          int wtid, int nch) {
   const KParams& p = *cx.p;
-  const bool norm = ph->bmode == B_NORM;
-  if (norm) norm_stats(cx, ph, t0, mt, wtid);
-  const int nacc = ph->nacc, kc = ph->kc;
-  const long long ks0 = r.c0 / nacc;
-  const long long ks1 = (r.c1 + nacc - 1) / nacc;
-  const bool all_k = (ks1 - ks0) >= kc;
-  const int nk = all_k ? kc : static_cast<int>(ks1 - ks0);
   const int per_slot = mt * 8;
-  const int items = nk * per_slot;
-  const bf16* normw = ph->normw;
-  for (int item0 = wtid; item0 < items; item0 += kWorkers * 4) {
-    uint4 xu[4], wu[4];
-    int slot[4], tok[4], vec[4];
+  const int items = (k1 - k0) * per_slot;
+  if (ph->bmode == B_PLAIN) {
+    for (int item0 = wtid; item0 < items; item0 += kWorkers * 4) {
+      uint4 xu[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int item = item0 + i * kWorkers;
-      if (item < items) {
-        slot[i] = item / per_slot;
-        const int rem = item - slot[i] * per_slot;
-        tok[i] = rem >> 3;
-        vec[i] = rem & 7;
-        const int kidx = all_k ? slot[i] : static_cast<int>((ks0 + slot[i]) % kc);
-        const int col = kidx * kChunkK + vec[i] * 8;
-        xu[i] = __ldcg(reinterpret_cast<const uint4*>(activation_row(p, ph, t0 + tok[i]) + col));
-        if (norm) wu[i] = __ldg(reinterpret_cast<const uint4*>(normw + col));
+      for (int i = 0; i < 4; ++i) {
+        const int item = item0 + i * kWorkers;
+        if (item < items) {
+          const int s = item / per_slot, rem = item - s * per_slot;
+          xu[i] = __ldcg(reinterpret_cast<const uint4*>(activation_row(p, ph, t0 + (rem >> 3)) + (k0 + s) * kChunkK +
+                                                        (rem & 7) * 8));
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int item = item0 + i * kWorkers;
+        if (item < items) {
+          const int s = item / per_slot, rem = item - s * per_slot;
+          *reinterpret_cast<uint4*>(b_slot_addr(cx, slot0 + s, rem >> 3, rem & 7)) = xu[i];
+        }
       }
     }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int item = item0 + i * kWorkers;
-      if (item < items) {
-        const uint4 u = norm ? normalise_vec(xu[i], wu[i], cx.misc->rinv[tok[i]]) : xu[i];
-        uint8_t* dst = cx.smem_b + slot[i] * kBSlotBytes + (tok[i] >> 3) * 1024 + (tok[i] & 7) * 128 +
-                       ((vec[i] ^ (tok[i] & 7)) << 4);
-        *reinterpret_cast<uint4*>(dst) = u;
-      }
-    }
+    return;
   }
-  fence_proxy_async_smem();
-  mbar_arrive(smem_u32(&cx.misc->bfull));
+  for (int item = wtid; item < items; item += kWorkers) {
+    const int s = item / per_slot, rem = item - s * per_slot;
+    const int t = rem >> 3, vec = rem & 7;
+    *reinterpret_cast<uint4*>(b_slot_addr(cx, slot0 + s, t, vec)) =
+        activation_vec(cx, ph, t0 + t, t, (k0 + s) * kChunkK + vec * 8, nch);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -405,202 +613,247 @@ __device__ __noinline__ void stage_b(const Ctx& cx, const GemmPhase* ph, const R
 
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
 
-__device__ void apply_epilogue(const Ctx& cx, const GemmPhase* ph, int tile, int rloc, float (*v)[kTok], int t0,
-                               int mt) {
+__device__ __forceinline__ float ldcg_bf16(const bf16* ptr) {
+  return __bfloat162float(__ushort_as_bfloat16(__ldcg(reinterpret_cast<const unsigned short*>(ptr))));
+}
+
+// Values an epilogue adds to the accumulators; loaded before the accumulator
+// wait so their latency hides behind the MMA: the residual stream (per token)
+// or the bias (one value).
+__device__ __forceinline__ void epilogue_prefetch(const Ctx& cx, const GemmPhase* ph, int seg, int n, int t0, int mt,
+                                                  float* pre) {
+  if (ph->epi == EPI_RESIDUAL) {
+#pragma unroll
+    for (int t = 0; t < kTok; ++t)
+      if (t < mt) pre[t] = ldcg_bf16(ph->dst + static_cast<size_t>(t0 + t) * ph->dst_ld + n);
+  } else if (ph->epi == EPI_STORE) {
+    pre[0] = ph->bias[seg] ? ldg_bf16(ph->bias[seg] + n) : 0.f;
+  }
+}
+
+// EPI_PARTIAL: this unit's fp32 sums over its K slice, for the next phase to add up.
+__device__ __forceinline__ void store_partial(const Ctx& cx, const GemmPhase* ph, int slice, int n, const float* v,
+                                              int t0, int mt) {
+#pragma unroll
+  for (int t = 0; t < kTok; ++t)
+    if (t < mt) __stcg(ph->partial + (static_cast<size_t>(slice) * cx.p->m + (t0 + t)) * ph->n[0] + n, v[t]);
+}
+
+// Finish output row n of matrix `seg` for the tokens of the tile.
+__device__ __forceinline__ void apply_epilogue(const Ctx& cx, const GemmPhase* ph, int seg, int n, float (*v)[kTok],
+                                               const float* pre, int t0, int mt) {
   const KParams& p = *cx.p;
-  if (ph->nacc == 2) {
-    const int n = tile * kTileRows + rloc;
-    if (n >= ph->n[0]) return;
-    for (int t = 0; t < mt; ++t) {
-      const float gate = bf16_round(v[0][t]);
-      const float up = bf16_round(v[1][t]);
-      const float act = bf16_round(silu(gate));
-      ph->dst[static_cast<size_t>(t0 + t) * ph->dst_ld + n] = __float2bfloat16_rn(act * up);
+  if (ph->epi == EPI_SILU) {
+#pragma unroll
+    for (int t = 0; t < kTok; ++t) {
+      if (t < mt) {
+        const float gate = bf16_round(v[0][t]);
+        const float up = bf16_round(v[1][t]);
+        const float act = bf16_round(silu(gate));
+        ph->dst[static_cast<size_t>(t0 + t) * ph->dst_ld + n] = __float2bfloat16_rn(act * up);
+      }
     }
     return;
   }
-  const int seg = segment_of_tile(ph, tile);
-  const int n = (tile - ph->tile_start[seg]) * kTileRows + rloc;
-  if (n >= ph->n[seg]) return;
   bf16* dst = ph->to_logits ? p.logits : ph->dst;
   const size_t col = static_cast<size_t>(ph->out_col[seg]) + n;
   if (ph->epi == EPI_STORE) {
-    const float bias = ph->bias[seg] ? ldg_bf16(ph->bias[seg] + n) : 0.f;
-    for (int t = 0; t < mt; ++t)
-      dst[static_cast<size_t>(t0 + t) * ph->dst_ld + col] = __float2bfloat16_rn(v[0][t] + bias);
+#pragma unroll
+    for (int t = 0; t < kTok; ++t)
+      if (t < mt) dst[static_cast<size_t>(t0 + t) * ph->dst_ld + col] = __float2bfloat16_rn(v[0][t] + pre[0]);
   } else {  // EPI_RESIDUAL: hidden += bf16(projection), in place
-    for (int t = 0; t < mt; ++t) {
-      bf16* h = dst + static_cast<size_t>(t0 + t) * ph->dst_ld + col;
-      const unsigned short raw = __ldcg(reinterpret_cast<const unsigned short*>(h));
-      const float residual = __bfloat162float(__ushort_as_bfloat16(raw));
-      *h = __float2bfloat16_rn(residual + bf16_round(v[0][t]));
-    }
+#pragma unroll
+    for (int t = 0; t < kTok; ++t)
+      if (t < mt) dst[static_cast<size_t>(t0 + t) * ph->dst_ld + col] = __float2bfloat16_rn(pre[t] + bf16_round(v[0][t]));
   }
 }
 
-// Split-K completion for one tile segment.  The CTA that holds the tile's first
-// chunk reduces: for it the tile is the last segment of its range, so by then
-// the other contributors (for which the tile comes first) have published their
-// fp32 partials.  Contributors store, fence, count themselves and move on; the
-// reducer waits (bounded) for the count, then adds the partials to its own
-// accumulators in CTA order, which fixes the summation order.
-__device__ __noinline__ bool finish_split(const Ctx& cx, const GemmPhase* ph, const Range& r, int tile, int rloc,
-                             float (*v)[kTok], int t0, int mt, int wtid) {
-  const KParams& p = *cx.p;
-  const int tc = ph->tc, nacc = ph->nacc;
-  const long long total = ph->total;
-  const int first = cta_of_chunk(static_cast<long long>(tile) * tc, total, r.geff);
-  const int last = cta_of_chunk(static_cast<long long>(tile + 1) * tc - 1, total, r.geff);
-  if (cx.cta != first) {
-    const int slot = (static_cast<int>(r.c0 / tc) == tile) ? 0 : 1;
-    float* mine = p.partials + static_cast<size_t>(cx.cta * 2 + slot) * kPartialFloats;
-    for (int a = 0; a < nacc; ++a)
-      for (int t = 0; t < mt; ++t) __stcg(mine + (a * kTok + t) * kTileRows + rloc, v[a][t]);
-    __threadfence();
-    named_bar_sync(1, kWorkers);
-    if (wtid == 0) red_release_add_u32(&p.tile_ctr[tile], 1u);
-    return true;
-  }
-  if (wtid == 0) {
-    const uint32_t expected = static_cast<uint32_t>(last - first);
-    uint32_t spins = 0;
-    while (ld_relaxed_u32(&p.tile_ctr[tile]) < expected) {
-      if ((++spins & 255u) == 0 && give_up(cx, SITE_SPLIT_REDUCE, tile)) {
-        cx.misc->wabort = 1;
-        break;
-      }
-    }
-    p.tile_ctr[tile] = 0;  // the next use is behind a grid barrier
-    __threadfence();
-  }
-  named_bar_sync(1, kWorkers);
-  if (*reinterpret_cast<volatile int*>(&cx.misc->wabort)) return false;
-  for (int g0 = first + 1; g0 <= last; g0 += 4) {
-    float part[4][2];
-    for (int t = 0; t < mt; ++t) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int g = g0 + i;
-        if (g <= last) {
-          const int gslot = (static_cast<int>((g * total / r.geff) / tc) == tile) ? 0 : 1;
-          const float* theirs = p.partials + static_cast<size_t>(g * 2 + gslot) * kPartialFloats;
-          part[i][0] = __ldcg(theirs + t * kTileRows + rloc);
-          if (nacc == 2) part[i][1] = __ldcg(theirs + (kTok + t) * kTileRows + rloc);
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        if (g0 + i <= last) {
-          v[0][t] += part[i][0];
-          if (nacc == 2) v[1][t] += part[i][1];
-        }
-      }
-    }
-  }
-  apply_epilogue(cx, ph, tile, rloc, v, t0, mt);
-  return true;
+// Copy the next projection phase's descriptor into shared memory so that no
+// worker pays a global round trip for it after the barrier.
+__device__ __forceinline__ void prefetch_phase(const Ctx& cx, int gp, int wtid) {
+  if (gp >= cx.p->n_gemm) return;
+  const uint32_t* src = reinterpret_cast<const uint32_t*>(cx.p->phases + gp);
+  uint32_t* dst = reinterpret_cast<uint32_t*>(&cx.misc->phase[gp & 1]);
+  for (int i = wtid; i < static_cast<int>(sizeof(GemmPhase) / 4); i += kWorkers) dst[i] = __ldg(src + i);
 }
 
-// Projection phase on the tcgen05 engine, worker side.
-__device__ bool worker_gemm_tc(const Ctx& cx, int gp, uint32_t& q, uint32_t& passed, int wtid) {
+// Wait until the MMA issuer has finished with the streamed batch last staged on half h.
+__device__ __forceinline__ bool acquire_half(const Ctx& cx, WorkerState& ws, int h, int gp) {
+  if (!ws.outstanding[h]) return true;
+  const bool ok = wait_mbar(cx, smem_u32(&cx.misc->bempty[h]), ws.be_cnt[h] & 1u, SITE_B_EMPTY, gp);
+  ws.be_cnt[h] += 1;
+  ws.outstanding[h] = false;
+  return ok;
+}
+
+// Build the activation operand for K chunks [k0, k0 + count) of the token tile in slots 0.. (not streamed).
+__device__ __forceinline__ void stage_resident(const Ctx& cx, const GemmPhase* ph, int k0, int count, int t0, int mt,
+                                               int wtid, int nch) {
+  if (ph->bmode == B_NORM) {
+    if (ph->add_parts > 0 || ph->h_out != nullptr || mt <= 2) stage_norm_block(cx, ph, t0, mt, wtid);
+    else stage_norm_resident(cx, ph, t0, mt, wtid);
+  } else {
+    stage_chunks(cx, ph, k0, k0 + count, 0, t0, mt, wtid, nch);
+  }
+  fence_proxy_async_smem();
+  mbar_arrive(smem_u32(&cx.misc->bfull[0]));
+  if (count > kBHalf) mbar_arrive(smem_u32(&cx.misc->bfull[1]));
+}
+
+// Projection phase on the tcgen05 engine, worker side.  The caller has made
+// phase gp's descriptor visible in cx.misc->phase[gp & 1].
+__device__ __noinline__ bool worker_gemm_tc(const Ctx& cx, int gp, WorkerState& ws, int wtid) {
   const KParams& p = *cx.p;
-  const GemmPhase* ph = p.phases + gp;
-  const Range r = cta_range(ph, cx.cta, cx.grid);
+  const GemmPhase* ph = &cx.misc->phase[gp & 1];
   const int ntt = (p.m + kTok - 1) / kTok;
-  const int tc = ph->tc, nacc = ph->nacc;
+  const int nacc = ph->nacc, nunits = ph->nunits, rows = ph->rows, ksplit = ph->ksplit, kslice = ph->kslice;
+  const bool per_unit = ksplit > 1;
+  const bool streamed = kslice > kBSlots;
   const int quad = ((wtid >> 5) + 2) & 3;  // TMEM lane quadrant this warp may read
   const int rloc = quad * 32 + (wtid & 31);
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&cx.misc->tmem_base);
-  for (int tt = 0; tt < ntt; ++tt) {
-    // Partials and tile counters are reused by the next token tile.
-    if (tt > 0 && !grid_barrier(cx, passed, wtid)) return false;
-    if (r.c1 <= r.c0) continue;
-    const int t0 = tt * kTok;
-    const int mt = min(kTok, p.m - t0);
-    trace_event(cx, wtid, EV_PHASE_ENTER);
-    stage_b(cx, ph, r, t0, mt, wtid);
-    trace_event(cx, wtid, EV_B_STAGED);
-    long long c = r.c0;
-    while (c < r.c1) {
-      const int tile = static_cast<int>(c / tc);
-      const long long tile_c0 = static_cast<long long>(tile) * tc;
-      long long seg_end = tile_c0 + tc;
-      if (seg_end > r.c1) seg_end = r.c1;
-      const bool complete = (c == tile_c0) && (seg_end == tile_c0 + tc);
-      const uint32_t buf = q & 1u;
-      bool ok = wait_mbar(cx, smem_u32(&cx.misc->accfull[buf]), (q >> 1) & 1u, SITE_EPI_ACC, gp);
-      ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below needs the whole warp
-      if (c == r.c0) trace_event(cx, wtid, EV_FIRST_ACC);
-      tc_fence_after();
-      float v[2][kTok];
-      if (ok) {
-        for (int a = 0; a < nacc; ++a) {
-          const bool has = (nacc == 1) || (seg_end - c >= 2) || (((c & 1) != 0) == (a == 1));
-          if (has) {
-            tmem_ld16(tmem + (static_cast<uint32_t>(quad * 32) << 16) + (buf * 2u + a) * kTok, v[a]);
-          } else {
-#pragma unroll
-            for (int t = 0; t < kTok; ++t) v[a][t] = 0.f;
+  const int nch = (ph->bmode == B_ATTN) ? *reinterpret_cast<volatile int*>(&cx.ctrl->att_nch) : 1;
+  if (cx.cta < nunits) {
+    for (int tt = 0; tt < ntt; ++tt) {
+      const int t0 = tt * kTok;
+      const int mt = min(kTok, p.m - t0);
+      trace_event(cx, wtid, EV_PHASE_ENTER);
+      if (streamed && ph->bmode == B_NORM) norm_stats(cx, ph, t0, mt, wtid);
+      for (int unit = cx.cta; unit < nunits; unit += cx.grid) {
+        const int tile = unit / ksplit, slice = unit - tile * ksplit;
+        if (!streamed) {
+          if (per_unit || unit == cx.cta) {
+            bool ok = acquire_half(cx, ws, 0, gp);
+            ok = acquire_half(cx, ws, 1, gp) && ok;
+            if (!workers_ok(cx, ok)) return false;
+            stage_resident(cx, ph, slice * kslice, kslice, t0, mt, wtid, nch);
+            if (unit == cx.cta) trace_event(cx, wtid, EV_B_STAGED);
+          }
+        } else {
+          const int batches = (kslice + kBHalf - 1) / kBHalf;
+          const int rot = k_rotation(cx.cta, cx.grid, kslice);
+          for (int vb = 0; vb < batches; ++vb) {
+            const int b = (rot + vb) % batches, h = vb & 1;
+            if (!workers_ok(cx, acquire_half(cx, ws, h, gp))) return false;
+            const int k0 = slice * kslice + b * kBHalf;
+            stage_chunks(cx, ph, k0, min(slice * kslice + kslice, k0 + kBHalf), h * kBHalf, t0, mt, wtid, nch);
+            fence_proxy_async_smem();
+            mbar_arrive(smem_u32(&cx.misc->bfull[h]));
+            ws.outstanding[h] = true;
           }
         }
+        int seg, row0;
+        tile_origin(ph, tile, seg, row0);
+        const int n = row0 + rloc;
+        const bool valid = rloc < rows && n < ph->n[seg];
+        float pre[kTok];
+        if (valid) epilogue_prefetch(cx, ph, seg, n, t0, mt, pre);
+        const uint32_t buf = ws.tiles & 1u;
+        bool ok = wait_mbar(cx, smem_u32(&cx.misc->accfull[buf]), (ws.tiles >> 1) & 1u, SITE_EPI_ACC, gp);
+        ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below needs the whole warp
+        if (unit == cx.cta) trace_event(cx, wtid, EV_FIRST_ACC);
+        tc_fence_after();
+        float v[2][kTok];
+        if (ok && quad * 32 < rows) {
+          tmem_ld16(tmem + (static_cast<uint32_t>(quad * 32) << 16) + (buf * 2u) * kTok, v[0]);
+          if (nacc == 2) tmem_ld16(tmem + (static_cast<uint32_t>(quad * 32) << 16) + (buf * 2u + 1u) * kTok, v[1]);
+        }
+        tc_fence_before();
+        mbar_arrive(smem_u32(&cx.misc->accempty[buf]));
+        ws.tiles += 1;
+        if (!workers_ok(cx, ok)) return false;
+        if (valid) {
+          if (ph->epi == EPI_PARTIAL) store_partial(cx, ph, slice, n, v[0], t0, mt);
+          else apply_epilogue(cx, ph, seg, n, v, pre, t0, mt);
+        }
       }
-      tc_fence_before();
-      mbar_arrive(smem_u32(&cx.misc->accempty[buf]));
-      ++q;
-      if (!workers_ok(cx, ok)) return false;
-      if (complete) {
-        apply_epilogue(cx, ph, tile, rloc, v, t0, mt);
-      } else {
-        if (!finish_split(cx, ph, r, tile, rloc, v, t0, mt, wtid)) return false;
-      }
-      c = seg_end;
+      trace_event(cx, wtid, EV_PHASE_DONE);
     }
-    trace_event(cx, wtid, EV_PHASE_DONE);
   }
+  prefetch_phase(cx, gp + 1, wtid);
   return true;
 }
 
-// Projection phase on the SIMT engine (bring-up / diagnostics): every worker
-// warp of the grid takes output rows round-robin and does plain dot products.
-__device__ __noinline__ bool worker_gemm_simt(const Ctx& cx, int gp, uint32_t& passed, int wtid) {
+// One 8-element vector of the residual stream after the pending update (see stage_norm_block).
+__device__ __forceinline__ uint4 residual_vec(const Ctx& cx, const GemmPhase* ph, int token, int v) {
   const KParams& p = *cx.p;
-  const GemmPhase* ph = p.phases + gp;
+  const uint4 xu = __ldcg(reinterpret_cast<const uint4*>(activation_row(p, ph, token)) + v);
+  if (ph->add_parts == 0) return xu;
+  float f[8], acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  unpack8(xu, f);
+  for (int s8 = 0; s8 < ph->add_parts; ++s8) {
+    const float4* part = reinterpret_cast<const float4*>(ph->partial + (static_cast<size_t>(s8) * p.m + token) * ph->k) + v * 2;
+    const float4 lo = __ldcg(part), hi = __ldcg(part + 1);
+    acc[0] += lo.x; acc[1] += lo.y; acc[2] += lo.z; acc[3] += lo.w;
+    acc[4] += hi.x; acc[5] += hi.y; acc[6] += hi.z; acc[7] += hi.w;
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) f[e] = bf16_round(f[e] + bf16_round(acc[e]));
+  return pack8(f);
+}
+
+// Projection phase on the SIMT engine (bring-up / diagnostics): every worker
+// warp of the grid takes output rows round-robin and does plain dot products
+// over the whole reduction length (a K-split phase gets the full sum in slice 0
+// and zeros in the other slices).
+__device__ __noinline__ bool worker_gemm_simt(const Ctx& cx, int gp, int wtid) {
+  const KParams& p = *cx.p;
+  const GemmPhase* ph = &cx.misc->phase[gp & 1];
   const int warp = wtid >> 5, lane = wtid & 31;
-  const int k = ph->k;
+  const int k = ph->k, nvec = k / 8;
   int tb = kBBytes / (k * 2);
   if (tb > kTok) tb = kTok;
   if (tb < 1) tb = 1;
   bf16* bs = reinterpret_cast<bf16*>(cx.smem_b);
+  const int nch = (ph->bmode == B_ATTN) ? *reinterpret_cast<volatile int*>(&cx.ctrl->att_nch) : 1;
+  int total_rows = 0;
+  for (int s = 0; s < (ph->nacc == 2 ? 1 : ph->nseg); ++s) total_rows += ph->n[s];
   float v[2][kTok];
+  float pre[kTok];
   for (int t0 = 0; t0 < p.m; t0 += tb) {
     const int mt = min(tb, p.m - t0);
     named_bar_sync(1, kWorkers);
-    if (ph->bmode == B_NORM) norm_stats(cx, ph, t0, mt, wtid);
-    for (int item = wtid; item < mt * (k / 8); item += kWorkers) {
-      const int t = item / (k / 8), vec = item % (k / 8);
-      const uint4 u = activation_vec(cx, ph, activation_row(p, ph, t0 + t), t, vec * 8);
-      *reinterpret_cast<uint4*>(bs + t * k + vec * 8) = u;
+    if (ph->bmode == B_NORM) {
+      for (int item = wtid; item < mt * nvec; item += kWorkers) {
+        const int t = item / nvec, vec = item - t * nvec;
+        const uint4 xu = residual_vec(cx, ph, t0 + t, vec);
+        *reinterpret_cast<uint4*>(bs + t * k + vec * 8) = xu;
+        if (ph->h_out && (vec * cx.grid) / nvec == cx.cta)
+          __stcg(reinterpret_cast<uint4*>(ph->h_out + static_cast<size_t>(t0 + t) * k) + vec, xu);
+      }
+      named_bar_sync(1, kWorkers);
+      for (int t = warp; t < mt; t += kWorkerWarps) {
+        float sum = 0.f;
+        for (int vec = lane; vec < nvec; vec += 32) {
+          float f[8];
+          unpack8(*reinterpret_cast<const uint4*>(bs + t * k + vec * 8), f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) sum = fmaf(f[e], f[e], sum);
+        }
+        sum = warp_sum(sum);
+        const float r = 1.0f / sqrtf(sum / static_cast<float>(k) + p.eps);
+        for (int vec = lane; vec < nvec; vec += 32) {
+          uint4* at = reinterpret_cast<uint4*>(bs + t * k + vec * 8);
+          *at = normalise_vec(*at, __ldg(reinterpret_cast<const uint4*>(ph->normw) + vec), r);
+        }
+      }
+    } else {
+      for (int item = wtid; item < mt * nvec; item += kWorkers) {
+        const int t = item / nvec, vec = item - t * nvec;
+        *reinterpret_cast<uint4*>(bs + t * k + vec * 8) = activation_vec(cx, ph, t0 + t, t, vec * 8, nch);
+      }
     }
     named_bar_sync(1, kWorkers);
-    const int total_rows = ph->ntiles * kTileRows;
     for (int row = cx.cta * kWorkerWarps + warp; row < total_rows; row += cx.grid * kWorkerWarps) {
-      const int tile = row / kTileRows, rloc = row % kTileRows;
+      int seg = 0, n = row;
+      if (ph->nacc == 1) {
+        while (seg + 1 < ph->nseg && n >= ph->n[seg]) { n -= ph->n[seg]; ++seg; }
+      }
       for (int a = 0; a < ph->nacc; ++a) {
-        const bf16* w;
-        int n;
-        if (ph->nacc == 2) {
-          n = row;
-          w = ph->w[a];
-          if (n >= ph->n[0]) { for (int t = 0; t < mt; ++t) v[a][t] = 0.f; continue; }
-        } else {
-          const int seg = segment_of_tile(ph, tile);
-          n = (tile - ph->tile_start[seg]) * kTileRows + rloc;
-          w = ph->w[seg];
-          if (n >= ph->n[seg]) { for (int t = 0; t < mt; ++t) v[a][t] = 0.f; continue; }
-        }
+        const bf16* w = ph->w[ph->nacc == 2 ? a : seg];
         const uint4* wrow = reinterpret_cast<const uint4*>(w + static_cast<size_t>(n) * k);
         for (int t = 0; t < mt; ++t) v[a][t] = 0.f;
-        for (int vec = lane; vec < k / 8; vec += 32) {
+        for (int vec = lane; vec < nvec; vec += 32) {
           float wf[8], xf[8];
           unpack8(__ldg(wrow + vec), wf);
           for (int t = 0; t < mt; ++t) {
@@ -611,10 +864,20 @@ __device__ __noinline__ bool worker_gemm_simt(const Ctx& cx, int gp, uint32_t& p
         }
         for (int t = 0; t < mt; ++t) v[a][t] = warp_sum(v[a][t]);
       }
-      if (lane == 0) apply_epilogue(cx, ph, tile, rloc, v, t0, mt);
+      if (lane == 0) {
+        if (ph->epi == EPI_PARTIAL) {
+          store_partial(cx, ph, 0, n, v[0], t0, mt);
+          for (int t = 0; t < mt; ++t) v[1][t] = 0.f;
+          for (int s8 = 1; s8 < ph->ksplit; ++s8) store_partial(cx, ph, s8, n, v[1], t0, mt);
+        } else {
+          epilogue_prefetch(cx, ph, seg, n, t0, mt, pre);
+          apply_epilogue(cx, ph, seg, n, v, pre, t0, mt);
+        }
+      }
     }
   }
-  (void)passed;
+  named_bar_sync(1, kWorkers);
+  prefetch_phase(cx, gp + 1, wtid);
   return true;
 }
 
@@ -637,30 +900,10 @@ struct AttnArgs {
   int decode;         // 1: append the new key/value at `len` and attend over [0, len]
   int rope;           // 1: rotate q and the new key while loading (decode)
   int causal;         // prefill without a mask tensor: key j <= query qi
+  int combine;        // 1: a split context is summed here into `out`; 0: the consumer sums att_part
+  uint32_t stamp;     // value the chunks of this phase publish with their softmax statistics
   float scale;
 };
-
-// Publish one value per query head of this chunk, wait (bounded) until every
-// chunk of the row group has published.
-__device__ bool attn_exchange(const Ctx& cx, float* slots, uint32_t* counter, int rowg, int ch, int nch, int gs,
-                              const float* mine, int wtid) {
-  if (wtid < gs) __stcg(slots + (static_cast<size_t>(rowg) * kMaxChunks + ch) * 8 + wtid, mine[wtid]);
-  __threadfence();
-  named_bar_sync(1, kWorkers);
-  if (wtid == 0) {
-    red_release_add_u32(counter, 1u);
-    uint32_t spins = 0;
-    while (ld_relaxed_u32(counter) < static_cast<uint32_t>(nch)) {
-      if ((++spins & 255u) == 0 && give_up(cx, SITE_ATT_EXCHANGE, rowg)) {
-        cx.misc->wabort = 1;
-        break;
-      }
-    }
-    __threadfence();
-  }
-  named_bar_sync(1, kWorkers);
-  return *reinterpret_cast<volatile int*>(&cx.misc->wabort) == 0;
-}
 
 __device__ __forceinline__ void rope_pair(float x1, float x2, float c, float s, int style, float& first, float& second) {
   if (style == MK_ROPE_HALF_SWAP) {
@@ -673,18 +916,30 @@ __device__ __forceinline__ void rope_pair(float x1, float x2, float c, float s, 
   }
 }
 
-__device__ __forceinline__ float ldcg_bf16(const bf16* ptr) {
-  return __bfloat162float(__ushort_as_bfloat16(__ldcg(reinterpret_cast<const unsigned short*>(ptr))));
+// How many chunks the context of a decode attention phase is cut into.
+__device__ __forceinline__ int decode_chunks(int keys, int rows, int grid, int gs) {
+  const int max_len = (kScoreBytes / 4 / gs) & ~7;
+  int nch = grid / rows;
+  if (nch < 1) nch = 1;
+  const int by_len = (keys + 63) / 64;
+  if (nch > by_len) nch = by_len;
+  if (nch > kMaxChunks) nch = kMaxChunks;
+  const int need = (keys + max_len - 1) / max_len;
+  if (nch < need) nch = need;
+  return nch;
 }
 
 // Softmax attention for every (sequence, kv head, query token) row group; all
 // query heads of the kv head share one pass over K and V.  In decode the
-// context is split into chunks across CTAs, which exchange the running max
-// and sum through global memory so that every probability is rounded to bf16
-// against the global normaliser, as the reference ops do:
+// context is split into chunks across CTAs.  Each chunk publishes its max and
+// its sum of exp(score - max) with a stamp; once every chunk's stamp is there,
+// each chunk rebuilds the global max and sum, so that every probability is
+// rounded to bf16 against the global normaliser, as the reference ops do:
 //   decode  (kv_attention): score = bf16(q.k) * scale in fp32
 //   prefill (attention):    score = bf16(bf16(q.k) * scale) (+ mask, rounded again)
-// then fp32 softmax, probability rounded to bf16, fp32 value sum rounded once.
+// then fp32 softmax, probability rounded to bf16, fp32 value sum rounded once
+// (chunk partials are summed in chunk order by the consumer or by chunk 0's
+// peers, see AttnArgs::combine).
 __device__ __noinline__ bool attention_phase(const Ctx& cx, const AttnArgs& A, int wtid) {
   const KParams& p = *cx.p;
   const int hd = p.head_dim, half = hd / 2;
@@ -695,18 +950,7 @@ __device__ __noinline__ bool attention_phase(const Ctx& cx, const AttnArgs& A, i
   const int lpk = hd / 8;    // lanes per key (16 B each)
   const int kpw = 32 / lpk;  // keys per warp pass
   const int sub = lane / lpk, dg = lane % lpk;
-
-  const int max_len = (kScoreBytes / 4 / gs) & ~7;
-  int nch = 1;
-  if (A.decode) {
-    nch = cx.grid / rows;
-    if (nch < 1) nch = 1;
-    const int by_len = (n_max + 63) / 64;
-    if (nch > by_len) nch = by_len;
-    if (nch > kMaxChunks) nch = kMaxChunks;
-    const int need = (n_max + max_len - 1) / max_len;
-    if (nch < need) nch = need;
-  }
+  const int nch = A.decode ? decode_chunks(n_max, rows, cx.grid, gs) : 1;
   const int chunk = (n_max + nch - 1) / nch;
   const int units = rows * nch;
 
@@ -715,7 +959,7 @@ __device__ __noinline__ bool attention_phase(const Ctx& cx, const AttnArgs& A, i
   float* red = qs + 8 * 128;                                      // [4][128]
   bf16* kn = reinterpret_cast<bf16*>(red + 4 * 128);              // [hd]
   bf16* vn = kn + 128;                                            // [hd]
-  float* stat = reinterpret_cast<float*>(vn + 128);               // [8]
+  float* stat = reinterpret_cast<float*>(vn + 128);               // [16]: max[8], sum[8]
 
   for (int u = cx.cta; u < units; u += cx.grid) {
     const int rowg = u / nch, ch = u - rowg * nch;
@@ -811,7 +1055,7 @@ __device__ __noinline__ bool attention_phase(const Ctx& cx, const AttnArgs& A, i
     }
     named_bar_sync(1, kWorkers);
 
-    // --- max
+    // --- chunk max, then chunk sum of exp(score - chunk max)
     for (int g = 0; g < gs; ++g) {
       float m = -INFINITY;
       for (int i = wtid; i < cl; i += kWorkers) m = fmaxf(m, sc[g * chunk + i]);
@@ -819,48 +1063,56 @@ __device__ __noinline__ bool attention_phase(const Ctx& cx, const AttnArgs& A, i
       if (lane == 0) red[warp * 8 + g] = m;
     }
     named_bar_sync(1, kWorkers);
-    if (wtid < gs) stat[wtid] = fmaxf(fmaxf(red[wtid], red[8 + wtid]), fmaxf(red[16 + wtid], red[24 + wtid]));
-    named_bar_sync(1, kWorkers);
-    if (nch > 1) {
-      if (!attn_exchange(cx, p.att_max, p.att_ctr + rowg * 4 + 0, rowg, ch, nch, gs, stat, wtid)) return false;
-      if (wtid < gs) {
-        float m = -INFINITY;
-        for (int c = 0; c < nch; ++c)
-          m = fmaxf(m, __ldcg(p.att_max + (static_cast<size_t>(rowg) * kMaxChunks + c) * 8 + wtid));
-        stat[wtid] = m;
-      }
-      named_bar_sync(1, kWorkers);
-    }
-
-    // --- exp and sum
     for (int g = 0; g < gs; ++g) {
-      const float m = stat[g];
+      const float m = fmaxf(fmaxf(red[g], red[8 + g]), fmaxf(red[16 + g], red[24 + g]));
       float s = 0.f;
-      for (int i = wtid; i < cl; i += kWorkers) {
-        const float e = expf(sc[g * chunk + i] - m);
-        sc[g * chunk + i] = e;
-        s += e;
-      }
+      for (int i = wtid; i < cl; i += kWorkers) s += expf(sc[g * chunk + i] - m);
       s = warp_sum(s);
       if (lane == 0) red[32 + warp * 8 + g] = s;
+      if (wtid == 0) stat[g] = m;
     }
     named_bar_sync(1, kWorkers);
-    if (wtid < gs) stat[wtid] = ((red[32 + wtid] + red[40 + wtid]) + red[48 + wtid]) + red[56 + wtid];
+    if (wtid < gs) stat[8 + wtid] = ((red[32 + wtid] + red[40 + wtid]) + red[48 + wtid]) + red[56 + wtid];
     named_bar_sync(1, kWorkers);
+
     if (nch > 1) {
-      if (!attn_exchange(cx, p.att_sum, p.att_ctr + rowg * 4 + 1, rowg, ch, nch, gs, stat, wtid)) return false;
+      // --- publish (max, sum) with this phase's stamp; wait for every chunk of the row group
+      float* mine = p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + ch) * kExchangeFloats;
+      if (wtid < 16) __stcg(mine + wtid, stat[wtid]);
+      __threadfence();
+      named_bar_sync(1, kWorkers);
+      if (wtid == 0) st_relaxed_u32(reinterpret_cast<uint32_t*>(mine + 16), A.stamp);
+      bool ok = true;
+      if (wtid < nch) {
+        const uint32_t* theirs = reinterpret_cast<const uint32_t*>(
+            p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + wtid) * kExchangeFloats + 16);
+        uint32_t spins = 0;
+        while (ld_relaxed_u32(theirs) != A.stamp) {
+          if ((++spins & 255u) == 0 && give_up(cx, SITE_ATT_EXCHANGE, rowg)) {
+            ok = false;
+            break;
+          }
+        }
+        __threadfence();
+      }
+      if (!workers_ok(cx, ok)) return false;
       if (wtid < gs) {
+        const float* all = p.att_xch + static_cast<size_t>(rowg) * kMaxChunks * kExchangeFloats;
+        float m = -INFINITY;
+        for (int c = 0; c < nch; ++c) m = fmaxf(m, __ldcg(all + c * kExchangeFloats + wtid));
         float s = 0.f;
-        for (int c = 0; c < nch; ++c) s += __ldcg(p.att_sum + (static_cast<size_t>(rowg) * kMaxChunks + c) * 8 + wtid);
-        stat[wtid] = s;
+        for (int c = 0; c < nch; ++c)
+          s += __ldcg(all + c * kExchangeFloats + 8 + wtid) * expf(__ldcg(all + c * kExchangeFloats + wtid) - m);
+        stat[wtid] = m;
+        stat[8 + wtid] = s;
       }
       named_bar_sync(1, kWorkers);
     }
 
-    // --- probabilities (bf16) and value accumulation
+    // --- probabilities (bf16, against the global max and sum) and value accumulation
     for (int g = 0; g < gs; ++g) {
-      const float denom = stat[g];
-      for (int i = wtid; i < cl; i += kWorkers) sc[g * chunk + i] = bf16_round(sc[g * chunk + i] / denom);
+      const float m = stat[g], denom = stat[8 + g];
+      for (int i = wtid; i < cl; i += kWorkers) sc[g * chunk + i] = bf16_round(expf(sc[g * chunk + i] - m) / denom);
     }
     named_bar_sync(1, kWorkers);
     for (int g = 0; g < gs; ++g) {
@@ -912,22 +1164,28 @@ __device__ __noinline__ bool attention_phase(const Ctx& cx, const AttnArgs& A, i
         }
       }
     }
-    if (nch > 1) {
+    if (nch > 1 && A.combine) {
+      // Stand-alone op: there is no consumer phase, so chunk 0's CTA waits for the
+      // partials of its peers (second stamp) and sums them in chunk order.
+      float* mine = p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + ch) * kExchangeFloats;
       __threadfence();
       named_bar_sync(1, kWorkers);
-      if (wtid == 0) {
-        const uint32_t old = atomicAdd(p.att_ctr + rowg * 4 + 2, 1u);
-        const int is_last = (old == static_cast<uint32_t>(nch - 1));
-        if (is_last) {  // every chunk is past both exchanges: safe to reset for the next use
-          p.att_ctr[rowg * 4 + 0] = 0;
-          p.att_ctr[rowg * 4 + 1] = 0;
-          p.att_ctr[rowg * 4 + 2] = 0;
+      if (wtid == 0) st_relaxed_u32(reinterpret_cast<uint32_t*>(mine + 17), A.stamp);
+      if (ch == 0) {
+        bool ok = true;
+        if (wtid < nch) {
+          const uint32_t* theirs = reinterpret_cast<const uint32_t*>(
+              p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + wtid) * kExchangeFloats + 17);
+          uint32_t spins = 0;
+          while (ld_relaxed_u32(theirs) != A.stamp) {
+            if ((++spins & 255u) == 0 && give_up(cx, SITE_ATT_EXCHANGE, rowg)) {
+              ok = false;
+              break;
+            }
+          }
+          __threadfence();
         }
-        cx.misc->flag = is_last;
-      }
-      named_bar_sync(1, kWorkers);
-      if (*reinterpret_cast<volatile int*>(&cx.misc->flag)) {
-        __threadfence();
+        if (!workers_ok(cx, ok)) return false;
         for (int idx = wtid; idx < gs * hd; idx += kWorkers) {
           const int g = idx / hd, d = idx - g * hd;
           const int head = kvh * gs + g;
@@ -939,6 +1197,7 @@ __device__ __noinline__ bool attention_phase(const Ctx& cx, const AttnArgs& A, i
       }
     }
   }
+  if (A.decode && !A.combine && cx.cta == 0 && wtid == 0) cx.ctrl->att_nch = nch;  // read after the barrier
   return true;
 }
 
@@ -971,14 +1230,22 @@ __device__ __noinline__ void rope_phase(const Ctx& cx, int wtid) {
 
 __device__ void worker_loop(const Ctx& cx, int wtid) {
   const KParams& p = *cx.p;
-  uint32_t q = 0, passed = 0;
+  WorkerState ws;
+  ws.tiles = 0; ws.passed = 0;
+  ws.be_cnt[0] = ws.be_cnt[1] = 0;
+  ws.outstanding[0] = ws.outstanding[1] = false;
   auto gemm = [&](int gp) -> bool {
-    return p.engine == MK_ENGINE_SIMT ? worker_gemm_simt(cx, gp, passed, wtid) : worker_gemm_tc(cx, gp, q, passed, wtid);
+    return p.engine == MK_ENGINE_SIMT ? worker_gemm_simt(cx, gp, wtid) : worker_gemm_tc(cx, gp, ws, wtid);
   };
   const int q_size = p.q_heads * p.head_dim, kv_size = p.kv_heads * p.head_dim;
   AttnArgs A;
   A.knew = nullptr; A.vnew = nullptr; A.new_ld = 0; A.mask = nullptr;
-  A.sq = 1; A.klen = 0; A.len = 0; A.decode = 0; A.rope = 0; A.causal = 0; A.scale = p.att_scale;
+  A.sq = 1; A.klen = 0; A.len = 0; A.decode = 0; A.rope = 0; A.causal = 0; A.combine = 0;
+  A.stamp = p.att_epoch + 1; A.scale = p.att_scale;
+  if (p.n_gemm > 0) {
+    prefetch_phase(cx, 0, wtid);
+    named_bar_sync(1, kWorkers);
+  }
   if (p.mode == MODE_LINEAR) {
     gemm(0);
     return;
@@ -989,9 +1256,9 @@ __device__ void worker_loop(const Ctx& cx, int wtid) {
     A.kv_bstride = static_cast<long long>(p.capacity) * kv_size; A.kv_ld = kv_size;
     A.knew = p.op_k; A.vnew = p.op_v; A.new_ld = kv_size;
     A.out = p.op_out; A.out_bstride = q_size; A.out_tstride = 0; A.out_hstride = p.head_dim;
-    A.len = *p.len[0]; A.decode = 1;
+    A.len = *p.len[0]; A.decode = 1; A.combine = 1;
     if (!attention_phase(cx, A, wtid)) return;
-    if (!grid_barrier(cx, passed, wtid)) return;
+    if (!grid_barrier(cx, ws, wtid)) return;
     if (cx.cta == 0 && wtid == 0) *p.len[0] = A.len + 1;
     return;
   }
@@ -1006,8 +1273,8 @@ __device__ void worker_loop(const Ctx& cx, int wtid) {
     attention_phase(cx, A, wtid);
     return;
   }
-  // Layer 0's residual stream starts as the embedding rows.
-  for (int v = cx.cta * kWorkers + wtid; v < p.m * (p.hidden / 8); v += cx.grid * kWorkers) {
+  // Layer 0's residual stream starts as the embedding rows (the split-K table writes them from its first phase).
+  for (int v = cx.cta * kWorkers + wtid; !p.split && v < p.m * (p.hidden / 8); v += cx.grid * kWorkers) {
     const int t = v / (p.hidden / 8), c = v - t * (p.hidden / 8);
     long long id = p.ids[t];
     if (id < 0 || id >= p.vocab) id = 0;
@@ -1021,10 +1288,11 @@ __device__ void worker_loop(const Ctx& cx, int wtid) {
   for (int layer = 0; layer < p.layers; ++layer) {
     if (!gemm(layer * 4 + 0)) return;                       // [RMSNorm] q, k, v (+bias)
     MK_DEBUG_STEP();
-    if (!grid_barrier(cx, passed, wtid)) return;
+    if (!grid_barrier(cx, ws, wtid)) return;
     MK_DEBUG_STEP();
     A.q = p.qkv; A.q_ld = p.qkv_ld;
     A.out = p.attn; A.out_tstride = q_size; A.out_hstride = p.head_dim;
+    A.stamp = p.att_epoch + static_cast<uint32_t>(layer) + 1u;
     if (decode) {
       A.q_bstride = p.qkv_ld;
       A.k = static_cast<bf16*>(p.kc[layer]); A.v = static_cast<bf16*>(p.vc[layer]);
@@ -1034,28 +1302,29 @@ __device__ void worker_loop(const Ctx& cx, int wtid) {
       A.len = *p.len[layer]; A.decode = 1; A.rope = 1;
     } else {
       rope_phase(cx, wtid);
-      if (!grid_barrier(cx, passed, wtid)) return;
+      if (!grid_barrier(cx, ws, wtid)) return;
       A.q_bstride = static_cast<long long>(p.seq) * p.qkv_ld;
       A.k = p.qkv + q_size; A.v = A.k + kv_size;
       A.kv_bstride = static_cast<long long>(p.seq) * p.qkv_ld; A.kv_ld = p.qkv_ld;
       A.out_bstride = static_cast<long long>(p.seq) * q_size;
       A.mask = p.mask; A.sq = p.seq; A.klen = p.seq; A.causal = (p.mask == nullptr);
+      if (cx.cta == 0 && wtid == 0) cx.ctrl->att_nch = 1;
     }
     if (!attention_phase(cx, A, wtid)) return;              // [RoPE] attention (+ KV append)
     trace_event(cx, wtid, EV_ATTENTION_DONE);
     MK_DEBUG_STEP();
-    if (!grid_barrier(cx, passed, wtid)) return;
+    if (!grid_barrier(cx, ws, wtid)) return;
     if (decode && cx.cta == 0 && wtid == 0) *p.len[layer] = A.len + 1;  // publish after the interval closes
     MK_DEBUG_STEP();
     if (!gemm(layer * 4 + 1)) return;                       // o_proj + residual
     MK_DEBUG_STEP();
-    if (!grid_barrier(cx, passed, wtid)) return;
+    if (!grid_barrier(cx, ws, wtid)) return;
     if (!gemm(layer * 4 + 2)) return;                       // [RMSNorm] gate, up -> SiLU*up
     MK_DEBUG_STEP();
-    if (!grid_barrier(cx, passed, wtid)) return;
+    if (!grid_barrier(cx, ws, wtid)) return;
     if (!gemm(layer * 4 + 3)) return;                       // down + residual
     MK_DEBUG_STEP();
-    if (!grid_barrier(cx, passed, wtid)) return;
+    if (!grid_barrier(cx, ws, wtid)) return;
   }
 #undef MK_DEBUG_STEP
   gemm(p.layers * 4);                                       // [final RMSNorm] lm_head
@@ -1071,7 +1340,7 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
   cx.p = &p;
   cx.ctrl = p.ctrl;
   cx.smem_a = smem;
-  cx.smem_b = smem + kStages * kStageBytes;
+  cx.smem_b = smem + kRingBytes;
   cx.misc = reinterpret_cast<SmemMisc*>(cx.smem_b + kBBytes);
   cx.deadline = clock64() + p.timeout_cycles;
   cx.cta = blockIdx.x;
@@ -1080,23 +1349,27 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
   const bool tc = (p.engine == MK_ENGINE_TCGEN05) && p.n_gemm > 0;
 
   if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kChunkBars; ++s) {
       mbar_init(smem_u32(&cx.misc->full[s]), 1);
       mbar_init(smem_u32(&cx.misc->empty[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&cx.misc->accfull[b]), 1);
       mbar_init(smem_u32(&cx.misc->accempty[b]), kWorkers);
+      mbar_init(smem_u32(&cx.misc->bfull[b]), kWorkers);
+      mbar_init(smem_u32(&cx.misc->bempty[b]), 1);
     }
-    mbar_init(smem_u32(&cx.misc->bfull), kWorkers);
     cx.misc->wabort = 0;
     cx.misc->bad = 0;
     cx.misc->flag = 0;
     cx.misc->trace_n = 0;
     mbar_fence_init();
   }
-  // Token rows a launch does not fill must not hold NaN patterns from earlier kernels.
-  for (int i = tid; i < kBBytes / 16; i += kThreads) reinterpret_cast<uint4*>(cx.smem_b)[i] = make_uint4(0, 0, 0, 0);
+  // Rows of the ring and of the activation slots that a launch does not fill are
+  // still multiplied: make sure they never start out as NaN patterns.
+  for (int i = tid; i < (kRingBytes + kBBytes) / 16; i += kThreads)
+    reinterpret_cast<uint4*>(cx.smem_a)[i] = make_uint4(0, 0, 0, 0);
+  fence_proxy_async_smem();
   __syncthreads();
   if (warp == 1 && tc) {
     tmem_alloc(smem_u32(&cx.misc->tmem_base), kTmemCols);

@@ -13,52 +13,69 @@ typedef __nv_bfloat16 bf16;
 constexpr int kThreads = 192;            // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: workers
 constexpr int kWorkers = 128;
 constexpr int kWorkerWarps = 4;
-constexpr int kStages = 9;               // weight ring depth
-constexpr int kTileRows = 128;           // weight rows per MMA (UMMA M)
-constexpr int kChunkK = 64;              // K elements per ring stage (128 B of bf16 = one swizzle row)
-constexpr int kStageBytes = kTileRows * kChunkK * 2;  // 16 KiB
+constexpr int kTileRows = 128;           // UMMA M; a tile fills only its first `rows` rows
+constexpr int kChunkK = 64;              // K elements per weight chunk (128 B of bf16 = one swizzle row)
+constexpr int kGranule = 1024;           // weight ring allocation unit (8 rows of 128 B)
+constexpr int kRingGranules = 156;
+constexpr int kRingBytes = kRingGranules * kGranule;
+constexpr int kChunkBars = 128;          // full/empty barrier pairs, indexed by chunk sequence number
 constexpr int kTok = MK_TOKEN_TILE;      // tokens per MMA (UMMA N)
-constexpr int kBSlots = 32;              // activation K-chunks resident per CTA
+constexpr int kBSlots = 32;              // activation K-chunks resident per CTA (two halves of 16)
+constexpr int kBHalf = kBSlots / 2;
 constexpr int kBSlotBytes = kTok * 128;  // 2 KiB
 constexpr int kBBytes = kBSlots * kBSlotBytes;
 constexpr int kTmemCols = 64;            // 2 buffers x 2 accumulators x 16 columns
-constexpr int kMiscBytes = 1024;
-constexpr int kSmemBytes = 1024 /*alignment slack*/ + kStages * kStageBytes + kBBytes + kMiscBytes;
+constexpr int kMiscBytes = 4096;
+constexpr int kSmemBytes = 1024 /*alignment slack*/ + kRingBytes + kBBytes + kMiscBytes;
 constexpr int kMaxChunks = 16;           // split-context chunks per (sequence, kv head)
 constexpr int kScoreBytes = 40960;       // fp32 scores of one attention unit (inside the B region)
-constexpr int kPartialFloats = 2 * kTok * kTileRows;  // one split-K partial: [acc][token][row]
+constexpr int kExchangeFloats = 20;      // per (row group, chunk): max[8], sum[8], stamp, pad
+constexpr int kMaxSplit = 4;             // K slices a projection may be cut into
+constexpr int kSplitTokens = 4;          // launches with at most this many tokens use the split-K table
 
 static_assert(kSmemBytes <= 232448, "dynamic shared memory exceeds 227 KiB");
 
-enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU = 2 };
-enum { B_PLAIN = 0, B_NORM = 1 };
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU = 2, EPI_PARTIAL = 3 };
+enum { B_PLAIN = 0, B_NORM = 1, B_ATTN = 2 };
 enum { MODE_DECODE = 0, MODE_PREFILL = 1, MODE_LINEAR = 2, MODE_KVATT = 3, MODE_ATT = 4 };
 enum { EV_PHASE_ENTER = 1, EV_B_STAGED = 2, EV_FIRST_ACC = 3, EV_PHASE_DONE = 4, EV_BARRIER_DONE = 5, EV_ATTENTION_DONE = 6 };
 enum {
   SITE_PRODUCER_EMPTY = 1, SITE_MMA_FULL = 2, SITE_MMA_B = 3, SITE_MMA_ACC = 4, SITE_EPI_ACC = 5,
-  SITE_GRID_BARRIER = 6, SITE_ATT_EXCHANGE = 7, SITE_DRAIN = 8, SITE_PROLOGUE = 9, SITE_SPLIT_REDUCE = 10
+  SITE_GRID_BARRIER = 6, SITE_ATT_EXCHANGE = 7, SITE_DRAIN = 8, SITE_PROLOGUE = 9, SITE_B_EMPTY = 10
 };
 
 // One projection phase: up to three weight matrices sharing the same activation
 // operand (q,k,v), or a gate/up pair accumulated side by side (nacc == 2).
+// Output rows are cut into tiles of `rows` rows (<= 128) and the reduction
+// length into `ksplit` slices; a unit is (row tile, K slice).  rows and ksplit
+// are chosen on the host so that the unit count is just under a multiple of the
+// CTA count and a TMA box (rows x 128 B) stays large; CTA c takes units c,
+// c+grid, ...  With ksplit == 1 a unit finishes its outputs in one fp32 chain.
+// With ksplit > 1 (EPI_PARTIAL) each unit stores fp32 partial sums and the next
+// phase adds them, in slice order, while it builds its activation operand.
 struct GemmPhase {
-  const CUtensorMap* tmap[3];  // device copies of the TMA descriptors
+  const CUtensorMap* tmap[3];  // device copies of the TMA descriptors (box = 64 x rows)
   const bf16* w[3];            // raw weight pointers [N, K]
   const bf16* bias[3];
   int n[3];                    // rows of each matrix
-  int tile_start[4];           // first 128-row tile of each matrix, then the total
+  int tile_start[4];           // first row tile of each matrix, then the total
   int out_col[3];              // column of each matrix's rows in the output buffer
   int nseg, nacc;
   int k, kc;                   // reduction length, in elements and in 64-element chunks
-  int tc;                      // chunks per tile = kc * nacc
-  int ntiles;
-  long long total;             // chunks in the phase = ntiles * tc
+  int rows;                    // weight rows per tile
+  int gran;                    // ring granules one chunk occupies = ceil(rows * 128 / 1024)
+  int ntiles;                  // row tiles
+  int ksplit, kslice;          // K slices and chunks per slice (kc == ksplit * kslice)
+  int nunits;                  // ntiles * ksplit
   int epi, bmode;
   int gather;                  // 1: activation rows are embedding rows selected by the token ids
   int to_logits;               // 1: output goes to the caller's logits buffer
+  int add_parts;               // B_NORM: fp32 partial slices of the previous projection to add to the residual
   const bf16* normw;
-  const bf16* src; int src_ld;
+  const bf16* src; int src_ld; // activation source (B_NORM: the residual stream before this phase)
   bf16* dst; int dst_ld;
+  float* partial;              // EPI_PARTIAL output / B_NORM add_parts input: [slice][token][hidden]
+  bf16* h_out;                 // B_NORM with add_parts or gather: where the updated residual stream goes
 };
 
 struct Control {
@@ -66,7 +83,8 @@ struct Control {
   uint32_t abort;     // set once by whoever gives up a wait; every wait polls it
   int status;         // mk_device_status
   int where, cta, detail;
-  uint32_t pad[2];
+  int att_nch;        // context chunks the last attention phase used (read by the o projection)
+  uint32_t pad;
 };
 
 struct KParams {
@@ -82,19 +100,19 @@ struct KParams {
   int n_gemm;         // projection phases in this launch
   int nbar;           // grid barriers a CTA passes in this launch
   uint32_t epoch;     // barrier counter value when this launch starts
+  uint32_t att_epoch; // attention phases run before this launch (exchange stamps count up from it)
   int qkv_ld;
   int max_positions;
   int stream_once;    // 1: weights are read once per launch (L2 evict-first)
+  int split;          // 1: this launch runs the split-K phase table (residual updates applied by the consumer)
   int debug_stop;     // bring-up aid: leave the schedule after this many steps (0 = run everything)
   int trace_cap;      // events per CTA in `trace` (0 = tracing off)
   unsigned long long* trace;  // [grid][trace_cap] (event code << 56) | %globaltimer ns
   long long timeout_cycles;
   const GemmPhase* phases;
   bf16 *hidden_buf, *qkv, *attn, *act;
-  float* partials;
-  uint32_t* tile_ctr;
-  float *att_max, *att_sum, *att_part;
-  uint32_t* att_ctr;
+  float* att_xch;     // [row groups][kMaxChunks][kExchangeFloats]
+  float* att_part;    // [batch * q_heads][kMaxChunks][head_dim]
   Control* ctrl;
   const long long* ids;
   const long long* pos;
@@ -104,7 +122,6 @@ struct KParams {
   // stand-alone attention ops
   const bf16 *op_q, *op_k, *op_v;
   bf16* op_out;
-  float op_scale;
   int op_qlen, op_klen;
   void* kc[MK_MAX_LAYERS];
   void* vc[MK_MAX_LAYERS];

@@ -214,3 +214,13 @@ def rope_tables(config: DecoderConfig, positions: int, device="cpu") -> tuple[to
     cos = emb.cos().to(torch.bfloat16)
     sin = emb.sin().to(torch.bfloat16)
     return cos.to(device).contiguous(), sin.to(device).contiguous()
+
+
+def new_kv_state(config: DecoderConfig, batch: int, capacity: int, device="cpu"):
+    """Zeroed decode state: per layer a key cache and a value cache
+    ``[batch, capacity, kv_heads, head_dim]`` (bf16) and an int32 ``[1]`` valid length."""
+    shape = (batch, capacity, config.kv_heads, config.head_dim)
+    keys = [torch.zeros(shape, dtype=torch.bfloat16, device=device) for _ in range(config.layers)]
+    values = [torch.zeros(shape, dtype=torch.bfloat16, device=device) for _ in range(config.layers)]
+    lengths = [torch.zeros(1, dtype=torch.int32, device=device) for _ in range(config.layers)]
+    return keys, values, lengths
