@@ -45,7 +45,11 @@ typedef enum mk_device_status {
 } mk_device_status;
 
 enum { MK_ROPE_HF = 0, MK_ROPE_HALF_SWAP = 1 };
-enum { MK_ENGINE_TCGEN05 = 0, MK_ENGINE_SIMT = 1 };
+/* TCGEN05: tensor-core projections for every launch (the default).
+ * FMA: launches of at most 4 tokens consume the TMA-fed weight ring with CUDA-core FMAs
+ *      instead of tcgen05.mma; larger launches still use tcgen05.
+ * SIMT: bring-up engine without TMA or tensor cores. */
+enum { MK_ENGINE_TCGEN05 = 0, MK_ENGINE_SIMT = 1, MK_ENGINE_FMA = 2 };
 
 /* Decoder shape.  Mirrors the facts the reference reads off the captured graph
  * (src/megabake/lowering.py:1851-1870 for the attention contract,
@@ -63,7 +67,7 @@ typedef struct mk_config {
   int32_t rope_style;    /* MK_ROPE_* */
   int32_t max_tokens;    /* largest batch (decode) or batch*sequence (prefill) per launch */
   int32_t max_positions; /* rows of the cos/sin tables */
-  int32_t engine;        /* MK_ENGINE_*; SIMT is a bring-up/diagnostic engine */
+  int32_t engine;        /* MK_ENGINE_* */
   int32_t sm_limit;      /* 0: one CTA per SM on the whole GPU; >0: use this many CTAs */
 } mk_config;
 

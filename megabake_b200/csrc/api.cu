@@ -80,7 +80,8 @@ int check_config(const mk_config& c) {
   if (c.q_heads / c.kv_heads > 8) return fail(MK_ERR_UNSUPPORTED, "config: at most 8 query heads per kv head");
   if (c.hidden % 64 || c.intermediate % 64)
     return fail(MK_ERR_UNSUPPORTED, "config: hidden and intermediate must be multiples of 64");
-  if (c.engine != MK_ENGINE_TCGEN05 && c.engine != MK_ENGINE_SIMT) return fail(MK_ERR_INVALID, "config: engine");
+  if (c.engine != MK_ENGINE_TCGEN05 && c.engine != MK_ENGINE_SIMT && c.engine != MK_ENGINE_FMA)
+    return fail(MK_ERR_INVALID, "config: engine");
   if (c.rope_style != MK_ROPE_HF && c.rope_style != MK_ROPE_HALF_SWAP) return fail(MK_ERR_INVALID, "config: rope_style");
   return MK_OK;
 }
@@ -135,6 +136,7 @@ struct mk_handle_s {
   int64_t launches;
   long long timeout_cycles;
   float att_scale;
+  bool fma_ok;  // every phase of the split-K table keeps its K slice inside the activation slots
   unsigned long long* trace;
   int trace_cap;
   std::mutex lock;
@@ -208,7 +210,7 @@ void base_params(mk_handle h, KParams& p) {
   p.head_dim = c.head_dim; p.inter = c.intermediate; p.vocab = c.vocab; p.eps = c.rms_eps;
   p.rope_style = c.rope_style; p.prefill_rope_style = MK_ROPE_HF;
   p.att_scale = h->att_scale;
-  p.engine = c.engine;
+  p.engine = c.engine == MK_ENGINE_FMA ? MK_ENGINE_TCGEN05 : c.engine;
   p.epoch = h->epoch;
   p.att_epoch = h->att_epoch;
   p.qkv_ld = qkv_width(c);
@@ -282,6 +284,7 @@ int mk_create(const mk_config* config, void* workspace, size_t workspace_bytes, 
   if (major != 10) return fail(MK_ERR_UNSUPPORTED, "device %d is sm_%d0; this library is built for sm_100a only", device, major);
   if (!coop) return fail(MK_ERR_UNSUPPORTED, "device %d does not support cooperative launch", device);
   MK_CUDA(cudaFuncSetAttribute(megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+  MK_CUDA(cudaFuncSetAttribute(megakernel, cudaFuncAttributePreferredSharedMemoryCarveout, (kSmemBytes * 100 + 233471) / 233472));
   int per_sm = 0;
   MK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, megakernel, kThreads, kSmemBytes));
   if (per_sm < 1) return fail(MK_ERR_UNSUPPORTED, "the megakernel does not fit on an SM of device %d", device);
@@ -429,6 +432,9 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
                           cudaMemcpyHostToDevice, s));
   // The source vectors die at return: make sure the copies have read them.
   MK_CUDA(cudaStreamSynchronize(s));
+  h->fma_ok = split_table_ok(c);
+  for (size_t i = 0; i < nphases && h->fma_ok; ++i)
+    if (phases[i].kslice > kBSlots || phases[i].rows > kTileRows) h->fma_ok = false;
   h->layers.assign(w->layers, w->layers + L);
   h->weights = *w;
   h->weights.layers = h->layers.data();
@@ -460,6 +466,7 @@ int mk_decode(mk_handle h, const int64_t* ids, const int64_t* positions, int bat
   p.mode = MODE_DECODE; p.m = batch; p.batch = batch; p.seq = 1; p.capacity = capacity;
   p.split = (batch <= kSplitTokens && split_table_ok(h->cfg)) ? 1 : 0;
   p.phases = at<GemmPhase>(h, h->cv.phases) + (p.split ? 0 : phases_per_table(h->cfg));
+  if (h->cfg.engine == MK_ENGINE_FMA && p.split && h->fma_ok) p.engine = ENGINE_FMA;
   p.n_gemm = 4 * L + 1;
   p.nbar = 5 * L;
   p.stream_once = (ntt == 1);
@@ -488,6 +495,7 @@ int mk_prefill(mk_handle h, const int64_t* ids, const int64_t* positions, const 
   p.mode = MODE_PREFILL; p.m = static_cast<int>(m); p.batch = batch; p.seq = sequence; p.capacity = 0;
   p.split = (m <= kSplitTokens && split_table_ok(h->cfg)) ? 1 : 0;
   p.phases = at<GemmPhase>(h, h->cv.phases) + (p.split ? 0 : phases_per_table(h->cfg));
+  if (h->cfg.engine == MK_ENGINE_FMA && p.split && h->fma_ok) p.engine = ENGINE_FMA;
   p.n_gemm = 4 * L + 1;
   p.nbar = 6 * L;
   p.stream_once = (ntt == 1);
@@ -530,6 +538,7 @@ int mk_linear(mk_handle h, const void* x, const void* weight, const void* bias, 
   p.n_gemm = 1;
   p.nbar = 0;
   p.stream_once = (token_tiles(m) == 1);
+  if (h->cfg.engine == MK_ENGINE_FMA && m <= kSplitTokens && ph.kslice <= kBSlots) p.engine = ENGINE_FMA;
   return launch(h, p, stream);
 }
 

@@ -73,7 +73,7 @@ struct WorkerState {
 // ---------------------------------------------------------------------------
 // bounded waits
 
-__device__ __noinline__ bool give_up(const Ctx& cx, int site, int detail) {
+__device__ __forceinline__ bool give_up(const Ctx& cx, int site, int detail) {
   if (ld_relaxed_u32(&cx.ctrl->abort) != 0) return true;
   if (clock64() > cx.deadline) {
     if (atomicCAS(&cx.ctrl->status, 0, static_cast<int>(MK_STATUS_TIMEOUT)) == 0) {
@@ -104,9 +104,20 @@ __device__ __forceinline__ void trace_event(const Ctx& cx, int wtid, int code) {
 __device__ __forceinline__ bool wait_mbar(const Ctx& cx, uint32_t bar, uint32_t parity, int site, int detail) {
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 255u) == 0 && give_up(cx, site, detail)) return false;
+    if (++spins > 8) __nanosleep(64);  // a long wait must not steal issue slots from the warps that share this scheduler
+    if ((spins & 255u) == 0 && give_up(cx, site, detail)) return false;
   }
   return true;
+}
+
+// Same wait, adding the cycles it took to `cycles` (profiling of the single-thread roles).
+__device__ __forceinline__ bool wait_mbar_timed(const Ctx& cx, uint32_t bar, uint32_t parity, int site, int detail,
+                                                long long& cycles) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  const bool ok = wait_mbar(cx, bar, parity, site, detail);
+  cycles += clock64() - t0;
+  return ok;
 }
 
 // Worker-uniform decision: true only if no worker thread has given up.
@@ -180,9 +191,11 @@ __device__ __noinline__ void producer_loop(const Ctx& cx) {
   // the oldest chunk in flight until the wanted granules are free.
   int head = 0, seq = 0, oldest = 0;
   bool ok = true;
+  long long waited = 0;
+  const long long started = clock64();
   auto retire_oldest = [&](int gp) -> bool {
-    const bool done = wait_mbar(cx, smem_u32(&misc->empty[oldest % kChunkBars]), (oldest / kChunkBars) & 1,
-                                SITE_PRODUCER_EMPTY, gp);
+    const bool done = wait_mbar_timed(cx, smem_u32(&misc->empty[oldest % kChunkBars]), (oldest / kChunkBars) & 1,
+                                      SITE_PRODUCER_EMPTY, gp, waited);
     ++oldest;
     return done;
   };
@@ -245,6 +258,12 @@ __device__ __noinline__ void producer_loop(const Ctx& cx) {
       }
     }
   }
+  if (p.trace_cap >= 8) {  // role profile in the last slots of this CTA's trace row
+    unsigned long long* row = p.trace + static_cast<size_t>(cx.cta) * p.trace_cap + p.trace_cap;
+    row[-1] = (7ull << 56) | static_cast<unsigned long long>(clock64() - started);
+    row[-2] = (8ull << 56) | static_cast<unsigned long long>(waited);
+    row[-3] = (9ull << 56) | static_cast<unsigned long long>(seq);
+  }
   if (!ok) {
     // Leaving early: every copy already issued must land before the CTA exits.
     for (int i = max(0, seq - kChunkBars); i < seq; ++i) {
@@ -268,6 +287,8 @@ __device__ __noinline__ void mma_loop(const Ctx& cx) {
   const uint32_t ring_base = smem_u32(cx.smem_a), b_region = smem_u32(cx.smem_b);
   int head = 0, seq = 0;
   uint32_t q = 0, bf_cnt[2] = {0, 0};
+  long long wait_full = 0, wait_other = 0;
+  const long long started = clock64();
   for (int gp = 0; gp < p.n_gemm; ++gp) {
     const GemmPhase* ph = p.phases + gp;
     const int nacc = ph->nacc, gran = ph->gran, nunits = ph->nunits, kslice = ph->kslice;
@@ -280,13 +301,13 @@ __device__ __noinline__ void mma_loop(const Ctx& cx) {
       for (int unit = cx.cta; unit < nunits; unit += cx.grid) {
         if (!streamed && (per_unit || unit == cx.cta)) {
           for (int h = 0; h < (kslice > kBHalf ? 2 : 1); ++h) {
-            if (!wait_mbar(cx, smem_u32(&cx.misc->bfull[h]), bf_cnt[h] & 1u, SITE_MMA_B, gp)) return;
+            if (!wait_mbar_timed(cx, smem_u32(&cx.misc->bfull[h]), bf_cnt[h] & 1u, SITE_MMA_B, gp, wait_other)) return;
             ++bf_cnt[h];
           }
           tc_fence_after();
         }
         const uint32_t buf = q & 1u;
-        if (!wait_mbar(cx, smem_u32(&cx.misc->accempty[buf]), ((q >> 1) & 1u) ^ 1u, SITE_MMA_ACC, gp)) return;
+        if (!wait_mbar_timed(cx, smem_u32(&cx.misc->accempty[buf]), ((q >> 1) & 1u) ^ 1u, SITE_MMA_ACC, gp, wait_other)) return;
         tc_fence_after();
         uint32_t accumulate = 0;
         for (int vb = 0; vb < batches; ++vb) {
@@ -295,7 +316,7 @@ __device__ __noinline__ void mma_loop(const Ctx& cx) {
           const int h = vb & 1;
           const int len = streamed ? min(kBHalf, kslice - b * kBHalf) : kslice;
           if (streamed) {
-            if (!wait_mbar(cx, smem_u32(&cx.misc->bfull[h]), bf_cnt[h] & 1u, SITE_MMA_B, gp)) return;
+            if (!wait_mbar_timed(cx, smem_u32(&cx.misc->bfull[h]), bf_cnt[h] & 1u, SITE_MMA_B, gp, wait_other)) return;
             ++bf_cnt[h];
             tc_fence_after();
           }
@@ -306,7 +327,7 @@ __device__ __noinline__ void mma_loop(const Ctx& cx) {
               if (head + gran > kRingGranules) head = 0;
               const uint32_t a_addr = ring_base + head * kGranule;
               head += gran;
-              if (!wait_mbar(cx, smem_u32(&cx.misc->full[seq % kChunkBars]), (seq / kChunkBars) & 1, SITE_MMA_FULL, gp))
+              if (!wait_mbar_timed(cx, smem_u32(&cx.misc->full[seq % kChunkBars]), (seq / kChunkBars) & 1, SITE_MMA_FULL, gp, wait_full))
                 return;
               tc_fence_after();
               const uint64_t a_desc = desc_base + (a_addr >> 4);
@@ -328,6 +349,12 @@ __device__ __noinline__ void mma_loop(const Ctx& cx) {
         ++q;
       }
     }
+  }
+  if (p.trace_cap >= 8) {
+    unsigned long long* row = p.trace + static_cast<size_t>(cx.cta) * p.trace_cap + p.trace_cap;
+    row[-4] = (10ull << 56) | static_cast<unsigned long long>(clock64() - started);
+    row[-5] = (11ull << 56) | static_cast<unsigned long long>(wait_full);
+    row[-6] = (12ull << 56) | static_cast<unsigned long long>(wait_other);
   }
 }
 
@@ -620,11 +647,12 @@ __device__ __forceinline__ float ldcg_bf16(const bf16* ptr) {
 // Values an epilogue adds to the accumulators; loaded before the accumulator
 // wait so their latency hides behind the MMA: the residual stream (per token)
 // or the bias (one value).
+template <int NT>
 __device__ __forceinline__ void epilogue_prefetch(const Ctx& cx, const GemmPhase* ph, int seg, int n, int t0, int mt,
                                                   float* pre) {
   if (ph->epi == EPI_RESIDUAL) {
 #pragma unroll
-    for (int t = 0; t < kTok; ++t)
+    for (int t = 0; t < NT; ++t)
       if (t < mt) pre[t] = ldcg_bf16(ph->dst + static_cast<size_t>(t0 + t) * ph->dst_ld + n);
   } else if (ph->epi == EPI_STORE) {
     pre[0] = ph->bias[seg] ? ldg_bf16(ph->bias[seg] + n) : 0.f;
@@ -632,20 +660,22 @@ __device__ __forceinline__ void epilogue_prefetch(const Ctx& cx, const GemmPhase
 }
 
 // EPI_PARTIAL: this unit's fp32 sums over its K slice, for the next phase to add up.
+template <int NT>
 __device__ __forceinline__ void store_partial(const Ctx& cx, const GemmPhase* ph, int slice, int n, const float* v,
                                               int t0, int mt) {
 #pragma unroll
-  for (int t = 0; t < kTok; ++t)
+  for (int t = 0; t < NT; ++t)
     if (t < mt) __stcg(ph->partial + (static_cast<size_t>(slice) * cx.p->m + (t0 + t)) * ph->n[0] + n, v[t]);
 }
 
 // Finish output row n of matrix `seg` for the tokens of the tile.
-__device__ __forceinline__ void apply_epilogue(const Ctx& cx, const GemmPhase* ph, int seg, int n, float (*v)[kTok],
+template <int NT>
+__device__ __forceinline__ void apply_epilogue(const Ctx& cx, const GemmPhase* ph, int seg, int n, float (*v)[NT],
                                                const float* pre, int t0, int mt) {
   const KParams& p = *cx.p;
   if (ph->epi == EPI_SILU) {
 #pragma unroll
-    for (int t = 0; t < kTok; ++t) {
+    for (int t = 0; t < NT; ++t) {
       if (t < mt) {
         const float gate = bf16_round(v[0][t]);
         const float up = bf16_round(v[1][t]);
@@ -659,11 +689,11 @@ __device__ __forceinline__ void apply_epilogue(const Ctx& cx, const GemmPhase* p
   const size_t col = static_cast<size_t>(ph->out_col[seg]) + n;
   if (ph->epi == EPI_STORE) {
 #pragma unroll
-    for (int t = 0; t < kTok; ++t)
+    for (int t = 0; t < NT; ++t)
       if (t < mt) dst[static_cast<size_t>(t0 + t) * ph->dst_ld + col] = __float2bfloat16_rn(v[0][t] + pre[0]);
   } else {  // EPI_RESIDUAL: hidden += bf16(projection), in place
 #pragma unroll
-    for (int t = 0; t < kTok; ++t)
+    for (int t = 0; t < NT; ++t)
       if (t < mt) dst[static_cast<size_t>(t0 + t) * ph->dst_ld + col] = __float2bfloat16_rn(pre[t] + bf16_round(v[0][t]));
   }
 }
@@ -687,14 +717,20 @@ __device__ __forceinline__ bool acquire_half(const Ctx& cx, WorkerState& ws, int
 }
 
 // Build the activation operand for K chunks [k0, k0 + count) of the token tile in slots 0.. (not streamed).
-__device__ __forceinline__ void stage_resident(const Ctx& cx, const GemmPhase* ph, int k0, int count, int t0, int mt,
-                                               int wtid, int nch) {
+__device__ __forceinline__ void stage_operand(const Ctx& cx, const GemmPhase* ph, int k0, int count, int t0, int mt,
+                                              int wtid, int nch) {
   if (ph->bmode == B_NORM) {
     if (ph->add_parts > 0 || ph->h_out != nullptr || mt <= 2) stage_norm_block(cx, ph, t0, mt, wtid);
     else stage_norm_resident(cx, ph, t0, mt, wtid);
   } else {
     stage_chunks(cx, ph, k0, k0 + count, 0, t0, mt, wtid, nch);
   }
+}
+
+// The same for the tcgen05 engine: make the slots visible to the MMA and tell the issuer.
+__device__ __forceinline__ void stage_resident(const Ctx& cx, const GemmPhase* ph, int k0, int count, int t0, int mt,
+                                               int wtid, int nch) {
+  stage_operand(cx, ph, k0, count, t0, mt, wtid, nch);
   fence_proxy_async_smem();
   mbar_arrive(smem_u32(&cx.misc->bfull[0]));
   if (count > kBHalf) mbar_arrive(smem_u32(&cx.misc->bfull[1]));
@@ -747,7 +783,7 @@ __device__ __noinline__ bool worker_gemm_tc(const Ctx& cx, int gp, WorkerState& 
         const int n = row0 + rloc;
         const bool valid = rloc < rows && n < ph->n[seg];
         float pre[kTok];
-        if (valid) epilogue_prefetch(cx, ph, seg, n, t0, mt, pre);
+        if (valid) epilogue_prefetch<kTok>(cx, ph, seg, n, t0, mt, pre);
         const uint32_t buf = ws.tiles & 1u;
         bool ok = wait_mbar(cx, smem_u32(&cx.misc->accfull[buf]), (ws.tiles >> 1) & 1u, SITE_EPI_ACC, gp);
         ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below needs the whole warp
@@ -763,13 +799,142 @@ __device__ __noinline__ bool worker_gemm_tc(const Ctx& cx, int gp, WorkerState& 
         ws.tiles += 1;
         if (!workers_ok(cx, ok)) return false;
         if (valid) {
-          if (ph->epi == EPI_PARTIAL) store_partial(cx, ph, slice, n, v[0], t0, mt);
-          else apply_epilogue(cx, ph, seg, n, v, pre, t0, mt);
+          if (ph->epi == EPI_PARTIAL) store_partial<kTok>(cx, ph, slice, n, v[0], t0, mt);
+          else apply_epilogue<kTok>(cx, ph, seg, n, v, pre, t0, mt);
         }
       }
       trace_event(cx, wtid, EV_PHASE_DONE);
     }
   }
+  prefetch_phase(cx, gp + 1, wtid);
+  return true;
+}
+
+// Projection phase on the FMA engine: for launches of at most four tokens the
+// tensor core is the wrong tool (one UMMA of 128 weight rows by 16 token
+// columns occupies the tensor pipe for about a hundred cycles whatever the
+// token count, which caps a CTA near 40 bytes of weights per cycle and far less
+// for the short tiles an even split over 148 CTAs wants).  Here the four worker
+// warps read the TMA-filled ring slots themselves: eight lanes share a weight
+// row (16 bytes each), four rows per warp per step, fp32 FMA chains per
+// (row, lane), a fixed shuffle tree across the eight lanes at the end.  About
+// eighty issue cycles per 7 KB chunk, so the weight stream, not the arithmetic,
+// is the limit.  The ring, the producer, the activation slots and the
+// consumer-side split-K reduction are the same as for the tcgen05 engine.
+struct FmaState {
+  int head, seq;  // ring replay, same sequence as the producer's
+  long long waited, arith;  // profile: cycles waiting for weights / consuming them
+};
+
+template <int MT, int NACC>
+__device__ __noinline__ bool worker_gemm_fma(const Ctx& cx, int gp, FmaState& fs, int wtid) {
+  const KParams& p = *cx.p;
+  const GemmPhase* ph = &cx.misc->phase[gp & 1];
+  const int nunits = ph->nunits, rows = ph->rows, ksplit = ph->ksplit, kslice = ph->kslice;
+  const int gran = ph->gran;
+  const bool per_unit = ksplit > 1;
+  const int warp = wtid >> 5, lane = wtid & 31;
+  const int c = lane & 7, rsub = lane >> 3;
+  const int rot = k_rotation(cx.cta, cx.grid, kslice);
+  const int nch = (ph->bmode == B_ATTN) ? *reinterpret_cast<volatile int*>(&cx.ctrl->att_nch) : 1;
+  const int mt = p.m;  // == MT, one token tile
+  const uint32_t b_region = smem_u32(cx.smem_b), ring_base = smem_u32(cx.smem_a);
+  // Byte offset of this lane's 16 bytes in row (j * 16 + warp * 4 + rsub); (row & 7) does not depend on j.
+  const int lane_row = warp * 4 + rsub;
+  const uint32_t lane_off = lane_row * 128 + ((c ^ (lane_row & 7)) << 4);
+  int head = fs.head, seq = fs.seq;
+  bool ok = true;
+  long long waited = 0, arith = 0;
+  if (cx.cta < nunits) {
+    trace_event(cx, wtid, EV_PHASE_ENTER);
+    for (int unit = cx.cta; unit < nunits && ok; unit += cx.grid) {
+      const int tile = unit / ksplit, slice = unit - tile * ksplit;
+      if (per_unit || unit == cx.cta) {
+        named_bar_sync(1, kWorkers);  // the previous unit has finished reading the slots
+        stage_operand(cx, ph, slice * kslice, kslice, 0, mt, wtid, nch);
+        named_bar_sync(1, kWorkers);
+        if (unit == cx.cta) trace_event(cx, wtid, EV_B_STAGED);
+      }
+      // All eight row steps of the 128-row MMA-sized tile are always computed; the ones
+      // past `rows` read stale shared memory and are dropped at the end.
+      float acc[NACC][8][MT];
+#pragma unroll
+      for (int a = 0; a < NACC; ++a)
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+          for (int m = 0; m < MT; ++m) acc[a][j][m] = 0.f;
+      int slot = rot;
+      for (int i = 0; i < kslice; ++i) {
+        float xf[MT][8];
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+          unpack8(lds_v4(b_region + slot * kBSlotBytes + m * 128 + ((c ^ m) << 4)), xf[m]);
+#pragma unroll
+        for (int a = 0; a < NACC; ++a) {
+          if (head + gran > kRingGranules) head = 0;
+          const uint32_t base = ring_base + head * kGranule + lane_off;
+          head += gran;
+          const uint32_t bar = seq % kChunkBars;
+          const bool got = __all_sync(0xffffffffu, wait_mbar_timed(cx, smem_u32(&cx.misc->full[bar]),
+                                                                   (seq / kChunkBars) & 1, SITE_MMA_FULL, gp, waited));
+          ok = ok && got;
+          const long long t_arith = clock64();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float wf[8];
+            unpack8(lds_v4(base + j * 2048), wf);
+#pragma unroll
+            for (int m = 0; m < MT; ++m)
+#pragma unroll
+              for (int e = 0; e < 8; ++e) acc[a][j][m] = fmaf(wf[e], xf[m][e], acc[a][j][m]);
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&cx.misc->empty[bar]));
+          arith += clock64() - t_arith;
+          seq += 1;
+        }
+        ++slot;
+        if (slot == kslice) slot = 0;
+        if (!ok) break;
+      }
+      if (!ok) break;
+      // fixed-order sum over the eight lanes of a row, then the row's epilogue on lane c == 0
+      int seg, row0;
+      tile_origin(ph, tile, seg, row0);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float v[2][MT];
+#pragma unroll
+        for (int a = 0; a < NACC; ++a)
+#pragma unroll
+          for (int m = 0; m < MT; ++m) {
+            float x = acc[a][j][m];
+            x += __shfl_xor_sync(0xffffffffu, x, 1);
+            x += __shfl_xor_sync(0xffffffffu, x, 2);
+            x += __shfl_xor_sync(0xffffffffu, x, 4);
+            v[a][m] = x;
+          }
+        const int r = j * 16 + lane_row;
+        const int n = row0 + r;
+        if (c == 0 && r < rows && n < ph->n[seg]) {
+          if (ph->epi == EPI_PARTIAL) {
+            store_partial<MT>(cx, ph, slice, n, v[0], 0, mt);
+          } else {
+            float pre[MT];
+            epilogue_prefetch<MT>(cx, ph, seg, n, 0, mt, pre);
+            apply_epilogue<MT>(cx, ph, seg, n, v, pre, 0, mt);
+          }
+        }
+      }
+    }
+    trace_event(cx, wtid, EV_PHASE_DONE);
+  }
+  fs.head = head;
+  fs.seq = seq;
+  fs.waited += waited;
+  fs.arith += arith;
+  if (!workers_ok(cx, ok)) return false;
   prefetch_phase(cx, gp + 1, wtid);
   return true;
 }
@@ -866,12 +1031,12 @@ __device__ __noinline__ bool worker_gemm_simt(const Ctx& cx, int gp, int wtid) {
       }
       if (lane == 0) {
         if (ph->epi == EPI_PARTIAL) {
-          store_partial(cx, ph, 0, n, v[0], t0, mt);
+          store_partial<kTok>(cx, ph, 0, n, v[0], t0, mt);
           for (int t = 0; t < mt; ++t) v[1][t] = 0.f;
-          for (int s8 = 1; s8 < ph->ksplit; ++s8) store_partial(cx, ph, s8, n, v[1], t0, mt);
+          for (int s8 = 1; s8 < ph->ksplit; ++s8) store_partial<kTok>(cx, ph, s8, n, v[1], t0, mt);
         } else {
-          epilogue_prefetch(cx, ph, seg, n, t0, mt, pre);
-          apply_epilogue(cx, ph, seg, n, v, pre, t0, mt);
+          epilogue_prefetch<kTok>(cx, ph, seg, n, t0, mt, pre);
+          apply_epilogue<kTok>(cx, ph, seg, n, v, pre, t0, mt);
         }
       }
     }
@@ -1234,8 +1399,20 @@ __device__ void worker_loop(const Ctx& cx, int wtid) {
   ws.tiles = 0; ws.passed = 0;
   ws.be_cnt[0] = ws.be_cnt[1] = 0;
   ws.outstanding[0] = ws.outstanding[1] = false;
+  FmaState fs;
+  fs.head = 0; fs.seq = 0; fs.waited = 0; fs.arith = 0;
   auto gemm = [&](int gp) -> bool {
-    return p.engine == MK_ENGINE_SIMT ? worker_gemm_simt(cx, gp, wtid) : worker_gemm_tc(cx, gp, ws, wtid);
+    if (p.engine == MK_ENGINE_SIMT) return worker_gemm_simt(cx, gp, wtid);
+    if (p.engine == ENGINE_FMA) {
+      const bool pair = cx.misc->phase[gp & 1].nacc == 2;
+      switch (p.m) {
+        case 1: return pair ? worker_gemm_fma<1, 2>(cx, gp, fs, wtid) : worker_gemm_fma<1, 1>(cx, gp, fs, wtid);
+        case 2: return pair ? worker_gemm_fma<2, 2>(cx, gp, fs, wtid) : worker_gemm_fma<2, 1>(cx, gp, fs, wtid);
+        case 3: return pair ? worker_gemm_fma<3, 2>(cx, gp, fs, wtid) : worker_gemm_fma<3, 1>(cx, gp, fs, wtid);
+        default: return pair ? worker_gemm_fma<4, 2>(cx, gp, fs, wtid) : worker_gemm_fma<4, 1>(cx, gp, fs, wtid);
+      }
+    }
+    return worker_gemm_tc(cx, gp, ws, wtid);
   };
   const int q_size = p.q_heads * p.head_dim, kv_size = p.kv_heads * p.head_dim;
   AttnArgs A;
@@ -1328,6 +1505,11 @@ __device__ void worker_loop(const Ctx& cx, int wtid) {
   }
 #undef MK_DEBUG_STEP
   gemm(p.layers * 4);                                       // [final RMSNorm] lm_head
+  if (p.trace_cap >= 8 && p.engine == ENGINE_FMA && wtid == 0) {
+    unsigned long long* row = p.trace + static_cast<size_t>(cx.cta) * p.trace_cap + p.trace_cap;
+    row[-5] = (11ull << 56) | static_cast<unsigned long long>(fs.waited);
+    row[-6] = (12ull << 56) | static_cast<unsigned long long>(fs.arith);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -1346,12 +1528,13 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
   cx.cta = blockIdx.x;
   cx.grid = gridDim.x;
   const int tid = threadIdx.x, warp = tid >> 5;
-  const bool tc = (p.engine == MK_ENGINE_TCGEN05) && p.n_gemm > 0;
+  const bool tc = (p.engine == MK_ENGINE_TCGEN05) && p.n_gemm > 0;   // tensor-core roles (TMEM, MMA issuer)
+  const bool ring = (tc || p.engine == ENGINE_FMA) && p.n_gemm > 0;  // weight producer
 
   if (tid == 0) {
     for (int s = 0; s < kChunkBars; ++s) {
       mbar_init(smem_u32(&cx.misc->full[s]), 1);
-      mbar_init(smem_u32(&cx.misc->empty[s]), 1);
+      mbar_init(smem_u32(&cx.misc->empty[s]), tc ? 1 : kWorkerWarps);  // MMA commit, or one arrival per worker warp
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&cx.misc->accfull[b]), 1);
@@ -1409,7 +1592,7 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
       if (p.nbar > 0) atomicAdd(&cx.ctrl->barrier, static_cast<uint32_t>(p.nbar));
     }
   } else if (warp == 0) {
-    if (tc && tid == 0) producer_loop(cx);
+    if (ring && tid == 0) producer_loop(cx);
   } else if (warp == 1) {
     if (tc && tid == 32) mma_loop(cx);
   } else {

@@ -16,7 +16,7 @@ constexpr int kWorkerWarps = 4;
 constexpr int kTileRows = 128;           // UMMA M; a tile fills only its first `rows` rows
 constexpr int kChunkK = 64;              // K elements per weight chunk (128 B of bf16 = one swizzle row)
 constexpr int kGranule = 1024;           // weight ring allocation unit (8 rows of 128 B)
-constexpr int kRingGranules = 156;
+constexpr int kRingGranules = 120;       // keeps the CTA under 196 KiB of shared memory so ~60 KiB stay L1 (stack, spills)
 constexpr int kRingBytes = kRingGranules * kGranule;
 constexpr int kChunkBars = 128;          // full/empty barrier pairs, indexed by chunk sequence number
 constexpr int kTok = MK_TOKEN_TILE;      // tokens per MMA (UMMA N)
@@ -33,10 +33,11 @@ constexpr int kExchangeFloats = 20;      // per (row group, chunk): max[8], sum[
 constexpr int kMaxSplit = 4;             // K slices a projection may be cut into
 constexpr int kSplitTokens = 4;          // launches with at most this many tokens use the split-K table
 
-static_assert(kSmemBytes <= 232448, "dynamic shared memory exceeds 227 KiB");
+static_assert(kSmemBytes <= 200704, "dynamic shared memory exceeds the 196 KiB carve-out");
 
 enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU = 2, EPI_PARTIAL = 3 };
 enum { B_PLAIN = 0, B_NORM = 1, B_ATTN = 2 };
+enum { ENGINE_FMA = 3 };  // per-launch engine value next to MK_ENGINE_*: this launch consumes the ring with CUDA-core FMAs
 enum { MODE_DECODE = 0, MODE_PREFILL = 1, MODE_LINEAR = 2, MODE_KVATT = 3, MODE_ATT = 4 };
 enum { EV_PHASE_ENTER = 1, EV_B_STAGED = 2, EV_FIRST_ACC = 3, EV_PHASE_DONE = 4, EV_BARRIER_DONE = 5, EV_ATTENTION_DONE = 6 };
 enum {
