@@ -345,3 +345,57 @@ class DecoderKernel:
         self._call("mk_launch_info", self.lib.mk_launch_info(
             self._handle, ctypes.byref(ctas), ctypes.byref(smem), ctypes.byref(launches)))
         return dict(ctas=ctas.value, smem_bytes=smem.value, launches=launches.value)
+
+
+class AttentionKernels:
+    """Launch state for the two attention ops alone (no decoder weights): what
+    ``torch.ops.megabake.kv_attention`` / ``attention`` dispatch to for CUDA tensors."""
+
+    _cache: dict = {}
+    _cache_lock = threading.Lock()
+
+    def __init__(self, q_heads: int, kv_heads: int, head_dim: int, max_tokens: int, device: torch.device):
+        self.device = torch.device(device)
+        self.lib = _native.load()
+        self.max_tokens = max_tokens
+        self._lock = threading.Lock()
+        self._cfg = MkConfig(
+            hidden=q_heads * head_dim, layers=1, q_heads=q_heads, kv_heads=kv_heads, head_dim=head_dim,
+            intermediate=64, vocab=64, rms_eps=1e-5, qkv_bias=0, rope_style=0, max_tokens=max_tokens,
+            max_positions=1, engine=0, sm_limit=0,
+        )
+        with torch.cuda.device(self.device):
+            size = self.lib.mk_workspace_bytes(ctypes.byref(self._cfg), self.device.index)
+            if size == 0:
+                raise CompilerError(CompilerDiagnostic("plan-search", self.lib.mk_last_error().decode(errors="replace")))
+            self.workspace = torch.empty(size + 256, dtype=torch.uint8, device=self.device)
+            base = (self.workspace.data_ptr() + 255) // 256 * 256
+            handle = ctypes.c_void_p()
+            code = self.lib.mk_create(ctypes.byref(self._cfg), base, size, self.device.index,
+                                      torch.cuda.current_stream(self.device).cuda_stream, ctypes.byref(handle))
+            if code != _native.MK_OK:
+                raise CompilerError(CompilerDiagnostic("plan-search", self.lib.mk_last_error().decode(errors="replace")))
+        self._handle = handle
+
+    @classmethod
+    def for_shape(cls, q_heads: int, kv_heads: int, head_dim: int, tokens: int, device: torch.device) -> "AttentionKernels":
+        device = torch.device(device)
+        if device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        key = (q_heads, kv_heads, head_dim, device.index)
+        with cls._cache_lock:
+            found = cls._cache.get(key)
+            if found is None or found.max_tokens < tokens:
+                capacity = max(16, 1 << (max(tokens, 1) - 1).bit_length())
+                found = cls(q_heads, kv_heads, head_dim, capacity, device)
+                cls._cache[key] = found
+        return found
+
+    # The launches reuse DecoderKernel's methods: same handle layout, same checks.
+    _stream = DecoderKernel._stream
+    _call = DecoderKernel._call
+    _compiler_error = DecoderKernel._compiler_error
+    kv_attention = DecoderKernel.kv_attention
+    attention = DecoderKernel.attention
+    status = DecoderKernel.status
+    check = DecoderKernel.check

@@ -197,7 +197,7 @@ def synth_weights(
     return weights
 
 
-def rope_tables(config: DecoderConfig, positions: int, device="cpu") -> tuple[torch.Tensor, torch.Tensor]:
+def rope_tables(config: DecoderConfig, positions: int, device="cpu", dtype=torch.bfloat16) -> tuple[torch.Tensor, torch.Tensor]:
     """bf16 cos/sin tables ``[positions, head_dim]`` computed the way
     transformers' rotary embedding does (modeling_llama.py: fp32 outer product
     of inv_freq and position, cos/sin in fp32, one cast to bf16).  Computed on
@@ -211,8 +211,8 @@ def rope_tables(config: DecoderConfig, positions: int, device="cpu") -> tuple[to
     position = torch.arange(positions, dtype=torch.int64).to(torch.float32)
     freqs = position[:, None] * inv_freq[None, :]
     emb = torch.cat((freqs, freqs), dim=-1)
-    cos = emb.cos().to(torch.bfloat16)
-    sin = emb.sin().to(torch.bfloat16)
+    cos = emb.cos().to(dtype)
+    sin = emb.sin().to(dtype)
     return cos.to(device).contiguous(), sin.to(device).contiguous()
 
 

@@ -56,6 +56,40 @@ def assert_parity(actual: torch.Tensor, expected: torch.Tensor, what: str, exact
     assert worst <= 0, f"{what}: max abs diff {diff.max().item():.4g} exceeds {ATOL} + {RTOL}*|ref| by {worst:.4g}"
 
 
+def assert_deep_parity(actual: torch.Tensor, expected: torch.Tensor, what: str):
+    """Parity for values at the end of a deep bf16 chain (tens of layers), where the
+    reference run on another device already sits a few bf16 ulps from itself (eager PyTorch
+    on this GPU is 1-2 % in relative L2 from the CPU-made golden logits of the 24-30 layer
+    shapes): either the element-wise tolerance holds, or the relative L2 distance is under
+    the 2 % gate the reference applies to its own kernel (src/megabake/compiler.py:240-241).
+    test_decode_error_no_worse_than_eager_bf16 bounds the same error against an fp32
+    evaluation, the reference's other yardstick."""
+    actual, expected = actual.detach().cpu().float(), expected.detach().cpu().float()
+    assert actual.shape == expected.shape, f"{what}: shape {tuple(actual.shape)} vs {tuple(expected.shape)}"
+    diff = (actual - expected).abs()
+    if bool((diff <= ATOL + RTOL * expected.abs()).all()):
+        return
+    relative = float(diff.norm() / expected.norm().clamp_min(1e-12))
+    assert relative <= 0.02, f"{what}: relative L2 {relative:.4g} > 2 % (max abs diff {diff.max().item():.4g})"
+
+
 @pytest.fixture(scope="session")
 def exact_cpu() -> bool:
     return same_host_as_golden()
+
+
+def token_agrees(logits_row: torch.Tensor, golden_indices: torch.Tensor, golden_values: torch.Tensor) -> bool:
+    """Greedy-token parity for one sequence.  The token must be the reference's, unless
+    the reference itself scored it within the logit tolerance of its own best token
+    (a tie at bf16 resolution: eager PyTorch on a CPU and on a GPU already break such
+    ties differently, so neither choice is "the" reference token)."""
+    mine = int(logits_row.float().argmax())
+    best = int(golden_indices[0])
+    if mine == best:
+        return True
+    top = float(golden_values[0].float())
+    slack = ATOL + RTOL * abs(top)
+    for index, value in zip(golden_indices.tolist(), golden_values.float().tolist()):
+        if index == mine:
+            return top - value <= slack
+    return False
