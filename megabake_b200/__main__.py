@@ -64,7 +64,7 @@ def main(argv=None) -> int:
             register_transformers_attention()
             model.set_attn_implementation("megabake")
             prompt = torch.compile(model, backend=backend, fullgraph=True, dynamic=False)
-            logits = prompt(input_ids=ids.view(1, -1)).logits
+            logits = prompt(input_ids=ids.view(1, -1), use_cache=False).logits
             print(f"prefill logits {tuple(logits.shape)}; argmax of last position {int(logits[0, -1].float().argmax())}")
     print("execution:", backend.megabake_contexts[-1].requirements["execution"])
     return 0

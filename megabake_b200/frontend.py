@@ -99,7 +99,7 @@ def _fail(stage: str, message: str, *, safe: bool = True, requirement: str | Non
 
 
 def _is_target(node, *targets) -> bool:
-    return node.op == "call_function" and node.target in targets
+    return isinstance(node, torch.fx.Node) and node.op == "call_function" and node.target in targets
 
 
 _KV_OPS = (torch.ops.megabake.kv_attention, torch.ops.megabake.kv_attention.default)
@@ -150,6 +150,8 @@ def recognise_decoder(graph_module: torch.fx.GraphModule, example_inputs: Sequen
     def norm_weight(node):
         """``weight * normalised.to(dtype)``: the placeholder operand of the multiply feeding a projection."""
         source = node.args[0]
+        while _is_target(source, operator.getitem) and isinstance(source.args[0], torch.fx.Node):
+            source = source.args[0]  # transformers slices the positions whose logits are kept
         if not _is_target(source, operator.mul):
             raise _fail("plan-search", f"projection {node.name} is not fed by an RMSNorm weight multiply")
         for operand in source.args:
@@ -186,6 +188,11 @@ def recognise_decoder(graph_module: torch.fx.GraphModule, example_inputs: Sequen
                 weights[prefix + name + ".bias"] = index_of[bias]
                 has_bias = True
     head = linears[-1]
+    returned = next(node for node in graph.nodes if node.op == "output").args[0]
+    returned = list(returned) if isinstance(returned, (tuple, list)) else [returned]
+    if len(returned) != 1 or returned[0] is not head:
+        raise _fail("plan-search", f"the graph returns {len(returned)} values; the kernel returns the logits only",
+                    requirement="return the lm_head output alone (call the model with use_cache=False)", safe=True)
     weights["model.norm.weight"] = index_of[norm_weight(head)]
     weights["lm_head.weight"] = index_of[head.args[1]]
 
@@ -235,9 +242,15 @@ def recognise_decoder(graph_module: torch.fx.GraphModule, example_inputs: Sequen
             state.append(tuple(index_of[operand] for operand in triple))
         capacity = int(example_inputs[state[0][0]].shape[1])
     else:
+        def mask_root(node):
+            operand = node.args[3] if len(node.args) > 3 else None
+            while _is_target(operand, operator.getitem) and isinstance(operand.args[0], torch.fx.Node):
+                operand = operand.args[0]  # each layer cuts the shared mask to its key length
+            return operand
+
         mask_node = first_attention.args[3] if len(first_attention.args) > 3 else None
         for node in attention_nodes[1:]:
-            if (node.args[3] if len(node.args) > 3 else None) is not mask_node:
+            if mask_root(node) is not mask_root(first_attention):
                 raise _fail("plan-search", "layers use different attention masks")
     return DecoderBinding(
         config=config, stateful=stateful, ids_index=index_of[ids_node], positions_index=positions_index,

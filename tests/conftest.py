@@ -93,3 +93,37 @@ def token_agrees(logits_row: torch.Tensor, golden_indices: torch.Tensor, golden_
         if index == mine:
             return top - value <= slack
     return False
+
+
+def relative_l2(actual: torch.Tensor, expected: torch.Tensor) -> float:
+    actual, expected = actual.detach().float().cpu(), expected.detach().float().cpu()
+    return float((actual - expected).norm() / expected.norm().clamp_min(1e-12))
+
+
+def assert_no_worse_than(actual: torch.Tensor, rivals, truth: torch.Tensor, what: str):
+    """The reference's yardstick for deep models (tests/gpu/test_task31_full_model.py:205-211):
+    measured against an fp32 evaluation of the same model, the kernel may be no further off
+    than bf16 evaluations of the reference path (``rivals``: eager PyTorch on this device, the
+    reference's own CPU output from the golden file) times 1.25 plus 1e-3 -- in relative L2
+    and in the largest element error.  At 24 layers x 2048 channels two bf16 evaluations of the
+    reference path differ by 3-4 % in relative L2 (measured: CPU golden vs eager on a B200),
+    which is why the element-wise tolerance cannot be the gate there."""
+    truth = truth.detach().float().cpu()
+    actual = actual.detach().float().cpu()
+    rivals = [rival.detach().float().cpu() for rival in rivals]
+    mine_l2 = relative_l2(actual, truth)
+    rival_l2 = max(relative_l2(rival, truth) for rival in rivals)
+    assert mine_l2 <= 1.25 * rival_l2 + 1e-3, f"{what}: relative L2 to fp32 {mine_l2:.4g} vs reference path {rival_l2:.4g}"
+    mine_abs = float((actual - truth).abs().max())
+    rival_abs = max(float((rival - truth).abs().max()) for rival in rivals)
+    assert mine_abs <= 1.25 * rival_abs + 1e-3, f"{what}: max error to fp32 {mine_abs:.4g} vs reference path {rival_abs:.4g}"
+
+
+def token_defensible(mine_row: torch.Tensor, eager_row: torch.Tensor, truth_row: torch.Tensor) -> bool:
+    """Greedy-token parity where bf16 noise exceeds the gap between candidates: the chosen
+    token's fp32 score must be within the band in which a bf16 evaluation with the eager
+    path's error (E) can move the argmax, 2.25 E + 1e-3 (E for the rival, 1.25 E for us)."""
+    truth_row = truth_row.float()
+    error = float((eager_row.float() - truth_row).abs().max())
+    chosen = int(mine_row.float().argmax())
+    return float(truth_row.max() - truth_row[chosen]) <= 2.25 * error + 1e-3
