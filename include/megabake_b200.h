@@ -147,8 +147,7 @@ int mk_prefill(mk_handle handle, const int64_t* ids, const int64_t* positions, c
 /* y[M,N] = x[M,K] . W[N,K]^T (+ bias[N]), bf16 in/out, fp32 accumulate, one
  * rounding after the bias.  Runs the megakernel's projection engine on one
  * phase.  `handle` supplies workspace and engine; N, K multiples of 64,
- * M <= config.max_tokens, K <= 2048 or N*K/64 small enough per CTA (see
- * mk_last_error).  Synchronous set-up (encodes one TMA descriptor), async launch.
+ * M <= config.max_tokens.  Synchronous set-up (encodes one TMA descriptor), async launch.
  * Reference: the projection body, src/megabake/bodies/gemm.py:629-1114 with
  * its bias epilogue :1223-1251. */
 int mk_linear(mk_handle handle, const void* x, const void* weight, const void* bias, void* y,
@@ -187,6 +186,25 @@ int mk_set_trace(mk_handle handle, void* buffer, int events_per_cta);
 
 /* Number of CTAs each launch uses, bytes of dynamic shared memory, kernels launched so far. */
 int mk_launch_info(mk_handle handle, int32_t* ctas, int32_t* smem_bytes, int64_t* launches);
+
+/* mk_kv_attention without a handle and without any device allocation, for callers
+ * that may not allocate at the point of the call (a server that gave all of its HBM
+ * to its own pool at start and forbids later allocations; a call site where an
+ * allocation would serialise the device).  This entry point has no counterpart in
+ * the reference.  The exchange buffers live in a 4 MiB array inside the library
+ * image: batch * 16 * (80 * kv_heads + 4 * head_dim * q_heads) bytes (+ 512) must
+ * fit, e.g. batch 16 x 32 heads x head_dim 64; larger shapes return
+ * MK_ERR_WORKSPACE (use mk_kv_attention with a caller workspace).  `device` must be
+ * the current device.  The first call on a device looks the array up, sets the
+ * kernel attributes and clears the array on `stream`: make that call before any
+ * stream capture begins.  All calls on a device share the one array: calls that
+ * overlap (different streams or threads without ordering) race, so serialise
+ * them.  The device status word is not reported through this entry point: the
+ * caller guarantees valid_length < capacity (otherwise cache, length and output
+ * are left untouched, as with mk_kv_attention).  Tensors as in mk_kv_attention. */
+int mk_kv_attention_static(int q_heads, int kv_heads, int head_dim, const void* query, const void* key,
+                           const void* value, void* key_cache, void* value_cache, int32_t* valid_length,
+                           int batch, int capacity, void* output, int device, void* stream);
 
 /* Last error text for this thread (host string, valid until the next call). */
 const char* mk_last_error(void);

@@ -27,7 +27,7 @@ ENGINES = {"tcgen05": 0, "simt": 1, "fma": 2}
 
 EXPORTS = (
     "mk_workspace_bytes", "mk_create", "mk_bind_weights", "mk_decode", "mk_prefill", "mk_linear",
-    "mk_kv_attention", "mk_attention", "mk_status", "mk_set_trace", "mk_launch_info", "mk_last_error", "mk_destroy",
+    "mk_kv_attention", "mk_kv_attention_static", "mk_attention", "mk_status", "mk_set_trace", "mk_launch_info", "mk_last_error", "mk_destroy",
 )
 
 
@@ -100,6 +100,11 @@ def load() -> ctypes.CDLL:
     lib.mk_attention.restype = c_int
     lib.mk_attention.argtypes = [
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_void_p, c_void_p,
+    ]
+    lib.mk_kv_attention_static.restype = c_int
+    lib.mk_kv_attention_static.argtypes = [
+        c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+        c_int, c_void_p,
     ]
     lib.mk_status.restype = c_int
     lib.mk_status.argtypes = [c_void_p, c_void_p, POINTER(MkStatusInfo)]

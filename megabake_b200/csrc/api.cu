@@ -619,4 +619,145 @@ int mk_launch_info(mk_handle h, int32_t* ctas, int32_t* smem_bytes, int64_t* lau
   return MK_OK;
 }
 
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------
+// mk_kv_attention_static: the stand-alone decode attention on scratch that lives
+// in the library image instead of in a caller workspace.
+//
+// Who needs it: a caller that may not obtain device memory at the point of the
+// call -- a serving process that handed all of its HBM to its own pool at start
+// and forbids later allocations so a request can never fail or stall on one, or
+// a call site inside a latency-critical loop where an allocation would
+// serialise the device.  Such a caller has no workspace to give mk_create, so
+// the exchange buffers of the split-context attention live in a fixed array of
+// the module, sized for small decode batches.
+constexpr size_t kStaticScratchBytes = 4u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+
+constexpr int kStaticDevices = 16;
+
+struct StaticSlot {
+  bool ready = false;
+  uint8_t* base = nullptr;   // device address of g_static_scratch on this device
+  int grid = 0;
+  long long timeout_cycles = 0;
+  uint32_t epoch = 0, att_epoch = 0;
+  int64_t launches = 0;
+  std::mutex lock;
+};
+StaticSlot g_static_slots[kStaticDevices];
+
+// Scratch layout: control block, (max, sum, stamp) exchange, fp32 chunk partials.
+struct StaticLayout { size_t ctrl, att_xch, att_part, total; };
+
+StaticLayout static_layout(int batch, int q_heads, int kv_heads, int head_dim) {
+  StaticLayout v{};
+  v.ctrl = 0;
+  v.att_xch = align_up(sizeof(Control), 256);
+  v.att_part = align_up(v.att_xch + static_cast<size_t>(batch) * kv_heads * kMaxChunks * kExchangeFloats * 4, 256);
+  v.total = align_up(v.att_part + static_cast<size_t>(batch) * q_heads * kMaxChunks * head_dim * 4, 256);
+  return v;
+}
+
+// One-time set-up per device: symbol address, launch attributes, zeroed scratch.
+int static_setup(StaticSlot& slot, int device, cudaStream_t stream) {
+  int major = 0, coop = 0, khz = 0, sms = 0;
+  MK_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+  MK_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device));
+  MK_CUDA(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, device));
+  MK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  if (major != 10) return fail(MK_ERR_UNSUPPORTED, "device %d is sm_%d0; this library is built for sm_100a only", device, major);
+  if (!coop) return fail(MK_ERR_UNSUPPORTED, "device %d does not support cooperative launch", device);
+  void* address = nullptr;
+  const cudaError_t found = cudaGetSymbolAddress(&address, g_static_scratch);
+  if (found != cudaSuccess || !address)
+    return fail(MK_ERR_CUDA, "cudaGetSymbolAddress(static scratch) on device %d: %s", device, cudaGetErrorString(found));
+  MK_CUDA(cudaFuncSetAttribute(megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+  MK_CUDA(cudaFuncSetAttribute(megakernel, cudaFuncAttributePreferredSharedMemoryCarveout, (kSmemBytes * 100 + 233471) / 233472));
+  int per_sm = 0;
+  MK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, megakernel, kThreads, kSmemBytes));
+  if (per_sm < 1) return fail(MK_ERR_UNSUPPORTED, "the megakernel does not fit on an SM of device %d", device);
+  // Barrier counter, abort flag, status word and every exchange stamp must start at zero.
+  MK_CUDA(cudaMemsetAsync(address, 0, kStaticScratchBytes, stream));
+  double ms = 2000.0;
+  if (const char* env = getenv("MEGABAKE_WAIT_LIMIT_MS")) ms = atof(env) > 0 ? atof(env) : ms;
+  slot.base = static_cast<uint8_t*>(address);
+  slot.grid = sms;
+  slot.timeout_cycles = static_cast<long long>(ms * static_cast<double>(khz));
+  slot.epoch = slot.att_epoch = 0;
+  slot.launches = 0;
+  slot.ready = true;
+  return MK_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+// Overlapping calls on one device (two streams, two threads) share the scratch and race:
+// callers serialise them.  The first call on a device does the set-up (symbol lookup,
+// function attributes, clearing the scratch on `stream`); make it before any stream capture.
+int mk_kv_attention_static(int q_heads, int kv_heads, int head_dim, const void* query, const void* key,
+                           const void* value, void* key_cache, void* value_cache, int32_t* valid_length, int batch,
+                           int capacity, void* output, int device, void* stream) {
+  if (!query || !key || !value || !key_cache || !value_cache || !valid_length || !output)
+    return fail(MK_ERR_INVALID, "mk_kv_attention_static: null argument");
+  if (device < 0 || device >= kStaticDevices)
+    return fail(MK_ERR_INVALID, "mk_kv_attention_static: device %d outside [0, %d)", device, kStaticDevices);
+  if (batch < 1 || capacity < 1 || q_heads < 1 || kv_heads < 1)
+    return fail(MK_ERR_INVALID, "mk_kv_attention_static: sizes must be positive");
+  if (head_dim != 64 && head_dim != 128) return fail(MK_ERR_UNSUPPORTED, "mk_kv_attention_static: head_dim must be 64 or 128");
+  if (q_heads % kv_heads || q_heads / kv_heads > 8)
+    return fail(MK_ERR_UNSUPPORTED, "mk_kv_attention_static: q_heads must be 1..8 times kv_heads");
+  const StaticLayout lay = static_layout(batch, q_heads, kv_heads, head_dim);
+  if (lay.total > kStaticScratchBytes)
+    return fail(MK_ERR_WORKSPACE,
+                "mk_kv_attention_static: batch %d x %d query heads x head_dim %d needs %zu bytes of scratch, the static "
+                "array holds %zu; use mk_kv_attention with a caller workspace", batch, q_heads, head_dim, lay.total,
+                kStaticScratchBytes);
+  if (reinterpret_cast<uintptr_t>(key_cache) % 16 || reinterpret_cast<uintptr_t>(value_cache) % 16)
+    return fail(MK_ERR_ALIGNMENT, "mk_kv_attention_static: caches must be 16-byte aligned");
+  int current = -1;
+  MK_CUDA(cudaGetDevice(&current));
+  if (current != device)
+    return fail(MK_ERR_INVALID, "mk_kv_attention_static: device %d is not the current device (%d)", device, current);
+  StaticSlot& slot = g_static_slots[device];
+  std::lock_guard<std::mutex> guard(slot.lock);
+  if (!slot.ready) {
+    if (int e = static_setup(slot, device, static_cast<cudaStream_t>(stream))) return e;
+  }
+  // A handle on the stack (no device memory of its own) lets the shared parameter and
+  // launch helpers serve this entry point unchanged.
+  mk_handle_s view;
+  memset(&view.cfg, 0, sizeof(view.cfg));
+  view.cfg.hidden = q_heads * head_dim; view.cfg.layers = 1; view.cfg.q_heads = q_heads; view.cfg.kv_heads = kv_heads;
+  view.cfg.head_dim = head_dim; view.cfg.intermediate = 64; view.cfg.vocab = 64; view.cfg.rms_eps = 1e-5f;
+  view.cfg.rope_style = MK_ROPE_HF; view.cfg.max_tokens = batch; view.cfg.max_positions = capacity;
+  view.cfg.engine = MK_ENGINE_TCGEN05;
+  view.device = device; view.grid = slot.grid; view.ws = slot.base;
+  view.cv = Carve{};
+  view.cv.ctrl = lay.ctrl; view.cv.att_xch = lay.att_xch; view.cv.att_part = lay.att_part; view.cv.total = lay.total;
+  view.bound = false;
+  memset(&view.weights, 0, sizeof(view.weights));
+  view.epoch = slot.epoch; view.att_epoch = slot.att_epoch; view.launches = slot.launches;
+  view.timeout_cycles = slot.timeout_cycles;
+  view.att_scale = static_cast<float>(std::pow(static_cast<double>(head_dim), -0.5));
+  view.fma_ok = false; view.trace = nullptr; view.trace_cap = 0;
+  if (int e = attention_fits(&view, capacity, "mk_kv_attention_static")) return e;
+  KParams p;
+  base_params(&view, p);
+  p.mode = MODE_KVATT; p.m = batch; p.batch = batch; p.seq = 1; p.capacity = capacity;
+  p.n_gemm = 0; p.nbar = 1;
+  p.op_q = static_cast<const bf16*>(query); p.op_k = static_cast<const bf16*>(key); p.op_v = static_cast<const bf16*>(value);
+  p.op_out = static_cast<bf16*>(output);
+  p.kc[0] = key_cache; p.vc[0] = value_cache; p.len[0] = valid_length;
+  if (int e = launch(&view, p, stream, 1)) return e;
+  slot.epoch = view.epoch; slot.att_epoch = view.att_epoch; slot.launches = view.launches;
+  return MK_OK;
+}
+
 }  // extern "C"
