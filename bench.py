@@ -37,6 +37,9 @@ sys.path.insert(0, str(ROOT))
 from megabake_b200.synth import CONFIGS, new_kv_state, synth_ids, synth_normal, synth_weights  # noqa: E402
 
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
+# profiles/megakernel_decode_smollm-1.7b_launch_list.md (mean of the two captured launches).
+NCU_TRAFFIC = {("smollm-1.7b", 1, 1024): 3_805_020_672}
 
 
 def parse_args():
@@ -164,7 +167,7 @@ def main():
     workload = (f"{config.name}-shaped bf16 decode, batch {args.batch}, KV capacity {args.capacity} "
                 f"pre-filled to {args.context}")
     base = {
-        "metric": "decode_tokens_per_s", "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+        "metric": "decode tokens/s (us/call and roofline fraction alongside)", "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": workload, "parallelism": f"dp{args.gpus}" if args.gpus > 1 else "single",
@@ -290,13 +293,7 @@ def main():
     bytes_per_launch = config.decode_bytes(args.batch, int(round(mean_context)))
     launch_ms = statistics.mean(per_launch_ms)
     achieved = bytes_per_launch / (launch_ms / 1e3) / 1e9
-    traffic = None
-    traffic_file = ROOT / "profiles" / "decode_traffic.json"
-    if traffic_file.exists():
-        try:
-            traffic = json.loads(traffic_file.read_text()).get(f"{args.config}_b{args.batch}")
-        except Exception:
-            traffic = None
+    traffic = NCU_TRAFFIC.get((args.config, args.batch, args.context))
     line = dict(base)
     line.update({
         "value": value, "ms_per_step": total_ms / args.steps, "us_per_call": 1e3 * total_ms / args.steps,
