@@ -45,11 +45,14 @@ typedef enum mk_device_status {
 } mk_device_status;
 
 enum { MK_ROPE_HF = 0, MK_ROPE_HALF_SWAP = 1 };
-/* TCGEN05: tensor-core projections for every launch (the default).
- * FMA: launches of at most 4 tokens consume the TMA-fed weight ring with CUDA-core FMAs
- *      instead of tcgen05.mma; larger launches still use tcgen05.
+/* TCGEN05: tensor-core projections (tcgen05.mma, TMEM accumulators) for every launch.
+ * FMA: decode launches of at most 4 tokens run the small-launch kernel, which consumes the
+ *      TMA-fed weight ring with CUDA-core FMAs (a matrix-vector product cannot fill a
+ *      128-row MMA); every other launch uses tcgen05.  Falls back to tcgen05 when the shape
+ *      does not fit the small kernel (hidden > 2048 or a K slice longer than 2048).
+ * AUTO: the faster of the two per launch; today the same choice as FMA.
  * SIMT: bring-up engine without TMA or tensor cores. */
-enum { MK_ENGINE_TCGEN05 = 0, MK_ENGINE_SIMT = 1, MK_ENGINE_FMA = 2 };
+enum { MK_ENGINE_TCGEN05 = 0, MK_ENGINE_SIMT = 1, MK_ENGINE_FMA = 2, MK_ENGINE_AUTO = 3 };
 
 /* Decoder shape.  Mirrors the facts the reference reads off the captured graph
  * (src/megabake/lowering.py:1851-1870 for the attention contract,

@@ -23,7 +23,7 @@ MK_ERR_INVALID, MK_ERR_UNSUPPORTED, MK_ERR_CUDA, MK_ERR_ALIGNMENT = 1, 2, 3, 4
 MK_ERR_WORKSPACE, MK_ERR_UNBOUND, MK_ERR_DEVICE_STATUS = 5, 6, 7
 STATUS_NAMES = {0: "OK", 1: "KV_OVERFLOW", 2: "BAD_INDEX", 3: "TIMEOUT"}
 ROPE_STYLES = {"hf": 0, "half_swap": 1}
-ENGINES = {"tcgen05": 0, "simt": 1, "fma": 2}
+ENGINES = {"tcgen05": 0, "simt": 1, "fma": 2, "auto": 3}
 
 EXPORTS = (
     "mk_workspace_bytes", "mk_create", "mk_bind_weights", "mk_decode", "mk_prefill", "mk_linear",

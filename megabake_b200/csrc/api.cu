@@ -14,7 +14,7 @@
 #include <new>
 #include <vector>
 
-#include "decoder_kernel.cuh"
+#include "decode_small.cuh"
 
 using namespace mk;
 
@@ -56,8 +56,8 @@ Carve carve(const mk_config& c) {
   };
   const size_t m = static_cast<size_t>(c.max_tokens);
   v.ctrl = take(sizeof(Control));
-  v.tmaps = take(sizeof(CUtensorMap) * (2 * maps_per_table(c) + 1));    // split table, plain table, mk_linear
-  v.phases = take(sizeof(GemmPhase) * (2 * phases_per_table(c) + 1));
+  v.tmaps = take(sizeof(CUtensorMap) * (3 * maps_per_table(c) + 1));    // split table, plain table, small-launch table, mk_linear
+  v.phases = take(sizeof(GemmPhase) * (3 * phases_per_table(c) + 1));
   v.hidden = take(m * c.hidden * 2);
   v.hidden2 = take(static_cast<size_t>(kSplitTokens) * c.hidden * 2);
   v.qkv = take(m * qkv_width(c) * 2);
@@ -80,7 +80,7 @@ int check_config(const mk_config& c) {
   if (c.q_heads / c.kv_heads > 8) return fail(MK_ERR_UNSUPPORTED, "config: at most 8 query heads per kv head");
   if (c.hidden % 64 || c.intermediate % 64)
     return fail(MK_ERR_UNSUPPORTED, "config: hidden and intermediate must be multiples of 64");
-  if (c.engine != MK_ENGINE_TCGEN05 && c.engine != MK_ENGINE_SIMT && c.engine != MK_ENGINE_FMA)
+  if (c.engine != MK_ENGINE_TCGEN05 && c.engine != MK_ENGINE_SIMT && c.engine != MK_ENGINE_FMA && c.engine != MK_ENGINE_AUTO)
     return fail(MK_ERR_INVALID, "config: engine");
   if (c.rope_style != MK_ROPE_HF && c.rope_style != MK_ROPE_HALF_SWAP) return fail(MK_ERR_INVALID, "config: rope_style");
   return MK_OK;
@@ -107,17 +107,19 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 }
 
 // bf16 [rows, k] row-major -> boxes of box_rows rows x 64 columns, 128-byte swizzle.
-int encode_weight_map(CUtensorMap* out, const void* base, int rows, int k, int box_rows) {
+int encode_weight_map(CUtensorMap* out, const void* base, int rows, int k, int box_rows, int box_chunks = 1) {
   if (reinterpret_cast<uintptr_t>(base) % 16) return fail(MK_ERR_ALIGNMENT, "weight base %p is not 16-byte aligned", base);
   auto fn = encode_fn();
   if (!fn) return fail(MK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
-  const cuuint32_t box[2] = {kChunkK, static_cast<cuuint32_t>(box_rows)};
+  // box_chunks == 1: the tensor core's operand layout (64 elements = 128 bytes per row, 128-byte swizzle).
+  // box_chunks > 1: plain rows of box_chunks * 128 bytes for the CUDA-core consumer (no swizzle, up to 256 elements).
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kChunkK * box_chunks), static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t elem[2] = {1, 1};
   const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, box_chunks == 1 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(MK_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (rows %d, k %d)", (int)r, rows, k);
   return MK_OK;
 }
@@ -136,7 +138,7 @@ struct mk_handle_s {
   int64_t launches;
   long long timeout_cycles;
   float att_scale;
-  bool fma_ok;  // every phase of the split-K table keeps its K slice inside the activation slots
+  bool fma_ok;  // the small-launch kernel can run the split-K table: every K slice fits its fp32 operand buffer
   unsigned long long* trace;
   int trace_cap;
   std::mutex lock;
@@ -168,6 +170,7 @@ int choose_rows(const GemmPhase& ph, int slots) {
 // bandwidth busy (the copy engine retires roughly one box per 0.1 us), so a
 // projection with few output rows per CTA is cut along K as well.
 constexpr int kGoodBoxRows = 40;
+constexpr int kFatCopyBytes = 30 * 1024;  // largest weight copy of the small-launch table: four fit the ring
 
 void finish_phase(GemmPhase& ph, int grid, bool allow_split) {
   ph.kc = ph.k / kChunkK;
@@ -187,6 +190,7 @@ void finish_phase(GemmPhase& ph, int grid, bool allow_split) {
   ph.ksplit = best_split;
   ph.kslice = ph.kc / best_split;
   ph.rows = best_rows;
+  ph.kb = 1;
   ph.gran = (ph.rows * 128 + kGranule - 1) / kGranule;
   const int nseg = ph.nacc == 2 ? 1 : ph.nseg;
   int tile = 0;
@@ -210,7 +214,7 @@ void base_params(mk_handle h, KParams& p) {
   p.head_dim = c.head_dim; p.inter = c.intermediate; p.vocab = c.vocab; p.eps = c.rms_eps;
   p.rope_style = c.rope_style; p.prefill_rope_style = MK_ROPE_HF;
   p.att_scale = h->att_scale;
-  p.engine = c.engine == MK_ENGINE_FMA ? MK_ENGINE_TCGEN05 : c.engine;
+  p.engine = c.engine == MK_ENGINE_SIMT ? MK_ENGINE_SIMT : MK_ENGINE_TCGEN05;
   p.epoch = h->epoch;
   p.att_epoch = h->att_epoch;
   p.qkv_ld = qkv_width(c);
@@ -232,10 +236,14 @@ void base_params(mk_handle h, KParams& p) {
   p.sin_t = static_cast<const bf16*>(h->weights.rope_sin);
 }
 
-int launch(mk_handle h, KParams& p, void* stream, int attention_phases = 0) {
+int launch(mk_handle h, KParams& p, void* stream, int attention_phases = 0, bool small = false) {
   void* args[] = {&p};
-  MK_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(&megakernel), dim3(h->grid), dim3(kThreads), args,
-                                      kSmemBytes, static_cast<cudaStream_t>(stream)));
+  if (small)
+    MK_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(&megakernel_small), dim3(h->grid),
+                                        dim3(kSmallThreads), args, kSmemBytes, static_cast<cudaStream_t>(stream)));
+  else
+    MK_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(&megakernel), dim3(h->grid), dim3(kThreads), args,
+                                        kSmemBytes, static_cast<cudaStream_t>(stream)));
   h->epoch += static_cast<uint32_t>(p.nbar) * static_cast<uint32_t>(h->grid);
   h->att_epoch += static_cast<uint32_t>(attention_phases);
   h->launches += 1;
@@ -285,9 +293,13 @@ int mk_create(const mk_config* config, void* workspace, size_t workspace_bytes, 
   if (!coop) return fail(MK_ERR_UNSUPPORTED, "device %d does not support cooperative launch", device);
   MK_CUDA(cudaFuncSetAttribute(megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
   MK_CUDA(cudaFuncSetAttribute(megakernel, cudaFuncAttributePreferredSharedMemoryCarveout, (kSmemBytes * 100 + 233471) / 233472));
+  MK_CUDA(cudaFuncSetAttribute(megakernel_small, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+  MK_CUDA(cudaFuncSetAttribute(megakernel_small, cudaFuncAttributePreferredSharedMemoryCarveout, (kSmemBytes * 100 + 233471) / 233472));
   int per_sm = 0;
   MK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, megakernel, kThreads, kSmemBytes));
   if (per_sm < 1) return fail(MK_ERR_UNSUPPORTED, "the megakernel does not fit on an SM of device %d", device);
+  MK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, megakernel_small, kSmallThreads, kSmemBytes));
+  if (per_sm < 1) return fail(MK_ERR_UNSUPPORTED, "the small-launch megakernel does not fit on an SM of device %d", device);
   mk_handle h = new (std::nothrow) mk_handle_s();
   if (!h) return fail(MK_ERR_INVALID, "out of host memory");
   h->cfg = *config;
@@ -329,8 +341,8 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
   const int L = c.layers;
   const int q_size = c.q_heads * c.head_dim, kv_size = c.kv_heads * c.head_dim;
   const size_t nmaps = maps_per_table(c), nphases = phases_per_table(c);
-  std::vector<CUtensorMap> maps(2 * nmaps);
-  std::vector<GemmPhase> phases(2 * nphases);
+  std::vector<CUtensorMap> maps(3 * nmaps);
+  std::vector<GemmPhase> phases(3 * nphases);
   CUtensorMap* dmaps = at<CUtensorMap>(h, h->cv.tmaps);
   bf16* hidden_a = at<bf16>(h, h->cv.hidden);
   bf16* hidden_b = at<bf16>(h, h->cv.hidden2);
@@ -426,15 +438,35 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
     finish_phase(head, h->grid, false);
     if (int e = encode_weight_map(&tmaps_host[7 * L], w->lm_head, c.vocab, c.hidden, head.rows)) return e;
   }
+  // Table 2: the split-K table again for the small-launch kernel, whose CUDA-core consumer takes
+  // the weights as plain rows: one copy brings `kb` K chunks of a tile's rows (a copy of less than
+  // ~16 KB cannot keep an SM's share of HBM busy: the copy engine retires about three per microsecond).
+  h->fma_ok = split_table_ok(c);
+  for (size_t i = 0; i < nphases && h->fma_ok; ++i)
+    if (phases[i].kslice > kBSlots || phases[i].rows > kTileRows) h->fma_ok = false;
+  if (h->fma_ok) {
+    for (size_t i = 0; i < nphases; ++i) {
+      GemmPhase& ph = phases[2 * nphases + i];
+      ph = phases[i];
+      int kb = 1;
+      for (int cand = 2; cand <= 4; ++cand)
+        if (ph.kslice % cand == 0 && ph.rows * cand * 128 <= kFatCopyBytes) kb = cand;
+      ph.kb = kb;
+      ph.gran = (ph.rows * kb * 128 + kGranule - 1) / kGranule;
+      const int nseg = ph.nacc == 2 ? 2 : ph.nseg;
+      for (int sg = 0; sg < nseg; ++sg) {
+        const size_t index = static_cast<size_t>(ph.tmap[sg] - dmaps);  // same matrix, same slot in the third set
+        ph.tmap[sg] = dmaps + 2 * nmaps + index;
+        if (int e = encode_weight_map(&maps[2 * nmaps + index], ph.w[sg], ph.n[sg], ph.k, ph.rows, kb)) return e;
+      }
+    }
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   MK_CUDA(cudaMemcpyAsync(dmaps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, s));
   MK_CUDA(cudaMemcpyAsync(at<GemmPhase>(h, h->cv.phases), phases.data(), phases.size() * sizeof(GemmPhase),
                           cudaMemcpyHostToDevice, s));
   // The source vectors die at return: make sure the copies have read them.
   MK_CUDA(cudaStreamSynchronize(s));
-  h->fma_ok = split_table_ok(c);
-  for (size_t i = 0; i < nphases && h->fma_ok; ++i)
-    if (phases[i].kslice > kBSlots || phases[i].rows > kTileRows) h->fma_ok = false;
   h->layers.assign(w->layers, w->layers + L);
   h->weights = *w;
   h->weights.layers = h->layers.data();
@@ -466,14 +498,15 @@ int mk_decode(mk_handle h, const int64_t* ids, const int64_t* positions, int bat
   p.mode = MODE_DECODE; p.m = batch; p.batch = batch; p.seq = 1; p.capacity = capacity;
   p.split = (batch <= kSplitTokens && split_table_ok(h->cfg)) ? 1 : 0;
   p.phases = at<GemmPhase>(h, h->cv.phases) + (p.split ? 0 : phases_per_table(h->cfg));
-  if (h->cfg.engine == MK_ENGINE_FMA && p.split && h->fma_ok) p.engine = ENGINE_FMA;
+  const bool small = (h->cfg.engine == MK_ENGINE_FMA || h->cfg.engine == MK_ENGINE_AUTO) && p.split && h->fma_ok;
+  if (small) p.phases = at<GemmPhase>(h, h->cv.phases) + 2 * phases_per_table(h->cfg);
   p.n_gemm = 4 * L + 1;
   p.nbar = 5 * L;
   p.stream_once = (ntt == 1);
   p.ids = reinterpret_cast<const long long*>(ids);
   p.pos = reinterpret_cast<const long long*>(positions);
   p.logits = static_cast<bf16*>(logits);
-  return launch(h, p, stream, L);
+  return launch(h, p, stream, L, small);
 }
 
 int mk_prefill(mk_handle h, const int64_t* ids, const int64_t* positions, const void* mask, int batch, int sequence,
@@ -495,7 +528,6 @@ int mk_prefill(mk_handle h, const int64_t* ids, const int64_t* positions, const 
   p.mode = MODE_PREFILL; p.m = static_cast<int>(m); p.batch = batch; p.seq = sequence; p.capacity = 0;
   p.split = (m <= kSplitTokens && split_table_ok(h->cfg)) ? 1 : 0;
   p.phases = at<GemmPhase>(h, h->cv.phases) + (p.split ? 0 : phases_per_table(h->cfg));
-  if (h->cfg.engine == MK_ENGINE_FMA && p.split && h->fma_ok) p.engine = ENGINE_FMA;
   p.n_gemm = 4 * L + 1;
   p.nbar = 6 * L;
   p.stream_once = (ntt == 1);
@@ -514,8 +546,8 @@ int mk_linear(mk_handle h, const void* x, const void* weight, const void* bias, 
   if (n < 1 || k < 64 || k % 64) return fail(MK_ERR_UNSUPPORTED, "mk_linear: k must be a positive multiple of 64");
   if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(y) % 2)
     return fail(MK_ERR_ALIGNMENT, "mk_linear: x must be 16-byte aligned");
-  CUtensorMap* dmap = at<CUtensorMap>(h, h->cv.tmaps) + 2 * maps_per_table(h->cfg);
-  GemmPhase* dphase = at<GemmPhase>(h, h->cv.phases) + 2 * phases_per_table(h->cfg);
+  CUtensorMap* dmap = at<CUtensorMap>(h, h->cv.tmaps) + 3 * maps_per_table(h->cfg);
+  GemmPhase* dphase = at<GemmPhase>(h, h->cv.phases) + 3 * phases_per_table(h->cfg);
   GemmPhase ph;
   memset(&ph, 0, sizeof(ph));
   ph.nseg = 1; ph.nacc = 1; ph.k = k;
@@ -538,7 +570,6 @@ int mk_linear(mk_handle h, const void* x, const void* weight, const void* bias, 
   p.n_gemm = 1;
   p.nbar = 0;
   p.stream_once = (token_tiles(m) == 1);
-  if (h->cfg.engine == MK_ENGINE_FMA && m <= kSplitTokens && ph.kslice <= kBSlots) p.engine = ENGINE_FMA;
   return launch(h, p, stream);
 }
 

@@ -45,6 +45,9 @@ struct SmemMisc {
   int trace_n;  // events this CTA has recorded
   float rinv[kTok];
   float red4[4];           // cross-warp sums of the block-wide RMSNorm
+  float sred[kSplitTokens][8];   // small-launch kernel: per-token cross-warp sums
+  long long pos_s[kSplitTokens]; // small-launch kernel: validated positions
+  int len_s[MK_MAX_LAYERS];      // small-launch kernel: valid lengths before this call
   uint8_t qstart[kChunkBars];  // producer: first ring granule of each chunk in flight (by sequence % kChunkBars)
   uint8_t qgran[kChunkBars];   // producer: granules of that chunk
   GemmPhase phase[2];  // worker-side copies of the current / next projection phase
@@ -210,8 +213,9 @@ __device__ __noinline__ void producer_loop(const Ctx& cx) {
   for (int gp = 0; gp < p.n_gemm && ok; ++gp) {
     const GemmPhase* ph = p.phases + gp;
     const int nacc = ph->nacc, gran = ph->gran, nunits = ph->nunits, ksplit = ph->ksplit, kslice = ph->kslice;
-    const uint32_t bytes = static_cast<uint32_t>(ph->rows) * 128u;
-    const int rot = k_rotation(cx.cta, cx.grid, kslice);
+    const int kb = ph->kb;  // K chunks per copy (1 unless this is the small-launch table)
+    const uint32_t bytes = static_cast<uint32_t>(ph->rows) * 128u * static_cast<uint32_t>(kb);
+    const int rot = k_rotation(cx.cta, cx.grid, kslice / kb) * kb;
     const bool streamed = kslice > kBSlots;
     const int batches = (kslice + kBHalf - 1) / kBHalf;
     const CUtensorMap* map_a1 = ph->tmap[1];
@@ -225,7 +229,7 @@ __device__ __noinline__ void producer_loop(const Ctx& cx) {
         // visiting order: rotated within the slice (whole batches when the operand is streamed)
         int k = streamed ? rot * kBHalf : rot;
         int batch = rot, left_in_batch = streamed ? min(kBHalf, kslice - rot * kBHalf) : kslice;
-        for (int i = 0; i < kslice && ok; ++i) {
+        for (int i = 0; i < kslice && ok; i += kb) {
           for (int a = 0; a < nacc; ++a) {
             if (head + gran > kRingGranules) {  // the tail fragment is skipped: free it too, then wrap
               if (!reclaim(head, kRingGranules, gp)) { ok = false; break; }
@@ -244,7 +248,7 @@ __device__ __noinline__ void producer_loop(const Ctx& cx) {
             ++seq;
           }
           // next chunk of the slice in visiting order
-          ++k;
+          k += kb;
           if (streamed) {
             if (--left_in_batch == 0) {
               batch = (batch + 1 == batches) ? 0 : batch + 1;
@@ -810,135 +814,6 @@ __device__ __noinline__ bool worker_gemm_tc(const Ctx& cx, int gp, WorkerState& 
   return true;
 }
 
-// Projection phase on the FMA engine: for launches of at most four tokens the
-// tensor core is the wrong tool (one UMMA of 128 weight rows by 16 token
-// columns occupies the tensor pipe for about a hundred cycles whatever the
-// token count, which caps a CTA near 40 bytes of weights per cycle and far less
-// for the short tiles an even split over 148 CTAs wants).  Here the four worker
-// warps read the TMA-filled ring slots themselves: eight lanes share a weight
-// row (16 bytes each), four rows per warp per step, fp32 FMA chains per
-// (row, lane), a fixed shuffle tree across the eight lanes at the end.  About
-// eighty issue cycles per 7 KB chunk, so the weight stream, not the arithmetic,
-// is the limit.  The ring, the producer, the activation slots and the
-// consumer-side split-K reduction are the same as for the tcgen05 engine.
-struct FmaState {
-  int head, seq;  // ring replay, same sequence as the producer's
-  long long waited, arith;  // profile: cycles waiting for weights / consuming them
-};
-
-template <int MT, int NACC>
-__device__ __noinline__ bool worker_gemm_fma(const Ctx& cx, int gp, FmaState& fs, int wtid) {
-  const KParams& p = *cx.p;
-  const GemmPhase* ph = &cx.misc->phase[gp & 1];
-  const int nunits = ph->nunits, rows = ph->rows, ksplit = ph->ksplit, kslice = ph->kslice;
-  const int gran = ph->gran;
-  const bool per_unit = ksplit > 1;
-  const int warp = wtid >> 5, lane = wtid & 31;
-  const int c = lane & 7, rsub = lane >> 3;
-  const int rot = k_rotation(cx.cta, cx.grid, kslice);
-  const int nch = (ph->bmode == B_ATTN) ? *reinterpret_cast<volatile int*>(&cx.ctrl->att_nch) : 1;
-  const int mt = p.m;  // == MT, one token tile
-  const uint32_t b_region = smem_u32(cx.smem_b), ring_base = smem_u32(cx.smem_a);
-  // Byte offset of this lane's 16 bytes in row (j * 16 + warp * 4 + rsub); (row & 7) does not depend on j.
-  const int lane_row = warp * 4 + rsub;
-  const uint32_t lane_off = lane_row * 128 + ((c ^ (lane_row & 7)) << 4);
-  int head = fs.head, seq = fs.seq;
-  bool ok = true;
-  long long waited = 0, arith = 0;
-  if (cx.cta < nunits) {
-    trace_event(cx, wtid, EV_PHASE_ENTER);
-    for (int unit = cx.cta; unit < nunits && ok; unit += cx.grid) {
-      const int tile = unit / ksplit, slice = unit - tile * ksplit;
-      if (per_unit || unit == cx.cta) {
-        named_bar_sync(1, kWorkers);  // the previous unit has finished reading the slots
-        stage_operand(cx, ph, slice * kslice, kslice, 0, mt, wtid, nch);
-        named_bar_sync(1, kWorkers);
-        if (unit == cx.cta) trace_event(cx, wtid, EV_B_STAGED);
-      }
-      // All eight row steps of the 128-row MMA-sized tile are always computed; the ones
-      // past `rows` read stale shared memory and are dropped at the end.
-      float acc[NACC][8][MT];
-#pragma unroll
-      for (int a = 0; a < NACC; ++a)
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-#pragma unroll
-          for (int m = 0; m < MT; ++m) acc[a][j][m] = 0.f;
-      int slot = rot;
-      for (int i = 0; i < kslice; ++i) {
-        float xf[MT][8];
-#pragma unroll
-        for (int m = 0; m < MT; ++m)
-          unpack8(lds_v4(b_region + slot * kBSlotBytes + m * 128 + ((c ^ m) << 4)), xf[m]);
-#pragma unroll
-        for (int a = 0; a < NACC; ++a) {
-          if (head + gran > kRingGranules) head = 0;
-          const uint32_t base = ring_base + head * kGranule + lane_off;
-          head += gran;
-          const uint32_t bar = seq % kChunkBars;
-          const bool got = __all_sync(0xffffffffu, wait_mbar_timed(cx, smem_u32(&cx.misc->full[bar]),
-                                                                   (seq / kChunkBars) & 1, SITE_MMA_FULL, gp, waited));
-          ok = ok && got;
-          const long long t_arith = clock64();
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            float wf[8];
-            unpack8(lds_v4(base + j * 2048), wf);
-#pragma unroll
-            for (int m = 0; m < MT; ++m)
-#pragma unroll
-              for (int e = 0; e < 8; ++e) acc[a][j][m] = fmaf(wf[e], xf[m][e], acc[a][j][m]);
-          }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&cx.misc->empty[bar]));
-          arith += clock64() - t_arith;
-          seq += 1;
-        }
-        ++slot;
-        if (slot == kslice) slot = 0;
-        if (!ok) break;
-      }
-      if (!ok) break;
-      // fixed-order sum over the eight lanes of a row, then the row's epilogue on lane c == 0
-      int seg, row0;
-      tile_origin(ph, tile, seg, row0);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float v[2][MT];
-#pragma unroll
-        for (int a = 0; a < NACC; ++a)
-#pragma unroll
-          for (int m = 0; m < MT; ++m) {
-            float x = acc[a][j][m];
-            x += __shfl_xor_sync(0xffffffffu, x, 1);
-            x += __shfl_xor_sync(0xffffffffu, x, 2);
-            x += __shfl_xor_sync(0xffffffffu, x, 4);
-            v[a][m] = x;
-          }
-        const int r = j * 16 + lane_row;
-        const int n = row0 + r;
-        if (c == 0 && r < rows && n < ph->n[seg]) {
-          if (ph->epi == EPI_PARTIAL) {
-            store_partial<MT>(cx, ph, slice, n, v[0], 0, mt);
-          } else {
-            float pre[MT];
-            epilogue_prefetch<MT>(cx, ph, seg, n, 0, mt, pre);
-            apply_epilogue<MT>(cx, ph, seg, n, v, pre, 0, mt);
-          }
-        }
-      }
-    }
-    trace_event(cx, wtid, EV_PHASE_DONE);
-  }
-  fs.head = head;
-  fs.seq = seq;
-  fs.waited += waited;
-  fs.arith += arith;
-  if (!workers_ok(cx, ok)) return false;
-  prefetch_phase(cx, gp + 1, wtid);
-  return true;
-}
-
 // One 8-element vector of the residual stream after the pending update (see stage_norm_block).
 __device__ __forceinline__ uint4 residual_vec(const Ctx& cx, const GemmPhase* ph, int token, int v) {
   const KParams& p = *cx.p;
@@ -1399,19 +1274,8 @@ __device__ void worker_loop(const Ctx& cx, int wtid) {
   ws.tiles = 0; ws.passed = 0;
   ws.be_cnt[0] = ws.be_cnt[1] = 0;
   ws.outstanding[0] = ws.outstanding[1] = false;
-  FmaState fs;
-  fs.head = 0; fs.seq = 0; fs.waited = 0; fs.arith = 0;
   auto gemm = [&](int gp) -> bool {
     if (p.engine == MK_ENGINE_SIMT) return worker_gemm_simt(cx, gp, wtid);
-    if (p.engine == ENGINE_FMA) {
-      const bool pair = cx.misc->phase[gp & 1].nacc == 2;
-      switch (p.m) {
-        case 1: return pair ? worker_gemm_fma<1, 2>(cx, gp, fs, wtid) : worker_gemm_fma<1, 1>(cx, gp, fs, wtid);
-        case 2: return pair ? worker_gemm_fma<2, 2>(cx, gp, fs, wtid) : worker_gemm_fma<2, 1>(cx, gp, fs, wtid);
-        case 3: return pair ? worker_gemm_fma<3, 2>(cx, gp, fs, wtid) : worker_gemm_fma<3, 1>(cx, gp, fs, wtid);
-        default: return pair ? worker_gemm_fma<4, 2>(cx, gp, fs, wtid) : worker_gemm_fma<4, 1>(cx, gp, fs, wtid);
-      }
-    }
     return worker_gemm_tc(cx, gp, ws, wtid);
   };
   const int q_size = p.q_heads * p.head_dim, kv_size = p.kv_heads * p.head_dim;
@@ -1505,11 +1369,6 @@ __device__ void worker_loop(const Ctx& cx, int wtid) {
   }
 #undef MK_DEBUG_STEP
   gemm(p.layers * 4);                                       // [final RMSNorm] lm_head
-  if (p.trace_cap >= 8 && p.engine == ENGINE_FMA && wtid == 0) {
-    unsigned long long* row = p.trace + static_cast<size_t>(cx.cta) * p.trace_cap + p.trace_cap;
-    row[-5] = (11ull << 56) | static_cast<unsigned long long>(fs.waited);
-    row[-6] = (12ull << 56) | static_cast<unsigned long long>(fs.arith);
-  }
 }
 
 // ---------------------------------------------------------------------------
@@ -1529,7 +1388,7 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
   cx.grid = gridDim.x;
   const int tid = threadIdx.x, warp = tid >> 5;
   const bool tc = (p.engine == MK_ENGINE_TCGEN05) && p.n_gemm > 0;   // tensor-core roles (TMEM, MMA issuer)
-  const bool ring = (tc || p.engine == ENGINE_FMA) && p.n_gemm > 0;  // weight producer
+  const bool ring = tc;  // weight producer
 
   if (tid == 0) {
     for (int s = 0; s < kChunkBars; ++s) {

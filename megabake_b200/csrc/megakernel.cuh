@@ -37,7 +37,6 @@ static_assert(kSmemBytes <= 200704, "dynamic shared memory exceeds the 196 KiB c
 
 enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU = 2, EPI_PARTIAL = 3 };
 enum { B_PLAIN = 0, B_NORM = 1, B_ATTN = 2 };
-enum { ENGINE_FMA = 3 };  // per-launch engine value next to MK_ENGINE_*: this launch consumes the ring with CUDA-core FMAs
 enum { MODE_DECODE = 0, MODE_PREFILL = 1, MODE_LINEAR = 2, MODE_KVATT = 3, MODE_ATT = 4 };
 enum { EV_PHASE_ENTER = 1, EV_B_STAGED = 2, EV_FIRST_ACC = 3, EV_PHASE_DONE = 4, EV_BARRIER_DONE = 5, EV_ATTENTION_DONE = 6 };
 enum {
@@ -64,7 +63,9 @@ struct GemmPhase {
   int nseg, nacc;
   int k, kc;                   // reduction length, in elements and in 64-element chunks
   int rows;                    // weight rows per tile
-  int gran;                    // ring granules one chunk occupies = ceil(rows * 128 / 1024)
+  int kb;                      // K chunks one weight copy brings (1: 64 x rows swizzled boxes for the tensor core;
+                               // > 1: unswizzled boxes of kb * 64 elements x rows for the small-launch kernel)
+  int gran;                    // ring granules one copy occupies = ceil(rows * kb * 128 / 1024)
   int ntiles;                  // row tiles
   int ksplit, kslice;          // K slices and chunks per slice (kc == ksplit * kslice)
   int nunits;                  // ntiles * ksplit

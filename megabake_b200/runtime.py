@@ -66,7 +66,7 @@ class DecoderKernel:
         max_tokens: int = 16,
         max_positions: int = 2048,
         device: str | torch.device = "cuda:0",
-        engine: str = "tcgen05",
+        engine: str = "auto",
         sm_limit: int = 0,
         tables: tuple[torch.Tensor, torch.Tensor] | None = None,
     ) -> None:
