@@ -498,7 +498,10 @@ int mk_decode(mk_handle h, const int64_t* ids, const int64_t* positions, int bat
   p.mode = MODE_DECODE; p.m = batch; p.batch = batch; p.seq = 1; p.capacity = capacity;
   p.split = (batch <= kSplitTokens && split_table_ok(h->cfg)) ? 1 : 0;
   p.phases = at<GemmPhase>(h, h->cv.phases) + (p.split ? 0 : phases_per_table(h->cfg));
-  const bool small = (h->cfg.engine == MK_ENGINE_FMA || h->cfg.engine == MK_ENGINE_AUTO) && p.split && h->fma_ok;
+  // The small-launch kernel keeps a 16 KB score buffer: at most 16 context chunks of 4096 / group keys.
+  const int small_keys = kMaxChunks * ((kAttScoreBytes / 4 / (h->cfg.q_heads / h->cfg.kv_heads)) & ~7);
+  const bool small = (h->cfg.engine == MK_ENGINE_FMA || h->cfg.engine == MK_ENGINE_AUTO) && p.split && h->fma_ok &&
+                     capacity <= small_keys;
   if (small) p.phases = at<GemmPhase>(h, h->cv.phases) + 2 * phases_per_table(h->cfg);
   p.n_gemm = 4 * L + 1;
   p.nbar = 5 * L;

@@ -66,11 +66,15 @@ __device__ __forceinline__ bool small_wait(const Ctx& cx, SmallState& st, int wt
   return *reinterpret_cast<volatile int*>(&cx.misc->wabort) == 0;
 }
 
-__device__ __forceinline__ void small_prefetch_phase(const Ctx& cx, int gp, int wtid) {
-  if (gp >= cx.p->n_gemm) return;
-  const uint32_t* src = reinterpret_cast<const uint32_t*>(cx.p->phases + gp);
-  uint32_t* dst = reinterpret_cast<uint32_t*>(&cx.misc->phase[gp & 1]);
-  if (wtid < static_cast<int>(sizeof(GemmPhase) / 4)) dst[wtid] = __ldg(src + wtid);
+// The next phase's descriptor: requested when a phase starts, put into shared memory when the
+// phase has finished (a warp stalls on the store until its load has returned).
+__device__ __forceinline__ uint32_t small_phase_word(const Ctx& cx, int gp, int wtid) {
+  if (gp >= cx.p->n_gemm || wtid >= static_cast<int>(sizeof(GemmPhase) / 4)) return 0u;
+  return __ldg(reinterpret_cast<const uint32_t*>(cx.p->phases + gp) + wtid);
+}
+__device__ __forceinline__ void small_phase_store(const Ctx& cx, int gp, int wtid, uint32_t word) {
+  if (gp >= cx.p->n_gemm || wtid >= static_cast<int>(sizeof(GemmPhase) / 4)) return;
+  reinterpret_cast<uint32_t*>(&cx.misc->phase[gp & 1])[wtid] = word;
 }
 static_assert(sizeof(GemmPhase) / 4 <= kSmallWorkers, "one word of the phase descriptor per consumer thread");
 
@@ -155,33 +159,53 @@ __device__ __noinline__ void small_stage_norm(const Ctx& cx, const GemmPhase* ph
   }
 }
 
-// Plain or attention-output operand: K chunks [k0, k0 + count) of every token.
+// Plain or attention-output operand: K chunks [k0, k0 + count) of every token.  One vector per
+// thread and trip (256 vectors cover a 2048-element slice of one token); kept small on purpose.
 __device__ __noinline__ void small_stage_cols(const Ctx& cx, const GemmPhase* ph, int k0, int count, int mt, int wtid,
                                               int nch) {
   const KParams& p = *cx.p;
   const int per_token = count * 8;
   const int items = per_token * mt;
-  for (int item0 = wtid; item0 < items; item0 += kSmallWorkers * 4) {
-    uint4 u[4];
+#pragma unroll 1
+  for (int item = wtid; item < items; item += kSmallWorkers) {
+    const int t = item / per_token, rem = item - t * per_token;
+    const int col = (k0 + (rem >> 3)) * kChunkK + (rem & 7) * 8;
+    const uint4 u = (ph->bmode == B_ATTN) ? attention_vec(p, t, col, nch)
+                                          : __ldcg(reinterpret_cast<const uint4*>(activation_row(p, ph, t) + col));
+    float f[8];
+    unpack8(u, f);
+    x_store(cx, t, rem >> 3, rem & 7, f);
+  }
+}
+
+// Finish the rows of one unit: the reduced sums wait in shared memory ([accumulator][row][token]),
+// written by the lane that also finishes the row, so this is one short loop instead of an
+// epilogue unrolled per pass.
+constexpr int kRowSumOffset = kSplitTokens * kXFloats * 4;  // behind the activation operand
+static_assert(kRowSumOffset + 2 * kTileRows * kSplitTokens * 4 <= kBBytes, "row sums do not fit");
+
+template <int T>
+__device__ __noinline__ void small_finish_rows(const Ctx& cx, const GemmPhase* ph, int seg, int slice, int row0, int rows,
+                                               int lane_row, int passes) {
+  const float* sums = reinterpret_cast<const float*>(cx.smem_b + kRowSumOffset);
+#pragma unroll 1
+  for (int ps = 0; ps < passes; ++ps) {
+    const int r = ps * 32 + lane_row;
+    const int n = row0 + r;
+    if (r >= rows || n >= ph->n[seg]) continue;
+    float v[2][T];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int item = item0 + i * kSmallWorkers;
-      if (item < items) {
-        const int t = item / per_token, rem = item - t * per_token;
-        const int col = (k0 + (rem >> 3)) * kChunkK + (rem & 7) * 8;
-        u[i] = (ph->bmode == B_ATTN) ? attention_vec(p, t, col, nch)
-                                     : __ldcg(reinterpret_cast<const uint4*>(activation_row(p, ph, t) + col));
-      }
+    for (int t = 0; t < T; ++t) {
+      v[0][t] = sums[r * kSplitTokens + t];
+      v[1][t] = sums[(kTileRows + r) * kSplitTokens + t];
     }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int item = item0 + i * kSmallWorkers;
-      if (item < items) {
-        const int t = item / per_token, rem = item - t * per_token;
-        float f[8];
-        unpack8(u[i], f);
-        x_store(cx, t, rem >> 3, rem & 7, f);
-      }
+    if (ph->epi == EPI_PARTIAL) {
+      store_partial<T>(cx, ph, slice, n, v[0], 0, T);
+    } else {
+      float pre[T];
+      pre[0] = (ph->epi == EPI_STORE && ph->bias[seg]) ? ldg_bf16(ph->bias[seg] + n) : 0.f;
+      if (ph->epi == EPI_RESIDUAL) epilogue_prefetch<T>(cx, ph, seg, n, 0, T, pre);
+      apply_epilogue<T>(cx, ph, seg, n, v, pre, 0, T);
     }
   }
 }
@@ -222,15 +246,6 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
       }
       int seg, row0;
       tile_origin(ph, tile, seg, row0);
-      // bias of this lane's rows, fetched before the K loop
-      float bias_v[4] = {0.f, 0.f, 0.f, 0.f};
-      if (ph->epi == EPI_STORE && ph->bias[seg] && c == 0) {
-#pragma unroll
-        for (int ps = 0; ps < 4; ++ps) {
-          const int r = ps * 32 + lane_row;
-          if (ps < passes && r < rows && row0 + r < ph->n[seg]) bias_v[ps] = ldg_bf16(ph->bias[seg] + row0 + r);
-        }
-      }
       float acc[NACC][4][T];
 #pragma unroll
       for (int a = 0; a < NACC; ++a)
@@ -252,6 +267,7 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
           const bool got = ok && wait_mbar(cx, smem_u32(&cx.misc->full[bar]), ((seq + a) / kChunkBars) & 1, SITE_MMA_FULL, gp);
           ok = __all_sync(0xffffffffu, got);
         }
+#pragma unroll 1
         for (int j = 0; j < kb; ++j) {
           float xf[T][8];
 #pragma unroll
@@ -287,10 +303,10 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
         slot = (slot + kb == kslice) ? 0 : slot + kb;
       }
       if (unit == cx.cta) trace_event(cx, wtid, EV_FIRST_ACC);
+      float* sums = reinterpret_cast<float*>(cx.smem_b + kRowSumOffset);
 #pragma unroll
       for (int ps = 0; ps < 4; ++ps) {
         if (ps < passes) {
-          float v[2][T];
 #pragma unroll
           for (int a = 0; a < NACC; ++a)
 #pragma unroll
@@ -299,22 +315,11 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
               x += __shfl_xor_sync(0xffffffffu, x, 1);
               x += __shfl_xor_sync(0xffffffffu, x, 2);
               x += __shfl_xor_sync(0xffffffffu, x, 4);
-              v[a][t] = x;
+              if (c == 0) sums[(a * kTileRows + ps * 32 + lane_row) * kSplitTokens + t] = x;
             }
-          const int r = ps * 32 + lane_row;
-          const int n = row0 + r;
-          if (c == 0 && r < rows && n < ph->n[seg]) {
-            if (ph->epi == EPI_PARTIAL) {
-              store_partial<T>(cx, ph, slice, n, v[0], 0, T);
-            } else {
-              float pre[T];
-              pre[0] = bias_v[ps];
-              if (ph->epi == EPI_RESIDUAL) epilogue_prefetch<T>(cx, ph, seg, n, 0, T, pre);
-              apply_epilogue<T>(cx, ph, seg, n, v, pre, 0, T);
-            }
-          }
         }
       }
+      if (c == 0) small_finish_rows<T>(cx, ph, seg, slice, row0, rows, lane_row, passes);
     }
     trace_event(cx, wtid, EV_PHASE_DONE);
   }
@@ -357,6 +362,34 @@ struct SmallAttn {
   float scale;
 };
 
+// Shared-memory plan of the attention phase inside the 64 KB activation region.
+constexpr int kAttScoreBytes = 16 * 1024;   // fp32 scores [group][chunk]
+constexpr int kAttTileBytes = 38 * 1024;    // one tile of cached K (then V) rows of the unit's head (304 keys of 64)
+constexpr int kAttScratchBytes = 10 * 1024; // q, cross-warp sums, new key/value, statistics
+static_assert(kAttScoreBytes + kAttTileBytes + kAttScratchBytes <= kBBytes, "attention scratch exceeds its region");
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// Code size matters here: every instruction of this function runs a handful of times per
+// layer, so it is written as short loops (an unrolled version measured 128 KB of code and spent
+// its time fetching instructions).  Rows of the cache go to shared memory with cp.async: no
+// registers are tied up, and any number of keys can be in flight.
+// Copy `count` rows of head_dim bf16 (row stride ld elements) into shared memory with cp.async,
+// except row `skip` (the position being appended: its row is not in the cache yet).
+__device__ __noinline__ void small_fetch_rows(uint32_t dst, const bf16* src, int ld, int count, int skip, int hd, int wtid) {
+  const int shift = (hd == 64) ? 3 : 4;  // 16-byte pieces per row: 8 or 16
+  const int total = count << shift;
+#pragma unroll 1
+  for (int it = wtid; it < total; it += kSmallWorkers) {
+    const int key = it >> shift, piece = it & ((1 << shift) - 1);
+    if (key != skip)
+      cp_async16(dst + key * hd * 2 + piece * 16, reinterpret_cast<const uint4*>(src + static_cast<long long>(key) * ld) + piece);
+  }
+}
+
 __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, int wtid, int nch) {
   const KParams& p = *cx.p;
   const int hd = p.head_dim, half = hd / 2;
@@ -369,16 +402,21 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
   const int sub = lane / lpk, dg = lane % lpk;
   const int chunk = (n_max + nch - 1) / nch;
   const int units = rows * nch;
-  constexpr int kU = 8;
   const int pass = kSmallWarps * kpw;
+  const int tile_keys = kAttTileBytes / (hd * 2);
+  const int row_bytes = hd * 2;
 
-  float* sc = reinterpret_cast<float*>(cx.smem_b);                // [gs][chunk]
-  float* qs = reinterpret_cast<float*>(cx.smem_b + kScoreBytes);  // [gs][hd]
-  float* red = qs + 8 * 128;                                      // [8][128]
-  bf16* kn = reinterpret_cast<bf16*>(red + kSmallWarps * 128);    // [hd]
-  bf16* vn = kn + 128;                                            // [hd]
-  float* stat = reinterpret_cast<float*>(vn + 128);               // [16]: max[8], sum[8]
+  float* sc = reinterpret_cast<float*>(cx.smem_b);                       // [gs][chunk]
+  uint8_t* tile = cx.smem_b + kAttScoreBytes;                             // [tile_keys][hd] bf16
+  float* qs = reinterpret_cast<float*>(tile + kAttTileBytes);             // [gs][hd]                4 KB
+  float* red = qs + 8 * 128;                                              // [8 warps][128] / [parts][gs*hd]  4 KB
+  bf16* kn = reinterpret_cast<bf16*>(red + kSmallWarps * 128);            // [hd]
+  bf16* vn = kn + 128;                                                    // [hd]
+  float* stat = reinterpret_cast<float*>(vn + 128);                       // [16]: max[8], sum[8]
+  float* all = stat + 16;                                                 // [kMaxChunks][16]
+  const uint32_t tile_addr = smem_u32(tile);
 
+#pragma unroll 1
   for (int u = cx.cta; u < units; u += cx.grid) {
     const int rowg = u / nch, ch = u - rowg * nch;
     const int b = rowg / p.kv_heads, kvh = rowg - b * p.kv_heads;
@@ -389,201 +427,212 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
     const bool owner = (A.len >= j0 && A.len < j1);
     const bf16* kbase = A.k + b * A.kv_bstride + kvh * hd;
     const bf16* vbase = A.v + b * A.kv_bstride + kvh * hd;
+    const int ntiles = (cl + tile_keys - 1) / tile_keys;
     if (u != cx.cta) small_sync();  // previous unit is done with the scratch
 
-    // --- first batch of cached K rows: in flight while q is rotated
-    uint4 ku[kU];
-#pragma unroll
-    for (int u8 = 0; u8 < kU; ++u8) {
-      const int j = j0 + warp * kpw + u8 * pass + sub;
-      ku[u8] = make_uint4(0, 0, 0, 0);
-      if (j < j1 && j != newpos) ku[u8] = __ldcg(reinterpret_cast<const uint4*>(kbase + static_cast<long long>(j) * A.kv_ld) + dg);
-    }
-    // --- q of every head of the group, the new key (both rotated) and the new value
-    const long long pos = cx.misc->pos_s[b];
-    for (int idx = wtid; idx < (gs + 1) * half; idx += kSmallWorkers) {
-      const int g = idx / half, i = idx - g * half;
-      const bf16* src = (g < gs) ? A.q + static_cast<long long>(b) * A.q_ld + (kvh * gs + g) * hd
-                                 : A.knew + static_cast<long long>(b) * A.new_ld + kvh * hd;
-      float first = ldcg_bf16(src + i);
-      float second = ldcg_bf16(src + i + half);
-      const float cs = ldg_bf16(p.cos_t + pos * hd + i);
-      const float sn = ldg_bf16(p.sin_t + pos * hd + i);
-      rope_pair(first, second, cs, sn, p.rope_style, first, second);
-      if (g < gs) {
-        qs[g * hd + i] = first;
-        qs[g * hd + i + half] = second;
-      } else {
-        kn[i] = __float2bfloat16_rn(first);
-        kn[i + half] = __float2bfloat16_rn(second);
+    // Copy keys [t0, t1) of `cache` (not the new position: its row is still in kn/vn) into the tile.
+    auto fetch_tile = [&](const bf16* cache, int t0, int t1) {
+      small_fetch_rows(tile_addr, cache + static_cast<long long>(t0) * A.kv_ld, A.kv_ld, t1 - t0, newpos - t0, hd, wtid);
+    };
+    fetch_tile(kbase, j0, min(j1, j0 + tile_keys));  // in flight while q is rotated
+
+    // --- q of every head of the group and the new key (both rotated), and the new value: one round trip
+    {
+      const long long pos = cx.misc->pos_s[b];
+      const int ropes = (gs + 1) * half;
+#pragma unroll 1
+      for (int idx = wtid; idx < ropes + hd; idx += kSmallWorkers) {
+        if (idx < ropes) {
+          const int g = idx / half, i = idx - g * half;
+          const bf16* src = (g < gs) ? A.q + static_cast<long long>(b) * A.q_ld + (kvh * gs + g) * hd
+                                     : A.knew + static_cast<long long>(b) * A.new_ld + kvh * hd;
+          float x1 = ldcg_bf16(src + i);
+          float x2 = ldcg_bf16(src + i + half);
+          const float cs = ldg_bf16(p.cos_t + pos * hd + i);
+          const float sn = ldg_bf16(p.sin_t + pos * hd + i);
+          rope_pair(x1, x2, cs, sn, p.rope_style, x1, x2);
+          if (g < gs) {
+            qs[g * hd + i] = x1;
+            qs[g * hd + i + half] = x2;
+          } else {
+            kn[i] = __float2bfloat16_rn(x1);
+            kn[i + half] = __float2bfloat16_rn(x2);
+          }
+        } else {
+          const int i = idx - ropes;
+          vn[i] = __float2bfloat16_rn(ldcg_bf16(A.vnew + static_cast<long long>(b) * A.new_ld + kvh * hd + i));
+        }
       }
     }
-    for (int i = wtid; i < hd; i += kSmallWorkers)
-      vn[i] = __float2bfloat16_rn(ldcg_bf16(A.vnew + static_cast<long long>(b) * A.new_ld + kvh * hd + i));
+    cp_async_wait_all();
     small_sync();
     if (owner) {  // in-kernel KV append
       bf16* kd = A.k + b * A.kv_bstride + static_cast<long long>(A.len) * A.kv_ld + kvh * hd;
       bf16* vd = A.v + b * A.kv_bstride + static_cast<long long>(A.len) * A.kv_ld + kvh * hd;
+#pragma unroll 1
       for (int i = wtid; i < hd; i += kSmallWorkers) {
         kd[i] = kn[i];
         vd[i] = vn[i];
       }
     }
 
-    // --- scores
-    for (int base = j0 + warp * kpw; base < j1; base += pass * kU) {
-      if (base != j0 + warp * kpw) {
-#pragma unroll
-        for (int u8 = 0; u8 < kU; ++u8) {
-          const int j = base + u8 * pass + sub;
-          ku[u8] = make_uint4(0, 0, 0, 0);
-          if (j < j1 && j != newpos) ku[u8] = __ldcg(reinterpret_cast<const uint4*>(kbase + static_cast<long long>(j) * A.kv_ld) + dg);
-        }
+    // --- scores, tile by tile (one tile unless the chunk is longer than tile_keys)
+#pragma unroll 1
+    for (int t = 0; t < ntiles; ++t) {
+      const int t0 = j0 + t * tile_keys, t1 = min(j1, t0 + tile_keys);
+      if (t > 0) {
+        small_sync();  // everyone is done with the previous tile
+        fetch_tile(kbase, t0, t1);
+        cp_async_wait_all();
+        small_sync();
       }
-#pragma unroll
-      for (int u8 = 0; u8 < kU; ++u8) {
-        if (base + u8 * pass >= j1) break;  // warp-uniform
-        const int j = base + u8 * pass + sub;
-        if (j == newpos) ku[u8] = *reinterpret_cast<const uint4*>(kn + dg * 8);
+#pragma unroll 2
+      for (int base = warp * kpw; base < t1 - t0; base += pass) {  // warp-uniform trip count (shuffles inside)
+        const int key = base + sub;
+        const int j = t0 + key;
+        const bool live = j < t1;  // lanes of one key agree; a warp may hold both live and dead keys
+        uint4 kr = make_uint4(0, 0, 0, 0);
+        if (live) kr = (j == newpos) ? *reinterpret_cast<const uint4*>(kn + dg * 8)
+                                     : *reinterpret_cast<const uint4*>(tile + key * row_bytes + dg * 16);
         float kf[8];
-        unpack8(ku[u8], kf);
+        unpack8(kr, kf);
+#pragma unroll 1
         for (int g = 0; g < gs; ++g) {
-          const float* qv = qs + g * hd + dg * 8;
+          const float4 qa = *reinterpret_cast<const float4*>(qs + g * hd + dg * 8);
+          const float4 qb = *reinterpret_cast<const float4*>(qs + g * hd + dg * 8 + 4);
           float dot = 0.f;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) dot = fmaf(qv[e], kf[e], dot);
-          for (int o = 1; o < lpk; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-          if (dg == 0 && j < j1) sc[g * chunk + (j - j0)] = bf16_round(dot) * A.scale;
+          dot = fmaf(qa.x, kf[0], dot); dot = fmaf(qa.y, kf[1], dot); dot = fmaf(qa.z, kf[2], dot); dot = fmaf(qa.w, kf[3], dot);
+          dot = fmaf(qb.x, kf[4], dot); dot = fmaf(qb.y, kf[5], dot); dot = fmaf(qb.z, kf[6], dot); dot = fmaf(qb.w, kf[7], dot);
+          dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+          dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+          dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+          if (lpk == 16) dot += __shfl_xor_sync(0xffffffffu, dot, 8);
+          if (dg == 0 && live) sc[g * chunk + (j - j0)] = bf16_round(dot) * A.scale;
         }
       }
-    }
-    // --- first batch of V rows: in flight while the statistics are built and exchanged
-    uint4 vu[kU];
-#pragma unroll
-    for (int u8 = 0; u8 < kU; ++u8) {
-      const int j = j0 + warp * kpw + u8 * pass + sub;
-      vu[u8] = make_uint4(0, 0, 0, 0);
-      if (j < j1 && j != newpos) vu[u8] = __ldcg(reinterpret_cast<const uint4*>(vbase + static_cast<long long>(j) * A.kv_ld) + dg);
     }
     small_sync();
+    // --- the first tile of V rows replaces K: in flight while the statistics are built and exchanged
+    fetch_tile(vbase, j0, min(j1, j0 + tile_keys));
 
     // --- chunk max, then chunk sum of exp(score - chunk max)
+#pragma unroll 1
     for (int g = 0; g < gs; ++g) {
       float m = -INFINITY;
+#pragma unroll 1
       for (int i = wtid; i < cl; i += kSmallWorkers) m = fmaxf(m, sc[g * chunk + i]);
       m = warp_max(m);
       if (lane == 0) red[warp * 8 + g] = m;
     }
     small_sync();
+#pragma unroll 1
     for (int g = 0; g < gs; ++g) {
       float m = red[g];
 #pragma unroll
       for (int w8 = 1; w8 < kSmallWarps; ++w8) m = fmaxf(m, red[w8 * 8 + g]);
-      float s = 0.f;
-      for (int i = wtid; i < cl; i += kSmallWorkers) s += expf(sc[g * chunk + i] - m);
-      s = warp_sum(s);
-      if (lane == 0) red[64 + warp * 8 + g] = s;
+      float sum = 0.f;
+#pragma unroll 1
+      for (int i = wtid; i < cl; i += kSmallWorkers) sum += expf(sc[g * chunk + i] - m);
+      sum = warp_sum(sum);
+      if (lane == 0) red[64 + warp * 8 + g] = sum;
       if (wtid == 0) stat[g] = m;
     }
     small_sync();
     if (wtid < gs) {
-      float s = 0.f;
+      float sum = 0.f;
 #pragma unroll
-      for (int w8 = 0; w8 < kSmallWarps; ++w8) s += red[64 + w8 * 8 + wtid];
-      stat[8 + wtid] = s;
+      for (int w8 = 0; w8 < kSmallWarps; ++w8) sum += red[64 + w8 * 8 + wtid];
+      stat[8 + wtid] = sum;
     }
     small_sync();
 
     if (nch > 1) {
-      // --- publish (max, sum) with this phase's stamp; wait for every chunk of the row group
-      float* mine = p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + ch) * kExchangeFloats;
-      if (wtid < 16) __stcg(mine + wtid, stat[wtid]);
-      __threadfence();
-      small_sync();
-      if (wtid == 0) st_relaxed_u32(reinterpret_cast<uint32_t*>(mine + 16), A.stamp);
+      // --- publish (max, sum): every value travels with this phase's stamp in one 64-bit word,
+      // so a reader that sees the stamp has the value (no fence, one round trip)
+      unsigned long long* xch = reinterpret_cast<unsigned long long*>(p.att_xch) +
+                                static_cast<size_t>(rowg) * kMaxChunks * (kExchangeFloats / 2);
+      if (wtid < 16)
+        st_relaxed_u64(xch + ch * (kExchangeFloats / 2) + wtid,
+                       (static_cast<unsigned long long>(A.stamp) << 32) | __float_as_uint(stat[wtid]));
       bool ok = true;
-      if (wtid < nch) {
-        const uint32_t* theirs = reinterpret_cast<const uint32_t*>(
-            p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + wtid) * kExchangeFloats + 16);
+      if (wtid < nch * 16) {
+        const unsigned long long* theirs = xch + (wtid >> 4) * (kExchangeFloats / 2) + (wtid & 15);
+        unsigned long long word = ld_relaxed_u64(theirs);
         uint32_t spins = 0;
-        while (ld_relaxed_u32(theirs) != A.stamp) {
+        while (static_cast<uint32_t>(word >> 32) != A.stamp) {
           if ((++spins & 255u) == 0 && give_up(cx, SITE_ATT_EXCHANGE, rowg)) {
             ok = false;
             break;
           }
+          word = ld_relaxed_u64(theirs);
         }
-        __threadfence();
+        all[wtid] = __uint_as_float(static_cast<uint32_t>(word));
       }
       if (!small_ok(cx, ok)) return false;
       if (wtid < gs) {
-        const float* all = p.att_xch + static_cast<size_t>(rowg) * kMaxChunks * kExchangeFloats;
         float m = -INFINITY;
-        for (int c = 0; c < nch; ++c) m = fmaxf(m, __ldcg(all + c * kExchangeFloats + wtid));
-        float s = 0.f;
-        for (int c = 0; c < nch; ++c)
-          s += __ldcg(all + c * kExchangeFloats + 8 + wtid) * expf(__ldcg(all + c * kExchangeFloats + wtid) - m);
+#pragma unroll 1
+        for (int c = 0; c < nch; ++c) m = fmaxf(m, all[c * 16 + wtid]);
+        float sum = 0.f;
+#pragma unroll 1
+        for (int c = 0; c < nch; ++c) sum += all[c * 16 + 8 + wtid] * expf(all[c * 16 + wtid] - m);
         stat[wtid] = m;
-        stat[8 + wtid] = s;
+        stat[8 + wtid] = sum;
       }
       small_sync();
     }
 
-    // --- probabilities (bf16, against the global max and sum) and value accumulation
+    // --- probabilities (bf16, against the global max and sum)
+#pragma unroll 1
     for (int g = 0; g < gs; ++g) {
       const float m = stat[g], denom = stat[8 + g];
+#pragma unroll 1
       for (int i = wtid; i < cl; i += kSmallWorkers) sc[g * chunk + i] = bf16_round(expf(sc[g * chunk + i] - m) / denom);
     }
+    // --- value accumulation: an item is (part of the keys, head of the group, output column); its
+    // fp32 sum over the tiles lives in `red` (items <= 1024)
+    const int cols = gs * hd;
+    const int parts = max(1, kSmallWorkers / cols);
+    const int items = cols * parts;
+#pragma unroll 1
+    for (int t = 0; t < ntiles; ++t) {
+      const int t0 = j0 + t * tile_keys, t1 = min(j1, t0 + tile_keys);
+      if (t > 0) {
+        small_sync();
+        fetch_tile(vbase, t0, t1);
+      }
+      cp_async_wait_all();
+      small_sync();  // the tile has landed, and (first tile) the probabilities are complete
+      const int tk = t1 - t0;
+      const int per_part = (tk + parts - 1) / parts;
+#pragma unroll 1
+      for (int item = wtid; item < items; item += kSmallWorkers) {
+        const int part = item / cols, col = item - part * cols;
+        const int g = col / hd, d = col - g * hd;
+        const int k0 = part * per_part, k1 = min(tk, k0 + per_part);
+        float acc = (t == 0) ? 0.f : red[item];
+        const float* pr = sc + g * chunk + (t0 - j0);
+#pragma unroll 2
+        for (int key = k0; key < k1; ++key) {
+          const bf16* vrow = (t0 + key == newpos) ? vn : reinterpret_cast<const bf16*>(tile + key * row_bytes);
+          acc = fmaf(pr[key], __bfloat162float(vrow[d]), acc);
+        }
+        red[item] = acc;
+      }
+    }
     small_sync();
-    for (int g = 0; g < gs; ++g) {
-      float acc[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-      for (int base = j0 + warp * kpw; base < j1; base += pass * kU) {
-        const bool first_batch = (base == j0 + warp * kpw);
-        uint4 vv[kU];
-#pragma unroll
-        for (int u8 = 0; u8 < kU; ++u8) {
-          const int j = base + u8 * pass + sub;
-          vv[u8] = vu[u8];
-          if (!first_batch) {
-            vv[u8] = make_uint4(0, 0, 0, 0);
-            if (j < j1 && j != newpos) vv[u8] = __ldcg(reinterpret_cast<const uint4*>(vbase + static_cast<long long>(j) * A.kv_ld) + dg);
-          }
-        }
-#pragma unroll
-        for (int u8 = 0; u8 < kU; ++u8) {
-          const int j = base + u8 * pass + sub;
-          if (j < j1) {
-            if (j == newpos) vv[u8] = *reinterpret_cast<const uint4*>(vn + dg * 8);
-            float vf[8];
-            unpack8(vv[u8], vf);
-            const float pr = sc[g * chunk + (j - j0)];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) acc[e] = fmaf(pr, vf[e], acc[e]);
-          }
-        }
-      }
-      for (int o = lpk; o < 32; o <<= 1) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], o);
-      }
-      if (g > 0) small_sync();  // red is free (previous head consumed)
-      if (sub == 0) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) red[warp * 128 + dg * 8 + e] = acc[e];
-      }
-      small_sync();
-      if (wtid < hd) {
-        float o = red[wtid];
-#pragma unroll
-        for (int w8 = 1; w8 < kSmallWarps; ++w8) o += red[w8 * 128 + wtid];
-        const int head = kvh * gs + g;
-        if (nch == 1) {
-          A.out[static_cast<long long>(b) * A.out_ld + head * hd + wtid] = __float2bfloat16_rn(o);
-        } else {
-          const size_t row = static_cast<size_t>(b) * p.q_heads + head;
-          __stcg(p.att_part + (row * kMaxChunks + ch) * hd + wtid, o);
-        }
+#pragma unroll 1
+    for (int col = wtid; col < cols; col += kSmallWorkers) {
+      float o = red[col];
+#pragma unroll 1
+      for (int part = 1; part < parts; ++part) o += red[part * cols + col];
+      const int g = col / hd, d = col - g * hd;
+      const int head = kvh * gs + g;
+      if (nch == 1) {
+        A.out[static_cast<long long>(b) * A.out_ld + head * hd + d] = __float2bfloat16_rn(o);
+      } else {
+        const size_t row = static_cast<size_t>(b) * p.q_heads + head;
+        __stcg(p.att_part + (row * kMaxChunks + ch) * hd + d, o);
       }
     }
   }
@@ -612,7 +661,7 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
   A.out = p.attn; A.out_ld = q_size;
   A.kv_bstride = static_cast<long long>(p.capacity) * kv_size; A.kv_ld = kv_size;
   A.scale = p.att_scale;
-  small_prefetch_phase(cx, 0, wtid);
+  small_phase_store(cx, 0, wtid, small_phase_word(cx, 0, wtid));
   small_sync();
   uint4 wu = small_norm_weight(cx, 0, wtid);
   int step = 0;
@@ -620,8 +669,9 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
   // One projection phase: the next descriptor is fetched while this phase runs.
   bool ok = true;  // per warp; made block-uniform by every close()
   auto project = [&](int gp, int nch) {
-    small_prefetch_phase(cx, gp + 1, wtid);
+    const uint32_t word = small_phase_word(cx, gp + 1, wtid);
     ok = small_gemm_any(cx, gp, st, wtid, wu, nch) && ok;
+    small_phase_store(cx, gp + 1, wtid, word);
   };
   // Close a phase: arrive, fetch what the next phase needs that no other CTA writes, wait.
   auto close = [&](int next_gp) -> bool {
@@ -632,6 +682,29 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
   };
   for (int layer = 0; layer < p.layers; ++layer) {
     const int gp = layer * 4;
+    {
+      // The cached K and V rows of this CTA's attention units do not depend on this step: ask L2
+      // for them now, while the q/k/v weights stream, so that the attention phase finds them there
+      // (a (sequence, head) slice of the cache is 128-byte pieces 4 KB apart, slow to fetch cold).
+      const int len = cx.misc->len_s[layer];
+      const int nch = decode_chunks(len + 1, p.batch * p.kv_heads, cx.grid, gs, kAttScoreBytes);
+      const int chunk = (len + 1 + nch - 1) / nch;
+      const int units = p.batch * p.kv_heads * nch;
+      const int lines = p.head_dim / 64;  // 128-byte lines per cached row of one head
+      for (int u = cx.cta; u < units; u += cx.grid) {
+        const int rowg = u / nch, ch = u - rowg * nch;
+        const int b = rowg / p.kv_heads, kvh = rowg - b * p.kv_heads;
+        const int j0 = ch * chunk, j1 = min(len, j0 + chunk);
+        const size_t head_off = static_cast<size_t>(b) * A.kv_bstride + static_cast<size_t>(kvh) * p.head_dim;
+        const bf16* kb = static_cast<const bf16*>(p.kc[layer]) + head_off;
+        const bf16* vb = static_cast<const bf16*>(p.vc[layer]) + head_off;
+        for (int item = wtid; item < (j1 - j0) * lines; item += kSmallWorkers) {
+          const size_t off = static_cast<size_t>(j0 + item / lines) * A.kv_ld + (item % lines) * 64;
+          prefetch_l2(kb + off);
+          prefetch_l2(vb + off);
+        }
+      }
+    }
     project(gp, 1);                          // [residual update, RMSNorm] q, k, v (+bias)
     MK_SMALL_STEP();
     if (!close(gp + 1)) return;
@@ -639,7 +712,7 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
     A.k = static_cast<bf16*>(p.kc[layer]); A.v = static_cast<bf16*>(p.vc[layer]);
     A.len = cx.misc->len_s[layer];
     A.stamp = p.att_epoch + static_cast<uint32_t>(layer) + 1u;
-    const int nch = decode_chunks(A.len + 1, p.batch * p.kv_heads, cx.grid, gs);
+    const int nch = decode_chunks(A.len + 1, p.batch * p.kv_heads, cx.grid, gs, kAttScoreBytes);
     if (!small_attention(cx, A, wtid, nch)) return;       // RoPE, KV append, split-context attention
     trace_event(cx, wtid, EV_ATTENTION_DONE);
     MK_SMALL_STEP();

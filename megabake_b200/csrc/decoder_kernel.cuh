@@ -93,7 +93,7 @@ __device__ __forceinline__ bool give_up(const Ctx& cx, int site, int detail) {
 
 // Optional per-CTA event trace (worker thread 0 only): what the reference's
 // MEGABAKE_PHASE_TIMER stamps give (src/megabake/runtime.py:27-46).
-__device__ __forceinline__ void trace_event(const Ctx& cx, int wtid, int code) {
+__device__ __noinline__ void trace_event(const Ctx& cx, int wtid, int code) {
   if (cx.p->trace_cap == 0 || wtid != 0) return;
   const int n = cx.misc->trace_n;
   if (n >= cx.p->trace_cap) return;
@@ -957,8 +957,8 @@ __device__ __forceinline__ void rope_pair(float x1, float x2, float c, float s, 
 }
 
 // How many chunks the context of a decode attention phase is cut into.
-__device__ __forceinline__ int decode_chunks(int keys, int rows, int grid, int gs) {
-  const int max_len = (kScoreBytes / 4 / gs) & ~7;
+__device__ __forceinline__ int decode_chunks(int keys, int rows, int grid, int gs, int score_bytes = kScoreBytes) {
+  const int max_len = (score_bytes / 4 / gs) & ~7;
   int nch = grid / rows;
   if (nch < 1) nch = 1;
   const int by_len = (keys + 63) / 64;

@@ -29,7 +29,8 @@ constexpr int kMiscBytes = 4096;
 constexpr int kSmemBytes = 1024 /*alignment slack*/ + kRingBytes + kBBytes + kMiscBytes;
 constexpr int kMaxChunks = 16;           // split-context chunks per (sequence, kv head)
 constexpr int kScoreBytes = 40960;       // fp32 scores of one attention unit (inside the B region)
-constexpr int kExchangeFloats = 20;      // per (row group, chunk): max[8], sum[8], stamp, pad
+constexpr int kExchangeFloats = 32;      // per (row group, chunk), 128 bytes: max[8], sum[8], stamps (mk::megakernel),
+                                         // or 16 values each paired with the stamp in one 64-bit word (small-launch kernel)
 constexpr int kMaxSplit = 4;             // K slices a projection may be cut into
 constexpr int kSplitTokens = 4;          // launches with at most this many tokens use the split-K table
 
