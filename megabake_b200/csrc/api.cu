@@ -236,11 +236,33 @@ void base_params(mk_handle h, KParams& p) {
   p.sin_t = static_cast<const bf16*>(h->weights.rope_sin);
 }
 
+// The small-launch kernel is instantiated per token count (1..kSplitTokens).
+const void* small_kernel(int tokens) {
+  switch (tokens) {
+    case 1: return reinterpret_cast<const void*>(&megakernel_small<1>);
+    case 2: return reinterpret_cast<const void*>(&megakernel_small<2>);
+    case 3: return reinterpret_cast<const void*>(&megakernel_small<3>);
+    default: return reinterpret_cast<const void*>(&megakernel_small<4>);
+  }
+}
+
+int prepare_small_kernels(int device) {
+  for (int t = 1; t <= kSplitTokens; ++t) {
+    const void* fn = small_kernel(t);
+    MK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    MK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, (kSmemBytes * 100 + 233471) / 233472));
+    int per_sm = 0;
+    MK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kSmallThreads, kSmemBytes));
+    if (per_sm < 1) return fail(MK_ERR_UNSUPPORTED, "the small-launch megakernel does not fit on an SM of device %d", device);
+  }
+  return MK_OK;
+}
+
 int launch(mk_handle h, KParams& p, void* stream, int attention_phases = 0, bool small = false) {
   void* args[] = {&p};
   if (small)
-    MK_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(&megakernel_small), dim3(h->grid),
-                                        dim3(kSmallThreads), args, kSmemBytes, static_cast<cudaStream_t>(stream)));
+    MK_CUDA(cudaLaunchCooperativeKernel(small_kernel(p.m), dim3(h->grid), dim3(kSmallThreads), args, kSmemBytes,
+                                        static_cast<cudaStream_t>(stream)));
   else
     MK_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(&megakernel), dim3(h->grid), dim3(kThreads), args,
                                         kSmemBytes, static_cast<cudaStream_t>(stream)));
@@ -293,13 +315,10 @@ int mk_create(const mk_config* config, void* workspace, size_t workspace_bytes, 
   if (!coop) return fail(MK_ERR_UNSUPPORTED, "device %d does not support cooperative launch", device);
   MK_CUDA(cudaFuncSetAttribute(megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
   MK_CUDA(cudaFuncSetAttribute(megakernel, cudaFuncAttributePreferredSharedMemoryCarveout, (kSmemBytes * 100 + 233471) / 233472));
-  MK_CUDA(cudaFuncSetAttribute(megakernel_small, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-  MK_CUDA(cudaFuncSetAttribute(megakernel_small, cudaFuncAttributePreferredSharedMemoryCarveout, (kSmemBytes * 100 + 233471) / 233472));
   int per_sm = 0;
   MK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, megakernel, kThreads, kSmemBytes));
   if (per_sm < 1) return fail(MK_ERR_UNSUPPORTED, "the megakernel does not fit on an SM of device %d", device);
-  MK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, megakernel_small, kSmallThreads, kSmemBytes));
-  if (per_sm < 1) return fail(MK_ERR_UNSUPPORTED, "the small-launch megakernel does not fit on an SM of device %d", device);
+  if (int e = prepare_small_kernels(device)) return e;
   mk_handle h = new (std::nothrow) mk_handle_s();
   if (!h) return fail(MK_ERR_INVALID, "out of host memory");
   h->cfg = *config;

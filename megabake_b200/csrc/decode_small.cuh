@@ -334,15 +334,6 @@ __device__ __forceinline__ bool small_gemm_t(const Ctx& cx, int gp, SmallState& 
                                           : small_gemm<T, 1>(cx, gp, st, wtid, wu, nch);
 }
 
-__device__ __forceinline__ bool small_gemm_any(const Ctx& cx, int gp, SmallState& st, int wtid, uint4 wu, int nch) {
-  switch (cx.p->m) {
-    case 1: return small_gemm_t<1>(cx, gp, st, wtid, wu, nch);
-    case 2: return small_gemm_t<2>(cx, gp, st, wtid, wu, nch);
-    case 3: return small_gemm_t<3>(cx, gp, st, wtid, wu, nch);
-    default: return small_gemm_t<4>(cx, gp, st, wtid, wu, nch);
-  }
-}
-
 // Decode attention with RoPE, in-kernel KV append and a context split across
 // CTAs; same arithmetic and rounding points as mk::attention_phase (scores
 // bf16(q.k) * scale, fp32 softmax against the global max and sum of the row
@@ -649,6 +640,9 @@ __device__ __forceinline__ uint4 small_norm_weight(const Ctx& cx, int gp, int wt
   return __ldg(reinterpret_cast<const uint4*>(ph->normw) + wtid);
 }
 
+// One kernel per token count: code that is compiled in but never runs still costs instruction-cache
+// reach (a build with all four token counts in one kernel measured 8 % slower at one token).
+template <int T>
 __device__ void small_worker_loop(const Ctx& cx, int wtid) {
   const KParams& p = *cx.p;
   SmallState st;
@@ -670,7 +664,7 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
   bool ok = true;  // per warp; made block-uniform by every close()
   auto project = [&](int gp, int nch) {
     const uint32_t word = small_phase_word(cx, gp + 1, wtid);
-    ok = small_gemm_any(cx, gp, st, wtid, wu, nch) && ok;
+    ok = small_gemm_t<T>(cx, gp, st, wtid, wu, nch) && ok;
     small_phase_store(cx, gp + 1, wtid, word);
   };
   // Close a phase: arrive, fetch what the next phase needs that no other CTA writes, wait.
@@ -736,6 +730,7 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
 // ---------------------------------------------------------------------------
 // the kernel
 
+template <int T>
 __global__ void __launch_bounds__(kSmallThreads, 1) megakernel_small(const __grid_constant__ KParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -796,7 +791,7 @@ __global__ void __launch_bounds__(kSmallThreads, 1) megakernel_small(const __gri
   } else if (warp == 0) {
     if (tid == 0) producer_loop(cx);
   } else {
-    small_worker_loop(cx, tid - 32);
+    small_worker_loop<T>(cx, tid - 32);
   }
 }
 
