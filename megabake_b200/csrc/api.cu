@@ -151,14 +151,14 @@ T* at(mk_handle h, size_t off) { return reinterpret_cast<T*>(h->ws + off); }
 
 // Rows per tile: the smallest height for which the phase's row tiles fit in the
 // fewest possible rounds over `slots` CTAs (each round gives every CTA one unit).
-int choose_rows(const GemmPhase& ph, int slots) {
+int choose_rows(const GemmPhase& ph, int slots, int max_rows = kTileRows) {
   const int nseg = ph.nacc == 2 ? 1 : ph.nseg;
   long long total = 0;
   for (int s = 0; s < nseg; ++s) total += ph.n[s];
   if (slots < 1) slots = 1;
-  for (long long rounds = (total + static_cast<long long>(kTileRows) * slots - 1) / (static_cast<long long>(kTileRows) * slots);;
+  for (long long rounds = (total + static_cast<long long>(max_rows) * slots - 1) / (static_cast<long long>(max_rows) * slots);;
        ++rounds) {
-    for (int rows = static_cast<int>((total + rounds * slots - 1) / (rounds * slots)); rows <= kTileRows; ++rows) {
+    for (int rows = static_cast<int>((total + rounds * slots - 1) / (rounds * slots)); rows <= max_rows; ++rows) {
       long long tiles = 0;
       for (int s = 0; s < nseg; ++s) tiles += (ph.n[s] + rows - 1) / rows;
       if (tiles <= rounds * slots) return rows;
@@ -172,14 +172,14 @@ int choose_rows(const GemmPhase& ph, int slots) {
 constexpr int kGoodBoxRows = 40;
 constexpr int kFatCopyBytes = 30 * 1024;  // largest weight copy of the small-launch table: four fit the ring
 
-void finish_phase(GemmPhase& ph, int grid, bool allow_split) {
+void finish_phase(GemmPhase& ph, int grid, bool allow_split, int max_rows = kTileRows) {
   ph.kc = ph.k / kChunkK;
-  int best_split = 1, best_rows = choose_rows(ph, grid);
+  int best_split = 1, best_rows = choose_rows(ph, grid, max_rows);
   if (allow_split && best_rows < kGoodBoxRows) {
     static const int candidates[] = {2, 3, 4};
     for (int split : candidates) {
       if (ph.kc % split || ph.kc / split < 2 || grid / split < 1) continue;
-      const int rows = choose_rows(ph, grid / split);
+      const int rows = choose_rows(ph, grid / split, max_rows);
       if (rows > best_rows) {
         best_rows = rows;
         best_split = split;
@@ -467,8 +467,12 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
     for (size_t i = 0; i < nphases; ++i) {
       GemmPhase& ph = phases[2 * nphases + i];
       ph = phases[i];
+      if (ph.rows > kSmallTileRows) {  // the CUDA-core consumer keeps 8 rows per warp: tiles of at most 64 rows
+        if (ph.ksplit != 1) return fail(MK_ERR_UNSUPPORTED, "small-launch table: a split phase with more than 64 rows");
+        finish_phase(ph, h->grid, false, kSmallTileRows);
+      }
       int kb = 1;
-      for (int cand = 2; cand <= 4; ++cand)
+      for (int cand = 2; cand <= 4; cand += 2)
         if (ph.kslice % cand == 0 && ph.rows * cand * 128 <= kFatCopyBytes) kb = cand;
       ph.kb = kb;
       ph.gran = (ph.rows * kb * 128 + kGranule - 1) / kGranule;

@@ -178,63 +178,63 @@ __device__ __noinline__ void small_stage_cols(const Ctx& cx, const GemmPhase* ph
   }
 }
 
-// Finish the rows of one unit: the reduced sums wait in shared memory ([accumulator][row][token]),
-// written by the lane that also finishes the row, so this is one short loop instead of an
-// epilogue unrolled per pass.
+// Row sums of one unit wait in shared memory ([accumulator][row][token]) between the K loop and
+// the epilogue, which thread r runs for row r.
 constexpr int kRowSumOffset = kSplitTokens * kXFloats * 4;  // behind the activation operand
-static_assert(kRowSumOffset + 2 * kTileRows * kSplitTokens * 4 <= kBBytes, "row sums do not fit");
+constexpr int kSmallTileRows = 64;                          // tile height of the small-launch table
+static_assert(kRowSumOffset + 2 * kSmallTileRows * kSplitTokens * 4 <= kBBytes, "row sums do not fit");
 
 template <int T>
-__device__ __noinline__ void small_finish_rows(const Ctx& cx, const GemmPhase* ph, int seg, int slice, int row0, int rows,
-                                               int lane_row, int passes) {
+__device__ __noinline__ void small_finish_row(const Ctx& cx, const GemmPhase* ph, int seg, int slice, int n, int r) {
   const float* sums = reinterpret_cast<const float*>(cx.smem_b + kRowSumOffset);
-#pragma unroll 1
-  for (int ps = 0; ps < passes; ++ps) {
-    const int r = ps * 32 + lane_row;
-    const int n = row0 + r;
-    if (r >= rows || n >= ph->n[seg]) continue;
-    float v[2][T];
+  float v[2][T];
 #pragma unroll
-    for (int t = 0; t < T; ++t) {
-      v[0][t] = sums[r * kSplitTokens + t];
-      v[1][t] = sums[(kTileRows + r) * kSplitTokens + t];
-    }
-    if (ph->epi == EPI_PARTIAL) {
-      store_partial<T>(cx, ph, slice, n, v[0], 0, T);
-    } else {
-      float pre[T];
-      pre[0] = (ph->epi == EPI_STORE && ph->bias[seg]) ? ldg_bf16(ph->bias[seg] + n) : 0.f;
-      if (ph->epi == EPI_RESIDUAL) epilogue_prefetch<T>(cx, ph, seg, n, 0, T, pre);
-      apply_epilogue<T>(cx, ph, seg, n, v, pre, 0, T);
-    }
+  for (int t = 0; t < T; ++t) {
+    v[0][t] = sums[r * kSplitTokens + t];
+    v[1][t] = sums[(kSmallTileRows + r) * kSplitTokens + t];
+  }
+  if (ph->epi == EPI_PARTIAL) {
+    store_partial<T>(cx, ph, slice, n, v[0], 0, T);
+  } else {
+    float pre[T];
+    pre[0] = (ph->epi == EPI_STORE && ph->bias[seg]) ? ldg_bf16(ph->bias[seg] + n) : 0.f;
+    if (ph->epi == EPI_RESIDUAL) epilogue_prefetch<T>(cx, ph, seg, n, 0, T, pre);
+    apply_epilogue<T>(cx, ph, seg, n, v, pre, 0, T);
   }
 }
 
-// Projection phase gp for this CTA's units.  The caller has made the phase
-// descriptor visible in cx.misc->phase[gp & 1]; `wu` is the norm-weight vector
-// for B_NORM phases.  Accumulation order per output: lane c of the row's eight
-// lanes sums elements [8c, 8c+8) of every K chunk in the CTA's rotated chunk
-// order, then a fixed shuffle tree adds the eight lanes: no dependence on timing.
+// Projection phase gp for this CTA's units.  The caller has made the phase descriptor visible in
+// cx.misc->phase[gp & 1]; `wu` is the norm-weight vector for B_NORM phases.
+//
+// A weight copy holds [rows][kb * 64] bf16, plain rows.  The lanes of a warp split the K range of
+// the copy: lane l keeps its eight activation values (per token) in registers for the whole copy
+// and reads its 16 bytes of one row with one shared load; the warp walks the rows w, w + 8, ...
+// (two or four rows at once when a row segment is shorter than 512 bytes).  Every (row, lane)
+// keeps one fp32 chain over the K loop; at the end a fixed shuffle tree adds the lanes of a row.
+// Accumulation order depends only on the CTA's rotated chunk order: no dependence on timing.
 template <int T, int NACC>
 __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, int wtid, uint4 wu, int nch) {
   const GemmPhase* ph = &cx.misc->phase[gp & 1];
   const int nunits = ph->nunits, rows = ph->rows, ksplit = ph->ksplit, kslice = ph->kslice, gran = ph->gran;
   const bool per_unit = ksplit > 1;
   const int warp = wtid >> 5, lane = wtid & 31;
-  const int c = lane & 7, rsub = lane >> 3;
-  const int kb = ph->kb;                 // K chunks per weight copy; a slot holds [rows][kb * 64] bf16, unswizzled
-  const int lane_row = warp * 4 + rsub;  // row inside a 32-row pass
+  const int kb = ph->kb;                          // 1, 2 or 4 K chunks per copy
+  const int lpr = kb * 8;                         // lanes per row
+  const int rset = 32 / lpr;                      // rows a warp reads at once
+  const int sel = lane / lpr, cl = lane - sel * lpr;
+  const int row_first = warp * rset + sel;        // this lane's rows: row_first + i * 8 * rset
+  const int iters = (rows + 8 * rset - 1) / (8 * rset);  // <= 8
   const uint32_t row_bytes = static_cast<uint32_t>(kb) * 128u;
-  const uint32_t lane_off = lane_row * row_bytes + (c << 4);
-  const uint32_t pass_bytes = 32u * row_bytes;
-  const int passes = (rows + 31) >> 5;
+  const uint32_t lane_off = row_first * row_bytes + (cl << 4);
   const int rot = k_rotation(cx.cta, cx.grid, kslice / kb) * kb;
   const uint32_t ring_base = smem_u32(cx.smem_a);
-  const uint32_t x_base = smem_u32(cx.smem_b) + c * 16;
+  const uint32_t x_base = smem_u32(cx.smem_b) + ((cl >> 3) * kChunkK + (cl & 7) * 4) * 4;
+  float* sums = reinterpret_cast<float*>(cx.smem_b + kRowSumOffset);
   int head = st.head, seq = st.seq;
   bool ok = true;
   if (cx.cta < nunits) {
     trace_event(cx, wtid, EV_PHASE_ENTER);
+#pragma unroll 1
     for (int unit = cx.cta; unit < nunits; unit += cx.grid) {
       const int tile = unit / ksplit, slice = unit - tile * ksplit;
       if (per_unit || unit == cx.cta) {
@@ -246,80 +246,76 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
       }
       int seg, row0;
       tile_origin(ph, tile, seg, row0);
-      float acc[NACC][4][T];
+      float acc[NACC][8][T];
 #pragma unroll
       for (int a = 0; a < NACC; ++a)
 #pragma unroll
-        for (int ps = 0; ps < 4; ++ps)
+        for (int i = 0; i < 8; ++i)
 #pragma unroll
-          for (int t = 0; t < T; ++t) acc[a][ps][t] = 0.f;
+          for (int t = 0; t < T; ++t) acc[a][i][t] = 0.f;
       int slot = rot;
-      for (int i = 0; i < kslice; i += kb) {
-        uint32_t base[NACC];
+#pragma unroll 1
+      for (int k0 = 0; k0 < kslice; k0 += kb) {
+        // this lane's activation values for the K range of the copy
+        float xf[T][8];
+#pragma unroll
+        for (int t = 0; t < T; ++t) {
+          const uint4 lo = lds_v4(x_base + (t * kXFloats + slot * kChunkK) * 4);
+          const uint4 hi = lds_v4(x_base + (t * kXFloats + slot * kChunkK + 32) * 4);
+          xf[t][0] = __uint_as_float(lo.x); xf[t][1] = __uint_as_float(lo.y);
+          xf[t][2] = __uint_as_float(lo.z); xf[t][3] = __uint_as_float(lo.w);
+          xf[t][4] = __uint_as_float(hi.x); xf[t][5] = __uint_as_float(hi.y);
+          xf[t][6] = __uint_as_float(hi.z); xf[t][7] = __uint_as_float(hi.w);
+        }
 #pragma unroll
         for (int a = 0; a < NACC; ++a) {
           if (head + gran > kRingGranules) head = 0;
-          base[a] = ring_base + head * kGranule + lane_off;
+          const uint32_t base = ring_base + head * kGranule + lane_off;
           head += gran;
-          const uint32_t bar = (seq + a) % kChunkBars;
+          const uint32_t bar = seq % kChunkBars;
           // After a failed wait the warp keeps walking the schedule without waiting, so that
           // every consumer still reaches the same block-wide barriers and leaves together.
-          const bool got = ok && wait_mbar(cx, smem_u32(&cx.misc->full[bar]), ((seq + a) / kChunkBars) & 1, SITE_MMA_FULL, gp);
+          const bool got = ok && wait_mbar(cx, smem_u32(&cx.misc->full[bar]), (seq / kChunkBars) & 1, SITE_MMA_FULL, gp);
           ok = __all_sync(0xffffffffu, got);
-        }
-#pragma unroll 1
-        for (int j = 0; j < kb; ++j) {
-          float xf[T][8];
 #pragma unroll
-          for (int t = 0; t < T; ++t) {
-            const uint4 lo = lds_v4(x_base + (t * kXFloats + (slot + j) * kChunkK) * 4);
-            const uint4 hi = lds_v4(x_base + (t * kXFloats + (slot + j) * kChunkK + 32) * 4);
-            xf[t][0] = __uint_as_float(lo.x); xf[t][1] = __uint_as_float(lo.y);
-            xf[t][2] = __uint_as_float(lo.z); xf[t][3] = __uint_as_float(lo.w);
-            xf[t][4] = __uint_as_float(hi.x); xf[t][5] = __uint_as_float(hi.y);
-            xf[t][6] = __uint_as_float(hi.z); xf[t][7] = __uint_as_float(hi.w);
-          }
+          for (int i = 0; i < 8; ++i) {
+            if (i < iters && row_first + i * 8 * rset < rows) {
+              float wf[8];
+              unpack8(lds_v4(base + i * 4096), wf);  // 8 * rset rows of row_bytes = 4096 bytes further on
 #pragma unroll
-          for (int a = 0; a < NACC; ++a) {
+              for (int t = 0; t < T; ++t)
 #pragma unroll
-            for (int ps = 0; ps < 4; ++ps) {
-              if (ps < passes) {
-                float wf[8];
-                unpack8(lds_v4(base[a] + ps * pass_bytes + j * 128), wf);
-#pragma unroll
-                for (int t = 0; t < T; ++t)
-#pragma unroll
-                  for (int e = 0; e < 8; ++e) acc[a][ps][t] = fmaf(wf[e], xf[t][e], acc[a][ps][t]);
-              }
+                for (int e = 0; e < 8; ++e) acc[a][i][t] = fmaf(wf[e], xf[t][e], acc[a][i][t]);
             }
           }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&cx.misc->empty[bar]));
+          seq += 1;
         }
-        __syncwarp();
-        if (lane == 0) {
-#pragma unroll
-          for (int a = 0; a < NACC; ++a) mbar_arrive(smem_u32(&cx.misc->empty[(seq + a) % kChunkBars]));
-        }
-        seq += NACC;
         slot = (slot + kb == kslice) ? 0 : slot + kb;
       }
       if (unit == cx.cta) trace_event(cx, wtid, EV_FIRST_ACC);
-      float* sums = reinterpret_cast<float*>(cx.smem_b + kRowSumOffset);
+      if (unit != cx.cta) small_sync();  // the previous unit's rows have been finished: `sums` is free
 #pragma unroll
-      for (int ps = 0; ps < 4; ++ps) {
-        if (ps < passes) {
+      for (int i = 0; i < 8; ++i) {
+        if (i < iters) {
 #pragma unroll
           for (int a = 0; a < NACC; ++a)
 #pragma unroll
             for (int t = 0; t < T; ++t) {
-              float x = acc[a][ps][t];
+              float x = acc[a][i][t];
               x += __shfl_xor_sync(0xffffffffu, x, 1);
               x += __shfl_xor_sync(0xffffffffu, x, 2);
               x += __shfl_xor_sync(0xffffffffu, x, 4);
-              if (c == 0) sums[(a * kTileRows + ps * 32 + lane_row) * kSplitTokens + t] = x;
+              if (lpr > 8) x += __shfl_xor_sync(0xffffffffu, x, 8);
+              if (lpr > 16) x += __shfl_xor_sync(0xffffffffu, x, 16);
+              const int r = row_first + i * 8 * rset;
+              if (cl == 0 && r < rows) sums[(a * kSmallTileRows + r) * kSplitTokens + t] = x;
             }
         }
       }
-      if (c == 0) small_finish_rows<T>(cx, ph, seg, slice, row0, rows, lane_row, passes);
+      small_sync();
+      if (wtid < rows && row0 + wtid < ph->n[seg]) small_finish_row<T>(cx, ph, seg, slice, row0 + wtid, wtid);
     }
     trace_event(cx, wtid, EV_PHASE_DONE);
   }
@@ -631,13 +627,107 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
 }
 
 // ---------------------------------------------------------------------------
+// warp 0: weight producer of the small-launch kernel.  Same ring discipline as mk::producer_loop
+// (FIFO reclaim of 1 KB granules, one full/empty barrier pair per copy in flight) without the
+// streamed-operand and multi-token-tile cases, which this kernel never meets.
+__device__ __noinline__ void small_producer(const Ctx& cx) {
+  const KParams& p = *cx.p;
+  const uint64_t policy = l2_policy_evict_first();
+  SmemMisc* misc = cx.misc;
+  int head = 0, seq = 0, oldest = 0;
+  bool ok = true;
+#pragma unroll 1
+  for (int gp = 0; gp < p.n_gemm && ok; ++gp) {
+    const GemmPhase* ph = p.phases + gp;
+    const int nacc = ph->nacc, gran = ph->gran, nunits = ph->nunits, ksplit = ph->ksplit, kslice = ph->kslice, kb = ph->kb;
+    const uint32_t bytes = static_cast<uint32_t>(ph->rows) * 128u * static_cast<uint32_t>(kb);
+    const int rot = k_rotation(cx.cta, cx.grid, kslice / kb) * kb;
+#pragma unroll 1
+    for (int unit = cx.cta; unit < nunits && ok; unit += cx.grid) {
+      const int tile = unit / ksplit, slice = unit - tile * ksplit;
+      int seg, row0;
+      tile_origin(ph, tile, seg, row0);
+      const int kbase = slice * kslice;
+      int k = rot;
+#pragma unroll 1
+      for (int i = 0; i < kslice * nacc && ok; i += kb) {
+        const int a = (nacc == 2) ? ((i / kb) & 1) : 0;  // gate and up copies alternate
+        const CUtensorMap* map = ph->tmap[nacc == 2 ? a : seg];
+        // Copies are consumed in issue order, so ring space is reclaimed by retiring the oldest copy in
+        // flight until [lo, hi) is free; a copy never wraps, so the skipped tail is freed first.
+        int lo = head, hi = head + gran;
+        if (hi > kRingGranules) hi = kRingGranules;  // first the tail fragment, then (second trip) the slot at 0
+#pragma unroll 1
+        for (int trip = 0; trip < 2 && ok; ++trip) {
+#pragma unroll 1
+          while (oldest < seq) {
+            const int os = misc->qstart[oldest % kChunkBars], oe = os + misc->qgran[oldest % kChunkBars];
+            const bool overlaps = os < hi && lo < oe;
+            if (!overlaps && seq - oldest < kChunkBars) break;
+            if (!wait_mbar(cx, smem_u32(&misc->empty[oldest % kChunkBars]), (oldest / kChunkBars) & 1, SITE_PRODUCER_EMPTY, gp)) {
+              ok = false;
+              break;
+            }
+            ++oldest;
+          }
+          if (head + gran <= kRingGranules) break;  // no wrap: one trip
+          head = 0;
+          lo = 0;
+          hi = gran;
+        }
+        if (!ok) break;
+        const int start = head;
+        head += gran;
+        misc->qstart[seq % kChunkBars] = static_cast<uint8_t>(start);
+        misc->qgran[seq % kChunkBars] = static_cast<uint8_t>(gran);
+        const uint32_t full = smem_u32(&misc->full[seq % kChunkBars]);
+        mbar_expect_tx(full, bytes);
+        tma_load_2d(smem_u32(cx.smem_a + start * kGranule), map, (kbase + k) * kChunkK, row0, full, policy);
+        ++seq;
+        if (nacc == 1 || a == 1) {
+          k += kb;
+          if (k == kslice) k = 0;
+        }
+      }
+    }
+  }
+  if (!ok) {  // leaving early: every copy already issued must land before the CTA exits
+    for (int i = max(0, seq - kChunkBars); i < seq; ++i) {
+      const uint32_t bar = smem_u32(&misc->full[i % kChunkBars]);
+      for (uint32_t spins = 0; spins < (1u << 22); ++spins) {
+        if (mbar_try_wait(bar, (i / kChunkBars) & 1)) break;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // consumers: whole-launch schedule (decode with the split-K phase table)
+
 
 __device__ __forceinline__ uint4 small_norm_weight(const Ctx& cx, int gp, int wtid) {
   if (gp >= cx.p->n_gemm) return make_uint4(0, 0, 0, 0);
   const GemmPhase* ph = &cx.misc->phase[gp & 1];
   if (ph->bmode != B_NORM || wtid >= ph->k / 8) return make_uint4(0, 0, 0, 0);
   return __ldg(reinterpret_cast<const uint4*>(ph->normw) + wtid);
+}
+
+// One projection phase; the next phase's descriptor is requested first and stored last.
+template <int T>
+__device__ __forceinline__ bool small_project(const Ctx& cx, SmallState& st, int gp, int nch, uint4 wu, int wtid) {
+  const uint32_t word = small_phase_word(cx, gp + 1, wtid);
+  const bool ok = small_gemm_t<T>(cx, gp, st, wtid, wu, nch);
+  small_phase_store(cx, gp + 1, wtid, word);
+  return ok;
+}
+
+// Close a phase: arrive at the grid barrier, fetch what the next phase needs that no other CTA
+// writes (its norm weight), wait.  `ok` is per warp on entry; the result is block-uniform.
+__device__ __forceinline__ bool small_close(const Ctx& cx, SmallState& st, int next_gp, uint4& wu, bool ok, int wtid) {
+  if (!ok) cx.misc->wabort = 1;
+  small_arrive(cx, st, wtid);   // its bar.sync also publishes the prefetched descriptor to every consumer
+  wu = small_norm_weight(cx, next_gp, wtid);
+  return small_wait(cx, st, wtid);
 }
 
 // One kernel per token count: code that is compiled in but never runs still costs instruction-cache
@@ -662,18 +752,8 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
 #define MK_SMALL_STEP() do { if (p.debug_stop && ++step >= p.debug_stop) return; } while (0)
   // One projection phase: the next descriptor is fetched while this phase runs.
   bool ok = true;  // per warp; made block-uniform by every close()
-  auto project = [&](int gp, int nch) {
-    const uint32_t word = small_phase_word(cx, gp + 1, wtid);
-    ok = small_gemm_t<T>(cx, gp, st, wtid, wu, nch) && ok;
-    small_phase_store(cx, gp + 1, wtid, word);
-  };
-  // Close a phase: arrive, fetch what the next phase needs that no other CTA writes, wait.
-  auto close = [&](int next_gp) -> bool {
-    if (!ok) cx.misc->wabort = 1;
-    small_arrive(cx, st, wtid);   // its bar.sync also publishes the prefetched descriptor to every consumer
-    wu = small_norm_weight(cx, next_gp, wtid);
-    return small_wait(cx, st, wtid);
-  };
+  auto project = [&](int gp, int nch) { ok = small_project<T>(cx, st, gp, nch, wu, wtid) && ok; };
+  auto close = [&](int next_gp) -> bool { return small_close(cx, st, next_gp, wu, ok, wtid); };
   for (int layer = 0; layer < p.layers; ++layer) {
     const int gp = layer * 4;
     {
@@ -789,7 +869,7 @@ __global__ void __launch_bounds__(kSmallThreads, 1) megakernel_small(const __gri
       if (p.nbar > 0) atomicAdd(&cx.ctrl->barrier, static_cast<uint32_t>(p.nbar));  // keep the monotonic counter consistent
     }
   } else if (warp == 0) {
-    if (tid == 0) producer_loop(cx);
+    if (tid == 0) small_producer(cx);
   } else {
     small_worker_loop<T>(cx, tid - 32);
   }

@@ -51,7 +51,18 @@ struct SmemMisc {
   uint8_t qstart[kChunkBars];  // producer: first ring granule of each chunk in flight (by sequence % kChunkBars)
   uint8_t qgran[kChunkBars];   // producer: granules of that chunk
   GemmPhase phase[2];  // worker-side copies of the current / next projection phase
+#ifdef MK_STAMPS
+  int stamp_base;
+  long long stamps[96];
+#endif
 };
+#ifdef MK_STAMPS
+#define MK_STAMP(cx, wtid, id) do { if ((wtid) == 0) { long long t_; asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_) :: "memory"); (cx).misc->stamps[(cx).misc->stamp_base + (id)] = t_; } } while (0)
+#define MK_STAMP_BASE(cx, wtid, base) do { if ((wtid) == 0) (cx).misc->stamp_base = (base); } while (0)
+#else
+#define MK_STAMP(cx, wtid, id) do { } while (0)
+#define MK_STAMP_BASE(cx, wtid, base) do { } while (0)
+#endif
 static_assert(sizeof(SmemMisc) <= kMiscBytes, "misc shared block too large");
 static_assert(kRingGranules < 256, "ring positions are kept in bytes");
 
@@ -93,8 +104,7 @@ __device__ __forceinline__ bool give_up(const Ctx& cx, int site, int detail) {
 
 // Optional per-CTA event trace (worker thread 0 only): what the reference's
 // MEGABAKE_PHASE_TIMER stamps give (src/megabake/runtime.py:27-46).
-__device__ __noinline__ void trace_event(const Ctx& cx, int wtid, int code) {
-  if (cx.p->trace_cap == 0 || wtid != 0) return;
+__device__ __noinline__ void trace_event_record(const Ctx& cx, int code) {
   const int n = cx.misc->trace_n;
   if (n >= cx.p->trace_cap) return;
   unsigned long long t;
@@ -102,6 +112,10 @@ __device__ __noinline__ void trace_event(const Ctx& cx, int wtid, int code) {
   cx.p->trace[static_cast<size_t>(cx.cta) * cx.p->trace_cap + n] =
       (static_cast<unsigned long long>(code) << 56) | (t & 0x00FFFFFFFFFFFFFFull);
   cx.misc->trace_n = n + 1;
+}
+// The test is inline, the recording out of line: with tracing off an event costs a compare.
+__device__ __forceinline__ void trace_event(const Ctx& cx, int wtid, int code) {
+  if (cx.p->trace_cap != 0 && wtid == 0) trace_event_record(cx, code);
 }
 
 __device__ __forceinline__ bool wait_mbar(const Ctx& cx, uint32_t bar, uint32_t parity, int site, int detail) {

@@ -25,7 +25,11 @@ constexpr int kBHalf = kBSlots / 2;
 constexpr int kBSlotBytes = kTok * 128;  // 2 KiB
 constexpr int kBBytes = kBSlots * kBSlotBytes;
 constexpr int kTmemCols = 64;            // 2 buffers x 2 accumulators x 16 columns
+#ifdef MK_STAMPS
+constexpr int kMiscBytes = 5120;
+#else
 constexpr int kMiscBytes = 4096;
+#endif
 constexpr int kSmemBytes = 1024 /*alignment slack*/ + kRingBytes + kBBytes + kMiscBytes;
 constexpr int kMaxChunks = 16;           // split-context chunks per (sequence, kv head)
 constexpr int kScoreBytes = 40960;       // fp32 scores of one attention unit (inside the B region)
