@@ -249,10 +249,10 @@ const void* small_kernel(int tokens) {
 int prepare_small_kernels(int device) {
   for (int t = 1; t <= kSplitTokens; ++t) {
     const void* fn = small_kernel(t);
-    MK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-    MK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, (kSmemBytes * 100 + 233471) / 233472));
+    MK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmallSmemBytes));
+    MK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, (kSmallSmemBytes * 100 + 233471) / 233472));
     int per_sm = 0;
-    MK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kSmallThreads, kSmemBytes));
+    MK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kSmallThreads, kSmallSmemBytes));
     if (per_sm < 1) return fail(MK_ERR_UNSUPPORTED, "the small-launch megakernel does not fit on an SM of device %d", device);
   }
   return MK_OK;
@@ -261,7 +261,7 @@ int prepare_small_kernels(int device) {
 int launch(mk_handle h, KParams& p, void* stream, int attention_phases = 0, bool small = false) {
   void* args[] = {&p};
   if (small)
-    MK_CUDA(cudaLaunchCooperativeKernel(small_kernel(p.m), dim3(h->grid), dim3(kSmallThreads), args, kSmemBytes,
+    MK_CUDA(cudaLaunchCooperativeKernel(small_kernel(p.m), dim3(h->grid), dim3(kSmallThreads), args, kSmallSmemBytes,
                                         static_cast<cudaStream_t>(stream)));
   else
     MK_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(&megakernel), dim3(h->grid), dim3(kThreads), args,
