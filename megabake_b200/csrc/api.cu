@@ -107,18 +107,19 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 }
 
 // bf16 [rows, k] row-major -> boxes of box_rows rows x 64 columns, 128-byte swizzle.
-int encode_weight_map(CUtensorMap* out, const void* base, int rows, int k, int box_rows, int box_chunks = 1) {
+int encode_weight_map(CUtensorMap* out, const void* base, int rows, int k, int box_rows, int box_chunks = 1,
+                      bool swizzle = true) {
   if (reinterpret_cast<uintptr_t>(base) % 16) return fail(MK_ERR_ALIGNMENT, "weight base %p is not 16-byte aligned", base);
   auto fn = encode_fn();
   if (!fn) return fail(MK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
-  // box_chunks == 1: the tensor core's operand layout (64 elements = 128 bytes per row, 128-byte swizzle).
-  // box_chunks > 1: plain rows of box_chunks * 128 bytes for the CUDA-core consumer (no swizzle, up to 256 elements).
+  // swizzle: the tensor core's operand layout (64 elements = 128 bytes per row, 128-byte swizzle).
+  // !swizzle: plain rows of box_chunks * 128 bytes for the CUDA-core consumer (up to 256 elements).
   const cuuint32_t box[2] = {static_cast<cuuint32_t>(kChunkK * box_chunks), static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t elem[2] = {1, 1};
   const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, box_chunks == 1 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(MK_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (rows %d, k %d)", (int)r, rows, k);
   return MK_OK;
@@ -480,7 +481,7 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
       for (int sg = 0; sg < nseg; ++sg) {
         const size_t index = static_cast<size_t>(ph.tmap[sg] - dmaps);  // same matrix, same slot in the third set
         ph.tmap[sg] = dmaps + 2 * nmaps + index;
-        if (int e = encode_weight_map(&maps[2 * nmaps + index], ph.w[sg], ph.n[sg], ph.k, ph.rows, kb)) return e;
+        if (int e = encode_weight_map(&maps[2 * nmaps + index], ph.w[sg], ph.n[sg], ph.k, ph.rows, kb, false)) return e;
       }
     }
   }
