@@ -300,19 +300,54 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
       }
       if (unit == cx.cta) trace_event(cx, wtid, EV_FIRST_ACC);
       if (unit != cx.cta) small_sync();  // the previous unit's rows have been finished: `sums` is free
+      if (lpr == 32) {
+        // A row spans the warp: halve the rows a lane carries at each exchange (16, 8, 4), then add
+        // the last four lanes; 9 shuffles for eight rows instead of 40.  Lane l with (l & 3) == 0
+        // ends with row index i = bits 4, 3, 2 of l.
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        if (i < iters) {
+        for (int a = 0; a < NACC; ++a)
+#pragma unroll
+          for (int t = 0; t < T; ++t) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = acc[a][i][t];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const bool up = lane & 16;
+              const float send = up ? v[i] : v[i + 4], keep = up ? v[i + 4] : v[i];
+              v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              const bool up = lane & 8;
+              const float send = up ? v[i] : v[i + 2], keep = up ? v[i + 2] : v[i];
+              v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+            }
+            {
+              const bool up = lane & 4;
+              const float send = up ? v[0] : v[1], keep = up ? v[1] : v[0];
+              v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+            }
+            v[0] += __shfl_xor_sync(0xffffffffu, v[0], 2);
+            v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1);
+            const int i = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+            const int r = warp + i * 8;
+            if ((lane & 3) == 0 && r < rows) sums[(a * kSmallTileRows + r) * kSplitTokens + t] = v[0];
+          }
+      } else {
+#pragma unroll 1
+        for (int i = 0; i < iters; ++i) {
 #pragma unroll
           for (int a = 0; a < NACC; ++a)
 #pragma unroll
             for (int t = 0; t < T; ++t) {
-              float x = acc[a][i][t];
+              float x = 0.f;
+#pragma unroll
+              for (int i2 = 0; i2 < 8; ++i2) x = (i2 == i) ? acc[a][i2][t] : x;
               x += __shfl_xor_sync(0xffffffffu, x, 1);
               x += __shfl_xor_sync(0xffffffffu, x, 2);
               x += __shfl_xor_sync(0xffffffffu, x, 4);
               if (lpr > 8) x += __shfl_xor_sync(0xffffffffu, x, 8);
-              if (lpr > 16) x += __shfl_xor_sync(0xffffffffu, x, 16);
               const int r = row_first + i * 8 * rset;
               if (cl == 0 && r < rows) sums[(a * kSmallTileRows + r) * kSplitTokens + t] = x;
             }
@@ -376,8 +411,9 @@ __device__ __noinline__ void small_fetch_rows(uint32_t dst, const bf16* src, int
 #pragma unroll 1
   for (int it = wtid; it < total; it += kSmallWorkers) {
     const int key = it >> shift, piece = it & ((1 << shift) - 1);
-    if (key != skip)
-      cp_async16(dst + key * hd * 2 + piece * 16, reinterpret_cast<const uint4*>(src + static_cast<long long>(key) * ld) + piece);
+    if (key != skip)  // piece p of row `key` lands at piece p ^ (key & 7): a column of pieces spreads over all banks
+      cp_async16(dst + key * hd * 2 + ((piece ^ (key & 7)) << 4),
+                 reinterpret_cast<const uint4*>(src + static_cast<long long>(key) * ld) + piece);
   }
 }
 
@@ -477,28 +513,27 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
         cp_async_wait_all();
         small_sync();
       }
-#pragma unroll 2
-      for (int base = warp * kpw; base < t1 - t0; base += pass) {  // warp-uniform trip count (shuffles inside)
-        const int key = base + sub;
+      // one thread per key: a 64- or 128-term fp32 chain per (key, head), no shuffles
+#pragma unroll 1
+      for (int key = wtid; key < t1 - t0; key += kSmallWorkers) {
         const int j = t0 + key;
-        const bool live = j < t1;  // lanes of one key agree; a warp may hold both live and dead keys
-        uint4 kr = make_uint4(0, 0, 0, 0);
-        if (live) kr = (j == newpos) ? *reinterpret_cast<const uint4*>(kn + dg * 8)
-                                     : *reinterpret_cast<const uint4*>(tile + key * row_bytes + dg * 16);
-        float kf[8];
-        unpack8(kr, kf);
+        const uint8_t* krow = tile + key * row_bytes;
 #pragma unroll 1
         for (int g = 0; g < gs; ++g) {
-          const float4 qa = *reinterpret_cast<const float4*>(qs + g * hd + dg * 8);
-          const float4 qb = *reinterpret_cast<const float4*>(qs + g * hd + dg * 8 + 4);
+          const float* qv = qs + g * hd;
           float dot = 0.f;
-          dot = fmaf(qa.x, kf[0], dot); dot = fmaf(qa.y, kf[1], dot); dot = fmaf(qa.z, kf[2], dot); dot = fmaf(qa.w, kf[3], dot);
-          dot = fmaf(qb.x, kf[4], dot); dot = fmaf(qb.y, kf[5], dot); dot = fmaf(qb.z, kf[6], dot); dot = fmaf(qb.w, kf[7], dot);
-          dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-          dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-          dot += __shfl_xor_sync(0xffffffffu, dot, 4);
-          if (lpk == 16) dot += __shfl_xor_sync(0xffffffffu, dot, 8);
-          if (dg == 0 && live) sc[g * chunk + (j - j0)] = bf16_round(dot) * A.scale;
+#pragma unroll 4
+          for (int piece = 0; piece < lpk; ++piece) {
+            const uint4 kr = (j == newpos) ? *reinterpret_cast<const uint4*>(kn + piece * 8)
+                                           : *reinterpret_cast<const uint4*>(krow + ((piece ^ (key & 7)) << 4));
+            float kf[8];
+            unpack8(kr, kf);
+            const float4 qa = *reinterpret_cast<const float4*>(qv + piece * 8);
+            const float4 qb = *reinterpret_cast<const float4*>(qv + piece * 8 + 4);
+            dot = fmaf(qa.x, kf[0], dot); dot = fmaf(qa.y, kf[1], dot); dot = fmaf(qa.z, kf[2], dot); dot = fmaf(qa.w, kf[3], dot);
+            dot = fmaf(qb.x, kf[4], dot); dot = fmaf(qb.y, kf[5], dot); dot = fmaf(qb.z, kf[6], dot); dot = fmaf(qb.w, kf[7], dot);
+          }
+          sc[g * chunk + (j - j0)] = bf16_round(dot) * A.scale;
         }
       }
     }
@@ -601,13 +636,23 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
         const int part = item / cols, col = item - part * cols;
         const int g = col / hd, d = col - g * hd;
         const int k0 = part * per_part, k1 = min(tk, k0 + per_part);
-        float acc = (t == 0) ? 0.f : red[item];
+        // four interleaved chains (keys k0 + 4n + c), added in a fixed order at the end
+        float part4[4] = {0.f, 0.f, 0.f, 0.f};
         const float* pr = sc + g * chunk + (t0 - j0);
-#pragma unroll 2
-        for (int key = k0; key < k1; ++key) {
-          const bf16* vrow = (t0 + key == newpos) ? vn : reinterpret_cast<const bf16*>(tile + key * row_bytes);
-          acc = fmaf(pr[key], __bfloat162float(vrow[d]), acc);
+#pragma unroll 1
+        for (int key = k0; key < k1; key += 4) {
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) {
+            const int kk = key + c4;
+            if (kk < k1) {
+              const bf16* vrow = (t0 + kk == newpos)
+                                     ? vn + d
+                                     : reinterpret_cast<const bf16*>(tile + kk * row_bytes + (((d >> 3) ^ (kk & 7)) << 4)) + (d & 7);
+              part4[c4] = fmaf(pr[kk], __bfloat162float(*vrow), part4[c4]);
+            }
+          }
         }
+        const float acc = ((t == 0) ? 0.f : red[item]) + ((part4[0] + part4[1]) + (part4[2] + part4[3]));
         red[item] = acc;
       }
     }
