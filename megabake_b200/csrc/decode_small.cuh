@@ -493,6 +493,9 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
     }
     cp_async_wait_all();
     small_sync();
+    if (owner && newpos - j0 < tile_keys && wtid < lpk)  // the new key joins its tile (its row was not fetched)
+      *reinterpret_cast<uint4*>(tile + (newpos - j0) * row_bytes + ((wtid ^ ((newpos - j0) & 7)) << 4)) =
+          *reinterpret_cast<const uint4*>(kn + wtid * 8);
     if (owner) {  // in-kernel KV append
       bf16* kd = A.k + b * A.kv_bstride + static_cast<long long>(A.len) * A.kv_ld + kvh * hd;
       bf16* vd = A.v + b * A.kv_bstride + static_cast<long long>(A.len) * A.kv_ld + kvh * hd;
@@ -511,7 +514,12 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
         small_sync();  // everyone is done with the previous tile
         fetch_tile(kbase, t0, t1);
         cp_async_wait_all();
+        if (newpos >= t0 && newpos < t1 && wtid < lpk)
+          *reinterpret_cast<uint4*>(tile + (newpos - t0) * row_bytes + ((wtid ^ ((newpos - t0) & 7)) << 4)) =
+              *reinterpret_cast<const uint4*>(kn + wtid * 8);
         small_sync();
+      } else {
+        small_sync();  // the patched row of the first tile is visible
       }
       // one thread per key: a 64- or 128-term fp32 chain per (key, head), no shuffles
 #pragma unroll 1
@@ -524,8 +532,7 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
           float dot = 0.f;
 #pragma unroll 4
           for (int piece = 0; piece < lpk; ++piece) {
-            const uint4 kr = (j == newpos) ? *reinterpret_cast<const uint4*>(kn + piece * 8)
-                                           : *reinterpret_cast<const uint4*>(krow + ((piece ^ (key & 7)) << 4));
+            const uint4 kr = *reinterpret_cast<const uint4*>(krow + ((piece ^ (key & 7)) << 4));
             float kf[8];
             unpack8(kr, kf);
             const float4 qa = *reinterpret_cast<const float4*>(qv + piece * 8);
@@ -615,11 +622,15 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
 #pragma unroll 1
       for (int i = wtid; i < cl; i += kSmallWorkers) sc[g * chunk + i] = bf16_round(expf(sc[g * chunk + i] - m) / denom);
     }
-    // --- value accumulation: an item is (part of the keys, head of the group, output column); its
-    // fp32 sum over the tiles lives in `red` (items <= 1024)
+    // --- value accumulation: an item is (part of the keys, head of the group, 16-byte piece of the
+    // output row); part p takes keys p, p + parts, ...; the fp32 sums of an item live in `red`
+    // between tiles and for the final addition of the parts (parts * group * head_dim <= 1024 floats)
     const int cols = gs * hd;
-    const int parts = max(1, kSmallWorkers / cols);
-    const int items = cols * parts;
+    const int pieces = gs * lpk;
+    int parts = kSmallWorkers / pieces;
+    if (parts * cols > 1024) parts = 1024 / cols;
+    if (parts < 1) parts = 1;
+    const int items = parts * pieces;
 #pragma unroll 1
     for (int t = 0; t < ntiles; ++t) {
       const int t0 = j0 + t * tile_keys, t1 = min(j1, t0 + tile_keys);
@@ -628,32 +639,30 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
         fetch_tile(vbase, t0, t1);
       }
       cp_async_wait_all();
+      if (newpos >= t0 && newpos < t1 && wtid < lpk)  // the new value row joins its tile
+        *reinterpret_cast<uint4*>(tile + (newpos - t0) * row_bytes + ((wtid ^ ((newpos - t0) & 7)) << 4)) =
+            *reinterpret_cast<const uint4*>(vn + wtid * 8);
       small_sync();  // the tile has landed, and (first tile) the probabilities are complete
       const int tk = t1 - t0;
-      const int per_part = (tk + parts - 1) / parts;
 #pragma unroll 1
       for (int item = wtid; item < items; item += kSmallWorkers) {
-        const int part = item / cols, col = item - part * cols;
-        const int g = col / hd, d = col - g * hd;
-        const int k0 = part * per_part, k1 = min(tk, k0 + per_part);
-        // four interleaved chains (keys k0 + 4n + c), added in a fixed order at the end
-        float part4[4] = {0.f, 0.f, 0.f, 0.f};
-        const float* pr = sc + g * chunk + (t0 - j0);
-#pragma unroll 1
-        for (int key = k0; key < k1; key += 4) {
+        const int part = item / pieces, pc = item - part * pieces;
+        const int g = pc / lpk, piece = pc - g * lpk;
+        float* mine = red + (part * gs + g) * hd + piece * 8;
+        float acc[8];
 #pragma unroll
-          for (int c4 = 0; c4 < 4; ++c4) {
-            const int kk = key + c4;
-            if (kk < k1) {
-              const bf16* vrow = (t0 + kk == newpos)
-                                     ? vn + d
-                                     : reinterpret_cast<const bf16*>(tile + kk * row_bytes + (((d >> 3) ^ (kk & 7)) << 4)) + (d & 7);
-              part4[c4] = fmaf(pr[kk], __bfloat162float(*vrow), part4[c4]);
-            }
-          }
+        for (int e = 0; e < 8; ++e) acc[e] = (t == 0) ? 0.f : mine[e];
+        const float* pr = sc + g * chunk + (t0 - j0);
+#pragma unroll 2
+        for (int kk = part; kk < tk; kk += parts) {
+          float vf[8];
+          unpack8(*reinterpret_cast<const uint4*>(tile + kk * row_bytes + ((piece ^ (kk & 7)) << 4)), vf);
+          const float w = pr[kk];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] = fmaf(w, vf[e], acc[e]);
         }
-        const float acc = ((t == 0) ? 0.f : red[item]) + ((part4[0] + part4[1]) + (part4[2] + part4[3]));
-        red[item] = acc;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) mine[e] = acc[e];
       }
     }
     small_sync();
