@@ -39,7 +39,7 @@ from megabake_b200.synth import CONFIGS, new_kv_state, synth_ids, synth_normal, 
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
 # profiles/megakernel_decode_smollm-1.7b_launch_list.md (mean of the two captured launches).
-NCU_TRAFFIC = {("smollm-1.7b", 1, 1024): 3_805_020_672}
+NCU_TRAFFIC = {("smollm-1.7b", 1, 1024): 3_638_545_216}
 
 
 def parse_args():
@@ -300,7 +300,8 @@ def main():
         "tokens_per_s_per_gpu": value / args.gpus,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": traffic, "peak_source": f"of {peak_kind}",
-                     "algorithmic_bytes_per_launch": bytes_per_launch, "kernel": "mk::megakernel",
+                     "algorithmic_bytes_per_launch": bytes_per_launch,
+                     "kernel": "mk::megakernel_small<%d>" % args.batch if args.batch <= 4 else "mk::megakernel",
                      "launch_us": launch_ms * 1e3, "frac_of_8TBps_nominal": achieved / 8000.0},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": 16 * args.batch,
                 "d2h_bytes_per_step": 2 * config.vocab * args.batch, "us_per_call": 1e3 * e2e_ms / e2e_steps},

@@ -1,6 +1,6 @@
 // Thin inline-PTX wrappers for the sm_100a features the megakernel uses:
 // mbarrier, TMA tiled loads, tcgen05 (MMA, TMEM alloc/load, commit) and the
-// proxy/thread-sync fences that order them.  No multicast forms are used.
+// proxy/thread-sync fences that order them.  Every copy lands in the issuing CTA only.
 #pragma once
 #include <cuda_bf16.h>
 #include <stdint.h>
