@@ -812,31 +812,36 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
   bool ok = true;  // per warp; made block-uniform by every close()
   auto project = [&](int gp, int nch) { ok = small_project<T>(cx, st, gp, nch, wu, wtid) && ok; };
   auto close = [&](int next_gp) -> bool { return small_close(cx, st, next_gp, wu, ok, wtid); };
-  for (int layer = 0; layer < p.layers; ++layer) {
-    const int gp = layer * 4;
-    {
-      // The cached K and V rows of this CTA's attention units do not depend on this step: ask L2
-      // for them now, while the q/k/v weights stream, so that the attention phase finds them there
-      // (a (sequence, head) slice of the cache is 128-byte pieces 4 KB apart, slow to fetch cold).
-      const int len = cx.misc->len_s[layer];
-      const int nch = decode_chunks(len + 1, p.batch * p.kv_heads, cx.grid, gs, kAttScoreBytes);
-      const int chunk = (len + 1 + nch - 1) / nch;
-      const int units = p.batch * p.kv_heads * nch;
-      const int lines = p.head_dim / 64;  // 128-byte lines per cached row of one head
-      for (int u = cx.cta; u < units; u += cx.grid) {
-        const int rowg = u / nch, ch = u - rowg * nch;
-        const int b = rowg / p.kv_heads, kvh = rowg - b * p.kv_heads;
-        const int j0 = ch * chunk, j1 = min(len, j0 + chunk);
-        const size_t head_off = static_cast<size_t>(b) * A.kv_bstride + static_cast<size_t>(kvh) * p.head_dim;
-        const bf16* kb = static_cast<const bf16*>(p.kc[layer]) + head_off;
-        const bf16* vb = static_cast<const bf16*>(p.vc[layer]) + head_off;
-        for (int item = wtid; item < (j1 - j0) * lines; item += kSmallWorkers) {
-          const size_t off = static_cast<size_t>(j0 + item / lines) * A.kv_ld + (item % lines) * 64;
-          prefetch_l2(kb + off);
-          prefetch_l2(vb + off);
-        }
+  // The cached K and V rows of this CTA's attention units do not depend on this step: ask L2 for
+  // them ahead of time (a (sequence, head) slice of the cache is 128-byte pieces 4 KB apart, slow
+  // to fetch cold).  Layer 0 asks before its first phase; every later layer while the barrier that
+  // closes the previous layer is pending, when the consumers have nothing else to do.
+  auto prefetch_kv = [&](int layer) {
+    if (layer >= p.layers) return;
+    const int len = cx.misc->len_s[layer];
+    const int nch = decode_chunks(len + 1, p.batch * p.kv_heads, cx.grid, gs, kAttScoreBytes);
+    const int chunk = (len + 1 + nch - 1) / nch;
+    const int units = p.batch * p.kv_heads * nch;
+    const int shift = (p.head_dim == 64) ? 0 : 1;  // 128-byte lines per cached row of one head: 1 or 2
+#pragma unroll 1
+    for (int u = cx.cta; u < units; u += cx.grid) {
+      const int rowg = u / nch, ch = u - rowg * nch;
+      const int b = rowg / p.kv_heads, kvh = rowg - b * p.kv_heads;
+      const int j0 = ch * chunk, j1 = min(len, j0 + chunk);
+      const size_t head_off = static_cast<size_t>(b) * A.kv_bstride + static_cast<size_t>(kvh) * p.head_dim;
+      const bf16* kb = static_cast<const bf16*>(p.kc[layer]) + head_off;
+      const bf16* vb = static_cast<const bf16*>(p.vc[layer]) + head_off;
+#pragma unroll 1
+      for (int item = wtid; item < ((j1 - j0) << shift); item += kSmallWorkers) {
+        const size_t off = static_cast<size_t>(j0 + (item >> shift)) * A.kv_ld + (item & shift) * 64;
+        prefetch_l2(kb + off);
+        prefetch_l2(vb + off);
       }
     }
+  };
+  prefetch_kv(0);
+  for (int layer = 0; layer < p.layers; ++layer) {
+    const int gp = layer * 4;
     project(gp, 1);                          // [residual update, RMSNorm] q, k, v (+bias)
     MK_SMALL_STEP();
     if (!close(gp + 1)) return;
@@ -859,7 +864,13 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
     if (!close(gp + 3)) return;
     project(gp + 3, 1);                      // down (fp32 K-slice partials)
     MK_SMALL_STEP();
-    if (!close(gp + 4)) return;
+    {  // the barrier that closes the layer, with the next layer's cache prefetch between its halves
+      if (!ok) cx.misc->wabort = 1;
+      small_arrive(cx, st, wtid);
+      wu = small_norm_weight(cx, gp + 4, wtid);
+      prefetch_kv(layer + 1);
+      if (!small_wait(cx, st, wtid)) return;
+    }
   }
 #undef MK_SMALL_STEP
   project(p.layers * 4, 1);                               // [residual update, final RMSNorm] lm_head
