@@ -107,8 +107,9 @@ def test_decode_smollm_135m_64_steps(device, engine):
     assert run == 67 and ties <= 8  # positions where the reference's own top two logits tie in bf16
 
 
-def test_decode_qwen2_half_b_64_steps(device):
-    ties, run = run_golden_decode("c2", device, "tcgen05", deep=True)
+@pytest.mark.parametrize("engine", ["auto", "tcgen05"])
+def test_decode_qwen2_half_b_64_steps(device, engine):
+    ties, run = run_golden_decode("c2", device, engine, deep=True)
     assert run == 67 and ties <= 8
 
 
@@ -178,7 +179,7 @@ def test_decode_smollm_1_7b_context_1024(device):
 
 
 # --------------------------------------------------------------------------- decode vs oracle on the same device
-def oracle_decode_compare(config, device, batch, capacity, prefill, steps, engine="tcgen05", seed=5):
+def oracle_decode_compare(config, device, batch, capacity, prefill, steps, engine="auto", seed=5):
     from oracle import decoder_oracle as oracle
 
     weights = synth_weights(config, seed=seed, norm_std=0.1, device=device)
@@ -246,9 +247,12 @@ def test_decode_error_no_worse_than_eager_bf16(device):
             assert mine_error <= 1.25 * eager_error + 1e-3, f"cache {layer}: {mine_error:.4g} vs eager {eager_error:.4g}"
 
 
-@pytest.mark.parametrize("batch", [1, 3, 4, 5, 16, 21])
-def test_decode_batches_match_oracle(device, batch):
-    oracle_decode_compare(tiny_config(q_heads=4, kv_heads=1, hidden=256), device, batch, capacity=24, prefill=0, steps=4)
+@pytest.mark.parametrize("engine", ["auto", "tcgen05"])
+@pytest.mark.parametrize("batch", [1, 2, 3, 4, 5, 16, 21])
+def test_decode_batches_match_oracle(device, batch, engine):
+    """Batches 1-4 run the small-launch kernel under "auto" (one instantiation per token count)."""
+    oracle_decode_compare(tiny_config(q_heads=4, kv_heads=1, hidden=256), device, batch, capacity=24, prefill=0, steps=4,
+                          engine=engine)
 
 
 @pytest.mark.parametrize("engine", ["tcgen05", "fma"])
@@ -262,15 +266,31 @@ def test_decode_to_the_last_cache_row(device):
     oracle_decode_compare(tiny_config(), device, batch=2, capacity=8, prefill=5, steps=3)
 
 
-def test_decode_qwen_form_gqa7_bias(device):
+@pytest.mark.parametrize("engine", ["auto", "tcgen05"])
+def test_decode_qwen_form_gqa7_bias(device, engine):
     config = tiny_config(hidden=448, q_heads=7, kv_heads=1, intermediate=960, qkv_bias=True, rope_style="hf",
                          rms_eps=1e-6, rope_theta=1e6)
-    oracle_decode_compare(config, device, batch=2, capacity=96, prefill=70, steps=3)
+    oracle_decode_compare(config, device, batch=2, capacity=96, prefill=70, steps=3, engine=engine)
 
 
-def test_decode_head_dim_128(device):
+@pytest.mark.parametrize("engine", ["auto", "tcgen05"])
+def test_decode_head_dim_128(device, engine):
     config = tiny_config(hidden=512, q_heads=4, kv_heads=2, head_dim=128, intermediate=768)
-    oracle_decode_compare(config, device, batch=1, capacity=160, prefill=130, steps=3)
+    oracle_decode_compare(config, device, batch=1, capacity=160, prefill=130, steps=3, engine=engine)
+
+
+@pytest.mark.parametrize("head_dim", [64, 128])
+def test_small_launch_attention_walks_several_tiles(device, head_dim):
+    """32 (sequence, head) row groups leave four context chunks of ~350 keys: more than one
+    shared-memory tile per chunk (304 keys of 64, 152 of 128), the new key in the last tile."""
+    config = tiny_config(hidden=512, q_heads=8, kv_heads=8, head_dim=head_dim, intermediate=768)
+    oracle_decode_compare(config, device, batch=4, capacity=1500, prefill=1400, steps=2)
+
+
+def test_small_launch_kernel_falls_back_beyond_its_score_buffer(device):
+    """Capacities past 16 chunks x 4096 / group keys go to the tensor engine, same results."""
+    config = tiny_config(q_heads=8, kv_heads=1, hidden=512, intermediate=1024)
+    oracle_decode_compare(config, device, batch=1, capacity=8200, prefill=600, steps=2)
 
 
 def test_decode_is_deterministic_at_full_size(device):
