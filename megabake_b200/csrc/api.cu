@@ -39,7 +39,7 @@ int fail(int code, const char* fmt, ...) {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct Carve {
-  size_t ctrl, tmaps, phases, hidden, hidden2, qkv, attn, act, partial, att_xch, att_part, total;
+  size_t ctrl, tmaps, phases, hidden, hidden2, qkv, qkv_ll, attn, act, partial, att_xch, att_part, total;
 };
 
 int qkv_width(const mk_config& c) { return (c.q_heads + 2 * c.kv_heads) * c.head_dim; }
@@ -61,6 +61,7 @@ Carve carve(const mk_config& c) {
   v.hidden = take(m * c.hidden * 2);
   v.hidden2 = take(static_cast<size_t>(kSplitTokens) * c.hidden * 2);
   v.qkv = take(m * qkv_width(c) * 2);
+  v.qkv_ll = take(static_cast<size_t>(kSplitTokens) * qkv_width(c) * 4);
   v.attn = take(m * c.q_heads * c.head_dim * 2);
   v.act = take(m * c.intermediate * 2);
   v.partial = take(static_cast<size_t>(kMaxSplit) * kSplitTokens * c.hidden * 4);
@@ -140,6 +141,7 @@ struct mk_handle_s {
   long long timeout_cycles;
   float att_scale;
   bool fma_ok;  // the small-launch kernel can run the split-K table: every K slice fits its fp32 operand buffer
+  bool small_ll;  // its q/k/v phases hand their outputs to attention as stamped words (one grid barrier fewer per layer)
   unsigned long long* trace;
   int trace_cap;
   std::mutex lock;
@@ -229,6 +231,7 @@ void base_params(mk_handle h, KParams& p) {
   p.qkv = at<bf16>(h, h->cv.qkv);
   p.attn = at<bf16>(h, h->cv.attn);
   p.act = at<bf16>(h, h->cv.act);
+  p.qkv_ll = at<unsigned long long>(h, h->cv.qkv_ll);
   p.att_xch = at<float>(h, h->cv.att_xch);
   p.att_part = at<float>(h, h->cv.att_part);
   p.ctrl = at<Control>(h, h->cv.ctrl);
@@ -472,6 +475,20 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
         if (ph.ksplit != 1) return fail(MK_ERR_UNSUPPORTED, "small-launch table: a split phase with more than 64 rows");
         finish_phase(ph, h->grid, false, kSmallTileRows);
       }
+      if (ph.nseg == 3) {  // q, k, v: outputs leave in pairs of rows, so a tile holds an even number of rows
+        if (ph.rows & 1) {
+          ph.rows += 1;
+          int tile = 0;
+          for (int sg = 0; sg < 3; ++sg) {
+            ph.tile_start[sg] = tile;
+            tile += (ph.n[sg] + ph.rows - 1) / ph.rows;
+          }
+          ph.tile_start[3] = tile;
+          ph.ntiles = tile;
+          ph.nunits = tile * ph.ksplit;
+        }
+        ph.ll = (ph.rows <= kSmallTileRows && ph.n[0] % 2 == 0 && ph.n[1] % 2 == 0 && ph.ksplit == 1) ? 1 : 0;
+      }
       int kb = 1;
       for (int cand = 2; cand <= 4; cand += 2)
         if (ph.kslice % cand == 0 && ph.rows * cand * 128 <= kFatCopyBytes) kb = cand;
@@ -485,6 +502,11 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
       }
     }
   }
+  h->small_ll = h->fma_ok;
+  for (int l = 0; l < L && h->small_ll; ++l)
+    if (!phases[2 * nphases + 4 * l].ll) h->small_ll = false;
+  if (!h->small_ll)
+    for (int l = 0; l < L; ++l) phases[2 * nphases + 4 * l].ll = 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   MK_CUDA(cudaMemcpyAsync(dmaps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, s));
   MK_CUDA(cudaMemcpyAsync(at<GemmPhase>(h, h->cv.phases), phases.data(), phases.size() * sizeof(GemmPhase),
@@ -529,6 +551,7 @@ int mk_decode(mk_handle h, const int64_t* ids, const int64_t* positions, int bat
   if (small) p.phases = at<GemmPhase>(h, h->cv.phases) + 2 * phases_per_table(h->cfg);
   p.n_gemm = 4 * L + 1;
   p.nbar = 5 * L;
+  if (small && h->small_ll) p.nbar = 4 * L;  // no grid barrier between q/k/v and attention
   p.stream_once = (ntt == 1);
   p.ids = reinterpret_cast<const long long*>(ids);
   p.pos = reinterpret_cast<const long long*>(positions);
@@ -804,7 +827,7 @@ int mk_kv_attention_static(int q_heads, int kv_heads, int head_dim, const void* 
   view.epoch = slot.epoch; view.att_epoch = slot.att_epoch; view.launches = slot.launches;
   view.timeout_cycles = slot.timeout_cycles;
   view.att_scale = static_cast<float>(std::pow(static_cast<double>(head_dim), -0.5));
-  view.fma_ok = false; view.trace = nullptr; view.trace_cap = 0;
+  view.fma_ok = false; view.small_ll = false; view.trace = nullptr; view.trace_cap = 0;
   if (int e = attention_fits(&view, capacity, "mk_kv_attention_static")) return e;
   KParams p;
   base_params(&view, p);

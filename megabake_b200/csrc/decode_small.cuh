@@ -189,13 +189,20 @@ constexpr int kSmallTileRows = 64;                          // tile height of th
 static_assert(kRowSumOffset + 2 * kSmallTileRows * kSplitTokens * 4 <= kBBytes, "row sums do not fit");
 
 template <int T>
-__device__ __noinline__ void small_finish_row(const Ctx& cx, const GemmPhase* ph, int seg, int slice, int n, int r) {
+__device__ __noinline__ void small_finish_row(const Ctx& cx, const GemmPhase* ph, int seg, int slice, int n, int r,
+                                              uint32_t* bits) {
   const float* sums = reinterpret_cast<const float*>(cx.smem_b + kRowSumOffset);
   float v[2][T];
 #pragma unroll
   for (int t = 0; t < T; ++t) {
     v[0][t] = sums[r * kSplitTokens + t];
     v[1][t] = sums[(kSmallTileRows + r) * kSplitTokens + t];
+  }
+  if (ph->ll) {  // q/k/v of the small-launch table: the caller sends the rounded outputs as stamped words
+    const float bias = ph->bias[seg] ? ldg_bf16(ph->bias[seg] + n) : 0.f;
+#pragma unroll
+    for (int t = 0; t < T; ++t) bits[t] = __bfloat16_as_ushort(__float2bfloat16_rn(v[0][t] + bias));
+    return;
   }
   if (ph->epi == EPI_PARTIAL) {
     store_partial<T>(cx, ph, slice, n, v[0], 0, T);
@@ -217,7 +224,7 @@ __device__ __noinline__ void small_finish_row(const Ctx& cx, const GemmPhase* ph
 // keeps one fp32 chain over the K loop; at the end a fixed shuffle tree adds the lanes of a row.
 // Accumulation order depends only on the CTA's rotated chunk order: no dependence on timing.
 template <int T, int NACC>
-__device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, int wtid, uint4 wu, int nch) {
+__device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, int wtid, uint4 wu, int nch, uint32_t stamp) {
   const GemmPhase* ph = &cx.misc->phase[gp & 1];
   const int nunits = ph->nunits, rows = ph->rows, ksplit = ph->ksplit, kslice = ph->kslice, gran = ph->gran;
   const bool per_unit = ksplit > 1;
@@ -354,7 +361,25 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
         }
       }
       small_sync();
-      if (wtid < rows && row0 + wtid < ph->n[seg]) small_finish_row<T>(cx, ph, seg, slice, row0 + wtid, wtid);
+      {
+        const bool mine = wtid < rows && row0 + wtid < ph->n[seg];
+        uint32_t bits[T];
+#pragma unroll
+        for (int t = 0; t < T; ++t) bits[t] = 0u;
+        if (mine) small_finish_row<T>(cx, ph, seg, slice, row0 + wtid, wtid, bits);
+        if (ph->ll) {
+          // Rows 2k and 2k + 1 (even tile height, even segment sizes) share a word:
+          // {stamp, bf16 of the odd column, bf16 of the even column}, one 64-bit store.
+          const int col = ph->out_col[seg] + row0 + wtid;
+#pragma unroll
+          for (int t = 0; t < T; ++t) {
+            const uint32_t other = __shfl_xor_sync(0xffffffffu, bits[t], 1);
+            if (mine && !(wtid & 1))
+              st_relaxed_u64(cx.p->qkv_ll + static_cast<size_t>(t) * (cx.p->qkv_ld / 2) + (col >> 1),
+                             (static_cast<unsigned long long>(stamp) << 32) | (other << 16) | bits[t]);
+          }
+        }
+      }
     }
     trace_event(cx, wtid, EV_PHASE_DONE);
   }
@@ -364,9 +389,10 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
 }
 
 template <int T>
-__device__ __forceinline__ bool small_gemm_t(const Ctx& cx, int gp, SmallState& st, int wtid, uint4 wu, int nch) {
-  return cx.misc->phase[gp & 1].nacc == 2 ? small_gemm<T, 2>(cx, gp, st, wtid, wu, nch)
-                                          : small_gemm<T, 1>(cx, gp, st, wtid, wu, nch);
+__device__ __forceinline__ bool small_gemm_t(const Ctx& cx, int gp, SmallState& st, int wtid, uint4 wu, int nch,
+                                             uint32_t stamp) {
+  return cx.misc->phase[gp & 1].nacc == 2 ? small_gemm<T, 2>(cx, gp, st, wtid, wu, nch, stamp)
+                                          : small_gemm<T, 1>(cx, gp, st, wtid, wu, nch, stamp);
 }
 
 // Decode attention with RoPE, in-kernel KV append and a context split across
@@ -378,6 +404,7 @@ __device__ __forceinline__ bool small_gemm_t(const Ctx& cx, int gp, SmallState& 
 // rotated, the V rows before the softmax statistics are exchanged, so that one
 // memory latency hides behind each of those steps.
 struct SmallAttn {
+  const unsigned long long* ll;    // stamped q/k/v words [batch][qkv width / 2], or null: read the bf16 buffer
   const bf16* q; int q_ld;         // [batch][q_heads * hd] inside the qkv row
   bf16 *k, *v;                     // caches [batch][capacity][kv_heads][hd]
   long long kv_bstride; int kv_ld;
@@ -464,17 +491,35 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
     fetch_tile(kbase, j0, min(j1, j0 + tile_keys));  // in flight while q is rotated
 
     // --- q of every head of the group and the new key (both rotated), and the new value: one round trip
+    bool fresh = true;  // every stamped word this thread needs has arrived
     {
       const long long pos = cx.misc->pos_s[b];
       const int ropes = (gs + 1) * half;
+      const int q_size = p.q_heads * hd, kv_size = p.kv_heads * hd;
+      // Column c of sequence b's q/k/v row: from the bf16 buffer, or (small-launch table) from the word the
+      // projection's epilogue stamped; waiting for the stamp is what orders this phase after that one.
+      auto qkv_at = [&](int c) -> float {
+        if (A.ll == nullptr) return ldcg_bf16(A.q + static_cast<long long>(b) * A.q_ld + c);
+        const unsigned long long* word = A.ll + static_cast<size_t>(b) * (p.qkv_ld / 2) + (c >> 1);
+        unsigned long long w = ld_relaxed_u64(word);
+        uint32_t spins = 0;
+        while (static_cast<uint32_t>(w >> 32) != A.stamp) {
+          if ((++spins & 255u) == 0 && give_up(cx, SITE_ATT_EXCHANGE, -1 - rowg)) {
+            fresh = false;
+            break;
+          }
+          w = ld_relaxed_u64(word);
+        }
+        const uint32_t lo = static_cast<uint32_t>(w);
+        return __uint_as_float((c & 1) ? (lo & 0xFFFF0000u) : (lo << 16));
+      };
 #pragma unroll 1
       for (int idx = wtid; idx < ropes + hd; idx += kSmallWorkers) {
         if (idx < ropes) {
           const int g = idx / half, i = idx - g * half;
-          const bf16* src = (g < gs) ? A.q + static_cast<long long>(b) * A.q_ld + (kvh * gs + g) * hd
-                                     : A.knew + static_cast<long long>(b) * A.new_ld + kvh * hd;
-          float x1 = ldcg_bf16(src + i);
-          float x2 = ldcg_bf16(src + i + half);
+          const int c0 = (g < gs) ? (kvh * gs + g) * hd : q_size + kvh * hd;
+          float x1 = qkv_at(c0 + i);
+          float x2 = qkv_at(c0 + i + half);
           const float cs = ldg_bf16(p.cos_t + pos * hd + i);
           const float sn = ldg_bf16(p.sin_t + pos * hd + i);
           rope_pair(x1, x2, cs, sn, p.rope_style, x1, x2);
@@ -487,12 +532,12 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
           }
         } else {
           const int i = idx - ropes;
-          vn[i] = __float2bfloat16_rn(ldcg_bf16(A.vnew + static_cast<long long>(b) * A.new_ld + kvh * hd + i));
+          vn[i] = __float2bfloat16_rn(qkv_at(q_size + kv_size + kvh * hd + i));
         }
       }
     }
     cp_async_wait_all();
-    small_sync();
+    if (!small_ok(cx, fresh)) return false;
     if (owner && newpos - j0 < tile_keys && wtid < lpk)  // the new key joins its tile (its row was not fetched)
       *reinterpret_cast<uint4*>(tile + (newpos - j0) * row_bytes + ((wtid ^ ((newpos - j0) & 7)) << 4)) =
           *reinterpret_cast<const uint4*>(kn + wtid * 8);
@@ -772,9 +817,10 @@ __device__ __forceinline__ uint4 small_norm_weight(const Ctx& cx, int gp, int wt
 
 // One projection phase; the next phase's descriptor is requested first and stored last.
 template <int T>
-__device__ __forceinline__ bool small_project(const Ctx& cx, SmallState& st, int gp, int nch, uint4 wu, int wtid) {
+__device__ __forceinline__ bool small_project(const Ctx& cx, SmallState& st, int gp, int nch, uint4 wu, int wtid,
+                                              uint32_t stamp) {
   const uint32_t word = small_phase_word(cx, gp + 1, wtid);
-  const bool ok = small_gemm_t<T>(cx, gp, st, wtid, wu, nch);
+  const bool ok = small_gemm_t<T>(cx, gp, st, wtid, wu, nch, stamp);
   small_phase_store(cx, gp + 1, wtid, word);
   return ok;
 }
@@ -798,6 +844,7 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
   const int q_size = p.q_heads * p.head_dim, kv_size = p.kv_heads * p.head_dim;
   const int gs = p.q_heads / p.kv_heads;
   SmallAttn A;
+  A.ll = nullptr;
   A.q = p.qkv; A.q_ld = p.qkv_ld;
   A.knew = p.qkv + q_size; A.vnew = A.knew + kv_size; A.new_ld = p.qkv_ld;
   A.out = p.attn; A.out_ld = q_size;
@@ -810,7 +857,9 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
 #define MK_SMALL_STEP() do { if (p.debug_stop && ++step >= p.debug_stop) return; } while (0)
   // One projection phase: the next descriptor is fetched while this phase runs.
   bool ok = true;  // per warp; made block-uniform by every close()
-  auto project = [&](int gp, int nch) { ok = small_project<T>(cx, st, gp, nch, wu, wtid) && ok; };
+  auto project = [&](int gp, int nch) {
+    ok = small_project<T>(cx, st, gp, nch, wu, wtid, p.att_epoch + static_cast<uint32_t>(gp >> 2) + 1u) && ok;
+  };
   auto close = [&](int next_gp) -> bool { return small_close(cx, st, next_gp, wu, ok, wtid); };
   // The cached K and V rows of this CTA's attention units do not depend on this step: ask L2 for
   // them ahead of time (a (sequence, head) slice of the cache is 128-byte pieces 4 KB apart, slow
@@ -842,9 +891,17 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
   prefetch_kv(0);
   for (int layer = 0; layer < p.layers; ++layer) {
     const int gp = layer * 4;
+    const bool handoff = cx.misc->phase[gp & 1].ll != 0;  // same for every layer and CTA
     project(gp, 1);                          // [residual update, RMSNorm] q, k, v (+bias)
     MK_SMALL_STEP();
-    if (!close(gp + 1)) return;
+    if (handoff) {
+      // q/k/v travel as stamped words: attention starts as soon as this CTA's own tile is out and waits
+      // word by word for the rows of its head; only the shared memory has to be handed over.
+      A.ll = p.qkv_ll;
+      if (!small_ok(cx, ok)) return;
+    } else if (!close(gp + 1)) {
+      return;
+    }
     MK_SMALL_STEP();
     A.k = static_cast<bf16*>(p.kc[layer]); A.v = static_cast<bf16*>(p.vc[layer]);
     A.len = cx.misc->len_s[layer];

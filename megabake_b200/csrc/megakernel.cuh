@@ -77,6 +77,8 @@ struct GemmPhase {
   int epi, bmode;
   int gather;                  // 1: activation rows are embedding rows selected by the token ids
   int to_logits;               // 1: output goes to the caller's logits buffer
+  int ll;                      // 1 (small-launch q/k/v phase): outputs leave as 64-bit words {bf16 pair, stamp} in
+                               // KParams::qkv_ll, which the attention phase polls instead of waiting at a grid barrier
   int add_parts;               // B_NORM: fp32 partial slices of the previous projection to add to the residual
   const bf16* normw;
   const bf16* src; int src_ld; // activation source (B_NORM: the residual stream before this phase)
@@ -118,6 +120,7 @@ struct KParams {
   long long timeout_cycles;
   const GemmPhase* phases;
   bf16 *hidden_buf, *qkv, *attn, *act;
+  unsigned long long* qkv_ll;  // [kSplitTokens][qkv width / 2]: stamped q/k/v outputs of the small-launch kernel
   float* att_xch;     // [row groups][kMaxChunks][kExchangeFloats]
   float* att_part;    // [batch * q_heads][kMaxChunks][head_dim]
   Control* ctrl;
