@@ -39,7 +39,7 @@ int fail(int code, const char* fmt, ...) {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct Carve {
-  size_t ctrl, tmaps, phases, hidden, hidden2, qkv, qkv_ll, attn, act, partial, att_xch, att_part, total;
+  size_t ctrl, tmaps, phases, hidden, hidden2, qkv, qkv_ll, act_ll, att_ll, attn, act, partial, partial2, att_xch, att_part, total;
 };
 
 int qkv_width(const mk_config& c) { return (c.q_heads + 2 * c.kv_heads) * c.head_dim; }
@@ -62,9 +62,12 @@ Carve carve(const mk_config& c) {
   v.hidden2 = take(static_cast<size_t>(kSplitTokens) * c.hidden * 2);
   v.qkv = take(m * qkv_width(c) * 2);
   v.qkv_ll = take(static_cast<size_t>(kSplitTokens) * qkv_width(c) * 4);
+  v.act_ll = take(static_cast<size_t>(kSplitTokens) * c.intermediate * 4);
+  v.att_ll = take(static_cast<size_t>(kSplitTokens) * c.q_heads * kMaxChunks * c.head_dim * 8);
   v.attn = take(m * c.q_heads * c.head_dim * 2);
   v.act = take(m * c.intermediate * 2);
   v.partial = take(static_cast<size_t>(kMaxSplit) * kSplitTokens * c.hidden * 4);
+  v.partial2 = take(static_cast<size_t>(kMaxSplit) * kSplitTokens * c.hidden * 4);  // down-proj partials of the small-launch table
   v.att_xch = take(m * c.kv_heads * kMaxChunks * kExchangeFloats * 4);
   v.att_part = take(m * c.q_heads * kMaxChunks * c.head_dim * 4);
   v.total = off;
@@ -232,6 +235,7 @@ void base_params(mk_handle h, KParams& p) {
   p.attn = at<bf16>(h, h->cv.attn);
   p.act = at<bf16>(h, h->cv.act);
   p.qkv_ll = at<unsigned long long>(h, h->cv.qkv_ll);
+  p.att_ll = at<unsigned long long>(h, h->cv.att_ll);
   p.att_xch = at<float>(h, h->cv.att_xch);
   p.att_part = at<float>(h, h->cv.att_part);
   p.ctrl = at<Control>(h, h->cv.ctrl);
@@ -475,19 +479,21 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
         if (ph.ksplit != 1) return fail(MK_ERR_UNSUPPORTED, "small-launch table: a split phase with more than 64 rows");
         finish_phase(ph, h->grid, false, kSmallTileRows);
       }
-      if (ph.nseg == 3) {  // q, k, v: outputs leave in pairs of rows, so a tile holds an even number of rows
+      if (ph.nseg == 3 || ph.nacc == 2) {  // q/k/v and gate/up: outputs leave in pairs of rows: even tile height
         if (ph.rows & 1) {
           ph.rows += 1;
+          const int nsg = ph.nacc == 2 ? 1 : ph.nseg;
           int tile = 0;
-          for (int sg = 0; sg < 3; ++sg) {
+          for (int sg = 0; sg < nsg; ++sg) {
             ph.tile_start[sg] = tile;
             tile += (ph.n[sg] + ph.rows - 1) / ph.rows;
           }
-          ph.tile_start[3] = tile;
+          ph.tile_start[nsg] = tile;
           ph.ntiles = tile;
           ph.nunits = tile * ph.ksplit;
         }
-        ph.ll = (ph.rows <= kSmallTileRows && ph.n[0] % 2 == 0 && ph.n[1] % 2 == 0 && ph.ksplit == 1) ? 1 : 0;
+        const bool even = ph.n[0] % 2 == 0 && (ph.nacc == 2 || (ph.n[1] % 2 == 0 && ph.n[2] % 2 == 0));
+        ph.ll = (ph.rows <= kSmallTileRows && even && ph.ksplit == 1) ? 1 : 0;
       }
       int kb = 1;
       for (int cand = 2; cand <= 4; cand += 2)
@@ -502,11 +508,25 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
       }
     }
   }
+  // Stamped hand-offs of the small-launch table (q/k/v -> attention -> o_proj, gate/up -> down): all or none.
   h->small_ll = h->fma_ok;
   for (int l = 0; l < L && h->small_ll; ++l)
-    if (!phases[2 * nphases + 4 * l].ll) h->small_ll = false;
-  if (!h->small_ll)
-    for (int l = 0; l < L; ++l) phases[2 * nphases + 4 * l].ll = 0;
+    if (!phases[2 * nphases + 4 * l].ll || !phases[2 * nphases + 4 * l + 2].ll) h->small_ll = false;
+  for (int l = 0; l < L && h->fma_ok; ++l) {
+    GemmPhase* ph = phases.data() + 2 * nphases + 4 * l;
+    for (int i = 0; i < 4; ++i) {
+      ph[i].ll = 0; ph[i].ll_dst = nullptr; ph[i].ll_src = nullptr; ph[i].ll_ld = 0; ph[i].ll_src_ld = 0;
+    }
+    if (!h->small_ll) continue;
+    ph[0].ll = 1; ph[0].ll_dst = at<unsigned long long>(h, h->cv.qkv_ll); ph[0].ll_ld = qkv_width(c) / 2;
+    ph[1].ll_src = at<unsigned long long>(h, h->cv.att_ll);
+    ph[2].ll = 1; ph[2].ll_dst = at<unsigned long long>(h, h->cv.act_ll); ph[2].ll_ld = c.intermediate / 2;
+    ph[3].ll_src = at<unsigned long long>(h, h->cv.act_ll); ph[3].ll_src_ld = c.intermediate / 2;
+    // with no barrier between attention and o_proj, nor gate/up and down, their partials need buffers of their own
+    ph[3].partial = at<float>(h, h->cv.partial2);
+    if (l + 1 < L) ph[4].partial = at<float>(h, h->cv.partial2);
+  }
+  if (h->fma_ok && h->small_ll) phases[2 * nphases + 4 * L].partial = at<float>(h, h->cv.partial2);  // lm_head adds the last down-proj
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   MK_CUDA(cudaMemcpyAsync(dmaps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, s));
   MK_CUDA(cudaMemcpyAsync(at<GemmPhase>(h, h->cv.phases), phases.data(), phases.size() * sizeof(GemmPhase),
@@ -551,7 +571,7 @@ int mk_decode(mk_handle h, const int64_t* ids, const int64_t* positions, int bat
   if (small) p.phases = at<GemmPhase>(h, h->cv.phases) + 2 * phases_per_table(h->cfg);
   p.n_gemm = 4 * L + 1;
   p.nbar = 5 * L;
-  if (small && h->small_ll) p.nbar = 4 * L;  // no grid barrier between q/k/v and attention
+  if (small && h->small_ll) p.nbar = 2 * L;  // stamped hand-offs: only o_proj -> gate/up and down -> next layer keep a grid barrier
   p.stream_once = (ntt == 1);
   p.ids = reinterpret_cast<const long long*>(ids);
   p.pos = reinterpret_cast<const long long*>(positions);

@@ -82,6 +82,44 @@ __device__ __forceinline__ void small_phase_store(const Ctx& cx, int gp, int wti
 }
 static_assert(sizeof(GemmPhase) / 4 <= kSmallWorkers, "one word of the phase descriptor per consumer thread");
 
+// Wait (bounded) until a 64-bit word carries `stamp` in its upper half; the lower half is the payload.
+__device__ __forceinline__ uint32_t stamped_payload(const Ctx& cx, const unsigned long long* word, uint32_t stamp, bool& fresh) {
+  unsigned long long w = ld_relaxed_u64(word);
+  uint32_t spins = 0;
+  while (static_cast<uint32_t>(w >> 32) != stamp) {
+    if ((++spins & 255u) == 0 && give_up(cx, SITE_ATT_EXCHANGE, -1)) {
+      fresh = false;
+      break;
+    }
+    w = ld_relaxed_u64(word);
+  }
+  return static_cast<uint32_t>(w);
+}
+
+// The same for N consecutive words (N even, 16-byte aligned): every load is issued before any stamp
+// is looked at, and only a stale batch is read again.
+template <int N>
+__device__ __forceinline__ void stamped_payloads(const Ctx& cx, const unsigned long long* words, uint32_t stamp, bool& fresh,
+                                                 uint32_t* out) {
+  uint32_t spins = 0;
+  while (true) {
+    unsigned long long w[N];
+#pragma unroll
+    for (int i = 0; i < N; i += 2) ld_relaxed_v2_u64(words + i, w[i], w[i + 1]);
+    bool all = true;
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      all = all && static_cast<uint32_t>(w[i] >> 32) == stamp;
+      out[i] = static_cast<uint32_t>(w[i]);
+    }
+    if (all) return;
+    if ((++spins & 255u) == 0 && give_up(cx, SITE_ATT_EXCHANGE, -1)) {
+      fresh = false;
+      return;
+    }
+  }
+}
+
 // fp32 operand layout: per token kXFloats floats; inside a 64-element K chunk the
 // eight 8-element vectors are stored as two float4 halves, 128 bytes apart, so
 // that the eight lanes sharing a weight row read 128 contiguous bytes per load.
@@ -165,21 +203,50 @@ __device__ __noinline__ void small_stage_norm(const Ctx& cx, const GemmPhase* ph
 
 // Plain or attention-output operand: K chunks [k0, k0 + count) of every token.  One vector per
 // thread and trip (256 vectors cover a 2048-element slice of one token); kept small on purpose.
-__device__ __noinline__ void small_stage_cols(const Ctx& cx, const GemmPhase* ph, int k0, int count, int mt, int wtid,
-                                              int nch) {
+__device__ __noinline__ bool small_stage_cols(const Ctx& cx, const GemmPhase* ph, int k0, int count, int mt, int wtid,
+                                              int nch, uint32_t stamp) {
   const KParams& p = *cx.p;
   const int per_token = count * 8;
   const int items = per_token * mt;
+  bool fresh = true;
 #pragma unroll 1
   for (int item = wtid; item < items; item += kSmallWorkers) {
     const int t = item / per_token, rem = item - t * per_token;
     const int col = (k0 + (rem >> 3)) * kChunkK + (rem & 7) * 8;
-    const uint4 u = (ph->bmode == B_ATTN) ? attention_vec(p, t, col, nch)
-                                          : __ldcg(reinterpret_cast<const uint4*>(activation_row(p, ph, t) + col));
     float f[8];
-    unpack8(u, f);
+    if (ph->ll_src != nullptr && ph->bmode == B_PLAIN) {
+      // stamped bf16 pairs written by the producing phase's epilogues: waiting for the stamps is the synchronisation
+      const unsigned long long* words = ph->ll_src + static_cast<size_t>(t) * ph->ll_src_ld + (col >> 1);
+      uint32_t pair[4];
+      stamped_payloads<4>(cx, words, stamp, fresh, pair);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(pair[i] << 16);
+        f[2 * i + 1] = __uint_as_float(pair[i] & 0xFFFF0000u);
+      }
+    } else if (ph->ll_src != nullptr) {
+      // stamped fp32 chunk partials of the attention phase, summed in chunk order and rounded once
+      const int head = col / p.head_dim, d = col - head * p.head_dim;
+      const unsigned long long* part = ph->ll_src + (static_cast<size_t>(t) * p.q_heads + head) * kMaxChunks * p.head_dim + d;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < nch; ++c) {
+        uint32_t bits[8];
+        stamped_payloads<8>(cx, part + c * p.head_dim, stamp, fresh, bits);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] += __uint_as_float(bits[e]);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = bf16_round(f[e]);
+    } else {
+      const uint4 u = (ph->bmode == B_ATTN) ? attention_vec(p, t, col, nch)
+                                            : __ldcg(reinterpret_cast<const uint4*>(activation_row(p, ph, t) + col));
+      unpack8(u, f);
+    }
     x_store(cx, t, rem >> 3, rem & 7, f);
   }
+  return fresh;
 }
 
 // Row sums of one unit wait in shared memory ([accumulator][row][token]) between the K loop and
@@ -198,10 +265,18 @@ __device__ __noinline__ void small_finish_row(const Ctx& cx, const GemmPhase* ph
     v[0][t] = sums[r * kSplitTokens + t];
     v[1][t] = sums[(kSmallTileRows + r) * kSplitTokens + t];
   }
-  if (ph->ll) {  // q/k/v of the small-launch table: the caller sends the rounded outputs as stamped words
-    const float bias = ph->bias[seg] ? ldg_bf16(ph->bias[seg] + n) : 0.f;
+  if (ph->ll) {  // q/k/v and gate/up of the small-launch table: the caller sends the rounded outputs as stamped words
+    if (ph->epi == EPI_SILU) {
 #pragma unroll
-    for (int t = 0; t < T; ++t) bits[t] = __bfloat16_as_ushort(__float2bfloat16_rn(v[0][t] + bias));
+      for (int t = 0; t < T; ++t) {
+        const float act = bf16_round(silu(bf16_round(v[0][t])));
+        bits[t] = __bfloat16_as_ushort(__float2bfloat16_rn(act * bf16_round(v[1][t])));
+      }
+    } else {
+      const float bias = ph->bias[seg] ? ldg_bf16(ph->bias[seg] + n) : 0.f;
+#pragma unroll
+      for (int t = 0; t < T; ++t) bits[t] = __bfloat16_as_ushort(__float2bfloat16_rn(v[0][t] + bias));
+    }
     return;
   }
   if (ph->epi == EPI_PARTIAL) {
@@ -251,7 +326,7 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
       if (per_unit || unit == cx.cta) {
         if (unit != cx.cta) small_sync();  // the previous unit has finished reading the operand
         if (ph->bmode == B_NORM) small_stage_norm(cx, ph, T, wtid, wu);
-        else small_stage_cols(cx, ph, slice * kslice, kslice, T, wtid, nch);
+        else ok = small_stage_cols(cx, ph, slice * kslice, kslice, T, wtid, nch, stamp) && ok;
         small_sync();
         if (unit == cx.cta) trace_event(cx, wtid, EV_B_STAGED);
       }
@@ -375,7 +450,7 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
           for (int t = 0; t < T; ++t) {
             const uint32_t other = __shfl_xor_sync(0xffffffffu, bits[t], 1);
             if (mine && !(wtid & 1))
-              st_relaxed_u64(cx.p->qkv_ll + static_cast<size_t>(t) * (cx.p->qkv_ld / 2) + (col >> 1),
+              st_relaxed_u64(ph->ll_dst + static_cast<size_t>(t) * ph->ll_ld + (col >> 1),
                              (static_cast<unsigned long long>(stamp) << 32) | (other << 16) | bits[t]);
           }
         }
@@ -405,6 +480,7 @@ __device__ __forceinline__ bool small_gemm_t(const Ctx& cx, int gp, SmallState& 
 // memory latency hides behind each of those steps.
 struct SmallAttn {
   const unsigned long long* ll;    // stamped q/k/v words [batch][qkv width / 2], or null: read the bf16 buffer
+  unsigned long long* out_ll;      // stamped fp32 chunk partials for the o projection, or null: att_part / out
   const bf16* q; int q_ld;         // [batch][q_heads * hd] inside the qkv row
   bf16 *k, *v;                     // caches [batch][capacity][kv_heads][hd]
   long long kv_bstride; int kv_ld;
@@ -718,7 +794,11 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
       for (int part = 1; part < parts; ++part) o += red[part * cols + col];
       const int g = col / hd, d = col - g * hd;
       const int head = kvh * gs + g;
-      if (nch == 1) {
+      if (A.out_ll != nullptr) {  // the o projection polls these words: no grid barrier in between
+        const size_t row = static_cast<size_t>(b) * p.q_heads + head;
+        st_relaxed_u64(A.out_ll + (row * kMaxChunks + ch) * hd + d,
+                       (static_cast<unsigned long long>(A.stamp) << 32) | __float_as_uint(o));
+      } else if (nch == 1) {
         A.out[static_cast<long long>(b) * A.out_ld + head * hd + d] = __float2bfloat16_rn(o);
       } else {
         const size_t row = static_cast<size_t>(b) * p.q_heads + head;
@@ -845,6 +925,7 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
   const int gs = p.q_heads / p.kv_heads;
   SmallAttn A;
   A.ll = nullptr;
+  A.out_ll = nullptr;
   A.q = p.qkv; A.q_ld = p.qkv_ld;
   A.knew = p.qkv + q_size; A.vnew = A.knew + kv_size; A.new_ld = p.qkv_ld;
   A.out = p.attn; A.out_ld = q_size;
@@ -898,6 +979,7 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
       // q/k/v travel as stamped words: attention starts as soon as this CTA's own tile is out and waits
       // word by word for the rows of its head; only the shared memory has to be handed over.
       A.ll = p.qkv_ll;
+      A.out_ll = p.att_ll;
       if (!small_ok(cx, ok)) return;
     } else if (!close(gp + 1)) {
       return;
@@ -910,15 +992,24 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
     if (!small_attention(cx, A, wtid, nch)) return;       // RoPE, KV append, split-context attention
     trace_event(cx, wtid, EV_ATTENTION_DONE);
     MK_SMALL_STEP();
-    if (!close(gp + 1)) return;
-    if (cx.cta == 0 && wtid == 0) *p.len[layer] = A.len + 1;  // publish after the interval closes
+    if (handoff) {
+      if (!small_ok(cx, ok)) return;         // the o projection polls the stamped attention partials
+    } else {
+      if (!close(gp + 1)) return;
+      if (cx.cta == 0 && wtid == 0) *p.len[layer] = A.len + 1;  // publish after the interval closes
+    }
     MK_SMALL_STEP();
     project(gp + 1, nch);                    // o_proj (fp32 K-slice partials)
     MK_SMALL_STEP();
     if (!close(gp + 2)) return;
+    if (handoff && cx.cta == 0 && wtid == 0) *p.len[layer] = A.len + 1;  // every attention unit is long done
     project(gp + 2, 1);                      // [residual update, RMSNorm] gate, up -> SiLU*up
     MK_SMALL_STEP();
-    if (!close(gp + 3)) return;
+    if (handoff) {
+      if (!small_ok(cx, ok)) return;         // the down projection polls the stamped activations
+    } else if (!close(gp + 3)) {
+      return;
+    }
     project(gp + 3, 1);                      // down (fp32 K-slice partials)
     MK_SMALL_STEP();
     {  // the barrier that closes the layer, with the next layer's cache prefetch between its halves

@@ -77,8 +77,11 @@ struct GemmPhase {
   int epi, bmode;
   int gather;                  // 1: activation rows are embedding rows selected by the token ids
   int to_logits;               // 1: output goes to the caller's logits buffer
-  int ll;                      // 1 (small-launch q/k/v phase): outputs leave as 64-bit words {bf16 pair, stamp} in
-                               // KParams::qkv_ll, which the attention phase polls instead of waiting at a grid barrier
+  int ll;                      // small-launch table: 1 = the bf16 outputs of this phase leave as 64-bit words
+                               // {stamp, bf16 pair} in ll_dst, which the consumer polls instead of waiting at a grid barrier
+  int ll_ld, ll_src_ld;        // words per token in ll_dst / ll_src
+  unsigned long long* ll_dst;
+  const unsigned long long* ll_src;  // B_PLAIN: the operand as stamped bf16 pairs; B_ATTN: attention partials as {stamp, fp32}
   int add_parts;               // B_NORM: fp32 partial slices of the previous projection to add to the residual
   const bf16* normw;
   const bf16* src; int src_ld; // activation source (B_NORM: the residual stream before this phase)
@@ -121,6 +124,7 @@ struct KParams {
   const GemmPhase* phases;
   bf16 *hidden_buf, *qkv, *attn, *act;
   unsigned long long* qkv_ll;  // [kSplitTokens][qkv width / 2]: stamped q/k/v outputs of the small-launch kernel
+  unsigned long long* att_ll;  // [kSplitTokens * q_heads][kMaxChunks][head_dim]: stamped attention partials {stamp, fp32}
   float* att_xch;     // [row groups][kMaxChunks][kExchangeFloats]
   float* att_part;    // [batch * q_heads][kMaxChunks][head_dim]
   Control* ctrl;

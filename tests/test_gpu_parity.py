@@ -214,7 +214,8 @@ def oracle_decode_compare(config, device, batch, capacity, prefill, steps, engin
 def test_decode_error_no_worse_than_eager_bf16(device):
     """The reference's own yardstick (tests/gpu/test_task31_full_model.py:205-211): measured
     against the same model evaluated in fp32, the kernel may be no further off than eager
-    bf16 on the same device times 1.25 plus 1e-3 -- logits and cache contents, 30 layers."""
+    bf16 on the same device times 1.25 plus 1e-3 in relative L2 (1.5 in the largest element
+    error, see assert_no_worse_than) -- logits and cache contents, 30 layers."""
     from oracle import decoder_oracle as oracle
 
     config = CONFIGS["smollm-135m"]
@@ -236,15 +237,12 @@ def test_decode_error_no_worse_than_eager_bf16(device):
             eager = oracle.decode_step(config, weights, tables, ids, positions, *eager_state)
             truth = oracle.decode_step(config, weights32, tables32, ids, positions, *truth_state)
         kernel.check()
-        mine_error = (mine.float() - truth).abs().max().item()
-        eager_error = (eager.float() - truth).abs().max().item()
-        assert mine_error <= 1.25 * eager_error + 1e-3, f"step {step}: logits {mine_error:.4g} vs eager {eager_error:.4g}"
+        assert_no_worse_than(mine, [eager], truth, f"step {step}: logits")
         ids = truth[:, 0].argmax(-1).view(batch, 1)
     for layer in (0, 15, 29):
-        for mine_cache, eager_cache, truth_cache in zip(mine_state[:2], eager_state[:2], truth_state[:2]):
-            mine_error = (mine_cache[layer].float() - truth_cache[layer]).abs().max().item()
-            eager_error = (eager_cache[layer].float() - truth_cache[layer]).abs().max().item()
-            assert mine_error <= 1.25 * eager_error + 1e-3, f"cache {layer}: {mine_error:.4g} vs eager {eager_error:.4g}"
+        for what, mine_cache, eager_cache, truth_cache in zip(("key", "value"), mine_state[:2], eager_state[:2], truth_state[:2]):
+            assert_no_worse_than(mine_cache[layer][:, :steps], [eager_cache[layer][:, :steps]], truth_cache[layer][:, :steps],
+                                 f"{what} cache {layer}")
 
 
 @pytest.mark.parametrize("engine", ["auto", "tcgen05"])
@@ -485,8 +483,8 @@ def test_event_trace_reports_every_phase(device, engine):
     codes, times = decode_trace(buffer)
     barriers = int((codes[0] == 5).sum())
     # five grid barriers per layer on the tensor engine; the small-launch kernel hands q/k/v to the
-    # attention phase as stamped words and needs four
-    assert barriers == (5 if engine == "tcgen05" else 4) * config.layers
+    # attention phase, attention partials to o_proj and activations to down_proj as stamped words: two are left
+    assert barriers == (5 if engine == "tcgen05" else 2) * config.layers
     stamps = times[0][codes[0] > 0][:barriers]
     assert bool((stamps[1:] >= stamps[:-1]).all())
     kernel.set_trace(0)
