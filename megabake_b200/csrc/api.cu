@@ -12,6 +12,7 @@
 #include <cstring>
 #include <mutex>
 #include <new>
+#include <algorithm>
 #include <vector>
 
 #include "decode_small.cuh"
@@ -39,7 +40,7 @@ int fail(int code, const char* fmt, ...) {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct Carve {
-  size_t ctrl, tmaps, phases, hidden, hidden2, qkv, qkv_ll, act_ll, att_ll, attn, act, partial, partial2, att_xch, att_part, total;
+  size_t ctrl, tmaps, phases, hidden, hidden2, qkv, qkv_ll, act_ll, att_ll, attn_ll, res_a, res_b, attn, act, partial, partial2, att_xch, att_part, total;
 };
 
 int qkv_width(const mk_config& c) { return (c.q_heads + 2 * c.kv_heads) * c.head_dim; }
@@ -57,13 +58,16 @@ Carve carve(const mk_config& c) {
   const size_t m = static_cast<size_t>(c.max_tokens);
   v.ctrl = take(sizeof(Control));
   v.tmaps = take(sizeof(CUtensorMap) * (3 * maps_per_table(c) + 1));    // split table, plain table, small-launch table, mk_linear
-  v.phases = take(sizeof(GemmPhase) * (3 * phases_per_table(c) + 1));
+  v.phases = take(sizeof(GemmPhase) * (4 * phases_per_table(c) + 1));  // + the one-token row table
   v.hidden = take(m * c.hidden * 2);
   v.hidden2 = take(static_cast<size_t>(kSplitTokens) * c.hidden * 2);
   v.qkv = take(m * qkv_width(c) * 2);
   v.qkv_ll = take(static_cast<size_t>(kSplitTokens) * qkv_width(c) * 4);
   v.act_ll = take(static_cast<size_t>(kSplitTokens) * c.intermediate * 4);
   v.att_ll = take(static_cast<size_t>(kSplitTokens) * c.q_heads * kMaxChunks * c.head_dim * 8);
+  v.attn_ll = take(static_cast<size_t>(kSplitTokens) * c.q_heads * c.head_dim * 4);
+  v.res_a = take(static_cast<size_t>(kSplitTokens) * c.hidden * 4);  // stamped residual stream after the MLP
+  v.res_b = take(static_cast<size_t>(kSplitTokens) * c.hidden * 4);  // ... and after attention
   v.attn = take(m * c.q_heads * c.head_dim * 2);
   v.act = take(m * c.intermediate * 2);
   v.partial = take(static_cast<size_t>(kMaxSplit) * kSplitTokens * c.hidden * 4);
@@ -144,6 +148,7 @@ struct mk_handle_s {
   long long timeout_cycles;
   float att_scale;
   bool fma_ok;  // the small-launch kernel can run the split-K table: every K slice fits its fp32 operand buffer
+  bool row_ok;    // the one-token row table (no K split, no per-layer grid barrier) is available
   bool small_ll;  // its q/k/v phases hand their outputs to attention as stamped words (one grid barrier fewer per layer)
   unsigned long long* trace;
   int trace_cap;
@@ -236,6 +241,7 @@ void base_params(mk_handle h, KParams& p) {
   p.act = at<bf16>(h, h->cv.act);
   p.qkv_ll = at<unsigned long long>(h, h->cv.qkv_ll);
   p.att_ll = at<unsigned long long>(h, h->cv.att_ll);
+  p.attn_ll = at<unsigned long long>(h, h->cv.attn_ll);
   p.att_xch = at<float>(h, h->cv.att_xch);
   p.att_part = at<float>(h, h->cv.att_part);
   p.ctrl = at<Control>(h, h->cv.ctrl);
@@ -369,7 +375,7 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
   const int q_size = c.q_heads * c.head_dim, kv_size = c.kv_heads * c.head_dim;
   const size_t nmaps = maps_per_table(c), nphases = phases_per_table(c);
   std::vector<CUtensorMap> maps(3 * nmaps);
-  std::vector<GemmPhase> phases(3 * nphases);
+  std::vector<GemmPhase> phases(4 * nphases);
   CUtensorMap* dmaps = at<CUtensorMap>(h, h->cv.tmaps);
   bf16* hidden_a = at<bf16>(h, h->cv.hidden);
   bf16* hidden_b = at<bf16>(h, h->cv.hidden2);
@@ -519,7 +525,8 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
     }
     if (!h->small_ll) continue;
     ph[0].ll = 1; ph[0].ll_dst = at<unsigned long long>(h, h->cv.qkv_ll); ph[0].ll_ld = qkv_width(c) / 2;
-    ph[1].ll_src = at<unsigned long long>(h, h->cv.att_ll);
+    // o_proj reads the attention output that the first chunk's CTA of every head combined and stamped as bf16 pairs
+    ph[1].ll_src = at<unsigned long long>(h, h->cv.attn_ll); ph[1].ll_src_ld = q_size / 2; ph[1].bmode = B_PLAIN;
     ph[2].ll = 1; ph[2].ll_dst = at<unsigned long long>(h, h->cv.act_ll); ph[2].ll_ld = c.intermediate / 2;
     ph[3].ll_src = at<unsigned long long>(h, h->cv.act_ll); ph[3].ll_src_ld = c.intermediate / 2;
     // with no barrier between attention and o_proj, nor gate/up and down, their partials need buffers of their own
@@ -527,6 +534,47 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
     if (l + 1 < L) ph[4].partial = at<float>(h, h->cv.partial2);
   }
   if (h->fma_ok && h->small_ll) phases[2 * nphases + 4 * L].partial = at<float>(h, h->cv.partial2);  // lm_head adds the last down-proj
+  // Table 3, one-token launches: o_proj and down_proj are not cut along K.  A CTA takes whole weight rows
+  // (contiguous in memory, fetched by one-dimensional bulk copies of up to 28 KB), adds the residual in its
+  // epilogue and stamps the new residual stream, which the next normalising phase polls: no fp32 partials,
+  // no grid barrier inside a layer.  The residual stream alternates between res_a (after the MLP) and res_b.
+  h->row_ok = h->small_ll && c.hidden % 2 == 0 && q_size * 2 <= kFatCopyBytes - 2048 && c.intermediate * 2 <= kFatCopyBytes - 2048 &&
+              c.intermediate <= kSplitTokens * kBSlots * kChunkK && q_size <= kSplitTokens * kBSlots * kChunkK;
+  if (h->row_ok) {
+    unsigned long long* res_a = at<unsigned long long>(h, h->cv.res_a);
+    unsigned long long* res_b = at<unsigned long long>(h, h->cv.res_b);
+    for (size_t i = 0; i < nphases; ++i) phases[3 * nphases + i] = phases[2 * nphases + i];
+    for (int l = 0; l <= L; ++l) {
+      GemmPhase* ph = phases.data() + 3 * nphases + 4 * l;
+      // normalising phases read the stamped residual stream (layer 0 still gathers embedding rows)
+      ph[0].add_parts = 0; ph[0].h_out = nullptr; ph[0].partial = nullptr;
+      ph[0].ll_src = ph[0].gather ? nullptr : res_a; ph[0].ll_src_ld = c.hidden / 2;
+      if (l == L) break;  // the lm_head phase
+      ph[2].add_parts = 0; ph[2].h_out = nullptr; ph[2].partial = nullptr;
+      ph[2].ll_src = res_b; ph[2].ll_src_ld = c.hidden / 2;
+      for (int which = 1; which <= 3; which += 2) {
+        GemmPhase& rp = ph[which];
+        rp.ksplit = 1; rp.kslice = rp.kc;
+        rp.rows = choose_rows(rp, h->grid, kSmallTileRows);
+        if (rp.rows & 1) rp.rows += 1;
+        rp.tile_start[0] = 0;
+        rp.ntiles = (rp.n[0] + rp.rows - 1) / rp.rows;
+        rp.tile_start[1] = rp.ntiles;
+        rp.nunits = rp.ntiles;
+        rp.bulk = 1;
+        const int row_bytes = rp.k * 2;
+        rp.rpc = std::max(1, std::min(8, (kFatCopyBytes - 2048) / row_bytes));
+        if (rp.rpc > rp.rows) rp.rpc = rp.rows;
+        rp.kb = 1;
+        rp.gran = (rp.rpc * row_bytes + kGranule - 1) / kGranule;
+        rp.epi = EPI_ROWRES; rp.partial = nullptr;
+        rp.ll = 1; rp.ll_ld = c.hidden / 2;
+        rp.res_src = (which == 1) ? res_a : res_b;   // layer 0's o_proj adds the embedding row (rp.gather below)
+        rp.ll_dst = (which == 1) ? res_b : res_a;
+        rp.gather = (which == 1 && l == 0) ? 1 : 0;
+      }
+    }
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   MK_CUDA(cudaMemcpyAsync(dmaps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, s));
   MK_CUDA(cudaMemcpyAsync(at<GemmPhase>(h, h->cv.phases), phases.data(), phases.size() * sizeof(GemmPhase),
@@ -572,6 +620,11 @@ int mk_decode(mk_handle h, const int64_t* ids, const int64_t* positions, int bat
   p.n_gemm = 4 * L + 1;
   p.nbar = 5 * L;
   if (small && h->small_ll) p.nbar = 2 * L;  // stamped hand-offs: only o_proj -> gate/up and down -> next layer keep a grid barrier
+  if (small && h->row_ok && batch == 1) {     // one token: the row table, a single grid barrier at the very end
+    p.phases = at<GemmPhase>(h, h->cv.phases) + 3 * phases_per_table(h->cfg);
+    p.nbar = 1;
+    p.rowmode = 1;
+  }
   p.stream_once = (ntt == 1);
   p.ids = reinterpret_cast<const long long*>(ids);
   p.pos = reinterpret_cast<const long long*>(positions);
@@ -617,7 +670,7 @@ int mk_linear(mk_handle h, const void* x, const void* weight, const void* bias, 
   if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(y) % 2)
     return fail(MK_ERR_ALIGNMENT, "mk_linear: x must be 16-byte aligned");
   CUtensorMap* dmap = at<CUtensorMap>(h, h->cv.tmaps) + 3 * maps_per_table(h->cfg);
-  GemmPhase* dphase = at<GemmPhase>(h, h->cv.phases) + 3 * phases_per_table(h->cfg);
+  GemmPhase* dphase = at<GemmPhase>(h, h->cv.phases) + 4 * phases_per_table(h->cfg);
   GemmPhase ph;
   memset(&ph, 0, sizeof(ph));
   ph.nseg = 1; ph.nacc = 1; ph.k = k;
@@ -847,7 +900,7 @@ int mk_kv_attention_static(int q_heads, int kv_heads, int head_dim, const void* 
   view.epoch = slot.epoch; view.att_epoch = slot.att_epoch; view.launches = slot.launches;
   view.timeout_cycles = slot.timeout_cycles;
   view.att_scale = static_cast<float>(std::pow(static_cast<double>(head_dim), -0.5));
-  view.fma_ok = false; view.small_ll = false; view.trace = nullptr; view.trace_cap = 0;
+  view.fma_ok = false; view.small_ll = false; view.row_ok = false; view.trace = nullptr; view.trace_cap = 0;
   if (int e = attention_fits(&view, capacity, "mk_kv_attention_static")) return e;
   KParams p;
   base_params(&view, p);

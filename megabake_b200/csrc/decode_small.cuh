@@ -113,6 +113,7 @@ __device__ __forceinline__ void stamped_payloads(const Ctx& cx, const unsigned l
       out[i] = static_cast<uint32_t>(w[i]);
     }
     if (all) return;
+    __nanosleep(128);  // hundreds of CTAs poll the same lines: leave the L2 to the producers' stores
     if ((++spins & 255u) == 0 && give_up(cx, SITE_ATT_EXCHANGE, -1)) {
       fresh = false;
       return;
@@ -139,19 +140,30 @@ __device__ __forceinline__ void x_store(const Ctx& cx, int t, int chunk, int vec
 // residual stream, and normalises x with the two roundings of the Hugging Face
 // RMSNorm.  `wu` is this thread's vector of the norm weight, loaded by the
 // caller before the grid barrier opened.
-__device__ __noinline__ void small_stage_norm(const Ctx& cx, const GemmPhase* ph, int mt, int wtid, uint4 wu) {
+__device__ __noinline__ bool small_stage_norm(const Ctx& cx, const GemmPhase* ph, int mt, int wtid, uint4 wu, uint32_t stamp) {
   const KParams& p = *cx.p;
   const int warp = wtid >> 5, lane = wtid & 31;
   const int nvec = ph->k / 8;
   const int parts = ph->add_parts;
   const int writers = min(cx.grid, ph->nunits);
   const bool active = wtid < nvec;
+  bool fresh = true;
   float w[8];
   unpack8(wu, w);
   for (int t = 0; t < mt; ++t) {
     float f[8];
     uint4 xu = make_uint4(0, 0, 0, 0);
-    if (active) {
+    if (active && ph->ll_src != nullptr) {
+      // the residual stream as stamped bf16 pairs (one-token row table): waiting for the stamps of the
+      // previous projection's epilogues replaces the grid barrier; nothing is added, nothing written back
+      uint32_t pair[4];
+      stamped_payloads<4>(cx, ph->ll_src + static_cast<size_t>(t) * ph->ll_src_ld + wtid * 4, stamp, fresh, pair);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(pair[i] << 16);
+        f[2 * i + 1] = __uint_as_float(pair[i] & 0xFFFF0000u);
+      }
+    } else if (active) {
       const uint4* row = reinterpret_cast<const uint4*>(activation_row(p, ph, t));
       xu = __ldcg(row + wtid);
       float4 lo[kMaxSplit], hi[kMaxSplit];
@@ -199,6 +211,7 @@ __device__ __noinline__ void small_stage_norm(const Ctx& cx, const GemmPhase* ph
       x_store(cx, t, wtid >> 3, wtid & 7, f);
     }
   }
+  return fresh;
 }
 
 // Plain or attention-output operand: K chunks [k0, k0 + count) of every token.  One vector per
@@ -265,8 +278,20 @@ __device__ __noinline__ void small_finish_row(const Ctx& cx, const GemmPhase* ph
     v[0][t] = sums[r * kSplitTokens + t];
     v[1][t] = sums[(kSmallTileRows + r) * kSplitTokens + t];
   }
-  if (ph->ll) {  // q/k/v and gate/up of the small-launch table: the caller sends the rounded outputs as stamped words
-    if (ph->epi == EPI_SILU) {
+  if (ph->ll) {  // the caller sends the rounded outputs as stamped words
+    if (ph->epi == EPI_ROWRES) {  // new residual = residual + bf16(projection)
+#pragma unroll
+      for (int t = 0; t < T; ++t) {
+        float old;
+        if (ph->gather) {
+          old = ldg_bf16(activation_row(*cx.p, ph, t) + n);
+        } else {
+          const uint32_t pair = static_cast<uint32_t>(ld_relaxed_u64(ph->res_src + static_cast<size_t>(t) * ph->ll_ld + (n >> 1)));
+          old = __uint_as_float((n & 1) ? (pair & 0xFFFF0000u) : (pair << 16));
+        }
+        bits[t] = __bfloat16_as_ushort(__float2bfloat16_rn(old + bf16_round(v[0][t])));
+      }
+    } else if (ph->epi == EPI_SILU) {
 #pragma unroll
       for (int t = 0; t < T; ++t) {
         const float act = bf16_round(silu(bf16_round(v[0][t])));
@@ -325,7 +350,8 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
       const int tile = unit / ksplit, slice = unit - tile * ksplit;
       if (per_unit || unit == cx.cta) {
         if (unit != cx.cta) small_sync();  // the previous unit has finished reading the operand
-        if (ph->bmode == B_NORM) small_stage_norm(cx, ph, T, wtid, wu);
+        // a normalising phase that opens a layer (or the lm_head) reads what the previous layer stamped
+        if (ph->bmode == B_NORM) ok = small_stage_norm(cx, ph, T, wtid, wu, (gp & 3) == 0 ? stamp - 1u : stamp) && ok;
         else ok = small_stage_cols(cx, ph, slice * kslice, kslice, T, wtid, nch, stamp) && ok;
         small_sync();
         if (unit == cx.cta) trace_event(cx, wtid, EV_B_STAGED);
@@ -463,9 +489,110 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
   return ok;
 }
 
+// One-token projection whose tile is `rows` whole weight rows fetched as contiguous bytes (o_proj and
+// down_proj of the row table).  The 256 consumer threads split a row: thread t owns the 8-element
+// vectors t, t + 256, ... of every row and keeps its activation values in registers for the whole
+// tile; a copy brings 1-8 rows; per row one fp32 chain per thread, a warp shuffle tree, and the
+// eight warp sums are added in warp order by the thread that finishes the row.
+__device__ __noinline__ bool small_gemm_rows(const Ctx& cx, int gp, SmallState& st, int wtid, int nch, uint32_t stamp) {
+  const GemmPhase* ph = &cx.misc->phase[gp & 1];
+  const int nunits = ph->nunits, rows = ph->rows, gran = ph->gran, rpc = ph->rpc, kc = ph->kc;
+  const int warp = wtid >> 5, lane = wtid & 31;
+  const int kvecs = ph->k / 8;
+  const uint32_t ring_base = smem_u32(cx.smem_a);
+  const uint32_t row_bytes = static_cast<uint32_t>(ph->k) * 2u;
+  float* sums = reinterpret_cast<float*>(cx.smem_b + kRowSumOffset);   // [row][warp] here
+  int head = st.head, seq = st.seq;
+  bool ok = true;
+  if (cx.cta < nunits) {
+    trace_event(cx, wtid, EV_PHASE_ENTER);
+#pragma unroll 1
+    for (int unit = cx.cta; unit < nunits; unit += cx.grid) {
+      if (unit != cx.cta) small_sync();
+      ok = small_stage_cols(cx, ph, 0, kc, 1, wtid, nch, stamp) && ok;
+      small_sync();
+      if (unit == cx.cta) trace_event(cx, wtid, EV_B_STAGED);
+      const int row0 = unit * rows;
+      const int tile_rows = min(rows, ph->n[0] - row0);
+      float xr[4][8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int v = wtid + j * kSmallWorkers;
+        if (v < kvecs) {
+          const float* src = reinterpret_cast<const float*>(cx.smem_b) + (v >> 3) * kChunkK + (v & 7) * 4;
+          const float4 lo = *reinterpret_cast<const float4*>(src), hi = *reinterpret_cast<const float4*>(src + 32);
+          xr[j][0] = lo.x; xr[j][1] = lo.y; xr[j][2] = lo.z; xr[j][3] = lo.w;
+          xr[j][4] = hi.x; xr[j][5] = hi.y; xr[j][6] = hi.z; xr[j][7] = hi.w;
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) xr[j][e] = 0.f;
+        }
+      }
+#pragma unroll 1
+      for (int r0 = 0; r0 < tile_rows; r0 += rpc) {
+        if (head + gran > kSmallRingGranules) head = 0;
+        const uint32_t base = ring_base + head * kGranule + (wtid << 4);
+        head += gran;
+        const uint32_t bar = seq % kChunkBars;
+        const bool got = ok && wait_mbar(cx, smem_u32(&cx.misc->full[bar]), (seq / kChunkBars) & 1, SITE_MMA_FULL, gp);
+        ok = __all_sync(0xffffffffu, got);
+        const int count = min(rpc, tile_rows - r0);
+#pragma unroll 1
+        for (int r = 0; r < count; ++r) {
+          float acc = 0.f;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (wtid + j * kSmallWorkers < kvecs) {
+              float wf[8];
+              unpack8(lds_v4(base + r * row_bytes + j * (kSmallWorkers * 16)), wf);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) acc = fmaf(wf[e], xr[j][e], acc);
+            }
+          }
+          acc = warp_sum(acc);
+          if (lane == 0) sums[(r0 + r) * kSmallWarps + warp] = acc;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&cx.misc->empty[bar]));
+        seq += 1;
+      }
+      if (unit == cx.cta) trace_event(cx, wtid, EV_FIRST_ACC);
+      small_sync();
+      {
+        const bool mine = wtid < tile_rows;
+        uint32_t bits = 0u;
+        if (mine) {
+          float y = sums[wtid * kSmallWarps];
+#pragma unroll
+          for (int w8 = 1; w8 < kSmallWarps; ++w8) y += sums[wtid * kSmallWarps + w8];
+          const int n = row0 + wtid;
+          float old;
+          if (ph->gather) {
+            old = ldg_bf16(activation_row(*cx.p, ph, 0) + n);
+          } else {
+            const uint32_t pair = static_cast<uint32_t>(ld_relaxed_u64(ph->res_src + (n >> 1)));
+            old = __uint_as_float((n & 1) ? (pair & 0xFFFF0000u) : (pair << 16));
+          }
+          bits = __bfloat16_as_ushort(__float2bfloat16_rn(old + bf16_round(y)));
+        }
+        const uint32_t other = __shfl_xor_sync(0xffffffffu, bits, 1);
+        if (mine && !(wtid & 1))
+          st_relaxed_u64(ph->ll_dst + ((row0 + wtid) >> 1), (static_cast<unsigned long long>(stamp) << 32) | (other << 16) | bits);
+      }
+    }
+    trace_event(cx, wtid, EV_PHASE_DONE);
+  }
+  st.head = head;
+  st.seq = seq;
+  return ok;
+}
+
 template <int T>
 __device__ __forceinline__ bool small_gemm_t(const Ctx& cx, int gp, SmallState& st, int wtid, uint4 wu, int nch,
                                              uint32_t stamp) {
+  if constexpr (T == 1) {
+    if (cx.misc->phase[gp & 1].bulk) return small_gemm_rows(cx, gp, st, wtid, nch, stamp);
+  }
   return cx.misc->phase[gp & 1].nacc == 2 ? small_gemm<T, 2>(cx, gp, st, wtid, wu, nch, stamp)
                                           : small_gemm<T, 1>(cx, gp, st, wtid, wu, nch, stamp);
 }
@@ -480,7 +607,8 @@ __device__ __forceinline__ bool small_gemm_t(const Ctx& cx, int gp, SmallState& 
 // memory latency hides behind each of those steps.
 struct SmallAttn {
   const unsigned long long* ll;    // stamped q/k/v words [batch][qkv width / 2], or null: read the bf16 buffer
-  unsigned long long* out_ll;      // stamped fp32 chunk partials for the o projection, or null: att_part / out
+  unsigned long long* out_ll;      // stamped fp32 chunk partials {stamp, fp32}, or null: att_part / out
+  unsigned long long* out_pairs;   // with out_ll: the combined output as stamped bf16 pairs [batch][q_heads * hd / 2]
   const bf16* q; int q_ld;         // [batch][q_heads * hd] inside the qkv row
   bf16 *k, *v;                     // caches [batch][capacity][kv_heads][hd]
   long long kv_bstride; int kv_ld;
@@ -805,6 +933,30 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
         __stcg(p.att_part + (row * kMaxChunks + ch) * hd + d, o);
       }
     }
+    if (A.out_ll != nullptr && ch == 0) {
+      // The first chunk's CTA adds the chunk partials of its heads in chunk order, rounds once and stamps the
+      // result as bf16 pairs: the o projection then reads 4 bytes per output instead of 8 per chunk and output.
+      bool fresh = true;
+#pragma unroll 1
+      for (int col0 = 0; col0 < cols; col0 += kSmallWorkers) {
+        const int col = col0 + wtid;
+        uint32_t bits = 0u;
+        if (col < cols) {
+          const int g = col / hd, d = col - g * hd;
+          const size_t row = static_cast<size_t>(b) * p.q_heads + kvh * gs + g;
+          float o = 0.f;
+#pragma unroll 1
+          for (int c = 0; c < nch; ++c)
+            o += __uint_as_float(stamped_payload(cx, A.out_ll + (row * kMaxChunks + c) * hd + d, A.stamp, fresh));
+          bits = __bfloat16_as_ushort(__float2bfloat16_rn(o));
+        }
+        const uint32_t other = __shfl_xor_sync(0xffffffffu, bits, 1);
+        if (col < cols && !(col & 1))
+          st_relaxed_u64(A.out_pairs + static_cast<size_t>(b) * (p.q_heads * hd / 2) + ((kvh * gs * hd + col) >> 1),
+                         (static_cast<unsigned long long>(A.stamp) << 32) | (other << 16) | bits);
+      }
+      if (!small_ok(cx, fresh)) return false;
+    }
   }
   return true;
 }
@@ -832,8 +984,10 @@ __device__ __noinline__ void small_producer(const Ctx& cx) {
       tile_origin(ph, tile, seg, row0);
       const int kbase = slice * kslice;
       int k = rot;
+      const int tile_rows = min(ph->rows, ph->n[seg] - row0);
+      const int steps = ph->bulk ? (tile_rows + ph->rpc - 1) / ph->rpc * kb : kslice * nacc;  // bulk: one step per copy
 #pragma unroll 1
-      for (int i = 0; i < kslice * nacc && ok; i += kb) {
+      for (int i = 0; i < steps && ok; i += kb) {
         const int a = (nacc == 2) ? ((i / kb) & 1) : 0;  // gate and up copies alternate
         const CUtensorMap* map = ph->tmap[nacc == 2 ? a : seg];
         // Copies are consumed in issue order, so ring space is reclaimed by retiring the oldest copy in
@@ -864,8 +1018,16 @@ __device__ __noinline__ void small_producer(const Ctx& cx) {
         misc->qstart[seq % kChunkBars] = static_cast<uint8_t>(start);
         misc->qgran[seq % kChunkBars] = static_cast<uint8_t>(gran);
         const uint32_t full = smem_u32(&misc->full[seq % kChunkBars]);
-        mbar_expect_tx(full, bytes);
-        tma_load_2d(smem_u32(cx.smem_a + start * kGranule), map, (kbase + k) * kChunkK, row0, full, policy);
+        if (ph->bulk) {  // rows [r, r + count) of the tile: whole rows, contiguous in memory
+          const int r = i * ph->rpc, count = min(ph->rpc, tile_rows - r);
+          const uint32_t copy_bytes = static_cast<uint32_t>(count) * static_cast<uint32_t>(ph->k) * 2u;
+          mbar_expect_tx(full, copy_bytes);
+          bulk_load_1d(smem_u32(cx.smem_a + start * kGranule), ph->w[seg] + static_cast<size_t>(row0 + r) * ph->k, copy_bytes, full,
+                       policy);
+        } else {
+          mbar_expect_tx(full, bytes);
+          tma_load_2d(smem_u32(cx.smem_a + start * kGranule), map, (kbase + k) * kChunkK, row0, full, policy);
+        }
         ++seq;
         if (nacc == 1 || a == 1) {
           k += kb;
@@ -926,6 +1088,7 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
   SmallAttn A;
   A.ll = nullptr;
   A.out_ll = nullptr;
+  A.out_pairs = nullptr;
   A.q = p.qkv; A.q_ld = p.qkv_ld;
   A.knew = p.qkv + q_size; A.vnew = A.knew + kv_size; A.new_ld = p.qkv_ld;
   A.out = p.attn; A.out_ld = q_size;
@@ -970,6 +1133,43 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
     }
   };
   prefetch_kv(0);
+  if (p.rowmode) {
+    // One-token row table: every hand-off between phases travels as stamped words, so a layer needs no grid
+    // barrier; block barriers only pass the shared memory from one phase to the next.
+#pragma unroll 1
+    for (int layer = 0; layer < p.layers; ++layer) {
+      const int gp = layer * 4;
+      project(gp, 1);                        // [RMSNorm of the stamped residual] q, k, v (+bias)
+      if (!small_ok(cx, ok)) return;
+      A.ll = p.qkv_ll;
+      A.out_ll = p.att_ll;
+      A.out_pairs = p.attn_ll;
+      A.k = static_cast<bf16*>(p.kc[layer]); A.v = static_cast<bf16*>(p.vc[layer]);
+      A.len = cx.misc->len_s[layer];
+      A.stamp = p.att_epoch + static_cast<uint32_t>(layer) + 1u;
+      const int nch = decode_chunks(A.len + 1, p.batch * p.kv_heads, cx.grid, gs, kAttScoreBytes);
+      if (!small_attention(cx, A, wtid, nch)) return;
+      trace_event(cx, wtid, EV_ATTENTION_DONE);
+      if (!small_ok(cx, ok)) return;
+      project(gp + 1, nch);                  // o_proj rows + residual -> stamped residual
+      if (!small_ok(cx, ok)) return;
+      wu = small_norm_weight(cx, gp + 2, wtid);
+      project(gp + 2, 1);                    // [RMSNorm] gate, up -> SiLU*up, stamped
+      if (!small_ok(cx, ok)) return;
+      project(gp + 3, 1);                    // down rows + residual -> stamped residual
+      prefetch_kv(layer + 1);
+      if (!small_ok(cx, ok)) return;
+      wu = small_norm_weight(cx, gp + 4, wtid);
+    }
+    project(p.layers * 4, 1);                // [final RMSNorm] lm_head
+    // the only grid barrier: every CTA has read the valid lengths (in its prologue) before they move on
+    if (!ok) cx.misc->wabort = 1;
+    small_arrive(cx, st, wtid);
+    if (!small_wait(cx, st, wtid)) return;
+    if (cx.cta == 0)
+      for (int layer = wtid; layer < p.layers; layer += kSmallWorkers) *p.len[layer] = cx.misc->len_s[layer] + 1;
+    return;
+  }
   for (int layer = 0; layer < p.layers; ++layer) {
     const int gp = layer * 4;
     const bool handoff = cx.misc->phase[gp & 1].ll != 0;  // same for every layer and CTA
@@ -980,6 +1180,7 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
       // word by word for the rows of its head; only the shared memory has to be handed over.
       A.ll = p.qkv_ll;
       A.out_ll = p.att_ll;
+      A.out_pairs = p.attn_ll;
       if (!small_ok(cx, ok)) return;
     } else if (!close(gp + 1)) {
       return;

@@ -40,7 +40,7 @@ constexpr int kSplitTokens = 4;          // launches with at most this many toke
 
 static_assert(kSmemBytes <= 200704, "dynamic shared memory exceeds the 196 KiB carve-out");
 
-enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU = 2, EPI_PARTIAL = 3 };
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU = 2, EPI_PARTIAL = 3, EPI_ROWRES = 4 };
 enum { B_PLAIN = 0, B_NORM = 1, B_ATTN = 2 };
 enum { MODE_DECODE = 0, MODE_PREFILL = 1, MODE_LINEAR = 2, MODE_KVATT = 3, MODE_ATT = 4 };
 enum { EV_PHASE_ENTER = 1, EV_B_STAGED = 2, EV_FIRST_ACC = 3, EV_PHASE_DONE = 4, EV_BARRIER_DONE = 5, EV_ATTENTION_DONE = 6 };
@@ -81,7 +81,10 @@ struct GemmPhase {
                                // {stamp, bf16 pair} in ll_dst, which the consumer polls instead of waiting at a grid barrier
   int ll_ld, ll_src_ld;        // words per token in ll_dst / ll_src
   unsigned long long* ll_dst;
-  const unsigned long long* ll_src;  // B_PLAIN: the operand as stamped bf16 pairs; B_ATTN: attention partials as {stamp, fp32}
+  const unsigned long long* ll_src;  // B_PLAIN / B_NORM: the operand as stamped bf16 pairs; B_ATTN: attention partials as {stamp, fp32}
+  int bulk;                    // one-token row table: 1 = a tile is `rows` whole weight rows, contiguous in memory, fetched by
+  int rpc;                     // one-dimensional bulk copies of `rpc` rows; the epilogue (EPI_ROWRES) adds the residual it
+  const unsigned long long* res_src;  // reads as stamped pairs from res_src (or the embedding row when `gather`) and stamps the sum into ll_dst
   int add_parts;               // B_NORM: fp32 partial slices of the previous projection to add to the residual
   const bf16* normw;
   const bf16* src; int src_ld; // activation source (B_NORM: the residual stream before this phase)
@@ -117,6 +120,7 @@ struct KParams {
   int max_positions;
   int stream_once;    // 1: weights are read once per launch (L2 evict-first)
   int split;          // 1: this launch runs the split-K phase table (residual updates applied by the consumer)
+  int rowmode;        // 1: one-token row table: stamped hand-offs everywhere, one grid barrier at the end of the launch
   int debug_stop;     // bring-up aid: leave the schedule after this many steps (0 = run everything)
   int trace_cap;      // events per CTA in `trace` (0 = tracing off)
   unsigned long long* trace;  // [grid][trace_cap] (event code << 56) | %globaltimer ns
@@ -125,6 +129,7 @@ struct KParams {
   bf16 *hidden_buf, *qkv, *attn, *act;
   unsigned long long* qkv_ll;  // [kSplitTokens][qkv width / 2]: stamped q/k/v outputs of the small-launch kernel
   unsigned long long* att_ll;  // [kSplitTokens * q_heads][kMaxChunks][head_dim]: stamped attention partials {stamp, fp32}
+  unsigned long long* attn_ll; // [kSplitTokens][q_heads * head_dim / 2]: the combined attention output as stamped bf16 pairs
   float* att_xch;     // [row groups][kMaxChunks][kExchangeFloats]
   float* att_part;    // [batch * q_heads][kMaxChunks][head_dim]
   Control* ctrl;

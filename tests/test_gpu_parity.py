@@ -482,9 +482,9 @@ def test_event_trace_reports_every_phase(device, engine):
     kernel.check()
     codes, times = decode_trace(buffer)
     barriers = int((codes[0] == 5).sum())
-    # five grid barriers per layer on the tensor engine; the small-launch kernel hands q/k/v to the
-    # attention phase, attention partials to o_proj and activations to down_proj as stamped words: two are left
-    assert barriers == (5 if engine == "tcgen05" else 2) * config.layers
+    # five grid barriers per layer on the tensor engine; the small-launch kernel at one token hands every
+    # phase's outputs to the next as stamped words and keeps a single barrier at the end of the launch
+    assert barriers == (5 * config.layers if engine == "tcgen05" else 1)
     stamps = times[0][codes[0] > 0][:barriers]
     assert bool((stamps[1:] >= stamps[:-1]).all())
     kernel.set_trace(0)
