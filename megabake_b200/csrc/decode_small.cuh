@@ -537,60 +537,20 @@ __device__ __noinline__ bool small_gemm_rows(const Ctx& cx, int gp, SmallState& 
         const bool got = ok && wait_mbar(cx, smem_u32(&cx.misc->full[bar]), (seq / kChunkBars) & 1, SITE_MMA_FULL, gp);
         ok = __all_sync(0xffffffffu, got);
         const int count = min(rpc, tile_rows - r0);
-        if (rpc > 1) {
-          // several short rows per copy: independent chains for up to eight rows, then the butterfly that
-          // halves the rows a lane carries at each exchange (lane l with (l & 3) == 0 ends with row bits 4, 3, 2 of l)
-          float v[8];
-#pragma unroll
-          for (int r = 0; r < 8; ++r) {
-            v[r] = 0.f;
-            if (r < count) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                if (wtid + j * kSmallWorkers < kvecs) {
-                  float wf[8];
-                  unpack8(lds_v4(base + r * row_bytes + j * (kSmallWorkers * 16)), wf);
-#pragma unroll
-                  for (int e = 0; e < 8; ++e) v[r] = fmaf(wf[e], xr[j][e], v[r]);
-                }
-              }
-            }
-          }
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const bool up = lane & 16;
-            const float send = up ? v[i] : v[i + 4], keep = up ? v[i + 4] : v[i];
-            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
-          }
-#pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            const bool up = lane & 8;
-            const float send = up ? v[i] : v[i + 2], keep = up ? v[i + 2] : v[i];
-            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
-          }
-          {
-            const bool up = lane & 4;
-            const float send = up ? v[0] : v[1], keep = up ? v[1] : v[0];
-            v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
-          }
-          v[0] += __shfl_xor_sync(0xffffffffu, v[0], 2);
-          v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1);
-          const int r = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
-          if ((lane & 3) == 0 && r < count) sums[(r0 + r) * kSmallWarps + warp] = v[0];
-        } else {
-          // one long row per copy: four chains (one per vector of the thread), one shuffle tree
-          float a4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+        for (int r = 0; r < count; ++r) {
+          float acc = 0.f;
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             if (wtid + j * kSmallWorkers < kvecs) {
               float wf[8];
-              unpack8(lds_v4(base + j * (kSmallWorkers * 16)), wf);
+              unpack8(lds_v4(base + r * row_bytes + j * (kSmallWorkers * 16)), wf);
 #pragma unroll
-              for (int e = 0; e < 8; ++e) a4[j] = fmaf(wf[e], xr[j][e], a4[j]);
+              for (int e = 0; e < 8; ++e) acc = fmaf(wf[e], xr[j][e], acc);
             }
           }
-          const float acc = warp_sum((a4[0] + a4[1]) + (a4[2] + a4[3]));
-          if (lane == 0) sums[r0 * kSmallWarps + warp] = acc;
+          acc = warp_sum(acc);
+          if (lane == 0) sums[(r0 + r) * kSmallWarps + warp] = acc;
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&cx.misc->empty[bar]));
