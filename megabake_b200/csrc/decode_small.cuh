@@ -1,22 +1,31 @@
 // The decode megakernel for launches of at most four tokens (batch-1 decode is
-// the case that matters): same phase tables, weight ring, TMA producer and
-// consumer-side split-K reduction as mk::megakernel, but the weight tiles are
-// consumed by CUDA-core FMAs.
+// the case that matters).  Same phase tables, status protocol and bounded waits
+// as mk::megakernel, but the weights are consumed by CUDA-core FMAs.
 //
 // Why not the tensor core here: one tcgen05.mma of 128 weight rows by 16 token
 // columns occupies the tensor pipe for ~78 cycles whatever the token count and
 // however few of the 128 rows hold weights (an even split of a projection over
-// 148 CTAs wants tiles of 42-56 rows), which capped a CTA at 6-12 bytes of
+// 148 CTAs wants tiles of 14-56 rows), which capped a CTA at 6-12 bytes of
 // weights per cycle where HBM can deliver 22.  A matrix-vector product needs
-// one FMA per weight and token: eight consumer warps read the TMA-filled ring
-// slots with 16-byte shared loads (eight lanes share a weight row, 32 rows per
-// pass), which is about 80 issue slots per 7 KB chunk and token.
+// one FMA per weight and token.
 //
-// Roles: warp 0 = TMA producer (mk::producer_loop, unchanged), warps 1-8 =
-// consumers (operand staging with the RMSNorm and the pending residual update
-// fused in, FMA projection, epilogue, decode attention, grid barriers).  No
-// TMEM, no MMA warp.  Everything that can be fetched before a grid barrier
-// opens (phase descriptor, norm weights, K rows of the cache) is fetched there.
+// Roles: warp 0 = TMA producer (small_producer), warps 1-8 = consumers (operand
+// staging with the RMSNorm fused in, FMA projection, epilogue, decode attention).
+// No TMEM, no MMA warp.
+//
+// Weight copies are 14-28 KB each (plain rows of up to 256 K-elements through a
+// 2-D tensor map, or whole contiguous rows through a 1-D bulk copy): an SM's copy
+// engine retires about three copies per microsecond whatever their size.  The
+// lanes of a warp split the K range of a copy and keep their activation values
+// in registers; a thread holds one fp32 chain per (row, lane).
+//
+// Phases hand their outputs over as 64-bit words {stamp, payload} that the
+// consumer's staging polls (stamped_payloads): a reader that sees the stamp has
+// the data, so no fence and no grid barrier is needed, and a consumer starts as
+// soon as its own producers are done.  One-token launches run the "row table"
+// (o_proj and down_proj uncut along K, residual stream stamped) with a single
+// grid barrier per launch; two to four tokens keep the split-K table with two
+// grid barriers per layer.
 #pragma once
 #include "decoder_kernel.cuh"
 
