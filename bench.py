@@ -39,7 +39,7 @@ from megabake_b200.synth import CONFIGS, new_kv_state, synth_ids, synth_normal, 
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
 # profiles/megakernel_decode_smollm-1.7b_launch_list.md (mean of the two captured launches).
-NCU_TRAFFIC = {("smollm-1.7b", 1, 1024): 3_638_545_216}
+NCU_TRAFFIC = {("smollm-1.7b", 1, 1024): 3_640_695_296}
 
 
 def parse_args():
