@@ -634,11 +634,6 @@ constexpr int kAttTileBytes = 38 * 1024;    // one tile of cached K (then V) row
 constexpr int kAttScratchBytes = 10 * 1024; // q, cross-warp sums, new key/value, statistics
 static_assert(kAttScoreBytes + kAttTileBytes + kAttScratchBytes <= kBBytes, "attention scratch exceeds its region");
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
-
 // Code size matters here: every instruction of this function runs a handful of times per
 // layer, so it is written as short loops (an unrolled version measured 128 KB of code and spent
 // its time fetching instructions).  Rows of the cache go to shared memory with cp.async: no

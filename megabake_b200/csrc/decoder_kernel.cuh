@@ -983,6 +983,328 @@ __device__ __forceinline__ int decode_chunks(int keys, int rows, int grid, int g
   return nch;
 }
 
+// Decode attention (one query token per sequence) as a stream of cache tiles.
+// A unit is one (sequence, kv head, context chunk).  Its K rows and then its V
+// rows travel through three shared-memory stages with cp.async: while the
+// workers take the scores (or the value sums) of one tile, the next two tiles
+// are in flight, so a CTA keeps tens of kilobytes of the cache outstanding for
+// the whole unit instead of one register-load round trip per 128 keys.  The
+// new position's key/value row is not in the cache yet: it is patched into its
+// tile from shared memory.  Arithmetic and rounding points are those described
+// above attention_phase for decode; the exchange of the chunk statistics and
+// the hand-over of the chunk partials are the same protocol as there.
+constexpr int kDecStages = 3;
+constexpr int kDecScratchBytes = 10 * 1024;  // q [8][128] fp32, value partial sums [1024] fp32, new key/value, statistics
+constexpr int kDecTileBytes = 16 * 1024;     // upper bound of one stage
+static_assert(kScoreBytes + kDecScratchBytes + kDecStages * 256 <= kBBytes, "no room for one cache row per stage");
+
+// Copy `count` rows of head_dim bf16 (row stride ld elements) into a stage, except row `skip`.
+// Piece p of row r lands at piece p ^ (r & 7), so that a column of pieces spreads over all banks.
+__device__ __noinline__ void fetch_cache_tile(uint32_t dst, const bf16* src, int ld, int count, int skip, int hd, int wtid) {
+  const int shift = (hd == 64) ? 3 : 4;  // 16-byte pieces per row: 8 or 16
+  const int total = count << shift;
+#pragma unroll 2
+  for (int it = wtid; it < total; it += kWorkers) {
+    const int key = it >> shift, piece = it & ((1 << shift) - 1);
+    if (key != skip)
+      cp_async16(dst + key * hd * 2 + ((piece ^ (key & 7)) << 4),
+                 reinterpret_cast<const uint4*>(src + static_cast<long long>(key) * ld) + piece);
+  }
+}
+
+__device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, int wtid) {
+  const KParams& p = *cx.p;
+  const int hd = p.head_dim, half = hd / 2;
+  const int gs = p.q_heads / p.kv_heads;
+  const int rows = p.batch * p.kv_heads;
+  const int n_max = A.len + 1;
+  const int warp = wtid >> 5, lane = wtid & 31;
+  const int lpk = hd / 8;  // 16-byte pieces per cache row
+  const int nch = decode_chunks(n_max, rows, cx.grid, gs);
+  const int chunk = (n_max + nch - 1) / nch;
+  const int units = rows * nch;
+  const int row_bytes = hd * 2;
+  const int score_bytes = (gs * chunk * 4 + 15) & ~15;  // <= kScoreBytes by the choice of nch
+  const int tile_keys = min(kDecTileBytes, (kBBytes - kDecScratchBytes - score_bytes) / kDecStages) / row_bytes;
+  const int stage_bytes = tile_keys * row_bytes;
+
+  float* sc = reinterpret_cast<float*>(cx.smem_b);                                      // [gs][chunk]
+  uint8_t* tiles = cx.smem_b + score_bytes;                                             // [stages][tile_keys][hd] bf16
+  float* qs = reinterpret_cast<float*>(cx.smem_b + kBBytes - kDecScratchBytes);         // [gs][hd]
+  float* red = qs + 8 * 128;                                                            // [4][8] x 2, then [parts][gs*hd]
+  bf16* kn = reinterpret_cast<bf16*>(red + 1024);                                       // [hd]
+  bf16* vn = kn + 128;                                                                  // [hd]
+  float* stat = reinterpret_cast<float*>(vn + 128);                                     // [16]: max[8], sum[8]
+  const uint32_t tiles_addr = smem_u32(tiles);
+
+  // value accumulation: an item is (part of the keys, head of the group, 16-byte piece of the output row);
+  // part q takes keys q, q + parts, ... of every tile; the fp32 sums of an item stay in `red` between tiles
+  const int cols = gs * hd;
+  const int pieces = gs * lpk;
+  int parts = kWorkers / pieces;
+  if (parts * cols > 1024) parts = 1024 / cols;
+  if (parts < 1) parts = 1;
+  const int items = parts * pieces;
+
+#pragma unroll 1
+  for (int u = cx.cta; u < units; u += cx.grid) {
+    const int rowg = u / nch, ch = u - rowg * nch;
+    const int b = rowg / p.kv_heads, kvh = rowg - b * p.kv_heads;
+    const int j0 = ch * chunk;
+    const int j1 = min(n_max, j0 + chunk);
+    const int cl = max(0, j1 - j0);
+    const int newpos = A.len;
+    const bool owner = (A.len >= j0 && A.len < j1);
+    const int nt = (cl + tile_keys - 1) / tile_keys;
+    const bf16* kbase = A.k + b * A.kv_bstride + kvh * hd;
+    const bf16* vbase = A.v + b * A.kv_bstride + kvh * hd;
+    named_bar_sync(1, kWorkers);  // previous unit is done with the scratch and the stages
+
+    // Element s of the stream is K tile s (s < nt) or V tile s - nt; it uses stage s % kDecStages.
+    // Every call commits one group, an empty one past the end, so that the group count is uniform.
+    auto issue = [&](int s) {
+      if (s < 2 * nt) {
+        const int t = (s < nt) ? s : s - nt;
+        const int t0 = j0 + t * tile_keys, t1 = min(j1, t0 + tile_keys);
+        fetch_cache_tile(tiles_addr + (s % kDecStages) * stage_bytes,
+                         ((s < nt) ? kbase : vbase) + static_cast<long long>(t0) * A.kv_ld, A.kv_ld, t1 - t0, newpos - t0,
+                         hd, wtid);
+      }
+      cp_async_commit();
+    };
+    issue(0);
+    issue(1);
+
+    // --- q of every head of the group and the new key (rotated if asked), and the new value
+    {
+      long long pos = 0;
+      if (A.rope) {
+        pos = p.pos[b];
+        if (pos < 0 || pos >= p.max_positions) pos = 0;  // reported by the prologue
+      }
+#pragma unroll 1
+      for (int idx = wtid; idx < (gs + 1) * half; idx += kWorkers) {
+        const int g = idx / half, i = idx - g * half;
+        const bf16* src = (g < gs) ? A.q + b * A.q_bstride + (kvh * gs + g) * hd
+                                   : A.knew + static_cast<long long>(b) * A.new_ld + kvh * hd;
+        float first = ldcg_bf16(src + i);
+        float second = ldcg_bf16(src + i + half);
+        if (A.rope) {
+          const float c = ldg_bf16(p.cos_t + pos * hd + i);
+          const float sn = ldg_bf16(p.sin_t + pos * hd + i);
+          rope_pair(first, second, c, sn, p.rope_style, first, second);
+        }
+        if (g < gs) {
+          qs[g * hd + i] = first;
+          qs[g * hd + i + half] = second;
+        } else {
+          kn[i] = __float2bfloat16_rn(first);
+          kn[i + half] = __float2bfloat16_rn(second);
+        }
+      }
+#pragma unroll 1
+      for (int i = wtid; i < hd; i += kWorkers)
+        vn[i] = __float2bfloat16_rn(ldcg_bf16(A.vnew + static_cast<long long>(b) * A.new_ld + kvh * hd + i));
+    }
+    named_bar_sync(1, kWorkers);
+    if (owner) {  // in-kernel KV append
+      bf16* kd = A.k + b * A.kv_bstride + static_cast<long long>(A.len) * A.kv_ld + kvh * hd;
+      bf16* vd = A.v + b * A.kv_bstride + static_cast<long long>(A.len) * A.kv_ld + kvh * hd;
+#pragma unroll 1
+      for (int i = wtid; i < hd; i += kWorkers) {
+        kd[i] = kn[i];
+        vd[i] = vn[i];
+      }
+    }
+
+    // --- scores: one thread per (head of the group, key), a head_dim-term fp32 chain each
+#pragma unroll 1
+    for (int s = 0; s < nt; ++s) {
+      const int t0 = j0 + s * tile_keys, t1 = min(j1, t0 + tile_keys);
+      uint8_t* tile = tiles + (s % kDecStages) * stage_bytes;
+      cp_async_wait_group<1>();  // this thread's pieces of tile s have landed
+      if (newpos >= t0 && newpos < t1 && wtid < lpk)
+        *reinterpret_cast<uint4*>(tile + (newpos - t0) * row_bytes + ((wtid ^ ((newpos - t0) & 7)) << 4)) =
+            *reinterpret_cast<const uint4*>(kn + wtid * 8);
+      named_bar_sync(1, kWorkers);  // tile s is complete; every thread is done with tile s - 1
+      issue(s + 2);
+      const int tk = t1 - t0;
+#pragma unroll 1
+      for (int item = wtid; item < gs * tk; item += kWorkers) {
+        const int g = item / tk, key = item - g * tk;
+        const uint8_t* krow = tile + key * row_bytes;
+        const float* qv = qs + g * hd;
+        float dot = 0.f;
+#pragma unroll 4
+        for (int piece = 0; piece < lpk; ++piece) {
+          float kf[8];
+          unpack8(*reinterpret_cast<const uint4*>(krow + ((piece ^ (key & 7)) << 4)), kf);
+          const float4 qa = *reinterpret_cast<const float4*>(qv + piece * 8);
+          const float4 qb = *reinterpret_cast<const float4*>(qv + piece * 8 + 4);
+          dot = fmaf(qa.x, kf[0], dot); dot = fmaf(qa.y, kf[1], dot); dot = fmaf(qa.z, kf[2], dot); dot = fmaf(qa.w, kf[3], dot);
+          dot = fmaf(qb.x, kf[4], dot); dot = fmaf(qb.y, kf[5], dot); dot = fmaf(qb.z, kf[6], dot); dot = fmaf(qb.w, kf[7], dot);
+        }
+        sc[g * chunk + (t0 - j0) + key] = bf16_round(dot) * A.scale;
+      }
+    }
+    named_bar_sync(1, kWorkers);
+
+    // --- chunk max, then chunk sum of exp(score - chunk max); the first V tiles are in flight meanwhile
+#pragma unroll 1
+    for (int g = 0; g < gs; ++g) {
+      float m = -INFINITY;
+#pragma unroll 1
+      for (int i = wtid; i < cl; i += kWorkers) m = fmaxf(m, sc[g * chunk + i]);
+      m = warp_max(m);
+      if (lane == 0) red[warp * 8 + g] = m;
+    }
+    named_bar_sync(1, kWorkers);
+#pragma unroll 1
+    for (int g = 0; g < gs; ++g) {
+      const float m = fmaxf(fmaxf(red[g], red[8 + g]), fmaxf(red[16 + g], red[24 + g]));
+      float sum = 0.f;
+#pragma unroll 1
+      for (int i = wtid; i < cl; i += kWorkers) sum += expf(sc[g * chunk + i] - m);
+      sum = warp_sum(sum);
+      if (lane == 0) red[32 + warp * 8 + g] = sum;
+      if (wtid == 0) stat[g] = m;
+    }
+    named_bar_sync(1, kWorkers);
+    if (wtid < gs) stat[8 + wtid] = ((red[32 + wtid] + red[40 + wtid]) + red[48 + wtid]) + red[56 + wtid];
+    named_bar_sync(1, kWorkers);
+
+    if (nch > 1) {
+      // --- publish (max, sum) with this phase's stamp; wait for every chunk of the row group
+      float* mine = p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + ch) * kExchangeFloats;
+      if (wtid < 16) __stcg(mine + wtid, stat[wtid]);
+      __threadfence();
+      named_bar_sync(1, kWorkers);
+      if (wtid == 0) st_relaxed_u32(reinterpret_cast<uint32_t*>(mine + 16), A.stamp);
+      bool ok = true;
+      if (wtid < nch) {
+        const uint32_t* theirs = reinterpret_cast<const uint32_t*>(
+            p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + wtid) * kExchangeFloats + 16);
+        uint32_t spins = 0;
+        while (ld_relaxed_u32(theirs) != A.stamp) {
+          if ((++spins & 255u) == 0 && give_up(cx, SITE_ATT_EXCHANGE, rowg)) {
+            ok = false;
+            break;
+          }
+        }
+        __threadfence();
+      }
+      if (!workers_ok(cx, ok)) {
+        cp_async_wait_all();  // nothing of this CTA stays in flight past the return
+        return false;
+      }
+      if (wtid < gs) {
+        const float* all = p.att_xch + static_cast<size_t>(rowg) * kMaxChunks * kExchangeFloats;
+        float m = -INFINITY;
+        for (int c = 0; c < nch; ++c) m = fmaxf(m, __ldcg(all + c * kExchangeFloats + wtid));
+        float sum = 0.f;
+        for (int c = 0; c < nch; ++c)
+          sum += __ldcg(all + c * kExchangeFloats + 8 + wtid) * expf(__ldcg(all + c * kExchangeFloats + wtid) - m);
+        stat[wtid] = m;
+        stat[8 + wtid] = sum;
+      }
+      named_bar_sync(1, kWorkers);
+    }
+
+    // --- probabilities (bf16, against the global max and sum)
+#pragma unroll 1
+    for (int g = 0; g < gs; ++g) {
+      const float m = stat[g], denom = stat[8 + g];
+#pragma unroll 1
+      for (int i = wtid; i < cl; i += kWorkers) sc[g * chunk + i] = bf16_round(expf(sc[g * chunk + i] - m) / denom);
+    }
+    // --- value sums, tile by tile
+#pragma unroll 1
+    for (int s = nt; s < 2 * nt; ++s) {
+      const int t0 = j0 + (s - nt) * tile_keys, t1 = min(j1, t0 + tile_keys);
+      uint8_t* tile = tiles + (s % kDecStages) * stage_bytes;
+      cp_async_wait_group<1>();
+      if (newpos >= t0 && newpos < t1 && wtid < lpk)  // the new value row joins its tile
+        *reinterpret_cast<uint4*>(tile + (newpos - t0) * row_bytes + ((wtid ^ ((newpos - t0) & 7)) << 4)) =
+            *reinterpret_cast<const uint4*>(vn + wtid * 8);
+      named_bar_sync(1, kWorkers);  // the tile is complete and (first tile) so are the probabilities
+      issue(s + 2);
+      const int tk = t1 - t0;
+#pragma unroll 1
+      for (int item = wtid; item < items; item += kWorkers) {
+        const int part = item / pieces, pc = item - part * pieces;
+        const int g = pc / lpk, piece = pc - g * lpk;
+        float* mine = red + (part * gs + g) * hd + piece * 8;
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = (s == nt) ? 0.f : mine[e];
+        const float* pr = sc + g * chunk + (t0 - j0);
+#pragma unroll 2
+        for (int kk = part; kk < tk; kk += parts) {
+          float vf[8];
+          unpack8(*reinterpret_cast<const uint4*>(tile + kk * row_bytes + ((piece ^ (kk & 7)) << 4)), vf);
+          const float w = pr[kk];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] = fmaf(w, vf[e], acc[e]);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) mine[e] = acc[e];
+      }
+    }
+    named_bar_sync(1, kWorkers);
+#pragma unroll 1
+    for (int col = wtid; col < cols; col += kWorkers) {
+      float o = 0.f;
+      if (nt > 0) {
+        o = red[col];
+#pragma unroll 1
+        for (int part = 1; part < parts; ++part) o += red[part * cols + col];
+      }
+      const int g = col / hd, d = col - g * hd;
+      const int head = kvh * gs + g;
+      if (nch == 1) {
+        A.out[b * A.out_bstride + head * A.out_hstride + d] = __float2bfloat16_rn(o);
+      } else {
+        const size_t row = static_cast<size_t>(b) * p.q_heads + head;
+        __stcg(p.att_part + (row * kMaxChunks + ch) * hd + d, o);
+      }
+    }
+    if (nch > 1 && A.combine) {
+      // Stand-alone op: there is no consumer phase, so chunk 0's CTA waits for the
+      // partials of its peers (second stamp) and sums them in chunk order.
+      float* mine = p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + ch) * kExchangeFloats;
+      __threadfence();
+      named_bar_sync(1, kWorkers);
+      if (wtid == 0) st_relaxed_u32(reinterpret_cast<uint32_t*>(mine + 17), A.stamp);
+      if (ch == 0) {
+        bool ok = true;
+        if (wtid < nch) {
+          const uint32_t* theirs = reinterpret_cast<const uint32_t*>(
+              p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + wtid) * kExchangeFloats + 17);
+          uint32_t spins = 0;
+          while (ld_relaxed_u32(theirs) != A.stamp) {
+            if ((++spins & 255u) == 0 && give_up(cx, SITE_ATT_EXCHANGE, rowg)) {
+              ok = false;
+              break;
+            }
+          }
+          __threadfence();
+        }
+        if (!workers_ok(cx, ok)) return false;
+        for (int idx = wtid; idx < cols; idx += kWorkers) {
+          const int g = idx / hd, d = idx - g * hd;
+          const int head = kvh * gs + g;
+          const size_t row = static_cast<size_t>(b) * p.q_heads + head;
+          float o = 0.f;
+          for (int c = 0; c < nch; ++c) o += __ldcg(p.att_part + (row * kMaxChunks + c) * hd + d);
+          A.out[b * A.out_bstride + head * A.out_hstride + d] = __float2bfloat16_rn(o);
+        }
+      }
+    }
+  }
+  if (!A.combine && cx.cta == 0 && wtid == 0) cx.ctrl->att_nch = nch;  // read after the barrier
+  return true;
+}
+
 // Softmax attention for every (sequence, kv head, query token) row group; all
 // query heads of the kv head share one pass over K and V.  In decode the
 // context is split into chunks across CTAs.  Each chunk publishes its max and
@@ -995,6 +1317,7 @@ __device__ __forceinline__ int decode_chunks(int keys, int rows, int grid, int g
 // (chunk partials are summed in chunk order by the consumer or by chunk 0's
 // peers, see AttnArgs::combine).
 __device__ __noinline__ bool attention_phase(const Ctx& cx, const AttnArgs& A, int wtid) {
+  if (A.decode) return attention_decode(cx, A, wtid);
   const KParams& p = *cx.p;
   const int hd = p.head_dim, half = hd / 2;
   const int gs = p.q_heads / p.kv_heads;
