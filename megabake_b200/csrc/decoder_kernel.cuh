@@ -468,33 +468,40 @@ __device__ __noinline__ void stage_norm_resident(const Ctx& cx, const GemmPhase*
   const int warp = wtid >> 5, lane = wtid & 31;
   const int nvec = ph->k / 8;  // <= 256
   const uint4* wrow = reinterpret_cast<const uint4*>(ph->normw);
-  for (int t = warp; t < mt; t += kWorkerWarps) {
-    const uint4* row = reinterpret_cast<const uint4*>(activation_row(p, ph, t0 + t));
-    uint4 x[8], w[8];
+  constexpr int kRows = 2;  // token rows of a warp in flight together: all their loads are issued before the first is used
+#pragma unroll 1
+  for (int tb = warp; tb < mt; tb += kRows * kWorkerWarps) {
+    uint4 x[kRows][8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int v = i * 32 + lane;
-      x[i] = make_uint4(0, 0, 0, 0);
-      w[i] = x[i];
-      if (v < nvec) {
-        x[i] = __ldcg(row + v);
-        w[i] = __ldg(wrow + v);
+    for (int r = 0; r < kRows; ++r) {
+      const int t = tb + r * kWorkerWarps;
+      const uint4* row = reinterpret_cast<const uint4*>(activation_row(p, ph, t0 + min(t, mt - 1)));
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int v = i * 32 + lane;
+        x[r][i] = (t < mt && v < nvec) ? __ldcg(row + v) : make_uint4(0, 0, 0, 0);
       }
     }
-    float sum = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float f[8];
-      unpack8(x[i], f);
+    for (int r = 0; r < kRows; ++r) {
+      const int t = tb + r * kWorkerWarps;
+      if (t >= mt) break;  // warp-uniform
+      float sum = 0.f;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) sum = fmaf(f[e], f[e], sum);
-    }
-    sum = warp_sum(sum);
-    const float r = 1.0f / sqrtf(sum / static_cast<float>(ph->k) + p.eps);
+      for (int i = 0; i < 8; ++i) {
+        float f[8];
+        unpack8(x[r][i], f);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int v = i * 32 + lane;
-      if (v < nvec) *reinterpret_cast<uint4*>(b_slot_addr(cx, v >> 3, t, v & 7)) = normalise_vec(x[i], w[i], r);
+        for (int e = 0; e < 8; ++e) sum = fmaf(f[e], f[e], sum);
+      }
+      sum = warp_sum(sum);
+      const float rinv = 1.0f / sqrtf(sum / static_cast<float>(ph->k) + p.eps);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int v = i * 32 + lane;
+        if (v < nvec)  // the norm weights stay in L1 between rows
+          *reinterpret_cast<uint4*>(b_slot_addr(cx, v >> 3, t, v & 7)) = normalise_vec(x[r][i], __ldg(wrow + v), rinv);
+      }
     }
   }
 }
@@ -622,20 +629,24 @@ __device__ __noinline__ void stage_chunks(const Ctx& cx, const GemmPhase* ph, in
   const KParams& p = *cx.p;
   const int per_slot = mt * 8;
   const int items = (k1 - k0) * per_slot;
-  if (ph->bmode == B_PLAIN) {
-    for (int item0 = wtid; item0 < items; item0 += kWorkers * 4) {
-      uint4 xu[4];
+  if ((ph->bmode == B_PLAIN && !ph->gather) || (ph->bmode == B_ATTN && nch <= 1)) {
+    // Rows of a bf16 buffer: eight loads per thread are in flight before the first store.
+    constexpr int kDepth = 8;
+    const bf16* base = (ph->bmode == B_PLAIN) ? ph->src + static_cast<size_t>(t0) * ph->src_ld
+                                              : p.attn + static_cast<size_t>(t0) * p.q_heads * p.head_dim;
+    const size_t ld = (ph->bmode == B_PLAIN) ? static_cast<size_t>(ph->src_ld) : static_cast<size_t>(p.q_heads) * p.head_dim;
+    for (int item0 = wtid; item0 < items; item0 += kWorkers * kDepth) {
+      uint4 xu[kDepth];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < kDepth; ++i) {
         const int item = item0 + i * kWorkers;
         if (item < items) {
           const int s = item / per_slot, rem = item - s * per_slot;
-          xu[i] = __ldcg(reinterpret_cast<const uint4*>(activation_row(p, ph, t0 + (rem >> 3)) + (k0 + s) * kChunkK +
-                                                        (rem & 7) * 8));
+          xu[i] = __ldcg(reinterpret_cast<const uint4*>(base + (rem >> 3) * ld + (k0 + s) * kChunkK + (rem & 7) * 8));
         }
       }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < kDepth; ++i) {
         const int item = item0 + i * kWorkers;
         if (item < items) {
           const int s = item / per_slot, rem = item - s * per_slot;
@@ -993,7 +1004,7 @@ __device__ __forceinline__ int decode_chunks(int keys, int rows, int grid, int g
 // tile from shared memory.  Arithmetic and rounding points are those described
 // above attention_phase for decode; the exchange of the chunk statistics and
 // the hand-over of the chunk partials are the same protocol as there.
-constexpr int kDecStages = 3;
+constexpr int kDecStages = 3;                // more, smaller stages measured slower (6 x 8 KB: +30 %)
 constexpr int kDecScratchBytes = 10 * 1024;  // q [8][128] fp32, value partial sums [1024] fp32, new key/value, statistics
 constexpr int kDecTileBytes = 16 * 1024;     // upper bound of one stage
 static_assert(kScoreBytes + kDecScratchBytes + kDecStages * 256 <= kBBytes, "no room for one cache row per stage");
@@ -1072,8 +1083,8 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, 
       }
       cp_async_commit();
     };
-    issue(0);
-    issue(1);
+#pragma unroll
+    for (int s = 0; s < kDecStages - 1; ++s) issue(s);
 
     // --- q of every head of the group and the new key (rotated if asked), and the new value
     {
@@ -1122,12 +1133,12 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, 
     for (int s = 0; s < nt; ++s) {
       const int t0 = j0 + s * tile_keys, t1 = min(j1, t0 + tile_keys);
       uint8_t* tile = tiles + (s % kDecStages) * stage_bytes;
-      cp_async_wait_group<1>();  // this thread's pieces of tile s have landed
+      cp_async_wait_group<kDecStages - 2>();  // this thread's pieces of tile s have landed
       if (newpos >= t0 && newpos < t1 && wtid < lpk)
         *reinterpret_cast<uint4*>(tile + (newpos - t0) * row_bytes + ((wtid ^ ((newpos - t0) & 7)) << 4)) =
             *reinterpret_cast<const uint4*>(kn + wtid * 8);
       named_bar_sync(1, kWorkers);  // tile s is complete; every thread is done with tile s - 1
-      issue(s + 2);
+      issue(s + kDecStages - 1);
       const int tk = t1 - t0;
 #pragma unroll 1
       for (int item = wtid; item < gs * tk; item += kWorkers) {
@@ -1222,12 +1233,12 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, 
     for (int s = nt; s < 2 * nt; ++s) {
       const int t0 = j0 + (s - nt) * tile_keys, t1 = min(j1, t0 + tile_keys);
       uint8_t* tile = tiles + (s % kDecStages) * stage_bytes;
-      cp_async_wait_group<1>();
+      cp_async_wait_group<kDecStages - 2>();
       if (newpos >= t0 && newpos < t1 && wtid < lpk)  // the new value row joins its tile
         *reinterpret_cast<uint4*>(tile + (newpos - t0) * row_bytes + ((wtid ^ ((newpos - t0) & 7)) << 4)) =
             *reinterpret_cast<const uint4*>(vn + wtid * 8);
       named_bar_sync(1, kWorkers);  // the tile is complete and (first tile) so are the probabilities
-      issue(s + 2);
+      issue(s + kDecStages - 1);
       const int tk = t1 - t0;
 #pragma unroll 1
       for (int item = wtid; item < items; item += kWorkers) {
