@@ -1055,7 +1055,8 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, 
   int parts = kWorkers / pieces;
   if (parts * cols > 1024) parts = 1024 / cols;
   if (parts < 1) parts = 1;
-  const int items = parts * pieces;
+  const int items = parts * pieces;  // <= kWorkers
+  const int item_part = wtid / pieces, item_g = (wtid - item_part * pieces) / lpk, item_piece = wtid % lpk;
 
 #pragma unroll 1
   for (int u = cx.cta; u < units; u += cx.grid) {
@@ -1145,16 +1146,25 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, 
         const int g = item / tk, key = item - g * tk;
         const uint8_t* krow = tile + key * row_bytes;
         const float* qv = qs + g * hd;
-        float dot = 0.f;
-#pragma unroll 4
-        for (int piece = 0; piece < lpk; ++piece) {
-          float kf[8];
-          unpack8(*reinterpret_cast<const uint4*>(krow + ((piece ^ (key & 7)) << 4)), kf);
-          const float4 qa = *reinterpret_cast<const float4*>(qv + piece * 8);
-          const float4 qb = *reinterpret_cast<const float4*>(qv + piece * 8 + 4);
-          dot = fmaf(qa.x, kf[0], dot); dot = fmaf(qa.y, kf[1], dot); dot = fmaf(qa.z, kf[2], dot); dot = fmaf(qa.w, kf[3], dot);
-          dot = fmaf(qb.x, kf[4], dot); dot = fmaf(qb.y, kf[5], dot); dot = fmaf(qb.z, kf[6], dot); dot = fmaf(qb.w, kf[7], dot);
+        // four partial sums (pieces 0, 4, 8, ... / 1, 5, ... / ...): a lone warp per scheduler hides no latency,
+        // so the chains have to be independent
+        float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+        for (int piece0 = 0; piece0 < lpk; piece0 += 4) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int piece = piece0 + c;
+            float kf[8];
+            unpack8(*reinterpret_cast<const uint4*>(krow + ((piece ^ (key & 7)) << 4)), kf);
+            const float4 qa = *reinterpret_cast<const float4*>(qv + piece * 8);
+            const float4 qb = *reinterpret_cast<const float4*>(qv + piece * 8 + 4);
+            float acc = part[c];
+            acc = fmaf(qa.x, kf[0], acc); acc = fmaf(qa.y, kf[1], acc); acc = fmaf(qa.z, kf[2], acc); acc = fmaf(qa.w, kf[3], acc);
+            acc = fmaf(qb.x, kf[4], acc); acc = fmaf(qb.y, kf[5], acc); acc = fmaf(qb.z, kf[6], acc); acc = fmaf(qb.w, kf[7], acc);
+            part[c] = acc;
+          }
         }
+        const float dot = (part[0] + part[1]) + (part[2] + part[3]);
         sc[g * chunk + (t0 - j0) + key] = bf16_round(dot) * A.scale;
       }
     }
@@ -1229,6 +1239,7 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, 
       for (int i = wtid; i < cl; i += kWorkers) sc[g * chunk + i] = bf16_round(expf(sc[g * chunk + i] - m) / denom);
     }
     // --- value sums, tile by tile
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
     for (int s = nt; s < 2 * nt; ++s) {
       const int t0 = j0 + (s - nt) * tile_keys, t1 = min(j1, t0 + tile_keys);
@@ -1240,36 +1251,29 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, 
       named_bar_sync(1, kWorkers);  // the tile is complete and (first tile) so are the probabilities
       issue(s + kDecStages - 1);
       const int tk = t1 - t0;
-#pragma unroll 1
-      for (int item = wtid; item < items; item += kWorkers) {
-        const int part = item / pieces, pc = item - part * pieces;
-        const int g = pc / lpk, piece = pc - g * lpk;
-        float* mine = red + (part * gs + g) * hd + piece * 8;
-        float acc[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = (s == nt) ? 0.f : mine[e];
-        const float* pr = sc + g * chunk + (t0 - j0);
-#pragma unroll 2
-        for (int kk = part; kk < tk; kk += parts) {
+      if (wtid < items) {  // at most one item per thread: its sums stay in registers across the tiles
+        const float* pr = sc + item_g * chunk + (t0 - j0);
+#pragma unroll 4
+        for (int kk = item_part; kk < tk; kk += parts) {
           float vf[8];
-          unpack8(*reinterpret_cast<const uint4*>(tile + kk * row_bytes + ((piece ^ (kk & 7)) << 4)), vf);
+          unpack8(*reinterpret_cast<const uint4*>(tile + kk * row_bytes + ((item_piece ^ (kk & 7)) << 4)), vf);
           const float w = pr[kk];
 #pragma unroll
           for (int e = 0; e < 8; ++e) acc[e] = fmaf(w, vf[e], acc[e]);
         }
-#pragma unroll
-        for (int e = 0; e < 8; ++e) mine[e] = acc[e];
       }
+    }
+    if (wtid < items) {
+      float* mine = red + (item_part * gs + item_g) * hd + item_piece * 8;
+      *reinterpret_cast<float4*>(mine) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      *reinterpret_cast<float4*>(mine + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
     named_bar_sync(1, kWorkers);
 #pragma unroll 1
     for (int col = wtid; col < cols; col += kWorkers) {
-      float o = 0.f;
-      if (nt > 0) {
-        o = red[col];
+      float o = red[col];
 #pragma unroll 1
-        for (int part = 1; part < parts; ++part) o += red[part * cols + col];
-      }
+      for (int part = 1; part < parts; ++part) o += red[part * cols + col];
       const int g = col / hd, d = col - g * hd;
       const int head = kvh * gs + g;
       if (nch == 1) {
