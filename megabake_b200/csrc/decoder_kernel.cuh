@@ -1012,14 +1012,21 @@ static_assert(kScoreBytes + kDecScratchBytes + kDecStages * 256 <= kBBytes, "no 
 // Copy `count` rows of head_dim bf16 (row stride ld elements) into a stage, except row `skip`.
 // Piece p of row r lands at piece p ^ (r & 7), so that a column of pieces spreads over all banks.
 __device__ __noinline__ void fetch_cache_tile(uint32_t dst, const bf16* src, int ld, int count, int skip, int hd, int wtid) {
+  // A thread keeps its 16-byte piece and walks down the rows in steps of a multiple of eight, so that the
+  // swizzled column is fixed and both addresses advance by constants.
   const int shift = (hd == 64) ? 3 : 4;  // 16-byte pieces per row: 8 or 16
-  const int total = count << shift;
-#pragma unroll 2
-  for (int it = wtid; it < total; it += kWorkers) {
-    const int key = it >> shift, piece = it & ((1 << shift) - 1);
-    if (key != skip)
-      cp_async16(dst + key * hd * 2 + ((piece ^ (key & 7)) << 4),
-                 reinterpret_cast<const uint4*>(src + static_cast<long long>(key) * ld) + piece);
+  const int piece = wtid & ((1 << shift) - 1);
+  const int step = kWorkers >> shift;    // 16 or 8 rows
+  int key = wtid >> shift;
+  uint32_t to = dst + key * hd * 2 + ((piece ^ (key & 7)) << 4);
+  const uint4* from = reinterpret_cast<const uint4*>(src + static_cast<long long>(key) * ld) + piece;
+  const uint32_t to_step = step * hd * 2;
+  const long long from_step = static_cast<long long>(step) * ld / 8;  // in 16-byte units: ld is a multiple of 8
+#pragma unroll 4
+  for (; key < count; key += step) {
+    if (key != skip) cp_async16(to, from);
+    to += to_step;
+    from += from_step;
   }
 }
 
