@@ -421,13 +421,19 @@ __device__ __forceinline__ uint8_t* b_slot_addr(const Ctx& cx, int slot, int t, 
 
 // Normalise one 8-element vector: w * bf16(x * rinv), the two roundings of the
 // Hugging Face RMSNorm.
+// The second product is taken on bf16 pairs: the product of two bf16 values is exact in fp32, so
+// the packed multiply's single rounding equals rounding the fp32 product (4 instructions for 8 values;
+// the staging loops are bound by the instruction rate of the four worker warps).
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
 __device__ __forceinline__ uint4 normalise_vec(const uint4 xu, const uint4 wu, float r) {
-  float x[8], w[8];
+  float x[8];
   unpack8(xu, x);
-  unpack8(wu, w);
-#pragma unroll
-  for (int e = 0; e < 8; ++e) x[e] = w[e] * bf16_round(x[e] * r);
-  return pack8(x);
+  return make_uint4(mul_bf16x2(wu.x, pack2(x[0] * r, x[1] * r)), mul_bf16x2(wu.y, pack2(x[2] * r, x[3] * r)),
+                    mul_bf16x2(wu.z, pack2(x[4] * r, x[5] * r)), mul_bf16x2(wu.w, pack2(x[6] * r, x[7] * r)));
 }
 
 // RMSNorm statistics of the rows of one token tile: rinv[t] = 1/sqrt(mean(x^2)+eps).
@@ -635,21 +641,27 @@ __device__ __noinline__ void stage_chunks(const Ctx& cx, const GemmPhase* ph, in
     const bf16* base = (ph->bmode == B_PLAIN) ? ph->src + static_cast<size_t>(t0) * ph->src_ld
                                               : p.attn + static_cast<size_t>(t0) * p.q_heads * p.head_dim;
     const size_t ld = (ph->bmode == B_PLAIN) ? static_cast<size_t>(ph->src_ld) : static_cast<size_t>(p.q_heads) * p.head_dim;
-    for (int item0 = wtid; item0 < items; item0 += kWorkers * kDepth) {
+    // item = wtid + n * kWorkers -> (slot s, row and column `rem`).  When a slot's items divide the block
+    // (token tiles of 1, 2, 4, 8 or 16 rows) `rem` is fixed and s advances by a constant: no division.
+    const bool regular = (kWorkers % per_slot) == 0;
+    const int s_first = wtid / per_slot, rem_fixed = wtid - s_first * per_slot, s_step = kWorkers / per_slot;
+    for (int n0 = 0; wtid + n0 * kWorkers < items; n0 += kDepth) {
       uint4 xu[kDepth];
 #pragma unroll
       for (int i = 0; i < kDepth; ++i) {
-        const int item = item0 + i * kWorkers;
+        const int item = wtid + (n0 + i) * kWorkers;
         if (item < items) {
-          const int s = item / per_slot, rem = item - s * per_slot;
+          const int s = regular ? s_first + (n0 + i) * s_step : item / per_slot;
+          const int rem = regular ? rem_fixed : item - s * per_slot;
           xu[i] = __ldcg(reinterpret_cast<const uint4*>(base + (rem >> 3) * ld + (k0 + s) * kChunkK + (rem & 7) * 8));
         }
       }
 #pragma unroll
       for (int i = 0; i < kDepth; ++i) {
-        const int item = item0 + i * kWorkers;
+        const int item = wtid + (n0 + i) * kWorkers;
         if (item < items) {
-          const int s = item / per_slot, rem = item - s * per_slot;
+          const int s = regular ? s_first + (n0 + i) * s_step : item / per_slot;
+          const int rem = regular ? rem_fixed : item - s * per_slot;
           *reinterpret_cast<uint4*>(b_slot_addr(cx, slot0 + s, rem >> 3, rem & 7)) = xu[i];
         }
       }
