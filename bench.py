@@ -301,7 +301,9 @@ def main():
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": traffic, "peak_source": f"of {peak_kind}",
                      "algorithmic_bytes_per_launch": bytes_per_launch,
-                     "kernel": "mk::megakernel_small<%d>" % args.batch if args.batch <= 4 else "mk::megakernel",
+                     "kernel": ("mk::megakernel_small<%d>" % args.batch if args.batch <= 4 else
+                                "mk::megakernel_small<%d> + <%d> (two launches per step)" % ((args.batch + 1) // 2, args.batch // 2)
+                                if args.batch <= 8 else "mk::megakernel"),
                      "launch_us": launch_ms * 1e3, "frac_of_8TBps_nominal": achieved / 8000.0},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": 16 * args.batch,
                 "d2h_bytes_per_step": 2 * config.vocab * args.batch, "us_per_call": 1e3 * e2e_ms / e2e_steps},

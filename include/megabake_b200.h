@@ -126,7 +126,9 @@ int mk_create(const mk_config* config, void* workspace, size_t workspace_bytes, 
  * src/megabake/bodies/gemm.py:1809-1843. */
 int mk_bind_weights(mk_handle handle, const mk_weights* weights, void* stream);
 
-/* One decode step for `batch` sequences: one cooperative launch, no sync.
+/* One decode step for `batch` sequences, no sync: one cooperative launch; two
+ * (halves of the batch, plus a one-warp copy of the valid lengths) for 5..8
+ * sequences under MK_ENGINE_AUTO / MK_ENGINE_FMA when the small-launch kernel applies.
  * ids/positions: int64 [batch].  key_caches/value_caches: host arrays of
  * config.layers device pointers, each bf16 [batch, capacity, kv_heads,
  * head_dim] contiguous.  valid_lengths: host array of config.layers device

@@ -246,9 +246,10 @@ def test_decode_error_no_worse_than_eager_bf16(device):
 
 
 @pytest.mark.parametrize("engine", ["auto", "tcgen05"])
-@pytest.mark.parametrize("batch", [1, 2, 3, 4, 5, 16, 21])
+@pytest.mark.parametrize("batch", [1, 2, 3, 4, 5, 8, 16, 21])
 def test_decode_batches_match_oracle(device, batch, engine):
-    """Batches 1-4 run the small-launch kernel under "auto" (one instantiation per token count)."""
+    """Batches 1-4 run the small-launch kernel under "auto" (one instantiation per token count),
+    5-8 two launches of it (3+2 .. 4+4 sequences), larger ones the tensor engine."""
     oracle_decode_compare(tiny_config(q_heads=4, kv_heads=1, hidden=256), device, batch, capacity=24, prefill=0, steps=4,
                           engine=engine)
 
@@ -258,6 +259,22 @@ def test_decode_split_context_matches_oracle(device, engine):
     """A long filled prefix makes the attention phase cut the context across CTAs."""
     config = tiny_config(q_heads=8, kv_heads=2, hidden=512, intermediate=1024)
     oracle_decode_compare(config, device, batch=2, capacity=1024, prefill=700, steps=3, engine=engine)
+
+
+@pytest.mark.parametrize("batch,launches", [(4, 1), (5, 2), (8, 2), (9, 1)])
+def test_decode_launches_per_step(device, batch, launches):
+    """One launch per step, except 5-8 sequences under "auto": two launches of the small-launch kernel, the
+    first on a snapshot of the valid lengths so that each length still advances by exactly one."""
+    config = tiny_config(q_heads=4, kv_heads=1, hidden=256)
+    weights = synth_weights(config, seed=3, norm_std=0.1, device=device)
+    kernel = make_kernel(config, weights, device, max_tokens=batch, max_positions=16, engine="auto")
+    keys, values, lengths = new_kv_state(config, batch, 16, device)
+    ids = synth_ids(batch, config.vocab, seed=3).view(batch, 1).to(device)
+    before = kernel.launch_info()["launches"]
+    kernel.decode(ids, torch.zeros((batch, 1), dtype=torch.int64, device=device), keys, values, lengths)
+    kernel.check()
+    assert kernel.launch_info()["launches"] - before == launches
+    assert all(int(length.item()) == 1 for length in lengths)
 
 
 def test_decode_to_the_last_cache_row(device):
