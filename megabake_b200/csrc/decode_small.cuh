@@ -660,11 +660,8 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
   const int n_max = A.len + 1;
   const int warp = wtid >> 5, lane = wtid & 31;
   const int lpk = hd / 8;    // lanes per key (16 B each)
-  const int kpw = 32 / lpk;  // keys per warp pass
-  const int sub = lane / lpk, dg = lane % lpk;
   const int chunk = (n_max + nch - 1) / nch;
   const int units = rows * nch;
-  const int pass = kSmallWarps * kpw;
   const int tile_keys = kAttTileBytes / (hd * 2);
   const int row_bytes = hd * 2;
 
