@@ -51,8 +51,8 @@ enum { MK_ROPE_HF = 0, MK_ROPE_HALF_SWAP = 1 };
  *      128-row MMA); every other launch uses tcgen05.  Falls back to tcgen05 when the shape
  *      does not fit the small kernel (hidden > 2048 or a K slice longer than 2048).
  * AUTO: the faster of the two per launch; today the same choice as FMA.
- * SIMT: bring-up engine without TMA or tensor cores. */
-enum { MK_ENGINE_TCGEN05 = 0, MK_ENGINE_SIMT = 1, MK_ENGINE_FMA = 2, MK_ENGINE_AUTO = 3 };
+ * (Value 1 named a bring-up engine without TMA or tensor cores; it is gone and rejected.) */
+enum { MK_ENGINE_TCGEN05 = 0, MK_ENGINE_FMA = 2, MK_ENGINE_AUTO = 3 };
 
 /* Decoder shape.  Mirrors the facts the reference reads off the captured graph
  * (src/megabake/lowering.py:1851-1870 for the attention contract,
@@ -141,6 +141,21 @@ int mk_decode(mk_handle handle, const int64_t* ids, const int64_t* positions, in
               void* const* key_caches, void* const* value_caches, int32_t* const* valid_lengths,
               int capacity, void* logits, void* stream);
 
+/* `steps` greedy decode steps back to back without a host round trip: launch s picks each
+ * sequence's token on the device (largest bf16 logit, lowest index among equal ones: what
+ * torch.argmax returns), writes it to tokens_out[s * batch + b], stores it in ids[b] as the next
+ * step's input and adds one to positions[b].  ids and positions (int64 [batch], device) are
+ * therefore read and written; after the call they hold the inputs of the step that would come next.
+ * logits: bf16 [batch, vocab], overwritten by every step (the last step's stay).  No sync.
+ * A step whose prologue refuses (bad id/position, full cache) writes -1 tokens and NaN logits
+ * and leaves ids, positions, caches and lengths alone; the status word says why.
+ * Reference: none as an entry point; it stands in for the host loop of
+ * benchmarks/full_model.py:277-335 (argmax on the host between two calls) and removes the
+ * per-call host cost measured in ROADMAP.md:143. */
+int mk_decode_steps(mk_handle handle, int64_t* ids, int64_t* positions, int batch, void* const* key_caches,
+                    void* const* value_caches, int32_t* const* valid_lengths, int capacity, int steps,
+                    int64_t* tokens_out, void* logits, void* stream);
+
 /* Stateless prompt pass over [batch, sequence] tokens with causal or additive
  * attention mask (bf16 [batch, 1, sequence, sequence], NULL = causal).
  * logits: bf16 [batch, sequence, vocab].
@@ -180,6 +195,23 @@ int mk_attention(mk_handle handle, const void* query, const void* key, const voi
  * Reference: none (the reference traps and loses the context). */
 int mk_status(mk_handle handle, void* stream, mk_status_info* out);
 
+/* Mirror of the device status word in host memory: `host_word` is one int32 of pinned, mapped host
+ * memory (cudaHostAlloc / cudaHostRegister) that stays valid until it is replaced or the handle is
+ * destroyed; NULL turns the mirror off.  A kernel that records a status other than OK also stores
+ * it there, so the host can notice a refused or timed-out launch by reading the word, without a
+ * synchronisation, before its next call.  mk_status clears the word when it resets the handle.
+ * Reference: none (the reference traps; src/megabake/bodies/attention.py:540-543). */
+int mk_set_status_mirror(mk_handle handle, int32_t* host_word);
+
+/* Failure-detection hook for tests: adds `delta` to the grid-barrier count the host expects, so
+ * that the next launch's first grid barrier can never be reached and its bounded wait
+ * (MEGABAKE_WAIT_LIMIT_MS, read by mk_create; default 2000) runs out: the kernel records
+ * MK_STATUS_TIMEOUT, raises the abort flag every other wait polls, and every CTA leaves through
+ * the common exit.  mk_status then reports the timeout and resets the count.  Nothing waits
+ * without a limit and nothing traps.
+ * Reference: none (its barrier spins without a limit, src/megabake/runtime.py:157-159). */
+int mk_debug_skew_barrier(mk_handle handle, uint32_t delta);
+
 /* Event trace for the next launches: `buffer` is device memory of
  * ctas * events_per_cta * 8 bytes (NULL turns tracing off).  Worker thread 0 of
  * every CTA appends (event code << 56) | globaltimer-ns at phase entry, operand
@@ -204,12 +236,21 @@ int mk_launch_info(mk_handle handle, int32_t* ctas, int32_t* smem_bytes, int64_t
  * kernel attributes and clears the array on `stream`: make that call before any
  * stream capture begins.  All calls on a device share the one array: calls that
  * overlap (different streams or threads without ordering) race, so serialise
- * them.  The device status word is not reported through this entry point: the
- * caller guarantees valid_length < capacity (otherwise cache, length and output
- * are left untouched, as with mk_kv_attention).  Tensors as in mk_kv_attention. */
+ * them.  The device status word is read (and cleared) by mk_kv_attention_static_status;
+ * with valid_length == capacity the cache and the length are left untouched and the
+ * output is filled with NaN, as with mk_kv_attention.  Tensors as in mk_kv_attention. */
 int mk_kv_attention_static(int q_heads, int kv_heads, int head_dim, const void* query, const void* key,
                            const void* value, void* key_cache, void* value_cache, int32_t* valid_length,
                            int batch, int capacity, void* output, int device, void* stream);
+
+/* Status word of the static scratch array on `device` (the current device): synchronises
+ * `stream`, reports what the last mk_kv_attention_static launches recorded and, if that is not
+ * MK_STATUS_OK (a full cache, a wait that ran out), clears the word and the abort flag and
+ * restarts the barrier count, returning MK_ERR_DEVICE_STATUS.  Without this call a wait that
+ * timed out once would leave the abort flag set in the array for the life of the process and
+ * every later mk_kv_attention_static call on the device would leave at its first wait.
+ * Allocates nothing.  No counterpart in the reference. */
+int mk_kv_attention_static_status(int device, void* stream, mk_status_info* out);
 
 /* Last error text for this thread (host string, valid until the next call). */
 const char* mk_last_error(void);

@@ -23,11 +23,12 @@ MK_ERR_INVALID, MK_ERR_UNSUPPORTED, MK_ERR_CUDA, MK_ERR_ALIGNMENT = 1, 2, 3, 4
 MK_ERR_WORKSPACE, MK_ERR_UNBOUND, MK_ERR_DEVICE_STATUS = 5, 6, 7
 STATUS_NAMES = {0: "OK", 1: "KV_OVERFLOW", 2: "BAD_INDEX", 3: "TIMEOUT"}
 ROPE_STYLES = {"hf": 0, "half_swap": 1}
-ENGINES = {"tcgen05": 0, "simt": 1, "fma": 2, "auto": 3}
+ENGINES = {"tcgen05": 0, "fma": 2, "auto": 3}
 
 EXPORTS = (
     "mk_workspace_bytes", "mk_create", "mk_bind_weights", "mk_decode", "mk_prefill", "mk_linear",
-    "mk_kv_attention", "mk_kv_attention_static", "mk_attention", "mk_status", "mk_set_trace", "mk_launch_info", "mk_last_error", "mk_destroy",
+    "mk_kv_attention", "mk_kv_attention_static", "mk_kv_attention_static_status", "mk_attention", "mk_status", "mk_set_trace",
+    "mk_launch_info", "mk_last_error", "mk_destroy", "mk_decode_steps", "mk_set_status_mirror", "mk_debug_skew_barrier",
 )
 
 
@@ -106,6 +107,17 @@ def load() -> ctypes.CDLL:
         c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
         c_int, c_void_p,
     ]
+    lib.mk_kv_attention_static_status.restype = c_int
+    lib.mk_kv_attention_static_status.argtypes = [c_int, c_void_p, POINTER(MkStatusInfo)]
+    lib.mk_decode_steps.restype = c_int
+    lib.mk_decode_steps.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_int, POINTER(c_void_p), POINTER(c_void_p), POINTER(c_void_p),
+        c_int, c_int, c_void_p, c_void_p, c_void_p,
+    ]
+    lib.mk_debug_skew_barrier.restype = c_int
+    lib.mk_debug_skew_barrier.argtypes = [c_void_p, ctypes.c_uint32]
+    lib.mk_set_status_mirror.restype = c_int
+    lib.mk_set_status_mirror.argtypes = [c_void_p, c_void_p]
     lib.mk_status.restype = c_int
     lib.mk_status.argtypes = [c_void_p, c_void_p, POINTER(MkStatusInfo)]
     lib.mk_set_trace.restype = c_int

@@ -15,10 +15,13 @@ PACKAGE = Path(__file__).resolve().parent
 CSRC = PACKAGE / "csrc"
 LIBRARY = PACKAGE / "libmegabake_b200.so"
 SOURCES = [CSRC / "api.cu"]
-HEADERS = [
-    CSRC / "decoder_kernel.cuh", CSRC / "megakernel.cuh", CSRC / "ptx.cuh",
-    PACKAGE.parent / "include" / "megabake_b200.h",
-]
+
+
+def headers() -> list[Path]:
+    """Every header the library is built from: a new .cuh cannot be forgotten."""
+    return sorted(CSRC.glob("*.cuh")) + sorted((PACKAGE.parent / "include").glob("*.h"))
+
+
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-shared", "-Xcompiler", "-fPIC", "-Xptxas", "-v",
@@ -36,7 +39,7 @@ def is_stale() -> bool:
     if not LIBRARY.exists():
         return True
     built = LIBRARY.stat().st_mtime
-    return any(path.stat().st_mtime > built for path in SOURCES + HEADERS)
+    return any(path.stat().st_mtime > built for path in SOURCES + headers())
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:

@@ -89,7 +89,7 @@ int check_config(const mk_config& c) {
   if (c.q_heads / c.kv_heads > 8) return fail(MK_ERR_UNSUPPORTED, "config: at most 8 query heads per kv head");
   if (c.hidden % 64 || c.intermediate % 64)
     return fail(MK_ERR_UNSUPPORTED, "config: hidden and intermediate must be multiples of 64");
-  if (c.engine != MK_ENGINE_TCGEN05 && c.engine != MK_ENGINE_SIMT && c.engine != MK_ENGINE_FMA && c.engine != MK_ENGINE_AUTO)
+  if (c.engine != MK_ENGINE_TCGEN05 && c.engine != MK_ENGINE_FMA && c.engine != MK_ENGINE_AUTO)
     return fail(MK_ERR_INVALID, "config: engine");
   if (c.rope_style != MK_ROPE_HF && c.rope_style != MK_ROPE_HALF_SWAP) return fail(MK_ERR_INVALID, "config: rope_style");
   return MK_OK;
@@ -153,6 +153,8 @@ struct mk_handle_s {
   bool small_ll;  // its q/k/v phases hand their outputs to attention as stamped words (one grid barrier fewer per layer)
   unsigned long long* trace;
   int trace_cap;
+  int lookahead;        // bytes of weight look-ahead into L2 per CTA (small-launch kernel)
+  volatile int* mirror;  // host-mapped status word, or null
   std::mutex lock;
 };
 
@@ -226,15 +228,20 @@ void base_params(mk_handle h, KParams& p) {
   p.head_dim = c.head_dim; p.inter = c.intermediate; p.vocab = c.vocab; p.eps = c.rms_eps;
   p.rope_style = c.rope_style; p.prefill_rope_style = MK_ROPE_HF;
   p.att_scale = h->att_scale;
-  p.engine = c.engine == MK_ENGINE_SIMT ? MK_ENGINE_SIMT : MK_ENGINE_TCGEN05;
+  p.engine = MK_ENGINE_TCGEN05;
   p.epoch = h->epoch;
   p.att_epoch = h->att_epoch;
   p.qkv_ld = qkv_width(c);
   p.max_positions = c.max_positions;
   p.timeout_cycles = h->timeout_cycles;
-  if (const char* env = getenv("MEGABAKE_DEBUG_STOP")) p.debug_stop = atoi(env);
   p.trace = h->trace;
   p.trace_cap = h->trace ? h->trace_cap : 0;
+  p.lookahead = h->lookahead;
+  p.status_mirror = h->mirror;
+  p.ctrl = at<Control>(h, h->cv.ctrl);
+  p.att_xch = at<float>(h, h->cv.att_xch);
+  p.att_part = at<float>(h, h->cv.att_part);
+  if (h->cv.phases == 0) return;  // a view without decoder buffers (the static-scratch attention): the rest stays null
   p.phases = at<GemmPhase>(h, h->cv.phases);
   p.hidden_buf = at<bf16>(h, h->cv.hidden);
   p.qkv = at<bf16>(h, h->cv.qkv);
@@ -243,9 +250,6 @@ void base_params(mk_handle h, KParams& p) {
   p.qkv_ll = at<unsigned long long>(h, h->cv.qkv_ll);
   p.att_ll = at<unsigned long long>(h, h->cv.att_ll);
   p.attn_ll = at<unsigned long long>(h, h->cv.attn_ll);
-  p.att_xch = at<float>(h, h->cv.att_xch);
-  p.att_part = at<float>(h, h->cv.att_part);
-  p.ctrl = at<Control>(h, h->cv.ctrl);
   p.embed = static_cast<const bf16*>(h->weights.embed);
   p.cos_t = static_cast<const bf16*>(h->weights.rope_cos);
   p.sin_t = static_cast<const bf16*>(h->weights.rope_sin);
@@ -347,6 +351,9 @@ int mk_create(const mk_config* config, void* workspace, size_t workspace_bytes, 
   h->launches = 0;
   h->trace = nullptr;
   h->trace_cap = 0;
+  h->mirror = nullptr;
+  h->lookahead = 192 * 1024;
+  if (const char* env = getenv("MEGABAKE_LOOKAHEAD_KB")) h->lookahead = std::max(0, atoi(env)) * 1024;
   double ms = 2000.0;
   if (const char* env = getenv("MEGABAKE_WAIT_LIMIT_MS")) ms = atof(env) > 0 ? atof(env) : ms;
   h->timeout_cycles = static_cast<long long>(ms * static_cast<double>(khz));
@@ -599,7 +606,9 @@ bool small_launch_ok(mk_handle h, int capacity) {
 }
 
 int decode_once(mk_handle h, const int64_t* ids, const int64_t* positions, int batch, void* const* key_caches,
-                void* const* value_caches, int32_t* const* valid_lengths, int capacity, void* logits, void* stream);
+                void* const* value_caches, int32_t* const* valid_lengths, int capacity, void* logits, void* stream,
+                int64_t* tokens_out = nullptr, bool sample = false, const int64_t* all_ids = nullptr,
+                const int64_t* all_positions = nullptr, int all_batch = 0);
 
 // Copy the per-layer valid lengths into one array (the lengths live in separate caller tensors).
 struct LengthPointers { const int32_t* at[MK_MAX_LAYERS]; };
@@ -608,11 +617,40 @@ __global__ void snapshot_lengths(LengthPointers src, int32_t* dst, int layers) {
 }
 }  // namespace
 
+namespace {
+// One decode step (mk_decode), or one step of mk_decode_steps (`sample`: the kernel picks the greedy
+// tokens, stores them in tokens_out and as the next ids, and advances the positions).  Lock held.
+int decode_step(mk_handle h, const int64_t* ids, const int64_t* positions, int batch, void* const* key_caches,
+                void* const* value_caches, int32_t* const* valid_lengths, int capacity, void* logits, void* stream,
+                int64_t* tokens_out, bool sample);
+}  // namespace
+
 int mk_decode(mk_handle h, const int64_t* ids, const int64_t* positions, int batch, void* const* key_caches,
               void* const* value_caches, int32_t* const* valid_lengths, int capacity, void* logits, void* stream) {
   if (!h || !ids || !positions || !key_caches || !value_caches || !valid_lengths || !logits)
     return fail(MK_ERR_INVALID, "mk_decode: null argument");
   std::lock_guard<std::mutex> guard(h->lock);
+  return decode_step(h, ids, positions, batch, key_caches, value_caches, valid_lengths, capacity, logits, stream, nullptr, false);
+}
+
+int mk_decode_steps(mk_handle h, int64_t* ids, int64_t* positions, int batch, void* const* key_caches,
+                    void* const* value_caches, int32_t* const* valid_lengths, int capacity, int steps, int64_t* tokens_out,
+                    void* logits, void* stream) {
+  if (!h || !ids || !positions || !key_caches || !value_caches || !valid_lengths || !logits || !tokens_out)
+    return fail(MK_ERR_INVALID, "mk_decode_steps: null argument");
+  if (steps < 1) return fail(MK_ERR_INVALID, "mk_decode_steps: steps %d", steps);
+  std::lock_guard<std::mutex> guard(h->lock);
+  for (int step = 0; step < steps; ++step)
+    if (int e = decode_step(h, ids, positions, batch, key_caches, value_caches, valid_lengths, capacity, logits, stream,
+                            tokens_out + static_cast<size_t>(step) * batch, true))
+      return e;
+  return MK_OK;
+}
+
+namespace {
+int decode_step(mk_handle h, const int64_t* ids, const int64_t* positions, int batch, void* const* key_caches,
+                void* const* value_caches, int32_t* const* valid_lengths, int capacity, void* logits, void* stream,
+                int64_t* tokens_out, bool sample) {
   if (!h->bound) return fail(MK_ERR_UNBOUND, "mk_decode before mk_bind_weights");
   if (batch < 1 || batch > h->cfg.max_tokens) return fail(MK_ERR_INVALID, "mk_decode: batch %d outside [1, %d]", batch, h->cfg.max_tokens);
   if (capacity < 1) return fail(MK_ERR_INVALID, "mk_decode: capacity %d", capacity);
@@ -645,18 +683,27 @@ int mk_decode(mk_handle h, const int64_t* ids, const int64_t* positions, int bat
       kc2[l] = static_cast<uint8_t*>(key_caches[l]) + first * seq_bytes;
       vc2[l] = static_cast<uint8_t*>(value_caches[l]) + first * seq_bytes;
     }
-    if (int e = decode_once(h, ids, positions, first, key_caches, value_caches, len1, capacity, logits, stream)) return e;
+    // Both launches validate the ids and positions of the whole step, so that either both run or both refuse.
+    if (int e = decode_once(h, ids, positions, first, key_caches, value_caches, len1, capacity, logits, stream, tokens_out, sample,
+                            ids, positions, batch))
+      return e;
     return decode_once(h, ids + first, positions + first, batch - first, kc2, vc2, valid_lengths, capacity,
-                       static_cast<uint8_t*>(logits) + static_cast<size_t>(first) * h->cfg.vocab * 2, stream);
+                       static_cast<uint8_t*>(logits) + static_cast<size_t>(first) * h->cfg.vocab * 2, stream,
+                       tokens_out ? tokens_out + first : nullptr, sample, ids, positions, batch);
   }
-  return decode_once(h, ids, positions, batch, key_caches, value_caches, valid_lengths, capacity, logits, stream);
+  return decode_once(h, ids, positions, batch, key_caches, value_caches, valid_lengths, capacity, logits, stream, tokens_out, sample);
 }
+}  // namespace
 
 namespace {
 int decode_once(mk_handle h, const int64_t* ids, const int64_t* positions, int batch, void* const* key_caches,
-                void* const* value_caches, int32_t* const* valid_lengths, int capacity, void* logits, void* stream) {
+                void* const* value_caches, int32_t* const* valid_lengths, int capacity, void* logits, void* stream,
+                int64_t* tokens_out, bool sample, const int64_t* all_ids, const int64_t* all_positions, int all_batch) {
   KParams p;
   base_params(h, p);
+  p.check_ids = reinterpret_cast<const long long*>(all_ids);
+  p.check_pos = reinterpret_cast<const long long*>(all_positions);
+  p.check_m = all_ids ? all_batch : 0;
   const int L = h->cfg.layers;
   for (int l = 0; l < L; ++l) {
     p.kc[l] = key_caches[l];
@@ -678,9 +725,14 @@ int decode_once(mk_handle h, const int64_t* ids, const int64_t* positions, int b
     p.rowmode = 1;
   }
   p.stream_once = (ntt == 1);
-  p.ids = reinterpret_cast<const long long*>(ids);
-  p.pos = reinterpret_cast<const long long*>(positions);
+  p.ids = reinterpret_cast<long long*>(const_cast<int64_t*>(ids));
+  p.pos = reinterpret_cast<long long*>(const_cast<int64_t*>(positions));
   p.logits = static_cast<bf16*>(logits);
+  if (sample) {
+    p.sample = 1;
+    p.tokens_out = reinterpret_cast<long long*>(tokens_out);
+    if (!p.rowmode) p.nbar += 1;  // the sampler runs behind one more grid barrier (the row table already ends with one)
+  }
   return launch(h, p, stream, L, small);
 }
 }  // namespace
@@ -707,8 +759,8 @@ int mk_prefill(mk_handle h, const int64_t* ids, const int64_t* positions, const 
   p.n_gemm = 4 * L + 1;
   p.nbar = 6 * L;
   p.stream_once = (ntt == 1);
-  p.ids = reinterpret_cast<const long long*>(ids);
-  p.pos = reinterpret_cast<const long long*>(positions);
+  p.ids = reinterpret_cast<long long*>(const_cast<int64_t*>(ids));
+  p.pos = reinterpret_cast<long long*>(const_cast<int64_t*>(positions));
   p.mask = static_cast<const bf16*>(mask);
   p.logits = static_cast<bf16*>(logits);
   return launch(h, p, stream);
@@ -804,8 +856,30 @@ int mk_status(mk_handle h, void* stream, mk_status_info* out) {
     // Counters are in an unknown state after an aborted launch: start over.
     MK_CUDA(cudaMemset(at<Control>(h, h->cv.ctrl), 0, sizeof(Control)));
     h->epoch = 0;
+    if (h->mirror) *h->mirror = 0;
     return fail(MK_ERR_DEVICE_STATUS, "device status %d at site %d (cta %d, detail %d)", c.status, c.where, c.cta, c.detail);
   }
+  return MK_OK;
+}
+
+int mk_set_status_mirror(mk_handle h, int32_t* host_word) {
+  if (!h) return fail(MK_ERR_INVALID, "mk_set_status_mirror: null handle");
+  std::lock_guard<std::mutex> guard(h->lock);
+  if (host_word) {
+    void* device_view = nullptr;
+    MK_CUDA(cudaHostGetDevicePointer(&device_view, host_word, 0));  // fails unless the word is pinned, mapped host memory
+    *host_word = 0;
+    h->mirror = static_cast<volatile int*>(device_view);
+  } else {
+    h->mirror = nullptr;
+  }
+  return MK_OK;
+}
+
+int mk_debug_skew_barrier(mk_handle h, uint32_t delta) {
+  if (!h) return fail(MK_ERR_INVALID, "mk_debug_skew_barrier: null handle");
+  std::lock_guard<std::mutex> guard(h->lock);
+  h->epoch += delta;
   return MK_OK;
 }
 
@@ -905,6 +979,37 @@ int static_setup(StaticSlot& slot, int device, cudaStream_t stream) {
 
 extern "C" {
 
+// The status word and the abort flag of the static array, which no handle owns: synchronises
+// `stream`, copies them out and, if a launch was refused or gave up a wait, clears them and
+// restarts the barrier count, so that the next mk_kv_attention_static call on the device works
+// again (without this a timed-out wait would leave the abort flag set for the life of the process
+// and every later call would return at its first wait).  Allocates nothing.
+int mk_kv_attention_static_status(int device, void* stream, mk_status_info* out) {
+  if (device < 0 || device >= kStaticDevices)
+    return fail(MK_ERR_INVALID, "mk_kv_attention_static_status: device %d outside [0, %d)", device, kStaticDevices);
+  int current = -1;
+  MK_CUDA(cudaGetDevice(&current));
+  if (current != device)
+    return fail(MK_ERR_INVALID, "mk_kv_attention_static_status: device %d is not the current device (%d)", device, current);
+  StaticSlot& slot = g_static_slots[device];
+  std::lock_guard<std::mutex> guard(slot.lock);
+  if (out) out->status = out->where = out->cta = out->detail = 0;
+  if (!slot.ready) return MK_OK;  // nothing has run on this device yet
+  MK_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  Control c;
+  MK_CUDA(cudaMemcpy(&c, slot.base, sizeof(c), cudaMemcpyDeviceToHost));
+  if (out) {
+    out->status = c.status; out->where = c.where; out->cta = c.cta; out->detail = c.detail;
+  }
+  if (c.status != MK_STATUS_OK || c.abort) {
+    MK_CUDA(cudaMemset(slot.base, 0, sizeof(Control)));
+    slot.epoch = 0;
+    return fail(MK_ERR_DEVICE_STATUS, "static scratch: device status %d at site %d (cta %d, detail %d)", c.status, c.where,
+                c.cta, c.detail);
+  }
+  return MK_OK;
+}
+
 // Overlapping calls on one device (two streams, two threads) share the scratch and race:
 // callers serialise them.  The first call on a device does the set-up (symbol lookup,
 // function attributes, clearing the scratch on `stream`); make it before any stream capture.
@@ -954,6 +1059,7 @@ int mk_kv_attention_static(int q_heads, int kv_heads, int head_dim, const void* 
   view.timeout_cycles = slot.timeout_cycles;
   view.att_scale = static_cast<float>(std::pow(static_cast<double>(head_dim), -0.5));
   view.fma_ok = false; view.small_ll = false; view.row_ok = false; view.trace = nullptr; view.trace_cap = 0;
+  view.lookahead = 0; view.mirror = nullptr;
   if (int e = attention_fits(&view, capacity, "mk_kv_attention_static")) return e;
   KParams p;
   base_params(&view, p);

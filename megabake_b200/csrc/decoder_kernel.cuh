@@ -51,18 +51,7 @@ struct SmemMisc {
   uint8_t qstart[kChunkBars];  // producer: first ring granule of each chunk in flight (by sequence % kChunkBars)
   uint8_t qgran[kChunkBars];   // producer: granules of that chunk
   GemmPhase phase[2];  // worker-side copies of the current / next projection phase
-#ifdef MK_STAMPS
-  int stamp_base;
-  long long stamps[96];
-#endif
 };
-#ifdef MK_STAMPS
-#define MK_STAMP(cx, wtid, id) do { if ((wtid) == 0) { long long t_; asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_) :: "memory"); (cx).misc->stamps[(cx).misc->stamp_base + (id)] = t_; } } while (0)
-#define MK_STAMP_BASE(cx, wtid, base) do { if ((wtid) == 0) (cx).misc->stamp_base = (base); } while (0)
-#else
-#define MK_STAMP(cx, wtid, id) do { } while (0)
-#define MK_STAMP_BASE(cx, wtid, base) do { } while (0)
-#endif
 static_assert(sizeof(SmemMisc) <= kMiscBytes, "misc shared block too large");
 static_assert(kRingGranules < 256, "ring positions are kept in bytes");
 
@@ -94,6 +83,7 @@ __device__ __forceinline__ bool give_up(const Ctx& cx, int site, int detail) {
       cx.ctrl->where = site;
       cx.ctrl->cta = cx.cta;
       cx.ctrl->detail = detail;
+      if (cx.p->status_mirror) *cx.p->status_mirror = static_cast<int>(MK_STATUS_TIMEOUT);
     }
     atomicExch(&cx.ctrl->abort, 1u);
     __threadfence();
@@ -869,95 +859,6 @@ __device__ __forceinline__ uint4 residual_vec(const Ctx& cx, const GemmPhase* ph
   return pack8(f);
 }
 
-// Projection phase on the SIMT engine (bring-up / diagnostics): every worker
-// warp of the grid takes output rows round-robin and does plain dot products
-// over the whole reduction length (a K-split phase gets the full sum in slice 0
-// and zeros in the other slices).
-__device__ __noinline__ bool worker_gemm_simt(const Ctx& cx, int gp, int wtid) {
-  const KParams& p = *cx.p;
-  const GemmPhase* ph = &cx.misc->phase[gp & 1];
-  const int warp = wtid >> 5, lane = wtid & 31;
-  const int k = ph->k, nvec = k / 8;
-  int tb = kBBytes / (k * 2);
-  if (tb > kTok) tb = kTok;
-  if (tb < 1) tb = 1;
-  bf16* bs = reinterpret_cast<bf16*>(cx.smem_b);
-  const int nch = (ph->bmode == B_ATTN) ? *reinterpret_cast<volatile int*>(&cx.ctrl->att_nch) : 1;
-  int total_rows = 0;
-  for (int s = 0; s < (ph->nacc == 2 ? 1 : ph->nseg); ++s) total_rows += ph->n[s];
-  float v[2][kTok];
-  float pre[kTok];
-  for (int t0 = 0; t0 < p.m; t0 += tb) {
-    const int mt = min(tb, p.m - t0);
-    named_bar_sync(1, kWorkers);
-    if (ph->bmode == B_NORM) {
-      for (int item = wtid; item < mt * nvec; item += kWorkers) {
-        const int t = item / nvec, vec = item - t * nvec;
-        const uint4 xu = residual_vec(cx, ph, t0 + t, vec);
-        *reinterpret_cast<uint4*>(bs + t * k + vec * 8) = xu;
-        if (ph->h_out && (vec * cx.grid) / nvec == cx.cta)
-          __stcg(reinterpret_cast<uint4*>(ph->h_out + static_cast<size_t>(t0 + t) * k) + vec, xu);
-      }
-      named_bar_sync(1, kWorkers);
-      for (int t = warp; t < mt; t += kWorkerWarps) {
-        float sum = 0.f;
-        for (int vec = lane; vec < nvec; vec += 32) {
-          float f[8];
-          unpack8(*reinterpret_cast<const uint4*>(bs + t * k + vec * 8), f);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) sum = fmaf(f[e], f[e], sum);
-        }
-        sum = warp_sum(sum);
-        const float r = 1.0f / sqrtf(sum / static_cast<float>(k) + p.eps);
-        for (int vec = lane; vec < nvec; vec += 32) {
-          uint4* at = reinterpret_cast<uint4*>(bs + t * k + vec * 8);
-          *at = normalise_vec(*at, __ldg(reinterpret_cast<const uint4*>(ph->normw) + vec), r);
-        }
-      }
-    } else {
-      for (int item = wtid; item < mt * nvec; item += kWorkers) {
-        const int t = item / nvec, vec = item - t * nvec;
-        *reinterpret_cast<uint4*>(bs + t * k + vec * 8) = activation_vec(cx, ph, t0 + t, t, vec * 8, nch);
-      }
-    }
-    named_bar_sync(1, kWorkers);
-    for (int row = cx.cta * kWorkerWarps + warp; row < total_rows; row += cx.grid * kWorkerWarps) {
-      int seg = 0, n = row;
-      if (ph->nacc == 1) {
-        while (seg + 1 < ph->nseg && n >= ph->n[seg]) { n -= ph->n[seg]; ++seg; }
-      }
-      for (int a = 0; a < ph->nacc; ++a) {
-        const bf16* w = ph->w[ph->nacc == 2 ? a : seg];
-        const uint4* wrow = reinterpret_cast<const uint4*>(w + static_cast<size_t>(n) * k);
-        for (int t = 0; t < mt; ++t) v[a][t] = 0.f;
-        for (int vec = lane; vec < nvec; vec += 32) {
-          float wf[8], xf[8];
-          unpack8(__ldg(wrow + vec), wf);
-          for (int t = 0; t < mt; ++t) {
-            unpack8(*reinterpret_cast<const uint4*>(bs + t * k + vec * 8), xf);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[a][t] = fmaf(wf[e], xf[e], v[a][t]);
-          }
-        }
-        for (int t = 0; t < mt; ++t) v[a][t] = warp_sum(v[a][t]);
-      }
-      if (lane == 0) {
-        if (ph->epi == EPI_PARTIAL) {
-          store_partial<kTok>(cx, ph, 0, n, v[0], t0, mt);
-          for (int t = 0; t < mt; ++t) v[1][t] = 0.f;
-          for (int s8 = 1; s8 < ph->ksplit; ++s8) store_partial<kTok>(cx, ph, s8, n, v[1], t0, mt);
-        } else {
-          epilogue_prefetch<kTok>(cx, ph, seg, n, t0, mt, pre);
-          apply_epilogue<kTok>(cx, ph, seg, n, v, pre, t0, mt);
-        }
-      }
-    }
-  }
-  named_bar_sync(1, kWorkers);
-  prefetch_phase(cx, gp + 1, wtid);
-  return true;
-}
-
 // ---------------------------------------------------------------------------
 // workers: attention
 
@@ -1637,6 +1538,92 @@ __device__ __noinline__ void rope_phase(const Ctx& cx, int wtid) {
 }
 
 // ---------------------------------------------------------------------------
+// outputs of a launch that the prologue refused, and the device-side greedy sampler
+
+// A launch whose prologue found a bad id, position or a full cache does no work.  Its outputs are
+// filled with NaN so that a caller who reads them before looking at the status cannot mistake
+// uninitialised memory for logits (the reference raises at this point: src/megabake/lowering.py:229).
+__device__ __noinline__ void refuse_outputs(const Ctx& cx, int bad, int tid, int nthreads) {
+  const KParams& p = *cx.p;
+  bf16* out = nullptr;
+  long long count = 0;
+  if (p.mode == MODE_DECODE || p.mode == MODE_PREFILL) {
+    out = p.logits;
+    count = static_cast<long long>(p.m) * p.vocab;
+  } else if (p.mode == MODE_KVATT) {
+    out = p.op_out;
+    count = static_cast<long long>(p.batch) * p.q_heads * p.head_dim;
+  }
+  const bf16 nan = __ushort_as_bfloat16(0x7FC0);
+  for (long long i = static_cast<long long>(cx.cta) * nthreads + tid; out != nullptr && i < count;
+       i += static_cast<long long>(cx.grid) * nthreads)
+    out[i] = nan;
+  if (cx.cta == 0 && tid == 0) {
+    if (atomicCAS(&cx.ctrl->status, 0, bad) == 0) {
+      cx.ctrl->where = SITE_PROLOGUE;
+      cx.ctrl->cta = 0;
+      cx.ctrl->detail = 0;
+      if (p.status_mirror) *p.status_mirror = bad;
+    }
+    if (p.sample && p.tokens_out)
+      for (int t = 0; t < p.m; ++t) p.tokens_out[t] = -1;
+  }
+  // Keep the monotonic barrier counter consistent with what the host expects.
+  if (tid == 0 && p.nbar > 0) atomicAdd(&cx.ctrl->barrier, static_cast<uint32_t>(p.nbar));
+}
+
+// Greedy token of every sequence of the launch, taken from the bf16 logits the lm_head phase has
+// written (the caller has passed a grid barrier since): the largest value, the lowest index among
+// equal ones, as torch.argmax on the host would return.  CTA t serves token t.  The token goes to
+// tokens_out[t] and becomes the next launch's id; the position moves on by one.  The kCount calling
+// threads synchronise on named barrier kBarrier; `scratch` holds 64 words of shared memory.
+template <int kBarrier, int kCount>
+__device__ __noinline__ void greedy_sample(const Ctx& cx, int wtid, float* scratch) {
+  const KParams& p = *cx.p;
+  constexpr int nthreads = kCount;
+  auto sync = [] { named_bar_sync(kBarrier, kCount); };
+  const int lane = wtid & 31, warp = wtid >> 5, nwarps = nthreads >> 5;
+  int* scratch_idx = reinterpret_cast<int*>(scratch + 32);
+  for (int t = cx.cta; t < p.m; t += cx.grid) {
+    const bf16* row = p.logits + static_cast<size_t>(t) * p.vocab;
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    if ((p.vocab & 7) == 0) {
+      const uint4* vrow = reinterpret_cast<const uint4*>(row);
+      for (int v = wtid; v < p.vocab / 8; v += nthreads) {
+        float f[8];
+        unpack8(__ldcg(vrow + v), f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          if (f[e] > best) { best = f[e]; idx = v * 8 + e; }
+      }
+    } else {
+      for (int i = wtid; i < p.vocab; i += nthreads) {
+        const float f = ldcg_bf16(row + i);
+        if (f > best) { best = f; idx = i; }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+      if (ob > best || (ob == best && oi < idx)) { best = ob; idx = oi; }
+    }
+    sync();  // the scratch of the previous token has been read
+    if (lane == 0) { scratch[warp] = best; scratch_idx[warp] = idx; }
+    sync();
+    if (wtid == 0) {
+      for (int w = 1; w < nwarps; ++w)
+        if (scratch[w] > best || (scratch[w] == best && scratch_idx[w] < idx)) { best = scratch[w]; idx = scratch_idx[w]; }
+      if (idx == 0x7fffffff) idx = 0;  // every logit NaN
+      if (p.tokens_out) p.tokens_out[t] = idx;
+      p.ids[t] = idx;
+      p.pos[t] += 1;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // workers: whole-launch schedule
 
 __device__ void worker_loop(const Ctx& cx, int wtid) {
@@ -1645,10 +1632,7 @@ __device__ void worker_loop(const Ctx& cx, int wtid) {
   ws.tiles = 0; ws.passed = 0;
   ws.be_cnt[0] = ws.be_cnt[1] = 0;
   ws.outstanding[0] = ws.outstanding[1] = false;
-  auto gemm = [&](int gp) -> bool {
-    if (p.engine == MK_ENGINE_SIMT) return worker_gemm_simt(cx, gp, wtid);
-    return worker_gemm_tc(cx, gp, ws, wtid);
-  };
+  auto gemm = [&](int gp) -> bool { return worker_gemm_tc(cx, gp, ws, wtid); };
   const int q_size = p.q_heads * p.head_dim, kv_size = p.kv_heads * p.head_dim;
   AttnArgs A;
   A.knew = nullptr; A.vnew = nullptr; A.new_ld = 0; A.mask = nullptr;
@@ -1694,14 +1678,9 @@ __device__ void worker_loop(const Ctx& cx, int wtid) {
         __ldg(reinterpret_cast<const uint4*>(p.embed + id * p.hidden) + c);
   }
   const bool decode = (p.mode == MODE_DECODE);
-  int step = 0;
-#define MK_DEBUG_STEP() do { if (p.debug_stop && ++step >= p.debug_stop) return; } while (0)
-  MK_DEBUG_STEP();
   for (int layer = 0; layer < p.layers; ++layer) {
     if (!gemm(layer * 4 + 0)) return;                       // [RMSNorm] q, k, v (+bias)
-    MK_DEBUG_STEP();
     if (!grid_barrier(cx, ws, wtid)) return;
-    MK_DEBUG_STEP();
     A.q = p.qkv; A.q_ld = p.qkv_ld;
     A.out = p.attn; A.out_tstride = q_size; A.out_hstride = p.head_dim;
     A.stamp = p.att_epoch + static_cast<uint32_t>(layer) + 1u;
@@ -1724,22 +1703,20 @@ __device__ void worker_loop(const Ctx& cx, int wtid) {
     }
     if (!attention_phase(cx, A, wtid)) return;              // [RoPE] attention (+ KV append)
     trace_event(cx, wtid, EV_ATTENTION_DONE);
-    MK_DEBUG_STEP();
     if (!grid_barrier(cx, ws, wtid)) return;
     if (decode && cx.cta == 0 && wtid == 0) *p.len[layer] = A.len + 1;  // publish after the interval closes
-    MK_DEBUG_STEP();
     if (!gemm(layer * 4 + 1)) return;                       // o_proj + residual
-    MK_DEBUG_STEP();
     if (!grid_barrier(cx, ws, wtid)) return;
     if (!gemm(layer * 4 + 2)) return;                       // [RMSNorm] gate, up -> SiLU*up
-    MK_DEBUG_STEP();
     if (!grid_barrier(cx, ws, wtid)) return;
     if (!gemm(layer * 4 + 3)) return;                       // down + residual
-    MK_DEBUG_STEP();
     if (!grid_barrier(cx, ws, wtid)) return;
   }
-#undef MK_DEBUG_STEP
-  gemm(p.layers * 4);                                       // [final RMSNorm] lm_head
+  if (!gemm(p.layers * 4)) return;                          // [final RMSNorm] lm_head
+  if (p.sample) {
+    if (!grid_barrier(cx, ws, wtid)) return;                // every CTA's logits are out and nobody reads ids/positions any more
+    greedy_sample<1, kWorkers>(cx, wtid, reinterpret_cast<float*>(cx.smem_b));
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -1758,7 +1735,7 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
   cx.cta = blockIdx.x;
   cx.grid = gridDim.x;
   const int tid = threadIdx.x, warp = tid >> 5;
-  const bool tc = (p.engine == MK_ENGINE_TCGEN05) && p.n_gemm > 0;   // tensor-core roles (TMEM, MMA issuer)
+  const bool tc = p.n_gemm > 0;   // tensor-core roles (TMEM, MMA issuer)
   const bool ring = tc;  // weight producer
 
   if (tid == 0) {
@@ -1798,6 +1775,10 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
         const long long id = p.ids[t], pos = p.pos[t];
         if (id < 0 || id >= p.vocab || pos < 0 || pos >= p.max_positions) bad = MK_STATUS_BAD_INDEX;
       }
+      for (int t = tid; t < p.check_m; t += kThreads) {
+        const long long id = p.check_ids[t], pos = p.check_pos[t];
+        if (id < 0 || id >= p.vocab || pos < 0 || pos >= p.max_positions) bad = MK_STATUS_BAD_INDEX;
+      }
     }
     if (p.mode != MODE_PREFILL) {
       const int nl = (p.mode == MODE_KVATT) ? 1 : p.layers;
@@ -1812,15 +1793,7 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
   tc_fence_after();
   const int bad = *reinterpret_cast<volatile int*>(&cx.misc->bad);
   if (bad) {
-    if (tid == 0) {
-      if (cx.cta == 0 && atomicCAS(&cx.ctrl->status, 0, bad) == 0) {
-        cx.ctrl->where = SITE_PROLOGUE;
-        cx.ctrl->cta = 0;
-        cx.ctrl->detail = 0;
-      }
-      // Keep the monotonic barrier counter consistent with what the host expects.
-      if (p.nbar > 0) atomicAdd(&cx.ctrl->barrier, static_cast<uint32_t>(p.nbar));
-    }
+    refuse_outputs(cx, bad, tid, kThreads);
   } else if (warp == 0) {
     if (ring && tid == 0) producer_loop(cx);
   } else if (warp == 1) {

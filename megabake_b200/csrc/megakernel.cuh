@@ -25,11 +25,7 @@ constexpr int kBHalf = kBSlots / 2;
 constexpr int kBSlotBytes = kTok * 128;  // 2 KiB
 constexpr int kBBytes = kBSlots * kBSlotBytes;
 constexpr int kTmemCols = 64;            // 2 buffers x 2 accumulators x 16 columns
-#ifdef MK_STAMPS
-constexpr int kMiscBytes = 5120;
-#else
 constexpr int kMiscBytes = 4096;
-#endif
 constexpr int kSmemBytes = 1024 /*alignment slack*/ + kRingBytes + kBBytes + kMiscBytes;
 constexpr int kMaxChunks = 16;           // split-context chunks per (sequence, kv head)
 constexpr int kScoreBytes = 40960;       // fp32 scores of one attention unit (inside the B region)
@@ -121,7 +117,11 @@ struct KParams {
   int stream_once;    // 1: weights are read once per launch (L2 evict-first)
   int split;          // 1: this launch runs the split-K phase table (residual updates applied by the consumer)
   int rowmode;        // 1: one-token row table: stamped hand-offs everywhere, one grid barrier at the end of the launch
-  int debug_stop;     // bring-up aid: leave the schedule after this many steps (0 = run everything)
+  int lookahead;      // bytes of this CTA's coming weight copies that the producer keeps requested into L2 ahead of the ring (0 = off)
+  int sample;         // 1: after the logits, pick each sequence's greedy token on the device, store it in tokens_out and as the
+                      //    next id, and advance the position: the next launch needs no host round trip
+  long long* tokens_out;      // [m] with `sample`
+  volatile int* status_mirror;  // host-mapped copy of Control::status (pinned memory), or null
   int trace_cap;      // events per CTA in `trace` (0 = tracing off)
   unsigned long long* trace;  // [grid][trace_cap] (event code << 56) | %globaltimer ns
   long long timeout_cycles;
@@ -133,8 +133,11 @@ struct KParams {
   float* att_xch;     // [row groups][kMaxChunks][kExchangeFloats]
   float* att_part;    // [batch * q_heads][kMaxChunks][head_dim]
   Control* ctrl;
-  const long long* ids;
-  const long long* pos;
+  long long* ids;     // read by every CTA; rewritten at the very end of a launch with `sample`
+  long long* pos;
+  const long long* check_ids;  // when a step is cut into two launches: the ids and positions of the whole step,
+  const long long* check_pos;  // validated by both so that they run or refuse together
+  int check_m;
   const bf16* mask;
   const bf16 *embed, *cos_t, *sin_t;
   bf16* logits;

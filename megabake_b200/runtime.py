@@ -101,6 +101,7 @@ class DecoderKernel:
         self._bound_ptrs: tuple[int, ...] | None = None
         self._state_key = None
         self._state_arrays = None
+        self._install_status_mirror()
         if tables is None:
             tables = rope_tables(config, self.max_positions, device=self.device)
         self.tables = tables
@@ -122,6 +123,20 @@ class DecoderKernel:
         if code in (_native.MK_ERR_ALIGNMENT, _native.MK_ERR_INVALID, _native.MK_ERR_UNBOUND):
             raise self._compiler_error(stage, error)
         raise error
+
+    def _install_status_mirror(self) -> None:
+        """One pinned int32 the kernel also writes its status to: `raise_if_failed` reads it
+        without synchronising, so a launch that was refused (full cache, bad id) or gave up a
+        wait is reported at the caller's next call instead of handing out NaN silently
+        (the reference raises: src/megabake/lowering.py:229, src/megabake/compiler.py:2690)."""
+        self._mirror = torch.zeros(1, dtype=torch.int32).pin_memory()
+        with torch.cuda.device(self.device):
+            self._call("mk_set_status_mirror", self.lib.mk_set_status_mirror(self._handle, self._mirror.data_ptr()))
+
+    def raise_if_failed(self) -> None:
+        """Non-blocking: raise what an earlier launch reported, if anything."""
+        if int(self._mirror[0]) != 0:
+            self.check()
 
     def close(self) -> None:
         handle, self._handle = getattr(self, "_handle", None), None
@@ -197,16 +212,6 @@ class DecoderKernel:
         return True
 
     # ------------------------------------------------------------------ launches
-    def _state_pointers(self, key_caches, value_caches, valid_lengths):
-        key = tuple(t.data_ptr() for t in key_caches) + tuple(t.data_ptr() for t in value_caches) + tuple(
-            t.data_ptr() for t in valid_lengths)
-        if key != self._state_key:
-            count = self.config.layers
-            arrays = tuple((ctypes.c_void_p * count)(*[t.data_ptr() for t in group])
-                           for group in (key_caches, value_caches, valid_lengths))
-            self._state_key, self._state_arrays = key, arrays
-        return self._state_arrays
-
     def decode(
         self,
         input_ids: torch.Tensor,
@@ -224,23 +229,65 @@ class DecoderKernel:
             raise RuntimeError("megabake kv_attention supports one-token decode only")
         _require(input_ids, "input_ids", dtype=torch.int64, device=self.device, shape=(batch, 1))
         _require(position_ids, "position_ids", dtype=torch.int64, device=self.device, shape=(batch, 1))
-        if not (len(key_caches) == len(value_caches) == len(valid_lengths) == config.layers):
-            raise ValueError(f"expected {3 * config.layers} state tensors, got "
-                             f"{len(key_caches) + len(value_caches) + len(valid_lengths)}")
-        capacity = key_caches[0].shape[1]
-        cache_shape = (batch, capacity, config.kv_heads, config.head_dim)
-        if self._state_key is None or self._state_key[0] != key_caches[0].data_ptr():
-            for layer in range(config.layers):
-                _require(key_caches[layer], f"key cache {layer}", dtype=torch.bfloat16, device=self.device, shape=cache_shape)
-                _require(value_caches[layer], f"value cache {layer}", dtype=torch.bfloat16, device=self.device, shape=cache_shape)
-                _require(valid_lengths[layer], f"valid length {layer}", dtype=torch.int32, device=self.device, shape=(1,))
-        keys, values, lengths = self._state_pointers(key_caches, value_caches, valid_lengths)
+        keys, values, lengths, capacity = self._checked_state(batch, key_caches, value_caches, valid_lengths)
+        self.raise_if_failed()
         logits = torch.empty((batch, 1, config.vocab), dtype=torch.bfloat16, device=self.device)
         with self._lock, torch.cuda.device(self.device):
             self._call("mk_decode", self.lib.mk_decode(
                 self._handle, input_ids.data_ptr(), position_ids.data_ptr(), batch, keys, values, lengths,
                 capacity, logits.data_ptr(), self._stream()), stage="input-binding")
         return logits
+
+    def _checked_state(self, batch, key_caches, value_caches, valid_lengths):
+        """Pointer arrays of the caller's state; shapes and dtypes are validated whenever any
+        state tensor or the batch differs from the last call's."""
+        config = self.config
+        if not (len(key_caches) == len(value_caches) == len(valid_lengths) == config.layers):
+            raise ValueError(f"expected {3 * config.layers} state tensors, got "
+                             f"{len(key_caches) + len(value_caches) + len(valid_lengths)}")
+        capacity = key_caches[0].shape[1]
+        key = (batch,) + tuple(t.data_ptr() for group in (key_caches, value_caches, valid_lengths) for t in group)
+        if key != self._state_key:
+            cache_shape = (batch, capacity, config.kv_heads, config.head_dim)
+            for layer in range(config.layers):
+                _require(key_caches[layer], f"key cache {layer}", dtype=torch.bfloat16, device=self.device, shape=cache_shape)
+                _require(value_caches[layer], f"value cache {layer}", dtype=torch.bfloat16, device=self.device, shape=cache_shape)
+                _require(valid_lengths[layer], f"valid length {layer}", dtype=torch.int32, device=self.device, shape=(1,))
+            count = config.layers
+            self._state_arrays = tuple((ctypes.c_void_p * count)(*[t.data_ptr() for t in group])
+                                       for group in (key_caches, value_caches, valid_lengths))
+            self._state_key = key
+        return (*self._state_arrays, capacity)
+
+    def decode_steps(
+        self,
+        input_ids: torch.Tensor,
+        position_ids: torch.Tensor,
+        key_caches: Sequence[torch.Tensor],
+        value_caches: Sequence[torch.Tensor],
+        valid_lengths: Sequence[torch.Tensor],
+        steps: int,
+        return_logits: bool = False,
+    ):
+        """``steps`` greedy decode steps with no host round trip in between: the kernel picks each
+        token (``torch.argmax`` semantics on the bf16 logits), feeds it back as the next id and
+        advances the position.  ``input_ids`` and ``position_ids`` ([batch, 1] int64) are updated in
+        place and hold the next step's inputs afterwards.  Returns the tokens [batch, steps]
+        (and the last step's logits [batch, 1, vocab] if asked).  No synchronisation."""
+        config = self.config
+        batch = input_ids.shape[0]
+        _require(input_ids, "input_ids", dtype=torch.int64, device=self.device, shape=(batch, 1))
+        _require(position_ids, "position_ids", dtype=torch.int64, device=self.device, shape=(batch, 1))
+        keys, values, lengths, capacity = self._checked_state(batch, key_caches, value_caches, valid_lengths)
+        self.raise_if_failed()
+        tokens = torch.empty((steps, batch), dtype=torch.int64, device=self.device)
+        logits = torch.empty((batch, 1, config.vocab), dtype=torch.bfloat16, device=self.device)
+        with self._lock, torch.cuda.device(self.device):
+            self._call("mk_decode_steps", self.lib.mk_decode_steps(
+                self._handle, input_ids.data_ptr(), position_ids.data_ptr(), batch, keys, values, lengths,
+                capacity, int(steps), tokens.data_ptr(), logits.data_ptr(), self._stream()), stage="input-binding")
+        tokens = tokens.transpose(0, 1)
+        return (tokens, logits) if return_logits else tokens
 
     def prefill(self, input_ids: torch.Tensor, position_ids: torch.Tensor | None = None,
                 mask: torch.Tensor | None = None) -> torch.Tensor:
@@ -253,6 +300,7 @@ class DecoderKernel:
         _require(position_ids, "position_ids", dtype=torch.int64, device=self.device, shape=(batch, sequence))
         if mask is not None:
             _require(mask, "attention mask", dtype=torch.bfloat16, device=self.device, shape=(batch, 1, sequence, sequence))
+        self.raise_if_failed()
         logits = torch.empty((batch, sequence, self.config.vocab), dtype=torch.bfloat16, device=self.device)
         with self._lock, torch.cuda.device(self.device):
             self._call("mk_prefill", self.lib.mk_prefill(
@@ -283,6 +331,7 @@ class DecoderKernel:
         for name, tensor in (("source", source), ("key", key), ("value", value), ("key_cache", key_cache), ("value_cache", value_cache)):
             _require(tensor, name, dtype=torch.bfloat16, device=self.device)
         _require(valid_length, "valid_length", dtype=torch.int32, device=self.device, shape=(1,))
+        self.raise_if_failed()
         out = torch.empty((batch * heads, 1, dim), dtype=torch.bfloat16, device=self.device)
         with self._lock, torch.cuda.device(self.device):
             self._call("mk_kv_attention", self.lib.mk_kv_attention(
@@ -376,6 +425,7 @@ class AttentionKernels:
             if code != _native.MK_OK:
                 raise CompilerError(CompilerDiagnostic("plan-search", self.lib.mk_last_error().decode(errors="replace")))
         self._handle = handle
+        self._install_status_mirror()
 
     @classmethod
     def for_shape(cls, q_heads: int, kv_heads: int, head_dim: int, tokens: int, device: torch.device) -> "AttentionKernels":
@@ -399,3 +449,5 @@ class AttentionKernels:
     attention = DecoderKernel.attention
     status = DecoderKernel.status
     check = DecoderKernel.check
+    raise_if_failed = DecoderKernel.raise_if_failed
+    _install_status_mirror = DecoderKernel._install_status_mirror

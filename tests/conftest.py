@@ -1,4 +1,5 @@
 import json
+import os
 import sys
 from pathlib import Path
 
@@ -14,6 +15,16 @@ GOLDEN = ROOT / "tests" / "golden"
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+def record_stat(name: str, **values) -> None:
+    """Measured parity figures (mismatch counts, relative L2, first diverging step) as one JSON line
+    per call in the file MEGABAKE_PARITY_LOG names, so that the asserted bounds can be set to what
+    was measured; without the variable nothing is written."""
+    path = os.environ.get("MEGABAKE_PARITY_LOG")
+    if path:
+        with open(path, "a") as handle:
+            handle.write(json.dumps({"name": name, **values}) + "\n")
 
 
 def load_golden(name: str):

@@ -30,7 +30,7 @@ def make_kernel(config, weights, device, **kwargs):
 
 
 # --------------------------------------------------------------------------- projections
-@pytest.mark.parametrize("engine", ["tcgen05", "fma", "simt"])
+@pytest.mark.parametrize("engine", ["tcgen05", "fma"])
 @pytest.mark.parametrize("shape", [(1, 128, 64), (1, 256, 2048), (4, 576, 576), (3, 192, 576), (1, 2048, 8192),
                                    (16, 2048, 2048), (20, 1024, 1024), (2, 896, 4864), (5, 100, 128)])
 def test_linear_matches_fp32_reference(device, engine, shape):
@@ -94,7 +94,7 @@ def run_golden_decode(name, device, engine, steps=None, deep=False):
     return ties, run
 
 
-@pytest.mark.parametrize("engine", ["tcgen05", "fma", "simt"])
+@pytest.mark.parametrize("engine", ["tcgen05", "fma"])
 @pytest.mark.parametrize("name", ["tiny", "tiny_hf"])
 def test_decode_tiny_matches_reference(device, name, engine):
     ties, _ = run_golden_decode(name, device, engine)
