@@ -72,6 +72,13 @@ typedef struct mk_config {
   int32_t max_positions; /* rows of the cos/sin tables */
   int32_t engine;        /* MK_ENGINE_* */
   int32_t sm_limit;      /* 0: one CTA per SM on the whole GPU; >0: use this many CTAs */
+  /* Tensor parallel (0 or 1: off).  With tp_size > 1 this handle is one rank of a group on one
+   * node: q_heads, kv_heads and intermediate are the rank's shard (q/k/v and gate/up sharded by
+   * output rows, o and down by input columns), hidden is whole, vocab is the rows of this rank's
+   * lm_head shard, embed_rows the rows of the (replicated) embedding table. */
+  int32_t tp_size;
+  int32_t tp_rank;
+  int32_t embed_rows;    /* 0: same as vocab */
 } mk_config;
 
 typedef struct mk_layer_weights {
@@ -202,6 +209,33 @@ int mk_status(mk_handle handle, void* stream, mk_status_info* out);
  * synchronisation, before its next call.  mk_status clears the word when it resets the handle.
  * Reference: none (the reference traps; src/megabake/bodies/attention.py:540-543). */
 int mk_set_status_mirror(mk_handle handle, int32_t* host_word);
+
+/* Tensor-parallel decode (benchmark configuration "Llama-3-8B shape, heads and MLP columns sharded,
+ * all-reduce after o_proj and down_proj").  The reference is single-device
+ * (src/megabake/compiler.py:1518-1528 rejects inputs on more than one device), so these entry
+ * points have no counterpart there.  Every rank is one process with one GPU and one handle created
+ * with tp_size/tp_rank set.  Each rank owns an exchange buffer of mk_tp_exchange_bytes bytes
+ * (256-byte aligned, plain cudaMalloc memory, zeroed) and makes it addressable by its peers
+ * (mk_ipc_export / mk_ipc_open, or peer access inside one process); mk_tp_bind takes the tp_size
+ * addresses, index = rank, as THIS process sees them.  After every rank has bound, the group
+ * synchronises once on the host; from then on each mk_decode / mk_prefill call is made by all
+ * ranks with the same batch and finishes its all-reduces inside the kernel: fp32 partial sums are
+ * stored into every rank's buffer over NVLink, a stamped flag per source rank says they are there,
+ * every wait is bounded (MK_STATUS_TIMEOUT names the rank that did not arrive), and each rank adds
+ * the partial sums in rank order.  logits are this rank's vocabulary shard, bf16 [batch, vocab]. */
+size_t mk_tp_exchange_bytes(const mk_config* config);
+int mk_tp_bind(mk_handle handle, void* const* exchange, size_t exchange_bytes, void* stream);
+
+/* A device allocation made addressable from another process on the same node (CUDA IPC):
+ * export in the owner, open in the peer (peer access is enabled on first use), close when done.
+ * `pointer` may lie inside a larger allocation: the offset travels with the handle. */
+typedef struct mk_ipc_handle {
+  unsigned char bytes[64];
+  uint64_t offset;
+} mk_ipc_handle;
+int mk_ipc_export(void* pointer, mk_ipc_handle* out);
+int mk_ipc_open(const mk_ipc_handle* in, void** pointer, void** base_out);
+int mk_ipc_close(void* base);
 
 /* Failure-detection hook for tests: adds `delta` to the grid-barrier count the host expects, so
  * that the next launch's first grid barrier can never be reached and its bounded wait

@@ -29,6 +29,7 @@ EXPORTS = (
     "mk_workspace_bytes", "mk_create", "mk_bind_weights", "mk_decode", "mk_prefill", "mk_linear",
     "mk_kv_attention", "mk_kv_attention_static", "mk_kv_attention_static_status", "mk_attention", "mk_status", "mk_set_trace",
     "mk_launch_info", "mk_last_error", "mk_destroy", "mk_decode_steps", "mk_set_status_mirror", "mk_debug_skew_barrier",
+    "mk_tp_exchange_bytes", "mk_tp_bind", "mk_ipc_export", "mk_ipc_open", "mk_ipc_close",
 )
 
 
@@ -38,6 +39,7 @@ class MkConfig(Structure):
         ("head_dim", c_int32), ("intermediate", c_int32), ("vocab", c_int32), ("rms_eps", c_float),
         ("qkv_bias", c_int32), ("rope_style", c_int32), ("max_tokens", c_int32),
         ("max_positions", c_int32), ("engine", c_int32), ("sm_limit", c_int32),
+        ("tp_size", c_int32), ("tp_rank", c_int32), ("embed_rows", c_int32),
     ]
 
 
@@ -51,6 +53,10 @@ class MkWeights(Structure):
         ("embed", c_void_p), ("final_norm", c_void_p), ("lm_head", c_void_p),
         ("rope_cos", c_void_p), ("rope_sin", c_void_p), ("layers", POINTER(MkLayerWeights)),
     ]
+
+
+class MkIpcHandle(Structure):
+    _fields_ = [("bytes", ctypes.c_ubyte * 64), ("offset", ctypes.c_uint64)]
 
 
 class MkStatusInfo(Structure):
@@ -114,6 +120,16 @@ def load() -> ctypes.CDLL:
         c_void_p, c_void_p, c_void_p, c_int, POINTER(c_void_p), POINTER(c_void_p), POINTER(c_void_p),
         c_int, c_int, c_void_p, c_void_p, c_void_p,
     ]
+    lib.mk_tp_exchange_bytes.restype = c_size_t
+    lib.mk_tp_exchange_bytes.argtypes = [POINTER(MkConfig)]
+    lib.mk_tp_bind.restype = c_int
+    lib.mk_tp_bind.argtypes = [c_void_p, POINTER(c_void_p), c_size_t, c_void_p]
+    lib.mk_ipc_export.restype = c_int
+    lib.mk_ipc_export.argtypes = [c_void_p, POINTER(MkIpcHandle)]
+    lib.mk_ipc_open.restype = c_int
+    lib.mk_ipc_open.argtypes = [POINTER(MkIpcHandle), POINTER(c_void_p), POINTER(c_void_p)]
+    lib.mk_ipc_close.restype = c_int
+    lib.mk_ipc_close.argtypes = [c_void_p]
     lib.mk_debug_skew_barrier.restype = c_int
     lib.mk_debug_skew_barrier.argtypes = [c_void_p, ctypes.c_uint32]
     lib.mk_set_status_mirror.restype = c_int

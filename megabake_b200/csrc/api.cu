@@ -92,6 +92,9 @@ int check_config(const mk_config& c) {
   if (c.engine != MK_ENGINE_TCGEN05 && c.engine != MK_ENGINE_FMA && c.engine != MK_ENGINE_AUTO)
     return fail(MK_ERR_INVALID, "config: engine");
   if (c.rope_style != MK_ROPE_HF && c.rope_style != MK_ROPE_HALF_SWAP) return fail(MK_ERR_INVALID, "config: rope_style");
+  if (c.tp_size < 0 || c.tp_size > kMaxTp) return fail(MK_ERR_UNSUPPORTED, "config: tensor-parallel groups have 1..%d ranks", kMaxTp);
+  if (c.tp_size > 1 && (c.tp_rank < 0 || c.tp_rank >= c.tp_size)) return fail(MK_ERR_INVALID, "config: tp_rank outside the group");
+  if (c.embed_rows < 0) return fail(MK_ERR_INVALID, "config: embed_rows");
   return MK_OK;
 }
 
@@ -153,7 +156,9 @@ struct mk_handle_s {
   bool small_ll;  // its q/k/v phases hand their outputs to attention as stamped words (one grid barrier fewer per layer)
   unsigned long long* trace;
   int trace_cap;
-  int lookahead;        // bytes of weight look-ahead into L2 per CTA (small-launch kernel)
+  uint32_t tp_epoch;    // all-reduces launched so far (tensor parallel)
+  uint8_t* tp_peer[kMaxTp];
+  bool tp_bound;
   volatile int* mirror;  // host-mapped status word, or null
   std::mutex lock;
 };
@@ -219,13 +224,18 @@ void finish_phase(GemmPhase& ph, int grid, bool allow_split, int max_rows = kTil
 
 // Can launches of at most kSplitTokens tokens use the split-K table?  Its
 // consumer-side residual update keeps a whole hidden row in the activation slots.
-bool split_table_ok(const mk_config& c) { return c.hidden / kChunkK <= kBSlots; }
+bool split_table_ok(const mk_config& c) { return c.hidden / kChunkK <= kBSlots && c.tp_size <= 1; }
 
 void base_params(mk_handle h, KParams& p) {
   memset(&p, 0, sizeof(p));
   const mk_config& c = h->cfg;
   p.hidden = c.hidden; p.layers = c.layers; p.q_heads = c.q_heads; p.kv_heads = c.kv_heads;
   p.head_dim = c.head_dim; p.inter = c.intermediate; p.vocab = c.vocab; p.eps = c.rms_eps;
+  p.embed_rows = c.embed_rows > 0 ? c.embed_rows : c.vocab;
+  p.tp_size = c.tp_size > 1 ? c.tp_size : 1;
+  p.tp_rank = c.tp_size > 1 ? c.tp_rank : 0;
+  p.tp_epoch = h->tp_epoch;
+  for (int r = 0; r < kMaxTp; ++r) p.tp_peer[r] = h->tp_peer[r];
   p.rope_style = c.rope_style; p.prefill_rope_style = MK_ROPE_HF;
   p.att_scale = h->att_scale;
   p.engine = MK_ENGINE_TCGEN05;
@@ -236,7 +246,6 @@ void base_params(mk_handle h, KParams& p) {
   p.timeout_cycles = h->timeout_cycles;
   p.trace = h->trace;
   p.trace_cap = h->trace ? h->trace_cap : 0;
-  p.lookahead = h->lookahead;
   p.status_mirror = h->mirror;
   p.ctrl = at<Control>(h, h->cv.ctrl);
   p.att_xch = at<float>(h, h->cv.att_xch);
@@ -352,8 +361,9 @@ int mk_create(const mk_config* config, void* workspace, size_t workspace_bytes, 
   h->trace = nullptr;
   h->trace_cap = 0;
   h->mirror = nullptr;
-  h->lookahead = 192 * 1024;
-  if (const char* env = getenv("MEGABAKE_LOOKAHEAD_KB")) h->lookahead = std::max(0, atoi(env)) * 1024;
+  h->tp_epoch = 0;
+  h->tp_bound = false;
+  for (int r = 0; r < kMaxTp; ++r) h->tp_peer[r] = nullptr;
   double ms = 2000.0;
   if (const char* env = getenv("MEGABAKE_WAIT_LIMIT_MS")) ms = atof(env) > 0 ? atof(env) : ms;
   h->timeout_cycles = static_cast<long long>(ms * static_cast<double>(khz));
@@ -453,6 +463,10 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
       ph[3].epi = split ? EPI_PARTIAL : EPI_RESIDUAL; ph[3].bmode = B_PLAIN;
       ph[3].src = act; ph[3].src_ld = c.intermediate; ph[3].dst = hidden_a; ph[3].dst_ld = c.hidden;
       ph[3].partial = partial;
+      if (c.tp_size > 1) {  // tensor parallel: the residual add moves behind the all-reduce (tp_allreduce)
+        ph[1].epi = EPI_TP; ph[1].tp_buf = 0;
+        ph[3].epi = EPI_TP; ph[3].tp_buf = 1;
+      }
       for (int i = 0; i < 4; ++i) finish_phase(ph[i], h->grid, split && ph[i].epi == EPI_PARTIAL);
       if (split) {
         ph[2].add_parts = ph[1].ksplit; ph[2].partial = partial; ph[2].h_out = hidden_a;
@@ -728,12 +742,19 @@ int decode_once(mk_handle h, const int64_t* ids, const int64_t* positions, int b
   p.ids = reinterpret_cast<long long*>(const_cast<int64_t*>(ids));
   p.pos = reinterpret_cast<long long*>(const_cast<int64_t*>(positions));
   p.logits = static_cast<bf16*>(logits);
+  if (p.tp_size > 1) {
+    if (!h->tp_bound) return fail(MK_ERR_UNBOUND, "mk_decode: tensor-parallel handle without mk_tp_bind");
+    if (sample) return fail(MK_ERR_UNSUPPORTED, "mk_decode_steps: the device-side sampler needs the whole vocabulary on one rank");
+    p.nbar += 2 * L;  // one more grid barrier behind each of the two all-reduces of a layer
+  }
   if (sample) {
     p.sample = 1;
     p.tokens_out = reinterpret_cast<long long*>(tokens_out);
     if (!p.rowmode) p.nbar += 1;  // the sampler runs behind one more grid barrier (the row table already ends with one)
   }
-  return launch(h, p, stream, L, small);
+  if (int e = launch(h, p, stream, L, small)) return e;
+  if (p.tp_size > 1) h->tp_epoch += 2u * static_cast<uint32_t>(L);
+  return MK_OK;
 }
 }  // namespace
 
@@ -763,7 +784,13 @@ int mk_prefill(mk_handle h, const int64_t* ids, const int64_t* positions, const 
   p.pos = reinterpret_cast<long long*>(const_cast<int64_t*>(positions));
   p.mask = static_cast<const bf16*>(mask);
   p.logits = static_cast<bf16*>(logits);
-  return launch(h, p, stream);
+  if (p.tp_size > 1) {
+    if (!h->tp_bound) return fail(MK_ERR_UNBOUND, "mk_prefill: tensor-parallel handle without mk_tp_bind");
+    p.nbar += 2 * L;
+  }
+  if (int e = launch(h, p, stream)) return e;
+  if (p.tp_size > 1) h->tp_epoch += 2u * static_cast<uint32_t>(L);
+  return MK_OK;
 }
 
 int mk_linear(mk_handle h, const void* x, const void* weight, const void* bias, void* y, int m, int n, int k,
@@ -873,6 +900,69 @@ int mk_set_status_mirror(mk_handle h, int32_t* host_word) {
   } else {
     h->mirror = nullptr;
   }
+  return MK_OK;
+}
+
+size_t mk_tp_exchange_bytes(const mk_config* config) {
+  if (!config || check_config(*config) != MK_OK || config->tp_size < 2) return 0;
+  return kTpFlagBytes + 2 * static_cast<size_t>(config->tp_size) * config->max_tokens * config->hidden * sizeof(float);
+}
+
+int mk_tp_bind(mk_handle h, void* const* exchange, size_t exchange_bytes, void* stream) {
+  if (!h || !exchange) return fail(MK_ERR_INVALID, "mk_tp_bind: null argument");
+  std::lock_guard<std::mutex> guard(h->lock);
+  const mk_config& c = h->cfg;
+  if (c.tp_size < 2) return fail(MK_ERR_INVALID, "mk_tp_bind: the handle was not created for a tensor-parallel group");
+  if (exchange_bytes < mk_tp_exchange_bytes(&c))
+    return fail(MK_ERR_WORKSPACE, "mk_tp_bind: exchange buffers have %zu bytes, %zu needed", exchange_bytes, mk_tp_exchange_bytes(&c));
+  for (int r = 0; r < c.tp_size; ++r) {
+    if (!exchange[r]) return fail(MK_ERR_INVALID, "mk_tp_bind: rank %d has no exchange buffer", r);
+    if (reinterpret_cast<uintptr_t>(exchange[r]) % 256) return fail(MK_ERR_ALIGNMENT, "mk_tp_bind: exchange buffers must be 256-byte aligned");
+    h->tp_peer[r] = static_cast<uint8_t*>(exchange[r]);
+  }
+  // This rank's own flags start at zero; stamps count up from one.  (Every rank clears its own before any launch:
+  // the caller synchronises the group between mk_tp_bind and the first decode.)
+  MK_CUDA(cudaMemsetAsync(h->tp_peer[c.tp_rank], 0, kTpFlagBytes, static_cast<cudaStream_t>(stream)));
+  h->tp_epoch = 0;
+  h->tp_bound = true;
+  return MK_OK;
+}
+
+int mk_ipc_export(void* pointer, mk_ipc_handle* out) {
+  if (!pointer || !out) return fail(MK_ERR_INVALID, "mk_ipc_export: null argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) <= sizeof(out->bytes), "handle does not fit");
+  cudaIpcMemHandle_t handle;
+  MK_CUDA(cudaIpcGetMemHandle(&handle, pointer));
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult found;
+  if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &found) != cudaSuccess ||
+      found != cudaDriverEntryPointSuccess)
+    return fail(MK_ERR_CUDA, "cuMemGetAddressRange is not available from this driver");
+  const CUresult r = reinterpret_cast<CUresult (*)(CUdeviceptr*, size_t*, CUdeviceptr)>(fn)(
+      &base, &size, reinterpret_cast<CUdeviceptr>(pointer));
+  if (r != CUDA_SUCCESS) return fail(MK_ERR_CUDA, "cuMemGetAddressRange failed with %d", static_cast<int>(r));
+  memset(out, 0, sizeof(*out));
+  memcpy(out->bytes, &handle, sizeof(handle));
+  out->offset = static_cast<uint64_t>(reinterpret_cast<CUdeviceptr>(pointer) - base);
+  return MK_OK;
+}
+
+int mk_ipc_open(const mk_ipc_handle* in, void** pointer, void** base_out) {
+  if (!in || !pointer || !base_out) return fail(MK_ERR_INVALID, "mk_ipc_open: null argument");
+  cudaIpcMemHandle_t handle;
+  memcpy(&handle, in->bytes, sizeof(handle));
+  void* base = nullptr;
+  MK_CUDA(cudaIpcOpenMemHandle(&base, handle, cudaIpcMemLazyEnablePeerAccess));
+  *base_out = base;
+  *pointer = static_cast<uint8_t*>(base) + in->offset;
+  return MK_OK;
+}
+
+int mk_ipc_close(void* base) {
+  if (!base) return MK_OK;
+  MK_CUDA(cudaIpcCloseMemHandle(base));
   return MK_OK;
 }
 
@@ -1059,7 +1149,9 @@ int mk_kv_attention_static(int q_heads, int kv_heads, int head_dim, const void* 
   view.timeout_cycles = slot.timeout_cycles;
   view.att_scale = static_cast<float>(std::pow(static_cast<double>(head_dim), -0.5));
   view.fma_ok = false; view.small_ll = false; view.row_ok = false; view.trace = nullptr; view.trace_cap = 0;
-  view.lookahead = 0; view.mirror = nullptr;
+  view.mirror = nullptr;
+  view.tp_epoch = 0; view.tp_bound = false;
+  for (int r = 0; r < kMaxTp; ++r) view.tp_peer[r] = nullptr;
   if (int e = attention_fits(&view, capacity, "mk_kv_attention_static")) return e;
   KParams p;
   base_params(&view, p);

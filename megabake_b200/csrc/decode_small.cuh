@@ -231,68 +231,22 @@ __device__ __noinline__ bool small_stage_cols(const Ctx& cx, const GemmPhase* ph
   const int per_token = count * 8;
   const int items = per_token * mt;
   bool fresh = true;
-  if (ph->ll_src != nullptr && ph->bmode == B_PLAIN) {
-    // Stamped bf16 pairs written by the producing phase's epilogues: waiting for the stamps is the
-    // synchronisation.  A thread's (up to four) vectors are requested together and only a stale
-    // batch is read again: one L2 round trip per poll instead of one per vector.
-    constexpr int kBatch = 4;
-#pragma unroll 1
-    for (int item0 = wtid; item0 < items; item0 += kBatch * kSmallWorkers) {
-      const unsigned long long* words[kBatch];
-      int tok[kBatch], rem_of[kBatch];
-#pragma unroll
-      for (int j = 0; j < kBatch; ++j) {
-        const int item = min(item0 + j * kSmallWorkers, items - 1);  // a surplus slot repeats the last item (never stored)
-        tok[j] = item / per_token;
-        rem_of[j] = item - tok[j] * per_token;
-        const int col = (k0 + (rem_of[j] >> 3)) * kChunkK + (rem_of[j] & 7) * 8;
-        words[j] = ph->ll_src + static_cast<size_t>(tok[j]) * ph->ll_src_ld + (col >> 1);
-      }
-      uint32_t pair[kBatch][4];
-      uint32_t spins = 0;
-      while (true) {
-        unsigned long long w[kBatch][4];
-#pragma unroll
-        for (int j = 0; j < kBatch; ++j) {
-          ld_relaxed_v2_u64(words[j], w[j][0], w[j][1]);
-          ld_relaxed_v2_u64(words[j] + 2, w[j][2], w[j][3]);
-        }
-        bool all = true;
-#pragma unroll
-        for (int j = 0; j < kBatch; ++j)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            all = all && static_cast<uint32_t>(w[j][i] >> 32) == stamp;
-            pair[j][i] = static_cast<uint32_t>(w[j][i]);
-          }
-        if (all) break;
-        __nanosleep(64);
-        if ((++spins & 255u) == 0 && give_up(cx, SITE_ATT_EXCHANGE, -1)) {
-          fresh = false;
-          break;
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < kBatch; ++j) {
-        if (item0 + j * kSmallWorkers < items) {
-          float f[8];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            f[2 * i] = __uint_as_float(pair[j][i] << 16);
-            f[2 * i + 1] = __uint_as_float(pair[j][i] & 0xFFFF0000u);
-          }
-          x_store(cx, tok[j], rem_of[j] >> 3, rem_of[j] & 7, f);
-        }
-      }
-    }
-    return fresh;
-  }
 #pragma unroll 1
   for (int item = wtid; item < items; item += kSmallWorkers) {
     const int t = item / per_token, rem = item - t * per_token;
     const int col = (k0 + (rem >> 3)) * kChunkK + (rem & 7) * 8;
     float f[8];
-    if (ph->ll_src != nullptr) {
+    if (ph->ll_src != nullptr && ph->bmode == B_PLAIN) {
+      // stamped bf16 pairs written by the producing phase's epilogues: waiting for the stamps is the synchronisation
+      const unsigned long long* words = ph->ll_src + static_cast<size_t>(t) * ph->ll_src_ld + (col >> 1);
+      uint32_t pair[4];
+      stamped_payloads<4>(cx, words, stamp, fresh, pair);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(pair[i] << 16);
+        f[2 * i + 1] = __uint_as_float(pair[i] & 0xFFFF0000u);
+      }
+    } else if (ph->ll_src != nullptr) {
       // stamped fp32 chunk partials of the attention phase, summed in chunk order and rounded once
       const int head = col / p.head_dim, d = col - head * p.head_dim;
       const unsigned long long* part = ph->ll_src + (static_cast<size_t>(t) * p.q_heads + head) * kMaxChunks * p.head_dim + d;
@@ -1020,73 +974,12 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
 // warp 0: weight producer of the small-launch kernel.  Same ring discipline as mk::producer_loop
 // (FIFO reclaim of 1 KB granules, one full/empty barrier pair per copy in flight) without the
 // streamed-operand and multi-token-tile cases, which this kernel never meets.
-// Look-ahead of the weight stream: the ring holds ~2 us of HBM time, the steps between two K loops
-// (hand-off latency, operand staging, attention, epilogues) take longer, and HBM would idle meanwhile.
-// The producer therefore keeps the next `lookahead` bytes of this CTA's copy schedule requested into
-// L2 (126 MB) with bulk prefetches of up to 32 KB: the copies that follow a stall then come from L2 at
-// more than the HBM rate while HBM fetches further ahead.  A unit's weights are contiguous in memory
-// (a row tile over the whole reduction length; a K-split tile is shared out by rows among its
-// slices), so a request is one instruction per 32 KB.  Prefetches are hints: they complete nothing
-// and order nothing.
-constexpr uint32_t kLookaheadPiece = 32 * 1024;
-
-struct Lookahead {
-  int gp, unit, a;          // next block to open: phase, unit of this CTA (-1: first of the phase), accumulator matrix
-  const uint8_t* base;      // block being requested
-  uint32_t off, len;
-  long long issued;         // bytes requested so far
-};
-
-__device__ __noinline__ bool lookahead_next_block(const Ctx& cx, Lookahead& la) {
-  const KParams& p = *cx.p;
-  while (la.gp < p.n_gemm) {
-    const GemmPhase* ph = p.phases + la.gp;
-    if (la.unit < 0) la.unit = cx.cta;
-    if (la.unit >= ph->nunits) {
-      la.gp += 1; la.unit = -1; la.a = 0;
-      continue;
-    }
-    const int ksplit = ph->ksplit, nacc = ph->nacc;
-    const int tile = la.unit / ksplit, slice = la.unit - tile * ksplit;
-    int seg, row0;
-    tile_origin(ph, tile, seg, row0);
-    const int tile_rows = min(ph->rows, ph->n[seg] - row0);
-    const uint32_t row_bytes = static_cast<uint32_t>(ph->k) * 2u;
-    const uint32_t total = static_cast<uint32_t>(tile_rows) * row_bytes;
-    const uint32_t share = ((total / static_cast<uint32_t>(ksplit)) + 15u) & ~15u;
-    const uint32_t begin = min(total, static_cast<uint32_t>(slice) * share), end = min(total, begin + share);
-    la.base = reinterpret_cast<const uint8_t*>(ph->w[nacc == 2 ? la.a : seg]) + static_cast<size_t>(row0) * row_bytes + begin;
-    la.len = end - begin;
-    la.off = 0;
-    if (++la.a >= nacc) { la.a = 0; la.unit += cx.grid; }
-    if (la.len > 0) return true;
-  }
-  return false;
-}
-
-__device__ __forceinline__ void lookahead_advance(const Ctx& cx, Lookahead& la, long long want) {
-  while (la.issued < want) {
-    if (la.off >= la.len && !lookahead_next_block(cx, la)) {
-      la.issued = 0x7fffffffffffffffll;  // the schedule is exhausted
-      return;
-    }
-    const uint32_t piece = min(kLookaheadPiece, la.len - la.off);
-    l2_prefetch_bulk(la.base + la.off, piece);
-    la.off += piece;
-    la.issued += piece;
-  }
-}
-
 __device__ __noinline__ void small_producer(const Ctx& cx) {
   const KParams& p = *cx.p;
   const uint64_t policy = l2_policy_evict_first();
   SmemMisc* misc = cx.misc;
   int head = 0, seq = 0, oldest = 0;
   bool ok = true;
-  Lookahead la;
-  la.gp = 0; la.unit = -1; la.a = 0; la.base = nullptr; la.off = 0; la.len = 0;
-  la.issued = p.lookahead > 0 ? 0 : 0x7fffffffffffffffll;
-  long long copied = 0;  // bytes of weight copies issued into the ring
 #pragma unroll 1
   for (int gp = 0; gp < p.n_gemm && ok; ++gp) {
     const GemmPhase* ph = p.phases + gp;
@@ -1106,7 +999,6 @@ __device__ __noinline__ void small_producer(const Ctx& cx) {
       for (int i = 0; i < steps && ok; i += kb) {
         const int a = (nacc == 2) ? ((i / kb) & 1) : 0;  // gate and up copies alternate
         const CUtensorMap* map = ph->tmap[nacc == 2 ? a : seg];
-        lookahead_advance(cx, la, copied + p.lookahead);  // before the wait for ring space: HBM keeps working
         // Copies are consumed in issue order, so ring space is reclaimed by retiring the oldest copy in
         // flight until [lo, hi) is free; a copy never wraps, so the skipped tail is freed first.
         int lo = head, hi = head + gran;
@@ -1141,11 +1033,9 @@ __device__ __noinline__ void small_producer(const Ctx& cx) {
           mbar_expect_tx(full, copy_bytes);
           bulk_load_1d(smem_u32(cx.smem_a + start * kGranule), ph->w[seg] + static_cast<size_t>(row0 + r) * ph->k, copy_bytes, full,
                        policy);
-          copied += copy_bytes;
         } else {
           mbar_expect_tx(full, bytes);
           tma_load_2d(smem_u32(cx.smem_a + start * kGranule), map, (kbase + k) * kChunkK, row0, full, policy);
-          copied += bytes;
         }
         ++seq;
         if (nacc == 1 || a == 1) {
@@ -1378,7 +1268,7 @@ __global__ void __launch_bounds__(kSmallThreads, 1) megakernel_small(const __gri
     for (int t = tid; t < p.m; t += kSmallThreads) {
       const long long id = p.ids[t];
       long long pos = p.pos[t];
-      if (id < 0 || id >= p.vocab || pos < 0 || pos >= p.max_positions) {
+      if (id < 0 || id >= p.embed_rows || pos < 0 || pos >= p.max_positions) {
         bad = MK_STATUS_BAD_INDEX;
         pos = 0;
       }
@@ -1386,7 +1276,7 @@ __global__ void __launch_bounds__(kSmallThreads, 1) megakernel_small(const __gri
     }
     for (int t = tid; t < p.check_m; t += kSmallThreads) {
       const long long id = p.check_ids[t], pos = p.check_pos[t];
-      if (id < 0 || id >= p.vocab || pos < 0 || pos >= p.max_positions) bad = MK_STATUS_BAD_INDEX;
+      if (id < 0 || id >= p.embed_rows || pos < 0 || pos >= p.max_positions) bad = MK_STATUS_BAD_INDEX;
     }
     for (int l = tid; l < p.layers; l += kSmallThreads) {
       const int len = *p.len[l];

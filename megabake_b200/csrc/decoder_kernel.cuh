@@ -372,7 +372,7 @@ __device__ __noinline__ void mma_loop(const Ctx& cx) {
 __device__ __forceinline__ const bf16* activation_row(const KParams& p, const GemmPhase* ph, int token) {
   if (ph->gather) {
     long long id = p.ids[token];
-    if (id < 0 || id >= p.vocab) id = 0;  // reported by the prologue; never dereference out of range
+    if (id < 0 || id >= p.embed_rows) id = 0;  // reported by the prologue; never dereference out of range
     return p.embed + id * p.hidden;
   }
   return ph->src + static_cast<size_t>(token) * ph->src_ld;
@@ -699,6 +699,26 @@ __device__ __forceinline__ void store_partial(const Ctx& cx, const GemmPhase* ph
     if (t < mt) __stcg(ph->partial + (static_cast<size_t>(slice) * cx.p->m + (t0 + t)) * ph->n[0] + n, v[t]);
 }
 
+// Where source rank `src`'s partial sums of half `half` live in rank `peer`'s exchange buffer.
+__device__ __forceinline__ float* tp_slot(const KParams& p, int peer, int half, int src) {
+  return reinterpret_cast<float*>(p.tp_peer[peer] + kTpFlagBytes) +
+         (static_cast<size_t>(half) * p.tp_size + src) * p.m * p.hidden;
+}
+
+// EPI_TP: this rank's fp32 sums over its share of the reduction length go, unrounded, into the
+// slot of this rank in every rank's exchange buffer (plain peer stores over NVLink; the local
+// rank is one of them).  The all-reduce is finished by tp_allreduce once every rank has stored.
+template <int NT>
+__device__ __forceinline__ void store_tp_partial(const Ctx& cx, const GemmPhase* ph, int n, const float* v, int t0, int mt) {
+  const KParams& p = *cx.p;
+  for (int peer = 0; peer < p.tp_size; ++peer) {
+    float* dst = tp_slot(p, peer, ph->tp_buf, p.tp_rank) + n;
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+      if (t < mt) dst[static_cast<size_t>(t0 + t) * p.hidden] = v[t];
+  }
+}
+
 // Finish output row n of matrix `seg` for the tokens of the tile.
 template <int NT>
 __device__ __forceinline__ void apply_epilogue(const Ctx& cx, const GemmPhase* ph, int seg, int n, float (*v)[NT],
@@ -831,12 +851,14 @@ __device__ __noinline__ bool worker_gemm_tc(const Ctx& cx, int gp, WorkerState& 
         if (!workers_ok(cx, ok)) return false;
         if (valid) {
           if (ph->epi == EPI_PARTIAL) store_partial<kTok>(cx, ph, slice, n, v[0], t0, mt);
+          else if (ph->epi == EPI_TP) store_tp_partial<kTok>(cx, ph, n, v[0], t0, mt);
           else apply_epilogue<kTok>(cx, ph, seg, n, v, pre, t0, mt);
         }
       }
       trace_event(cx, wtid, EV_PHASE_DONE);
     }
   }
+  if (ph->epi == EPI_TP) __threadfence_system();  // this thread's peer stores are performed before it arrives at the grid barrier
   prefetch_phase(cx, gp + 1, wtid);
   return true;
 }
@@ -1538,6 +1560,59 @@ __device__ __noinline__ void rope_phase(const Ctx& cx, int wtid) {
 }
 
 // ---------------------------------------------------------------------------
+// tensor parallel: the all-reduce behind o_proj and down_proj, inside the kernel
+//
+// Called by every CTA of every rank after the grid barrier that closes an EPI_TP projection: by
+// then each rank's CTAs have stored their partial sums into every rank's exchange buffer and
+// fenced them at system scope.  CTA 0 posts this rank's arrival stamp in every rank's flag block
+// (one release store per peer); every CTA waits, with the usual bound, until all stamps have
+// reached its own GPU's flag block, then the grid adds, for its share of the residual stream,
+//     hidden = bf16(hidden + bf16(sum over ranks, in rank order, of the fp32 partial sums)),
+// the same rounding as the single-GPU split-K path, identical bits on every rank.  A grid
+// barrier closes it.  Only plain loads of this GPU's own memory and plain peer stores are used:
+// no multicast, no TMA on peer memory.  Stamps count up monotonically over the life of the
+// group; the two halves of the exchange buffers alternate, so a rank that is one all-reduce
+// ahead never overwrites what a slower rank is still adding.
+__device__ __noinline__ bool tp_allreduce(const Ctx& cx, WorkerState& ws, int wtid, int index) {
+  const KParams& p = *cx.p;
+  const uint32_t stamp = p.tp_epoch + static_cast<uint32_t>(index) + 1u;
+  const int half = index & 1;
+  if (cx.cta == 0 && wtid < p.tp_size)
+    st_release_sys_u32(reinterpret_cast<uint32_t*>(p.tp_peer[wtid]) + p.tp_rank, stamp);
+  bool ok = true;
+  if (wtid < p.tp_size) {
+    const uint32_t* flag = reinterpret_cast<const uint32_t*>(p.tp_peer[p.tp_rank]) + wtid;
+    uint32_t spins = 0;
+    while (static_cast<int32_t>(ld_acquire_sys_u32(flag) - stamp) < 0) {
+      if ((++spins & 255u) == 0 && give_up(cx, SITE_TP_FLAG, wtid)) {
+        ok = false;
+        break;
+      }
+    }
+  }
+  if (!workers_ok(cx, ok)) return false;
+  const int row_vecs = p.hidden / 8;
+  const int nvec = p.m * row_vecs;
+  for (int v = cx.cta * kWorkers + wtid; v < nvec; v += cx.grid * kWorkers) {
+    const int t = v / row_vecs, c = v - t * row_vecs;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int src = 0; src < p.tp_size; ++src) {
+      const float4* part = reinterpret_cast<const float4*>(tp_slot(p, p.tp_rank, half, src) + static_cast<size_t>(t) * p.hidden) + c * 2;
+      const float4 lo = __ldcg(part), hi = __ldcg(part + 1);
+      acc[0] += lo.x; acc[1] += lo.y; acc[2] += lo.z; acc[3] += lo.w;
+      acc[4] += hi.x; acc[5] += hi.y; acc[6] += hi.z; acc[7] += hi.w;
+    }
+    uint4* at = reinterpret_cast<uint4*>(p.hidden_buf + static_cast<size_t>(t) * p.hidden) + c;
+    float f[8];
+    unpack8(__ldcg(at), f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = bf16_round(f[e] + bf16_round(acc[e]));
+    __stcg(at, pack8(f));
+  }
+  return grid_barrier(cx, ws, wtid);
+}
+
+// ---------------------------------------------------------------------------
 // outputs of a launch that the prologue refused, and the device-side greedy sampler
 
 // A launch whose prologue found a bad id, position or a full cache does no work.  Its outputs are
@@ -1673,7 +1748,7 @@ __device__ void worker_loop(const Ctx& cx, int wtid) {
   for (int v = cx.cta * kWorkers + wtid; !p.split && v < p.m * (p.hidden / 8); v += cx.grid * kWorkers) {
     const int t = v / (p.hidden / 8), c = v - t * (p.hidden / 8);
     long long id = p.ids[t];
-    if (id < 0 || id >= p.vocab) id = 0;
+    if (id < 0 || id >= p.embed_rows) id = 0;
     reinterpret_cast<uint4*>(p.hidden_buf + static_cast<size_t>(t) * p.hidden)[c] =
         __ldg(reinterpret_cast<const uint4*>(p.embed + id * p.hidden) + c);
   }
@@ -1705,12 +1780,14 @@ __device__ void worker_loop(const Ctx& cx, int wtid) {
     trace_event(cx, wtid, EV_ATTENTION_DONE);
     if (!grid_barrier(cx, ws, wtid)) return;
     if (decode && cx.cta == 0 && wtid == 0) *p.len[layer] = A.len + 1;  // publish after the interval closes
-    if (!gemm(layer * 4 + 1)) return;                       // o_proj + residual
+    if (!gemm(layer * 4 + 1)) return;                       // o_proj + residual (tensor parallel: partial sums to every rank)
     if (!grid_barrier(cx, ws, wtid)) return;
+    if (p.tp_size > 1 && !tp_allreduce(cx, ws, wtid, 2 * layer)) return;
     if (!gemm(layer * 4 + 2)) return;                       // [RMSNorm] gate, up -> SiLU*up
     if (!grid_barrier(cx, ws, wtid)) return;
     if (!gemm(layer * 4 + 3)) return;                       // down + residual
     if (!grid_barrier(cx, ws, wtid)) return;
+    if (p.tp_size > 1 && !tp_allreduce(cx, ws, wtid, 2 * layer + 1)) return;
   }
   if (!gemm(p.layers * 4)) return;                          // [final RMSNorm] lm_head
   if (p.sample) {
@@ -1773,11 +1850,11 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
     if (p.mode != MODE_KVATT) {
       for (int t = tid; t < p.m; t += kThreads) {
         const long long id = p.ids[t], pos = p.pos[t];
-        if (id < 0 || id >= p.vocab || pos < 0 || pos >= p.max_positions) bad = MK_STATUS_BAD_INDEX;
+        if (id < 0 || id >= p.embed_rows || pos < 0 || pos >= p.max_positions) bad = MK_STATUS_BAD_INDEX;
       }
       for (int t = tid; t < p.check_m; t += kThreads) {
         const long long id = p.check_ids[t], pos = p.check_pos[t];
-        if (id < 0 || id >= p.vocab || pos < 0 || pos >= p.max_positions) bad = MK_STATUS_BAD_INDEX;
+        if (id < 0 || id >= p.embed_rows || pos < 0 || pos >= p.max_positions) bad = MK_STATUS_BAD_INDEX;
       }
     }
     if (p.mode != MODE_PREFILL) {

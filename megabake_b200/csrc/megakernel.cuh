@@ -36,14 +36,17 @@ constexpr int kSplitTokens = 4;          // launches with at most this many toke
 
 static_assert(kSmemBytes <= 200704, "dynamic shared memory exceeds the 196 KiB carve-out");
 
-enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU = 2, EPI_PARTIAL = 3, EPI_ROWRES = 4 };
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU = 2, EPI_PARTIAL = 3, EPI_ROWRES = 4, EPI_TP = 5 };
 enum { B_PLAIN = 0, B_NORM = 1, B_ATTN = 2 };
 enum { MODE_DECODE = 0, MODE_PREFILL = 1, MODE_LINEAR = 2, MODE_KVATT = 3, MODE_ATT = 4 };
 enum { EV_PHASE_ENTER = 1, EV_B_STAGED = 2, EV_FIRST_ACC = 3, EV_PHASE_DONE = 4, EV_BARRIER_DONE = 5, EV_ATTENTION_DONE = 6 };
 enum {
   SITE_PRODUCER_EMPTY = 1, SITE_MMA_FULL = 2, SITE_MMA_B = 3, SITE_MMA_ACC = 4, SITE_EPI_ACC = 5,
-  SITE_GRID_BARRIER = 6, SITE_ATT_EXCHANGE = 7, SITE_DRAIN = 8, SITE_PROLOGUE = 9, SITE_B_EMPTY = 10
+  SITE_GRID_BARRIER = 6, SITE_ATT_EXCHANGE = 7, SITE_DRAIN = 8, SITE_PROLOGUE = 9, SITE_B_EMPTY = 10,
+  SITE_TP_FLAG = 11
 };
+constexpr int kMaxTp = 8;                // ranks of a tensor-parallel group (one node, NVLink peers)
+constexpr int kTpFlagBytes = 256;        // head of a rank's exchange buffer: one arrival stamp per peer
 
 // One projection phase: up to three weight matrices sharing the same activation
 // operand (q,k,v), or a gate/up pair accumulated side by side (nacc == 2).
@@ -81,6 +84,7 @@ struct GemmPhase {
   int bulk;                    // one-token row table: 1 = a tile is `rows` whole weight rows, contiguous in memory, fetched by
   int rpc;                     // one-dimensional bulk copies of `rpc` rows; the epilogue (EPI_ROWRES) adds the residual it
   const unsigned long long* res_src;  // reads as stamped pairs from res_src (or the embedding row when `gather`) and stamps the sum into ll_dst
+  int tp_buf;                  // EPI_TP: which half of the exchange buffers this projection's partial sums go to
   int add_parts;               // B_NORM: fp32 partial slices of the previous projection to add to the residual
   const bf16* normw;
   const bf16* src; int src_ld; // activation source (B_NORM: the residual stream before this phase)
@@ -100,6 +104,7 @@ struct Control {
 
 struct KParams {
   int hidden, layers, q_heads, kv_heads, head_dim, inter, vocab;
+  int embed_rows;     // rows of the embedding table (token ids are checked against it); vocab = rows of this rank's lm_head
   float eps;
   int rope_style, prefill_rope_style;
   float att_scale;    // head_dim ** -0.5 rounded to fp32 on the host
@@ -117,7 +122,6 @@ struct KParams {
   int stream_once;    // 1: weights are read once per launch (L2 evict-first)
   int split;          // 1: this launch runs the split-K phase table (residual updates applied by the consumer)
   int rowmode;        // 1: one-token row table: stamped hand-offs everywhere, one grid barrier at the end of the launch
-  int lookahead;      // bytes of this CTA's coming weight copies that the producer keeps requested into L2 ahead of the ring (0 = off)
   int sample;         // 1: after the logits, pick each sequence's greedy token on the device, store it in tokens_out and as the
                       //    next id, and advance the position: the next launch needs no host round trip
   long long* tokens_out;      // [m] with `sample`
@@ -135,6 +139,13 @@ struct KParams {
   Control* ctrl;
   long long* ids;     // read by every CTA; rewritten at the very end of a launch with `sample`
   long long* pos;
+  // Tensor parallel group (tp_size > 1): this rank holds q_heads, kv_heads and inter of its shard; o_proj and
+  // down_proj produce partial sums over the rank's share of the reduction length.  tp_peer[r] is rank r's
+  // exchange buffer as this process addresses it (peer-mapped; tp_peer[tp_rank] is local):
+  //   [kTpFlagBytes: uint32 stamp per source rank][2 halves][tp_size source ranks][m tokens][hidden] fp32
+  int tp_rank, tp_size;
+  uint32_t tp_epoch;  // all-reduces this group has finished before this launch (stamps count up from it)
+  uint8_t* tp_peer[kMaxTp];
   const long long* check_ids;  // when a step is cut into two launches: the ids and positions of the whole step,
   const long long* check_pos;  // validated by both so that they run or refuse together
   int check_m;

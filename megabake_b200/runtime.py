@@ -69,7 +69,10 @@ class DecoderKernel:
         engine: str = "auto",
         sm_limit: int = 0,
         tables: tuple[torch.Tensor, torch.Tensor] | None = None,
+        tensor_parallel: tuple[int, int, int] | None = None,
     ) -> None:
+        """``tensor_parallel`` = (rank, size, rows of the replicated embedding table) makes this
+        kernel one rank of a group: ``config`` is then the rank's shard (see megabake_b200/tp.py)."""
         self.config = config
         self.device = torch.device(device)
         if self.device.type != "cuda":
@@ -86,7 +89,10 @@ class DecoderKernel:
             rms_eps=config.rms_eps, qkv_bias=int(config.qkv_bias),
             rope_style=_native.ROPE_STYLES[config.rope_style], max_tokens=self.max_tokens,
             max_positions=self.max_positions, engine=_native.ENGINES[engine], sm_limit=int(sm_limit),
+            tp_size=0, tp_rank=0, embed_rows=0,
         )
+        if tensor_parallel is not None:
+            self._cfg.tp_rank, self._cfg.tp_size, self._cfg.embed_rows = (int(v) for v in tensor_parallel)
         with torch.cuda.device(self.device):
             size = self.lib.mk_workspace_bytes(ctypes.byref(self._cfg), self.device.index)
             if size == 0:

@@ -9,8 +9,8 @@ copied from inputs) must match exactly.
 import pytest
 import torch
 
-from conftest import (ATOL, RTOL, assert_deep_parity, assert_no_worse_than, assert_parity, load_golden, token_agrees,
-                      token_defensible)
+from conftest import (ATOL, RTOL, assert_deep_parity, assert_no_worse_than, assert_parity, load_golden, record_stat,
+                      relative_l2, token_agrees, token_defensible)
 from megabake_b200.synth import (CONFIGS, DecoderConfig, new_kv_state, rope_tables, synth_ids, synth_normal,
                                  synth_weights, tiny_config)
 
@@ -66,12 +66,14 @@ def run_golden_decode(name, device, engine, steps=None, deep=False):
     run = total - 1 if steps is None else min(total - 1, steps)
     offset = total - 1 - record["topk_values"].shape[0]
     ties = 0
+    worst_l2 = 0.0
     for position in range(run):
         ids = tokens[:, position].reshape(batch, 1).contiguous()
         positions = torch.full((batch, 1), position, dtype=torch.int64, device=device)
         logits = kernel.decode(ids, positions, keys, values, lengths)
         if position in record["full_logits"]:
             close(logits, record["full_logits"][position], f"{name} logits at {position}")
+            worst_l2 = max(worst_l2, relative_l2(logits, record["full_logits"][position]))
         if position >= offset:
             golden_indices = record["topk_indices"][position - offset]
             golden_values = record["topk_values"][position - offset]
@@ -83,6 +85,8 @@ def run_golden_decode(name, device, engine, steps=None, deep=False):
                         f"{name}: greedy token at position {position + 1} differs beyond a bf16 tie")
                     ties += int(int(logits[row, 0].float().argmax()) != int(golden_indices[row, 0]))
     kernel.check()
+    record_stat(f"teacher_forced_{name}_{engine}", calls=run, argmax_differs_from_golden=ties,
+                worst_rel_l2_to_golden_logits=worst_l2)
     if run == total - 1:
         assert torch.equal(torch.stack(lengths).cpu(), record["lengths"])
         rows = record.get("cache_rows")
@@ -157,6 +161,7 @@ def run_yardstick_decode(name, device):
                 assert token_defensible(mine[row, 0], eager[row, 0], truth[row, 0]), (
                     f"{name}: greedy token at position {position + 1} is not one bf16 noise can defend")
     kernel.check()
+    record_stat(f"teacher_forced_{name}", generated=generated, same_as_golden=same_as_golden)
     assert generated > 0 and same_as_golden >= 0.8 * generated, f"{same_as_golden} of {generated} tokens equal the golden ones"
     assert torch.equal(torch.stack(mine_state[2]).cpu(), record["lengths"])
     rows = record.get("cache_rows")
