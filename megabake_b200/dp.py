@@ -36,17 +36,25 @@ def greedy_stream(step: Callable[[torch.Tensor, torch.Tensor], torch.Tensor], fi
 
 
 def run_data_parallel(make_step: Callable[[int], Callable], first_ids: Sequence[torch.Tensor], start: int,
-                      steps: int, *, rank: int | None = None, world: int | None = None) -> list[torch.Tensor] | None:
+                      steps: int, *, rank: int | None = None, world: int | None = None,
+                      on_device: bool = False) -> list[torch.Tensor] | None:
     """Every rank decodes its own streams; rank 0 returns the ids of all streams in stream
     order, the others return None.  ``make_step(stream)`` builds the step callable (and the KV
-    state) of one stream on the calling rank's device."""
+    state) of one stream on the calling rank's device.  With ``on_device`` the callable is
+    ``run(first_ids, start, steps) -> ids [B, steps]`` instead and keeps the whole greedy loop on
+    the GPU (``DecoderKernel.decode_steps``): the streams of a rank are then queued back to back
+    with no host round trip between steps."""
     import torch.distributed as dist
 
     distributed = dist.is_available() and dist.is_initialized()
     rank = (dist.get_rank() if distributed else 0) if rank is None else rank
     world = (dist.get_world_size() if distributed else 1) if world is None else world
     mine = assign_streams(len(first_ids), world)[rank]
-    local = {stream: greedy_stream(make_step(stream), first_ids[stream], start, steps) for stream in mine}
+    if on_device:
+        queued = {stream: make_step(stream)(first_ids[stream], start, steps) for stream in mine}
+        local = {stream: tokens.cpu() for stream, tokens in queued.items()}  # one synchronisation, at the end
+    else:
+        local = {stream: greedy_stream(make_step(stream), first_ids[stream], start, steps) for stream in mine}
     if not distributed or world == 1:
         return [local[stream] for stream in range(len(first_ids))]
     gathered: list = [None] * world

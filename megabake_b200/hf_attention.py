@@ -110,35 +110,47 @@ def _pass_through_cache(layer_count: int, capacity: int):
 
 
 class DecodeStep(torch.nn.Module):
-    """One-token decode for a Hugging Face attention model with explicit state:
-    ``forward(input_ids, position_ids, *state)`` where state holds, per layer, a key cache
-    and a value cache [batch, capacity, kv_heads, head_dim] and an int32 [1] valid length
-    (``state_shapes`` lists them).  Switches ``model`` to the ``megabake`` attention."""
+    """Explicit-state single-token decode around a Hugging Face causal LM.
+
+    Call it as ``step(input_ids[B, 1], position_ids[B, 1], *state)``.  ``state`` is flat and
+    interleaved per layer: key cache, value cache (both ``[B, capacity, kv_heads, head_dim]``),
+    valid length (int32 ``[1]``); ``state_shapes`` describes it.  The wrapped model is switched to
+    the ``megabake`` attention, whose decode branch hands each layer's triple to
+    ``megabake::kv_attention``.  Same calling convention as the reference's ``DecodeStep``
+    (src/megabake/fx_handler/hf_attention.py:150-187); unlike it, the stand-in cache object also
+    answers the queries transformers 5.5 makes (``get_max_cache_shape``)."""
+
+    _SUPPORTED_LAYER_KINDS = frozenset({"full_attention", "sliding_attention"})
 
     def __init__(self, model: torch.nn.Module, capacity: int):
         super().__init__()
+        text = model.config.get_text_config(decoder=True)
+        kinds = set(getattr(text, "layer_types", None) or ())
+        if not kinds <= self._SUPPORTED_LAYER_KINDS:
+            raise NotImplementedError(
+                f"decode of {sorted(kinds - self._SUPPORTED_LAYER_KINDS)} layers is not declared yet")
+        self.capacity = int(capacity)
+        self.layer_count = int(text.num_hidden_layers)
+        self.kv_heads = int(text.num_key_value_heads)
+        self.head_dim = int(getattr(text, "head_dim", None) or text.hidden_size // text.num_attention_heads)
         register_transformers_attention()
         model.set_attn_implementation(ATTENTION_IMPLEMENTATION)
         self.model = model
-        self.capacity = capacity
-        config = model.config.get_text_config(decoder=True)
-        other = set(getattr(config, "layer_types", None) or ()) - {"full_attention", "sliding_attention"}
-        if other:
-            raise NotImplementedError(f"decode of {sorted(other)} layers is not declared yet")
-        self.layer_count = config.num_hidden_layers
-        self.kv_heads = config.num_key_value_heads
-        self.head_dim = getattr(config, "head_dim", None) or config.hidden_size // config.num_attention_heads
 
     def state_shapes(self, batch: int = 1, dtype: torch.dtype = torch.bfloat16):
-        cache = ((batch, self.capacity, self.kv_heads, self.head_dim), dtype)
-        return [[cache, cache, ((1,), torch.int32)] for _ in range(self.layer_count)]
+        """Per layer: [(key cache shape, dtype), (value cache shape, dtype), ((1,), int32)]."""
+        cache_shape = (batch, self.capacity, self.kv_heads, self.head_dim)
+        return [[(cache_shape, dtype), (cache_shape, dtype), ((1,), torch.int32)] for _ in range(self.layer_count)]
+
+    def _per_layer(self, state: tuple[torch.Tensor, ...]):
+        wanted = 3 * self.layer_count
+        if len(state) != wanted:
+            raise ValueError(f"expected {wanted} state tensors, got {len(state)}")
+        return tuple(zip(state[0::3], state[1::3], state[2::3]))
 
     def forward(self, input_ids: torch.Tensor, position_ids: torch.Tensor, *state: torch.Tensor):
-        if len(state) != 3 * self.layer_count:
-            raise ValueError(f"expected {3 * self.layer_count} state tensors, got {len(state)}")
-        layers = tuple(tuple(state[3 * i: 3 * i + 3]) for i in range(self.layer_count))
-        return self.model(
-            input_ids=input_ids, position_ids=position_ids, cache_position=position_ids[0],
-            past_key_values=_pass_through_cache(self.layer_count, self.capacity), use_cache=True,
-            megabake_state=layers,
-        ).logits
+        triples = self._per_layer(state)
+        stand_in = _pass_through_cache(self.layer_count, self.capacity)
+        result = self.model(input_ids=input_ids, position_ids=position_ids, cache_position=position_ids[0],
+                            past_key_values=stand_in, use_cache=True, megabake_state=triples)
+        return result.logits

@@ -135,13 +135,26 @@ def synth_normal(
     out = torch.empty(count, dtype=dtype, device=device)
     salt = _salt(seed, name)
     scale = torch.tensor(std / _BYTES_STD, dtype=torch.float32, device=device)
-    for start in range(0, count, chunk):
-        stop = min(count, start + chunk)
+
+    def fill(start: int, stop: int) -> None:
         index = torch.arange(start, stop, dtype=torch.int64, device=device)
         first = _mix32((index + salt) & _MASK32)
         second = _mix32((first + 0x9E3779B9 + (index >> 32)) & _MASK32)
         total = _byte_sum(first) + _byte_sum(second) - 1020
         out[start:stop] = (total.to(torch.float32) * scale).to(dtype)
+
+    if torch.device(device).type == "cpu" and count > (1 << 22):
+        # On the host the two dozen element-wise passes are memory-bound: pieces that stay in cache,
+        # spread over the cores, fill a 1.7 G-parameter model in a minute instead of four.
+        from concurrent.futures import ThreadPoolExecutor
+        import os
+
+        piece = 1 << 20
+        with ThreadPoolExecutor(max(1, min(32, os.cpu_count() or 1))) as pool:
+            list(pool.map(lambda start: fill(start, min(count, start + piece)), range(0, count, piece)))
+    else:
+        for start in range(0, count, chunk):
+            fill(start, min(count, start + chunk))
     return out.view(*shape)
 
 

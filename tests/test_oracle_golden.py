@@ -6,7 +6,7 @@ and floating-point values within the parity tolerance."""
 import pytest
 import torch
 
-from conftest import assert_parity, load_golden
+from conftest import assert_deep_parity, assert_parity, load_golden
 from megabake_b200.synth import DecoderConfig, rope_tables, synth_weights
 from oracle import decoder_oracle as oracle
 
@@ -42,7 +42,10 @@ def test_attention_matches_reference_op(exact_cpu):
     assert_parity(plain, record["output_nomask"], "attention without mask", exact=exact_cpu)
 
 
-def _decode_against(name, exact, steps=None):
+def _decode_against(name, exact, steps=None, deep=False):
+    """``deep``: on a host other than the one that wrote the file, a 24-layer x 2048-channel model's
+    bf16 logits are compared by relative L2 (two CPU generations already differ by a few percent
+    there) and near-tied greedy tokens may differ; on the writing host everything is bit for bit."""
     record = load_golden(f"decode_{name}.pt")
     config = DecoderConfig(**record["config"])
     weights = synth_weights(config, seed=record["seed"], norm_std=record["norm_std"])
@@ -58,18 +61,23 @@ def _decode_against(name, exact, steps=None):
             ids = tokens[:, position].reshape(-1, 1)
             positions = torch.full_like(ids, position)
             logits = oracle.decode_step(config, weights, tables, ids, positions, keys, values, lengths)
-            if position + 1 >= prompt.shape[1]:
+            loose = deep and not exact
+            if position + 1 >= prompt.shape[1] and not loose:
                 assert torch.equal(logits[:, 0].float().argmax(-1), tokens[:, position + 1]), f"{name}: token {position + 1}"
             if position in record["full_logits"]:
-                assert_parity(logits, record["full_logits"][position], f"{name} logits at {position}", exact=exact)
-            if position >= offset:
+                if loose:
+                    assert_deep_parity(logits, record["full_logits"][position], f"{name} logits at {position}")
+                else:
+                    assert_parity(logits, record["full_logits"][position], f"{name} logits at {position}", exact=exact)
+            if position >= offset and not loose:
                 top = torch.gather(logits[:, 0].float(), 1, record["topk_indices"][position - offset].long())
                 assert_parity(top.to(torch.bfloat16), record["topk_values"][position - offset], f"{name} top-k at {position}", exact=exact)
     if run == total - 1:
         assert torch.equal(torch.stack(lengths), record["lengths"])
+        close = assert_deep_parity if (deep and not exact) else (lambda a, b, what: assert_parity(a, b, what, exact=exact))
         for layer, (key_cache, value_cache) in record["caches"].items():
-            assert_parity(keys[layer], key_cache, f"{name} key cache {layer}", exact=exact)
-            assert_parity(values[layer], value_cache, f"{name} value cache {layer}", exact=exact)
+            close(keys[layer], key_cache, f"{name} key cache {layer}")
+            close(values[layer], value_cache, f"{name} value cache {layer}")
 
 
 def test_decode_tiny_llama_form(exact_cpu):
@@ -88,7 +96,12 @@ def test_decode_qwen2_half_b_shape_first_steps(exact_cpu):
     _decode_against("c2", exact_cpu, steps=10)
 
 
-@pytest.mark.parametrize("name", ["tiny", "c1"])
+def test_decode_smollm_1_7b_shape_short_run(exact_cpu):
+    """The headline shape (24 layers x 2048 channels): the reference's 4-token prompt and 28 greedy tokens."""
+    _decode_against("c3_short", exact_cpu, deep=True)
+
+
+@pytest.mark.parametrize("name", ["tiny", "c1", "c2"])
 def test_prefill_matches_reference_model(name, exact_cpu):
     record = load_golden(f"prefill_{name}.pt")
     config = DecoderConfig(**record["config"])
