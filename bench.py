@@ -64,6 +64,7 @@ def parse_args():
     parser.add_argument("--capacity", type=int, default=2048)
     parser.add_argument("--cpu-steps", type=int, default=40, help="CPU baseline sample size")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--engine", default="auto", choices=["auto", "tcgen05", "fma"], help="kernel choice for the headline run")
     parser.add_argument("--no-extras", action="store_true", help="headline only: skip the c4 / tp / prefill blocks")
     parser.add_argument("--c4-steps", type=int, default=256)
     parser.add_argument("--tp-steps", type=int, default=128)
@@ -248,7 +249,7 @@ def run_c4(args, config, weights, group: Group, rank: int, peak: float):
         "value": n_streams * batch * steps / (elapsed_ms / 1e3), "unit": "tokens/s", "n_gpus": group.world,
         "ms_total": elapsed_ms, "us_per_stream_step": 1e3 * elapsed_ms / (steps * streams_per_gpu),
         "per_gpu_roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                             "kernel": "mk::megakernel_small<4> x 2 launches per step"},
+                             "kernel": "mk::megakernel (one launch per step of 8 sequences)"},
         "gpu_launches_per_gpu": launches,
         "tokens_checked": None if tokens is None else int(sum(t.numel() for t in tokens)),
     }
@@ -395,7 +396,8 @@ def main():
         dist.init_process_group("nccl", device_id=device)
     group = Group(device, world)
     weights = synth_weights(config, seed=0, device=device)
-    kernel = DecoderKernel(config, weights, max_tokens=args.batch, max_positions=args.capacity, device=device)
+    kernel = DecoderKernel(config, weights, max_tokens=args.batch, max_positions=args.capacity, device=device,
+                           engine=args.engine)
     keys, values, lengths = build_state(config, args.batch, args.context, args.capacity, device)
     ids = synth_ids(args.batch, config.vocab, seed=1 + rank, name="bench").view(args.batch, 1).to(device)
     if args.context + args.warmup + args.steps + 1 > args.capacity:
@@ -495,9 +497,8 @@ def main():
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": traffic, "traffic_source": traffic_source, "peak_source": f"of {peak_kind}",
                      "algorithmic_bytes_per_launch": bytes_per_launch,
-                     "kernel": ("mk::megakernel_small<%d>" % args.batch if args.batch <= 4 else
-                                "mk::megakernel_small<%d> + <%d> (two launches per step)" % ((args.batch + 1) // 2, args.batch // 2)
-                                if args.batch <= 8 else "mk::megakernel"),
+                     "kernel": ("mk::megakernel_small<%d>" % args.batch if args.batch <= 4 and args.engine != "tcgen05"
+                                else "mk::megakernel"),
                      "launch_us": launch_ms * 1e3, "frac_of_8TBps_nominal": achieved / 8000.0},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": 16 * args.batch,
                 "d2h_bytes_per_step": 8 * args.batch, "us_per_call": 1e3 * e2e_ms / e2e_steps,

@@ -133,9 +133,8 @@ int mk_create(const mk_config* config, void* workspace, size_t workspace_bytes, 
  * src/megabake/bodies/gemm.py:1809-1843. */
 int mk_bind_weights(mk_handle handle, const mk_weights* weights, void* stream);
 
-/* One decode step for `batch` sequences, no sync: one cooperative launch; two
- * (halves of the batch, plus a one-warp copy of the valid lengths) for 5..8
- * sequences under MK_ENGINE_AUTO / MK_ENGINE_FMA when the small-launch kernel applies.
+/* One decode step for `batch` sequences, no sync: one cooperative launch (the small-launch kernel for
+ * up to 4 sequences under MK_ENGINE_AUTO / MK_ENGINE_FMA when the shape allows, else the tensor engine).
  * ids/positions: int64 [batch].  key_caches/value_caches: host arrays of
  * config.layers device pointers, each bf16 [batch, capacity, kv_heads,
  * head_dim] contiguous.  valid_lengths: host array of config.layers device
@@ -147,6 +146,17 @@ int mk_bind_weights(mk_handle handle, const mk_weights* weights, void* stream);
 int mk_decode(mk_handle handle, const int64_t* ids, const int64_t* positions, int batch,
               void* const* key_caches, void* const* value_caches, int32_t* const* valid_lengths,
               int capacity, void* logits, void* stream);
+
+/* mk_decode for sequences of different lengths in one batch: valid_lengths[layer] points to int32 [batch],
+ * one filled-position count per sequence (each is read, used as that sequence's append row and advanced by
+ * one); sequence b attends over its own [0, valid_length[b]] and rotates with positions[b].  Everything else
+ * as mk_decode.  Runs on the tensor engine (the context split follows the longest sequence; chunks past a
+ * shorter sequence's end are empty).
+ * Reference: none; its contract is one length shared by the batch (src/megabake/lowering.py:160-190,
+ * README.md:29 lists per-sequence lengths as not supported). */
+int mk_decode_ragged(mk_handle handle, const int64_t* ids, const int64_t* positions, int batch,
+                     void* const* key_caches, void* const* value_caches, int32_t* const* valid_lengths,
+                     int capacity, void* logits, void* stream);
 
 /* `steps` greedy decode steps back to back without a host round trip: launch s picks each
  * sequence's token on the device (largest bf16 logit, lowest index among equal ones: what
@@ -173,8 +183,9 @@ int mk_prefill(mk_handle handle, const int64_t* ids, const int64_t* positions, c
 
 /* y[M,N] = x[M,K] . W[N,K]^T (+ bias[N]), bf16 in/out, fp32 accumulate, one
  * rounding after the bias.  Runs the megakernel's projection engine on one
- * phase.  `handle` supplies workspace and engine; N, K multiples of 64,
- * M <= config.max_tokens.  Synchronous set-up (encodes one TMA descriptor), async launch.
+ * phase.  `handle` supplies workspace and engine; K a multiple of 64,
+ * M <= config.max_tokens.  The two TMA descriptors are encoded on the host and travel in the
+ * kernel's parameter block: no upload, no synchronisation.
  * Reference: the projection body, src/megabake/bodies/gemm.py:629-1114 with
  * its bias epilogue :1223-1251. */
 int mk_linear(mk_handle handle, const void* x, const void* weight, const void* bias, void* y,
@@ -236,6 +247,18 @@ typedef struct mk_ipc_handle {
 int mk_ipc_export(void* pointer, mk_ipc_handle* out);
 int mk_ipc_open(const mk_ipc_handle* in, void** pointer, void** base_out);
 int mk_ipc_close(void* base);
+
+/* Measurement baseline, outside the decoder path: y[M,N] = x[M,K] . W[N,K]^T (bf16, fp32 accumulate, no
+ * bias) by the algorithm of the reference's only sm_100 kernel, its "blackwell_mma" body
+ * (src/megabake/bodies/blackwell.py:91-159: 16 x 32 CTA tiles, four warps of mma.sync.m16n8k16,
+ * per-element predicated global loads, no shared memory), restated in CUDA C.  The projection engine
+ * (mk_linear) is timed against it by `python -m megabake_b200.bench_linear`. */
+int mk_baseline_mma_gemm(const void* x, const void* weight, void* y, int m, int n, int k, void* stream);
+
+/* Plain-text summary of what the handle will launch (CTAs, the form of the weight copies, tile height /
+ * K split / chunks per copy / unit count of each projection phase per table).  Synchronous (reads the
+ * phase tables back).  Reference: the plan report, src/megabake/plan.py:342-395. */
+int mk_describe(mk_handle handle, char* buffer, size_t bytes);
 
 /* Failure-detection hook for tests: adds `delta` to the grid-barrier count the host expects, so
  * that the next launch's first grid barrier can never be reached and its bounded wait

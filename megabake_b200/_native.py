@@ -29,7 +29,7 @@ EXPORTS = (
     "mk_workspace_bytes", "mk_create", "mk_bind_weights", "mk_decode", "mk_prefill", "mk_linear",
     "mk_kv_attention", "mk_kv_attention_static", "mk_kv_attention_static_status", "mk_attention", "mk_status", "mk_set_trace",
     "mk_launch_info", "mk_last_error", "mk_destroy", "mk_decode_steps", "mk_set_status_mirror", "mk_debug_skew_barrier",
-    "mk_tp_exchange_bytes", "mk_tp_bind", "mk_ipc_export", "mk_ipc_open", "mk_ipc_close",
+    "mk_describe", "mk_decode_ragged", "mk_baseline_mma_gemm", "mk_tp_exchange_bytes", "mk_tp_bind", "mk_ipc_export", "mk_ipc_open", "mk_ipc_close",
 )
 
 
@@ -96,6 +96,8 @@ def load() -> ctypes.CDLL:
         c_void_p, c_void_p, c_void_p, c_int, POINTER(c_void_p), POINTER(c_void_p), POINTER(c_void_p),
         c_int, c_void_p, c_void_p,
     ]
+    lib.mk_decode_ragged.restype = c_int
+    lib.mk_decode_ragged.argtypes = lib.mk_decode.argtypes
     lib.mk_prefill.restype = c_int
     lib.mk_prefill.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
     lib.mk_linear.restype = c_int
@@ -130,6 +132,10 @@ def load() -> ctypes.CDLL:
     lib.mk_ipc_open.argtypes = [POINTER(MkIpcHandle), POINTER(c_void_p), POINTER(c_void_p)]
     lib.mk_ipc_close.restype = c_int
     lib.mk_ipc_close.argtypes = [c_void_p]
+    lib.mk_baseline_mma_gemm.restype = c_int
+    lib.mk_baseline_mma_gemm.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    lib.mk_describe.restype = c_int
+    lib.mk_describe.argtypes = [c_void_p, ctypes.c_char_p, c_size_t]
     lib.mk_debug_skew_barrier.restype = c_int
     lib.mk_debug_skew_barrier.argtypes = [c_void_p, ctypes.c_uint32]
     lib.mk_set_status_mirror.restype = c_int

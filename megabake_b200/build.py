@@ -14,7 +14,7 @@ from pathlib import Path
 PACKAGE = Path(__file__).resolve().parent
 CSRC = PACKAGE / "csrc"
 LIBRARY = PACKAGE / "libmegabake_b200.so"
-SOURCES = [CSRC / "api.cu"]
+SOURCES = [CSRC / "api.cu", CSRC / "reference_mma_baseline.cu"]
 
 
 def headers() -> list[Path]:

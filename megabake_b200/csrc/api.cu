@@ -40,10 +40,15 @@ int fail(int code, const char* fmt, ...) {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct Carve {
-  size_t ctrl, tmaps, phases, hidden, hidden2, qkv, qkv_ll, act_ll, att_ll, attn_ll, res_a, res_b, attn, act, partial, partial2, att_xch, att_part, len_copy, total;
+  size_t ctrl, tmaps, phases, hidden, hidden2, xnorm, qkv, qkv_ll, act_ll, att_ll, attn_ll, res_a, res_b, attn, act, partial, partial2, att_xch, att_part, total;
 };
 
 int qkv_width(const mk_config& c) { return (c.q_heads + 2 * c.kv_heads) * c.head_dim; }
+// Token-operand descriptors of the tensor engine: (normalised rows, attention output, SiLU*up, mk_linear's
+// source) x (token tiles of 16, 32, 64), behind the weight descriptors.
+constexpr int kOperandKinds = 4, kOperandMaps = kOperandKinds * 3;
+enum { OPERAND_XNORM = 0, OPERAND_ATTN = 1, OPERAND_ACT = 2, OPERAND_LINEAR = 3 };
+int token_tile_of(int m) { return m <= 16 ? 16 : (m <= 32 ? 32 : 64); }
 size_t maps_per_table(const mk_config& c) { return 7 * static_cast<size_t>(c.layers) + 1; }
 size_t phases_per_table(const mk_config& c) { return 4 * static_cast<size_t>(c.layers) + 1; }
 
@@ -57,10 +62,11 @@ Carve carve(const mk_config& c) {
   };
   const size_t m = static_cast<size_t>(c.max_tokens);
   v.ctrl = take(sizeof(Control));
-  v.tmaps = take(sizeof(CUtensorMap) * (3 * maps_per_table(c) + 1));    // split table, plain table, small-launch table, mk_linear
+  v.tmaps = take(sizeof(CUtensorMap) * (3 * maps_per_table(c) + 1 + kOperandMaps));  // split, plain and small-launch tables, mk_linear, token operands
   v.phases = take(sizeof(GemmPhase) * (4 * phases_per_table(c) + 1));  // + the one-token row table
   v.hidden = take(m * c.hidden * 2);
-  v.hidden2 = take(static_cast<size_t>(kSplitTokens) * c.hidden * 2);
+  v.hidden2 = take(m * c.hidden * 2);
+  v.xnorm = take(m * c.hidden * 2);
   v.qkv = take(m * qkv_width(c) * 2);
   v.qkv_ll = take(static_cast<size_t>(kSplitTokens) * qkv_width(c) * 4);
   v.act_ll = take(static_cast<size_t>(kSplitTokens) * c.intermediate * 4);
@@ -70,11 +76,10 @@ Carve carve(const mk_config& c) {
   v.res_b = take(static_cast<size_t>(kSplitTokens) * c.hidden * 4);  // ... and after attention
   v.attn = take(m * c.q_heads * c.head_dim * 2);
   v.act = take(m * c.intermediate * 2);
-  v.partial = take(static_cast<size_t>(kMaxSplit) * kSplitTokens * c.hidden * 4);
+  v.partial = take(static_cast<size_t>(kMaxSplit) * std::max<size_t>(m, kSplitTokens) * c.hidden * 4);
   v.partial2 = take(static_cast<size_t>(kMaxSplit) * kSplitTokens * c.hidden * 4);  // down-proj partials of the small-launch table
   v.att_xch = take(m * c.kv_heads * kMaxChunks * kExchangeFloats * 4);
   v.att_part = take(m * c.q_heads * kMaxChunks * c.head_dim * 4);
-  v.len_copy = take(MK_MAX_LAYERS * 4);  // snapshot of the valid lengths for the first of two launches of one step
   v.total = off;
   return v;
 }
@@ -89,6 +94,8 @@ int check_config(const mk_config& c) {
   if (c.q_heads / c.kv_heads > 8) return fail(MK_ERR_UNSUPPORTED, "config: at most 8 query heads per kv head");
   if (c.hidden % 64 || c.intermediate % 64)
     return fail(MK_ERR_UNSUPPORTED, "config: hidden and intermediate must be multiples of 64");
+  if (c.hidden > kNormVecs * kWorkers * 8)
+    return fail(MK_ERR_UNSUPPORTED, "config: hidden above %d (a norm phase keeps a row in the registers of one CTA)", kNormVecs * kWorkers * 8);
   if (c.engine != MK_ENGINE_TCGEN05 && c.engine != MK_ENGINE_FMA && c.engine != MK_ENGINE_AUTO)
     return fail(MK_ERR_INVALID, "config: engine");
   if (c.rope_style != MK_ROPE_HF && c.rope_style != MK_ROPE_HALF_SWAP) return fail(MK_ERR_INVALID, "config: rope_style");
@@ -137,6 +144,55 @@ int encode_weight_map(CUtensorMap* out, const void* base, int rows, int k, int b
   return MK_OK;
 }
 
+// Tensor engine, weights: bf16 [rows, k] row-major seen as (64 elements, rows, k / 64 chunks); a box is
+// box_rows rows x box_chunks chunks, each chunk 128-byte swizzled: one copy brings several K chunks of a tile.
+int encode_weight_map3(CUtensorMap* out, const void* base, int rows, int k, int box_rows, int box_chunks) {
+  if (reinterpret_cast<uintptr_t>(base) % 16) return fail(MK_ERR_ALIGNMENT, "weight base %p is not 16-byte aligned", base);
+  auto fn = encode_fn();
+  if (!fn) return fail(MK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(kChunkK), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(k / kChunkK)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(k) * 2, static_cast<cuuint64_t>(kChunkK) * 2};
+  const cuuint32_t box[3] = {static_cast<cuuint32_t>(kChunkK), static_cast<cuuint32_t>(box_rows), static_cast<cuuint32_t>(box_chunks)};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(MK_ERR_CUDA, "cuTensorMapEncodeTiled (3-D) failed with %d (rows %d, k %d, box %d x %d)", (int)r, rows, k, box_rows, box_chunks);
+  return MK_OK;
+}
+
+// The weight descriptor of a tensor-engine phase: three-dimensional when the driver accepts the chunk-major
+// view (its chunk stride, 128 bytes, is smaller than its row stride), else one 64-column box per copy.
+int encode_phase_weight_map(CUtensorMap* out, const void* base, int rows, int k, GemmPhase& ph, bool& use3d) {
+  if (use3d) {
+    if (encode_weight_map3(out, base, rows, k, ph.rows, ph.kb) == MK_OK) {
+      ph.map3d = 1;
+      return MK_OK;
+    }
+    use3d = false;  // fall back for this and every later matrix of the handle
+  }
+  ph.map3d = 0;
+  return encode_weight_map(out, base, rows, k, ph.rows);
+}
+
+// Tensor engine, token operand: bf16 [tokens, k] row-major, box = 64 elements x `tile` tokens, 128-byte
+// swizzle; token rows past `tokens` read as zeros.
+int encode_operand_map(CUtensorMap* out, const void* base, int tokens, int k, int tile) {
+  if (reinterpret_cast<uintptr_t>(base) % 16) return fail(MK_ERR_ALIGNMENT, "operand base %p is not 16-byte aligned", base);
+  auto fn = encode_fn();
+  if (!fn) return fail(MK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(tokens)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kChunkK), static_cast<cuuint32_t>(tile)};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MK_ERR_CUDA, "cuTensorMapEncodeTiled (operand) failed with %d (tokens %d, k %d)", (int)r, tokens, k);
+  return MK_OK;
+}
+
 }  // namespace
 
 struct mk_handle_s {
@@ -156,6 +212,7 @@ struct mk_handle_s {
   bool small_ll;  // its q/k/v phases hand their outputs to attention as stamped words (one grid barrier fewer per layer)
   unsigned long long* trace;
   int trace_cap;
+  bool use3d;           // weight descriptors of the tensor engine are three-dimensional (several K chunks per copy)
   uint32_t tp_epoch;    // all-reduces launched so far (tensor parallel)
   uint8_t* tp_peer[kMaxTp];
   bool tp_bound;
@@ -222,9 +279,34 @@ void finish_phase(GemmPhase& ph, int grid, bool allow_split, int max_rows = kTil
   ph.nunits = tile * best_split;
 }
 
-// Can launches of at most kSplitTokens tokens use the split-K table?  Its
-// consumer-side residual update keeps a whole hidden row in the activation slots.
-bool split_table_ok(const mk_config& c) { return c.hidden / kChunkK <= kBSlots && c.tp_size <= 1; }
+// Tensor engine: tile heights are multiples of 8 (a swizzled chunk of a tile must start on a 1 KiB boundary
+// inside a ring entry), and an entry carries `kb` K chunks per matrix: as many as divide the K range and keep
+// the entry under ~36 KB (three entries of the 120 KB ring in flight); two at most when launches can have
+// token tiles of 64 (the activation ring holds 64 KB).
+void finish_phase_tc(GemmPhase& ph, int grid, bool allow_split, int max_tokens) {
+  finish_phase(ph, grid, allow_split);
+  ph.rows = std::min(kTileRows, (ph.rows + 7) / 8 * 8);
+  const int nseg = ph.nacc == 2 ? 1 : ph.nseg;
+  int tile = 0;
+  for (int s = 0; s < nseg; ++s) {
+    ph.tile_start[s] = tile;
+    tile += (ph.n[s] + ph.rows - 1) / ph.rows;
+  }
+  ph.tile_start[nseg] = tile;
+  ph.ntiles = tile;
+  ph.nunits = tile * ph.ksplit;
+  int kb = 1;
+  for (int cand = 2; cand <= (max_tokens > 32 ? 2 : 4); ++cand)
+    if (ph.kslice % cand == 0 && ph.nacc * cand * ph.rows * 128 <= 36 * 1024) kb = cand;
+  ph.kb = kb;
+  ph.gran = ph.nacc * kb * ph.rows / 8;
+}
+
+// The split-K table (o_proj and down_proj cut along K so that every SM streams, fp32 partial sums added by
+// the next norm phase) serves every launch of a single-GPU handle.  The small-launch kernel further needs a
+// reduction length of at most 2048 per K slice (its fp32 operand buffer).
+bool split_table_ok(const mk_config& c) { return c.tp_size <= 1; }
+bool small_shape_ok(const mk_config& c) { return c.hidden / kChunkK <= kBSlots && c.tp_size <= 1; }
 
 void base_params(mk_handle h, KParams& p) {
   memset(&p, 0, sizeof(p));
@@ -253,6 +335,7 @@ void base_params(mk_handle h, KParams& p) {
   if (h->cv.phases == 0) return;  // a view without decoder buffers (the static-scratch attention): the rest stays null
   p.phases = at<GemmPhase>(h, h->cv.phases);
   p.hidden_buf = at<bf16>(h, h->cv.hidden);
+  p.xnorm = at<bf16>(h, h->cv.xnorm);
   p.qkv = at<bf16>(h, h->cv.qkv);
   p.attn = at<bf16>(h, h->cv.attn);
   p.act = at<bf16>(h, h->cv.act);
@@ -300,11 +383,12 @@ int launch(mk_handle h, KParams& p, void* stream, int attention_phases = 0, bool
   return MK_OK;
 }
 
-int token_tiles(int m) { return (m + kTok - 1) / kTok; }
+int token_tiles(int m) { return (m + token_tile_of(m) - 1) / token_tile_of(m); }
 
 int attention_fits(mk_handle h, int keys, const char* what) {
   const int gs = h->cfg.q_heads / h->cfg.kv_heads;
-  const int max_len = (kScoreBytes / 4 / gs) & ~7;
+  const int heads = gs * decode_heads_per_unit(h->cfg.kv_heads, gs, h->cfg.head_dim);  // query heads of one attention unit
+  const int max_len = (kScoreBytes / 4 / heads) & ~7;
   const int need = (keys + max_len - 1) / max_len;
   if (need > kMaxChunks || need > h->grid)
     return fail(MK_ERR_UNSUPPORTED, "%s: %d keys exceed %d chunks of %d", what, keys, kMaxChunks, max_len);
@@ -361,6 +445,11 @@ int mk_create(const mk_config* config, void* workspace, size_t workspace_bytes, 
   h->trace = nullptr;
   h->trace_cap = 0;
   h->mirror = nullptr;
+  {  // does this driver take the chunk-major three-dimensional view of a weight matrix?
+    CUtensorMap probe;
+    h->use3d = getenv("MEGABAKE_NO_3D_MAPS") == nullptr &&
+               encode_weight_map3(&probe, workspace, 128, 256, 64, 2) == MK_OK;
+  }
   h->tp_epoch = 0;
   h->tp_bound = false;
   for (int r = 0; r < kMaxTp; ++r) h->tp_peer[r] = nullptr;
@@ -395,6 +484,7 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
   std::vector<CUtensorMap> maps(3 * nmaps);
   std::vector<GemmPhase> phases(4 * nphases);
   CUtensorMap* dmaps = at<CUtensorMap>(h, h->cv.tmaps);
+  CUtensorMap* operand_maps = dmaps + 3 * nmaps + 1;
   bf16* hidden_a = at<bf16>(h, h->cv.hidden);
   bf16* hidden_b = at<bf16>(h, h->cv.hidden2);
   bf16* qkv = at<bf16>(h, h->cv.qkv);
@@ -411,6 +501,7 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
   // Table 0: split-K (small launches): o and down store K-slice partials; the next
   // normalising phase adds them to the residual stream, which ping-pongs between
   // hidden_b (after attention) and hidden_a (after the MLP).  Table 1: plain.
+  bool use3d = h->use3d;
   for (int table = 0; table < 2; ++table) {
     const bool split = (table == 0);
     if (split && !split_table_ok(c)) continue;
@@ -467,18 +558,25 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
         ph[1].epi = EPI_TP; ph[1].tp_buf = 0;
         ph[3].epi = EPI_TP; ph[3].tp_buf = 1;
       }
-      for (int i = 0; i < 4; ++i) finish_phase(ph[i], h->grid, split && ph[i].epi == EPI_PARTIAL);
+      ph[1].gate = 1;  // decode attention streams cache tiles through the weight ring just before this phase
+      for (int i = 0; i < 4; ++i) finish_phase_tc(ph[i], h->grid, split && ph[i].epi == EPI_PARTIAL, c.max_tokens);
       if (split) {
         ph[2].add_parts = ph[1].ksplit; ph[2].partial = partial; ph[2].h_out = hidden_a;
         prev_parts = ph[3].ksplit;
       }
-      // One TMA descriptor per matrix, boxed to the tile height its phase chose.
+      for (int t = 0; t < 3; ++t) {  // token operands: normalised rows, attention output, SiLU*up
+        ph[0].bmap[t] = operand_maps + OPERAND_XNORM * 3 + t;
+        ph[1].bmap[t] = operand_maps + OPERAND_ATTN * 3 + t;
+        ph[2].bmap[t] = operand_maps + OPERAND_XNORM * 3 + t;
+        ph[3].bmap[t] = operand_maps + OPERAND_ACT * 3 + t;
+      }
+      // One TMA descriptor per matrix, boxed to the tile height and the K chunks per copy its phase chose.
       const void* mats[7] = {lw.q, lw.k, lw.v, lw.o, lw.gate, lw.up, lw.down};
       const int rows[7] = {q_size, kv_size, kv_size, c.hidden, c.intermediate, c.intermediate, c.hidden};
       const int ks[7] = {c.hidden, c.hidden, c.hidden, q_size, c.hidden, c.hidden, c.intermediate};
-      const int box[7] = {ph[0].rows, ph[0].rows, ph[0].rows, ph[1].rows, ph[2].rows, ph[2].rows, ph[3].rows};
+      const int which[7] = {0, 0, 0, 1, 2, 2, 3};
       for (int i = 0; i < 7; ++i)
-        if (int e = encode_weight_map(&tmaps_host[7 * l + i], mats[i], rows[i], ks[i], box[i])) return e;
+        if (int e = encode_phase_weight_map(&tmaps_host[7 * l + i], mats[i], rows[i], ks[i], ph[which[i]], use3d)) return e;
     }
     GemmPhase& head = tp[4 * L];
     memset(&head, 0, sizeof(head));
@@ -490,19 +588,21 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
     if (split) {
       head.add_parts = prev_parts; head.partial = partial;
     }
-    finish_phase(head, h->grid, false);
-    if (int e = encode_weight_map(&tmaps_host[7 * L], w->lm_head, c.vocab, c.hidden, head.rows)) return e;
+    finish_phase_tc(head, h->grid, false, c.max_tokens);
+    for (int t = 0; t < 3; ++t) head.bmap[t] = operand_maps + OPERAND_XNORM * 3 + t;
+    if (int e = encode_phase_weight_map(&tmaps_host[7 * L], w->lm_head, c.vocab, c.hidden, head, use3d)) return e;
   }
   // Table 2: the split-K table again for the small-launch kernel, whose CUDA-core consumer takes
   // the weights as plain rows: one copy brings `kb` K chunks of a tile's rows (a copy of less than
   // ~16 KB cannot keep an SM's share of HBM busy: the copy engine retires about three per microsecond).
-  h->fma_ok = split_table_ok(c);
+  h->fma_ok = small_shape_ok(c);
   for (size_t i = 0; i < nphases && h->fma_ok; ++i)
     if (phases[i].kslice > kBSlots || phases[i].rows > kTileRows) h->fma_ok = false;
   if (h->fma_ok) {
     for (size_t i = 0; i < nphases; ++i) {
       GemmPhase& ph = phases[2 * nphases + i];
       ph = phases[i];
+      finish_phase(ph, h->grid, ph.epi == EPI_PARTIAL);  // the CUDA-core consumer takes any tile height: no rounding to 8
       if (ph.rows > kSmallTileRows) {  // the CUDA-core consumer keeps 8 rows per warp: tiles of at most 64 rows
         if (ph.ksplit != 1) return fail(MK_ERR_UNSUPPORTED, "small-launch table: a split phase with more than 64 rows");
         finish_phase(ph, h->grid, false, kSmallTileRows);
@@ -598,6 +698,18 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
     }
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  {
+    CUtensorMap operand_host[kOperandMaps];
+    memset(operand_host, 0, sizeof(operand_host));
+    const void* bases[3] = {at<bf16>(h, h->cv.xnorm), attn, act};
+    const int widths[3] = {c.hidden, q_size, c.intermediate};
+    static const int tiles[3] = {16, 32, 64};
+    for (int kind = 0; kind < 3; ++kind)
+      for (int t = 0; t < 3; ++t)
+        if (int e = encode_operand_map(&operand_host[kind * 3 + t], bases[kind], c.max_tokens, widths[kind], tiles[t])) return e;
+    MK_CUDA(cudaMemcpyAsync(operand_maps, operand_host, sizeof(operand_host), cudaMemcpyHostToDevice, s));
+    MK_CUDA(cudaStreamSynchronize(s));
+  }
   MK_CUDA(cudaMemcpyAsync(dmaps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, s));
   MK_CUDA(cudaMemcpyAsync(at<GemmPhase>(h, h->cv.phases), phases.data(), phases.size() * sizeof(GemmPhase),
                           cudaMemcpyHostToDevice, s));
@@ -615,20 +727,14 @@ namespace {
 int small_launch_keys(const mk_config& c) { return kMaxChunks * ((kAttScoreBytes / 4 / (c.q_heads / c.kv_heads)) & ~7); }
 
 bool small_launch_ok(mk_handle h, int capacity) {
-  return (h->cfg.engine == MK_ENGINE_FMA || h->cfg.engine == MK_ENGINE_AUTO) && split_table_ok(h->cfg) && h->fma_ok &&
+  return (h->cfg.engine == MK_ENGINE_FMA || h->cfg.engine == MK_ENGINE_AUTO) && small_shape_ok(h->cfg) && h->fma_ok &&
          capacity <= small_launch_keys(h->cfg);
 }
 
 int decode_once(mk_handle h, const int64_t* ids, const int64_t* positions, int batch, void* const* key_caches,
                 void* const* value_caches, int32_t* const* valid_lengths, int capacity, void* logits, void* stream,
-                int64_t* tokens_out = nullptr, bool sample = false, const int64_t* all_ids = nullptr,
-                const int64_t* all_positions = nullptr, int all_batch = 0);
+                int64_t* tokens_out = nullptr, bool sample = false, bool ragged = false);
 
-// Copy the per-layer valid lengths into one array (the lengths live in separate caller tensors).
-struct LengthPointers { const int32_t* at[MK_MAX_LAYERS]; };
-__global__ void snapshot_lengths(LengthPointers src, int32_t* dst, int layers) {
-  for (int l = threadIdx.x; l < layers; l += blockDim.x) dst[l] = *src.at[l];
-}
 }  // namespace
 
 namespace {
@@ -645,6 +751,23 @@ int mk_decode(mk_handle h, const int64_t* ids, const int64_t* positions, int bat
     return fail(MK_ERR_INVALID, "mk_decode: null argument");
   std::lock_guard<std::mutex> guard(h->lock);
   return decode_step(h, ids, positions, batch, key_caches, value_caches, valid_lengths, capacity, logits, stream, nullptr, false);
+}
+
+int mk_decode_ragged(mk_handle h, const int64_t* ids, const int64_t* positions, int batch, void* const* key_caches,
+                     void* const* value_caches, int32_t* const* valid_lengths, int capacity, void* logits, void* stream) {
+  if (!h || !ids || !positions || !key_caches || !value_caches || !valid_lengths || !logits)
+    return fail(MK_ERR_INVALID, "mk_decode_ragged: null argument");
+  std::lock_guard<std::mutex> guard(h->lock);
+  if (!h->bound) return fail(MK_ERR_UNBOUND, "mk_decode_ragged before mk_bind_weights");
+  if (batch < 1 || batch > h->cfg.max_tokens) return fail(MK_ERR_INVALID, "mk_decode_ragged: batch %d outside [1, %d]", batch, h->cfg.max_tokens);
+  if (capacity < 1) return fail(MK_ERR_INVALID, "mk_decode_ragged: capacity %d", capacity);
+  if (int e = attention_fits(h, capacity, "mk_decode_ragged")) return e;
+  for (int l = 0; l < h->cfg.layers; ++l) {
+    if (!key_caches[l] || !value_caches[l] || !valid_lengths[l]) return fail(MK_ERR_INVALID, "mk_decode_ragged: layer %d state is null", l);
+    if (reinterpret_cast<uintptr_t>(key_caches[l]) % 16 || reinterpret_cast<uintptr_t>(value_caches[l]) % 16)
+      return fail(MK_ERR_ALIGNMENT, "mk_decode_ragged: layer %d cache is not 16-byte aligned", l);
+  }
+  return decode_once(h, ids, positions, batch, key_caches, value_caches, valid_lengths, capacity, logits, stream, nullptr, false, true);
 }
 
 int mk_decode_steps(mk_handle h, int64_t* ids, int64_t* positions, int batch, void* const* key_caches,
@@ -675,36 +798,6 @@ int decode_step(mk_handle h, const int64_t* ids, const int64_t* positions, int b
     if (reinterpret_cast<uintptr_t>(key_caches[l]) % 16 || reinterpret_cast<uintptr_t>(value_caches[l]) % 16)
       return fail(MK_ERR_ALIGNMENT, "mk_decode: layer %d cache is not 16-byte aligned", l);
   }
-  if (batch > kSplitTokens && batch <= 2 * kSplitTokens && small_launch_ok(h, capacity)) {
-    // 5..8 sequences: two launches of the small-launch kernel (3+2, 3+3, 4+3, 4+4 sequences) are faster than one of
-    // the tensor engine (measured: 2 x 2 383 us against 5 213 us at 8).  The sequences are independent; the first
-    // launch works on a snapshot of the shared valid lengths (it advances the snapshot), the second on the
-    // caller's own and publishes them.  The decoder kernels are the same as for any other batch.
-    const int first = (batch + 1) / 2;
-    LengthPointers lens;
-    int32_t* snapshot = at<int32_t>(h, h->cv.len_copy);
-    int32_t* len1[MK_MAX_LAYERS];
-    for (int l = 0; l < L; ++l) {
-      lens.at[l] = valid_lengths[l];
-      len1[l] = snapshot + l;
-    }
-    snapshot_lengths<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(lens, snapshot, L);
-    MK_CUDA(cudaGetLastError());
-    const size_t seq_bytes = static_cast<size_t>(capacity) * h->cfg.kv_heads * h->cfg.head_dim * 2;
-    void* kc2[MK_MAX_LAYERS];
-    void* vc2[MK_MAX_LAYERS];
-    for (int l = 0; l < L; ++l) {
-      kc2[l] = static_cast<uint8_t*>(key_caches[l]) + first * seq_bytes;
-      vc2[l] = static_cast<uint8_t*>(value_caches[l]) + first * seq_bytes;
-    }
-    // Both launches validate the ids and positions of the whole step, so that either both run or both refuse.
-    if (int e = decode_once(h, ids, positions, first, key_caches, value_caches, len1, capacity, logits, stream, tokens_out, sample,
-                            ids, positions, batch))
-      return e;
-    return decode_once(h, ids + first, positions + first, batch - first, kc2, vc2, valid_lengths, capacity,
-                       static_cast<uint8_t*>(logits) + static_cast<size_t>(first) * h->cfg.vocab * 2, stream,
-                       tokens_out ? tokens_out + first : nullptr, sample, ids, positions, batch);
-  }
   return decode_once(h, ids, positions, batch, key_caches, value_caches, valid_lengths, capacity, logits, stream, tokens_out, sample);
 }
 }  // namespace
@@ -712,12 +805,9 @@ int decode_step(mk_handle h, const int64_t* ids, const int64_t* positions, int b
 namespace {
 int decode_once(mk_handle h, const int64_t* ids, const int64_t* positions, int batch, void* const* key_caches,
                 void* const* value_caches, int32_t* const* valid_lengths, int capacity, void* logits, void* stream,
-                int64_t* tokens_out, bool sample, const int64_t* all_ids, const int64_t* all_positions, int all_batch) {
+                int64_t* tokens_out, bool sample, bool ragged) {
   KParams p;
   base_params(h, p);
-  p.check_ids = reinterpret_cast<const long long*>(all_ids);
-  p.check_pos = reinterpret_cast<const long long*>(all_positions);
-  p.check_m = all_ids ? all_batch : 0;
   const int L = h->cfg.layers;
   for (int l = 0; l < L; ++l) {
     p.kc[l] = key_caches[l];
@@ -726,12 +816,14 @@ int decode_once(mk_handle h, const int64_t* ids, const int64_t* positions, int b
   }
   const int ntt = token_tiles(batch);
   p.mode = MODE_DECODE; p.m = batch; p.batch = batch; p.seq = 1; p.capacity = capacity;
-  p.split = (batch <= kSplitTokens && split_table_ok(h->cfg)) ? 1 : 0;
+  p.split = split_table_ok(h->cfg) ? 1 : 0;
   p.phases = at<GemmPhase>(h, h->cv.phases) + (p.split ? 0 : phases_per_table(h->cfg));
-  const bool small = p.split && small_launch_ok(h, capacity);
+  const bool small = !ragged && batch <= kSplitTokens && small_launch_ok(h, capacity);
+  p.ragged = ragged ? 1 : 0;
   if (small) p.phases = at<GemmPhase>(h, h->cv.phases) + 2 * phases_per_table(h->cfg);
   p.n_gemm = 4 * L + 1;
-  p.nbar = 5 * L;
+  p.nbar = 7 * L + 1;  // tensor engine: five per layer and one behind each norm phase (two per layer, one for the lm_head)
+  if (small) p.nbar = 5 * L;
   if (small && h->small_ll) p.nbar = 2 * L;  // stamped hand-offs: only o_proj -> gate/up and down -> next layer keep a grid barrier
   if (small && h->row_ok && batch == 1) {     // one token: the row table, a single grid barrier at the very end
     p.phases = at<GemmPhase>(h, h->cv.phases) + 3 * phases_per_table(h->cfg);
@@ -775,10 +867,10 @@ int mk_prefill(mk_handle h, const int64_t* ids, const int64_t* positions, const 
   const int L = h->cfg.layers;
   const int ntt = token_tiles(static_cast<int>(m));
   p.mode = MODE_PREFILL; p.m = static_cast<int>(m); p.batch = batch; p.seq = sequence; p.capacity = 0;
-  p.split = (m <= kSplitTokens && split_table_ok(h->cfg)) ? 1 : 0;
+  p.split = split_table_ok(h->cfg) ? 1 : 0;
   p.phases = at<GemmPhase>(h, h->cv.phases) + (p.split ? 0 : phases_per_table(h->cfg));
   p.n_gemm = 4 * L + 1;
-  p.nbar = 6 * L;
+  p.nbar = 8 * L + 1;  // as decode, plus one behind the rotation of q and k
   p.stream_once = (ntt == 1);
   p.ids = reinterpret_cast<long long*>(const_cast<int64_t*>(ids));
   p.pos = reinterpret_cast<long long*>(const_cast<int64_t*>(positions));
@@ -801,26 +893,22 @@ int mk_linear(mk_handle h, const void* x, const void* weight, const void* bias, 
   if (n < 1 || k < 64 || k % 64) return fail(MK_ERR_UNSUPPORTED, "mk_linear: k must be a positive multiple of 64");
   if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(y) % 2)
     return fail(MK_ERR_ALIGNMENT, "mk_linear: x must be 16-byte aligned");
-  CUtensorMap* dmap = at<CUtensorMap>(h, h->cv.tmaps) + 3 * maps_per_table(h->cfg);
-  GemmPhase* dphase = at<GemmPhase>(h, h->cv.phases) + 4 * phases_per_table(h->cfg);
-  GemmPhase ph;
+  KParams p;
+  base_params(h, p);
+  GemmPhase& ph = p.linear_phase;
   memset(&ph, 0, sizeof(ph));
   ph.nseg = 1; ph.nacc = 1; ph.k = k;
-  ph.tmap[0] = dmap; ph.w[0] = static_cast<const bf16*>(weight); ph.bias[0] = static_cast<const bf16*>(bias);
+  ph.w[0] = static_cast<const bf16*>(weight); ph.bias[0] = static_cast<const bf16*>(bias);
   ph.n[0] = n;
   ph.epi = EPI_STORE; ph.bmode = B_PLAIN;
   ph.src = static_cast<const bf16*>(x); ph.src_ld = k;
   ph.dst = static_cast<bf16*>(y); ph.dst_ld = n;
-  finish_phase(ph, h->grid, false);
-  CUtensorMap map;
-  if (int e = encode_weight_map(&map, weight, n, k, ph.rows)) return e;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  MK_CUDA(cudaMemcpyAsync(dmap, &map, sizeof(map), cudaMemcpyHostToDevice, s));
-  MK_CUDA(cudaMemcpyAsync(dphase, &ph, sizeof(ph), cudaMemcpyHostToDevice, s));
-  MK_CUDA(cudaStreamSynchronize(s));
-  KParams p;
-  base_params(h, p);
-  p.phases = dphase;
+  finish_phase_tc(ph, h->grid, false, h->cfg.max_tokens);
+  // Phase and descriptors go into the kernel's parameter block: nothing is uploaded, nothing synchronised.
+  bool use3d = h->use3d;
+  if (int e = encode_phase_weight_map(&p.linear_wmap, weight, n, k, ph, use3d)) return e;
+  if (int e = encode_operand_map(&p.linear_xmap, x, m, k, token_tile_of(m))) return e;
+  p.phases = nullptr;
   p.mode = MODE_LINEAR; p.m = m; p.batch = m; p.seq = 1;
   p.n_gemm = 1;
   p.nbar = 0;
@@ -963,6 +1051,41 @@ int mk_ipc_open(const mk_ipc_handle* in, void** pointer, void** base_out) {
 int mk_ipc_close(void* base) {
   if (!base) return MK_OK;
   MK_CUDA(cudaIpcCloseMemHandle(base));
+  return MK_OK;
+}
+
+int mk_describe(mk_handle h, char* buffer, size_t bytes) {
+  if (!h || !buffer || bytes == 0) return fail(MK_ERR_INVALID, "mk_describe: null argument");
+  std::lock_guard<std::mutex> guard(h->lock);
+  size_t used = 0;
+  auto add = [&](const char* fmt, ...) {
+    if (used >= bytes) return;
+    va_list ap;
+    va_start(ap, fmt);
+    const int n = vsnprintf(buffer + used, bytes - used, fmt, ap);
+    va_end(ap);
+    if (n > 0) used += static_cast<size_t>(n);
+  };
+  add("ctas %d, weight copies %s, small-launch tables %s/%s/%s, tp %d/%d\n", h->grid,
+      h->use3d ? "3-D (several K chunks per copy)" : "2-D (one K chunk per copy)", h->fma_ok ? "split-K" : "-",
+      h->small_ll ? "stamped" : "-", h->row_ok ? "rows" : "-", h->cfg.tp_size > 1 ? h->cfg.tp_rank : 0,
+      h->cfg.tp_size > 1 ? h->cfg.tp_size : 1);
+  if (h->bound) {
+    std::vector<GemmPhase> phases(phases_per_table(h->cfg) * 4);
+    MK_CUDA(cudaMemcpy(phases.data(), at<GemmPhase>(h, h->cv.phases), phases.size() * sizeof(GemmPhase), cudaMemcpyDeviceToHost));
+    static const char* names[5] = {"qkv", "o", "gate/up", "down", "lm_head"};
+    for (int table = 0; table < 4; ++table) {
+      if (table == 0 && !split_table_ok(h->cfg)) continue;
+      if (table == 2 && !h->fma_ok) continue;
+      if (table == 3 && !h->row_ok) continue;
+      add("table %d:", table);
+      for (int i = 0; i < 5; ++i) {
+        const GemmPhase& ph = phases[table * phases_per_table(h->cfg) + (i < 4 ? i : 4 * h->cfg.layers)];
+        add(" %s rows %d ksplit %d kb %d units %d;", names[i], ph.rows, ph.ksplit, ph.kb, ph.nunits);
+      }
+      add("\n");
+    }
+  }
   return MK_OK;
 }
 
@@ -1149,7 +1272,7 @@ int mk_kv_attention_static(int q_heads, int kv_heads, int head_dim, const void* 
   view.timeout_cycles = slot.timeout_cycles;
   view.att_scale = static_cast<float>(std::pow(static_cast<double>(head_dim), -0.5));
   view.fma_ok = false; view.small_ll = false; view.row_ok = false; view.trace = nullptr; view.trace_cap = 0;
-  view.mirror = nullptr;
+  view.mirror = nullptr; view.use3d = false;
   view.tp_epoch = 0; view.tp_bound = false;
   for (int r = 0; r < kMaxTp; ++r) view.tp_peer[r] = nullptr;
   if (int e = attention_fits(&view, capacity, "mk_kv_attention_static")) return e;

@@ -1244,6 +1244,7 @@ __global__ void __launch_bounds__(kSmallThreads, 1) megakernel_small(const __gri
   cx.smem_a = smem;
   cx.smem_b = smem + kSmallRingGranules * kGranule;
   cx.misc = reinterpret_cast<SmemMisc*>(cx.smem_b + kBBytes);
+  cx.tc = nullptr;
   cx.deadline = clock64() + p.timeout_cycles;
   cx.cta = blockIdx.x;
   cx.grid = gridDim.x;
@@ -1273,10 +1274,6 @@ __global__ void __launch_bounds__(kSmallThreads, 1) megakernel_small(const __gri
         pos = 0;
       }
       cx.misc->pos_s[t] = pos;
-    }
-    for (int t = tid; t < p.check_m; t += kSmallThreads) {
-      const long long id = p.check_ids[t], pos = p.check_pos[t];
-      if (id < 0 || id >= p.embed_rows || pos < 0 || pos >= p.max_positions) bad = MK_STATUS_BAD_INDEX;
     }
     for (int l = tid; l < p.layers; l += kSmallThreads) {
       const int len = *p.len[l];

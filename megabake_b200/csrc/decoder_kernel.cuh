@@ -1,26 +1,33 @@
 // The persistent decoder megakernel for sm_100a: one cooperative launch runs a
-// whole Llama/Qwen2-style decoder step.
+// whole Llama/Qwen2-style decoder step (decode or prompt pass).
 //
-// Roles inside each CTA (one CTA per SM):
+// Roles inside each CTA (one CTA per SM, 224 threads):
 //   warp 0      weight producer: walks the static schedule of every projection
 //               phase of the launch and streams this CTA's weight tiles through
 //               a ring of TMA-filled shared-memory slots.  Weights never depend
 //               on a barrier, so the stream runs ahead across phases and layers.
+//   warp 6      activation producer: the token operand of a projection is a
+//               bf16 matrix in global memory (normalised rows, attention output,
+//               SiLU*up); once the workers signal that it is complete, this warp
+//               streams its K chunks through a second ring with TMA, entry for
+//               entry in step with the weight ring.  No thread copies operands.
 //   warp 1      MMA issuer: tcgen05.mma with the weight tile as the M operand
-//               and the token activations as the N=16 operand (the "swapAB"
-//               orientation), fp32 accumulators in TMEM.
-//   warps 2-5   workers: build the activation operand in shared memory
-//               (RMSNorm fused here), run the epilogues out of TMEM (bias,
-//               residual add, SiLU*up), the attention phase (RoPE, KV append,
-//               split-context softmax attention) and the grid barriers.
+//               and 16, 32 or 64 tokens as the N operand (the "swapAB"
+//               orientation), fp32 accumulators in TMEM, one commit per ring
+//               entry (an entry carries up to four 64-element K chunks).
+//   warps 2-5   workers: RMSNorm as a distributed pass over token rows, the
+//               epilogues out of TMEM (bias, residual add, SiLU*up, partial
+//               sums), the attention phases (RoPE, KV append, split-context
+//               softmax attention) and the grid barriers.
 //
 // Work split: the output rows of a projection phase are cut into tiles of
-// `rows` rows, chosen on the host so the tile count is just under a multiple of
-// the CTA count.  A CTA runs each of its tiles over the whole reduction length
-// into one TMEM accumulator: a single fp32 chain per output, no partial sums
-// cross CTAs, results do not depend on timing.  Only `rows` rows of the 128-row
+// `rows` rows (a multiple of 8), chosen on the host so the tile count is just
+// under a multiple of the CTA count.  A CTA runs each of its tiles over the
+// whole reduction length into one TMEM accumulator: a single fp32 chain per
+// output, results do not depend on timing.  Only `rows` rows of the 128-row
 // MMA tile hold weights; the tensor core computes the rest on stale bytes and
-// the epilogue ignores them.
+// the epilogue ignores them.  Launches of more than 64 tokens walk token tiles
+// inside each weight tile, so the repeated passes over a tile come from L2.
 //
 // Every device wait is bounded: a wait that runs out records where in the
 // status block, raises the abort flag that all other waits poll, and the CTA
@@ -36,29 +43,38 @@ struct SmemMisc {
   uint64_t empty[kChunkBars];
   uint64_t accfull[2];
   uint64_t accempty[2];
-  uint64_t bfull[2];
-  uint64_t bempty[2];
   uint32_t tmem_base;
   int wabort;   // sticky: a worker thread gave up a wait
   int bad;      // prologue validation result
   int flag;
   int trace_n;  // events this CTA has recorded
-  float rinv[kTok];
-  float red4[4];           // cross-warp sums of the block-wide RMSNorm
   float sred[kSplitTokens][8];   // small-launch kernel: per-token cross-warp sums
   long long pos_s[kSplitTokens]; // small-launch kernel: validated positions
   int len_s[MK_MAX_LAYERS];      // small-launch kernel: valid lengths before this call
-  uint8_t qstart[kChunkBars];  // producer: first ring granule of each chunk in flight (by sequence % kChunkBars)
-  uint8_t qgran[kChunkBars];   // producer: granules of that chunk
+  uint8_t qstart[kChunkBars];  // producer: first ring granule of each entry in flight (by sequence % kChunkBars)
+  uint8_t qgran[kChunkBars];   // producer: granules of that entry
   GemmPhase phase[2];  // worker-side copies of the current / next projection phase
 };
 static_assert(sizeof(SmemMisc) <= kMiscBytes, "misc shared block too large");
 static_assert(kRingGranules < 256, "ring positions are kept in bytes");
 
+// Tensor engine only: the activation ring's barriers and bookkeeping (behind SmemMisc).
+struct SmemMiscTc {
+  uint64_t bfull[kChunkBars];
+  uint64_t bempty[kChunkBars];
+  uint8_t bstart[kChunkBars];
+  uint8_t bgran[kChunkBars];
+  int b_ready;  // projection phases whose activation operand is complete in global memory (workers -> activation producer)
+  int a_ready;  // gated projection phases whose weights may be fetched: the workers no longer use the ring (workers -> weight producer)
+};
+static_assert(sizeof(SmemMiscTc) <= kMiscTcBytes, "tensor-engine misc block too large");
+static_assert(kBBytes / kGranule < 256, "activation ring positions are kept in bytes");
+
 struct Ctx {
   const KParams* p;
   Control* ctrl;
   SmemMisc* misc;
+  SmemMiscTc* tc;   // null in the small-launch kernel
   uint8_t* smem_a;
   uint8_t* smem_b;
   long long deadline;
@@ -69,16 +85,19 @@ struct Ctx {
 struct WorkerState {
   uint32_t tiles;        // accumulator buffers consumed so far
   uint32_t passed;       // grid barriers passed
-  uint32_t be_cnt[2];    // bempty completions consumed per half
-  bool outstanding[2];   // a streamed batch on this half still awaits its bempty
 };
 
 // ---------------------------------------------------------------------------
 // bounded waits
 
+// Waits between CTAs or GPUs (grid barrier, attention exchange, tensor-parallel flag) give up at the
+// deadline; waits inside a CTA's own pipeline (ring slots, accumulators) an eighth of the limit later,
+// so that when a peer is late the status names the wait on the peer, not a thread starved behind it.
 __device__ __forceinline__ bool give_up(const Ctx& cx, int site, int detail) {
   if (ld_relaxed_u32(&cx.ctrl->abort) != 0) return true;
-  if (clock64() > cx.deadline) {
+  const bool internal = site == SITE_PRODUCER_EMPTY || site == SITE_MMA_FULL || site == SITE_MMA_B || site == SITE_MMA_ACC ||
+                        site == SITE_EPI_ACC || site == SITE_B_EMPTY;
+  if (clock64() > cx.deadline + (internal ? (cx.p->timeout_cycles >> 3) : 0)) {
     if (atomicCAS(&cx.ctrl->status, 0, static_cast<int>(MK_STATUS_TIMEOUT)) == 0) {
       cx.ctrl->where = site;
       cx.ctrl->cta = cx.cta;
@@ -137,6 +156,7 @@ __device__ __forceinline__ bool workers_ok(const Ctx& cx, bool ok) {
 // Monotonic-counter grid barrier over the worker warps of every CTA: one
 // release-add to arrive, relaxed polling, one fence once the count is reached.
 __device__ bool grid_barrier(const Ctx& cx, WorkerState& ws, int wtid) {
+  fence_proxy_async_all();  // what this thread stored may be the next phase's TMA-loaded operand in another CTA
   named_bar_sync(1, kWorkers);
   ws.passed += 1;
   if (wtid == 0) {
@@ -177,110 +197,197 @@ __device__ __forceinline__ int k_rotation(int cta, int grid, int kslice) {
   return static_cast<int>((static_cast<long long>(cta) * batches) / grid);  // in batches
 }
 
-// The weight ring hands out runs of 1 KiB granules in FIFO order; a run never
-// wraps.  Producer and MMA issuer replay the same sequence.
-__device__ __forceinline__ int ring_alloc(int& head, int granules) {
-  if (head + granules > kRingGranules) head = 0;
-  const int start = head;
-  head += granules;
-  return start;
+// Phase gp of the launch: a row of the phase table in global memory, or, for a stand-alone projection, the
+// descriptor that came with the kernel parameters.
+__device__ __forceinline__ const GemmPhase* phase_at(const KParams& p, int gp) {
+  return p.mode == MODE_LINEAR ? &p.linear_phase : p.phases + gp;
+}
+
+// Tokens per MMA (UMMA N) for a launch of m tokens: the smallest of 16, 32, 64 that holds them, 64 beyond.
+__device__ __forceinline__ int token_tile(int m) { return m <= 16 ? 16 : (m <= 32 ? 32 : 64); }
+__device__ __forceinline__ int token_tile_index(int m) { return m <= 16 ? 0 : (m <= 32 ? 1 : 2); }
+
+// Every CTA walks its K range from a different starting entry (and wraps), so that at any moment the
+// grid's loads spread over all of a weight row's 128-byte columns.
+__device__ __forceinline__ int group_rotation(int cta, int grid, int groups) {
+  return static_cast<int>((static_cast<long long>(cta) * groups) / grid);
+}
+
+// A ring of 1 KiB granules handed out in FIFO order; an entry never wraps.  Entries are consumed in
+// issue order, so space is reclaimed by retiring the oldest entry in flight (waiting for its `empty`
+// barrier) until the wanted granules are free.  One instance per producer.
+struct RingCursor {
+  int head, seq, oldest;
+};
+
+__device__ __forceinline__ bool ring_claim(const Ctx& cx, RingCursor& rc, int total, int gran, uint64_t* empty,
+                                           uint8_t* qstart, uint8_t* qgran, int site, int gp, int& start) {
+  auto retire = [&]() -> bool {
+    const bool done = wait_mbar(cx, smem_u32(&empty[rc.oldest % kChunkBars]), (rc.oldest / kChunkBars) & 1, site, gp);
+    ++rc.oldest;
+    return done;
+  };
+  auto reclaim = [&](int lo, int hi) -> bool {
+    while (rc.oldest < rc.seq) {
+      const int os = qstart[rc.oldest % kChunkBars], oe = os + qgran[rc.oldest % kChunkBars];
+      if (!(os < hi && lo < oe)) break;
+      if (!retire()) return false;
+    }
+    return true;
+  };
+  if (rc.head + gran > total) {  // the tail fragment is skipped: free it too, then wrap
+    if (!reclaim(rc.head, total)) return false;
+    rc.head = 0;
+  }
+  start = rc.head;
+  rc.head += gran;
+  if (!reclaim(start, start + gran)) return false;
+  if (rc.seq - rc.oldest >= kChunkBars && !retire()) return false;  // barrier pair reuse
+  qstart[rc.seq % kChunkBars] = static_cast<uint8_t>(start);
+  qgran[rc.seq % kChunkBars] = static_cast<uint8_t>(gran);
+  return true;
+}
+
+// Leaving early: every copy already issued must land before the CTA exits.
+__device__ __forceinline__ void ring_drain(const RingCursor& rc, uint64_t* full) {
+  for (int i = max(0, rc.seq - kChunkBars); i < rc.seq; ++i) {
+    const uint32_t bar = smem_u32(&full[i % kChunkBars]);
+    for (uint32_t spins = 0; spins < (1u << 22); ++spins) {
+      if (mbar_try_wait(bar, (i / kChunkBars) & 1)) break;
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------
 // warp 0: weight producer
-
+//
+// An entry of the weight ring holds `kb` consecutive 64-element K chunks of a tile's rows, for each
+// accumulator matrix of the phase (gate and up side by side):
+//     [matrix 0: kb x (rows x 128 B, 128-byte swizzled)][matrix 1: ...]
+// One three-dimensional TMA box (64 elements, rows, kb chunks) brings a matrix's share, so a copy
+// carries 14-32 KB where a single chunk of a 56-row tile would carry 7 KB.
 __device__ __noinline__ void producer_loop(const Ctx& cx) {
   const KParams& p = *cx.p;
   const uint64_t policy = p.stream_once ? l2_policy_evict_first() : l2_policy_evict_normal();
-  const int ntt = (p.m + kTok - 1) / kTok;
+  const int ntok = token_tile(p.m);
+  const int ntt = (p.m + ntok - 1) / ntok;
   SmemMisc* misc = cx.misc;
-  // Chunks are consumed in issue order, so ring space is reclaimed by retiring
-  // the oldest chunk in flight until the wanted granules are free.
-  int head = 0, seq = 0, oldest = 0;
+  RingCursor rc;
+  rc.head = 0; rc.seq = 0; rc.oldest = 0;
   bool ok = true;
-  long long waited = 0;
-  const long long started = clock64();
-  auto retire_oldest = [&](int gp) -> bool {
-    const bool done = wait_mbar_timed(cx, smem_u32(&misc->empty[oldest % kChunkBars]), (oldest / kChunkBars) & 1,
-                                      SITE_PRODUCER_EMPTY, gp, waited);
-    ++oldest;
-    return done;
-  };
-  auto reclaim = [&](int start, int end, int gp) -> bool {  // free [start, end) of the ring
-    while (oldest < seq) {
-      const int os = misc->qstart[oldest % kChunkBars], oe = os + misc->qgran[oldest % kChunkBars];
-      if (!(os < end && start < oe)) break;
-      if (!retire_oldest(gp)) return false;
-    }
-    return true;
-  };
   for (int gp = 0; gp < p.n_gemm && ok; ++gp) {
-    const GemmPhase* ph = p.phases + gp;
-    const int nacc = ph->nacc, gran = ph->gran, nunits = ph->nunits, ksplit = ph->ksplit, kslice = ph->kslice;
-    const int kb = ph->kb;  // K chunks per copy (1 unless this is the small-launch table)
-    const uint32_t bytes = static_cast<uint32_t>(ph->rows) * 128u * static_cast<uint32_t>(kb);
-    const int rot = k_rotation(cx.cta, cx.grid, kslice / kb) * kb;
-    const bool streamed = kslice > kBSlots;
-    const int batches = (kslice + kBHalf - 1) / kBHalf;
-    const CUtensorMap* map_a1 = ph->tmap[1];
-    for (int tt = 0; tt < ntt && ok; ++tt) {
-      for (int unit = cx.cta; unit < nunits && ok; unit += cx.grid) {
-        const int tile = unit / ksplit, slice = unit - tile * ksplit;
-        int seg, row0;
-        tile_origin(ph, tile, seg, row0);
-        const CUtensorMap* map_a0 = ph->tmap[nacc == 2 ? 0 : seg];
-        const int kbase = slice * kslice;
-        // visiting order: rotated within the slice (whole batches when the operand is streamed)
-        int k = streamed ? rot * kBHalf : rot;
-        int batch = rot, left_in_batch = streamed ? min(kBHalf, kslice - rot * kBHalf) : kslice;
-        for (int i = 0; i < kslice && ok; i += kb) {
+    const GemmPhase* ph = phase_at(p, gp);
+    const int nacc = ph->nacc, gran = ph->gran, nunits = ph->nunits, ksplit = ph->ksplit, kslice = ph->kslice, kb = ph->kb;
+    const uint32_t matrix_bytes = static_cast<uint32_t>(ph->rows) * 128u * static_cast<uint32_t>(kb);
+    const int groups = kslice / kb;
+    const int rot = group_rotation(cx.cta, cx.grid, groups);
+    const int map3d = ph->map3d;
+    if (ph->gate) {  // the attention phase before this one streams cache tiles through the ring
+      uint32_t spins = 0;
+      while (*reinterpret_cast<volatile int*>(&cx.tc->a_ready) <= gp) {
+        __nanosleep(64);
+        if ((++spins & 255u) == 0 && give_up(cx, SITE_PRODUCER_EMPTY, -gp)) {
+          ok = false;
+          break;
+        }
+      }
+      if (!ok) break;
+    }
+    for (int unit = cx.cta; unit < nunits && ok; unit += cx.grid) {
+      const int tile = unit / ksplit, slice = unit - tile * ksplit;
+      int seg, row0;
+      tile_origin(ph, tile, seg, row0);
+      const int kbase = slice * kslice;
+      for (int tt = 0; tt < ntt && ok; ++tt) {
+        int g = rot;
+        for (int i = 0; i < groups; ++i) {
+          int start;
+          if (!ring_claim(cx, rc, kRingGranules, gran, misc->empty, misc->qstart, misc->qgran, SITE_PRODUCER_EMPTY, gp, start)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = smem_u32(&misc->full[rc.seq % kChunkBars]);
+          const uint32_t dst = smem_u32(cx.smem_a + start * kGranule);
+          mbar_expect_tx(full, matrix_bytes * static_cast<uint32_t>(nacc));
           for (int a = 0; a < nacc; ++a) {
-            if (head + gran > kRingGranules) {  // the tail fragment is skipped: free it too, then wrap
-              if (!reclaim(head, kRingGranules, gp)) { ok = false; break; }
-              head = 0;
+            const CUtensorMap* map = p.mode == MODE_LINEAR ? &p.linear_wmap : ph->tmap[nacc == 2 ? a : seg];
+            if (map3d) {
+              tma_load_3d(dst + a * matrix_bytes, map, 0, row0, kbase + g * kb, full, policy);
+            } else {
+              for (int c = 0; c < kb; ++c)
+                tma_load_2d(dst + a * matrix_bytes + c * (matrix_bytes / kb), map, (kbase + g * kb + c) * kChunkK, row0, full, policy);
             }
-            const int start = head;
-            head += gran;
-            if (!reclaim(start, start + gran, gp)) { ok = false; break; }
-            if (seq - oldest >= kChunkBars && !retire_oldest(gp)) { ok = false; break; }  // barrier pair reuse
-            misc->qstart[seq % kChunkBars] = static_cast<uint8_t>(start);
-            misc->qgran[seq % kChunkBars] = static_cast<uint8_t>(gran);
-            const uint32_t full = smem_u32(&misc->full[seq % kChunkBars]);
-            mbar_expect_tx(full, bytes);
-            tma_load_2d(smem_u32(cx.smem_a + start * kGranule), a ? map_a1 : map_a0, (kbase + k) * kChunkK, row0, full,
-                        policy);
-            ++seq;
           }
-          // next chunk of the slice in visiting order
-          k += kb;
-          if (streamed) {
-            if (--left_in_batch == 0) {
-              batch = (batch + 1 == batches) ? 0 : batch + 1;
-              k = batch * kBHalf;
-              left_in_batch = min(kBHalf, kslice - k);
-            }
-          } else if (k == kslice) {
-            k = 0;
-          }
+          ++rc.seq;
+          g = (g + 1 == groups) ? 0 : g + 1;
         }
       }
     }
   }
-  if (p.trace_cap >= 8) {  // role profile in the last slots of this CTA's trace row
-    unsigned long long* row = p.trace + static_cast<size_t>(cx.cta) * p.trace_cap + p.trace_cap;
-    row[-1] = (7ull << 56) | static_cast<unsigned long long>(clock64() - started);
-    row[-2] = (8ull << 56) | static_cast<unsigned long long>(waited);
-    row[-3] = (9ull << 56) | static_cast<unsigned long long>(seq);
-  }
-  if (!ok) {
-    // Leaving early: every copy already issued must land before the CTA exits.
-    for (int i = max(0, seq - kChunkBars); i < seq; ++i) {
-      const uint32_t bar = smem_u32(&misc->full[i % kChunkBars]);
-      for (uint32_t spins = 0; spins < (1u << 22); ++spins) {
-        if (mbar_try_wait(bar, (i / kChunkBars) & 1)) break;
+  if (!ok) ring_drain(rc, misc->full);
+}
+
+// ---------------------------------------------------------------------------
+// warp 6: activation producer
+//
+// The token operand of phase gp is rows [tt * ntok, +ntok) x K of a bf16 matrix in global memory.
+// Its entries mirror the weight ring's one for one (same unit, token tile and K group order): entry
+// = kb boxes of (64 elements x ntok tokens), 128-byte swizzled, rows past the matrix read as zero.
+// The matrix is written by other CTAs during the preceding phase, so this warp starts a phase only
+// after the workers, having passed the grid barrier, publish it in `b_ready`.
+__device__ __noinline__ void activation_producer_loop(const Ctx& cx) {
+  const KParams& p = *cx.p;
+  const uint64_t policy = l2_policy_evict_normal();
+  const int ntok = token_tile(p.m), tile_index = token_tile_index(p.m);
+  const int ntt = (p.m + ntok - 1) / ntok;
+  SmemMiscTc* tc = cx.tc;
+  RingCursor rc;
+  rc.head = 0; rc.seq = 0; rc.oldest = 0;
+  bool ok = true;
+  for (int gp = 0; gp < p.n_gemm && ok; ++gp) {
+    const GemmPhase* ph = phase_at(p, gp);
+    const int nunits = ph->nunits, ksplit = ph->ksplit, kslice = ph->kslice, kb = ph->kb;
+    if (cx.cta >= nunits) continue;
+    {  // wait for the operand of this phase
+      uint32_t spins = 0;
+      while (*reinterpret_cast<volatile int*>(&tc->b_ready) <= gp) {
+        __nanosleep(64);
+        if ((++spins & 255u) == 0 && give_up(cx, SITE_MMA_B, gp)) {
+          ok = false;
+          break;
+        }
+      }
+      if (!ok) break;
+      fence_proxy_async_all();  // generic-proxy stores of the operand (acquired through the barrier) before async-proxy reads
+    }
+    const CUtensorMap* map = p.mode == MODE_LINEAR ? &p.linear_xmap : ph->bmap[tile_index];
+    const int groups = kslice / kb;
+    const int rot = group_rotation(cx.cta, cx.grid, groups);
+    const int gran = kb * ntok / 8;
+    const uint32_t chunk_bytes = static_cast<uint32_t>(ntok) * 128u;
+    for (int unit = cx.cta; unit < nunits && ok; unit += cx.grid) {
+      const int slice = unit % ksplit;
+      const int kbase = slice * kslice;
+      for (int tt = 0; tt < ntt && ok; ++tt) {
+        int g = rot;
+        for (int i = 0; i < groups; ++i) {
+          int start;
+          if (!ring_claim(cx, rc, kBBytes / kGranule, gran, tc->bempty, tc->bstart, tc->bgran, SITE_B_EMPTY, gp, start)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = smem_u32(&tc->bfull[rc.seq % kChunkBars]);
+          const uint32_t dst = smem_u32(cx.smem_b + start * kGranule);
+          mbar_expect_tx(full, chunk_bytes * static_cast<uint32_t>(kb));
+          for (int c = 0; c < kb; ++c)
+            tma_load_2d(dst + c * chunk_bytes, map, (kbase + g * kb + c) * kChunkK, tt * ntok, full, policy);
+          ++rc.seq;
+          g = (g + 1 == groups) ? 0 : g + 1;
+        }
       }
     }
   }
+  if (!ok) ring_drain(rc, tc->bfull);
 }
 
 // ---------------------------------------------------------------------------
@@ -288,86 +395,62 @@ __device__ __noinline__ void producer_loop(const Ctx& cx) {
 
 __device__ __noinline__ void mma_loop(const Ctx& cx) {
   const KParams& p = *cx.p;
-  const int ntt = (p.m + kTok - 1) / kTok;
+  const int ntok = token_tile(p.m);
+  const int ntt = (p.m + ntok - 1) / ntok;
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&cx.misc->tmem_base);
-  constexpr uint32_t idesc = umma_idesc_bf16(kTileRows, kTok);
+  const uint32_t idesc = umma_idesc_bf16(kTileRows, ntok);
   const uint64_t desc_base = umma_desc_sw128(0);
-  const uint32_t ring_base = smem_u32(cx.smem_a), b_region = smem_u32(cx.smem_b);
-  int head = 0, seq = 0;
-  uint32_t q = 0, bf_cnt[2] = {0, 0};
-  long long wait_full = 0, wait_other = 0;
-  const long long started = clock64();
+  const uint32_t ring_base = smem_u32(cx.smem_a), b_base = smem_u32(cx.smem_b);
+  const uint32_t b_chunk = static_cast<uint32_t>(ntok) * 128u;
+  SmemMisc* misc = cx.misc;
+  SmemMiscTc* tc = cx.tc;
+  int seq = 0;
+  uint32_t q = 0;
   for (int gp = 0; gp < p.n_gemm; ++gp) {
-    const GemmPhase* ph = p.phases + gp;
-    const int nacc = ph->nacc, gran = ph->gran, nunits = ph->nunits, kslice = ph->kslice;
-    const bool per_unit = ph->ksplit > 1;      // the operand differs from unit to unit
-    const bool streamed = kslice > kBSlots;    // the operand does not fit: batches ping-pong through two halves
-    const int rot = k_rotation(cx.cta, cx.grid, kslice);
-    const int batches = streamed ? (kslice + kBHalf - 1) / kBHalf : 1;
+    const GemmPhase* ph = phase_at(p, gp);
+    const int nacc = ph->nacc, nunits = ph->nunits, kslice = ph->kslice, kb = ph->kb;
+    const uint32_t a_chunk = static_cast<uint32_t>(ph->rows) * 128u;
+    const int groups = kslice / kb;
     if (cx.cta >= nunits) continue;
-    for (int tt = 0; tt < ntt; ++tt) {
-      for (int unit = cx.cta; unit < nunits; unit += cx.grid) {
-        if (!streamed && (per_unit || unit == cx.cta)) {
-          for (int h = 0; h < (kslice > kBHalf ? 2 : 1); ++h) {
-            if (!wait_mbar_timed(cx, smem_u32(&cx.misc->bfull[h]), bf_cnt[h] & 1u, SITE_MMA_B, gp, wait_other)) return;
-            ++bf_cnt[h];
-          }
-          tc_fence_after();
-        }
+    for (int unit = cx.cta; unit < nunits; unit += cx.grid) {
+      for (int tt = 0; tt < ntt; ++tt) {
         const uint32_t buf = q & 1u;
-        if (!wait_mbar_timed(cx, smem_u32(&cx.misc->accempty[buf]), ((q >> 1) & 1u) ^ 1u, SITE_MMA_ACC, gp, wait_other)) return;
+        if (!wait_mbar(cx, smem_u32(&misc->accempty[buf]), ((q >> 1) & 1u) ^ 1u, SITE_MMA_ACC, gp)) return;
         tc_fence_after();
         uint32_t accumulate = 0;
-        for (int vb = 0; vb < batches; ++vb) {
-          int b = rot + vb;
-          if (b >= batches) b -= batches;
-          const int h = vb & 1;
-          const int len = streamed ? min(kBHalf, kslice - b * kBHalf) : kslice;
-          if (streamed) {
-            if (!wait_mbar_timed(cx, smem_u32(&cx.misc->bfull[h]), bf_cnt[h] & 1u, SITE_MMA_B, gp, wait_other)) return;
-            ++bf_cnt[h];
-            tc_fence_after();
-          }
-          int slot = streamed ? h * kBHalf : rot;
-          for (int j = 0; j < len; ++j) {
-            const uint64_t b_desc = desc_base + ((b_region + slot * kBSlotBytes) >> 4);
+        for (int i = 0; i < groups; ++i) {
+          const uint32_t parity = (seq / kChunkBars) & 1;
+          if (!wait_mbar(cx, smem_u32(&misc->full[seq % kChunkBars]), parity, SITE_MMA_FULL, gp)) return;
+          if (!wait_mbar(cx, smem_u32(&tc->bfull[seq % kChunkBars]), parity, SITE_MMA_B, gp)) return;
+          tc_fence_after();
+          // the producers recorded where they put this entry before they issued its copies
+          const uint32_t a_addr = ring_base + static_cast<uint32_t>(misc->qstart[seq % kChunkBars]) * kGranule;
+          const uint32_t b_addr = b_base + static_cast<uint32_t>(tc->bstart[seq % kChunkBars]) * kGranule;
+          for (int c = 0; c < kb; ++c) {
+            const uint64_t b_desc = desc_base + ((b_addr + c * b_chunk) >> 4);
             for (int a = 0; a < nacc; ++a) {
-              if (head + gran > kRingGranules) head = 0;
-              const uint32_t a_addr = ring_base + head * kGranule;
-              head += gran;
-              if (!wait_mbar_timed(cx, smem_u32(&cx.misc->full[seq % kChunkBars]), (seq / kChunkBars) & 1, SITE_MMA_FULL, gp, wait_full))
-                return;
-              tc_fence_after();
-              const uint64_t a_desc = desc_base + (a_addr >> 4);
-              const uint32_t d = tmem + (buf * 2u + static_cast<uint32_t>(a)) * kTok;
+              const uint64_t a_desc = desc_base + ((a_addr + (a * kb + c) * a_chunk) >> 4);
+              const uint32_t d = tmem + (buf * 2u + static_cast<uint32_t>(a)) * kMaxTok;
               umma_bf16(d, a_desc, b_desc, idesc, accumulate);
               umma_bf16(d, a_desc + 2, b_desc + 2, idesc, 1u);
               umma_bf16(d, a_desc + 4, b_desc + 4, idesc, 1u);
               umma_bf16(d, a_desc + 6, b_desc + 6, idesc, 1u);
-              umma_commit(smem_u32(&cx.misc->empty[seq % kChunkBars]));
-              ++seq;
             }
             accumulate = 1u;
-            ++slot;
-            if (!streamed && slot == kslice) slot = 0;
           }
-          if (streamed) umma_commit(smem_u32(&cx.misc->bempty[h]));
+          umma_commit(smem_u32(&misc->empty[seq % kChunkBars]));
+          umma_commit(smem_u32(&tc->bempty[seq % kChunkBars]));
+          ++seq;
         }
-        umma_commit(smem_u32(&cx.misc->accfull[buf]));
+        umma_commit(smem_u32(&misc->accfull[buf]));
         ++q;
       }
     }
   }
-  if (p.trace_cap >= 8) {
-    unsigned long long* row = p.trace + static_cast<size_t>(cx.cta) * p.trace_cap + p.trace_cap;
-    row[-4] = (10ull << 56) | static_cast<unsigned long long>(clock64() - started);
-    row[-5] = (11ull << 56) | static_cast<unsigned long long>(wait_full);
-    row[-6] = (12ull << 56) | static_cast<unsigned long long>(wait_other);
-  }
 }
 
 // ---------------------------------------------------------------------------
-// workers: activation operand staging
+// workers: helpers for rows of activations
 
 __device__ __forceinline__ const bf16* activation_row(const KParams& p, const GemmPhase* ph, int token) {
   if (ph->gather) {
@@ -404,11 +487,6 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
   return make_uint4(pack2(f[0], f[1]), pack2(f[2], f[3]), pack2(f[4], f[5]), pack2(f[6], f[7]));
 }
 
-// Swizzled (SWIZZLE_128B, K-major) address of 8 elements: slot = K chunk, t = token row, vec = 16-byte column.
-__device__ __forceinline__ uint8_t* b_slot_addr(const Ctx& cx, int slot, int t, int vec) {
-  return cx.smem_b + slot * kBSlotBytes + (t >> 3) * 1024 + (t & 7) * 128 + ((vec ^ (t & 7)) << 4);
-}
-
 // Normalise one 8-element vector: w * bf16(x * rinv), the two roundings of the
 // Hugging Face RMSNorm.
 // The second product is taken on bf16 pairs: the product of two bf16 values is exact in fp32, so
@@ -424,156 +502,6 @@ __device__ __forceinline__ uint4 normalise_vec(const uint4 xu, const uint4 wu, f
   unpack8(xu, x);
   return make_uint4(mul_bf16x2(wu.x, pack2(x[0] * r, x[1] * r)), mul_bf16x2(wu.y, pack2(x[2] * r, x[3] * r)),
                     mul_bf16x2(wu.z, pack2(x[4] * r, x[5] * r)), mul_bf16x2(wu.w, pack2(x[6] * r, x[7] * r)));
-}
-
-// RMSNorm statistics of the rows of one token tile: rinv[t] = 1/sqrt(mean(x^2)+eps).
-// One warp per token; eight 16-byte loads are in flight per lane before any is used.
-__device__ __noinline__ void norm_stats(const Ctx& cx, const GemmPhase* ph, int t0, int mt, int wtid) {
-  const KParams& p = *cx.p;
-  const int warp = wtid >> 5, lane = wtid & 31;
-  const int nvec = ph->k / 8;
-  for (int t = warp; t < mt; t += kWorkerWarps) {
-    const uint4* row = reinterpret_cast<const uint4*>(activation_row(p, ph, t0 + t));
-    float sum = 0.f;
-    for (int v0 = 0; v0 < nvec; v0 += 32 * 8) {
-      uint4 u[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int v = v0 + i * 32 + lane;
-        u[i] = v < nvec ? __ldcg(row + v) : make_uint4(0, 0, 0, 0);
-      }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float f[8];
-        unpack8(u[i], f);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) sum = fmaf(f[e], f[e], sum);
-      }
-    }
-    sum = warp_sum(sum);
-    if (lane == 0) cx.misc->rinv[t] = 1.0f / sqrtf(sum / static_cast<float>(ph->k) + p.eps);
-  }
-  named_bar_sync(1, kWorkers);
-}
-
-// RMSNorm fused with staging for a reduction length that fits the activation
-// slots (K <= 2048): one warp per token keeps the row in registers between the
-// statistics and the normalised store, so the row is read once.
-__device__ __noinline__ void stage_norm_resident(const Ctx& cx, const GemmPhase* ph, int t0, int mt, int wtid) {
-  const KParams& p = *cx.p;
-  const int warp = wtid >> 5, lane = wtid & 31;
-  const int nvec = ph->k / 8;  // <= 256
-  const uint4* wrow = reinterpret_cast<const uint4*>(ph->normw);
-  constexpr int kRows = 2;  // token rows of a warp in flight together: all their loads are issued before the first is used
-#pragma unroll 1
-  for (int tb = warp; tb < mt; tb += kRows * kWorkerWarps) {
-    uint4 x[kRows][8];
-#pragma unroll
-    for (int r = 0; r < kRows; ++r) {
-      const int t = tb + r * kWorkerWarps;
-      const uint4* row = reinterpret_cast<const uint4*>(activation_row(p, ph, t0 + min(t, mt - 1)));
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int v = i * 32 + lane;
-        x[r][i] = (t < mt && v < nvec) ? __ldcg(row + v) : make_uint4(0, 0, 0, 0);
-      }
-    }
-#pragma unroll
-    for (int r = 0; r < kRows; ++r) {
-      const int t = tb + r * kWorkerWarps;
-      if (t >= mt) break;  // warp-uniform
-      float sum = 0.f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float f[8];
-        unpack8(x[r][i], f);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) sum = fmaf(f[e], f[e], sum);
-      }
-      sum = warp_sum(sum);
-      const float rinv = 1.0f / sqrtf(sum / static_cast<float>(ph->k) + p.eps);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int v = i * 32 + lane;
-        if (v < nvec)  // the norm weights stay in L1 between rows
-          *reinterpret_cast<uint4*>(b_slot_addr(cx, v >> 3, t, v & 7)) = normalise_vec(x[r][i], __ldg(wrow + v), rinv);
-      }
-    }
-  }
-}
-
-// RMSNorm fused with staging, one token at a time over the whole worker block
-// (two 8-element vectors per thread, K <= 2048).  This variant also applies the
-// pending residual update: x = residual + bf16(sum of the previous projection's
-// fp32 K-slice partials, in slice order), writes this CTA's share of x back as
-// the new residual stream, and normalises x.  Every load of a token is issued
-// before the first is used.
-__device__ __noinline__ void stage_norm_block(const Ctx& cx, const GemmPhase* ph, int t0, int mt, int wtid) {
-  const KParams& p = *cx.p;
-  const int warp = wtid >> 5, lane = wtid & 31;
-  const int nvec = ph->k / 8;  // <= 256
-  const int parts = ph->add_parts;
-  const int writers = min(cx.grid, ph->nunits);  // only CTAs that have a unit in this phase get here
-  const uint4* wrow = reinterpret_cast<const uint4*>(ph->normw);
-  for (int t = 0; t < mt; ++t) {
-    const uint4* row = reinterpret_cast<const uint4*>(activation_row(p, ph, t0 + t));
-    uint4 x[2], w[2];
-    float4 lo[2][kMaxSplit], hi[2][kMaxSplit];
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int v = i * kWorkers + wtid;
-      x[i] = make_uint4(0, 0, 0, 0);
-      w[i] = x[i];
-      if (v < nvec) {
-        x[i] = __ldcg(row + v);
-        w[i] = __ldg(wrow + v);
-#pragma unroll
-        for (int s8 = 0; s8 < kMaxSplit; ++s8) {
-          if (s8 < parts) {
-            const float4* part = reinterpret_cast<const float4*>(
-                ph->partial + (static_cast<size_t>(s8) * p.m + (t0 + t)) * ph->k) + v * 2;
-            lo[i][s8] = __ldcg(part);
-            hi[i][s8] = __ldcg(part + 1);
-          }
-        }
-      }
-    }
-    float sum = 0.f;
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int v = i * kWorkers + wtid;
-      float f[8];
-      unpack8(x[i], f);
-      if (parts > 0 && v < nvec) {
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int s8 = 0; s8 < kMaxSplit; ++s8) {
-          if (s8 < parts) {
-            acc[0] += lo[i][s8].x; acc[1] += lo[i][s8].y; acc[2] += lo[i][s8].z; acc[3] += lo[i][s8].w;
-            acc[4] += hi[i][s8].x; acc[5] += hi[i][s8].y; acc[6] += hi[i][s8].z; acc[7] += hi[i][s8].w;
-          }
-        }
-#pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] = bf16_round(f[e] + bf16_round(acc[e]));
-        x[i] = pack8(f);
-      }
-      if (ph->h_out && v < nvec && (v * writers) / nvec == cx.cta)
-        __stcg(reinterpret_cast<uint4*>(ph->h_out + static_cast<size_t>(t0 + t) * ph->k) + v, x[i]);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) sum = fmaf(f[e], f[e], sum);
-    }
-    sum = warp_sum(sum);
-    named_bar_sync(1, kWorkers);  // red4 of the previous token has been read
-    if (lane == 0) cx.misc->red4[warp] = sum;
-    named_bar_sync(1, kWorkers);
-    const float total = ((cx.misc->red4[0] + cx.misc->red4[1]) + cx.misc->red4[2]) + cx.misc->red4[3];
-    const float r = 1.0f / sqrtf(total / static_cast<float>(ph->k) + p.eps);
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int v = i * kWorkers + wtid;
-      if (v < nvec) *reinterpret_cast<uint4*>(b_slot_addr(cx, v >> 3, t, v & 7)) = normalise_vec(x[i], w[i], r);
-    }
-  }
 }
 
 // Attention output for 8 consecutive columns of one token: the bf16 buffer when
@@ -606,64 +534,6 @@ __device__ __forceinline__ uint4 attention_vec(const KParams& p, int token, int 
     }
   }
   return pack8(acc);
-}
-
-// One 8-element vector of the activation operand for (token, column).
-__device__ __forceinline__ uint4 activation_vec(const Ctx& cx, const GemmPhase* ph, int token, int t, int col,
-                                                int nch) {
-  const KParams& p = *cx.p;
-  if (ph->bmode == B_ATTN) return attention_vec(p, token, col, nch);
-  const uint4 u = __ldcg(reinterpret_cast<const uint4*>(activation_row(p, ph, token) + col));
-  if (ph->bmode != B_NORM) return u;
-  return normalise_vec(u, __ldg(reinterpret_cast<const uint4*>(ph->normw + col)), cx.misc->rinv[t]);
-}
-
-// Stage K chunks [k0, k1) of the token tile into slots slot0, slot0+1, ...
-// (B_NORM expects rinv to be ready).  Plain loads go four at a time per thread.
-__device__ __noinline__ void stage_chunks(const Ctx& cx, const GemmPhase* ph, int k0, int k1, int slot0, int t0, int mt,
-                                          int wtid, int nch) {
-  const KParams& p = *cx.p;
-  const int per_slot = mt * 8;
-  const int items = (k1 - k0) * per_slot;
-  if ((ph->bmode == B_PLAIN && !ph->gather) || (ph->bmode == B_ATTN && nch <= 1)) {
-    // Rows of a bf16 buffer: eight loads per thread are in flight before the first store.
-    constexpr int kDepth = 8;
-    const bf16* base = (ph->bmode == B_PLAIN) ? ph->src + static_cast<size_t>(t0) * ph->src_ld
-                                              : p.attn + static_cast<size_t>(t0) * p.q_heads * p.head_dim;
-    const size_t ld = (ph->bmode == B_PLAIN) ? static_cast<size_t>(ph->src_ld) : static_cast<size_t>(p.q_heads) * p.head_dim;
-    // item = wtid + n * kWorkers -> (slot s, row and column `rem`).  When a slot's items divide the block
-    // (token tiles of 1, 2, 4, 8 or 16 rows) `rem` is fixed and s advances by a constant: no division.
-    const bool regular = (kWorkers % per_slot) == 0;
-    const int s_first = wtid / per_slot, rem_fixed = wtid - s_first * per_slot, s_step = kWorkers / per_slot;
-    for (int n0 = 0; wtid + n0 * kWorkers < items; n0 += kDepth) {
-      uint4 xu[kDepth];
-#pragma unroll
-      for (int i = 0; i < kDepth; ++i) {
-        const int item = wtid + (n0 + i) * kWorkers;
-        if (item < items) {
-          const int s = regular ? s_first + (n0 + i) * s_step : item / per_slot;
-          const int rem = regular ? rem_fixed : item - s * per_slot;
-          xu[i] = __ldcg(reinterpret_cast<const uint4*>(base + (rem >> 3) * ld + (k0 + s) * kChunkK + (rem & 7) * 8));
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < kDepth; ++i) {
-        const int item = wtid + (n0 + i) * kWorkers;
-        if (item < items) {
-          const int s = regular ? s_first + (n0 + i) * s_step : item / per_slot;
-          const int rem = regular ? rem_fixed : item - s * per_slot;
-          *reinterpret_cast<uint4*>(b_slot_addr(cx, slot0 + s, rem >> 3, rem & 7)) = xu[i];
-        }
-      }
-    }
-    return;
-  }
-  for (int item = wtid; item < items; item += kWorkers) {
-    const int s = item / per_slot, rem = item - s * per_slot;
-    const int t = rem >> 3, vec = rem & 7;
-    *reinterpret_cast<uint4*>(b_slot_addr(cx, slot0 + s, t, vec)) =
-        activation_vec(cx, ph, t0 + t, t, (k0 + s) * kChunkK + vec * 8, nch);
-  }
 }
 
 // ---------------------------------------------------------------------------
@@ -753,117 +623,77 @@ __device__ __forceinline__ void apply_epilogue(const Ctx& cx, const GemmPhase* p
 // worker pays a global round trip for it after the barrier.
 __device__ __forceinline__ void prefetch_phase(const Ctx& cx, int gp, int wtid) {
   if (gp >= cx.p->n_gemm) return;
-  const uint32_t* src = reinterpret_cast<const uint32_t*>(cx.p->phases + gp);
+  const uint32_t* src = reinterpret_cast<const uint32_t*>(phase_at(*cx.p, gp));
   uint32_t* dst = reinterpret_cast<uint32_t*>(&cx.misc->phase[gp & 1]);
   for (int i = wtid; i < static_cast<int>(sizeof(GemmPhase) / 4); i += kWorkers) dst[i] = __ldg(src + i);
 }
 
-// Wait until the MMA issuer has finished with the streamed batch last staged on half h.
-__device__ __forceinline__ bool acquire_half(const Ctx& cx, WorkerState& ws, int h, int gp) {
-  if (!ws.outstanding[h]) return true;
-  const bool ok = wait_mbar(cx, smem_u32(&cx.misc->bempty[h]), ws.be_cnt[h] & 1u, SITE_B_EMPTY, gp);
-  ws.be_cnt[h] += 1;
-  ws.outstanding[h] = false;
-  return ok;
-}
-
-// Build the activation operand for K chunks [k0, k0 + count) of the token tile in slots 0.. (not streamed).
-__device__ __forceinline__ void stage_operand(const Ctx& cx, const GemmPhase* ph, int k0, int count, int t0, int mt,
-                                              int wtid, int nch) {
-  if (ph->bmode == B_NORM) {
-    if (ph->add_parts > 0 || ph->h_out != nullptr || mt <= 2) stage_norm_block(cx, ph, t0, mt, wtid);
-    else stage_norm_resident(cx, ph, t0, mt, wtid);
-  } else {
-    stage_chunks(cx, ph, k0, k0 + count, 0, t0, mt, wtid, nch);
-  }
-}
-
-// The same for the tcgen05 engine: make the slots visible to the MMA and tell the issuer.
-__device__ __forceinline__ void stage_resident(const Ctx& cx, const GemmPhase* ph, int k0, int count, int t0, int mt,
-                                               int wtid, int nch) {
-  stage_operand(cx, ph, k0, count, t0, mt, wtid, nch);
-  fence_proxy_async_smem();
-  mbar_arrive(smem_u32(&cx.misc->bfull[0]));
-  if (count > kBHalf) mbar_arrive(smem_u32(&cx.misc->bfull[1]));
-}
-
-// Projection phase on the tcgen05 engine, worker side.  The caller has made
-// phase gp's descriptor visible in cx.misc->phase[gp & 1].
+// Projection phase on the tcgen05 engine, worker side: the epilogues.  The caller has made phase
+// gp's descriptor visible in cx.misc->phase[gp & 1] and published the phase's operand (signal_operand).
+// A warp may read TMEM lanes [32 * (warp index % 4), +32): thread (quadrant, lane) finishes weight row
+// quadrant * 32 + lane of the tile, sixteen token columns at a time.
 __device__ __noinline__ bool worker_gemm_tc(const Ctx& cx, int gp, WorkerState& ws, int wtid) {
   const KParams& p = *cx.p;
   const GemmPhase* ph = &cx.misc->phase[gp & 1];
-  const int ntt = (p.m + kTok - 1) / kTok;
-  const int nacc = ph->nacc, nunits = ph->nunits, rows = ph->rows, ksplit = ph->ksplit, kslice = ph->kslice;
-  const bool per_unit = ksplit > 1;
-  const bool streamed = kslice > kBSlots;
+  const int ntok = token_tile(p.m);
+  const int ntt = (p.m + ntok - 1) / ntok;
+  const int nacc = ph->nacc, nunits = ph->nunits, rows = ph->rows, ksplit = ph->ksplit;
   const int quad = ((wtid >> 5) + 2) & 3;  // TMEM lane quadrant this warp may read
   const int rloc = quad * 32 + (wtid & 31);
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&cx.misc->tmem_base);
-  const int nch = (ph->bmode == B_ATTN) ? *reinterpret_cast<volatile int*>(&cx.ctrl->att_nch) : 1;
   if (cx.cta < nunits) {
-    for (int tt = 0; tt < ntt; ++tt) {
-      const int t0 = tt * kTok;
-      const int mt = min(kTok, p.m - t0);
-      trace_event(cx, wtid, EV_PHASE_ENTER);
-      if (streamed && ph->bmode == B_NORM) norm_stats(cx, ph, t0, mt, wtid);
-      for (int unit = cx.cta; unit < nunits; unit += cx.grid) {
-        const int tile = unit / ksplit, slice = unit - tile * ksplit;
-        if (!streamed) {
-          if (per_unit || unit == cx.cta) {
-            bool ok = acquire_half(cx, ws, 0, gp);
-            ok = acquire_half(cx, ws, 1, gp) && ok;
-            if (!workers_ok(cx, ok)) return false;
-            stage_resident(cx, ph, slice * kslice, kslice, t0, mt, wtid, nch);
-            if (unit == cx.cta) trace_event(cx, wtid, EV_B_STAGED);
-          }
-        } else {
-          const int batches = (kslice + kBHalf - 1) / kBHalf;
-          const int rot = k_rotation(cx.cta, cx.grid, kslice);
-          for (int vb = 0; vb < batches; ++vb) {
-            const int b = (rot + vb) % batches, h = vb & 1;
-            if (!workers_ok(cx, acquire_half(cx, ws, h, gp))) return false;
-            const int k0 = slice * kslice + b * kBHalf;
-            stage_chunks(cx, ph, k0, min(slice * kslice + kslice, k0 + kBHalf), h * kBHalf, t0, mt, wtid, nch);
-            fence_proxy_async_smem();
-            mbar_arrive(smem_u32(&cx.misc->bfull[h]));
-            ws.outstanding[h] = true;
-          }
-        }
-        int seg, row0;
-        tile_origin(ph, tile, seg, row0);
-        const int n = row0 + rloc;
-        const bool valid = rloc < rows && n < ph->n[seg];
-        float pre[kTok];
-        if (valid) epilogue_prefetch<kTok>(cx, ph, seg, n, t0, mt, pre);
+    trace_event(cx, wtid, EV_PHASE_ENTER);
+    for (int unit = cx.cta; unit < nunits; unit += cx.grid) {
+      const int tile = unit / ksplit, slice = unit - tile * ksplit;
+      int seg, row0;
+      tile_origin(ph, tile, seg, row0);
+      const int n = row0 + rloc;
+      const bool valid = rloc < rows && n < ph->n[seg];
+      for (int tt = 0; tt < ntt; ++tt) {
         const uint32_t buf = ws.tiles & 1u;
         bool ok = wait_mbar(cx, smem_u32(&cx.misc->accfull[buf]), (ws.tiles >> 1) & 1u, SITE_EPI_ACC, gp);
         ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below needs the whole warp
-        if (unit == cx.cta) trace_event(cx, wtid, EV_FIRST_ACC);
+        if (unit == cx.cta && tt == 0) trace_event(cx, wtid, EV_FIRST_ACC);
         tc_fence_after();
-        float v[2][kTok];
-        if (ok && quad * 32 < rows) {
-          tmem_ld16(tmem + (static_cast<uint32_t>(quad * 32) << 16) + (buf * 2u) * kTok, v[0]);
-          if (nacc == 2) tmem_ld16(tmem + (static_cast<uint32_t>(quad * 32) << 16) + (buf * 2u + 1u) * kTok, v[1]);
+        const int tile_tokens = min(ntok, p.m - tt * ntok);
+        // the two warps that share a TMEM lane quadrant take alternate groups of sixteen token columns
+        for (int cg = (wtid >> 5) / 4; cg * kTok < tile_tokens; cg += kWorkerWarps / 4) {
+          const int t0 = tt * ntok + cg * kTok;
+          const int mt = min(kTok, p.m - t0);
+          float pre[kTok];
+          if (valid) epilogue_prefetch<kTok>(cx, ph, seg, n, t0, mt, pre);
+          float v[2][kTok];
+          if (ok && quad * 32 < rows) {
+            const uint32_t at = tmem + (static_cast<uint32_t>(quad * 32) << 16) + (buf * 2u) * kMaxTok + cg * kTok;
+            tmem_ld16(at, v[0]);
+            if (nacc == 2) tmem_ld16(at + kMaxTok, v[1]);
+          }
+          if (ok && valid) {
+            if (ph->epi == EPI_PARTIAL) store_partial<kTok>(cx, ph, slice, n, v[0], t0, mt);
+            else if (ph->epi == EPI_TP) store_tp_partial<kTok>(cx, ph, n, v[0], t0, mt);
+            else apply_epilogue<kTok>(cx, ph, seg, n, v, pre, t0, mt);
+          }
         }
         tc_fence_before();
         mbar_arrive(smem_u32(&cx.misc->accempty[buf]));
         ws.tiles += 1;
         if (!workers_ok(cx, ok)) return false;
-        if (valid) {
-          if (ph->epi == EPI_PARTIAL) store_partial<kTok>(cx, ph, slice, n, v[0], t0, mt);
-          else if (ph->epi == EPI_TP) store_tp_partial<kTok>(cx, ph, n, v[0], t0, mt);
-          else apply_epilogue<kTok>(cx, ph, seg, n, v, pre, t0, mt);
-        }
       }
-      trace_event(cx, wtid, EV_PHASE_DONE);
     }
+    trace_event(cx, wtid, EV_PHASE_DONE);
   }
   if (ph->epi == EPI_TP) __threadfence_system();  // this thread's peer stores are performed before it arrives at the grid barrier
   prefetch_phase(cx, gp + 1, wtid);
   return true;
 }
 
-// One 8-element vector of the residual stream after the pending update (see stage_norm_block).
+// Tell the activation producer that phase gp's operand is complete (called after the grid barrier
+// that closes whatever wrote it; for the first phase of a stand-alone projection, at once).
+__device__ __forceinline__ void signal_operand(const Ctx& cx, int gp, int wtid) {
+  if (wtid == 0) *reinterpret_cast<volatile int*>(&cx.tc->b_ready) = gp + 1;
+}
+
+// One 8-element vector of the residual stream after the pending update (see norm_phase).
 __device__ __forceinline__ uint4 residual_vec(const Ctx& cx, const GemmPhase* ph, int token, int v) {
   const KParams& p = *cx.p;
   const uint4 xu = __ldcg(reinterpret_cast<const uint4*>(activation_row(p, ph, token)) + v);
@@ -881,6 +711,88 @@ __device__ __forceinline__ uint4 residual_vec(const Ctx& cx, const GemmPhase* ph
   return pack8(f);
 }
 
+// RMSNorm as a phase of its own, ahead of the projections that take normalised rows: one CTA of the
+// grid per token row, every worker thread a few 8-element vectors of it, all of a thread's loads in
+// flight together.  The row is the residual stream (or, in layer 0, the embedding row of the token
+// id) plus, on the split-K table, the pending update x = residual + bf16(sum of the previous
+// projection's fp32 K-slice partials, in slice order), which is written back as the new residual
+// stream.  The normalised row, w * bf16(x * rsqrt(mean(x^2) + eps)) with the two roundings of the
+// Hugging Face RMSNorm, goes to `xnorm` in global memory, from where every CTA's activation
+// producer fetches it with TMA.  The caller closes the phase with a grid barrier.
+constexpr int kNormVecs = 4;  // vectors a worker thread holds: rows of up to kNormVecs * kWorkers * 8 = 8192 elements
+
+__device__ __noinline__ void norm_phase(const Ctx& cx, const GemmPhase* ph, int wtid) {
+  const KParams& p = *cx.p;
+  const int warp = wtid >> 5, lane = wtid & 31;
+  const int nvec = ph->k / 8;
+  const int parts = ph->add_parts;
+  const uint4* wrow = reinterpret_cast<const uint4*>(ph->normw);
+  float* red = &cx.misc->sred[0][0];  // kWorkerWarps partial sums (the small-launch kernel's scratch, free here)
+  for (int t = cx.cta; t < p.m; t += cx.grid) {
+    const uint4* row = reinterpret_cast<const uint4*>(activation_row(p, ph, t));
+    uint4 x[kNormVecs];
+    float sum = 0.f;
+#pragma unroll
+    for (int j0 = 0; j0 < kNormVecs; j0 += 2) {
+      // two vectors at a time: their residual and partial loads are all issued before any is used
+      float4 lo[2][kMaxSplit], hi[2][kMaxSplit];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int v = (j0 + j) * kWorkers + wtid;
+        x[j0 + j] = make_uint4(0, 0, 0, 0);
+        if (v < nvec) {
+          x[j0 + j] = __ldcg(row + v);
+#pragma unroll
+          for (int s8 = 0; s8 < kMaxSplit; ++s8) {
+            if (s8 < parts) {
+              const float4* part = reinterpret_cast<const float4*>(ph->partial + (static_cast<size_t>(s8) * p.m + t) * ph->k) + v * 2;
+              lo[j][s8] = __ldcg(part);
+              hi[j][s8] = __ldcg(part + 1);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int v = (j0 + j) * kWorkers + wtid;
+        if (v >= nvec) continue;
+        float f[8];
+        unpack8(x[j0 + j], f);
+        if (parts > 0) {
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int s8 = 0; s8 < kMaxSplit; ++s8) {
+            if (s8 < parts) {
+              acc[0] += lo[j][s8].x; acc[1] += lo[j][s8].y; acc[2] += lo[j][s8].z; acc[3] += lo[j][s8].w;
+              acc[4] += hi[j][s8].x; acc[5] += hi[j][s8].y; acc[6] += hi[j][s8].z; acc[7] += hi[j][s8].w;
+            }
+          }
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = bf16_round(f[e] + bf16_round(acc[e]));
+          x[j0 + j] = pack8(f);
+        }
+        if (ph->h_out) __stcg(reinterpret_cast<uint4*>(ph->h_out + static_cast<size_t>(t) * ph->k) + v, x[j0 + j]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sum = fmaf(f[e], f[e], sum);
+      }
+    }
+    sum = warp_sum(sum);
+    named_bar_sync(1, kWorkers);  // the partial sums of the previous row have been read
+    if (lane == 0) red[warp] = sum;
+    named_bar_sync(1, kWorkers);
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWorkerWarps; ++w) total += red[w];
+    const float rinv = 1.0f / sqrtf(total / static_cast<float>(ph->k) + p.eps);
+    uint4* out = reinterpret_cast<uint4*>(p.xnorm + static_cast<size_t>(t) * ph->k);
+#pragma unroll
+    for (int j = 0; j < kNormVecs; ++j) {
+      const int v = j * kWorkers + wtid;
+      if (v < nvec) __stcg(out + v, normalise_vec(x[j], __ldg(wrow + v), rinv));
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // workers: attention
 
@@ -896,7 +808,8 @@ struct AttnArgs {
   const bf16* mask;   // additive bf16 [batch, 1, sq, klen] or null
   int sq;             // query tokens per sequence (1 in decode)
   int klen;           // keys per sequence (prefill); decode attends len + 1
-  int len;            // decode: filled positions before this call
+  int len;            // decode: filled positions before this call (the longest sequence's when lengths are per sequence)
+  const int* lens;    // decode with per-sequence valid lengths: filled positions of each sequence; null = `len` for all
   int decode;         // 1: append the new key/value at `len` and attend over [0, len]
   int rope;           // 1: rotate q and the new key while loading (decode)
   int causal;         // prefill without a mask tensor: key j <= query qi
@@ -930,38 +843,73 @@ __device__ __forceinline__ int decode_chunks(int keys, int rows, int grid, int g
 }
 
 // Decode attention (one query token per sequence) as a stream of cache tiles.
-// A unit is one (sequence, kv head, context chunk).  Its K rows and then its V
-// rows travel through three shared-memory stages with cp.async: while the
-// workers take the scores (or the value sums) of one tile, the next two tiles
-// are in flight, so a CTA keeps tens of kilobytes of the cache outstanding for
-// the whole unit instead of one register-load round trip per 128 keys.  The
-// new position's key/value row is not in the cache yet: it is patched into its
-// tile from shared memory.  Arithmetic and rounding points are those described
-// above attention_phase for decode; the exchange of the chunk statistics and
-// the hand-over of the chunk partials are the same protocol as there.
-constexpr int kDecStages = 3;                // more, smaller stages measured slower (6 x 8 KB: +30 %)
-constexpr int kDecScratchBytes = 10 * 1024;  // q [8][128] fp32, value partial sums [1024] fp32, new key/value, statistics
-constexpr int kDecTileBytes = 16 * 1024;     // upper bound of one stage
-static_assert(kScoreBytes + kDecScratchBytes + kDecStages * 256 <= kBBytes, "no room for one cache row per stage");
+// A unit is one (sequence, group of adjacent KV heads, context chunk).  The cache is
+// [batch, capacity, kv_heads, head_dim]: one KV head's rows are 128-256 byte pieces a whole cache
+// row apart, which DRAM serves at a fraction of its rate, so a unit takes as many adjacent KV heads
+// as its query heads allow (up to eight query heads per unit): every cached position then
+// contributes one contiguous run of up to 1 KB.  The K rows and then the V rows of the unit travel
+// through three shared-memory stages with cp.async (each head's rows in a sub-tile of its own, so
+// the inner loops see the same [key][128 or 256 B] tile as for a single head): while the workers
+// take the scores (or the value sums) of one tile, the next two tiles are in flight.  The new
+// position's key/value rows are not in the cache yet: they are patched into their tile from shared
+// memory.  Arithmetic and rounding points are those described above attention_phase for decode;
+// the exchange of the chunk statistics and the hand-over of the chunk partials are the same
+// protocol as there.
+// The stages live in the weight ring, which is idle during attention (the weight producer waits at the
+// projection that follows, GemmPhase::gate): three stages of 32 KB keep two tiles, 64 KB per SM, in
+// flight.
+constexpr int kDecStages = 3;
+constexpr int kDecScratchBytes = 11 * 1024;  // q [8][128] fp32, value partial sums [1024] fp32, new keys/values [2][512] bf16, statistics
+constexpr int kDecTileBytes = 32 * 1024;     // one stage
+static_assert(kScoreBytes + kDecScratchBytes <= kBBytes, "scores and scratch exceed their region");
+static_assert(kDecStages * kDecTileBytes <= kRingBytes, "cache stages exceed the weight ring");
 
-// Copy `count` rows of head_dim bf16 (row stride ld elements) into a stage, except row `skip`.
-// Piece p of row r lands at piece p ^ (r & 7), so that a column of pieces spreads over all banks.
-__device__ __noinline__ void fetch_cache_tile(uint32_t dst, const bf16* src, int ld, int count, int skip, int hd, int wtid) {
-  // A thread keeps its 16-byte piece and walks down the rows in steps of a multiple of eight, so that the
-  // swizzled column is fixed and both addresses advance by constants.
-  const int shift = (hd == 64) ? 3 : 4;  // 16-byte pieces per row: 8 or 16
-  const int piece = wtid & ((1 << shift) - 1);
-  const int step = kWorkers >> shift;    // 16 or 8 rows
-  int key = wtid >> shift;
-  uint32_t to = dst + key * hd * 2 + ((piece ^ (key & 7)) << 4);
-  const uint4* from = reinterpret_cast<const uint4*>(src + static_cast<long long>(key) * ld) + piece;
-  const uint32_t to_step = step * hd * 2;
-  const long long from_step = static_cast<long long>(step) * ld / 8;  // in 16-byte units: ld is a multiple of 8
+// KV heads one decode-attention unit covers: the largest divisor of kv_heads that keeps the unit at
+// eight query heads and 1 KB of cache row (512 elements) or fewer.
+__host__ __device__ inline int decode_heads_per_unit(int kv_heads, int gs, int head_dim) {
+  int hpu = 8 / gs;
+  if (hpu > 512 / head_dim) hpu = 512 / head_dim;
+  if (hpu < 1) hpu = 1;
+  while (kv_heads % hpu) --hpu;
+  return hpu;
+}
+
+// Copy `count` cached positions of `hpu` adjacent heads (head_dim bf16 each, contiguous in a cache row;
+// rows `ld` elements apart) into a stage, except position `skip`.  Head h's rows form a sub-tile of
+// `tile_keys` rows at dst + h * tile_keys * row_bytes; piece p of row r lands at piece p ^ (r & 7) of
+// its 128-byte group, so that a column of pieces spreads over all banks.
+__device__ __noinline__ void fetch_cache_tile(uint32_t dst, const bf16* src, int ld, int count, int skip, int hd, int hpu,
+                                              int tile_keys, int wtid) {
+  const int shift = (hd == 64) ? 3 : 4;          // 16-byte pieces per head row: 8 or 16
+  const int per_key = hpu << shift;              // pieces per cached position: a power of two times hpu, at most 64
+  const uint32_t row_bytes = static_cast<uint32_t>(hd) * 2u;
+  // A thread keeps its (head, piece) column and walks down the positions in steps of kWorkers / per_key,
+  // so that both addresses advance by constants (per_key divides kWorkers for every supported shape but
+  // hpu in {3, 5, 6, 7}, which take the general loop).
+  if (kWorkers % per_key == 0) {
+    const int rest = wtid % per_key, step = kWorkers / per_key;
+    const int head = rest >> shift, piece = rest & ((1 << shift) - 1);
+    int key = wtid / per_key;
+    const uint4* from = reinterpret_cast<const uint4*>(src + static_cast<long long>(key) * ld) + rest;
+    const long long from_step = static_cast<long long>(step) * ld / 8;  // in 16-byte units: ld is a multiple of 8
+    uint32_t to = dst + (static_cast<uint32_t>(head) * tile_keys + key) * row_bytes;
+    const uint32_t to_step = step * row_bytes;
 #pragma unroll 4
-  for (; key < count; key += step) {
-    if (key != skip) cp_async16(to, from);
-    to += to_step;
-    from += from_step;
+    for (; key < count; key += step) {
+      if (key != skip) cp_async16(to + ((piece ^ (key & 7)) << 4), from);
+      to += to_step;
+      from += from_step;
+    }
+    return;
+  }
+  const int total = count * per_key;
+#pragma unroll 2
+  for (int it = wtid; it < total; it += kWorkers) {
+    const int key = it / per_key, rest = it - key * per_key;
+    const int head = rest >> shift, piece = rest & ((1 << shift) - 1);
+    if (key != skip)
+      cp_async16(dst + (static_cast<uint32_t>(head) * tile_keys + key) * row_bytes + ((piece ^ (key & 7)) << 4),
+                 reinterpret_cast<const uint4*>(src + static_cast<long long>(key) * ld) + rest);
   }
 }
 
@@ -969,31 +917,34 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, 
   const KParams& p = *cx.p;
   const int hd = p.head_dim, half = hd / 2;
   const int gs = p.q_heads / p.kv_heads;
-  const int rows = p.batch * p.kv_heads;
+  const int hpu = decode_heads_per_unit(p.kv_heads, gs, hd);  // KV heads per unit
+  const int G = gs * hpu;                                  // query heads per unit (<= 8)
+  const int groups = p.kv_heads / hpu;
+  const int rows = p.batch * groups;
   const int n_max = A.len + 1;
   const int warp = wtid >> 5, lane = wtid & 31;
-  const int lpk = hd / 8;  // 16-byte pieces per cache row
-  const int nch = decode_chunks(n_max, rows, cx.grid, gs);
+  const int lpk = hd / 8;  // 16-byte pieces per head row
+  const int nch = decode_chunks(n_max, rows, cx.grid, G);
   const int chunk = (n_max + nch - 1) / nch;
   const int units = rows * nch;
   const int row_bytes = hd * 2;
-  const int score_bytes = (gs * chunk * 4 + 15) & ~15;  // <= kScoreBytes by the choice of nch
-  const int tile_keys = min(kDecTileBytes, (kBBytes - kDecScratchBytes - score_bytes) / kDecStages) / row_bytes;
-  const int stage_bytes = tile_keys * row_bytes;
+  const int tile_keys = kDecTileBytes / (row_bytes * hpu);
+  const int sub_bytes = tile_keys * row_bytes;     // one head's sub-tile
+  const int stage_bytes = sub_bytes * hpu;
 
-  float* sc = reinterpret_cast<float*>(cx.smem_b);                                      // [gs][chunk]
-  uint8_t* tiles = cx.smem_b + score_bytes;                                             // [stages][tile_keys][hd] bf16
-  float* qs = reinterpret_cast<float*>(cx.smem_b + kBBytes - kDecScratchBytes);         // [gs][hd]
-  float* red = qs + 8 * 128;                                                            // [4][8] x 2, then [parts][gs*hd]
-  bf16* kn = reinterpret_cast<bf16*>(red + 1024);                                       // [hd]
-  bf16* vn = kn + 128;                                                                  // [hd]
-  float* stat = reinterpret_cast<float*>(vn + 128);                                     // [16]: max[8], sum[8]
+  float* sc = reinterpret_cast<float*>(cx.smem_b);                                      // [G][chunk]
+  uint8_t* tiles = cx.smem_a;                                                           // [stages][hpu][tile_keys][hd] bf16, in the weight ring
+  float* qs = reinterpret_cast<float*>(cx.smem_b + kBBytes - kDecScratchBytes);         // [G][hd]
+  float* red = qs + 8 * 128;                                                            // [worker warps][8] x 2, then [parts][G*hd]
+  bf16* kn = reinterpret_cast<bf16*>(red + 1024);                                       // [hpu][hd]
+  bf16* vn = kn + 512;                                                                  // [hpu][hd]
+  float* stat = reinterpret_cast<float*>(vn + 512);                                     // [16]: max[8], sum[8]
   const uint32_t tiles_addr = smem_u32(tiles);
 
-  // value accumulation: an item is (part of the keys, head of the group, 16-byte piece of the output row);
+  // value accumulation: an item is (part of the keys, query head of the unit, 16-byte piece of the output row);
   // part q takes keys q, q + parts, ... of every tile; the fp32 sums of an item stay in `red` between tiles
-  const int cols = gs * hd;
-  const int pieces = gs * lpk;
+  const int cols = G * hd;
+  const int pieces = G * lpk;
   int parts = kWorkers / pieces;
   if (parts * cols > 1024) parts = 1024 / cols;
   if (parts < 1) parts = 1;
@@ -1003,15 +954,16 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, 
 #pragma unroll 1
   for (int u = cx.cta; u < units; u += cx.grid) {
     const int rowg = u / nch, ch = u - rowg * nch;
-    const int b = rowg / p.kv_heads, kvh = rowg - b * p.kv_heads;
+    const int b = rowg / groups, kvh0 = (rowg - b * groups) * hpu;  // first KV head of the unit
+    const int filled = A.lens ? A.lens[b] : A.len;  // this sequence's cached positions; chunks past its end are empty
     const int j0 = ch * chunk;
-    const int j1 = min(n_max, j0 + chunk);
+    const int j1 = min(filled + 1, j0 + chunk);
     const int cl = max(0, j1 - j0);
-    const int newpos = A.len;
-    const bool owner = (A.len >= j0 && A.len < j1);
+    const int newpos = filled;
+    const bool owner = (filled >= j0 && filled < j1);
     const int nt = (cl + tile_keys - 1) / tile_keys;
-    const bf16* kbase = A.k + b * A.kv_bstride + kvh * hd;
-    const bf16* vbase = A.v + b * A.kv_bstride + kvh * hd;
+    const bf16* kbase = A.k + b * A.kv_bstride + kvh0 * hd;
+    const bf16* vbase = A.v + b * A.kv_bstride + kvh0 * hd;
     named_bar_sync(1, kWorkers);  // previous unit is done with the scratch and the stages
 
     // Element s of the stream is K tile s (s < nt) or V tile s - nt; it uses stage s % kDecStages.
@@ -1022,14 +974,14 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, 
         const int t0 = j0 + t * tile_keys, t1 = min(j1, t0 + tile_keys);
         fetch_cache_tile(tiles_addr + (s % kDecStages) * stage_bytes,
                          ((s < nt) ? kbase : vbase) + static_cast<long long>(t0) * A.kv_ld, A.kv_ld, t1 - t0, newpos - t0,
-                         hd, wtid);
+                         hd, hpu, tile_keys, wtid);
       }
       cp_async_commit();
     };
 #pragma unroll
     for (int s = 0; s < kDecStages - 1; ++s) issue(s);
 
-    // --- q of every head of the group and the new key (rotated if asked), and the new value
+    // --- q of every query head of the unit and the new keys (rotated if asked), and the new values
     {
       long long pos = 0;
       if (A.rope) {
@@ -1037,10 +989,10 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, 
         if (pos < 0 || pos >= p.max_positions) pos = 0;  // reported by the prologue
       }
 #pragma unroll 1
-      for (int idx = wtid; idx < (gs + 1) * half; idx += kWorkers) {
-        const int g = idx / half, i = idx - g * half;
-        const bf16* src = (g < gs) ? A.q + b * A.q_bstride + (kvh * gs + g) * hd
-                                   : A.knew + static_cast<long long>(b) * A.new_ld + kvh * hd;
+      for (int idx = wtid; idx < (G + hpu) * half; idx += kWorkers) {
+        const int g = idx / half, i = idx - g * half;  // g < G: query head g of the unit; else new key of KV head g - G
+        const bf16* src = (g < G) ? A.q + b * A.q_bstride + (kvh0 * gs + g) * hd
+                                  : A.knew + static_cast<long long>(b) * A.new_ld + (kvh0 + g - G) * hd;
         float first = ldcg_bf16(src + i);
         float second = ldcg_bf16(src + i + half);
         if (A.rope) {
@@ -1048,48 +1000,53 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, 
           const float sn = ldg_bf16(p.sin_t + pos * hd + i);
           rope_pair(first, second, c, sn, p.rope_style, first, second);
         }
-        if (g < gs) {
+        if (g < G) {
           qs[g * hd + i] = first;
           qs[g * hd + i + half] = second;
         } else {
-          kn[i] = __float2bfloat16_rn(first);
-          kn[i + half] = __float2bfloat16_rn(second);
+          kn[(g - G) * hd + i] = __float2bfloat16_rn(first);
+          kn[(g - G) * hd + i + half] = __float2bfloat16_rn(second);
         }
       }
 #pragma unroll 1
-      for (int i = wtid; i < hd; i += kWorkers)
-        vn[i] = __float2bfloat16_rn(ldcg_bf16(A.vnew + static_cast<long long>(b) * A.new_ld + kvh * hd + i));
+      for (int i = wtid; i < hpu * hd; i += kWorkers)
+        vn[i] = __float2bfloat16_rn(ldcg_bf16(A.vnew + static_cast<long long>(b) * A.new_ld + kvh0 * hd + i));
     }
     named_bar_sync(1, kWorkers);
-    if (owner) {  // in-kernel KV append
-      bf16* kd = A.k + b * A.kv_bstride + static_cast<long long>(A.len) * A.kv_ld + kvh * hd;
-      bf16* vd = A.v + b * A.kv_bstride + static_cast<long long>(A.len) * A.kv_ld + kvh * hd;
+    if (owner) {  // in-kernel KV append: the unit's heads are adjacent in the cache row
+      bf16* kd = A.k + b * A.kv_bstride + static_cast<long long>(filled) * A.kv_ld + kvh0 * hd;
+      bf16* vd = A.v + b * A.kv_bstride + static_cast<long long>(filled) * A.kv_ld + kvh0 * hd;
 #pragma unroll 1
-      for (int i = wtid; i < hd; i += kWorkers) {
+      for (int i = wtid; i < hpu * hd; i += kWorkers) {
         kd[i] = kn[i];
         vd[i] = vn[i];
       }
     }
+    // The new position's row joins its tile (its row was not fetched): one 16-byte piece per thread.
+    auto patch = [&](uint8_t* tile, const bf16* fresh, int local) {
+      if (wtid < hpu * lpk) {
+        const int head = wtid / lpk, piece = wtid - head * lpk;
+        *reinterpret_cast<uint4*>(tile + head * sub_bytes + local * row_bytes + ((piece ^ (local & 7)) << 4)) =
+            *reinterpret_cast<const uint4*>(fresh + head * hd + piece * 8);
+      }
+    };
 
-    // --- scores: one thread per (head of the group, key), a head_dim-term fp32 chain each
+    // --- scores: one thread per (query head of the unit, key), a head_dim-term fp32 chain each
 #pragma unroll 1
     for (int s = 0; s < nt; ++s) {
       const int t0 = j0 + s * tile_keys, t1 = min(j1, t0 + tile_keys);
       uint8_t* tile = tiles + (s % kDecStages) * stage_bytes;
       cp_async_wait_group<kDecStages - 2>();  // this thread's pieces of tile s have landed
-      if (newpos >= t0 && newpos < t1 && wtid < lpk)
-        *reinterpret_cast<uint4*>(tile + (newpos - t0) * row_bytes + ((wtid ^ ((newpos - t0) & 7)) << 4)) =
-            *reinterpret_cast<const uint4*>(kn + wtid * 8);
+      if (newpos >= t0 && newpos < t1) patch(tile, kn, newpos - t0);
       named_bar_sync(1, kWorkers);  // tile s is complete; every thread is done with tile s - 1
       issue(s + kDecStages - 1);
       const int tk = t1 - t0;
 #pragma unroll 1
-      for (int item = wtid; item < gs * tk; item += kWorkers) {
+      for (int item = wtid; item < G * tk; item += kWorkers) {
         const int g = item / tk, key = item - g * tk;
-        const uint8_t* krow = tile + key * row_bytes;
+        const uint8_t* krow = tile + (g / gs) * sub_bytes + key * row_bytes;
         const float* qv = qs + g * hd;
-        // four partial sums (pieces 0, 4, 8, ... / 1, 5, ... / ...): a lone warp per scheduler hides no latency,
-        // so the chains have to be independent
+        // four partial sums (pieces 0, 4, 8, ... / 1, 5, ... / ...): the chains have to be independent
         float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
         for (int piece0 = 0; piece0 < lpk; piece0 += 4) {
@@ -1114,7 +1071,7 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, 
 
     // --- chunk max, then chunk sum of exp(score - chunk max); the first V tiles are in flight meanwhile
 #pragma unroll 1
-    for (int g = 0; g < gs; ++g) {
+    for (int g = 0; g < G; ++g) {
       float m = -INFINITY;
 #pragma unroll 1
       for (int i = wtid; i < cl; i += kWorkers) m = fmaxf(m, sc[g * chunk + i]);
@@ -1123,17 +1080,24 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, 
     }
     named_bar_sync(1, kWorkers);
 #pragma unroll 1
-    for (int g = 0; g < gs; ++g) {
-      const float m = fmaxf(fmaxf(red[g], red[8 + g]), fmaxf(red[16 + g], red[24 + g]));
+    for (int g = 0; g < G; ++g) {
+      float m = red[g];
+#pragma unroll
+      for (int w = 1; w < kWorkerWarps; ++w) m = fmaxf(m, red[w * 8 + g]);
       float sum = 0.f;
 #pragma unroll 1
       for (int i = wtid; i < cl; i += kWorkers) sum += expf(sc[g * chunk + i] - m);
       sum = warp_sum(sum);
-      if (lane == 0) red[32 + warp * 8 + g] = sum;
+      if (lane == 0) red[kWorkerWarps * 8 + warp * 8 + g] = sum;
       if (wtid == 0) stat[g] = m;
     }
     named_bar_sync(1, kWorkers);
-    if (wtid < gs) stat[8 + wtid] = ((red[32 + wtid] + red[40 + wtid]) + red[48 + wtid]) + red[56 + wtid];
+    if (wtid < G) {
+      float total = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWorkerWarps; ++w) total += red[kWorkerWarps * 8 + w * 8 + wtid];
+      stat[8 + wtid] = total;
+    }
     named_bar_sync(1, kWorkers);
 
     if (nch > 1) {
@@ -1160,7 +1124,7 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, 
         cp_async_wait_all();  // nothing of this CTA stays in flight past the return
         return false;
       }
-      if (wtid < gs) {
+      if (wtid < G) {
         const float* all = p.att_xch + static_cast<size_t>(rowg) * kMaxChunks * kExchangeFloats;
         float m = -INFINITY;
         for (int c = 0; c < nch; ++c) m = fmaxf(m, __ldcg(all + c * kExchangeFloats + wtid));
@@ -1175,7 +1139,7 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, 
 
     // --- probabilities (bf16, against the global max and sum)
 #pragma unroll 1
-    for (int g = 0; g < gs; ++g) {
+    for (int g = 0; g < G; ++g) {
       const float m = stat[g], denom = stat[8 + g];
 #pragma unroll 1
       for (int i = wtid; i < cl; i += kWorkers) sc[g * chunk + i] = bf16_round(expf(sc[g * chunk + i] - m) / denom);
@@ -1187,18 +1151,17 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, 
       const int t0 = j0 + (s - nt) * tile_keys, t1 = min(j1, t0 + tile_keys);
       uint8_t* tile = tiles + (s % kDecStages) * stage_bytes;
       cp_async_wait_group<kDecStages - 2>();
-      if (newpos >= t0 && newpos < t1 && wtid < lpk)  // the new value row joins its tile
-        *reinterpret_cast<uint4*>(tile + (newpos - t0) * row_bytes + ((wtid ^ ((newpos - t0) & 7)) << 4)) =
-            *reinterpret_cast<const uint4*>(vn + wtid * 8);
+      if (newpos >= t0 && newpos < t1) patch(tile, vn, newpos - t0);  // the new value rows join their tile
       named_bar_sync(1, kWorkers);  // the tile is complete and (first tile) so are the probabilities
       issue(s + kDecStages - 1);
       const int tk = t1 - t0;
       if (wtid < items) {  // at most one item per thread: its sums stay in registers across the tiles
         const float* pr = sc + item_g * chunk + (t0 - j0);
+        const uint8_t* vtile = tile + (item_g / gs) * sub_bytes;
 #pragma unroll 4
         for (int kk = item_part; kk < tk; kk += parts) {
           float vf[8];
-          unpack8(*reinterpret_cast<const uint4*>(tile + kk * row_bytes + ((item_piece ^ (kk & 7)) << 4)), vf);
+          unpack8(*reinterpret_cast<const uint4*>(vtile + kk * row_bytes + ((item_piece ^ (kk & 7)) << 4)), vf);
           const float w = pr[kk];
 #pragma unroll
           for (int e = 0; e < 8; ++e) acc[e] = fmaf(w, vf[e], acc[e]);
@@ -1206,7 +1169,7 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, 
       }
     }
     if (wtid < items) {
-      float* mine = red + (item_part * gs + item_g) * hd + item_piece * 8;
+      float* mine = red + (item_part * G + item_g) * hd + item_piece * 8;
       *reinterpret_cast<float4*>(mine) = make_float4(acc[0], acc[1], acc[2], acc[3]);
       *reinterpret_cast<float4*>(mine + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
@@ -1217,7 +1180,7 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, 
 #pragma unroll 1
       for (int part = 1; part < parts; ++part) o += red[part * cols + col];
       const int g = col / hd, d = col - g * hd;
-      const int head = kvh * gs + g;
+      const int head = kvh0 * gs + g;
       if (nch == 1) {
         A.out[b * A.out_bstride + head * A.out_hstride + d] = __float2bfloat16_rn(o);
       } else {
@@ -1226,8 +1189,8 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, 
       }
     }
     if (nch > 1 && A.combine) {
-      // Stand-alone op: there is no consumer phase, so chunk 0's CTA waits for the
-      // partials of its peers (second stamp) and sums them in chunk order.
+      // There is no consumer phase that adds chunk partials: chunk 0's CTA waits for the partials of its
+      // peers (second stamp) and sums them in chunk order.
       float* mine = p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + ch) * kExchangeFloats;
       __threadfence();
       named_bar_sync(1, kWorkers);
@@ -1246,10 +1209,13 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, 
           }
           __threadfence();
         }
-        if (!workers_ok(cx, ok)) return false;
+        if (!workers_ok(cx, ok)) {
+          cp_async_wait_all();
+          return false;
+        }
         for (int idx = wtid; idx < cols; idx += kWorkers) {
           const int g = idx / hd, d = idx - g * hd;
-          const int head = kvh * gs + g;
+          const int head = kvh0 * gs + g;
           const size_t row = static_cast<size_t>(b) * p.q_heads + head;
           float o = 0.f;
           for (int c = 0; c < nch; ++c) o += __ldcg(p.att_part + (row * kMaxChunks + c) * hd + d);
@@ -1258,7 +1224,6 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, 
       }
     }
   }
-  if (!A.combine && cx.cta == 0 && wtid == 0) cx.ctrl->att_nch = nch;  // read after the barrier
   return true;
 }
 
@@ -1290,8 +1255,8 @@ __device__ __noinline__ bool attention_phase(const Ctx& cx, const AttnArgs& A, i
 
   float* sc = reinterpret_cast<float*>(cx.smem_b);                // [gs][chunk]
   float* qs = reinterpret_cast<float*>(cx.smem_b + kScoreBytes);  // [gs][hd]
-  float* red = qs + 8 * 128;                                      // [4][128]
-  bf16* kn = reinterpret_cast<bf16*>(red + 4 * 128);              // [hd]
+  float* red = qs + 8 * 128;                                      // [worker warps][128]
+  bf16* kn = reinterpret_cast<bf16*>(red + kWorkerWarps * 128);   // [hd]
   bf16* vn = kn + 128;                                            // [hd]
   float* stat = reinterpret_cast<float*>(vn + 128);               // [16]: max[8], sum[8]
 
@@ -1398,15 +1363,22 @@ __device__ __noinline__ bool attention_phase(const Ctx& cx, const AttnArgs& A, i
     }
     named_bar_sync(1, kWorkers);
     for (int g = 0; g < gs; ++g) {
-      const float m = fmaxf(fmaxf(red[g], red[8 + g]), fmaxf(red[16 + g], red[24 + g]));
+      float m = red[g];
+#pragma unroll
+      for (int w = 1; w < kWorkerWarps; ++w) m = fmaxf(m, red[w * 8 + g]);
       float s = 0.f;
       for (int i = wtid; i < cl; i += kWorkers) s += expf(sc[g * chunk + i] - m);
       s = warp_sum(s);
-      if (lane == 0) red[32 + warp * 8 + g] = s;
+      if (lane == 0) red[kWorkerWarps * 8 + warp * 8 + g] = s;
       if (wtid == 0) stat[g] = m;
     }
     named_bar_sync(1, kWorkers);
-    if (wtid < gs) stat[8 + wtid] = ((red[32 + wtid] + red[40 + wtid]) + red[48 + wtid]) + red[56 + wtid];
+    if (wtid < gs) {
+      float total = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWorkerWarps; ++w) total += red[kWorkerWarps * 8 + w * 8 + wtid];
+      stat[8 + wtid] = total;
+    }
     named_bar_sync(1, kWorkers);
 
     if (nch > 1) {
@@ -1487,7 +1459,9 @@ __device__ __noinline__ bool attention_phase(const Ctx& cx, const AttnArgs& A, i
       }
       named_bar_sync(1, kWorkers);
       if (wtid < hd) {
-        const float o = ((red[wtid] + red[128 + wtid]) + red[256 + wtid]) + red[384 + wtid];
+        float o = red[wtid];
+#pragma unroll
+        for (int w = 1; w < kWorkerWarps; ++w) o += red[w * 128 + wtid];
         const int head = kvh * gs + g;
         if (nch == 1) {
           A.out[b * A.out_bstride + static_cast<long long>(qi) * A.out_tstride + head * A.out_hstride + wtid] =
@@ -1705,13 +1679,21 @@ __device__ void worker_loop(const Ctx& cx, int wtid) {
   const KParams& p = *cx.p;
   WorkerState ws;
   ws.tiles = 0; ws.passed = 0;
-  ws.be_cnt[0] = ws.be_cnt[1] = 0;
-  ws.outstanding[0] = ws.outstanding[1] = false;
-  auto gemm = [&](int gp) -> bool { return worker_gemm_tc(cx, gp, ws, wtid); };
+  // A projection phase: publish its operand (complete since the last grid barrier), run the epilogues.
+  auto gemm = [&](int gp) -> bool {
+    signal_operand(cx, gp, wtid);
+    return worker_gemm_tc(cx, gp, ws, wtid);
+  };
+  // A projection whose operand is the RMSNorm of the residual stream: normalise the rows first.
+  auto normed_gemm = [&](int gp) -> bool {
+    norm_phase(cx, &cx.misc->phase[gp & 1], wtid);
+    if (!grid_barrier(cx, ws, wtid)) return false;
+    return gemm(gp);
+  };
   const int q_size = p.q_heads * p.head_dim, kv_size = p.kv_heads * p.head_dim;
   AttnArgs A;
   A.knew = nullptr; A.vnew = nullptr; A.new_ld = 0; A.mask = nullptr;
-  A.sq = 1; A.klen = 0; A.len = 0; A.decode = 0; A.rope = 0; A.causal = 0; A.combine = 0;
+  A.sq = 1; A.klen = 0; A.len = 0; A.lens = nullptr; A.decode = 0; A.rope = 0; A.causal = 0; A.combine = 0;
   A.stamp = p.att_epoch + 1; A.scale = p.att_scale;
   if (p.n_gemm > 0) {
     prefetch_phase(cx, 0, wtid);
@@ -1727,7 +1709,7 @@ __device__ void worker_loop(const Ctx& cx, int wtid) {
     A.kv_bstride = static_cast<long long>(p.capacity) * kv_size; A.kv_ld = kv_size;
     A.knew = p.op_k; A.vnew = p.op_v; A.new_ld = kv_size;
     A.out = p.op_out; A.out_bstride = q_size; A.out_tstride = 0; A.out_hstride = p.head_dim;
-    A.len = *p.len[0]; A.decode = 1; A.combine = 1;
+    A.len = *p.len[0]; A.lens = nullptr; A.decode = 1; A.combine = 1;
     if (!attention_phase(cx, A, wtid)) return;
     if (!grid_barrier(cx, ws, wtid)) return;
     if (cx.cta == 0 && wtid == 0) *p.len[0] = A.len + 1;
@@ -1744,7 +1726,8 @@ __device__ void worker_loop(const Ctx& cx, int wtid) {
     attention_phase(cx, A, wtid);
     return;
   }
-  // Layer 0's residual stream starts as the embedding rows (the split-K table writes them from its first phase).
+  // Layer 0's residual stream starts as the embedding rows (the split-K table writes them from its first
+  // normalising phase).  Its first reader is layer 0's o_proj epilogue, two grid barriers on.
   for (int v = cx.cta * kWorkers + wtid; !p.split && v < p.m * (p.hidden / 8); v += cx.grid * kWorkers) {
     const int t = v / (p.hidden / 8), c = v - t * (p.hidden / 8);
     long long id = p.ids[t];
@@ -1754,7 +1737,7 @@ __device__ void worker_loop(const Ctx& cx, int wtid) {
   }
   const bool decode = (p.mode == MODE_DECODE);
   for (int layer = 0; layer < p.layers; ++layer) {
-    if (!gemm(layer * 4 + 0)) return;                       // [RMSNorm] q, k, v (+bias)
+    if (!normed_gemm(layer * 4 + 0)) return;                // RMSNorm | q, k, v (+bias)
     if (!grid_barrier(cx, ws, wtid)) return;
     A.q = p.qkv; A.q_ld = p.qkv_ld;
     A.out = p.attn; A.out_tstride = q_size; A.out_hstride = p.head_dim;
@@ -1765,7 +1748,16 @@ __device__ void worker_loop(const Ctx& cx, int wtid) {
       A.kv_bstride = static_cast<long long>(p.capacity) * kv_size; A.kv_ld = kv_size;
       A.knew = p.qkv + q_size; A.vnew = A.knew + kv_size; A.new_ld = p.qkv_ld;
       A.out_bstride = q_size;
-      A.len = *p.len[layer]; A.decode = 1; A.rope = 1;
+      if (p.ragged) {  // one valid length per sequence: the context split follows the longest
+        A.lens = p.len[layer];
+        int longest = 0;
+        for (int b = 0; b < p.batch; ++b) longest = max(longest, A.lens[b]);
+        A.len = longest;
+      } else {
+        A.len = *p.len[layer];
+      }
+      A.decode = 1; A.rope = 1;
+      A.combine = 1;  // the o projection fetches a finished bf16 matrix: the first chunk's CTA sums the chunk partials
     } else {
       rope_phase(cx, wtid);
       if (!grid_barrier(cx, ws, wtid)) return;
@@ -1774,22 +1766,29 @@ __device__ void worker_loop(const Ctx& cx, int wtid) {
       A.kv_bstride = static_cast<long long>(p.seq) * p.qkv_ld; A.kv_ld = p.qkv_ld;
       A.out_bstride = static_cast<long long>(p.seq) * q_size;
       A.mask = p.mask; A.sq = p.seq; A.klen = p.seq; A.causal = (p.mask == nullptr);
-      if (cx.cta == 0 && wtid == 0) cx.ctrl->att_nch = 1;
     }
-    if (!attention_phase(cx, A, wtid)) return;              // [RoPE] attention (+ KV append)
+    if (!attention_phase(cx, A, wtid)) return;              // [RoPE] attention (+ KV append); decode streams cache tiles through the ring
+    named_bar_sync(1, kWorkers);                            // every worker is done with the ring
+    if (wtid == 0) *reinterpret_cast<volatile int*>(&cx.tc->a_ready) = layer * 4 + 2;  // o_proj's weights may come
     trace_event(cx, wtid, EV_ATTENTION_DONE);
     if (!grid_barrier(cx, ws, wtid)) return;
-    if (decode && cx.cta == 0 && wtid == 0) *p.len[layer] = A.len + 1;  // publish after the interval closes
+    if (decode && cx.cta == 0) {  // publish after the interval closes
+      if (p.ragged) {
+        for (int b = wtid; b < p.batch; b += kWorkers) p.len[layer][b] = A.lens[b] + 1;
+      } else if (wtid == 0) {
+        *p.len[layer] = A.len + 1;
+      }
+    }
     if (!gemm(layer * 4 + 1)) return;                       // o_proj + residual (tensor parallel: partial sums to every rank)
     if (!grid_barrier(cx, ws, wtid)) return;
     if (p.tp_size > 1 && !tp_allreduce(cx, ws, wtid, 2 * layer)) return;
-    if (!gemm(layer * 4 + 2)) return;                       // [RMSNorm] gate, up -> SiLU*up
+    if (!normed_gemm(layer * 4 + 2)) return;                // RMSNorm | gate, up -> SiLU*up
     if (!grid_barrier(cx, ws, wtid)) return;
     if (!gemm(layer * 4 + 3)) return;                       // down + residual
     if (!grid_barrier(cx, ws, wtid)) return;
     if (p.tp_size > 1 && !tp_allreduce(cx, ws, wtid, 2 * layer + 1)) return;
   }
-  if (!gemm(p.layers * 4)) return;                          // [final RMSNorm] lm_head
+  if (!normed_gemm(p.layers * 4)) return;                   // final RMSNorm | lm_head
   if (p.sample) {
     if (!grid_barrier(cx, ws, wtid)) return;                // every CTA's logits are out and nobody reads ids/positions any more
     greedy_sample<1, kWorkers>(cx, wtid, reinterpret_cast<float*>(cx.smem_b));
@@ -1808,35 +1807,35 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
   cx.smem_a = smem;
   cx.smem_b = smem + kRingBytes;
   cx.misc = reinterpret_cast<SmemMisc*>(cx.smem_b + kBBytes);
+  cx.tc = reinterpret_cast<SmemMiscTc*>(cx.smem_b + kBBytes + kMiscBytes);
   cx.deadline = clock64() + p.timeout_cycles;
   cx.cta = blockIdx.x;
   cx.grid = gridDim.x;
   const int tid = threadIdx.x, warp = tid >> 5;
-  const bool tc = p.n_gemm > 0;   // tensor-core roles (TMEM, MMA issuer)
-  const bool ring = tc;  // weight producer
+  const bool tc = p.n_gemm > 0;   // tensor-core roles (TMEM, MMA issuer, the two producers)
 
+  if (tid < kChunkBars) {  // one barrier quadruple per thread
+    mbar_init(smem_u32(&cx.misc->full[tid]), 1);
+    mbar_init(smem_u32(&cx.misc->empty[tid]), 1);   // one MMA commit
+    mbar_init(smem_u32(&cx.tc->bfull[tid]), 1);
+    mbar_init(smem_u32(&cx.tc->bempty[tid]), 1);
+    mbar_fence_init();
+  }
   if (tid == 0) {
-    for (int s = 0; s < kChunkBars; ++s) {
-      mbar_init(smem_u32(&cx.misc->full[s]), 1);
-      mbar_init(smem_u32(&cx.misc->empty[s]), tc ? 1 : kWorkerWarps);  // MMA commit, or one arrival per worker warp
-    }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&cx.misc->accfull[b]), 1);
       mbar_init(smem_u32(&cx.misc->accempty[b]), kWorkers);
-      mbar_init(smem_u32(&cx.misc->bfull[b]), kWorkers);
-      mbar_init(smem_u32(&cx.misc->bempty[b]), 1);
     }
     cx.misc->wabort = 0;
     cx.misc->bad = 0;
     cx.misc->flag = 0;
     cx.misc->trace_n = 0;
+    cx.tc->b_ready = 0;
+    cx.tc->a_ready = 0;
     mbar_fence_init();
   }
-  // Rows of the ring and of the activation slots that a launch does not fill are
-  // still multiplied: make sure they never start out as NaN patterns.
-  for (int i = tid; i < (kRingBytes + kBBytes) / 16; i += kThreads)
-    reinterpret_cast<uint4*>(cx.smem_a)[i] = make_uint4(0, 0, 0, 0);
-  fence_proxy_async_smem();
+  // The rows of a 128-row MMA tile that a weight copy does not fill hold whatever the ring held before;
+  // they only ever reach accumulator rows that no epilogue reads, so the ring needs no clearing.
   __syncthreads();
   if (warp == 1 && tc) {
     tmem_alloc(smem_u32(&cx.misc->tmem_base), kTmemCols);
@@ -1852,15 +1851,12 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
         const long long id = p.ids[t], pos = p.pos[t];
         if (id < 0 || id >= p.embed_rows || pos < 0 || pos >= p.max_positions) bad = MK_STATUS_BAD_INDEX;
       }
-      for (int t = tid; t < p.check_m; t += kThreads) {
-        const long long id = p.check_ids[t], pos = p.check_pos[t];
-        if (id < 0 || id >= p.embed_rows || pos < 0 || pos >= p.max_positions) bad = MK_STATUS_BAD_INDEX;
-      }
     }
     if (p.mode != MODE_PREFILL) {
       const int nl = (p.mode == MODE_KVATT) ? 1 : p.layers;
-      for (int l = tid; l < nl; l += kThreads) {
-        const int len = *p.len[l];
+      const int per_layer = p.ragged ? p.batch : 1;
+      for (int i = tid; i < nl * per_layer; i += kThreads) {
+        const int len = p.len[i / per_layer][i % per_layer];
         if (len < 0 || len + 1 > p.capacity) bad = MK_STATUS_KV_OVERFLOW;
       }
     }
@@ -1872,11 +1868,13 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
   if (bad) {
     refuse_outputs(cx, bad, tid, kThreads);
   } else if (warp == 0) {
-    if (ring && tid == 0) producer_loop(cx);
+    if (tc && tid == 0) producer_loop(cx);
   } else if (warp == 1) {
     if (tc && tid == 32) mma_loop(cx);
-  } else {
+  } else if (warp <= 1 + kWorkerWarps) {
     worker_loop(cx, tid - 64);
+  } else {
+    if (tc && tid == 64 + kWorkers) activation_producer_loop(cx);
   }
   __syncwarp();
   tc_fence_before();

@@ -10,23 +10,25 @@ namespace mk {
 
 typedef __nv_bfloat16 bf16;
 
-constexpr int kThreads = 192;            // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: workers
-constexpr int kWorkers = 128;
-constexpr int kWorkerWarps = 4;
+constexpr int kWorkerWarps = 8;
+constexpr int kWorkers = kWorkerWarps * 32;
+constexpr int kThreads = 64 + kWorkers + 32;  // warp 0: weight producer, warp 1: MMA issuer, then the workers, last warp: activation producer
 constexpr int kTileRows = 128;           // UMMA M; a tile fills only its first `rows` rows
 constexpr int kChunkK = 64;              // K elements per weight chunk (128 B of bf16 = one swizzle row)
 constexpr int kGranule = 1024;           // weight ring allocation unit (8 rows of 128 B)
 constexpr int kRingGranules = 120;       // keeps the CTA under 196 KiB of shared memory so ~60 KiB stay L1 (stack, spills)
 constexpr int kRingBytes = kRingGranules * kGranule;
 constexpr int kChunkBars = 128;          // full/empty barrier pairs, indexed by chunk sequence number
-constexpr int kTok = MK_TOKEN_TILE;      // tokens per MMA (UMMA N)
+constexpr int kTok = MK_TOKEN_TILE;      // token columns an epilogue step reads from TMEM
+constexpr int kMaxTok = 64;              // largest token tile (UMMA N is 16, 32 or 64)
 constexpr int kBSlots = 32;              // activation K-chunks resident per CTA (two halves of 16)
 constexpr int kBHalf = kBSlots / 2;
 constexpr int kBSlotBytes = kTok * 128;  // 2 KiB
 constexpr int kBBytes = kBSlots * kBSlotBytes;
-constexpr int kTmemCols = 64;            // 2 buffers x 2 accumulators x 16 columns
+constexpr int kTmemCols = 256;           // 2 buffers x 2 accumulators x 64 columns
 constexpr int kMiscBytes = 4096;
-constexpr int kSmemBytes = 1024 /*alignment slack*/ + kRingBytes + kBBytes + kMiscBytes;
+constexpr int kMiscTcBytes = 3072;       // tensor engine only: barriers of the activation ring
+constexpr int kSmemBytes = 1024 /*alignment slack*/ + kRingBytes + kBBytes + kMiscBytes + kMiscTcBytes;
 constexpr int kMaxChunks = 16;           // split-context chunks per (sequence, kv head)
 constexpr int kScoreBytes = 40960;       // fp32 scores of one attention unit (inside the B region)
 constexpr int kExchangeFloats = 32;      // per (row group, chunk), 128 bytes: max[8], sum[8], stamps (mk::megakernel),
@@ -58,7 +60,8 @@ constexpr int kTpFlagBytes = 256;        // head of a rank's exchange buffer: on
 // With ksplit > 1 (EPI_PARTIAL) each unit stores fp32 partial sums and the next
 // phase adds them, in slice order, while it builds its activation operand.
 struct GemmPhase {
-  const CUtensorMap* tmap[3];  // device copies of the TMA descriptors (box = 64 x rows)
+  const CUtensorMap* tmap[3];  // device copies of the weights' TMA descriptors (tensor engine: box = 64 x rows x kb chunks)
+  const CUtensorMap* bmap[3];  // tensor engine: descriptors of the token operand for token tiles of 16, 32, 64 (box = 64 x tile)
   const bf16* w[3];            // raw weight pointers [N, K]
   const bf16* bias[3];
   int n[3];                    // rows of each matrix
@@ -67,9 +70,12 @@ struct GemmPhase {
   int nseg, nacc;
   int k, kc;                   // reduction length, in elements and in 64-element chunks
   int rows;                    // weight rows per tile
-  int kb;                      // K chunks one weight copy brings (1: 64 x rows swizzled boxes for the tensor core;
-                               // > 1: unswizzled boxes of kb * 64 elements x rows for the small-launch kernel)
-  int gran;                    // ring granules one copy occupies = ceil(rows * kb * 128 / 1024)
+  int kb;                      // K chunks one weight copy brings (tensor engine: kb swizzled chunks of rows x 128 B per matrix;
+                               // small-launch kernel: unswizzled boxes of kb * 64 elements x rows)
+  int gran;                    // ring granules one entry occupies (tensor engine: nacc * kb * rows / 8)
+  int gate;                    // tensor engine: 1 = this phase follows decode attention, whose cache tiles stream through the weight
+                               // ring: its weights may be fetched only once the workers have released the ring (a_ready)
+  int map3d;                   // tensor engine: 1 = tmap is three-dimensional and one copy brings kb chunks; 0 = one 2-D copy per chunk
   int ntiles;                  // row tiles
   int ksplit, kslice;          // K slices and chunks per slice (kc == ksplit * kslice)
   int nunits;                  // ntiles * ksplit
@@ -122,6 +128,7 @@ struct KParams {
   int stream_once;    // 1: weights are read once per launch (L2 evict-first)
   int split;          // 1: this launch runs the split-K phase table (residual updates applied by the consumer)
   int rowmode;        // 1: one-token row table: stamped hand-offs everywhere, one grid barrier at the end of the launch
+  int ragged;         // 1: len[l] points to one valid length per sequence (int32 [batch]) instead of one shared by the batch
   int sample;         // 1: after the logits, pick each sequence's greedy token on the device, store it in tokens_out and as the
                       //    next id, and advance the position: the next launch needs no host round trip
   long long* tokens_out;      // [m] with `sample`
@@ -131,6 +138,7 @@ struct KParams {
   long long timeout_cycles;
   const GemmPhase* phases;
   bf16 *hidden_buf, *qkv, *attn, *act;
+  bf16* xnorm;        // [m][hidden]: the normalised rows a norm phase leaves for the projections that follow
   unsigned long long* qkv_ll;  // [kSplitTokens][qkv width / 2]: stamped q/k/v outputs of the small-launch kernel
   unsigned long long* att_ll;  // [kSplitTokens * q_heads][kMaxChunks][head_dim]: stamped attention partials {stamp, fp32}
   unsigned long long* attn_ll; // [kSplitTokens][q_heads * head_dim / 2]: the combined attention output as stamped bf16 pairs
@@ -146,9 +154,6 @@ struct KParams {
   int tp_rank, tp_size;
   uint32_t tp_epoch;  // all-reduces this group has finished before this launch (stamps count up from it)
   uint8_t* tp_peer[kMaxTp];
-  const long long* check_ids;  // when a step is cut into two launches: the ids and positions of the whole step,
-  const long long* check_pos;  // validated by both so that they run or refuse together
-  int check_m;
   const bf16* mask;
   const bf16 *embed, *cos_t, *sin_t;
   bf16* logits;
@@ -156,9 +161,15 @@ struct KParams {
   const bf16 *op_q, *op_k, *op_v;
   bf16* op_out;
   int op_qlen, op_klen;
+  // stand-alone projection (MODE_LINEAR): its phase and its two descriptors travel in the parameter block,
+  // so the call needs no upload and no synchronisation
+  GemmPhase linear_phase;
+  CUtensorMap linear_wmap, linear_xmap;
   void* kc[MK_MAX_LAYERS];
   void* vc[MK_MAX_LAYERS];
   int* len[MK_MAX_LAYERS];
 };
+
+static_assert(sizeof(KParams) <= 4096, "the parameter block must stay within the classic 4 KB kernel-parameter limit");
 
 }  // namespace mk

@@ -40,6 +40,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+// Generic-proxy accesses (plain loads and stores) before async-proxy accesses (TMA) of the same global or shared data.
+__device__ __forceinline__ void fence_proxy_async_all() {
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -66,6 +70,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int 
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
       " [%0], [%1, {%2, %3}], [%4], %5;"
       ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar), "l"(policy)
+      : "memory");
+}
+// 3-D tiled load: z is the outermost coordinate.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, int x, int y, int z, uint32_t bar,
+                                            uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%2, %3, %4}], [%5], %6;"
+      ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(bar), "l"(policy)
       : "memory");
 }
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {

@@ -244,7 +244,25 @@ class DecoderKernel:
                 capacity, logits.data_ptr(), self._stream()), stage="input-binding")
         return logits
 
-    def _checked_state(self, batch, key_caches, value_caches, valid_lengths):
+    def decode_ragged(self, input_ids, position_ids, key_caches, value_caches, valid_lengths) -> torch.Tensor:
+        """``decode`` for sequences of different lengths: every ``valid_lengths[layer]`` is int32
+        ``[batch]`` (one filled-position count per sequence), ``position_ids[b]`` that sequence's
+        position.  Beyond the reference's contract of one length per batch
+        (src/megabake/lowering.py:160-190)."""
+        config = self.config
+        batch = input_ids.shape[0]
+        _require(input_ids, "input_ids", dtype=torch.int64, device=self.device, shape=(batch, 1))
+        _require(position_ids, "position_ids", dtype=torch.int64, device=self.device, shape=(batch, 1))
+        keys, values, lengths, capacity = self._checked_state(batch, key_caches, value_caches, valid_lengths, per_sequence=True)
+        self.raise_if_failed()
+        logits = torch.empty((batch, 1, config.vocab), dtype=torch.bfloat16, device=self.device)
+        with self._lock, torch.cuda.device(self.device):
+            self._call("mk_decode_ragged", self.lib.mk_decode_ragged(
+                self._handle, input_ids.data_ptr(), position_ids.data_ptr(), batch, keys, values, lengths,
+                capacity, logits.data_ptr(), self._stream()), stage="input-binding")
+        return logits
+
+    def _checked_state(self, batch, key_caches, value_caches, valid_lengths, per_sequence: bool = False):
         """Pointer arrays of the caller's state; shapes and dtypes are validated whenever any
         state tensor or the batch differs from the last call's."""
         config = self.config
@@ -252,13 +270,14 @@ class DecoderKernel:
             raise ValueError(f"expected {3 * config.layers} state tensors, got "
                              f"{len(key_caches) + len(value_caches) + len(valid_lengths)}")
         capacity = key_caches[0].shape[1]
-        key = (batch,) + tuple(t.data_ptr() for group in (key_caches, value_caches, valid_lengths) for t in group)
+        key = (batch, per_sequence) + tuple(t.data_ptr() for group in (key_caches, value_caches, valid_lengths) for t in group)
         if key != self._state_key:
             cache_shape = (batch, capacity, config.kv_heads, config.head_dim)
             for layer in range(config.layers):
                 _require(key_caches[layer], f"key cache {layer}", dtype=torch.bfloat16, device=self.device, shape=cache_shape)
                 _require(value_caches[layer], f"value cache {layer}", dtype=torch.bfloat16, device=self.device, shape=cache_shape)
-                _require(valid_lengths[layer], f"valid length {layer}", dtype=torch.int32, device=self.device, shape=(1,))
+                _require(valid_lengths[layer], f"valid length {layer}", dtype=torch.int32, device=self.device,
+                         shape=(batch,) if per_sequence else (1,))
             count = config.layers
             self._state_arrays = tuple((ctypes.c_void_p * count)(*[t.data_ptr() for t in group])
                                        for group in (key_caches, value_caches, valid_lengths))
@@ -394,6 +413,12 @@ class DecoderKernel:
         self._trace = torch.zeros((ctas, events_per_cta), dtype=torch.int64, device=self.device)
         self._call("mk_set_trace", self.lib.mk_set_trace(self._handle, self._trace.data_ptr(), events_per_cta))
         return self._trace
+
+    def describe(self) -> str:
+        """What this kernel will launch: CTAs, copy form, tile plan per phase table."""
+        buffer = ctypes.create_string_buffer(4096)
+        self._call("mk_describe", self.lib.mk_describe(self._handle, buffer, len(buffer)))
+        return buffer.value.decode()
 
     def launch_info(self) -> dict:
         ctas, smem, launches = ctypes.c_int32(), ctypes.c_int32(), ctypes.c_int64()

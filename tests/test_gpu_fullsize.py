@@ -85,9 +85,9 @@ def test_smollm_1_7b_batch_16_context_1024():
 
 
 def test_smollm_1_7b_batch_8_context_512():
-    """The per-GPU workload of the data-parallel sweep: 8 sequences from a 512-token prefix, which run
-    as two launches of the small-launch kernel on a snapshot of the shared valid lengths."""
-    assert three_way_decode("c4_batch8_ctx512", CONFIGS["smollm-1.7b"], 8, 1024, 512, steps=3) == 2
+    """The per-GPU workload of the data-parallel sweep: 8 sequences from a 512-token prefix (tensor engine,
+    one launch per step)."""
+    assert three_way_decode("c4_batch8_ctx512", CONFIGS["smollm-1.7b"], 8, 1024, 512, steps=3) == 1
 
 
 def llama3_two_layers() -> DecoderConfig:

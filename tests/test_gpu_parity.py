@@ -108,13 +108,15 @@ def test_decode_tiny_matches_reference(device, name, engine):
 @pytest.mark.parametrize("engine", ["tcgen05", "fma"])
 def test_decode_smollm_135m_64_steps(device, engine):
     ties, run = run_golden_decode("c1", device, engine, deep=True)
-    assert run == 67 and ties <= 8  # positions where the reference's own top two logits tie in bf16
+    # measured on a B200: 5 of 64 greedy tokens differ from the CPU-made golden ones (both engines), each at a
+    # position where the reference's own top two logits tie in bf16 (token_agrees checks that)
+    assert run == 67 and ties <= 5
 
 
 @pytest.mark.parametrize("engine", ["auto", "tcgen05"])
 def test_decode_qwen2_half_b_64_steps(device, engine):
     ties, run = run_golden_decode("c2", device, engine, deep=True)
-    assert run == 67 and ties <= 8
+    assert run == 67 and ties <= 1  # measured on a B200: 1 of 64 (both engines), a bf16 tie of the reference's own logits
 
 
 def run_yardstick_decode(name, device):
@@ -162,7 +164,9 @@ def run_yardstick_decode(name, device):
                     f"{name}: greedy token at position {position + 1} is not one bf16 noise can defend")
     kernel.check()
     record_stat(f"teacher_forced_{name}", generated=generated, same_as_golden=same_as_golden)
-    assert generated > 0 and same_as_golden >= 0.8 * generated, f"{same_as_golden} of {generated} tokens equal the golden ones"
+    # measured on a B200: 26 of 28 (short run) and 14 of 16 (context 1024) equal the CPU-made golden tokens; the
+    # others are defensible (above) and eager PyTorch on the same GPU differs from the golden run as often
+    assert generated > 0 and generated - same_as_golden <= 2, f"{same_as_golden} of {generated} tokens equal the golden ones"
     assert torch.equal(torch.stack(mine_state[2]).cpu(), record["lengths"])
     rows = record.get("cache_rows")
     for layer, (key_cache, value_cache) in record["caches"].items():
@@ -254,7 +258,7 @@ def test_decode_error_no_worse_than_eager_bf16(device):
 @pytest.mark.parametrize("batch", [1, 2, 3, 4, 5, 8, 16, 21])
 def test_decode_batches_match_oracle(device, batch, engine):
     """Batches 1-4 run the small-launch kernel under "auto" (one instantiation per token count),
-    5-8 two launches of it (3+2 .. 4+4 sequences), larger ones the tensor engine."""
+    larger ones the tensor engine (token tiles of 16 and 32)."""
     oracle_decode_compare(tiny_config(q_heads=4, kv_heads=1, hidden=256), device, batch, capacity=24, prefill=0, steps=4,
                           engine=engine)
 
@@ -266,10 +270,9 @@ def test_decode_split_context_matches_oracle(device, engine):
     oracle_decode_compare(config, device, batch=2, capacity=1024, prefill=700, steps=3, engine=engine)
 
 
-@pytest.mark.parametrize("batch,launches", [(4, 1), (5, 2), (8, 2), (9, 1)])
-def test_decode_launches_per_step(device, batch, launches):
-    """One launch per step, except 5-8 sequences under "auto": two launches of the small-launch kernel, the
-    first on a snapshot of the valid lengths so that each length still advances by exactly one."""
+@pytest.mark.parametrize("batch", [4, 5, 8, 9, 33])
+def test_decode_is_one_launch_per_step(device, batch):
+    """Every decode step is exactly one cooperative launch, whatever the batch."""
     config = tiny_config(q_heads=4, kv_heads=1, hidden=256)
     weights = synth_weights(config, seed=3, norm_std=0.1, device=device)
     kernel = make_kernel(config, weights, device, max_tokens=batch, max_positions=16, engine="auto")
@@ -278,7 +281,7 @@ def test_decode_launches_per_step(device, batch, launches):
     before = kernel.launch_info()["launches"]
     kernel.decode(ids, torch.zeros((batch, 1), dtype=torch.int64, device=device), keys, values, lengths)
     kernel.check()
-    assert kernel.launch_info()["launches"] - before == launches
+    assert kernel.launch_info()["launches"] - before == 1
     assert all(int(length.item()) == 1 for length in lengths)
 
 
@@ -504,9 +507,10 @@ def test_event_trace_reports_every_phase(device, engine):
     kernel.check()
     codes, times = decode_trace(buffer)
     barriers = int((codes[0] == 5).sum())
-    # five grid barriers per layer on the tensor engine; the small-launch kernel at one token hands every
-    # phase's outputs to the next as stamped words and keeps a single barrier at the end of the launch
-    assert barriers == (5 * config.layers if engine == "tcgen05" else 1)
+    # seven grid barriers per layer on the tensor engine (five between phases, two behind the norm phases) and one
+    # behind the final norm; the small-launch kernel at one token hands every phase's outputs to the next as
+    # stamped words and keeps a single barrier at the end of the launch
+    assert barriers == (7 * config.layers + 1 if engine == "tcgen05" else 1)
     stamps = times[0][codes[0] > 0][:barriers]
     assert bool((stamps[1:] >= stamps[:-1]).all())
     kernel.set_trace(0)

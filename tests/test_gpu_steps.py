@@ -38,7 +38,7 @@ def greedy_on_host(kernel, config, ids, start, steps, state):
 
 @pytest.mark.parametrize("batch,engine", [(1, "auto"), (3, "auto"), (6, "auto"), (9, "auto"), (2, "tcgen05")])
 def test_decode_steps_equals_the_step_by_step_path(batch, engine):
-    """Row table (1 token), split-K table (3), two launches per step (6) and the tensor engine (9, forced 2)."""
+    """Row table (1 token), split-K table (3) and the tensor engine (6, 9, forced 2)."""
     config = tiny_config(q_heads=4, kv_heads=2, hidden=256)
     weights = synth_weights(config, seed=4, norm_std=0.1, device=DEVICE)
     kernel = make_kernel(config, weights, max_tokens=batch, max_positions=32, engine=engine)
@@ -129,13 +129,13 @@ def test_cuda_op_reports_a_full_cache_on_its_next_call():
     assert torch.isfinite(ok.float()).all() and int(length) == 1
 
 
-def test_a_bad_id_in_either_half_of_a_split_step_refuses_the_whole_step():
-    """Six sequences run as two launches of three; a bad id in the first half must stop the second too."""
+def test_a_bad_id_refuses_the_whole_step():
+    """One out-of-range id among six sequences: nothing is appended, no length moves, the logits are NaN."""
     config = tiny_config(q_heads=4, kv_heads=1, hidden=256)
     kernel = make_kernel(config, synth_weights(config, seed=3, norm_std=0.1, device=DEVICE), max_tokens=6, max_positions=16)
     keys, values, lengths = new_kv_state(config, 6, 16, DEVICE)
     ids = synth_ids(6, config.vocab, seed=3).view(6, 1).to(DEVICE)
-    ids[1, 0] = config.vocab  # out of range, first launch
+    ids[1, 0] = config.vocab  # out of range
     logits = kernel.decode(ids, torch.zeros((6, 1), dtype=torch.int64, device=DEVICE), keys, values, lengths)
     assert kernel.status()["status"] == "BAD_INDEX"
     assert torch.isnan(logits.float()).all() and all(int(length) == 0 for length in lengths)
@@ -193,3 +193,39 @@ def test_static_scratch_status_recovers_from_a_refused_launch():
     assert call() == _native.MK_OK
     assert lib.mk_kv_attention_static_status(0, stream, ctypes.byref(info)) == _native.MK_OK
     assert int(length) == 1 and torch.isfinite(output.float()).all()
+
+
+@pytest.mark.parametrize("lengths_now", [[5, 0, 9], [700, 3, 350, 64, 699]])
+def test_per_sequence_valid_lengths_match_the_oracle_one_sequence_at_a_time(lengths_now):
+    """Sequences of different lengths in one batch (beyond the reference's one-length-per-batch contract):
+    every sequence must come out as if it had been decoded alone by the reference path."""
+    from megabake_b200.synth import rope_tables, synth_normal
+    from oracle import decoder_oracle as oracle
+
+    config = tiny_config(q_heads=8, kv_heads=2, hidden=512, intermediate=1024)
+    batch, capacity = len(lengths_now), 768
+    weights = synth_weights(config, seed=8, norm_std=0.1, device=DEVICE)
+    kernel = make_kernel(config, weights, max_tokens=batch, max_positions=capacity)
+    tables = rope_tables(config, capacity, device=DEVICE)
+    keys, values, _ = new_kv_state(config, batch, capacity, DEVICE)
+    for layer in range(config.layers):
+        keys[layer].copy_(synth_normal(tuple(keys[layer].shape), seed=8, name=f"k{layer}", std=0.5, device=DEVICE))
+        values[layer].copy_(synth_normal(tuple(values[layer].shape), seed=8, name=f"v{layer}", std=0.5, device=DEVICE))
+    lengths = [torch.tensor(lengths_now, dtype=torch.int32, device=DEVICE) for _ in range(config.layers)]
+    alone = []  # one private batch-1 state per sequence for the oracle
+    for row, filled in enumerate(lengths_now):
+        alone.append(([k[row:row + 1].clone() for k in keys], [v[row:row + 1].clone() for v in values],
+                      [torch.full((1,), filled, dtype=torch.int32, device=DEVICE) for _ in range(config.layers)]))
+    ids = synth_ids(batch, config.vocab, seed=8).view(batch, 1).to(DEVICE)
+    for step in range(3):
+        positions = torch.tensor([[n + step] for n in lengths_now], dtype=torch.int64, device=DEVICE)
+        logits = kernel.decode_ragged(ids, positions, keys, values, lengths)
+        kernel.check()
+        with torch.no_grad():
+            expected = torch.cat([oracle.decode_step(config, weights, tables, ids[row:row + 1], positions[row:row + 1], *alone[row])
+                                  for row in range(batch)])
+        assert_parity(logits, expected, f"ragged logits at step {step}")
+        ids = expected[:, 0].float().argmax(-1).view(batch, 1)
+    assert all(torch.equal(length.cpu(), torch.tensor([n + 3 for n in lengths_now], dtype=torch.int32)) for length in lengths)
+    for row, filled in enumerate(lengths_now):
+        assert_parity(keys[-1][row:row + 1, :filled + 3], alone[row][0][-1][:, :filled + 3], f"sequence {row} key cache")
