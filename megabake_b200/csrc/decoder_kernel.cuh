@@ -1227,286 +1227,174 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, 
   return true;
 }
 
-// Softmax attention for every (sequence, kv head, query token) row group; all
-// query heads of the kv head share one pass over K and V.  In decode the
-// context is split into chunks across CTAs.  Each chunk publishes its max and
-// its sum of exp(score - max) with a stamp; once every chunk's stamp is there,
-// each chunk rebuilds the global max and sum, so that every probability is
-// rounded to bf16 against the global normaliser, as the reference ops do:
-//   decode  (kv_attention): score = bf16(q.k) * scale in fp32
-//   prefill (attention):    score = bf16(bf16(q.k) * scale) (+ mask, rounded again)
-// then fp32 softmax, probability rounded to bf16, fp32 value sum rounded once
-// (chunk partials are summed in chunk order by the consumer or by chunk 0's
-// peers, see AttnArgs::combine).
-__device__ __noinline__ bool attention_phase(const Ctx& cx, const AttnArgs& A, int wtid) {
-  if (A.decode) return attention_decode(cx, A, wtid);
+// Prompt attention (megabake::attention and the prefill pass) on the warp-level tensor cores.
+//
+// A unit is (sequence, query head, block of 128 query tokens); each of the eight worker warps owns 16
+// of the block's query rows and keeps their q fragments in registers.  Keys and values of the unit's
+// KV head stream through the (idle) weight ring in tiles of 64 positions.  Two passes over the key
+// tiles reproduce the reference's rounding points (src/megabake/lowering.py:274-300, the Hugging
+// Face eager form): score = bf16(bf16(q.k) * scale) (+ additive mask, rounded again); softmax in fp32
+// against the row's global maximum and sum; probability rounded to bf16; fp32 value sums rounded once.
+//   pass 1: scores of every tile -> running row maximum and sum of exp (rescaled when the maximum grows);
+//   pass 2: the same scores again (same instructions, same bits) -> p = bf16(exp(s - max) / sum), which is
+//           already the A-fragment layout of the next product, times the V tile (ldmatrix.trans).
+// Without a mask tensor attention is causal: key j <= query token index, tiles past the block's last
+// query are skipped.  Rounded scores are bf16, so recomputing them costs tensor-core time only; no
+// score buffer limits the key count.
+constexpr int kPromptQueries = 16 * kWorkerWarps;  // query rows per unit
+constexpr int kPromptKeys = 64;                    // positions per K / V tile
+
+__device__ __forceinline__ uint32_t ldcg_u32(const void* ptr) { return __ldcg(reinterpret_cast<const unsigned int*>(ptr)); }
+
+__device__ __noinline__ bool attention_prompt(const Ctx& cx, const AttnArgs& A, int wtid) {
   const KParams& p = *cx.p;
-  const int hd = p.head_dim, half = hd / 2;
+  const int hd = p.head_dim;
   const int gs = p.q_heads / p.kv_heads;
-  const int rows = p.batch * p.kv_heads * A.sq;
-  const int n_max = A.decode ? A.len + 1 : A.klen;
-  const int warp = wtid >> 5, lane = wtid & 31;
-  const int lpk = hd / 8;    // lanes per key (16 B each)
-  const int kpw = 32 / lpk;  // keys per warp pass
-  const int sub = lane / lpk, dg = lane % lpk;
-  const int nch = A.decode ? decode_chunks(n_max, rows, cx.grid, gs) : 1;
-  const int chunk = (n_max + nch - 1) / nch;
-  const int units = rows * nch;
+  const int warp = wtid >> 5, lane = wtid & 31, g = lane >> 2, t = lane & 3;
+  const int ksteps = hd / 16;   // k steps of the score product: 4 or 8
+  const int dtiles = hd / 8;    // 8-column tiles of the output row: 8 or 16
+  const int pitch = hd * 2 + 16;  // bytes per tile row: 16 bytes of padding keep fragment loads conflict-free
+  const int qblocks = (A.sq + kPromptQueries - 1) / kPromptQueries;
+  const int units = p.batch * p.q_heads * qblocks;
+  const uint32_t ks_addr = smem_u32(cx.smem_a), vs_addr = ks_addr + kPromptKeys * pitch;
+  const int pieces = hd / 8;  // 16-byte pieces per row
 
-  float* sc = reinterpret_cast<float*>(cx.smem_b);                // [gs][chunk]
-  float* qs = reinterpret_cast<float*>(cx.smem_b + kScoreBytes);  // [gs][hd]
-  float* red = qs + 8 * 128;                                      // [worker warps][128]
-  bf16* kn = reinterpret_cast<bf16*>(red + kWorkerWarps * 128);   // [hd]
-  bf16* vn = kn + 128;                                            // [hd]
-  float* stat = reinterpret_cast<float*>(vn + 128);               // [16]: max[8], sum[8]
-
+#pragma unroll 1
   for (int u = cx.cta; u < units; u += cx.grid) {
-    const int rowg = u / nch, ch = u - rowg * nch;
-    const int bk = rowg / A.sq, qi = rowg - bk * A.sq;  // (sequence, kv head) index and query token
-    const int b = bk / p.kv_heads, kvh = bk - b * p.kv_heads;
-    const int n = A.decode ? n_max : (A.causal ? min(qi + 1, A.klen) : A.klen);
-    const int j0 = ch * chunk;
-    const int j1 = min(n, j0 + chunk);
-    const int cl = max(0, j1 - j0);
-    const int newpos = A.decode ? A.len : -1;
-    const bool owner = A.decode && (A.len >= j0 && A.len < j1);
-    named_bar_sync(1, kWorkers);  // previous unit is done with the scratch
-
-    // --- load q (all heads of the group) and, in decode, the new key/value
-    long long pos = 0;
-    if (A.rope) {
-      pos = p.pos[b];
-      if (pos < 0 || pos >= p.max_positions) pos = 0;  // reported by the prologue
-    }
-    const int loads = A.decode ? gs + 1 : gs;
-    for (int idx = wtid; idx < loads * half; idx += kWorkers) {
-      const int g = idx / half, i = idx - g * half;
-      const bf16* src = (g < gs) ? A.q + b * A.q_bstride + static_cast<long long>(qi) * A.q_ld + (kvh * gs + g) * hd
-                                 : A.knew + static_cast<long long>(b) * A.new_ld + kvh * hd;
-      float first = ldcg_bf16(src + i);
-      float second = ldcg_bf16(src + i + half);
-      if (A.rope) {
-        const float c = ldg_bf16(p.cos_t + pos * hd + i);
-        const float s = ldg_bf16(p.sin_t + pos * hd + i);
-        rope_pair(first, second, c, s, p.rope_style, first, second);
-      }
-      if (g < gs) {
-        qs[g * hd + i] = first;
-        qs[g * hd + i + half] = second;
-      } else {
-        kn[i] = __float2bfloat16_rn(first);
-        kn[i + half] = __float2bfloat16_rn(second);
+    const int qb = u % qblocks, bh = u / qblocks;
+    const int h = bh % p.q_heads, b = bh / p.q_heads, kvh = h / gs;
+    const int q0 = qb * kPromptQueries + warp * 16;
+    const int r0 = q0 + g, r1 = r0 + 8;  // this thread's two query rows
+    const int r0c = min(r0, A.sq - 1), r1c = min(r1, A.sq - 1);
+    const bf16* qrow0 = A.q + b * A.q_bstride + static_cast<long long>(r0c) * A.q_ld + h * hd;
+    const bf16* qrow1 = A.q + b * A.q_bstride + static_cast<long long>(r1c) * A.q_ld + h * hd;
+    uint32_t qf[8][4];
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      if (ks < ksteps) {
+        qf[ks][0] = ldcg_u32(qrow0 + ks * 16 + t * 2);
+        qf[ks][1] = ldcg_u32(qrow1 + ks * 16 + t * 2);
+        qf[ks][2] = ldcg_u32(qrow0 + ks * 16 + 8 + t * 2);
+        qf[ks][3] = ldcg_u32(qrow1 + ks * 16 + 8 + t * 2);
       }
     }
-    if (A.decode) {
-      for (int i = wtid; i < hd; i += kWorkers)
-        vn[i] = __float2bfloat16_rn(ldcg_bf16(A.vnew + static_cast<long long>(b) * A.new_ld + kvh * hd + i));
-    }
-    named_bar_sync(1, kWorkers);
     const bf16* kbase = A.k + b * A.kv_bstride + kvh * hd;
     const bf16* vbase = A.v + b * A.kv_bstride + kvh * hd;
-    if (owner) {  // in-kernel KV append
-      bf16* kd = A.k + b * A.kv_bstride + static_cast<long long>(A.len) * A.kv_ld + kvh * hd;
-      bf16* vd = A.v + b * A.kv_bstride + static_cast<long long>(A.len) * A.kv_ld + kvh * hd;
-      for (int i = wtid; i < hd; i += kWorkers) {
-        kd[i] = kn[i];
-        vd[i] = vn[i];
-      }
-    }
-    const bf16* mrow = A.mask ? A.mask + (static_cast<long long>(b) * A.sq + qi) * A.klen : nullptr;
+    const bf16* mrow0 = A.mask ? A.mask + (static_cast<long long>(b) * A.sq + r0c) * A.klen : nullptr;
+    const bf16* mrow1 = A.mask ? A.mask + (static_cast<long long>(b) * A.sq + r1c) * A.klen : nullptr;
+    const int kend = A.causal ? min(A.klen, qb * kPromptQueries + kPromptQueries) : A.klen;
+    const int ntiles = (kend + kPromptKeys - 1) / kPromptKeys;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    float o[16][4];
+#pragma unroll
+    for (int d = 0; d < 16; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
 
-    // --- scores: eight keys per thread are loaded before any is used
-    constexpr int kU = 8;
-    const int pass = kWorkerWarps * kpw;
-    for (int base = j0 + warp * kpw; base < j1; base += pass * kU) {
-      uint4 ku[kU];
-#pragma unroll
-      for (int u8 = 0; u8 < kU; ++u8) {
-        const int j = base + u8 * pass + sub;
-        ku[u8] = make_uint4(0, 0, 0, 0);
-        if (j < j1) {
-          if (j == newpos) ku[u8] = *reinterpret_cast<const uint4*>(kn + dg * 8);
-          else ku[u8] = __ldcg(reinterpret_cast<const uint4*>(kbase + static_cast<long long>(j) * A.kv_ld) + dg);
+#pragma unroll 1
+    for (int pass = 0; pass < 2; ++pass) {
+#pragma unroll 1
+      for (int kt = 0; kt < ntiles; ++kt) {
+        const int j0 = kt * kPromptKeys;
+        named_bar_sync(1, kWorkers);  // every warp is done with the previous tile
+#pragma unroll 1
+        for (int it = wtid; it < kPromptKeys * pieces; it += kWorkers) {
+          const int r = it / pieces, piece = it - r * pieces;
+          const long long j = min(j0 + r, A.klen - 1);  // rows past the last key repeat it; they are masked below
+          cp_async16(ks_addr + r * pitch + piece * 16, reinterpret_cast<const uint4*>(kbase + j * A.kv_ld) + piece);
+          if (pass == 1) cp_async16(vs_addr + r * pitch + piece * 16, reinterpret_cast<const uint4*>(vbase + j * A.kv_ld) + piece);
         }
-      }
+        cp_async_wait_all();
+        named_bar_sync(1, kWorkers);
+        if (A.causal && j0 > q0 + 15) continue;  // no query of this warp sees this tile (barriers stay uniform)
+
+        // scores of this warp's 16 rows against the tile's 64 keys
+        float sv[8][4];
 #pragma unroll
-      for (int u8 = 0; u8 < kU; ++u8) {
-        if (base + u8 * pass >= j1) break;  // warp-uniform
-        const int j = base + u8 * pass + sub;
-        float kf[8];
-        unpack8(ku[u8], kf);
-        for (int g = 0; g < gs; ++g) {
-          const float* qv = qs + g * hd + dg * 8;
-          float dot = 0.f;
+        for (int nt = 0; nt < 8; ++nt) {
+          float acc[4] = {0.f, 0.f, 0.f, 0.f};
+          const uint32_t krow = ks_addr + (nt * 8 + g) * pitch + t * 4;
 #pragma unroll
-          for (int e = 0; e < 8; ++e) dot = fmaf(qv[e], kf[e], dot);
-          for (int o = 1; o < lpk; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-          if (dg == 0 && j < j1) {
-            float sv = bf16_round(dot) * A.scale;
-            if (!A.decode) {
-              sv = bf16_round(sv);
-              if (mrow) sv = bf16_round(sv + ldg_bf16(mrow + j));
-            }
-            sc[g * chunk + (j - j0)] = sv;
+          for (int ks = 0; ks < 8; ++ks)
+            if (ks < ksteps) mma_bf16_16816(acc, qf[ks], lds_u32(krow + ks * 32), lds_u32(krow + ks * 32 + 16));
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int j = j0 + nt * 8 + t * 2 + (e & 1);
+            const int qi = (e < 2) ? r0 : r1;
+            float v = bf16_round(bf16_round(acc[e]) * A.scale);
+            if (A.mask) v = bf16_round(v + ldg_bf16(((e < 2) ? mrow0 : mrow1) + min(j, A.klen - 1)));
+            const bool valid = j < A.klen && (!A.causal || j <= qi);
+            sv[nt][e] = valid ? v : -INFINITY;
           }
         }
-      }
-    }
-    named_bar_sync(1, kWorkers);
-
-    // --- chunk max, then chunk sum of exp(score - chunk max)
-    for (int g = 0; g < gs; ++g) {
-      float m = -INFINITY;
-      for (int i = wtid; i < cl; i += kWorkers) m = fmaxf(m, sc[g * chunk + i]);
-      m = warp_max(m);
-      if (lane == 0) red[warp * 8 + g] = m;
-    }
-    named_bar_sync(1, kWorkers);
-    for (int g = 0; g < gs; ++g) {
-      float m = red[g];
+        if (pass == 0) {
+          float t0 = -INFINITY, t1 = -INFINITY;
 #pragma unroll
-      for (int w = 1; w < kWorkerWarps; ++w) m = fmaxf(m, red[w * 8 + g]);
-      float s = 0.f;
-      for (int i = wtid; i < cl; i += kWorkers) s += expf(sc[g * chunk + i] - m);
-      s = warp_sum(s);
-      if (lane == 0) red[kWorkerWarps * 8 + warp * 8 + g] = s;
-      if (wtid == 0) stat[g] = m;
-    }
-    named_bar_sync(1, kWorkers);
-    if (wtid < gs) {
-      float total = 0.f;
-#pragma unroll
-      for (int w = 0; w < kWorkerWarps; ++w) total += red[kWorkerWarps * 8 + w * 8 + wtid];
-      stat[8 + wtid] = total;
-    }
-    named_bar_sync(1, kWorkers);
-
-    if (nch > 1) {
-      // --- publish (max, sum) with this phase's stamp; wait for every chunk of the row group
-      float* mine = p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + ch) * kExchangeFloats;
-      if (wtid < 16) __stcg(mine + wtid, stat[wtid]);
-      __threadfence();
-      named_bar_sync(1, kWorkers);
-      if (wtid == 0) st_relaxed_u32(reinterpret_cast<uint32_t*>(mine + 16), A.stamp);
-      bool ok = true;
-      if (wtid < nch) {
-        const uint32_t* theirs = reinterpret_cast<const uint32_t*>(
-            p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + wtid) * kExchangeFloats + 16);
-        uint32_t spins = 0;
-        while (ld_relaxed_u32(theirs) != A.stamp) {
-          if ((++spins & 255u) == 0 && give_up(cx, SITE_ATT_EXCHANGE, rowg)) {
-            ok = false;
-            break;
+          for (int nt = 0; nt < 8; ++nt) {
+            t0 = fmaxf(t0, fmaxf(sv[nt][0], sv[nt][1]));
+            t1 = fmaxf(t1, fmaxf(sv[nt][2], sv[nt][3]));
           }
-        }
-        __threadfence();
-      }
-      if (!workers_ok(cx, ok)) return false;
-      if (wtid < gs) {
-        const float* all = p.att_xch + static_cast<size_t>(rowg) * kMaxChunks * kExchangeFloats;
-        float m = -INFINITY;
-        for (int c = 0; c < nch; ++c) m = fmaxf(m, __ldcg(all + c * kExchangeFloats + wtid));
-        float s = 0.f;
-        for (int c = 0; c < nch; ++c)
-          s += __ldcg(all + c * kExchangeFloats + 8 + wtid) * expf(__ldcg(all + c * kExchangeFloats + wtid) - m);
-        stat[wtid] = m;
-        stat[8 + wtid] = s;
-      }
-      named_bar_sync(1, kWorkers);
-    }
-
-    // --- probabilities (bf16, against the global max and sum) and value accumulation
-    for (int g = 0; g < gs; ++g) {
-      const float m = stat[g], denom = stat[8 + g];
-      for (int i = wtid; i < cl; i += kWorkers) sc[g * chunk + i] = bf16_round(expf(sc[g * chunk + i] - m) / denom);
-    }
-    named_bar_sync(1, kWorkers);
-    for (int g = 0; g < gs; ++g) {
-      float acc[8];
+          t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 1)); t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 2));
+          t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 1)); t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 2));
+          const float n0 = fmaxf(m0, t0), n1 = fmaxf(m1, t1);
+          float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-      for (int base = j0 + warp * kpw; base < j1; base += pass * kU) {
-        uint4 vu[kU];
-#pragma unroll
-        for (int u8 = 0; u8 < kU; ++u8) {
-          const int j = base + u8 * pass + sub;
-          vu[u8] = make_uint4(0, 0, 0, 0);
-          if (j < j1) {
-            if (j == newpos) vu[u8] = *reinterpret_cast<const uint4*>(vn + dg * 8);
-            else vu[u8] = __ldcg(reinterpret_cast<const uint4*>(vbase + static_cast<long long>(j) * A.kv_ld) + dg);
+          for (int nt = 0; nt < 8; ++nt) {
+            if (n0 > -INFINITY) s0 += expf(sv[nt][0] - n0) + expf(sv[nt][1] - n0);
+            if (n1 > -INFINITY) s1 += expf(sv[nt][2] - n1) + expf(sv[nt][3] - n1);
           }
-        }
-#pragma unroll
-        for (int u8 = 0; u8 < kU; ++u8) {
-          const int j = base + u8 * pass + sub;
-          if (j < j1) {
-            float vf[8];
-            unpack8(vu[u8], vf);
-            const float pr = sc[g * chunk + (j - j0)];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) acc[e] = fmaf(pr, vf[e], acc[e]);
-          }
-        }
-      }
-      for (int o = lpk; o < 32; o <<= 1) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], o);
-      }
-      named_bar_sync(1, kWorkers);  // red is free (previous head consumed)
-      if (sub == 0) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) red[warp * 128 + dg * 8 + e] = acc[e];
-      }
-      named_bar_sync(1, kWorkers);
-      if (wtid < hd) {
-        float o = red[wtid];
-#pragma unroll
-        for (int w = 1; w < kWorkerWarps; ++w) o += red[w * 128 + wtid];
-        const int head = kvh * gs + g;
-        if (nch == 1) {
-          A.out[b * A.out_bstride + static_cast<long long>(qi) * A.out_tstride + head * A.out_hstride + wtid] =
-              __float2bfloat16_rn(o);
+          s0 += __shfl_xor_sync(0xffffffffu, s0, 1); s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+          s1 += __shfl_xor_sync(0xffffffffu, s1, 1); s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+          if (n0 > -INFINITY) { l0 = l0 * expf(m0 - n0) + s0; m0 = n0; }
+          if (n1 > -INFINITY) { l1 = l1 * expf(m1 - n1) + s1; m1 = n1; }
         } else {
-          const size_t row = static_cast<size_t>(b) * p.q_heads + head;  // decode: sq == 1
-          __stcg(p.att_part + (row * kMaxChunks + ch) * hd + wtid, o);
+          // probabilities, rounded to bf16, straight into A fragments: two adjacent 8-key tiles make one 16-key step
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            uint32_t pa[4];
+            float pr[2][4];
+#pragma unroll
+            for (int half = 0; half < 2; ++half)
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float s = sv[kk * 2 + half][e];
+                const float m = (e < 2) ? m0 : m1, l = (e < 2) ? l0 : l1;
+                pr[half][e] = (s > -INFINITY) ? expf(s - m) / l : 0.f;
+              }
+            pa[0] = pack2(pr[0][0], pr[0][1]);
+            pa[1] = pack2(pr[0][2], pr[0][3]);
+            pa[2] = pack2(pr[1][0], pr[1][1]);
+            pa[3] = pack2(pr[1][2], pr[1][3]);
+#pragma unroll
+            for (int d = 0; d < 16; d += 2) {
+              if (d < dtiles) {
+                uint32_t vb[4];
+                // matrices: (keys kk*16 + 0..7, dims d*8..), (keys + 8, same dims), then the same two for dims (d+1)*8..
+                ldmatrix_x4_trans(vb, vs_addr + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * pitch + (d + (lane >> 4)) * 16);
+                mma_bf16_16816(o[d], pa, vb[0], vb[1]);
+                mma_bf16_16816(o[d + 1], pa, vb[2], vb[3]);
+              }
+            }
+          }
         }
       }
     }
-    if (nch > 1 && A.combine) {
-      // Stand-alone op: there is no consumer phase, so chunk 0's CTA waits for the
-      // partials of its peers (second stamp) and sums them in chunk order.
-      float* mine = p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + ch) * kExchangeFloats;
-      __threadfence();
-      named_bar_sync(1, kWorkers);
-      if (wtid == 0) st_relaxed_u32(reinterpret_cast<uint32_t*>(mine + 17), A.stamp);
-      if (ch == 0) {
-        bool ok = true;
-        if (wtid < nch) {
-          const uint32_t* theirs = reinterpret_cast<const uint32_t*>(
-              p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + wtid) * kExchangeFloats + 17);
-          uint32_t spins = 0;
-          while (ld_relaxed_u32(theirs) != A.stamp) {
-            if ((++spins & 255u) == 0 && give_up(cx, SITE_ATT_EXCHANGE, rowg)) {
-              ok = false;
-              break;
-            }
-          }
-          __threadfence();
-        }
-        if (!workers_ok(cx, ok)) return false;
-        for (int idx = wtid; idx < gs * hd; idx += kWorkers) {
-          const int g = idx / hd, d = idx - g * hd;
-          const int head = kvh * gs + g;
-          const size_t row = static_cast<size_t>(b) * p.q_heads + head;
-          float o = 0.f;
-          for (int c = 0; c < nch; ++c) o += __ldcg(p.att_part + (row * kMaxChunks + c) * hd + d);
-          A.out[b * A.out_bstride + head * A.out_hstride + d] = __float2bfloat16_rn(o);
-        }
+    // this thread's output elements: rows r0, r1; columns d * 8 + t * 2, + 1
+#pragma unroll
+    for (int d = 0; d < 16; ++d) {
+      if (d < dtiles) {
+        if (r0 < A.sq)
+          *reinterpret_cast<uint32_t*>(A.out + b * A.out_bstride + static_cast<long long>(r0) * A.out_tstride + h * A.out_hstride +
+                                       d * 8 + t * 2) = pack2(o[d][0], o[d][1]);
+        if (r1 < A.sq)
+          *reinterpret_cast<uint32_t*>(A.out + b * A.out_bstride + static_cast<long long>(r1) * A.out_tstride + h * A.out_hstride +
+                                       d * 8 + t * 2) = pack2(o[d][2], o[d][3]);
       }
     }
   }
-  if (A.decode && !A.combine && cx.cta == 0 && wtid == 0) cx.ctrl->att_nch = nch;  // read after the barrier
   return true;
+}
+
+__device__ __forceinline__ bool attention_phase(const Ctx& cx, const AttnArgs& A, int wtid) {
+  return A.decode ? attention_decode(cx, A, wtid) : attention_prompt(cx, A, wtid);
 }
 
 // Prefill: rotate q and k of every token in place in the qkv buffer.
