@@ -41,7 +41,7 @@ import torch
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-from megabake_b200.synth import CONFIGS, new_kv_state, synth_ids, synth_normal, synth_weights  # noqa: E402
+from megabake_b200.synth import CONFIGS, DecoderConfig, new_kv_state, synth_ids, synth_normal, synth_weights  # noqa: E402
 
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1400.0
@@ -62,6 +62,8 @@ def parse_args():
     parser.add_argument("--batch", type=int, default=1)
     parser.add_argument("--context", type=int, default=1024)
     parser.add_argument("--capacity", type=int, default=2048)
+    parser.add_argument("--layers", type=int, default=0,
+                        help="keep only the first N layers of the shape (profiler captures of a few hundred MB; never a bench value)")
     parser.add_argument("--cpu-steps", type=int, default=40, help="CPU baseline sample size")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--engine", default="auto", choices=["auto", "tcgen05", "fma"], help="kernel choice for the headline run")
@@ -353,6 +355,10 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     config = CONFIGS[args.config]
+    if args.layers:
+        values = config.to_dict()
+        values.update(layers=args.layers, name=f"{config.name}-first-{args.layers}-layers")
+        config = DecoderConfig(**values)
     workload = (f"{config.name}-shaped bf16 decode, batch {args.batch}, KV capacity {args.capacity} "
                 f"pre-filled to {args.context}")
     base = {

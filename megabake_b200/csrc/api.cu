@@ -212,6 +212,8 @@ struct mk_handle_s {
   bool small_ll;  // its q/k/v phases hand their outputs to attention as stamped words (one grid barrier fewer per layer)
   unsigned long long* trace;
   int trace_cap;
+  int small_ring;       // weight ring of the small-launch kernel, 1 KiB granules
+  int fat_copy;         // largest weight copy of the small-launch tables, bytes (three to four fit the ring)
   bool use3d;           // weight descriptors of the tensor engine are three-dimensional (several K chunks per copy)
   uint32_t tp_epoch;    // all-reduces launched so far (tensor parallel)
   uint8_t* tp_peer[kMaxTp];
@@ -246,7 +248,6 @@ int choose_rows(const GemmPhase& ph, int slots, int max_rows = kTileRows) {
 // bandwidth busy (the copy engine retires roughly one box per 0.1 us), so a
 // projection with few output rows per CTA is cut along K as well.
 constexpr int kGoodBoxRows = 40;
-constexpr int kFatCopyBytes = 30 * 1024;  // largest weight copy of the small-launch table: four fit the ring
 
 void finish_phase(GemmPhase& ph, int grid, bool allow_split, int max_rows = kTileRows) {
   ph.kc = ph.k / kChunkK;
@@ -308,6 +309,12 @@ void finish_phase_tc(GemmPhase& ph, int grid, bool allow_split, int max_tokens) 
 bool split_table_ok(const mk_config& c) { return c.tp_size <= 1; }
 bool small_shape_ok(const mk_config& c) { return c.hidden / kChunkK <= kBSlots && c.tp_size <= 1; }
 
+// One-token launches run the row table with the handle's ring; the split-K table of two to four tokens
+// measured best with a 92 KiB ring and copies of at most 30 KiB.
+constexpr int kSplitTableRing = 92;
+constexpr int kBoxCopyBytes = 30 * 1024;
+int small_ring_for(mk_handle h, int tokens) { return tokens == 1 ? h->small_ring : std::min(h->small_ring, kSplitTableRing); }
+
 void base_params(mk_handle h, KParams& p) {
   memset(&p, 0, sizeof(p));
   const mk_config& c = h->cfg;
@@ -329,6 +336,7 @@ void base_params(mk_handle h, KParams& p) {
   p.trace = h->trace;
   p.trace_cap = h->trace ? h->trace_cap : 0;
   p.status_mirror = h->mirror;
+  p.small_ring = small_ring_for(h, 1);  // launches of two to four tokens overwrite it
   p.ctrl = at<Control>(h, h->cv.ctrl);
   p.att_xch = at<float>(h, h->cv.att_xch);
   p.att_part = at<float>(h, h->cv.att_part);
@@ -357,13 +365,14 @@ const void* small_kernel(int tokens) {
   }
 }
 
-int prepare_small_kernels(int device) {
+int prepare_small_kernels(int device, int ring_granules) {
   for (int t = 1; t <= kSplitTokens; ++t) {
     const void* fn = small_kernel(t);
-    MK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmallSmemBytes));
-    MK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, (kSmallSmemBytes * 100 + 233471) / 233472));
+    const int bytes = small_smem_bytes(t == 1 ? ring_granules : std::min(ring_granules, kSplitTableRing));
+    MK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    MK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, (bytes * 100 + 233471) / 233472));
     int per_sm = 0;
-    MK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kSmallThreads, kSmallSmemBytes));
+    MK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kSmallThreads, bytes));
     if (per_sm < 1) return fail(MK_ERR_UNSUPPORTED, "the small-launch megakernel does not fit on an SM of device %d", device);
   }
   return MK_OK;
@@ -372,7 +381,7 @@ int prepare_small_kernels(int device) {
 int launch(mk_handle h, KParams& p, void* stream, int attention_phases = 0, bool small = false) {
   void* args[] = {&p};
   if (small)
-    MK_CUDA(cudaLaunchCooperativeKernel(small_kernel(p.m), dim3(h->grid), dim3(kSmallThreads), args, kSmallSmemBytes,
+    MK_CUDA(cudaLaunchCooperativeKernel(small_kernel(p.m), dim3(h->grid), dim3(kSmallThreads), args, small_smem_bytes(p.small_ring),
                                         static_cast<cudaStream_t>(stream)));
   else
     MK_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(&megakernel), dim3(h->grid), dim3(kThreads), args,
@@ -430,9 +439,15 @@ int mk_create(const mk_config* config, void* workspace, size_t workspace_bytes, 
   int per_sm = 0;
   MK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, megakernel, kThreads, kSmemBytes));
   if (per_sm < 1) return fail(MK_ERR_UNSUPPORTED, "the megakernel does not fit on an SM of device %d", device);
-  if (int e = prepare_small_kernels(device)) return e;
+  // Tunables of the small-launch kernel (process-wide: shared-memory attributes belong to the function).
+  int small_ring = kSmallRingGranules, fat_copy = 36 * 1024;
+  if (const char* env = getenv("MEGABAKE_SMALL_RING_KB")) small_ring = std::max(64, std::min(kSmallRingMax, atoi(env)));
+  if (const char* env = getenv("MEGABAKE_SMALL_COPY_KB")) fat_copy = std::max(16, std::min(small_ring / 2, atoi(env))) * 1024;
+  if (int e = prepare_small_kernels(device, small_ring)) return e;
   mk_handle h = new (std::nothrow) mk_handle_s();
   if (!h) return fail(MK_ERR_INVALID, "out of host memory");
+  h->small_ring = small_ring;
+  h->fat_copy = fat_copy;
   h->cfg = *config;
   h->device = device;
   h->grid = grid;
@@ -625,7 +640,7 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
       }
       int kb = 1;
       for (int cand = 2; cand <= 4; cand += 2)
-        if (ph.kslice % cand == 0 && ph.rows * cand * 128 <= kFatCopyBytes) kb = cand;
+        if (ph.kslice % cand == 0 && ph.rows * cand * 128 <= kBoxCopyBytes) kb = cand;
       ph.kb = kb;
       ph.gran = (ph.rows * kb * 128 + kGranule - 1) / kGranule;
       const int nseg = ph.nacc == 2 ? 2 : ph.nseg;
@@ -660,7 +675,7 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
   // (contiguous in memory, fetched by one-dimensional bulk copies of up to 28 KB), adds the residual in its
   // epilogue and stamps the new residual stream, which the next normalising phase polls: no fp32 partials,
   // no grid barrier inside a layer.  The residual stream alternates between res_a (after the MLP) and res_b.
-  h->row_ok = h->small_ll && c.hidden % 2 == 0 && q_size * 2 <= kFatCopyBytes - 2048 && c.intermediate * 2 <= kFatCopyBytes - 2048 &&
+  h->row_ok = h->small_ll && c.hidden % 2 == 0 && q_size * 2 <= h->fat_copy - 2048 && c.intermediate * 2 <= h->fat_copy - 2048 &&
               c.intermediate <= kSplitTokens * kBSlots * kChunkK && q_size <= kSplitTokens * kBSlots * kChunkK;
   if (h->row_ok) {
     unsigned long long* res_a = at<unsigned long long>(h, h->cv.res_a);
@@ -685,7 +700,7 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
         rp.nunits = rp.ntiles;
         rp.bulk = 1;
         const int row_bytes = rp.k * 2;
-        rp.rpc = std::max(1, std::min(8, (kFatCopyBytes - 2048) / row_bytes));
+        rp.rpc = std::max(1, std::min(8, (h->fat_copy - 2048) / row_bytes));
         if (rp.rpc > rp.rows) rp.rpc = rp.rows;
         rp.kb = 1;
         rp.gran = (rp.rpc * row_bytes + kGranule - 1) / kGranule;
@@ -830,6 +845,7 @@ int decode_once(mk_handle h, const int64_t* ids, const int64_t* positions, int b
     p.nbar = 1;
     p.rowmode = 1;
   }
+  p.small_ring = small_ring_for(h, p.rowmode ? 1 : 2);
   p.stream_once = (ntt == 1);
   p.ids = reinterpret_cast<long long*>(const_cast<int64_t*>(ids));
   p.pos = reinterpret_cast<long long*>(const_cast<int64_t*>(positions));

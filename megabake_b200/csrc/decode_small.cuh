@@ -35,10 +35,13 @@ constexpr int kSmallWarps = 8;
 constexpr int kSmallWorkers = kSmallWarps * 32;
 constexpr int kSmallThreads = 32 + kSmallWorkers;
 constexpr int kXFloats = kBSlots * kChunkK;  // activation operand of one K slice per token, fp32
-// Weight ring of this kernel: 92 KB (three to four copies in flight) measured faster than both 64 and
-// 120 KB; it also keeps the CTA under the 164 KB shared-memory carve-out, which leaves 92 KB of L1.
-constexpr int kSmallRingGranules = 92;
-constexpr int kSmallSmemBytes = 1024 + kSmallRingGranules * kGranule + kBBytes + kMiscBytes;
+// Weight ring of this kernel.  Measured on the 1.7B shape (batch 1, us per step): 92 KB with copies of
+// up to 30 KB 1252; 120 KB / 36 KB 1185; 126 KB and more 1276-1310: past 196 KB of shared memory per CTA
+// the carve-out jumps to 228 KB and the 28 KB of L1 that remain no longer hold the stack frames.
+constexpr int kSmallRingGranules = 120;    // default; a handle may choose up to kSmallRingMax (KParams::small_ring)
+constexpr int kSmallRingMax = 152;
+constexpr int small_smem_bytes(int ring_granules) { return 1024 + ring_granules * kGranule + kBBytes + kMiscBytes; }
+static_assert(small_smem_bytes(kSmallRingMax) <= 232448, "the largest ring exceeds 227 KiB of shared memory");
 static_assert(kSplitTokens * kXFloats * 4 <= kBBytes, "activation operand does not fit its region");
 
 struct SmallState {
@@ -332,6 +335,30 @@ __device__ __noinline__ void small_finish_row(const Ctx& cx, const GemmPhase* ph
 // (two or four rows at once when a row segment is shorter than 512 bytes).  Every (row, lane)
 // keeps one fp32 chain over the K loop; at the end a fixed shuffle tree adds the lanes of a row.
 // Accumulation order depends only on the CTA's rotated chunk order: no dependence on timing.
+template <int N>
+struct IntTag {
+  static constexpr int value = N;
+};
+
+// One weight copy's share of a lane: ITERS rows, 4096 bytes apart, eight weights of each.  All loads
+// first, then one FMA chain per row (the chains are independent, so they overlap).  Rows past the
+// tile's last row read whatever the ring holds there; their sums are never stored.
+template <int T, int ITERS>
+__device__ __forceinline__ void small_fma_rows(uint32_t base, const float (&xf)[T][8], float (&acc)[8][T]) {
+  uint4 w[ITERS];
+#pragma unroll
+  for (int i = 0; i < ITERS; ++i) w[i] = lds_v4(base + i * 4096);
+#pragma unroll
+  for (int i = 0; i < ITERS; ++i) {
+    float wf[8];
+    unpack8(w[i], wf);
+#pragma unroll
+    for (int t = 0; t < T; ++t)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[i][t] = fmaf(wf[e], xf[t][e], acc[i][t]);
+  }
+}
+
 template <int T, int NACC>
 __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, int wtid, uint4 wu, int nch, uint32_t stamp) {
   const GemmPhase* ph = &cx.misc->phase[gp & 1];
@@ -348,6 +375,7 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
   const uint32_t lane_off = row_first * row_bytes + (cl << 4);
   const int rot = k_rotation(cx.cta, cx.grid, kslice / kb) * kb;
   const uint32_t ring_base = smem_u32(cx.smem_a);
+  const int ring_granules = cx.p->small_ring;
   const uint32_t x_base = smem_u32(cx.smem_b) + ((cl >> 3) * kChunkK + (cl & 7) * 4) * 4;
   float* sums = reinterpret_cast<float*>(cx.smem_b + kRowSumOffset);
   int head = st.head, seq = st.seq;
@@ -375,6 +403,11 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
 #pragma unroll
           for (int t = 0; t < T; ++t) acc[a][i][t] = 0.f;
       int slot = rot;
+      // The K loop, instantiated once per row-iteration count for one-token launches (ITERS > 0: no
+      // predicate inside the unrolled body, so the loads of a copy issue back to back and the rows' FMA
+      // chains interleave), and once in the general, predicated form (ITERS == 0).
+      auto k_loop = [&](auto iters_tag) {
+      constexpr int ITERS = decltype(iters_tag)::value;
 #pragma unroll 1
       for (int k0 = 0; k0 < kslice; k0 += kb) {
         // this lane's activation values for the K range of the copy
@@ -390,7 +423,7 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
         }
 #pragma unroll
         for (int a = 0; a < NACC; ++a) {
-          if (head + gran > kSmallRingGranules) head = 0;
+          if (head + gran > ring_granules) head = 0;
           const uint32_t base = ring_base + head * kGranule + lane_off;
           head += gran;
           const uint32_t bar = seq % kChunkBars;
@@ -398,15 +431,20 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
           // every consumer still reaches the same block-wide barriers and leaves together.
           const bool got = ok && wait_mbar(cx, smem_u32(&cx.misc->full[bar]), (seq / kChunkBars) & 1, SITE_MMA_FULL, gp);
           ok = __all_sync(0xffffffffu, got);
+          if (k0 == 0 && a == 0 && unit == cx.cta) trace_event(cx, wtid, EV_FIRST_COPY);
+          if constexpr (ITERS > 0) {
+            small_fma_rows<T, ITERS>(base, xf, acc[a]);
+          } else {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            if (i < iters && row_first + i * 8 * rset < rows) {
-              float wf[8];
-              unpack8(lds_v4(base + i * 4096), wf);  // 8 * rset rows of row_bytes = 4096 bytes further on
+            for (int i = 0; i < 8; ++i) {
+              if (i < iters && row_first + i * 8 * rset < rows) {
+                float wf[8];
+                unpack8(lds_v4(base + i * 4096), wf);  // 8 * rset rows of row_bytes = 4096 bytes further on
 #pragma unroll
-              for (int t = 0; t < T; ++t)
+                for (int t = 0; t < T; ++t)
 #pragma unroll
-                for (int e = 0; e < 8; ++e) acc[a][i][t] = fmaf(wf[e], xf[t][e], acc[a][i][t]);
+                  for (int e = 0; e < 8; ++e) acc[a][i][t] = fmaf(wf[e], xf[t][e], acc[a][i][t]);
+              }
             }
           }
           __syncwarp();
@@ -414,6 +452,21 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
           seq += 1;
         }
         slot = (slot + kb == kslice) ? 0 : slot + kb;
+      }
+      };
+      if constexpr (T == 1) {
+        switch (iters) {
+          case 1: k_loop(IntTag<1>{}); break;
+          case 2: k_loop(IntTag<2>{}); break;
+          case 3: k_loop(IntTag<3>{}); break;
+          case 4: k_loop(IntTag<4>{}); break;
+          case 5: k_loop(IntTag<5>{}); break;
+          case 6: k_loop(IntTag<6>{}); break;
+          case 7: k_loop(IntTag<7>{}); break;
+          default: k_loop(IntTag<8>{}); break;
+        }
+      } else {
+        k_loop(IntTag<0>{});
       }
       if (unit == cx.cta) trace_event(cx, wtid, EV_FIRST_ACC);
       if (unit != cx.cta) small_sync();  // the previous unit's rows have been finished: `sums` is free
@@ -509,6 +562,7 @@ __device__ __noinline__ bool small_gemm_rows(const Ctx& cx, int gp, SmallState& 
   const int warp = wtid >> 5, lane = wtid & 31;
   const int kvecs = ph->k / 8;
   const uint32_t ring_base = smem_u32(cx.smem_a);
+  const int ring_granules = cx.p->small_ring;
   const uint32_t row_bytes = static_cast<uint32_t>(ph->k) * 2u;
   float* sums = reinterpret_cast<float*>(cx.smem_b + kRowSumOffset);   // [row][warp] here
   int head = st.head, seq = st.seq;
@@ -539,28 +593,57 @@ __device__ __noinline__ bool small_gemm_rows(const Ctx& cx, int gp, SmallState& 
       }
 #pragma unroll 1
       for (int r0 = 0; r0 < tile_rows; r0 += rpc) {
-        if (head + gran > kSmallRingGranules) head = 0;
+        if (head + gran > ring_granules) head = 0;
         const uint32_t base = ring_base + head * kGranule + (wtid << 4);
         head += gran;
         const uint32_t bar = seq % kChunkBars;
         const bool got = ok && wait_mbar(cx, smem_u32(&cx.misc->full[bar]), (seq / kChunkBars) & 1, SITE_MMA_FULL, gp);
         ok = __all_sync(0xffffffffu, got);
+        if (r0 == 0 && unit == cx.cta) trace_event(cx, wtid, EV_FIRST_COPY);
         const int count = min(rpc, tile_rows - r0);
+        // G rows of the copy at a time: their loads issue together and their FMA chains and shuffle
+        // trees interleave (one row alone is a chain of up to 32 dependent FMAs and 5 dependent shuffles).
+        // A group that runs past the copy repeats its last row and drops the repeats.
+        auto row_groups = [&](auto group_tag) {
+          constexpr int G = decltype(group_tag)::value;
 #pragma unroll 1
-        for (int r = 0; r < count; ++r) {
-          float acc = 0.f;
+          for (int r = 0; r < count; r += G) {
+            float acc[G];
+            uint32_t at[G];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            if (wtid + j * kSmallWorkers < kvecs) {
-              float wf[8];
-              unpack8(lds_v4(base + r * row_bytes + j * (kSmallWorkers * 16)), wf);
+            for (int g = 0; g < G; ++g) {
+              acc[g] = 0.f;
+              at[g] = base + static_cast<uint32_t>(min(r + g, count - 1)) * row_bytes;
+            }
 #pragma unroll
-              for (int e = 0; e < 8; ++e) acc = fmaf(wf[e], xr[j][e], acc);
+            for (int j = 0; j < 4; ++j) {
+              if (wtid + j * kSmallWorkers < kvecs) {
+                uint4 w[G];
+#pragma unroll
+                for (int g = 0; g < G; ++g) w[g] = lds_v4(at[g] + j * (kSmallWorkers * 16));
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                  float wf[8];
+                  unpack8(w[g], wf);
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) acc[g] = fmaf(wf[e], xr[j][e], acc[g]);
+                }
+              }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+              for (int g = 0; g < G; ++g) acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], o);
+            if (lane == 0) {
+#pragma unroll
+              for (int g = 0; g < G; ++g)
+                if (r + g < count) sums[(r0 + r + g) * kSmallWarps + warp] = acc[g];
             }
           }
-          acc = warp_sum(acc);
-          if (lane == 0) sums[(r0 + r) * kSmallWarps + warp] = acc;
-        }
+        };
+        if (rpc >= 4) row_groups(IntTag<4>{});
+        else if (rpc >= 2) row_groups(IntTag<2>{});
+        else row_groups(IntTag<1>{});
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&cx.misc->empty[bar]));
         seq += 1;
@@ -743,6 +826,7 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
     }
     cp_async_wait_all();
     if (!small_ok(cx, fresh)) return false;
+    trace_event(cx, wtid, EV_ATT_INPUTS);
     if (owner && newpos - j0 < tile_keys && wtid < lpk)  // the new key joins its tile (its row was not fetched)
       *reinterpret_cast<uint4*>(tile + (newpos - j0) * row_bytes + ((wtid ^ ((newpos - j0) & 7)) << 4)) =
           *reinterpret_cast<const uint4*>(kn + wtid * 8);
@@ -803,6 +887,7 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
       }
     }
     small_sync();
+    trace_event(cx, wtid, EV_ATT_SCORES);
     // --- the first tile of V rows replaces K: in flight while the statistics are built and exchanged
     fetch_tile(vbase, j0, min(j1, j0 + tile_keys));
 
@@ -873,6 +958,7 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
       small_sync();
     }
 
+    trace_event(cx, wtid, EV_ATT_STATS);
     // --- probabilities (bf16, against the global max and sum)
 #pragma unroll 1
     for (int g = 0; g < gs; ++g) {
@@ -924,6 +1010,7 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
       }
     }
     small_sync();
+    trace_event(cx, wtid, EV_ATT_VALUES);
 #pragma unroll 1
     for (int col = wtid; col < cols; col += kSmallWorkers) {
       float o = red[col];
@@ -942,6 +1029,7 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
         __stcg(p.att_part + (row * kMaxChunks + ch) * hd + d, o);
       }
     }
+    trace_event(cx, wtid, EV_ATT_PARTIAL);
     if (A.out_ll != nullptr && ch == 0) {
       // The first chunk's CTA adds the chunk partials of its heads in chunk order, rounds once and stamps the
       // result as bf16 pairs: the o projection then reads 4 bytes per output instead of 8 per chunk and output.
@@ -978,6 +1066,7 @@ __device__ __noinline__ void small_producer(const Ctx& cx) {
   const KParams& p = *cx.p;
   const uint64_t policy = l2_policy_evict_first();
   SmemMisc* misc = cx.misc;
+  const int ring_granules = p.small_ring;
   int head = 0, seq = 0, oldest = 0;
   bool ok = true;
 #pragma unroll 1
@@ -1002,7 +1091,7 @@ __device__ __noinline__ void small_producer(const Ctx& cx) {
         // Copies are consumed in issue order, so ring space is reclaimed by retiring the oldest copy in
         // flight until [lo, hi) is free; a copy never wraps, so the skipped tail is freed first.
         int lo = head, hi = head + gran;
-        if (hi > kSmallRingGranules) hi = kSmallRingGranules;  // first the tail fragment, then (second trip) the slot at 0
+        if (hi > ring_granules) hi = ring_granules;  // first the tail fragment, then (second trip) the slot at 0
 #pragma unroll 1
         for (int trip = 0; trip < 2 && ok; ++trip) {
 #pragma unroll 1
@@ -1016,7 +1105,7 @@ __device__ __noinline__ void small_producer(const Ctx& cx) {
             }
             ++oldest;
           }
-          if (head + gran <= kSmallRingGranules) break;  // no wrap: one trip
+          if (head + gran <= ring_granules) break;  // no wrap: one trip
           head = 0;
           lo = 0;
           hi = gran;
@@ -1242,7 +1331,7 @@ __global__ void __launch_bounds__(kSmallThreads, 1) megakernel_small(const __gri
   cx.p = &p;
   cx.ctrl = p.ctrl;
   cx.smem_a = smem;
-  cx.smem_b = smem + kSmallRingGranules * kGranule;
+  cx.smem_b = smem + p.small_ring * kGranule;
   cx.misc = reinterpret_cast<SmemMisc*>(cx.smem_b + kBBytes);
   cx.tc = nullptr;
   cx.deadline = clock64() + p.timeout_cycles;

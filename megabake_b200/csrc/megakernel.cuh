@@ -41,7 +41,8 @@ static_assert(kSmemBytes <= 200704, "dynamic shared memory exceeds the 196 KiB c
 enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU = 2, EPI_PARTIAL = 3, EPI_ROWRES = 4, EPI_TP = 5 };
 enum { B_PLAIN = 0, B_NORM = 1, B_ATTN = 2 };
 enum { MODE_DECODE = 0, MODE_PREFILL = 1, MODE_LINEAR = 2, MODE_KVATT = 3, MODE_ATT = 4 };
-enum { EV_PHASE_ENTER = 1, EV_B_STAGED = 2, EV_FIRST_ACC = 3, EV_PHASE_DONE = 4, EV_BARRIER_DONE = 5, EV_ATTENTION_DONE = 6 };
+enum { EV_PHASE_ENTER = 1, EV_B_STAGED = 2, EV_FIRST_ACC = 3, EV_PHASE_DONE = 4, EV_BARRIER_DONE = 5, EV_ATTENTION_DONE = 6,
+       EV_ATT_INPUTS = 7, EV_ATT_SCORES = 8, EV_ATT_STATS = 9, EV_ATT_VALUES = 10, EV_ATT_PARTIAL = 11, EV_FIRST_COPY = 12 };
 enum {
   SITE_PRODUCER_EMPTY = 1, SITE_MMA_FULL = 2, SITE_MMA_B = 3, SITE_MMA_ACC = 4, SITE_EPI_ACC = 5,
   SITE_GRID_BARRIER = 6, SITE_ATT_EXCHANGE = 7, SITE_DRAIN = 8, SITE_PROLOGUE = 9, SITE_B_EMPTY = 10,
@@ -164,6 +165,7 @@ struct KParams {
   // stand-alone projection (MODE_LINEAR): its phase and its two descriptors travel in the parameter block,
   // so the call needs no upload and no synchronisation
   GemmPhase linear_phase;
+  int small_ring;  // weight ring of the small-launch kernel, in 1 KiB granules
   CUtensorMap linear_wmap, linear_xmap;
   void* kc[MK_MAX_LAYERS];
   void* vc[MK_MAX_LAYERS];

@@ -40,7 +40,8 @@ def _require(tensor: torch.Tensor, name: str, *, dtype, device, shape=None) -> N
 
 
 EVENT_NAMES = {1: "phase_enter", 2: "operand_staged", 3: "first_accumulator", 4: "phase_done",
-               5: "barrier_done", 6: "attention_done"}
+               5: "barrier_done", 6: "attention_done", 7: "attention_inputs", 8: "attention_scores",
+               9: "attention_statistics", 10: "attention_values", 11: "attention_partial", 12: "first_copy"}
 
 
 def decode_trace(buffer: torch.Tensor):
