@@ -62,7 +62,7 @@ Carve carve(const mk_config& c) {
   };
   const size_t m = static_cast<size_t>(c.max_tokens);
   v.ctrl = take(sizeof(Control));
-  v.tmaps = take(sizeof(CUtensorMap) * (3 * maps_per_table(c) + 1 + kOperandMaps));  // split, plain and small-launch tables, mk_linear, token operands
+  v.tmaps = take(sizeof(CUtensorMap) * (4 * maps_per_table(c) + 1 + kOperandMaps));  // split, plain and small-launch tables, mk_linear, token operands, row table
   v.phases = take(sizeof(GemmPhase) * (4 * phases_per_table(c) + 1));  // + the one-token row table
   v.hidden = take(m * c.hidden * 2);
   v.hidden2 = take(m * c.hidden * 2);
@@ -356,19 +356,22 @@ void base_params(mk_handle h, KParams& p) {
 }
 
 // The small-launch kernel is instantiated per token count (1..kSplitTokens).
-const void* small_kernel(int tokens) {
+// One kernel per token count, and one more for the one-token row table (`row`): code that is compiled in
+// but never runs still costs instruction-cache reach.
+const void* small_kernel(int tokens, bool row) {
+  if (row) return reinterpret_cast<const void*>(&megakernel_small<1, true>);
   switch (tokens) {
-    case 1: return reinterpret_cast<const void*>(&megakernel_small<1>);
-    case 2: return reinterpret_cast<const void*>(&megakernel_small<2>);
-    case 3: return reinterpret_cast<const void*>(&megakernel_small<3>);
-    default: return reinterpret_cast<const void*>(&megakernel_small<4>);
+    case 1: return reinterpret_cast<const void*>(&megakernel_small<1, false>);
+    case 2: return reinterpret_cast<const void*>(&megakernel_small<2, false>);
+    case 3: return reinterpret_cast<const void*>(&megakernel_small<3, false>);
+    default: return reinterpret_cast<const void*>(&megakernel_small<4, false>);
   }
 }
 
 int prepare_small_kernels(int device, int ring_granules) {
-  for (int t = 1; t <= kSplitTokens; ++t) {
-    const void* fn = small_kernel(t);
-    const int bytes = small_smem_bytes(t == 1 ? ring_granules : std::min(ring_granules, kSplitTableRing));
+  for (int t = 0; t <= kSplitTokens; ++t) {  // 0: the row-table kernel
+    const void* fn = small_kernel(t, t == 0);
+    const int bytes = small_smem_bytes(t == 0 ? ring_granules : std::min(ring_granules, kSplitTableRing));
     MK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
     MK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, (bytes * 100 + 233471) / 233472));
     int per_sm = 0;
@@ -381,7 +384,7 @@ int prepare_small_kernels(int device, int ring_granules) {
 int launch(mk_handle h, KParams& p, void* stream, int attention_phases = 0, bool small = false) {
   void* args[] = {&p};
   if (small)
-    MK_CUDA(cudaLaunchCooperativeKernel(small_kernel(p.m), dim3(h->grid), dim3(kSmallThreads), args, small_smem_bytes(p.small_ring),
+    MK_CUDA(cudaLaunchCooperativeKernel(small_kernel(p.m, p.rowmode != 0), dim3(h->grid), dim3(kSmallThreads), args, small_smem_bytes(p.small_ring),
                                         static_cast<cudaStream_t>(stream)));
   else
     MK_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(&megakernel), dim3(h->grid), dim3(kThreads), args,
@@ -500,6 +503,8 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
   std::vector<GemmPhase> phases(4 * nphases);
   CUtensorMap* dmaps = at<CUtensorMap>(h, h->cv.tmaps);
   CUtensorMap* operand_maps = dmaps + 3 * nmaps + 1;
+  CUtensorMap* row_dmaps = operand_maps + kOperandMaps;  // the one-token row table's own (plain-row) descriptors
+  std::vector<CUtensorMap> row_maps(nmaps);
   bf16* hidden_a = at<bf16>(h, h->cv.hidden);
   bf16* hidden_b = at<bf16>(h, h->cv.hidden2);
   bf16* qkv = at<bf16>(h, h->cv.qkv);
@@ -607,18 +612,17 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
     for (int t = 0; t < 3; ++t) head.bmap[t] = operand_maps + OPERAND_XNORM * 3 + t;
     if (int e = encode_phase_weight_map(&tmaps_host[7 * L], w->lm_head, c.vocab, c.hidden, head, use3d)) return e;
   }
-  // Table 2: the split-K table again for the small-launch kernel, whose CUDA-core consumer takes
-  // the weights as plain rows: one copy brings `kb` K chunks of a tile's rows (a copy of less than
-  // ~16 KB cannot keep an SM's share of HBM busy: the copy engine retires about three per microsecond).
-  h->fma_ok = small_shape_ok(c);
+  // Table 2: the split-K table again for the small-launch kernel, whose mma.sync consumer takes tiles of
+  // at most 64 rows (four 16-row fragments) of any height below that.
+  h->fma_ok = small_shape_ok(c) && h->use3d;
   for (size_t i = 0; i < nphases && h->fma_ok; ++i)
     if (phases[i].kslice > kBSlots || phases[i].rows > kTileRows) h->fma_ok = false;
   if (h->fma_ok) {
     for (size_t i = 0; i < nphases; ++i) {
       GemmPhase& ph = phases[2 * nphases + i];
       ph = phases[i];
-      finish_phase(ph, h->grid, ph.epi == EPI_PARTIAL);  // the CUDA-core consumer takes any tile height: no rounding to 8
-      if (ph.rows > kSmallTileRows) {  // the CUDA-core consumer keeps 8 rows per warp: tiles of at most 64 rows
+      finish_phase(ph, h->grid, ph.epi == EPI_PARTIAL);  // any tile height: no rounding to 8
+      if (ph.rows > kSmallTileRows) {
         if (ph.ksplit != 1) return fail(MK_ERR_UNSUPPORTED, "small-launch table: a split phase with more than 64 rows");
         finish_phase(ph, h->grid, false, kSmallTileRows);
       }
@@ -638,16 +642,20 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
         const bool even = ph.n[0] % 2 == 0 && (ph.nacc == 2 || (ph.n[1] % 2 == 0 && ph.n[2] % 2 == 0));
         ph.ll = (ph.rows <= kSmallTileRows && even && ph.ksplit == 1) ? 1 : 0;
       }
+      // One copy = one three-dimensional box: the tile's rows x kb K chunks, each chunk 128-byte swizzled
+      // for ldmatrix; as many chunks as fit the copy size (a copy of less than ~16 KB cannot keep an
+      // SM's share of HBM busy: the copy engine retires about three per microsecond).
       int kb = 1;
-      for (int cand = 2; cand <= 4; cand += 2)
+      for (int cand = 2; cand <= std::min(ph.kslice, 256); ++cand)
         if (ph.kslice % cand == 0 && ph.rows * cand * 128 <= kBoxCopyBytes) kb = cand;
       ph.kb = kb;
+      ph.map3d = 1;
       ph.gran = (ph.rows * kb * 128 + kGranule - 1) / kGranule;
       const int nseg = ph.nacc == 2 ? 2 : ph.nseg;
       for (int sg = 0; sg < nseg; ++sg) {
         const size_t index = static_cast<size_t>(ph.tmap[sg] - dmaps);  // same matrix, same slot in the third set
         ph.tmap[sg] = dmaps + 2 * nmaps + index;
-        if (int e = encode_weight_map(&maps[2 * nmaps + index], ph.w[sg], ph.n[sg], ph.k, ph.rows, kb, false)) return e;
+        if (encode_weight_map3(&maps[2 * nmaps + index], ph.w[sg], ph.n[sg], ph.k, ph.rows, kb) != MK_OK) h->fma_ok = false;
       }
     }
   }
@@ -680,7 +688,24 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
   if (h->row_ok) {
     unsigned long long* res_a = at<unsigned long long>(h, h->cv.res_a);
     unsigned long long* res_b = at<unsigned long long>(h, h->cv.res_b);
-    for (size_t i = 0; i < nphases; ++i) phases[3 * nphases + i] = phases[2 * nphases + i];
+    // The row table's consumer runs on CUDA cores over plain rows: its box phases (q/k/v, gate/up, lm_head)
+    // get descriptors of their own, boxes of kb * 64 elements x the tile's rows without swizzle.
+    for (size_t i = 0; i < nphases && h->row_ok; ++i) {
+      GemmPhase& ph = phases[3 * nphases + i];
+      ph = phases[2 * nphases + i];
+      ph.map3d = 0;
+      int kb = 1;
+      for (int cand = 2; cand <= 4; cand += 2)
+        if (ph.kslice % cand == 0 && ph.rows * cand * 128 <= kBoxCopyBytes) kb = cand;
+      ph.kb = kb;
+      ph.gran = (ph.rows * kb * 128 + kGranule - 1) / kGranule;
+      const int nseg = ph.nacc == 2 ? 2 : ph.nseg;
+      for (int sg = 0; sg < nseg; ++sg) {
+        const size_t index = static_cast<size_t>(ph.tmap[sg] - (dmaps + 2 * nmaps));
+        ph.tmap[sg] = row_dmaps + index;
+        if (encode_weight_map(&row_maps[index], ph.w[sg], ph.n[sg], ph.k, ph.rows, kb, false) != MK_OK) h->row_ok = false;
+      }
+    }
     for (int l = 0; l <= L; ++l) {
       GemmPhase* ph = phases.data() + 3 * nphases + 4 * l;
       // normalising phases read the stamped residual stream (layer 0 still gathers embedding rows)
@@ -726,6 +751,7 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
     MK_CUDA(cudaStreamSynchronize(s));
   }
   MK_CUDA(cudaMemcpyAsync(dmaps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, s));
+  MK_CUDA(cudaMemcpyAsync(row_dmaps, row_maps.data(), row_maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, s));
   MK_CUDA(cudaMemcpyAsync(at<GemmPhase>(h, h->cv.phases), phases.data(), phases.size() * sizeof(GemmPhase),
                           cudaMemcpyHostToDevice, s));
   // The source vectors die at return: make sure the copies have read them.

@@ -34,7 +34,9 @@ namespace mk {
 constexpr int kSmallWarps = 8;
 constexpr int kSmallWorkers = kSmallWarps * 32;
 constexpr int kSmallThreads = 32 + kSmallWorkers;
-constexpr int kXFloats = kBSlots * kChunkK;  // activation operand of one K slice per token, fp32
+constexpr int kXFloats = kBSlots * kChunkK;  // activation operand of one K slice per token, fp32 (one-token row table)
+constexpr int kXElems = kBSlots * kChunkK;      // the same as bf16 for the mma.sync consumer (2048 elements)
+constexpr int kXTokenBytes = kXElems * 2 + 16;  // its row pitch in shared memory (the padding spreads token rows over the banks)
 // Weight ring of this kernel.  Measured on the 1.7B shape (batch 1, us per step): 92 KB with copies of
 // up to 30 KB 1252; 120 KB / 36 KB 1185; 126 KB and more 1276-1310: past 196 KB of shared memory per CTA
 // the carve-out jumps to 228 KB and the 28 KB of L1 that remain no longer hold the stack frames.
@@ -139,10 +141,16 @@ __device__ __forceinline__ void stamped_payloads(const Ctx& cx, const unsigned l
 __device__ __forceinline__ float* x_slot(const Ctx& cx, int t, int chunk, int vec) {
   return reinterpret_cast<float*>(cx.smem_b) + t * kXFloats + chunk * kChunkK + vec * 4;
 }
+template <bool ROW>
 __device__ __forceinline__ void x_store(const Ctx& cx, int t, int chunk, int vec, const float* f) {
-  float* dst = x_slot(cx, t, chunk, vec);
-  *reinterpret_cast<float4*>(dst) = make_float4(f[0], f[1], f[2], f[3]);
-  *reinterpret_cast<float4*>(dst + 32) = make_float4(f[4], f[5], f[6], f[7]);
+  if constexpr (ROW) {  // one-token row table: fp32 for the CUDA-core consumer
+    float* dst = x_slot(cx, t, chunk, vec);
+    *reinterpret_cast<float4*>(dst) = make_float4(f[0], f[1], f[2], f[3]);
+    *reinterpret_cast<float4*>(dst + 32) = make_float4(f[4], f[5], f[6], f[7]);
+  } else {
+    // mma.sync consumer: bf16 (exact: every operand is a bf16 tensor in the reference), one row of K elements per token
+    *reinterpret_cast<uint4*>(cx.smem_b + t * kXTokenBytes + (chunk * kChunkK + vec * 8) * 2) = pack8(f);
+  }
 }
 
 // RMSNorm fused with staging (K = hidden <= 2048: one 8-element vector per
@@ -152,6 +160,7 @@ __device__ __forceinline__ void x_store(const Ctx& cx, int t, int chunk, int vec
 // residual stream, and normalises x with the two roundings of the Hugging Face
 // RMSNorm.  `wu` is this thread's vector of the norm weight, loaded by the
 // caller before the grid barrier opened.
+template <bool ROW>
 __device__ __noinline__ bool small_stage_norm(const Ctx& cx, const GemmPhase* ph, int mt, int wtid, uint4 wu, uint32_t stamp) {
   const KParams& p = *cx.p;
   const int warp = wtid >> 5, lane = wtid & 31;
@@ -220,7 +229,7 @@ __device__ __noinline__ bool small_stage_norm(const Ctx& cx, const GemmPhase* ph
     if (active) {
 #pragma unroll
       for (int e = 0; e < 8; ++e) f[e] = bf16_round(w[e] * bf16_round(f[e] * r));
-      x_store(cx, t, wtid >> 3, wtid & 7, f);
+      x_store<ROW>(cx, t, wtid >> 3, wtid & 7, f);
     }
   }
   return fresh;
@@ -228,6 +237,7 @@ __device__ __noinline__ bool small_stage_norm(const Ctx& cx, const GemmPhase* ph
 
 // Plain or attention-output operand: K chunks [k0, k0 + count) of every token.  One vector per
 // thread and trip (256 vectors cover a 2048-element slice of one token); kept small on purpose.
+template <bool ROW>
 __device__ __noinline__ bool small_stage_cols(const Ctx& cx, const GemmPhase* ph, int k0, int count, int mt, int wtid,
                                               int nch, uint32_t stamp) {
   const KParams& p = *cx.p;
@@ -269,7 +279,7 @@ __device__ __noinline__ bool small_stage_cols(const Ctx& cx, const GemmPhase* ph
                                             : __ldcg(reinterpret_cast<const uint4*>(activation_row(p, ph, t) + col));
       unpack8(u, f);
     }
-    x_store(cx, t, rem >> 3, rem & 7, f);
+    x_store<ROW>(cx, t, rem >> 3, rem & 7, f);
   }
   return fresh;
 }
@@ -280,15 +290,38 @@ constexpr int kRowSumOffset = kSplitTokens * kXFloats * 4;  // behind the activa
 constexpr int kSmallTileRows = 64;                          // tile height of the small-launch table
 static_assert(kRowSumOffset + 2 * kSmallTileRows * kSplitTokens * 4 <= kBBytes, "row sums do not fit");
 
-template <int T>
+// Cross-warp partial sums of the mma.sync consumer: [warp][accumulator][row][token], behind its bf16 operand.
+constexpr int kPartOffset = 20 * 1024;
+constexpr int kPartFloats = kSmallWarps * 2 * kSmallTileRows * kSplitTokens;
+static_assert(kSplitTokens * kXTokenBytes <= kPartOffset, "activation operand overlaps the partial sums");
+static_assert(kPartOffset + kPartFloats * 4 <= kBBytes, "partial sums do not fit");
+
+// Sum of the eight warps' partials of (accumulator a, row r, token t), in warp order.
+__device__ __forceinline__ float small_row_sum(const float* part, int a, int r, int t) {
+  float v = 0.f;
+#pragma unroll
+  for (int w8 = 0; w8 < kSmallWarps; ++w8) v += part[((w8 * 2 + a) * kSmallTileRows + r) * kSplitTokens + t];
+  return v;
+}
+
+template <int T, bool ROW>
 __device__ __noinline__ void small_finish_row(const Ctx& cx, const GemmPhase* ph, int seg, int slice, int n, int r,
                                               uint32_t* bits) {
-  const float* sums = reinterpret_cast<const float*>(cx.smem_b + kRowSumOffset);
   float v[2][T];
+  if constexpr (ROW) {
+    const float* sums = reinterpret_cast<const float*>(cx.smem_b + kRowSumOffset);
 #pragma unroll
-  for (int t = 0; t < T; ++t) {
-    v[0][t] = sums[r * kSplitTokens + t];
-    v[1][t] = sums[(kSmallTileRows + r) * kSplitTokens + t];
+    for (int t = 0; t < T; ++t) {
+      v[0][t] = sums[r * kSplitTokens + t];
+      v[1][t] = sums[(kSmallTileRows + r) * kSplitTokens + t];
+    }
+  } else {
+    const float* part = reinterpret_cast<const float*>(cx.smem_b + kPartOffset);
+#pragma unroll
+    for (int t = 0; t < T; ++t) {
+      v[0][t] = small_row_sum(part, 0, r, t);
+      v[1][t] = ph->nacc == 2 ? small_row_sum(part, 1, r, t) : 0.f;
+    }
   }
   if (ph->ll) {  // the caller sends the rounded outputs as stamped words
     if (ph->epi == EPI_ROWRES) {  // new residual = residual + bf16(projection)
@@ -388,8 +421,8 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
       if (per_unit || unit == cx.cta) {
         if (unit != cx.cta) small_sync();  // the previous unit has finished reading the operand
         // a normalising phase that opens a layer (or the lm_head) reads what the previous layer stamped
-        if (ph->bmode == B_NORM) ok = small_stage_norm(cx, ph, T, wtid, wu, (gp & 3) == 0 ? stamp - 1u : stamp) && ok;
-        else ok = small_stage_cols(cx, ph, slice * kslice, kslice, T, wtid, nch, stamp) && ok;
+        if (ph->bmode == B_NORM) ok = small_stage_norm<true>(cx, ph, T, wtid, wu, (gp & 3) == 0 ? stamp - 1u : stamp) && ok;
+        else ok = small_stage_cols<true>(cx, ph, slice * kslice, kslice, T, wtid, nch, stamp) && ok;
         small_sync();
         if (unit == cx.cta) trace_event(cx, wtid, EV_B_STAGED);
       }
@@ -529,7 +562,7 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
         uint32_t bits[T];
 #pragma unroll
         for (int t = 0; t < T; ++t) bits[t] = 0u;
-        if (mine) small_finish_row<T>(cx, ph, seg, slice, row0 + wtid, wtid, bits);
+        if (mine) small_finish_row<T, true>(cx, ph, seg, slice, row0 + wtid, wtid, bits);
         if (ph->ll) {
           // Rows 2k and 2k + 1 (even tile height, even segment sizes) share a word:
           // {stamp, bf16 of the odd column, bf16 of the even column}, one 64-bit store.
@@ -572,7 +605,7 @@ __device__ __noinline__ bool small_gemm_rows(const Ctx& cx, int gp, SmallState& 
 #pragma unroll 1
     for (int unit = cx.cta; unit < nunits; unit += cx.grid) {
       if (unit != cx.cta) small_sync();
-      ok = small_stage_cols(cx, ph, 0, kc, 1, wtid, nch, stamp) && ok;
+      ok = small_stage_cols<true>(cx, ph, 0, kc, 1, wtid, nch, stamp) && ok;
       small_sync();
       if (unit == cx.cta) trace_event(cx, wtid, EV_B_STAGED);
       const int row0 = unit * rows;
@@ -679,14 +712,182 @@ __device__ __noinline__ bool small_gemm_rows(const Ctx& cx, int gp, SmallState& 
   return ok;
 }
 
-template <int T>
+// The same projection phase for every launch that is not the one-token row table.
+//
+// The weights are consumed by warp-level mma.sync (m16n8k16, bf16 in, fp32 out): one instruction
+// multiplies 16 weight rows x 16 K-elements by up to eight token columns, where the CUDA-core loop
+// this replaces needed 17 instructions per lane for 8 weights and kept the consumer warps, not HBM,
+// the limit of a K loop.  A weight copy holds `kb` K chunks of the tile's rows, each chunk
+// [rows][64] bf16 with the 128-byte swizzle (one three-dimensional TMA box); ldmatrix.x4 reads a
+// 16 x 16 fragment from it without bank conflicts.  The eight warps split the K steps of a copy
+// (warp w takes steps w, w + 8, ...) and keep fp32 accumulators for all row tiles of the unit; at
+// the end of the unit the warps' partial sums meet in shared memory and are added in warp order.
+// The token operand is bf16 in shared memory ([token][K], exact: every operand is a bf16 tensor in
+// the reference), read as B fragments with two 32-bit loads per K step.
+// Accumulation order depends only on the CTA's rotated chunk order: no dependence on timing.
+template <int T, int NACC>
+__device__ __noinline__ bool small_gemm_mma(const Ctx& cx, int gp, SmallState& st, int wtid, uint4 wu, int nch, uint32_t stamp) {
+  const GemmPhase* ph = &cx.misc->phase[gp & 1];
+  const int nunits = ph->nunits, rows = ph->rows, ksplit = ph->ksplit, kslice = ph->kslice, gran = ph->gran;
+  const bool per_unit = ksplit > 1;
+  const int warp = wtid >> 5, lane = wtid & 31;
+  const int kb = ph->kb;                          // K chunks per copy
+  const int ksteps = kb * 4;                      // 16-element K steps per copy
+  const int row_tiles = (rows + 15) >> 4;         // <= 4
+  const uint32_t chunk_bytes = static_cast<uint32_t>(rows) * 128u;
+  const int rot = k_rotation(cx.cta, cx.grid, kslice / kb) * kb;
+  const uint32_t ring_base = smem_u32(cx.smem_a);
+  const int ring_granules = cx.p->small_ring;
+  // B fragment of this lane: token lane / 4, K elements 2 * (lane % 4) + {0, 1} and + 8 of a step
+  const bool has_token = (lane >> 2) < T;
+  const uint32_t x_lane = smem_u32(cx.smem_b) + (lane >> 2) * kXTokenBytes + (lane & 3) * 4;
+  // A fragment: lane l addresses row (l % 8) + 8 * ((l / 8) % 2) of a row tile, 16-byte unit l / 16 of the step
+  const uint32_t a_lane = static_cast<uint32_t>((lane & 7) + ((lane >> 3) & 1) * 8) * 128u;
+  const uint32_t a_unit_kk = static_cast<uint32_t>((warp & 3) * 2 + (lane >> 4));
+  const uint32_t x_lane_kk = x_lane + static_cast<uint32_t>(warp & 3) * 32u;
+  float* part = reinterpret_cast<float*>(cx.smem_b + kPartOffset);
+  int head = st.head, seq = st.seq;
+  bool ok = true;
+  if (cx.cta < nunits) {
+    trace_event(cx, wtid, EV_PHASE_ENTER);
+#pragma unroll 1
+    for (int unit = cx.cta; unit < nunits; unit += cx.grid) {
+      const int tile = unit / ksplit, slice = unit - tile * ksplit;
+      if (per_unit || unit == cx.cta) {
+        if (unit != cx.cta) small_sync();  // the previous unit has finished reading the operand
+        // a normalising phase that opens a layer (or the lm_head) reads what the previous layer stamped
+        if (ph->bmode == B_NORM) ok = small_stage_norm<false>(cx, ph, T, wtid, wu, (gp & 3) == 0 ? stamp - 1u : stamp) && ok;
+        else ok = small_stage_cols<false>(cx, ph, slice * kslice, kslice, T, wtid, nch, stamp) && ok;
+        small_sync();
+        if (unit == cx.cta) trace_event(cx, wtid, EV_B_STAGED);
+      }
+      int seg, row0;
+      tile_origin(ph, tile, seg, row0);
+      // Two accumulator sets per row tile (K steps alternate between them), so that consecutive
+      // mma.sync instructions do not wait for one another; they are added when the unit ends.
+      float acc[NACC][4][2][4];
+#pragma unroll
+      for (int a = 0; a < NACC; ++a)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[a][i][0][e] = acc[a][i][1][e] = 0.f;
+      int slot = rot;
+      // The K loop, instantiated per number of 16-row tiles: no branch inside, so the fragment loads of
+      // a group of K steps issue back to back ahead of the MMAs.  A step past the copy's last one
+      // re-reads the last step's fragment against a zero token operand.
+      auto k_loop = [&](auto tiles_tag) {
+        constexpr int RT = decltype(tiles_tag)::value;
+        constexpr int U = RT == 1 ? 4 : 2;  // K steps in flight per warp
+#pragma unroll 1
+        for (int k0 = 0; k0 < kslice; k0 += kb) {
+#pragma unroll
+          for (int a = 0; a < NACC; ++a) {
+            if (head + gran > ring_granules) head = 0;
+            const uint32_t base = ring_base + head * kGranule;
+            head += gran;
+            const uint32_t bar = seq % kChunkBars;
+            // After a failed wait the warp keeps walking the schedule without waiting, so that
+            // every consumer still reaches the same block-wide barriers and leaves together.
+            const bool got = ok && wait_mbar(cx, smem_u32(&cx.misc->full[bar]), (seq / kChunkBars) & 1, SITE_MMA_FULL, gp);
+            ok = __all_sync(0xffffffffu, got);
+            if (k0 == 0 && a == 0 && unit == cx.cta) trace_event(cx, wtid, EV_FIRST_COPY);
+            // Warp w takes K steps w, w + 8, ...: the step inside a chunk (w % 4) is fixed, the chunk
+            // advances by two per step, so a fragment address is the lane's constant plus chunk terms.
+            const uint32_t x_copy = x_lane_kk + static_cast<uint32_t>(slot) * 128u;
+            const uint32_t a_copy = base + a_lane;
+#pragma unroll 1
+            for (int c0 = warp >> 2; c0 < kb; c0 += 2 * U) {
+              uint32_t bf[U][2], af[U][RT][4];
+#pragma unroll
+              for (int j = 0; j < U; ++j) {
+                const int c = c0 + 2 * j;
+                const bool live = has_token && c < kb;
+                const uint32_t ce = static_cast<uint32_t>(min(c, kb - 1));
+                bf[j][0] = live ? lds_u32(x_copy + ce * 128u) : 0u;
+                bf[j][1] = live ? lds_u32(x_copy + ce * 128u + 16u) : 0u;
+                const uint32_t chunk_addr = a_copy + ce * chunk_bytes;
+                // the 128-byte swizzle exchanges the 16-byte units of a row by the row's position in its 1 KiB atom
+                const uint32_t swz = (((chunk_addr >> 7) & 7u) ^ a_unit_kk) << 4;
+#pragma unroll
+                for (int i = 0; i < RT; ++i) ldmatrix_x4(af[j][i], chunk_addr + static_cast<uint32_t>(i) * 2048u + swz);
+              }
+#pragma unroll
+              for (int j = 0; j < U; ++j)
+#pragma unroll
+                for (int i = 0; i < RT; ++i) mma_bf16_16816(acc[a][i][j & 1], af[j][i], bf[j][0], bf[j][1]);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&cx.misc->empty[bar]));
+            seq += 1;
+          }
+          slot = (slot + kb == kslice) ? 0 : slot + kb;
+        }
+      };
+      switch (row_tiles) {
+        case 1: k_loop(IntTag<1>{}); break;
+        case 2: k_loop(IntTag<2>{}); break;
+        case 3: k_loop(IntTag<3>{}); break;
+        default: k_loop(IntTag<4>{}); break;
+      }
+#pragma unroll
+      for (int a = 0; a < NACC; ++a)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[a][i][0][e] += acc[a][i][1][e];
+      if (unit == cx.cta) trace_event(cx, wtid, EV_FIRST_ACC);
+      if (unit != cx.cta) small_sync();  // the previous unit's rows have been finished: `part` is free
+      // D fragment: c0, c1 = row lane / 4, tokens 2 * (lane % 4) + {0, 1}; c2, c3 = eight rows further down
+#pragma unroll
+      for (int a = 0; a < NACC; ++a)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int r = i * 16 + (lane >> 2) + (e >> 1) * 8;
+            const int t = (lane & 3) * 2 + (e & 1);
+            if (i < row_tiles && t < T) part[((warp * 2 + a) * kSmallTileRows + r) * kSplitTokens + t] = acc[a][i][0][e];
+          }
+      small_sync();
+      {
+        const bool mine = wtid < rows && row0 + wtid < ph->n[seg];
+        uint32_t bits[T];
+#pragma unroll
+        for (int t = 0; t < T; ++t) bits[t] = 0u;
+        if (mine) small_finish_row<T, false>(cx, ph, seg, slice, row0 + wtid, wtid, bits);
+        if (ph->ll) {
+          // Rows 2k and 2k + 1 (even tile height, even segment sizes) share a word:
+          // {stamp, bf16 of the odd column, bf16 of the even column}, one 64-bit store.
+          const int col = ph->out_col[seg] + row0 + wtid;
+#pragma unroll
+          for (int t = 0; t < T; ++t) {
+            const uint32_t other = __shfl_xor_sync(0xffffffffu, bits[t], 1);
+            if (mine && !(wtid & 1))
+              st_relaxed_u64(ph->ll_dst + static_cast<size_t>(t) * ph->ll_ld + (col >> 1),
+                             (static_cast<unsigned long long>(stamp) << 32) | (other << 16) | bits[t]);
+          }
+        }
+      }
+    }
+    trace_event(cx, wtid, EV_PHASE_DONE);
+  }
+  st.head = head;
+  st.seq = seq;
+  return ok;
+}
+
+template <int T, bool ROW>
 __device__ __forceinline__ bool small_gemm_t(const Ctx& cx, int gp, SmallState& st, int wtid, uint4 wu, int nch,
                                              uint32_t stamp) {
-  if constexpr (T == 1) {
+  if constexpr (ROW) {  // one-token row table: CUDA-core consumer over plain rows
     if (cx.misc->phase[gp & 1].bulk) return small_gemm_rows(cx, gp, st, wtid, nch, stamp);
+    return cx.misc->phase[gp & 1].nacc == 2 ? small_gemm<1, 2>(cx, gp, st, wtid, wu, nch, stamp)
+                                            : small_gemm<1, 1>(cx, gp, st, wtid, wu, nch, stamp);
+  } else {
+    return cx.misc->phase[gp & 1].nacc == 2 ? small_gemm_mma<T, 2>(cx, gp, st, wtid, wu, nch, stamp)
+                                            : small_gemm_mma<T, 1>(cx, gp, st, wtid, wu, nch, stamp);
   }
-  return cx.misc->phase[gp & 1].nacc == 2 ? small_gemm<T, 2>(cx, gp, st, wtid, wu, nch, stamp)
-                                          : small_gemm<T, 1>(cx, gp, st, wtid, wu, nch, stamp);
 }
 
 // Decode attention with RoPE, in-kernel KV append and a context split across
@@ -1122,6 +1323,9 @@ __device__ __noinline__ void small_producer(const Ctx& cx) {
           mbar_expect_tx(full, copy_bytes);
           bulk_load_1d(smem_u32(cx.smem_a + start * kGranule), ph->w[seg] + static_cast<size_t>(row0 + r) * ph->k, copy_bytes, full,
                        policy);
+        } else if (ph->map3d) {  // mma.sync consumer: 64 elements x the tile's rows x kb chunks, each chunk 128-byte swizzled
+          mbar_expect_tx(full, bytes);
+          tma_load_3d(smem_u32(cx.smem_a + start * kGranule), map, 0, row0, kbase + k, full, policy);
         } else {
           mbar_expect_tx(full, bytes);
           tma_load_2d(smem_u32(cx.smem_a + start * kGranule), map, (kbase + k) * kChunkK, row0, full, policy);
@@ -1156,11 +1360,11 @@ __device__ __forceinline__ uint4 small_norm_weight(const Ctx& cx, int gp, int wt
 }
 
 // One projection phase; the next phase's descriptor is requested first and stored last.
-template <int T>
+template <int T, bool ROW>
 __device__ __forceinline__ bool small_project(const Ctx& cx, SmallState& st, int gp, int nch, uint4 wu, int wtid,
                                               uint32_t stamp) {
   const uint32_t word = small_phase_word(cx, gp + 1, wtid);
-  const bool ok = small_gemm_t<T>(cx, gp, st, wtid, wu, nch, stamp);
+  const bool ok = small_gemm_t<T, ROW>(cx, gp, st, wtid, wu, nch, stamp);
   small_phase_store(cx, gp + 1, wtid, word);
   return ok;
 }
@@ -1176,7 +1380,7 @@ __device__ __forceinline__ bool small_close(const Ctx& cx, SmallState& st, int n
 
 // One kernel per token count: code that is compiled in but never runs still costs instruction-cache
 // reach (a build with all four token counts in one kernel measured 8 % slower at one token).
-template <int T>
+template <int T, bool ROW>
 __device__ void small_worker_loop(const Ctx& cx, int wtid) {
   const KParams& p = *cx.p;
   SmallState st;
@@ -1198,7 +1402,7 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
   // One projection phase: the next descriptor is fetched while this phase runs.
   bool ok = true;  // per warp; made block-uniform by every close()
   auto project = [&](int gp, int nch) {
-    ok = small_project<T>(cx, st, gp, nch, wu, wtid, p.att_epoch + static_cast<uint32_t>(gp >> 2) + 1u) && ok;
+    ok = small_project<T, ROW>(cx, st, gp, nch, wu, wtid, p.att_epoch + static_cast<uint32_t>(gp >> 2) + 1u) && ok;
   };
   auto close = [&](int next_gp) -> bool { return small_close(cx, st, next_gp, wu, ok, wtid); };
   // The cached K and V rows of this CTA's attention units do not depend on this step: ask L2 for
@@ -1229,7 +1433,7 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
     }
   };
   prefetch_kv(0);
-  if (p.rowmode) {
+  if constexpr (ROW) {
     // One-token row table: every hand-off between phases travels as stamped words, so a layer needs no grid
     // barrier; block barriers only pass the shared memory from one phase to the next.
 #pragma unroll 1
@@ -1266,7 +1470,7 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
       for (int layer = wtid; layer < p.layers; layer += kSmallWorkers) *p.len[layer] = cx.misc->len_s[layer] + 1;
     if (p.sample) greedy_sample<1, kSmallWorkers>(cx, wtid, reinterpret_cast<float*>(cx.smem_b));
     return;
-  }
+  } else {
   for (int layer = 0; layer < p.layers; ++layer) {
     const int gp = layer * 4;
     const bool handoff = cx.misc->phase[gp & 1].ll != 0;  // same for every layer and CTA
@@ -1318,12 +1522,13 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
     if (!small_wait(cx, st, wtid)) return;
     greedy_sample<1, kSmallWorkers>(cx, wtid, reinterpret_cast<float*>(cx.smem_b));
   }
+  }
 }
 
 // ---------------------------------------------------------------------------
 // the kernel
 
-template <int T>
+template <int T, bool ROW>
 __global__ void __launch_bounds__(kSmallThreads, 1) megakernel_small(const __grid_constant__ KParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -1378,7 +1583,7 @@ __global__ void __launch_bounds__(kSmallThreads, 1) megakernel_small(const __gri
   } else if (warp == 0) {
     if (tid == 0) small_producer(cx);
   } else {
-    small_worker_loop<T>(cx, tid - 32);
+    small_worker_loop<T, ROW>(cx, tid - 32);
   }
 }
 

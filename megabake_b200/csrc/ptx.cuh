@@ -210,6 +210,10 @@ __device__ __forceinline__ void mma_bf16_16816(float* acc, const uint32_t* a, ui
 }
 // Four 8 x 8 bf16 matrices from shared memory, transposed on the way: lane l gives the address of row l % 8 of
 // matrix l / 8; thread (g = lane / 4, t = lane % 4) receives elements [2t, 2t + 1][g] of each matrix.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t* r, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
