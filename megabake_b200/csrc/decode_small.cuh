@@ -69,7 +69,7 @@ __device__ __forceinline__ void small_arrive(const Ctx& cx, SmallState& st, int 
 
 __device__ __forceinline__ bool small_wait(const Ctx& cx, SmallState& st, int wtid) {
   if (wtid == 0) {
-    const uint32_t target = cx.p->epoch + st.passed * static_cast<uint32_t>(cx.grid);
+    const uint32_t target = cx.misc->epoch + st.passed * static_cast<uint32_t>(cx.grid);
     uint32_t spins = 0;
     while (static_cast<int32_t>(ld_relaxed_u32(&cx.ctrl->barrier) - target) < 0) {
       if ((++spins & 255u) == 0 && give_up(cx, SITE_GRID_BARRIER, static_cast<int>(st.passed))) {
@@ -87,11 +87,11 @@ __device__ __forceinline__ bool small_wait(const Ctx& cx, SmallState& st, int wt
 // The next phase's descriptor: requested when a phase starts, put into shared memory when the
 // phase has finished (a warp stalls on the store until its load has returned).
 __device__ __forceinline__ uint32_t small_phase_word(const Ctx& cx, int gp, int wtid) {
-  if (gp >= cx.p->n_gemm || wtid >= static_cast<int>(sizeof(GemmPhase) / 4)) return 0u;
-  return __ldg(reinterpret_cast<const uint32_t*>(cx.p->phases + gp) + wtid);
+  if (gp >= cx.misc->n_gemm || wtid >= static_cast<int>(sizeof(GemmPhase) / 4)) return 0u;
+  return __ldg(reinterpret_cast<const uint32_t*>(cx.misc->phases + gp) + wtid);
 }
 __device__ __forceinline__ void small_phase_store(const Ctx& cx, int gp, int wtid, uint32_t word) {
-  if (gp >= cx.p->n_gemm || wtid >= static_cast<int>(sizeof(GemmPhase) / 4)) return;
+  if (gp >= cx.misc->n_gemm || wtid >= static_cast<int>(sizeof(GemmPhase) / 4)) return;
   reinterpret_cast<uint32_t*>(&cx.misc->phase[gp & 1])[wtid] = word;
 }
 static_assert(sizeof(GemmPhase) / 4 <= kSmallWorkers, "one word of the phase descriptor per consumer thread");
@@ -138,18 +138,18 @@ __device__ __forceinline__ void stamped_payloads(const Ctx& cx, const unsigned l
 // fp32 operand layout: per token kXFloats floats; inside a 64-element K chunk the
 // eight 8-element vectors are stored as two float4 halves, 128 bytes apart, so
 // that the eight lanes sharing a weight row read 128 contiguous bytes per load.
-__device__ __forceinline__ float* x_slot(const Ctx& cx, int t, int chunk, int vec) {
-  return reinterpret_cast<float*>(cx.smem_b) + t * kXFloats + chunk * kChunkK + vec * 4;
+__device__ __forceinline__ float* x_slot(uint8_t* region, int t, int chunk, int vec) {
+  return reinterpret_cast<float*>(region) + t * kXFloats + chunk * kChunkK + vec * 4;
 }
 template <bool ROW>
-__device__ __forceinline__ void x_store(const Ctx& cx, int t, int chunk, int vec, const float* f) {
+__device__ __forceinline__ void x_store(uint8_t* region, int t, int chunk, int vec, const float* f) {
   if constexpr (ROW) {  // one-token row table: fp32 for the CUDA-core consumer
-    float* dst = x_slot(cx, t, chunk, vec);
+    float* dst = x_slot(region, t, chunk, vec);
     *reinterpret_cast<float4*>(dst) = make_float4(f[0], f[1], f[2], f[3]);
     *reinterpret_cast<float4*>(dst + 32) = make_float4(f[4], f[5], f[6], f[7]);
   } else {
     // mma.sync consumer: bf16 (exact: every operand is a bf16 tensor in the reference), one row of K elements per token
-    *reinterpret_cast<uint4*>(cx.smem_b + t * kXTokenBytes + (chunk * kChunkK + vec * 8) * 2) = pack8(f);
+    *reinterpret_cast<uint4*>(region + t * kXTokenBytes + (chunk * kChunkK + vec * 8) * 2) = pack8(f);
   }
 }
 
@@ -164,9 +164,19 @@ template <bool ROW>
 __device__ __noinline__ bool small_stage_norm(const Ctx& cx, const GemmPhase* ph, int mt, int wtid, uint4 wu, uint32_t stamp) {
   const KParams& p = *cx.p;
   const int warp = wtid >> 5, lane = wtid & 31;
-  const int nvec = ph->k / 8;
+  // Everything the token loop needs, read once: the polls below are compiler barriers for memory, and the
+  // context, the parameters and the descriptor would otherwise be read again behind each of them.
+  const int k = ph->k, nvec = k / 8;
   const int parts = ph->add_parts;
   const int writers = min(cx.grid, ph->nunits);
+  const int cta = cx.cta, m = p.m;
+  const float eps = p.eps;
+  const unsigned long long* ll_src = ph->ll_src;
+  const int ll_src_ld = ph->ll_src_ld;
+  const float* partial = ph->partial;
+  bf16* h_out = ph->h_out;
+  uint8_t* region = cx.smem_b;
+  float (*sred)[8] = cx.misc->sred;
   const bool active = wtid < nvec;
   bool fresh = true;
   float w[8];
@@ -174,11 +184,11 @@ __device__ __noinline__ bool small_stage_norm(const Ctx& cx, const GemmPhase* ph
   for (int t = 0; t < mt; ++t) {
     float f[8];
     uint4 xu = make_uint4(0, 0, 0, 0);
-    if (active && ph->ll_src != nullptr) {
+    if (active && ll_src != nullptr) {
       // the residual stream as stamped bf16 pairs (one-token row table): waiting for the stamps of the
       // previous projection's epilogues replaces the grid barrier; nothing is added, nothing written back
       uint32_t pair[4];
-      stamped_payloads<4>(cx, ph->ll_src + static_cast<size_t>(t) * ph->ll_src_ld + wtid * 4, stamp, fresh, pair);
+      stamped_payloads<4>(cx, ll_src + static_cast<size_t>(t) * ll_src_ld + wtid * 4, stamp, fresh, pair);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         f[2 * i] = __uint_as_float(pair[i] << 16);
@@ -191,7 +201,7 @@ __device__ __noinline__ bool small_stage_norm(const Ctx& cx, const GemmPhase* ph
 #pragma unroll
       for (int s8 = 0; s8 < kMaxSplit; ++s8) {
         if (s8 < parts) {
-          const float4* part = reinterpret_cast<const float4*>(ph->partial + (static_cast<size_t>(s8) * p.m + t) * ph->k) + wtid * 2;
+          const float4* part = reinterpret_cast<const float4*>(partial + (static_cast<size_t>(s8) * m + t) * k) + wtid * 2;
           lo[s8] = __ldcg(part);
           hi[s8] = __ldcg(part + 1);
         }
@@ -210,8 +220,8 @@ __device__ __noinline__ bool small_stage_norm(const Ctx& cx, const GemmPhase* ph
         for (int e = 0; e < 8; ++e) f[e] = bf16_round(f[e] + bf16_round(acc[e]));
         xu = pack8(f);
       }
-      if (ph->h_out && (wtid * writers) / nvec == cx.cta)
-        __stcg(reinterpret_cast<uint4*>(ph->h_out + static_cast<size_t>(t) * ph->k) + wtid, xu);
+      if (h_out && (wtid * writers) / nvec == cta)
+        __stcg(reinterpret_cast<uint4*>(h_out + static_cast<size_t>(t) * k) + wtid, xu);
     } else {
 #pragma unroll
       for (int e = 0; e < 8; ++e) f[e] = 0.f;
@@ -220,16 +230,16 @@ __device__ __noinline__ bool small_stage_norm(const Ctx& cx, const GemmPhase* ph
 #pragma unroll
     for (int e = 0; e < 8; ++e) sum = fmaf(f[e], f[e], sum);
     sum = warp_sum(sum);
-    if (lane == 0) cx.misc->sred[t][warp] = sum;
+    if (lane == 0) sred[t][warp] = sum;
     small_sync();
     float total = 0.f;
 #pragma unroll
-    for (int i = 0; i < kSmallWarps; ++i) total += cx.misc->sred[t][i];
-    const float r = 1.0f / sqrtf(total / static_cast<float>(ph->k) + p.eps);
+    for (int i = 0; i < kSmallWarps; ++i) total += sred[t][i];
+    const float r = 1.0f / sqrtf(total / static_cast<float>(k) + eps);
     if (active) {
 #pragma unroll
       for (int e = 0; e < 8; ++e) f[e] = bf16_round(w[e] * bf16_round(f[e] * r));
-      x_store<ROW>(cx, t, wtid >> 3, wtid & 7, f);
+      x_store<ROW>(region, t, wtid >> 3, wtid & 7, f);
     }
   }
   return fresh;
@@ -241,6 +251,11 @@ template <bool ROW>
 __device__ __noinline__ bool small_stage_cols(const Ctx& cx, const GemmPhase* ph, int k0, int count, int mt, int wtid,
                                               int nch, uint32_t stamp) {
   const KParams& p = *cx.p;
+  // read once: every poll below is a compiler barrier for memory
+  const unsigned long long* ll_src = ph->ll_src;
+  const int ll_src_ld = ph->ll_src_ld, bmode = ph->bmode;
+  const int head_dim = p.head_dim, q_heads = p.q_heads;
+  uint8_t* region = cx.smem_b;
   const int per_token = count * 8;
   const int items = per_token * mt;
   bool fresh = true;
@@ -249,9 +264,9 @@ __device__ __noinline__ bool small_stage_cols(const Ctx& cx, const GemmPhase* ph
     const int t = item / per_token, rem = item - t * per_token;
     const int col = (k0 + (rem >> 3)) * kChunkK + (rem & 7) * 8;
     float f[8];
-    if (ph->ll_src != nullptr && ph->bmode == B_PLAIN) {
+    if (ll_src != nullptr && bmode == B_PLAIN) {
       // stamped bf16 pairs written by the producing phase's epilogues: waiting for the stamps is the synchronisation
-      const unsigned long long* words = ph->ll_src + static_cast<size_t>(t) * ph->ll_src_ld + (col >> 1);
+      const unsigned long long* words = ll_src + static_cast<size_t>(t) * ll_src_ld + (col >> 1);
       uint32_t pair[4];
       stamped_payloads<4>(cx, words, stamp, fresh, pair);
 #pragma unroll
@@ -259,27 +274,27 @@ __device__ __noinline__ bool small_stage_cols(const Ctx& cx, const GemmPhase* ph
         f[2 * i] = __uint_as_float(pair[i] << 16);
         f[2 * i + 1] = __uint_as_float(pair[i] & 0xFFFF0000u);
       }
-    } else if (ph->ll_src != nullptr) {
+    } else if (ll_src != nullptr) {
       // stamped fp32 chunk partials of the attention phase, summed in chunk order and rounded once
-      const int head = col / p.head_dim, d = col - head * p.head_dim;
-      const unsigned long long* part = ph->ll_src + (static_cast<size_t>(t) * p.q_heads + head) * kMaxChunks * p.head_dim + d;
+      const int head = col / head_dim, d = col - head * head_dim;
+      const unsigned long long* part = ll_src + (static_cast<size_t>(t) * q_heads + head) * kMaxChunks * head_dim + d;
 #pragma unroll
       for (int e = 0; e < 8; ++e) f[e] = 0.f;
 #pragma unroll 1
       for (int c = 0; c < nch; ++c) {
         uint32_t bits[8];
-        stamped_payloads<8>(cx, part + c * p.head_dim, stamp, fresh, bits);
+        stamped_payloads<8>(cx, part + c * head_dim, stamp, fresh, bits);
 #pragma unroll
         for (int e = 0; e < 8; ++e) f[e] += __uint_as_float(bits[e]);
       }
 #pragma unroll
       for (int e = 0; e < 8; ++e) f[e] = bf16_round(f[e]);
     } else {
-      const uint4 u = (ph->bmode == B_ATTN) ? attention_vec(p, t, col, nch)
+      const uint4 u = (bmode == B_ATTN) ? attention_vec(p, t, col, nch)
                                             : __ldcg(reinterpret_cast<const uint4*>(activation_row(p, ph, t) + col));
       unpack8(u, f);
     }
-    x_store<ROW>(cx, t, rem >> 3, rem & 7, f);
+    x_store<ROW>(region, t, rem >> 3, rem & 7, f);
   }
   return fresh;
 }
@@ -411,20 +426,24 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
   const int ring_granules = cx.p->small_ring;
   const uint32_t x_base = smem_u32(cx.smem_b) + ((cl >> 3) * kChunkK + (cl & 7) * 4) * 4;
   float* sums = reinterpret_cast<float*>(cx.smem_b + kRowSumOffset);
+  // barrier addresses and loop bounds in registers: the waits below are compiler barriers for memory
+  const uint32_t full0 = smem_u32(&cx.misc->full[0]), empty0 = smem_u32(&cx.misc->empty[0]);
+  const int my_cta = cx.cta, grid = cx.grid;
+  const bool tracing = wtid == 0 && cx.misc->trace_on != 0;
   int head = st.head, seq = st.seq;
   bool ok = true;
-  if (cx.cta < nunits) {
-    trace_event(cx, wtid, EV_PHASE_ENTER);
+  if (my_cta < nunits) {
+    if (tracing) trace_event(cx, wtid, EV_PHASE_ENTER);
 #pragma unroll 1
-    for (int unit = cx.cta; unit < nunits; unit += cx.grid) {
+    for (int unit = my_cta; unit < nunits; unit += grid) {
       const int tile = unit / ksplit, slice = unit - tile * ksplit;
-      if (per_unit || unit == cx.cta) {
-        if (unit != cx.cta) small_sync();  // the previous unit has finished reading the operand
+      if (per_unit || unit == my_cta) {
+        if (unit != my_cta) small_sync();  // the previous unit has finished reading the operand
         // a normalising phase that opens a layer (or the lm_head) reads what the previous layer stamped
         if (ph->bmode == B_NORM) ok = small_stage_norm<true>(cx, ph, T, wtid, wu, (gp & 3) == 0 ? stamp - 1u : stamp) && ok;
         else ok = small_stage_cols<true>(cx, ph, slice * kslice, kslice, T, wtid, nch, stamp) && ok;
         small_sync();
-        if (unit == cx.cta) trace_event(cx, wtid, EV_B_STAGED);
+        if (tracing && unit == my_cta) trace_event(cx, wtid, EV_B_STAGED);
       }
       int seg, row0;
       tile_origin(ph, tile, seg, row0);
@@ -462,9 +481,9 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
           const uint32_t bar = seq % kChunkBars;
           // After a failed wait the warp keeps walking the schedule without waiting, so that
           // every consumer still reaches the same block-wide barriers and leaves together.
-          const bool got = ok && wait_mbar(cx, smem_u32(&cx.misc->full[bar]), (seq / kChunkBars) & 1, SITE_MMA_FULL, gp);
+          const bool got = ok && wait_mbar(cx, full0 + bar * 8u, (seq / kChunkBars) & 1, SITE_MMA_FULL, gp);
           ok = __all_sync(0xffffffffu, got);
-          if (k0 == 0 && a == 0 && unit == cx.cta) trace_event(cx, wtid, EV_FIRST_COPY);
+          if (tracing && k0 == 0 && a == 0 && unit == my_cta) trace_event(cx, wtid, EV_FIRST_COPY);
           if constexpr (ITERS > 0) {
             small_fma_rows<T, ITERS>(base, xf, acc[a]);
           } else {
@@ -481,7 +500,7 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
             }
           }
           __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&cx.misc->empty[bar]));
+          if (lane == 0) mbar_arrive(empty0 + bar * 8u);
           seq += 1;
         }
         slot = (slot + kb == kslice) ? 0 : slot + kb;
@@ -501,8 +520,8 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
       } else {
         k_loop(IntTag<0>{});
       }
-      if (unit == cx.cta) trace_event(cx, wtid, EV_FIRST_ACC);
-      if (unit != cx.cta) small_sync();  // the previous unit's rows have been finished: `sums` is free
+      if (tracing && unit == my_cta) trace_event(cx, wtid, EV_FIRST_ACC);
+      if (unit != my_cta) small_sync();  // the previous unit's rows have been finished: `sums` is free
       if (lpr == 32) {
         // A row spans the warp: halve the rows a lane carries at each exchange (16, 8, 4), then add
         // the last four lanes; 9 shuffles for eight rows instead of 40.  Lane l with (l & 3) == 0
@@ -577,7 +596,7 @@ __device__ __noinline__ bool small_gemm(const Ctx& cx, int gp, SmallState& st, i
         }
       }
     }
-    trace_event(cx, wtid, EV_PHASE_DONE);
+    if (tracing) trace_event(cx, wtid, EV_PHASE_DONE);
   }
   st.head = head;
   st.seq = seq;
@@ -598,16 +617,21 @@ __device__ __noinline__ bool small_gemm_rows(const Ctx& cx, int gp, SmallState& 
   const int ring_granules = cx.p->small_ring;
   const uint32_t row_bytes = static_cast<uint32_t>(ph->k) * 2u;
   float* sums = reinterpret_cast<float*>(cx.smem_b + kRowSumOffset);   // [row][warp] here
+  // barrier addresses and loop bounds in registers: the waits below are compiler barriers for memory
+  const uint32_t full0 = smem_u32(&cx.misc->full[0]), empty0 = smem_u32(&cx.misc->empty[0]);
+  const int my_cta = cx.cta, grid = cx.grid;
+  const bool tracing = wtid == 0 && cx.misc->trace_on != 0;
+  const float* const xsrc = reinterpret_cast<const float*>(cx.smem_b);
   int head = st.head, seq = st.seq;
   bool ok = true;
-  if (cx.cta < nunits) {
-    trace_event(cx, wtid, EV_PHASE_ENTER);
+  if (my_cta < nunits) {
+    if (tracing) trace_event(cx, wtid, EV_PHASE_ENTER);
 #pragma unroll 1
-    for (int unit = cx.cta; unit < nunits; unit += cx.grid) {
-      if (unit != cx.cta) small_sync();
+    for (int unit = my_cta; unit < nunits; unit += grid) {
+      if (unit != my_cta) small_sync();
       ok = small_stage_cols<true>(cx, ph, 0, kc, 1, wtid, nch, stamp) && ok;
       small_sync();
-      if (unit == cx.cta) trace_event(cx, wtid, EV_B_STAGED);
+      if (tracing && unit == my_cta) trace_event(cx, wtid, EV_B_STAGED);
       const int row0 = unit * rows;
       const int tile_rows = min(rows, ph->n[0] - row0);
       float xr[4][8];
@@ -615,7 +639,7 @@ __device__ __noinline__ bool small_gemm_rows(const Ctx& cx, int gp, SmallState& 
       for (int j = 0; j < 4; ++j) {
         const int v = wtid + j * kSmallWorkers;
         if (v < kvecs) {
-          const float* src = reinterpret_cast<const float*>(cx.smem_b) + (v >> 3) * kChunkK + (v & 7) * 4;
+          const float* src = xsrc + (v >> 3) * kChunkK + (v & 7) * 4;
           const float4 lo = *reinterpret_cast<const float4*>(src), hi = *reinterpret_cast<const float4*>(src + 32);
           xr[j][0] = lo.x; xr[j][1] = lo.y; xr[j][2] = lo.z; xr[j][3] = lo.w;
           xr[j][4] = hi.x; xr[j][5] = hi.y; xr[j][6] = hi.z; xr[j][7] = hi.w;
@@ -630,9 +654,9 @@ __device__ __noinline__ bool small_gemm_rows(const Ctx& cx, int gp, SmallState& 
         const uint32_t base = ring_base + head * kGranule + (wtid << 4);
         head += gran;
         const uint32_t bar = seq % kChunkBars;
-        const bool got = ok && wait_mbar(cx, smem_u32(&cx.misc->full[bar]), (seq / kChunkBars) & 1, SITE_MMA_FULL, gp);
+        const bool got = ok && wait_mbar(cx, full0 + bar * 8u, (seq / kChunkBars) & 1, SITE_MMA_FULL, gp);
         ok = __all_sync(0xffffffffu, got);
-        if (r0 == 0 && unit == cx.cta) trace_event(cx, wtid, EV_FIRST_COPY);
+        if (tracing && r0 == 0 && unit == my_cta) trace_event(cx, wtid, EV_FIRST_COPY);
         const int count = min(rpc, tile_rows - r0);
         // G rows of the copy at a time: their loads issue together and their FMA chains and shuffle
         // trees interleave (one row alone is a chain of up to 32 dependent FMAs and 5 dependent shuffles).
@@ -678,10 +702,10 @@ __device__ __noinline__ bool small_gemm_rows(const Ctx& cx, int gp, SmallState& 
         else if (rpc >= 2) row_groups(IntTag<2>{});
         else row_groups(IntTag<1>{});
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&cx.misc->empty[bar]));
+        if (lane == 0) mbar_arrive(empty0 + bar * 8u);
         seq += 1;
       }
-      if (unit == cx.cta) trace_event(cx, wtid, EV_FIRST_ACC);
+      if (tracing && unit == my_cta) trace_event(cx, wtid, EV_FIRST_ACC);
       small_sync();
       {
         const bool mine = wtid < tile_rows;
@@ -705,7 +729,7 @@ __device__ __noinline__ bool small_gemm_rows(const Ctx& cx, int gp, SmallState& 
           st_relaxed_u64(ph->ll_dst + ((row0 + wtid) >> 1), (static_cast<unsigned long long>(stamp) << 32) | (other << 16) | bits);
       }
     }
-    trace_event(cx, wtid, EV_PHASE_DONE);
+    if (tracing) trace_event(cx, wtid, EV_PHASE_DONE);
   }
   st.head = head;
   st.seq = seq;
@@ -936,8 +960,20 @@ __device__ __noinline__ void small_fetch_rows(uint32_t dst, const bf16* src, int
   }
 }
 
-__device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, int wtid, int nch) {
-  const KParams& p = *cx.p;
+__device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A_in, int wtid, int nch) {
+  // Private copies of everything this phase reads from the context, the parameters and its own arguments:
+  // each poll and each barrier below is a compiler barrier for memory, behind which a value that lives
+  // behind a reference would be loaded again (two dependent loads for a kernel parameter).
+  const SmallAttn A = A_in;
+  struct {
+    int head_dim, q_heads, kv_heads, batch, qkv_ld, rope_style;
+    const bf16 *cos_t, *sin_t;
+    float *att_xch, *att_part;
+  } p = {cx.p->head_dim, cx.p->q_heads, cx.p->kv_heads, cx.p->batch, cx.p->qkv_ld, cx.p->rope_style,
+         cx.p->cos_t, cx.p->sin_t, cx.p->att_xch, cx.p->att_part};
+  const int my_cta = cx.cta, grid = cx.grid;
+  uint8_t* const region = cx.smem_b;
+  const long long* const pos_s = cx.misc->pos_s;
   const int hd = p.head_dim, half = hd / 2;
   const int gs = p.q_heads / p.kv_heads;
   const int rows = p.batch * p.kv_heads;
@@ -949,8 +985,8 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
   const int tile_keys = kAttTileBytes / (hd * 2);
   const int row_bytes = hd * 2;
 
-  float* sc = reinterpret_cast<float*>(cx.smem_b);                       // [gs][chunk]
-  uint8_t* tile = cx.smem_b + kAttScoreBytes;                             // [tile_keys][hd] bf16
+  float* sc = reinterpret_cast<float*>(region);                       // [gs][chunk]
+  uint8_t* tile = region + kAttScoreBytes;                             // [tile_keys][hd] bf16
   float* qs = reinterpret_cast<float*>(tile + kAttTileBytes);             // [gs][hd]                4 KB
   float* red = qs + 8 * 128;                                              // [8 warps][128] / [parts][gs*hd]  4 KB
   bf16* kn = reinterpret_cast<bf16*>(red + kSmallWarps * 128);            // [hd]
@@ -960,7 +996,7 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
   const uint32_t tile_addr = smem_u32(tile);
 
 #pragma unroll 1
-  for (int u = cx.cta; u < units; u += cx.grid) {
+  for (int u = my_cta; u < units; u += grid) {
     const int rowg = u / nch, ch = u - rowg * nch;
     const int b = rowg / p.kv_heads, kvh = rowg - b * p.kv_heads;
     const int j0 = ch * chunk;
@@ -971,7 +1007,7 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
     const bf16* kbase = A.k + b * A.kv_bstride + kvh * hd;
     const bf16* vbase = A.v + b * A.kv_bstride + kvh * hd;
     const int ntiles = (cl + tile_keys - 1) / tile_keys;
-    if (u != cx.cta) small_sync();  // previous unit is done with the scratch
+    if (u != my_cta) small_sync();  // previous unit is done with the scratch
 
     // Copy keys [t0, t1) of `cache` (not the new position: its row is still in kn/vn) into the tile.
     auto fetch_tile = [&](const bf16* cache, int t0, int t1) {
@@ -982,7 +1018,7 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
     // --- q of every head of the group and the new key (both rotated), and the new value: one round trip
     bool fresh = true;  // every stamped word this thread needs has arrived
     {
-      const long long pos = cx.misc->pos_s[b];
+      const long long pos = pos_s[b];
       const int ropes = (gs + 1) * half;
       const int q_size = p.q_heads * hd, kv_size = p.kv_heads * hd;
       // Column c of sequence b's q/k/v row: from the bf16 buffer, or (small-launch table) from the word the
@@ -1266,29 +1302,50 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A, 
 __device__ __noinline__ void small_producer(const Ctx& cx) {
   const KParams& p = *cx.p;
   const uint64_t policy = l2_policy_evict_first();
-  SmemMisc* misc = cx.misc;
-  const int ring_granules = p.small_ring;
+  // Everything below is read into registers once (per launch or per phase): each barrier wait is a compiler
+  // barrier for memory, and a descriptor field read again behind it is a round trip to L2 in the one
+  // thread whose pace decides how full the ring stays.
+  const int ring_granules = p.small_ring, n_gemm = p.n_gemm;
+  const GemmPhase* const table = p.phases;
+  const int my_cta = cx.cta, grid = cx.grid;
+  const uint32_t ring_base = smem_u32(cx.smem_a);
+  const uint32_t full0 = smem_u32(&cx.misc->full[0]), empty0 = smem_u32(&cx.misc->empty[0]);
+  uint8_t* const qstart = cx.misc->qstart;
+  uint8_t* const qgran = cx.misc->qgran;
   int head = 0, seq = 0, oldest = 0;
   bool ok = true;
 #pragma unroll 1
-  for (int gp = 0; gp < p.n_gemm && ok; ++gp) {
-    const GemmPhase* ph = p.phases + gp;
+  for (int gp = 0; gp < n_gemm && ok; ++gp) {
+    const GemmPhase* ph = table + gp;
     const int nacc = ph->nacc, gran = ph->gran, nunits = ph->nunits, ksplit = ph->ksplit, kslice = ph->kslice, kb = ph->kb;
-    const uint32_t bytes = static_cast<uint32_t>(ph->rows) * 128u * static_cast<uint32_t>(kb);
-    const int rot = k_rotation(cx.cta, cx.grid, kslice / kb) * kb;
+    const int rows = ph->rows, nseg = ph->nseg, bulk = ph->bulk, rpc = ph->rpc, map3d = ph->map3d, k_elems = ph->k;
+    const int ts1 = ph->tile_start[1], ts2 = ph->tile_start[2];
+    const int n0 = ph->n[0], n1 = ph->n[1], n2 = ph->n[2];
+    const CUtensorMap *m0 = ph->tmap[0], *m1 = ph->tmap[1], *m2 = ph->tmap[2];
+    const bf16 *w0 = ph->w[0], *w1 = ph->w[1], *w2 = ph->w[2];
+    const uint32_t bytes = static_cast<uint32_t>(rows) * 128u * static_cast<uint32_t>(kb);
+    const int rot = k_rotation(my_cta, grid, kslice / kb) * kb;
 #pragma unroll 1
-    for (int unit = cx.cta; unit < nunits && ok; unit += cx.grid) {
+    for (int unit = my_cta; unit < nunits && ok; unit += grid) {
       const int tile = unit / ksplit, slice = unit - tile * ksplit;
-      int seg, row0;
-      tile_origin(ph, tile, seg, row0);
+      // tile_origin() on the private copies
+      int seg = 0;
+      if (nacc == 1) {
+        if (nseg > 1 && tile >= ts1) seg = 1;
+        if (nseg > 2 && tile >= ts2) seg = 2;
+      }
+      const int row0 = (tile - (seg == 0 ? 0 : (seg == 1 ? ts1 : ts2))) * rows;
       const int kbase = slice * kslice;
       int k = rot;
-      const int tile_rows = min(ph->rows, ph->n[seg] - row0);
-      const int steps = ph->bulk ? (tile_rows + ph->rpc - 1) / ph->rpc * kb : kslice * nacc;  // bulk: one step per copy
+      const int n_seg = seg == 0 ? n0 : (seg == 1 ? n1 : n2);
+      const bf16* w_seg = seg == 0 ? w0 : (seg == 1 ? w1 : w2);
+      const CUtensorMap* map_seg = seg == 0 ? m0 : (seg == 1 ? m1 : m2);
+      const int tile_rows = min(rows, n_seg - row0);
+      const int steps = bulk ? (tile_rows + rpc - 1) / rpc * kb : kslice * nacc;  // bulk: one step per copy
 #pragma unroll 1
       for (int i = 0; i < steps && ok; i += kb) {
         const int a = (nacc == 2) ? ((i / kb) & 1) : 0;  // gate and up copies alternate
-        const CUtensorMap* map = ph->tmap[nacc == 2 ? a : seg];
+        const CUtensorMap* map = nacc == 2 ? (a ? m1 : m0) : map_seg;
         // Copies are consumed in issue order, so ring space is reclaimed by retiring the oldest copy in
         // flight until [lo, hi) is free; a copy never wraps, so the skipped tail is freed first.
         int lo = head, hi = head + gran;
@@ -1297,10 +1354,10 @@ __device__ __noinline__ void small_producer(const Ctx& cx) {
         for (int trip = 0; trip < 2 && ok; ++trip) {
 #pragma unroll 1
           while (oldest < seq) {
-            const int os = misc->qstart[oldest % kChunkBars], oe = os + misc->qgran[oldest % kChunkBars];
+            const int os = qstart[oldest % kChunkBars], oe = os + qgran[oldest % kChunkBars];
             const bool overlaps = os < hi && lo < oe;
             if (!overlaps && seq - oldest < kChunkBars) break;
-            if (!wait_mbar(cx, smem_u32(&misc->empty[oldest % kChunkBars]), (oldest / kChunkBars) & 1, SITE_PRODUCER_EMPTY, gp)) {
+            if (!wait_mbar(cx, empty0 + (oldest % kChunkBars) * 8u, (oldest / kChunkBars) & 1, SITE_PRODUCER_EMPTY, gp)) {
               ok = false;
               break;
             }
@@ -1314,21 +1371,21 @@ __device__ __noinline__ void small_producer(const Ctx& cx) {
         if (!ok) break;
         const int start = head;
         head += gran;
-        misc->qstart[seq % kChunkBars] = static_cast<uint8_t>(start);
-        misc->qgran[seq % kChunkBars] = static_cast<uint8_t>(gran);
-        const uint32_t full = smem_u32(&misc->full[seq % kChunkBars]);
-        if (ph->bulk) {  // rows [r, r + count) of the tile: whole rows, contiguous in memory
-          const int r = i * ph->rpc, count = min(ph->rpc, tile_rows - r);
-          const uint32_t copy_bytes = static_cast<uint32_t>(count) * static_cast<uint32_t>(ph->k) * 2u;
+        qstart[seq % kChunkBars] = static_cast<uint8_t>(start);
+        qgran[seq % kChunkBars] = static_cast<uint8_t>(gran);
+        const uint32_t full = full0 + (seq % kChunkBars) * 8u;
+        const uint32_t dst = ring_base + start * kGranule;
+        if (bulk) {  // rows [r, r + count) of the tile: whole rows, contiguous in memory
+          const int r = i * rpc, count = min(rpc, tile_rows - r);
+          const uint32_t copy_bytes = static_cast<uint32_t>(count) * static_cast<uint32_t>(k_elems) * 2u;
           mbar_expect_tx(full, copy_bytes);
-          bulk_load_1d(smem_u32(cx.smem_a + start * kGranule), ph->w[seg] + static_cast<size_t>(row0 + r) * ph->k, copy_bytes, full,
-                       policy);
-        } else if (ph->map3d) {  // mma.sync consumer: 64 elements x the tile's rows x kb chunks, each chunk 128-byte swizzled
+          bulk_load_1d(dst, w_seg + static_cast<size_t>(row0 + r) * k_elems, copy_bytes, full, policy);
+        } else if (map3d) {  // mma.sync consumer: 64 elements x the tile's rows x kb chunks, each chunk 128-byte swizzled
           mbar_expect_tx(full, bytes);
-          tma_load_3d(smem_u32(cx.smem_a + start * kGranule), map, 0, row0, kbase + k, full, policy);
+          tma_load_3d(dst, map, 0, row0, kbase + k, full, policy);
         } else {
           mbar_expect_tx(full, bytes);
-          tma_load_2d(smem_u32(cx.smem_a + start * kGranule), map, (kbase + k) * kChunkK, row0, full, policy);
+          tma_load_2d(dst, map, (kbase + k) * kChunkK, row0, full, policy);
         }
         ++seq;
         if (nacc == 1 || a == 1) {
@@ -1340,7 +1397,7 @@ __device__ __noinline__ void small_producer(const Ctx& cx) {
   }
   if (!ok) {  // leaving early: every copy already issued must land before the CTA exits
     for (int i = max(0, seq - kChunkBars); i < seq; ++i) {
-      const uint32_t bar = smem_u32(&misc->full[i % kChunkBars]);
+      const uint32_t bar = full0 + (i % kChunkBars) * 8u;
       for (uint32_t spins = 0; spins < (1u << 22); ++spins) {
         if (mbar_try_wait(bar, (i / kChunkBars) & 1)) break;
       }
@@ -1353,7 +1410,7 @@ __device__ __noinline__ void small_producer(const Ctx& cx) {
 
 
 __device__ __forceinline__ uint4 small_norm_weight(const Ctx& cx, int gp, int wtid) {
-  if (gp >= cx.p->n_gemm) return make_uint4(0, 0, 0, 0);
+  if (gp >= cx.misc->n_gemm) return make_uint4(0, 0, 0, 0);
   const GemmPhase* ph = &cx.misc->phase[gp & 1];
   if (ph->bmode != B_NORM || wtid >= ph->k / 8) return make_uint4(0, 0, 0, 0);
   return __ldg(reinterpret_cast<const uint4*>(ph->normw) + wtid);
@@ -1553,6 +1610,10 @@ __global__ void __launch_bounds__(kSmallThreads, 1) megakernel_small(const __gri
     cx.misc->bad = 0;
     cx.misc->flag = 0;
     cx.misc->trace_n = 0;
+    cx.misc->trace_on = p.trace_cap != 0;
+    cx.misc->n_gemm = p.n_gemm;
+    cx.misc->epoch = p.epoch;
+    cx.misc->phases = p.phases;
     mbar_fence_init();
   }
   __syncthreads();

@@ -48,6 +48,10 @@ struct SmemMisc {
   int bad;      // prologue validation result
   int flag;
   int trace_n;  // events this CTA has recorded
+  int trace_on; // copies of launch parameters the phases read often (a parameter read through the context costs two dependent loads)
+  int n_gemm;
+  uint32_t epoch;
+  const GemmPhase* phases;
   float sred[kSplitTokens][8];   // small-launch kernel: per-token cross-warp sums
   long long pos_s[kSplitTokens]; // small-launch kernel: validated positions
   int len_s[MK_MAX_LAYERS];      // small-launch kernel: valid lengths before this call
@@ -124,7 +128,7 @@ __device__ __noinline__ void trace_event_record(const Ctx& cx, int code) {
 }
 // The test is inline, the recording out of line: with tracing off an event costs a compare.
 __device__ __forceinline__ void trace_event(const Ctx& cx, int wtid, int code) {
-  if (cx.p->trace_cap != 0 && wtid == 0) trace_event_record(cx, code);
+  if (wtid == 0 && cx.misc->trace_on != 0) trace_event_record(cx, code);
 }
 
 __device__ __forceinline__ bool wait_mbar(const Ctx& cx, uint32_t bar, uint32_t parity, int site, int detail) {
@@ -282,6 +286,13 @@ __device__ __noinline__ void producer_loop(const Ctx& cx) {
     const int groups = kslice / kb;
     const int rot = group_rotation(cx.cta, cx.grid, groups);
     const int map3d = ph->map3d;
+    // descriptor pointers in registers: every barrier wait below is a compiler barrier for memory, and a
+    // field read again behind it costs this one thread a round trip to L2 per copy
+    const bool linear = p.mode == MODE_LINEAR;
+    const CUtensorMap* const m0 = linear ? &p.linear_wmap : ph->tmap[0];
+    const CUtensorMap* const m1 = linear ? &p.linear_wmap : ph->tmap[1];
+    const CUtensorMap* const m2 = linear ? &p.linear_wmap : ph->tmap[2];
+    const int nseg = ph->nseg, rows = ph->rows, ts1 = ph->tile_start[1], ts2 = ph->tile_start[2];
     if (ph->gate) {  // the attention phase before this one streams cache tiles through the ring
       uint32_t spins = 0;
       while (*reinterpret_cast<volatile int*>(&cx.tc->a_ready) <= gp) {
@@ -295,8 +306,13 @@ __device__ __noinline__ void producer_loop(const Ctx& cx) {
     }
     for (int unit = cx.cta; unit < nunits && ok; unit += cx.grid) {
       const int tile = unit / ksplit, slice = unit - tile * ksplit;
-      int seg, row0;
-      tile_origin(ph, tile, seg, row0);
+      int seg = 0;  // tile_origin() on the private copies
+      if (nacc == 1) {
+        if (nseg > 1 && tile >= ts1) seg = 1;
+        if (nseg > 2 && tile >= ts2) seg = 2;
+      }
+      const int row0 = (tile - (seg == 0 ? 0 : (seg == 1 ? ts1 : ts2))) * rows;
+      const CUtensorMap* const map_seg = seg == 0 ? m0 : (seg == 1 ? m1 : m2);
       const int kbase = slice * kslice;
       for (int tt = 0; tt < ntt && ok; ++tt) {
         int g = rot;
@@ -310,7 +326,7 @@ __device__ __noinline__ void producer_loop(const Ctx& cx) {
           const uint32_t dst = smem_u32(cx.smem_a + start * kGranule);
           mbar_expect_tx(full, matrix_bytes * static_cast<uint32_t>(nacc));
           for (int a = 0; a < nacc; ++a) {
-            const CUtensorMap* map = p.mode == MODE_LINEAR ? &p.linear_wmap : ph->tmap[nacc == 2 ? a : seg];
+            const CUtensorMap* map = nacc == 2 ? (a ? m1 : m0) : map_seg;
             if (map3d) {
               tma_load_3d(dst + a * matrix_bytes, map, 0, row0, kbase + g * kb, full, policy);
             } else {
@@ -633,17 +649,19 @@ __device__ __forceinline__ void prefetch_phase(const Ctx& cx, int gp, int wtid) 
 // A warp may read TMEM lanes [32 * (warp index % 4), +32): thread (quadrant, lane) finishes weight row
 // quadrant * 32 + lane of the tile, sixteen token columns at a time.
 __device__ __noinline__ bool worker_gemm_tc(const Ctx& cx, int gp, WorkerState& ws, int wtid) {
-  const KParams& p = *cx.p;
+  const int m = cx.p->m;  // read once: the waits below are compiler barriers for memory
   const GemmPhase* ph = &cx.misc->phase[gp & 1];
-  const int ntok = token_tile(p.m);
-  const int ntt = (p.m + ntok - 1) / ntok;
-  const int nacc = ph->nacc, nunits = ph->nunits, rows = ph->rows, ksplit = ph->ksplit;
+  const int ntok = token_tile(m);
+  const int ntt = (m + ntok - 1) / ntok;
+  const int nacc = ph->nacc, nunits = ph->nunits, rows = ph->rows, ksplit = ph->ksplit, epi = ph->epi;
+  const uint32_t accfull0 = smem_u32(&cx.misc->accfull[0]), accempty0 = smem_u32(&cx.misc->accempty[0]);
+  const int my_cta = cx.cta, grid = cx.grid;
   const int quad = ((wtid >> 5) + 2) & 3;  // TMEM lane quadrant this warp may read
   const int rloc = quad * 32 + (wtid & 31);
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&cx.misc->tmem_base);
-  if (cx.cta < nunits) {
+  if (my_cta < nunits) {
     trace_event(cx, wtid, EV_PHASE_ENTER);
-    for (int unit = cx.cta; unit < nunits; unit += cx.grid) {
+    for (int unit = my_cta; unit < nunits; unit += grid) {
       const int tile = unit / ksplit, slice = unit - tile * ksplit;
       int seg, row0;
       tile_origin(ph, tile, seg, row0);
@@ -651,15 +669,15 @@ __device__ __noinline__ bool worker_gemm_tc(const Ctx& cx, int gp, WorkerState& 
       const bool valid = rloc < rows && n < ph->n[seg];
       for (int tt = 0; tt < ntt; ++tt) {
         const uint32_t buf = ws.tiles & 1u;
-        bool ok = wait_mbar(cx, smem_u32(&cx.misc->accfull[buf]), (ws.tiles >> 1) & 1u, SITE_EPI_ACC, gp);
+        bool ok = wait_mbar(cx, accfull0 + buf * 8u, (ws.tiles >> 1) & 1u, SITE_EPI_ACC, gp);
         ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below needs the whole warp
-        if (unit == cx.cta && tt == 0) trace_event(cx, wtid, EV_FIRST_ACC);
+        if (unit == my_cta && tt == 0) trace_event(cx, wtid, EV_FIRST_ACC);
         tc_fence_after();
-        const int tile_tokens = min(ntok, p.m - tt * ntok);
+        const int tile_tokens = min(ntok, m - tt * ntok);
         // the two warps that share a TMEM lane quadrant take alternate groups of sixteen token columns
         for (int cg = (wtid >> 5) / 4; cg * kTok < tile_tokens; cg += kWorkerWarps / 4) {
           const int t0 = tt * ntok + cg * kTok;
-          const int mt = min(kTok, p.m - t0);
+          const int mt = min(kTok, m - t0);
           float pre[kTok];
           if (valid) epilogue_prefetch<kTok>(cx, ph, seg, n, t0, mt, pre);
           float v[2][kTok];
@@ -669,13 +687,13 @@ __device__ __noinline__ bool worker_gemm_tc(const Ctx& cx, int gp, WorkerState& 
             if (nacc == 2) tmem_ld16(at + kMaxTok, v[1]);
           }
           if (ok && valid) {
-            if (ph->epi == EPI_PARTIAL) store_partial<kTok>(cx, ph, slice, n, v[0], t0, mt);
-            else if (ph->epi == EPI_TP) store_tp_partial<kTok>(cx, ph, n, v[0], t0, mt);
+            if (epi == EPI_PARTIAL) store_partial<kTok>(cx, ph, slice, n, v[0], t0, mt);
+            else if (epi == EPI_TP) store_tp_partial<kTok>(cx, ph, n, v[0], t0, mt);
             else apply_epilogue<kTok>(cx, ph, seg, n, v, pre, t0, mt);
           }
         }
         tc_fence_before();
-        mbar_arrive(smem_u32(&cx.misc->accempty[buf]));
+        mbar_arrive(accempty0 + buf * 8u);
         ws.tiles += 1;
         if (!workers_ok(cx, ok)) return false;
       }
@@ -724,11 +742,17 @@ constexpr int kNormVecs = 4;  // vectors a worker thread holds: rows of up to kN
 __device__ __noinline__ void norm_phase(const Ctx& cx, const GemmPhase* ph, int wtid) {
   const KParams& p = *cx.p;
   const int warp = wtid >> 5, lane = wtid & 31;
-  const int nvec = ph->k / 8;
+  // read once: the block barriers below are compiler barriers for memory
+  const int m = p.m, k = ph->k, my_cta = cx.cta, grid = cx.grid;
+  const float eps = p.eps;
+  bf16* const xnorm = p.xnorm;
+  const float* const partial = ph->partial;
+  bf16* const h_out = ph->h_out;
+  const int nvec = k / 8;
   const int parts = ph->add_parts;
   const uint4* wrow = reinterpret_cast<const uint4*>(ph->normw);
   float* red = &cx.misc->sred[0][0];  // kWorkerWarps partial sums (the small-launch kernel's scratch, free here)
-  for (int t = cx.cta; t < p.m; t += cx.grid) {
+  for (int t = my_cta; t < m; t += grid) {
     const uint4* row = reinterpret_cast<const uint4*>(activation_row(p, ph, t));
     uint4 x[kNormVecs];
     float sum = 0.f;
@@ -745,7 +769,7 @@ __device__ __noinline__ void norm_phase(const Ctx& cx, const GemmPhase* ph, int 
 #pragma unroll
           for (int s8 = 0; s8 < kMaxSplit; ++s8) {
             if (s8 < parts) {
-              const float4* part = reinterpret_cast<const float4*>(ph->partial + (static_cast<size_t>(s8) * p.m + t) * ph->k) + v * 2;
+              const float4* part = reinterpret_cast<const float4*>(partial + (static_cast<size_t>(s8) * m + t) * k) + v * 2;
               lo[j][s8] = __ldcg(part);
               hi[j][s8] = __ldcg(part + 1);
             }
@@ -783,8 +807,8 @@ __device__ __noinline__ void norm_phase(const Ctx& cx, const GemmPhase* ph, int 
     float total = 0.f;
 #pragma unroll
     for (int w = 0; w < kWorkerWarps; ++w) total += red[w];
-    const float rinv = 1.0f / sqrtf(total / static_cast<float>(ph->k) + p.eps);
-    uint4* out = reinterpret_cast<uint4*>(p.xnorm + static_cast<size_t>(t) * ph->k);
+    const float rinv = 1.0f / sqrtf(total / static_cast<float>(k) + eps);
+    uint4* out = reinterpret_cast<uint4*>(xnorm + static_cast<size_t>(t) * k);
 #pragma unroll
     for (int j = 0; j < kNormVecs; ++j) {
       const int v = j * kWorkers + wtid;
@@ -1718,6 +1742,10 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
     cx.misc->bad = 0;
     cx.misc->flag = 0;
     cx.misc->trace_n = 0;
+    cx.misc->trace_on = p.trace_cap != 0;
+    cx.misc->n_gemm = p.n_gemm;
+    cx.misc->epoch = p.epoch;
+    cx.misc->phases = p.phases;
     cx.tc->b_ready = 0;
     cx.tc->a_ready = 0;
     mbar_fence_init();
