@@ -937,8 +937,18 @@ __device__ __noinline__ void fetch_cache_tile(uint32_t dst, const bf16* src, int
   }
 }
 
-__device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A, int wtid) {
-  const KParams& p = *cx.p;
+__device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A_in, int wtid) {
+  // Private copies of the arguments and of the parameters this phase reads: every poll, copy wait and block
+  // barrier below is a compiler barrier for memory, behind which a value that lives behind a reference is
+  // loaded again (a kernel parameter through the context: two dependent loads).
+  const AttnArgs A = A_in;
+  struct {
+    int head_dim, q_heads, kv_heads, batch, max_positions, rope_style, prefill_rope_style, m;
+    const bf16 *cos_t, *sin_t;
+    float *att_xch, *att_part;
+    long long* pos;
+  } p = {cx.p->head_dim, cx.p->q_heads, cx.p->kv_heads, cx.p->batch, cx.p->max_positions, cx.p->rope_style,
+         cx.p->prefill_rope_style, cx.p->m, cx.p->cos_t, cx.p->sin_t, cx.p->att_xch, cx.p->att_part, cx.p->pos};
   const int hd = p.head_dim, half = hd / 2;
   const int gs = p.q_heads / p.kv_heads;
   const int hpu = decode_heads_per_unit(p.kv_heads, gs, hd);  // KV heads per unit
@@ -1270,8 +1280,18 @@ constexpr int kPromptKeys = 64;                    // positions per K / V tile
 
 __device__ __forceinline__ uint32_t ldcg_u32(const void* ptr) { return __ldcg(reinterpret_cast<const unsigned int*>(ptr)); }
 
-__device__ __noinline__ bool attention_prompt(const Ctx& cx, const AttnArgs& A, int wtid) {
-  const KParams& p = *cx.p;
+__device__ __noinline__ bool attention_prompt(const Ctx& cx, const AttnArgs& A_in, int wtid) {
+  // Private copies of the arguments and of the parameters this phase reads: every poll, copy wait and block
+  // barrier below is a compiler barrier for memory, behind which a value that lives behind a reference is
+  // loaded again (a kernel parameter through the context: two dependent loads).
+  const AttnArgs A = A_in;
+  struct {
+    int head_dim, q_heads, kv_heads, batch, max_positions, rope_style, prefill_rope_style, m;
+    const bf16 *cos_t, *sin_t;
+    float *att_xch, *att_part;
+    long long* pos;
+  } p = {cx.p->head_dim, cx.p->q_heads, cx.p->kv_heads, cx.p->batch, cx.p->max_positions, cx.p->rope_style,
+         cx.p->prefill_rope_style, cx.p->m, cx.p->cos_t, cx.p->sin_t, cx.p->att_xch, cx.p->att_part, cx.p->pos};
   const int hd = p.head_dim;
   const int gs = p.q_heads / p.kv_heads;
   const int warp = wtid >> 5, lane = wtid & 31, g = lane >> 2, t = lane & 3;
