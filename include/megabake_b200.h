@@ -46,12 +46,17 @@ typedef enum mk_device_status {
 
 enum { MK_ROPE_HF = 0, MK_ROPE_HALF_SWAP = 1 };
 /* TCGEN05: tensor-core projections (tcgen05.mma, TMEM accumulators) for every launch.
- * FMA: decode launches of at most 4 tokens run the small-launch kernel, which consumes the
- *      TMA-fed weight ring with CUDA-core FMAs (a matrix-vector product cannot fill a
- *      128-row MMA); every other launch uses tcgen05.  Falls back to tcgen05 when the shape
- *      does not fit the small kernel (hidden > 2048 or a K slice longer than 2048).
+ * FMA: decode launches of at most 4 tokens run the small-launch kernel, which consumes its
+ *      TMA-fed weight ring without tcgen05 (a matrix-vector product cannot fill a 128-row
+ *      MMA): CUDA-core FMAs for one token (the row table: one grid barrier per launch),
+ *      warp-level mma.sync for two to four; every other launch uses tcgen05.  Falls back to
+ *      tcgen05 when the shape does not fit the small kernel (hidden > 2048 or a K slice
+ *      longer than 2048).
  * AUTO: the faster of the two per launch; today the same choice as FMA.
- * (Value 1 named a bring-up engine without TMA or tensor cores; it is gone and rejected.) */
+ * (Value 1 named a bring-up engine without TMA or tensor cores; it is gone and rejected.)
+ * Process-wide tunables of the small-launch kernel, read by mk_create: MEGABAKE_SMALL_RING_KB
+ * (weight ring of the one-token kernel, 64..152, default 120) and MEGABAKE_SMALL_COPY_KB
+ * (its largest weight copy, default 36). */
 enum { MK_ENGINE_TCGEN05 = 0, MK_ENGINE_FMA = 2, MK_ENGINE_AUTO = 3 };
 
 /* Decoder shape.  Mirrors the facts the reference reads off the captured graph

@@ -1,31 +1,35 @@
 // The decode megakernel for launches of at most four tokens (batch-1 decode is
 // the case that matters).  Same phase tables, status protocol and bounded waits
-// as mk::megakernel, but the weights are consumed by CUDA-core FMAs.
+// as mk::megakernel, but the weights are not consumed by tcgen05.
 //
-// Why not the tensor core here: one tcgen05.mma of 128 weight rows by 16 token
-// columns occupies the tensor pipe for ~78 cycles whatever the token count and
-// however few of the 128 rows hold weights (an even split of a projection over
-// 148 CTAs wants tiles of 14-56 rows), which capped a CTA at 6-12 bytes of
-// weights per cycle where HBM can deliver 22.  A matrix-vector product needs
-// one FMA per weight and token.
+// Why not tcgen05 here: one tcgen05.mma of 128 weight rows by 16 token columns
+// occupies the tensor pipe for ~78 cycles whatever the token count and however
+// few of the 128 rows hold weights (an even split of a projection over 148 CTAs
+// wants tiles of 14-56 rows), which capped a CTA at 6-12 bytes of weights per
+// cycle where HBM can deliver 22.
 //
 // Roles: warp 0 = TMA producer (small_producer), warps 1-8 = consumers (operand
-// staging with the RMSNorm fused in, FMA projection, epilogue, decode attention).
-// No TMEM, no MMA warp.
+// staging with the RMSNorm fused in, projection, epilogue, decode attention).
+// No TMEM, no MMA warp.  Two kernels are instantiated per token count:
+//   <1, true>   the one-token row table: CUDA-core FMAs over plain weight rows
+//               (small_gemm, small_gemm_rows), a single grid barrier per launch;
+//   <T, false>  the split-K table for one to four tokens: warp-level mma.sync
+//               over 128-byte-swizzled boxes (small_gemm_mma), two grid barriers
+//               per layer.
 //
-// Weight copies are 14-28 KB each (plain rows of up to 256 K-elements through a
-// 2-D tensor map, or whole contiguous rows through a 1-D bulk copy): an SM's copy
-// engine retires about three copies per microsecond whatever their size.  The
-// lanes of a warp split the K range of a copy and keep their activation values
-// in registers; a thread holds one fp32 chain per (row, lane).
+// Weight copies are 14-34 KB each (a two- or three-dimensional tensor-map box,
+// or whole contiguous rows through a 1-D bulk copy): an SM's copy engine retires
+// about three copies per microsecond whatever their size.
 //
 // Phases hand their outputs over as 64-bit words {stamp, payload} that the
 // consumer's staging polls (stamped_payloads): a reader that sees the stamp has
 // the data, so no fence and no grid barrier is needed, and a consumer starts as
-// soon as its own producers are done.  One-token launches run the "row table"
-// (o_proj and down_proj uncut along K, residual stream stamped) with a single
-// grid barrier per launch; two to four tokens keep the split-K table with two
-// grid barriers per layer.
+// soon as its own producers are done.
+//
+// Polls and barrier waits are compiler barriers for memory: whatever a loop
+// needs from the context, the parameters or a descriptor is copied into locals
+// before the loop (a kernel parameter read through the context is two dependent
+// loads; one such read in a staging loop measured 40 us per step).
 #pragma once
 #include "decoder_kernel.cuh"
 

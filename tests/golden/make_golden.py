@@ -2,7 +2,7 @@
 
 Run once, in a container that has the reference checkout (read-only):
 
-    python tests/golden/make_golden.py --reference /root/reference [--cases a,b,...]
+    python tests/golden/make_golden.py --reference <checkout of the reference> [--cases a,b,...]
 
 The reference package cannot be imported whole here (its ``__init__`` pulls in a
 CuTe-DSL release this image does not have), so a stub ``megabake`` package is
@@ -235,7 +235,7 @@ def host_fingerprint() -> dict:
 
 def main():
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--reference", required=True, help="path of a checkout of the reference project")
     parser.add_argument("--cases", default="ops,tiny,tiny_hf,prefill_tiny,c1,c2,prefill_c1,prefill_c2")
     parser.add_argument("--out", default=str(HERE))
     args = parser.parse_args()

@@ -50,6 +50,53 @@ def test_static_scratch_entry_point_matches_the_handle_one(shape):
         assert int(state_b[2]) == filled + call + 1 == int(state_a[2])
 
 
+def test_static_scratch_entry_point_matches_the_reference_recording_and_the_oracle():
+    """The same calls the reference's own op made when the golden file was recorded (tests/golden/ops.pt),
+    then two split-context steps against the oracle: outputs within the tolerance of the op tests
+    (2e-2 absolute + 1e-2 relative), caches and lengths exact."""
+    from conftest import assert_parity, load_golden
+    from oracle import decoder_oracle as oracle
+
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    lib = _native.load()
+    record = load_golden("ops.pt")
+    first = record["calls"][0]
+    key_cache = torch.zeros_like(first["key_cache"], device=device)
+    value_cache = torch.zeros_like(first["value_cache"], device=device)
+    length = torch.zeros(1, dtype=torch.int32, device=device)
+    for index, call in enumerate(record["calls"]):
+        source = call["source"].to(device)
+        batch, _, heads, dim = source.shape
+        kv_heads = call["key"].shape[2]
+        output = torch.full((batch * heads, 1, dim), float("nan"), dtype=torch.bfloat16, device=device)
+        _native.check("mk_kv_attention_static",
+                      _static_call(lib, heads, kv_heads, dim, source, call["key"].to(device), call["value"].to(device),
+                                   key_cache, value_cache, length, output))
+        torch.cuda.synchronize(device)
+        assert_parity(output, call["output"], f"static kv_attention, recorded call {index}")
+        assert torch.equal(key_cache.cpu(), call["key_cache"]) and torch.equal(value_cache.cpu(), call["value_cache"])
+        assert torch.equal(length.cpu(), call["length"])
+
+    batch, heads, kv_heads, dim, capacity, filled = 2, 8, 2, 64, 600, 597
+    key_cache = synth_normal((batch, capacity, kv_heads, dim), seed=31, name="kc", std=1.0, device=device)
+    value_cache = synth_normal((batch, capacity, kv_heads, dim), seed=31, name="vc", std=1.0, device=device)
+    ref_k, ref_v = key_cache.clone(), value_cache.clone()
+    length = torch.full((1,), filled, dtype=torch.int32, device=device)
+    ref_length = length.clone()
+    for step in range(2):
+        query = synth_normal((batch, 1, heads, dim), seed=31, name=f"q{step}", std=1.0, device=device)
+        key = synth_normal((batch, 1, kv_heads, dim), seed=31, name=f"k{step}", std=1.0, device=device)
+        value = synth_normal((batch, 1, kv_heads, dim), seed=31, name=f"v{step}", std=1.0, device=device)
+        output = torch.full((batch * heads, 1, dim), float("nan"), dtype=torch.bfloat16, device=device)
+        _native.check("mk_kv_attention_static",
+                      _static_call(lib, heads, kv_heads, dim, query, key, value, key_cache, value_cache, length, output))
+        torch.cuda.synchronize(device)
+        expected = oracle.kv_attention(query, key, value, ref_k, ref_v, ref_length)
+        assert_parity(output, expected, f"static kv_attention against the oracle, step {step}")
+    assert torch.equal(key_cache, ref_k) and torch.equal(value_cache, ref_v) and int(length) == filled + 2 == int(ref_length)
+
+
 def test_static_scratch_entry_point_rejects_what_does_not_fit():
     device = torch.device("cuda:0")
     torch.cuda.set_device(device)
