@@ -942,8 +942,8 @@ struct SmallAttn {
 
 // Shared-memory plan of the attention phase inside the 64 KB activation region.
 constexpr int kAttScoreBytes = 16 * 1024;   // fp32 scores [group][chunk]
-constexpr int kAttTileBytes = 38 * 1024;    // one tile of cached K (then V) rows of the unit's head (304 keys of 64)
-constexpr int kAttScratchBytes = 10 * 1024; // q, cross-warp sums, new key/value, statistics
+constexpr int kAttTileBytes = 36 * 1024;    // one tile of cached K (then V) rows of the unit's head (288 keys of 64)
+constexpr int kAttScratchBytes = 12 * 1024; // q (fp32 and bf16), cross-warp sums, new key/value, statistics
 static_assert(kAttScoreBytes + kAttTileBytes + kAttScratchBytes <= kBBytes, "attention scratch exceeds its region");
 
 // Code size matters here: every instruction of this function runs a handful of times per
@@ -964,6 +964,7 @@ __device__ __noinline__ void small_fetch_rows(uint32_t dst, const bf16* src, int
   }
 }
 
+template <bool use_mma>
 __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A_in, int wtid, int nch) {
   // Private copies of everything this phase reads from the context, the parameters and its own arguments:
   // each poll and each barrier below is a compiler barrier for memory, behind which a value that lives
@@ -997,7 +998,26 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A_i
   bf16* vn = kn + 128;                                                    // [hd]
   float* stat = reinterpret_cast<float*>(vn + 128);                       // [16]: max[8], sum[8]
   float* all = stat + 16;                                                 // [kMaxChunks][16]
+  bf16* qb = reinterpret_cast<bf16*>(all + kMaxChunks * 16);              // [gs][hd]: q again as bf16 (exact)
   const uint32_t tile_addr = smem_u32(tile);
+  // Both products run on the warp-level tensor cores: one mma.sync (m16n8k16) multiplies 16 cached
+  // positions x 16 head dimensions by the (up to eight) query heads of the KV head, where a CUDA-core loop
+  // needs 17 instructions per lane for eight elements; with eight warps per SM every instruction is ~8
+  // cycles of this phase's latency chain.
+  //   scores: D[16 keys][heads]  = K tile (ldmatrix)         x q[dims][heads]   (q fragments in registers)
+  //   values: D[16 dims][heads] += V tile^T (ldmatrix.trans) x p[keys][heads]
+  // Warps split the 16-key blocks (scores); for the values warp w takes dimension tile w % (hd / 16) and
+  // every (8 * 16 / hd)-th key block, and the parts are added in part order.
+  // (use_mma: a KV head with a single query head fills one of the eight MMA columns and measured 1.2 %
+  // slower than the CUDA-core loops on the 1.7B shape; seven heads per group, Qwen2-0.5B, 8 % faster.  The
+  // caller picks the instantiation by group size.)
+  const int ksteps = hd / 16, dim_tiles = hd / 16;
+  const int v_parts = kSmallWarps / dim_tiles > 0 ? kSmallWarps / dim_tiles : 1;   // 2 (hd 64) or 1 (hd 128)
+  const int my_dt = warp % dim_tiles, my_part = warp / dim_tiles;
+  const int lg = lane >> 2, lt = lane & 3;
+  auto piece_addr = [&](int key, int piece) -> uint32_t {
+    return tile_addr + key * row_bytes + ((piece ^ (key & 7)) << 4);
+  };
 
 #pragma unroll 1
   for (int u = my_cta; u < units; u += grid) {
@@ -1053,8 +1073,13 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A_i
           const float sn = ldg_bf16(p.sin_t + pos * hd + i);
           rope_pair(x1, x2, cs, sn, p.rope_style, x1, x2);
           if (g < gs) {
-            qs[g * hd + i] = x1;
-            qs[g * hd + i + half] = x2;
+            if constexpr (use_mma) {
+              qb[g * hd + i] = __float2bfloat16_rn(x1);  // exact: both are bf16 values
+              qb[g * hd + i + half] = __float2bfloat16_rn(x2);
+            } else {
+              qs[g * hd + i] = x1;
+              qs[g * hd + i + half] = x2;
+            }
           } else {
             kn[i] = __float2bfloat16_rn(x1);
             kn[i + half] = __float2bfloat16_rn(x2);
@@ -1068,6 +1093,16 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A_i
     cp_async_wait_all();
     if (!small_ok(cx, fresh)) return false;
     trace_event(cx, wtid, EV_ATT_INPUTS);
+    uint32_t qfrag[8][2];  // B fragments: q[dims][query heads], one pair per 16 dimensions
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      qfrag[ks][0] = qfrag[ks][1] = 0u;
+      if (use_mma && ks < ksteps && lg < gs) {
+        const bf16* at = qb + lg * hd + ks * 16 + lt * 2;
+        qfrag[ks][0] = *reinterpret_cast<const uint32_t*>(at);
+        qfrag[ks][1] = *reinterpret_cast<const uint32_t*>(at + 8);
+      }
+    }
     if (owner && newpos - j0 < tile_keys && wtid < lpk)  // the new key joins its tile (its row was not fetched)
       *reinterpret_cast<uint4*>(tile + (newpos - j0) * row_bytes + ((wtid ^ ((newpos - j0) & 7)) << 4)) =
           *reinterpret_cast<const uint4*>(kn + wtid * 8);
@@ -1096,34 +1131,54 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A_i
       } else {
         small_sync();  // the patched row of the first tile is visible
       }
+      if constexpr (use_mma) {
+      const int tk = t1 - t0;
+#pragma unroll 1
+        for (int blk = warp; blk * 16 < tk; blk += kSmallWarps) {
+          float d[4] = {0.f, 0.f, 0.f, 0.f};
+          const int row = blk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll 2
+          for (int ks = 0; ks < ksteps; ++ks) {
+            uint32_t af[4];
+            ldmatrix_x4(af, piece_addr(row, ks * 2 + (lane >> 4)));
+            mma_bf16_16816(d, af, qfrag[ks][0], qfrag[ks][1]);
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int key = blk * 16 + lg + (e >> 1) * 8, n = lt * 2 + (e & 1);
+            if (n < gs && key < tk) sc[n * chunk + (t0 - j0) + key] = bf16_round(d[e]) * A.scale;
+          }
+        }
+      } else {
       // one thread per key: a 64- or 128-term fp32 chain per (key, head), no shuffles
 #pragma unroll 1
-      for (int key = wtid; key < t1 - t0; key += kSmallWorkers) {
-        const int j = t0 + key;
-        const uint8_t* krow = tile + key * row_bytes;
+        for (int key = wtid; key < t1 - t0; key += kSmallWorkers) {
+          const int j = t0 + key;
+          const uint8_t* krow = tile + key * row_bytes;
 #pragma unroll 1
-        for (int g = 0; g < gs; ++g) {
-          const float* qv = qs + g * hd;
-          // four partial sums (pieces 0, 4, ... / 1, 5, ... / ...): the same order as mk::attention_decode,
-          // and a quarter of the dependent FMA chain
-          float part[4] = {0.f, 0.f, 0.f, 0.f};
+          for (int g = 0; g < gs; ++g) {
+            const float* qv = qs + g * hd;
+            // four partial sums (pieces 0, 4, ... / 1, 5, ... / ...): the same order as mk::attention_decode,
+            // and a quarter of the dependent FMA chain
+            float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
-          for (int piece0 = 0; piece0 < lpk; piece0 += 4) {
+            for (int piece0 = 0; piece0 < lpk; piece0 += 4) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              const int piece = piece0 + c;
-              float kf[8];
-              unpack8(*reinterpret_cast<const uint4*>(krow + ((piece ^ (key & 7)) << 4)), kf);
-              const float4 qa = *reinterpret_cast<const float4*>(qv + piece * 8);
-              const float4 qb = *reinterpret_cast<const float4*>(qv + piece * 8 + 4);
-              float acc = part[c];
-              acc = fmaf(qa.x, kf[0], acc); acc = fmaf(qa.y, kf[1], acc); acc = fmaf(qa.z, kf[2], acc); acc = fmaf(qa.w, kf[3], acc);
-              acc = fmaf(qb.x, kf[4], acc); acc = fmaf(qb.y, kf[5], acc); acc = fmaf(qb.z, kf[6], acc); acc = fmaf(qb.w, kf[7], acc);
-              part[c] = acc;
+              for (int c = 0; c < 4; ++c) {
+                const int piece = piece0 + c;
+                float kf[8];
+                unpack8(*reinterpret_cast<const uint4*>(krow + ((piece ^ (key & 7)) << 4)), kf);
+                const float4 qa = *reinterpret_cast<const float4*>(qv + piece * 8);
+                const float4 qb = *reinterpret_cast<const float4*>(qv + piece * 8 + 4);
+                float acc = part[c];
+                acc = fmaf(qa.x, kf[0], acc); acc = fmaf(qa.y, kf[1], acc); acc = fmaf(qa.z, kf[2], acc); acc = fmaf(qa.w, kf[3], acc);
+                acc = fmaf(qb.x, kf[4], acc); acc = fmaf(qb.y, kf[5], acc); acc = fmaf(qb.z, kf[6], acc); acc = fmaf(qb.w, kf[7], acc);
+                part[c] = acc;
+              }
             }
+            const float dot = (part[0] + part[1]) + (part[2] + part[3]);
+            sc[g * chunk + (j - j0)] = bf16_round(dot) * A.scale;
           }
-          const float dot = (part[0] + part[1]) + (part[2] + part[3]);
-          sc[g * chunk + (j - j0)] = bf16_round(dot) * A.scale;
         }
       }
     }
@@ -1207,47 +1262,102 @@ __device__ __noinline__ bool small_attention(const Ctx& cx, const SmallAttn& A_i
 #pragma unroll 1
       for (int i = wtid; i < cl; i += kSmallWorkers) sc[g * chunk + i] = bf16_round(expf(sc[g * chunk + i] - m) / denom);
     }
-    // --- value accumulation: an item is (part of the keys, head of the group, 16-byte piece of the
-    // output row); part p takes keys p, p + parts, ...; the fp32 sums of an item live in `red`
-    // between tiles and for the final addition of the parts (parts * group * head_dim <= 1024 floats)
     const int cols = gs * hd;
-    const int pieces = gs * lpk;
-    int parts = kSmallWorkers / pieces;
-    if (parts * cols > 1024) parts = 1024 / cols;
-    if (parts < 1) parts = 1;
-    const int items = parts * pieces;
+    int parts;
+    if constexpr (use_mma) {
+    // --- value accumulation on the tensor cores; the parts' fp32 sums meet in `red` ([part][gs * hd])
+      parts = v_parts;
+      float vacc[4] = {0.f, 0.f, 0.f, 0.f};  // D[16 dims of tile my_dt][query heads]
 #pragma unroll 1
-    for (int t = 0; t < ntiles; ++t) {
-      const int t0 = j0 + t * tile_keys, t1 = min(j1, t0 + tile_keys);
-      if (t > 0) {
-        small_sync();
-        fetch_tile(vbase, t0, t1);
-      }
-      cp_async_wait_all();
-      if (newpos >= t0 && newpos < t1 && wtid < lpk)  // the new value row joins its tile
-        *reinterpret_cast<uint4*>(tile + (newpos - t0) * row_bytes + ((wtid ^ ((newpos - t0) & 7)) << 4)) =
-            *reinterpret_cast<const uint4*>(vn + wtid * 8);
-      small_sync();  // the tile has landed, and (first tile) the probabilities are complete
-      const int tk = t1 - t0;
-#pragma unroll 1
-      for (int item = wtid; item < items; item += kSmallWorkers) {
-        const int part = item / pieces, pc = item - part * pieces;
-        const int g = pc / lpk, piece = pc - g * lpk;
-        float* mine = red + (part * gs + g) * hd + piece * 8;
-        float acc[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = (t == 0) ? 0.f : mine[e];
-        const float* pr = sc + g * chunk + (t0 - j0);
-#pragma unroll 2
-        for (int kk = part; kk < tk; kk += parts) {
-          float vf[8];
-          unpack8(*reinterpret_cast<const uint4*>(tile + kk * row_bytes + ((piece ^ (kk & 7)) << 4)), vf);
-          const float w = pr[kk];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) acc[e] = fmaf(w, vf[e], acc[e]);
+      for (int t = 0; t < ntiles; ++t) {
+        const int t0 = j0 + t * tile_keys, t1 = min(j1, t0 + tile_keys);
+        if (t > 0) {
+          small_sync();
+          fetch_tile(vbase, t0, t1);
         }
+        cp_async_wait_all();
+        if (newpos >= t0 && newpos < t1 && wtid < lpk)  // the new value row joins its tile
+          *reinterpret_cast<uint4*>(tile + (newpos - t0) * row_bytes + ((wtid ^ ((newpos - t0) & 7)) << 4)) =
+              *reinterpret_cast<const uint4*>(vn + wtid * 8);
+        const int tk = t1 - t0;
+        if (tk & 15) {
+          // the last 16-key block of a short tile: rows past the tile's keys meet zero probabilities, but what
+          // the tile holds there must be finite for that product to be zero
+          const int count = 16 - (tk & 15);
+          for (int it = wtid; it < count * lpk; it += kSmallWorkers)
+            *reinterpret_cast<uint4*>(tile + (tk + it / lpk) * row_bytes + ((it % lpk) << 4)) = make_uint4(0, 0, 0, 0);
+        }
+        small_sync();  // the tile has landed, and (first tile) the probabilities are complete
+        if (my_part < parts) {
+          const float* pr = sc + lg * chunk + (t0 - j0);
+#pragma unroll 1
+          for (int k16 = my_part; k16 * 16 < tk; k16 += parts) {
+            // B fragment: probabilities of query head lane / 4 for keys 2 * (lane % 4) + {0, 1} and + 8 of the block
+            const int key = k16 * 16 + lt * 2;
+            float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+            if (lg < gs) {
+              if (key < tk) p0 = pr[key];
+              if (key + 1 < tk) p1 = pr[key + 1];
+              if (key + 8 < tk) p2 = pr[key + 8];
+              if (key + 9 < tk) p3 = pr[key + 9];
+            }
+            // A fragment: V^T from the tile's rows (keys): matrices (keys 0-7 | 8-15) x (dims 0-7 | 8-15) of the block
+            const int row = k16 * 16 + (lane & 7) + (lane >> 4) * 8;
+            uint32_t af[4];
+            ldmatrix_x4_trans(af, piece_addr(row, my_dt * 2 + ((lane >> 3) & 1)));
+            mma_bf16_16816(vacc, af, pack2(p0, p1), pack2(p2, p3));
+          }
+        }
+      }
+      if (my_part < parts) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) mine[e] = acc[e];
+        for (int e = 0; e < 4; ++e) {
+          const int n = lt * 2 + (e & 1), d = my_dt * 16 + lg + (e >> 1) * 8;
+          if (n < gs) red[my_part * cols + n * hd + d] = vacc[e];
+        }
+      }
+    } else {
+    // --- value accumulation: an item is (part of the keys, head of the group, 16-byte piece of the
+      // output row); part p takes keys p, p + parts, ...; the fp32 sums of an item live in `red`
+      // between tiles and for the final addition of the parts (parts * group * head_dim <= 1024 floats)
+      const int pieces = gs * lpk;
+      parts = kSmallWorkers / pieces;
+      if (parts * cols > 1024) parts = 1024 / cols;
+      if (parts < 1) parts = 1;
+      const int items = parts * pieces;
+#pragma unroll 1
+      for (int t = 0; t < ntiles; ++t) {
+        const int t0 = j0 + t * tile_keys, t1 = min(j1, t0 + tile_keys);
+        if (t > 0) {
+          small_sync();
+          fetch_tile(vbase, t0, t1);
+        }
+        cp_async_wait_all();
+        if (newpos >= t0 && newpos < t1 && wtid < lpk)  // the new value row joins its tile
+          *reinterpret_cast<uint4*>(tile + (newpos - t0) * row_bytes + ((wtid ^ ((newpos - t0) & 7)) << 4)) =
+              *reinterpret_cast<const uint4*>(vn + wtid * 8);
+        small_sync();  // the tile has landed, and (first tile) the probabilities are complete
+        const int tk = t1 - t0;
+#pragma unroll 1
+        for (int item = wtid; item < items; item += kSmallWorkers) {
+          const int part = item / pieces, pc = item - part * pieces;
+          const int g = pc / lpk, piece = pc - g * lpk;
+          float* mine = red + (part * gs + g) * hd + piece * 8;
+          float acc[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] = (t == 0) ? 0.f : mine[e];
+          const float* pr = sc + g * chunk + (t0 - j0);
+#pragma unroll 2
+          for (int kk = part; kk < tk; kk += parts) {
+            float vf[8];
+            unpack8(*reinterpret_cast<const uint4*>(tile + kk * row_bytes + ((piece ^ (kk & 7)) << 4)), vf);
+            const float w = pr[kk];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] = fmaf(w, vf[e], acc[e]);
+          }
+#pragma unroll
+          for (int e = 0; e < 8; ++e) mine[e] = acc[e];
+        }
       }
     }
     small_sync();
@@ -1509,7 +1619,7 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
       A.len = cx.misc->len_s[layer];
       A.stamp = p.att_epoch + static_cast<uint32_t>(layer) + 1u;
       const int nch = decode_chunks(A.len + 1, p.batch * p.kv_heads, cx.grid, gs, kAttScoreBytes);
-      if (!small_attention(cx, A, wtid, nch)) return;
+      if (!(gs >= 2 ? small_attention<true>(cx, A, wtid, nch) : small_attention<false>(cx, A, wtid, nch))) return;
       trace_event(cx, wtid, EV_ATTENTION_DONE);
       if (!small_ok(cx, ok)) return;
       project(gp + 1, nch);                  // o_proj rows + residual -> stamped residual
@@ -1550,7 +1660,7 @@ __device__ void small_worker_loop(const Ctx& cx, int wtid) {
     A.len = cx.misc->len_s[layer];
     A.stamp = p.att_epoch + static_cast<uint32_t>(layer) + 1u;
     const int nch = decode_chunks(A.len + 1, p.batch * p.kv_heads, cx.grid, gs, kAttScoreBytes);
-    if (!small_attention(cx, A, wtid, nch)) return;       // RoPE, KV append, split-context attention
+    if (!(gs >= 2 ? small_attention<true>(cx, A, wtid, nch) : small_attention<false>(cx, A, wtid, nch))) return;       // RoPE, KV append, split-context attention
     trace_event(cx, wtid, EV_ATTENTION_DONE);
     if (handoff) {
       if (!small_ok(cx, ok)) return;         // the o projection polls the stamped attention partials

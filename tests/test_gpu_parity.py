@@ -108,15 +108,18 @@ def test_decode_tiny_matches_reference(device, name, engine):
 @pytest.mark.parametrize("engine", ["tcgen05", "fma"])
 def test_decode_smollm_135m_64_steps(device, engine):
     ties, run = run_golden_decode("c1", device, engine, deep=True)
-    # measured on a B200: 5 of 64 greedy tokens differ from the CPU-made golden ones (both engines), each at a
-    # position where the reference's own top two logits tie in bf16 (token_agrees checks that)
+    # measured on a B200: 5 (tensor engine) and 4 (small-launch kernel) of 64 greedy tokens differ from the
+    # CPU-made golden ones, each at a position where the reference's own top two logits tie in bf16
+    # (token_agrees checks that)
     assert run == 67 and ties <= 5
 
 
 @pytest.mark.parametrize("engine", ["auto", "tcgen05"])
 def test_decode_qwen2_half_b_64_steps(device, engine):
     ties, run = run_golden_decode("c2", device, engine, deep=True)
-    assert run == 67 and ties <= 1  # measured on a B200: 1 of 64 (both engines), a bf16 tie of the reference's own logits
+    # measured on a B200: 1 of 64 (tensor engine) and 2 of 64 (small-launch kernel, whose attention sums in
+    # tensor-core order for grouped heads), each a bf16 tie of the reference's own top two logits
+    assert run == 67 and ties <= 2
 
 
 def run_yardstick_decode(name, device):
