@@ -46,9 +46,10 @@ struct Carve {
 int qkv_width(const mk_config& c) { return (c.q_heads + 2 * c.kv_heads) * c.head_dim; }
 // Token-operand descriptors of the tensor engine: (normalised rows, attention output, SiLU*up, mk_linear's
 // source) x (token tiles of 16, 32, 64), behind the weight descriptors.
-constexpr int kOperandKinds = 4, kOperandMaps = kOperandKinds * 3;
+constexpr int kOperandTiles = 4;  // token tiles of 16, 32, 64, 128
+constexpr int kOperandKinds = 4, kOperandMaps = kOperandKinds * kOperandTiles;
 enum { OPERAND_XNORM = 0, OPERAND_ATTN = 1, OPERAND_ACT = 2, OPERAND_LINEAR = 3 };
-int token_tile_of(int m) { return m <= 16 ? 16 : (m <= 32 ? 32 : 64); }
+int token_tile_of(int m) { return m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : 128)); }
 size_t maps_per_table(const mk_config& c) { return 7 * static_cast<size_t>(c.layers) + 1; }
 size_t phases_per_table(const mk_config& c) { return 4 * static_cast<size_t>(c.layers) + 1; }
 
@@ -584,11 +585,11 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
         ph[2].add_parts = ph[1].ksplit; ph[2].partial = partial; ph[2].h_out = hidden_a;
         prev_parts = ph[3].ksplit;
       }
-      for (int t = 0; t < 3; ++t) {  // token operands: normalised rows, attention output, SiLU*up
-        ph[0].bmap[t] = operand_maps + OPERAND_XNORM * 3 + t;
-        ph[1].bmap[t] = operand_maps + OPERAND_ATTN * 3 + t;
-        ph[2].bmap[t] = operand_maps + OPERAND_XNORM * 3 + t;
-        ph[3].bmap[t] = operand_maps + OPERAND_ACT * 3 + t;
+      for (int t = 0; t < kOperandTiles; ++t) {  // token operands: normalised rows, attention output, SiLU*up
+        ph[0].bmap[t] = operand_maps + OPERAND_XNORM * kOperandTiles + t;
+        ph[1].bmap[t] = operand_maps + OPERAND_ATTN * kOperandTiles + t;
+        ph[2].bmap[t] = operand_maps + OPERAND_XNORM * kOperandTiles + t;
+        ph[3].bmap[t] = operand_maps + OPERAND_ACT * kOperandTiles + t;
       }
       // One TMA descriptor per matrix, boxed to the tile height and the K chunks per copy its phase chose.
       const void* mats[7] = {lw.q, lw.k, lw.v, lw.o, lw.gate, lw.up, lw.down};
@@ -609,7 +610,7 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
       head.add_parts = prev_parts; head.partial = partial;
     }
     finish_phase_tc(head, h->grid, false, c.max_tokens);
-    for (int t = 0; t < 3; ++t) head.bmap[t] = operand_maps + OPERAND_XNORM * 3 + t;
+    for (int t = 0; t < kOperandTiles; ++t) head.bmap[t] = operand_maps + OPERAND_XNORM * kOperandTiles + t;
     if (int e = encode_phase_weight_map(&tmaps_host[7 * L], w->lm_head, c.vocab, c.hidden, head, use3d)) return e;
   }
   // Table 2: the split-K table again for the small-launch kernel, whose mma.sync consumer takes tiles of
@@ -743,10 +744,10 @@ int mk_bind_weights(mk_handle h, const mk_weights* w, void* stream) {
     memset(operand_host, 0, sizeof(operand_host));
     const void* bases[3] = {at<bf16>(h, h->cv.xnorm), attn, act};
     const int widths[3] = {c.hidden, q_size, c.intermediate};
-    static const int tiles[3] = {16, 32, 64};
+    static const int tiles[kOperandTiles] = {16, 32, 64, 128};
     for (int kind = 0; kind < 3; ++kind)
-      for (int t = 0; t < 3; ++t)
-        if (int e = encode_operand_map(&operand_host[kind * 3 + t], bases[kind], c.max_tokens, widths[kind], tiles[t])) return e;
+      for (int t = 0; t < kOperandTiles; ++t)
+        if (int e = encode_operand_map(&operand_host[kind * kOperandTiles + t], bases[kind], c.max_tokens, widths[kind], tiles[t])) return e;
     MK_CUDA(cudaMemcpyAsync(operand_maps, operand_host, sizeof(operand_host), cudaMemcpyHostToDevice, s));
     MK_CUDA(cudaStreamSynchronize(s));
   }

@@ -207,9 +207,10 @@ __device__ __forceinline__ const GemmPhase* phase_at(const KParams& p, int gp) {
   return p.mode == MODE_LINEAR ? &p.linear_phase : p.phases + gp;
 }
 
-// Tokens per MMA (UMMA N) for a launch of m tokens: the smallest of 16, 32, 64 that holds them, 64 beyond.
-__device__ __forceinline__ int token_tile(int m) { return m <= 16 ? 16 : (m <= 32 ? 32 : 64); }
-__device__ __forceinline__ int token_tile_index(int m) { return m <= 16 ? 0 : (m <= 32 ? 1 : 2); }
+// Tokens per MMA (UMMA N) for a launch of m tokens: the smallest of 16, 32, 64, 128 that holds them, 128 beyond
+// (an MMA of 128 columns costs 64 issue cycles where two of 64 cost 92, and a weight tile is walked half as often).
+__device__ __forceinline__ int token_tile(int m) { return m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : 128)); }
+__device__ __forceinline__ int token_tile_index(int m) { return m <= 16 ? 0 : (m <= 32 ? 1 : (m <= 64 ? 2 : 3)); }
 
 // Every CTA walks its K range from a different starting entry (and wraps), so that at any moment the
 // grid's loads spread over all of a weight row's 128-byte columns.

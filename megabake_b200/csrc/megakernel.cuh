@@ -20,12 +20,12 @@ constexpr int kRingGranules = 120;       // keeps the CTA under 196 KiB of share
 constexpr int kRingBytes = kRingGranules * kGranule;
 constexpr int kChunkBars = 128;          // full/empty barrier pairs, indexed by chunk sequence number
 constexpr int kTok = MK_TOKEN_TILE;      // token columns an epilogue step reads from TMEM
-constexpr int kMaxTok = 64;              // largest token tile (UMMA N is 16, 32 or 64)
+constexpr int kMaxTok = 128;             // largest token tile (UMMA N is 16, 32, 64 or 128)
 constexpr int kBSlots = 32;              // activation K-chunks resident per CTA (two halves of 16)
 constexpr int kBHalf = kBSlots / 2;
 constexpr int kBSlotBytes = kTok * 128;  // 2 KiB
 constexpr int kBBytes = kBSlots * kBSlotBytes;
-constexpr int kTmemCols = 256;           // 2 buffers x 2 accumulators x 64 columns
+constexpr int kTmemCols = 512;           // 2 buffers x 2 accumulators x 128 columns: all of an SM's tensor memory
 constexpr int kMiscBytes = 4096;
 constexpr int kMiscTcBytes = 3072;       // tensor engine only: barriers of the activation ring
 constexpr int kSmemBytes = 1024 /*alignment slack*/ + kRingBytes + kBBytes + kMiscBytes + kMiscTcBytes;
@@ -62,7 +62,7 @@ constexpr int kTpFlagBytes = 256;        // head of a rank's exchange buffer: on
 // phase adds them, in slice order, while it builds its activation operand.
 struct GemmPhase {
   const CUtensorMap* tmap[3];  // device copies of the weights' TMA descriptors (tensor engine: box = 64 x rows x kb chunks)
-  const CUtensorMap* bmap[3];  // tensor engine: descriptors of the token operand for token tiles of 16, 32, 64 (box = 64 x tile)
+  const CUtensorMap* bmap[4];  // tensor engine: descriptors of the token operand for token tiles of 16, 32, 64, 128 (box = 64 x tile)
   const bf16* w[3];            // raw weight pointers [N, K]
   const bf16* bias[3];
   int n[3];                    // rows of each matrix
