@@ -1442,27 +1442,33 @@ __device__ __forceinline__ bool attention_phase(const Ctx& cx, const AttnArgs& A
   return A.decode ? attention_decode(cx, A, wtid) : attention_prompt(cx, A, wtid);
 }
 
-// Prefill: rotate q and k of every token in place in the qkv buffer.
+// Prefill: rotate q and k of every token in place in the qkv buffer.  An item is eight adjacent
+// pairs (i, i + head_dim / 2) of one head of one token: two 16-byte loads of the row, one each of the
+// cosine and sine rows, two 16-byte stores.
 __device__ __noinline__ void rope_phase(const Ctx& cx, int wtid) {
   const KParams& p = *cx.p;
-  const int hd = p.head_dim, half = hd / 2;
+  const int hd = p.head_dim, half = hd / 2, vecs = half / 8;
   const int heads = p.q_heads + p.kv_heads;  // q heads then k heads are contiguous in a qkv row
-  const long long items = static_cast<long long>(p.m) * heads * half;
-  for (long long it = static_cast<long long>(cx.cta) * kWorkers + wtid; it < items;
-       it += static_cast<long long>(cx.grid) * kWorkers) {
-    const int i = static_cast<int>(it % half);
-    const long long rest = it / half;
-    const int h = static_cast<int>(rest % heads);
-    const int t = static_cast<int>(rest / heads);
-    long long pos = p.pos[t];
-    if (pos < 0 || pos >= p.max_positions) pos = 0;
-    bf16* x = p.qkv + static_cast<size_t>(t) * p.qkv_ld + h * hd;
-    float first = ldcg_bf16(x + i), second = ldcg_bf16(x + i + half);
-    const float c = ldg_bf16(p.cos_t + pos * hd + i);
-    const float s = ldg_bf16(p.sin_t + pos * hd + i);
-    rope_pair(first, second, c, s, p.prefill_rope_style, first, second);
-    x[i] = __float2bfloat16_rn(first);
-    x[i + half] = __float2bfloat16_rn(second);
+  const int per_token = heads * vecs, items = p.m * per_token;
+  const int style = p.prefill_rope_style, qkv_ld = p.qkv_ld, max_positions = p.max_positions;
+  bf16* const qkv = p.qkv;
+  const bf16 *cos_t = p.cos_t, *sin_t = p.sin_t;
+  const long long* const positions = p.pos;
+  for (int it = cx.cta * kWorkers + wtid; it < items; it += cx.grid * kWorkers) {
+    const int t = it / per_token, rest = it - t * per_token;
+    const int h = rest / vecs, i = (rest - h * vecs) * 8;
+    long long pos = positions[t];
+    if (pos < 0 || pos >= max_positions) pos = 0;
+    bf16* x = qkv + static_cast<size_t>(t) * qkv_ld + h * hd + i;
+    float a[8], b[8], c[8], sn[8];
+    unpack8(__ldcg(reinterpret_cast<const uint4*>(x)), a);
+    unpack8(__ldcg(reinterpret_cast<const uint4*>(x + half)), b);
+    unpack8(__ldg(reinterpret_cast<const uint4*>(cos_t + pos * hd + i)), c);
+    unpack8(__ldg(reinterpret_cast<const uint4*>(sin_t + pos * hd + i)), sn);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) rope_pair(a[e], b[e], c[e], sn[e], style, a[e], b[e]);
+    *reinterpret_cast<uint4*>(x) = pack8(a);
+    *reinterpret_cast<uint4*>(x + half) = pack8(b);
   }
 }
 
