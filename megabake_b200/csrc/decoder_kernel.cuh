@@ -415,10 +415,13 @@ __device__ __noinline__ void mma_loop(const Ctx& cx) {
   const int ntok = token_tile(p.m);
   const int ntt = (p.m + ntok - 1) / ntok;
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&cx.misc->tmem_base);
-  const uint32_t idesc = umma_idesc_bf16(kTileRows, ntok);
+  // A tile of at most 64 weight rows is issued as an M = 64 MMA: in the running kernel an MMA's time is the read
+  // of its weight operand from shared memory (128 rows x 32 B), and half the rows are read in half the time.
+  const uint32_t idesc128 = umma_idesc_bf16(kTileRows, ntok), idesc64 = umma_idesc_bf16(64, ntok);
   const uint64_t desc_base = umma_desc_sw128(0);
+  const uint32_t desc_lo = static_cast<uint32_t>(desc_base), desc_hi = static_cast<uint32_t>(desc_base >> 32);
+  const uint32_t b_step = (static_cast<uint32_t>(ntok) * 128u) >> 4;
   const uint32_t ring_base = smem_u32(cx.smem_a), b_base = smem_u32(cx.smem_b);
-  const uint32_t b_chunk = static_cast<uint32_t>(ntok) * 128u;
   SmemMisc* misc = cx.misc;
   SmemMiscTc* tc = cx.tc;
   int seq = 0;
@@ -426,7 +429,8 @@ __device__ __noinline__ void mma_loop(const Ctx& cx) {
   for (int gp = 0; gp < p.n_gemm; ++gp) {
     const GemmPhase* ph = phase_at(p, gp);
     const int nacc = ph->nacc, nunits = ph->nunits, kslice = ph->kslice, kb = ph->kb;
-    const uint32_t a_chunk = static_cast<uint32_t>(ph->rows) * 128u;
+    const uint32_t a_step = (static_cast<uint32_t>(ph->rows) * 128u) >> 4;
+    const uint32_t idesc = ph->rows <= 64 ? idesc64 : idesc128;
     const int groups = kslice / kb;
     if (cx.cta >= nunits) continue;
     for (int unit = cx.cta; unit < nunits; unit += cx.grid) {
@@ -435,6 +439,7 @@ __device__ __noinline__ void mma_loop(const Ctx& cx) {
         if (!wait_mbar(cx, smem_u32(&misc->accempty[buf]), ((q >> 1) & 1u) ^ 1u, SITE_MMA_ACC, gp)) return;
         tc_fence_after();
         uint32_t accumulate = 0;
+        const uint32_t d0 = tmem + buf * 2u * kMaxTok;
         for (int i = 0; i < groups; ++i) {
           const uint32_t parity = (seq / kChunkBars) & 1;
           if (!wait_mbar(cx, smem_u32(&misc->full[seq % kChunkBars]), parity, SITE_MMA_FULL, gp)) return;
@@ -443,17 +448,26 @@ __device__ __noinline__ void mma_loop(const Ctx& cx) {
           // the producers recorded where they put this entry before they issued its copies
           const uint32_t a_addr = ring_base + static_cast<uint32_t>(misc->qstart[seq % kChunkBars]) * kGranule;
           const uint32_t b_addr = b_base + static_cast<uint32_t>(tc->bstart[seq % kChunkBars]) * kGranule;
-          for (int c = 0; c < kb; ++c) {
-            const uint64_t b_desc = desc_base + ((b_addr + c * b_chunk) >> 4);
-            for (int a = 0; a < nacc; ++a) {
-              const uint64_t a_desc = desc_base + ((a_addr + (a * kb + c) * a_chunk) >> 4);
-              const uint32_t d = tmem + (buf * 2u + static_cast<uint32_t>(a)) * kMaxTok;
-              umma_bf16(d, a_desc, b_desc, idesc, accumulate);
-              umma_bf16(d, a_desc + 2, b_desc + 2, idesc, 1u);
-              umma_bf16(d, a_desc + 4, b_desc + 4, idesc, 1u);
-              umma_bf16(d, a_desc + 6, b_desc + 6, idesc, 1u);
+          // descriptor low words of the entry's first chunk; a chunk further on is a constant further on
+          uint32_t a_lo = desc_lo + (a_addr >> 4), b_lo = desc_lo + (b_addr >> 4);
+          if (nacc == 1) {
+#pragma unroll 1
+            for (int c = 0; c < kb; ++c) {
+              umma_bf16_chunk(d0, a_lo, b_lo, desc_hi, idesc, accumulate);
+              accumulate = 1u;
+              a_lo += a_step;
+              b_lo += b_step;
             }
-            accumulate = 1u;
+          } else {  // gate and up: the second matrix's chunks follow the first matrix's in the entry
+            const uint32_t second = static_cast<uint32_t>(kb) * a_step;
+#pragma unroll 1
+            for (int c = 0; c < kb; ++c) {
+              umma_bf16_chunk(d0, a_lo, b_lo, desc_hi, idesc, accumulate);
+              umma_bf16_chunk(d0 + kMaxTok, a_lo + second, b_lo, desc_hi, idesc, accumulate);
+              accumulate = 1u;
+              a_lo += a_step;
+              b_lo += b_step;
+            }
           }
           umma_commit(smem_u32(&misc->empty[seq % kChunkBars]));
           umma_commit(smem_u32(&tc->bempty[seq % kChunkBars]));
@@ -658,7 +672,11 @@ __device__ __noinline__ bool worker_gemm_tc(const Ctx& cx, int gp, WorkerState& 
   const uint32_t accfull0 = smem_u32(&cx.misc->accfull[0]), accempty0 = smem_u32(&cx.misc->accempty[0]);
   const int my_cta = cx.cta, grid = cx.grid;
   const int quad = ((wtid >> 5) + 2) & 3;  // TMEM lane quadrant this warp may read
-  const int rloc = quad * 32 + (wtid & 31);
+  // M = 128: accumulator row r is TMEM lane r.  M = 64 (tiles of at most 64 rows): row r is lane 32 * (r / 16) + r % 16,
+  // the upper half of every quadrant is unused.
+  const bool m64 = rows <= 64;
+  const int lane_id = wtid & 31;
+  const int rloc = m64 ? (lane_id < 16 ? quad * 16 + lane_id : kTileRows) : quad * 32 + lane_id;
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&cx.misc->tmem_base);
   if (my_cta < nunits) {
     trace_event(cx, wtid, EV_PHASE_ENTER);
@@ -682,7 +700,7 @@ __device__ __noinline__ bool worker_gemm_tc(const Ctx& cx, int gp, WorkerState& 
           float pre[kTok];
           if (valid) epilogue_prefetch<kTok>(cx, ph, seg, n, t0, mt, pre);
           float v[2][kTok];
-          if (ok && quad * 32 < rows) {
+          if (ok && (m64 ? quad * 16 : quad * 32) < rows) {
             const uint32_t at = tmem + (static_cast<uint32_t>(quad * 32) << 16) + (buf * 2u) * kMaxTok + cg * kTok;
             tmem_ld16(at, v[0]);
             if (nacc == 2) tmem_ld16(at + kMaxTok, v[1]);

@@ -106,6 +106,38 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The four K = 16 steps of one 64-element K chunk in one go.  a_lo / b_lo are the low words of the two
+// operand descriptors (start address >> 4 plus the constant fields), `hi` their common high word; a step
+// advances both start addresses by 32 bytes.  Everything the issuing thread executes between two MMAs is a
+// 32-bit add: in the running kernel the pace of the MMAs is that thread's instruction stream (a tcgen05.mma
+// of up to 128 columns takes ~46 issue cycles; with descriptor arithmetic around each one it was ~160).
+__device__ __forceinline__ void umma_bf16_chunk(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .b64 da, db;\n\t.reg .b32 ta, tb;\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "setp.eq.b32 q, %4, %4;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t"
+      "add.u32 ta, %1, 2;\n\t"
+      "add.u32 tb, %2, 2;\n\t"
+      "mov.b64 da, {ta, %3};\n\t"
+      "mov.b64 db, {tb, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, q;\n\t"
+      "add.u32 ta, %1, 4;\n\t"
+      "add.u32 tb, %2, 4;\n\t"
+      "mov.b64 da, {ta, %3};\n\t"
+      "mov.b64 db, {tb, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, q;\n\t"
+      "add.u32 ta, %1, 6;\n\t"
+      "add.u32 tb, %2, 6;\n\t"
+      "mov.b64 da, {ta, %3};\n\t"
+      "mov.b64 db, {tb, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, q;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrive on an mbarrier once every MMA this thread issued so far has finished.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
