@@ -760,7 +760,6 @@ __device__ __noinline__ bool small_gemm_mma(const Ctx& cx, int gp, SmallState& s
   const bool per_unit = ksplit > 1;
   const int warp = wtid >> 5, lane = wtid & 31;
   const int kb = ph->kb;                          // K chunks per copy
-  const int ksteps = kb * 4;                      // 16-element K steps per copy
   const int row_tiles = (rows + 15) >> 4;         // <= 4
   const uint32_t chunk_bytes = static_cast<uint32_t>(rows) * 128u;
   const int rot = k_rotation(cx.cta, cx.grid, kslice / kb) * kb;

@@ -766,7 +766,6 @@ __device__ __noinline__ void norm_phase(const Ctx& cx, const GemmPhase* ph, int 
   const float eps = p.eps;
   bf16* const xnorm = p.xnorm;
   const float* const partial = ph->partial;
-  bf16* const h_out = ph->h_out;
   const int nvec = k / 8;
   const int parts = ph->add_parts;
   const uint4* wrow = reinterpret_cast<const uint4*>(ph->normw);
@@ -930,9 +929,18 @@ __device__ __noinline__ void fetch_cache_tile(uint32_t dst, const bf16* src, int
   // so that both addresses advance by constants (per_key divides kWorkers for every supported shape but
   // hpu in {3, 5, 6, 7}, which take the general loop).
   if (kWorkers % per_key == 0) {
-    const int rest = wtid % per_key, step = kWorkers / per_key;
+    int rest, step, key;
+    if ((per_key & (per_key - 1)) == 0) {  // a power of two (1, 2, 4 or 8 heads): shifts, no division
+      const int sh = 31 - __clz(per_key);
+      rest = wtid & (per_key - 1);
+      step = kWorkers >> sh;
+      key = wtid >> sh;
+    } else {
+      rest = wtid % per_key;
+      step = kWorkers / per_key;
+      key = wtid / per_key;
+    }
     const int head = rest >> shift, piece = rest & ((1 << shift) - 1);
-    int key = wtid / per_key;
     const uint4* from = reinterpret_cast<const uint4*>(src + static_cast<long long>(key) * ld) + rest;
     const long long from_step = static_cast<long long>(step) * ld / 8;  // in 16-byte units: ld is a multiple of 8
     uint32_t to = dst + (static_cast<uint32_t>(head) * tile_keys + key) * row_bytes;
@@ -1094,9 +1102,10 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A_i
       named_bar_sync(1, kWorkers);  // tile s is complete; every thread is done with tile s - 1
       issue(s + kDecStages - 1);
       const int tk = t1 - t0;
+      const int tk_shift = (tk & (tk - 1)) == 0 ? 31 - __clz(tk) : -1;  // full tiles hold a power of two of keys
 #pragma unroll 1
       for (int item = wtid; item < G * tk; item += kWorkers) {
-        const int g = item / tk, key = item - g * tk;
+        const int g = tk_shift >= 0 ? item >> tk_shift : item / tk, key = item - g * tk;
         const uint8_t* krow = tile + (g / gs) * sub_bytes + key * row_bytes;
         const float* qv = qs + g * hd;
         // four partial sums (pieces 0, 4, 8, ... / 1, 5, ... / ...): the chains have to be independent
