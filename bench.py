@@ -49,9 +49,9 @@ FALLBACK_BF16_TFLOPS = 1400.0
 # (config, batch, context); each entry names the summary under profiles/ that records the capture.
 NCU_TRAFFIC = {
     # dram__bytes_read.sum + dram__bytes_write.sum per launch.  The multi-pass capture runs the first four layers
-    # of the shape (read + write = 1.0095 x that launch's algorithmic bytes); the figure below scales the
+    # of the shape (read + write = 1.010 x that launch's algorithmic bytes); the figure below scales the
     # full launch's algorithmic bytes at context 1024 by the same ratio.
-    ("smollm-1.7b", 1, 1024): (int(3_625_848_832 * 1.0095), "profiles/megakernel_small_decode_smollm-1.7b_first-4-layers_sections.md"),
+    ("smollm-1.7b", 1, 1024): (int(3_625_848_832 * 1.010), "profiles/megakernel_small_decode_smollm-1.7b_first-4-layers_sections.md"),
 }
 
 
