@@ -40,12 +40,13 @@ int fail(int code, const char* fmt, ...) {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct Carve {
-  size_t ctrl, tmaps, phases, hidden, hidden2, xnorm, qkv, qkv_ll, act_ll, att_ll, attn_ll, res_a, res_b, attn, act, partial, partial2, att_xch, att_part, total;
+  size_t ctrl, tmaps, kvmaps, phases, hidden, hidden2, xnorm, qkv, qkv_ll, act_ll, att_ll, attn_ll, res_a, res_b, attn, act, partial, partial2, att_xch, att_part, total;
 };
 
 int qkv_width(const mk_config& c) { return (c.q_heads + 2 * c.kv_heads) * c.head_dim; }
 // Token-operand descriptors of the tensor engine: (normalised rows, attention output, SiLU*up, mk_linear's
 // source) x (token tiles of 16, 32, 64), behind the weight descriptors.
+constexpr int kCacheMapSets = 8;  // cache-descriptor sets a handle remembers (one per KV state it is called with in turn)
 constexpr int kOperandTiles = 4;  // token tiles of 16, 32, 64, 128
 constexpr int kOperandKinds = 4, kOperandMaps = kOperandKinds * kOperandTiles;
 enum { OPERAND_XNORM = 0, OPERAND_ATTN = 1, OPERAND_ACT = 2, OPERAND_LINEAR = 3 };
@@ -64,6 +65,7 @@ Carve carve(const mk_config& c) {
   const size_t m = static_cast<size_t>(c.max_tokens);
   v.ctrl = take(sizeof(Control));
   v.tmaps = take(sizeof(CUtensorMap) * (4 * maps_per_table(c) + 1 + kOperandMaps));  // split, plain and small-launch tables, mk_linear, token operands, row table
+  v.kvmaps = take(sizeof(CUtensorMap) * 2 * static_cast<size_t>(c.layers) * kCacheMapSets);  // decode attention: per set, key caches then value caches
   v.phases = take(sizeof(GemmPhase) * (4 * phases_per_table(c) + 1));  // + the one-token row table
   v.hidden = take(m * c.hidden * 2);
   v.hidden2 = take(m * c.hidden * 2);
@@ -194,6 +196,26 @@ int encode_operand_map(CUtensorMap* out, const void* base, int tokens, int k, in
   return MK_OK;
 }
 
+// Decode attention on the tensor engine: a cache [batch, capacity, kv_heads * head_dim] seen as
+// (64 dimensions, positions, 64-dimension chunks of a row, sequences); a box is one stage of a unit:
+// 64 x tile_keys positions x the unit's chunks, each chunk 128-byte swizzled.
+int encode_cache_map(CUtensorMap* out, const void* base, int batch, int capacity, int row_elems, int tile_keys, int unit_chunks) {
+  if (reinterpret_cast<uintptr_t>(base) % 16) return fail(MK_ERR_ALIGNMENT, "cache base %p is not 16-byte aligned", base);
+  auto fn = encode_fn();
+  if (!fn) return fail(MK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(kChunkK), static_cast<cuuint64_t>(capacity),
+                              static_cast<cuuint64_t>(row_elems / kChunkK), static_cast<cuuint64_t>(batch)};
+  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(row_elems) * 2, static_cast<cuuint64_t>(kChunkK) * 2,
+                                 static_cast<cuuint64_t>(capacity) * row_elems * 2};
+  const cuuint32_t box[4] = {static_cast<cuuint32_t>(kChunkK), static_cast<cuuint32_t>(tile_keys), static_cast<cuuint32_t>(unit_chunks), 1};
+  const cuuint32_t elem[4] = {1, 1, 1, 1};
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MK_ERR_CUDA, "cuTensorMapEncodeTiled (cache) failed with %d", (int)r);
+  return MK_OK;
+}
+
 }  // namespace
 
 struct mk_handle_s {
@@ -215,6 +237,13 @@ struct mk_handle_s {
   int trace_cap;
   int small_ring;       // weight ring of the small-launch kernel, 1 KiB granules
   int fat_copy;         // largest weight copy of the small-launch tables, bytes (three to four fit the ring)
+  struct CacheMapSet {
+    std::vector<const void*> seen;  // cache pointers the set's descriptors were encoded for (keys, then values)
+    int capacity = 0, batch = 0;
+    uint64_t used = 0;              // launch counter at the last use (least recently used is replaced)
+  };
+  CacheMapSet kv_sets[kCacheMapSets];
+  bool kv_maps_ok;      // the driver takes the four-dimensional view of a cache
   bool use3d;           // weight descriptors of the tensor engine are three-dimensional (several K chunks per copy)
   uint32_t tp_epoch;    // all-reduces launched so far (tensor parallel)
   uint8_t* tp_peer[kMaxTp];
@@ -469,6 +498,7 @@ int mk_create(const mk_config* config, void* workspace, size_t workspace_bytes, 
     h->use3d = getenv("MEGABAKE_NO_3D_MAPS") == nullptr &&
                encode_weight_map3(&probe, workspace, 128, 256, 64, 2) == MK_OK;
   }
+  h->kv_maps_ok = getenv("MEGABAKE_NO_CACHE_MAPS") == nullptr;
   h->tp_epoch = 0;
   h->tp_bound = false;
   for (int r = 0; r < kMaxTp; ++r) h->tp_peer[r] = nullptr;
@@ -862,6 +892,52 @@ int decode_once(mk_handle h, const int64_t* ids, const int64_t* positions, int b
   p.phases = at<GemmPhase>(h, h->cv.phases) + (p.split ? 0 : phases_per_table(h->cfg));
   const bool small = !ragged && batch <= kSplitTokens && small_launch_ok(h, capacity);
   p.ragged = ragged ? 1 : 0;
+  if (!small && h->kv_maps_ok) {
+    // Tiled descriptors of the caches for the tensor engine's decode attention, encoded again only when a
+    // cache pointer or the geometry differs from the last call's (the copy is ordered on `stream`
+    // before the launch; its pageable source is staged before cudaMemcpyAsync returns).
+    const mk_config& c = h->cfg;
+    const int gs = c.q_heads / c.kv_heads, row_elems = c.kv_heads * c.head_dim;
+    const int hpu = decode_heads_per_unit(c.kv_heads, gs, c.head_dim);
+    const int tile_keys = kDecTileBytes / (c.head_dim * 2 * hpu);
+    const bool shape_ok = (hpu & (hpu - 1)) == 0 && tile_keys % 16 == 0 && tile_keys <= 256 && c.head_dim % kChunkK == 0;
+    int slot = -1, oldest = 0;
+    for (int i = 0; i < kCacheMapSets && shape_ok && slot < 0; ++i) {
+      const auto& set = h->kv_sets[i];
+      if (set.used < h->kv_sets[oldest].used) oldest = i;
+      bool same = static_cast<int>(set.seen.size()) == 2 * L && set.capacity == capacity && set.batch == batch;
+      for (int l = 0; l < L && same; ++l) same = set.seen[l] == key_caches[l] && set.seen[L + l] == value_caches[l];
+      if (same) slot = i;
+    }
+    CUtensorMap* const device_sets = at<CUtensorMap>(h, h->cv.kvmaps);
+    if (shape_ok && slot < 0) {
+      std::vector<CUtensorMap> fresh(2 * static_cast<size_t>(L));
+      bool encoded = true;
+      for (int l = 0; l < L && encoded; ++l) {
+        encoded = encode_cache_map(&fresh[l], key_caches[l], batch, capacity, row_elems, tile_keys, hpu * (c.head_dim / kChunkK)) == MK_OK &&
+                  encode_cache_map(&fresh[L + l], value_caches[l], batch, capacity, row_elems, tile_keys, hpu * (c.head_dim / kChunkK)) == MK_OK;
+      }
+      if (encoded) {
+        slot = oldest;
+        MK_CUDA(cudaMemcpyAsync(device_sets + static_cast<size_t>(slot) * 2 * L, fresh.data(), fresh.size() * sizeof(CUtensorMap),
+                                cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+        auto& set = h->kv_sets[slot];
+        set.seen.assign(2 * static_cast<size_t>(L), nullptr);
+        for (int l = 0; l < L; ++l) {
+          set.seen[l] = key_caches[l];
+          set.seen[L + l] = value_caches[l];
+        }
+        set.capacity = capacity;
+        set.batch = batch;
+      } else {
+        h->kv_maps_ok = false;  // this driver refuses the view: plain copies from here on
+      }
+    }
+    if (slot >= 0) {
+      h->kv_sets[slot].used = static_cast<uint64_t>(h->launches) + 1;
+      p.kv_maps = device_sets + static_cast<size_t>(slot) * 2 * L;
+    }
+  }
   if (small) p.phases = at<GemmPhase>(h, h->cv.phases) + 2 * phases_per_table(h->cfg);
   p.n_gemm = 4 * L + 1;
   p.nbar = 7 * L + 1;  // tensor engine: five per layer and one behind each norm phase (two per layer, one for the lm_head)

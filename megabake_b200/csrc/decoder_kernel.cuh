@@ -70,6 +70,9 @@ struct SmemMiscTc {
   uint8_t bgran[kChunkBars];
   int b_ready;  // projection phases whose activation operand is complete in global memory (workers -> activation producer)
   int a_ready;  // gated projection phases whose weights may be fetched: the workers no longer use the ring (workers -> weight producer)
+  int kv_seq;   // cache tiles fetched by TMA so far in this launch (stage and barrier parity of the next one)
+  uint64_t kvfull[8];   // cache stages: the copy has landed
+  uint64_t kvempty[8];  // cache stages: every worker warp is done with the tile
 };
 static_assert(sizeof(SmemMiscTc) <= kMiscTcBytes, "tensor-engine misc block too large");
 static_assert(kBBytes / kGranule < 256, "activation ring positions are kept in bytes");
@@ -100,7 +103,7 @@ struct WorkerState {
 __device__ __forceinline__ bool give_up(const Ctx& cx, int site, int detail) {
   if (ld_relaxed_u32(&cx.ctrl->abort) != 0) return true;
   const bool internal = site == SITE_PRODUCER_EMPTY || site == SITE_MMA_FULL || site == SITE_MMA_B || site == SITE_MMA_ACC ||
-                        site == SITE_EPI_ACC || site == SITE_B_EMPTY;
+                        site == SITE_EPI_ACC || site == SITE_B_EMPTY || site == SITE_KV_TILE;
   if (clock64() > cx.deadline + (internal ? (cx.p->timeout_cycles >> 3) : 0)) {
     if (atomicCAS(&cx.ctrl->status, 0, static_cast<int>(MK_STATUS_TIMEOUT)) == 0) {
       cx.ctrl->where = site;
@@ -858,6 +861,7 @@ struct AttnArgs {
   int combine;        // 1: a split context is summed here into `out`; 0: the consumer sums att_part
   uint32_t stamp;     // value the chunks of this phase publish with their softmax statistics
   float scale;
+  const CUtensorMap *kmap, *vmap;  // decode: tiled descriptors of the two caches (see attention_decode), or null
 };
 
 __device__ __forceinline__ void rope_pair(float x1, float x2, float c, float s, int style, float& first, float& second) {
@@ -901,7 +905,7 @@ __device__ __forceinline__ int decode_chunks(int keys, int rows, int grid, int g
 // projection that follows, GemmPhase::gate): three stages of 32 KB keep two tiles, 64 KB per SM, in
 // flight.
 constexpr int kDecStages = 3;
-constexpr int kDecScratchBytes = 11 * 1024;  // q [8][128] fp32, value partial sums [1024] fp32, new keys/values [2][512] bf16, statistics
+constexpr int kDecScratchBytes = 13 * 1024;  // q [8][128] fp32 and bf16, value partial sums [1024] fp32, new keys/values [2][512] bf16, statistics
 constexpr int kDecTileBytes = 32 * 1024;     // one stage
 static_assert(kScoreBytes + kDecScratchBytes <= kBBytes, "scores and scratch exceed their region");
 static_assert(kDecStages * kDecTileBytes <= kRingBytes, "cache stages exceed the weight ring");
@@ -1289,6 +1293,532 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A_i
   return true;
 }
 
+// The same phase as a stream without a block barrier per tile, for long chunks and caches the host has
+// described (AttnArgs::kmap / vmap): one tiled TMA copy brings a stage (64 dimensions x tile_keys positions x
+// the unit's 64-dimension chunks, 128-byte swizzled: [chunk][key][128 B]), both products run on mma.sync
+// (scores: D[16 keys][heads] = K tile x q; values: D[16 dims][heads] += V tile^T x p), warp w works for KV
+// head w % hpu, waits for a stage's `full` barrier, releases it on its `empty` barrier, and the warps take
+// turns issuing the copy two tiles ahead.  The block meets only around what is exchanged between warps:
+// the scores -> statistics -> probabilities hand-over and the tiles that are written by hand (new row,
+// zeroed tail).  Measured on the 1.7B shape at context 1024: chunks of 513 / 1025 keys (batch 16 / 32) 4.5 % /
+// 9 % faster per step than attention_decode, chunks of 256 keys and fewer 2-7 % slower (a short chunk never
+// fills the pipeline), hence decode_stream_ok().
+__device__ __forceinline__ bool decode_stream_ok(const KParams& p, const AttnArgs& A, int grid) {
+  if (A.kmap == nullptr) return false;
+  const int gs = p.q_heads / p.kv_heads, hd = p.head_dim;
+  const int hpu = decode_heads_per_unit(p.kv_heads, gs, hd);
+  const int tile_keys = kDecTileBytes / (hd * 2 * hpu);
+  if ((hpu & (hpu - 1)) != 0 || (tile_keys & 15) != 0) return false;
+  const int n_max = A.len + 1;
+  const int nch = decode_chunks(n_max, p.batch * (p.kv_heads / hpu), grid, gs * hpu);
+  return (n_max + nch - 1) / nch >= 12 * tile_keys;
+}
+
+__device__ __noinline__ bool attention_decode_stream(const Ctx& cx, const AttnArgs& A_in, int wtid) {
+  // Private copies of the arguments and of the parameters this phase reads: every poll, copy wait and block
+  // barrier below is a compiler barrier for memory, behind which a value that lives behind a reference is
+  // loaded again (a kernel parameter through the context: two dependent loads).
+  const AttnArgs A = A_in;
+  struct {
+    int head_dim, q_heads, kv_heads, batch, max_positions, rope_style, prefill_rope_style, m;
+    const bf16 *cos_t, *sin_t;
+    float *att_xch, *att_part;
+    long long* pos;
+  } p = {cx.p->head_dim, cx.p->q_heads, cx.p->kv_heads, cx.p->batch, cx.p->max_positions, cx.p->rope_style,
+         cx.p->prefill_rope_style, cx.p->m, cx.p->cos_t, cx.p->sin_t, cx.p->att_xch, cx.p->att_part, cx.p->pos};
+  const int hd = p.head_dim, half = hd / 2;
+  const int gs = p.q_heads / p.kv_heads;
+  const int hpu = decode_heads_per_unit(p.kv_heads, gs, hd);  // KV heads per unit
+  const int G = gs * hpu;                                  // query heads per unit (<= 8)
+  const int groups = p.kv_heads / hpu;
+  const int rows = p.batch * groups;
+  const int n_max = A.len + 1;
+  const int warp = wtid >> 5, lane = wtid & 31;
+  const int lpk = hd / 8;  // 16-byte pieces per head row
+  const int nch = decode_chunks(n_max, rows, cx.grid, G);
+  const int chunk = (n_max + nch - 1) / nch;
+  const int units = rows * nch;
+  const int row_bytes = hd * 2;
+  const int tile_keys = kDecTileBytes / (row_bytes * hpu);
+  const int sub_bytes = tile_keys * row_bytes;     // one head's sub-tile
+  const int stage_bytes = sub_bytes * hpu;
+
+  float* sc = reinterpret_cast<float*>(cx.smem_b);                                      // [G][chunk]
+  uint8_t* tiles = cx.smem_a;                                                           // [stages][hpu][tile_keys][hd] bf16, in the weight ring
+  float* qs = reinterpret_cast<float*>(cx.smem_b + kBBytes - kDecScratchBytes);         // [G][hd]
+  float* red = qs + 8 * 128;                                                            // [worker warps][8] x 2, then [parts][G*hd]
+  bf16* kn = reinterpret_cast<bf16*>(red + 1024);                                       // [hpu][hd]
+  bf16* vn = kn + 512;                                                                  // [hpu][hd]
+  float* stat = reinterpret_cast<float*>(vn + 512);                                     // [16]: max[8], sum[8]
+  bf16* qb = reinterpret_cast<bf16*>(stat + 16);                                        // [G][hd], q again as bf16 (exact)
+  const uint32_t tiles_addr = smem_u32(tiles);
+  // Both products run on the warp-level tensor cores when the unit's KV heads divide the eight worker
+  // warps: one mma.sync (m16n8k16) multiplies 16 cached positions x 16 head dimensions by the (up to
+  // eight) query heads of a KV head, where the CUDA-core loops needed 17 instructions per lane for eight
+  // elements and kept this phase, not the cache stream, bound by instruction issue.
+  //   scores:  D[16 keys][heads]  = K tile (ldmatrix)        x q[dims][heads]   (q fragments stay in registers)
+  //   values:  D[16 dims][heads] += V tile^T (ldmatrix.trans) x p[keys][heads]
+  // Warp w works for KV head w % hpu; the 8 / hpu warps of a head split the 16-key blocks (scores) and
+  // the 16-dimension tiles of the output row (values).
+  constexpr bool use_mma = true;  // the caller checked decode_stream_ok()
+  // Tensor-core layout of a stage: the unit's cache rows as sub-tiles of 64 dimensions, [chunk][key][128 B]
+  // with the 16-byte pieces of a row exchanged by key % 8 (the 128-byte swizzle of a tiled TMA copy, also
+  // what the cp.async path writes), chunk = head * (head_dim / 64) + dimension / 64.
+  const int cph = hd / 64;                       // chunks per head
+  const uint32_t csub = tile_keys * 128u;        // one chunk's sub-tile
+  auto piece_at = [&](uint32_t stage, int head, int key, int piece) -> uint32_t {
+    return stage + (head * cph + (piece >> 3)) * csub + key * 128u + (((piece & 7) ^ (key & 7)) << 4);
+  };
+  // With descriptors of the two caches (decode through mk_decode*), one tiled TMA copy brings a whole stage
+  // (box = 64 dimensions x tile_keys positions x the unit's chunks); cp.async, 16 bytes per thread and
+  // request, measured 17 GB/s per SM on this stream, a third of an SM's share of HBM.
+  constexpr bool use_tma = true;
+  const uint32_t kvfull0 = smem_u32(&cx.tc->kvfull[0]), kvempty0 = smem_u32(&cx.tc->kvempty[0]);
+  const uint64_t kv_policy = l2_policy_evict_first();
+  int gtile = cx.tc->kv_seq;  // cache tiles issued by this CTA before this unit (same value in every thread)
+  const int my_head = warp & (hpu - 1), head_warps = kWorkerWarps / hpu, my_slot = warp / hpu;
+  const int ksteps = hd / 16, dim_tiles = hd / 16;
+  const int lg = lane >> 2, lt = lane & 3;
+
+  // value accumulation: an item is (part of the keys, query head of the unit, 16-byte piece of the output row);
+  // part q takes keys q, q + parts, ... of every tile; the fp32 sums of an item stay in `red` between tiles
+  const int cols = G * hd;
+  const int pieces = G * lpk;
+  int parts = kWorkers / pieces;
+  if (parts * cols > 1024) parts = 1024 / cols;
+  if (parts < 1) parts = 1;
+  const int items = parts * pieces;  // <= kWorkers
+  const int item_part = wtid / pieces, item_g = (wtid - item_part * pieces) / lpk, item_piece = wtid % lpk;
+
+#pragma unroll 1
+  for (int u = cx.cta; u < units; u += cx.grid) {
+    const int rowg = u / nch, ch = u - rowg * nch;
+    const int b = rowg / groups, kvh0 = (rowg - b * groups) * hpu;  // first KV head of the unit
+    const int filled = A.lens ? A.lens[b] : A.len;  // this sequence's cached positions; chunks past its end are empty
+    const int j0 = ch * chunk;
+    const int j1 = min(filled + 1, j0 + chunk);
+    const int cl = max(0, j1 - j0);
+    const int newpos = filled;
+    const bool owner = (filled >= j0 && filled < j1);
+    const int nt = (cl + tile_keys - 1) / tile_keys;
+    const bf16* kbase = A.k + b * A.kv_bstride + kvh0 * hd;
+    const bf16* vbase = A.v + b * A.kv_bstride + kvh0 * hd;
+    named_bar_sync(1, kWorkers);  // previous unit is done with the scratch and the stages
+
+    // Element s of the stream is K tile s (s < nt) or V tile s - nt; it uses stage s % kDecStages.
+    // Every call commits one group, an empty one past the end, so that the group count is uniform.
+    auto stage_of = [&](int s) -> int { return (gtile + s) % kDecStages; };
+    auto issue = [&](int s) {
+      if (s < 2 * nt) {
+        const int t = (s < nt) ? s : s - nt;
+        const int t0 = j0 + t * tile_keys, t1 = min(j1, t0 + tile_keys);
+        const uint32_t dst = tiles_addr + stage_of(s) * stage_bytes;
+        if (use_tma) {
+          if (wtid == ((s & (kWorkerWarps - 1)) << 5)) {  // the warps take turns: issuing costs its thread ~0.7 us
+            const int use = (gtile + s) / kDecStages;     // earlier uses of this stage in the launch
+            if (use > 0 && !wait_mbar(cx, kvempty0 + stage_of(s) * 8u, (use - 1) & 1, SITE_KV_TILE, -s)) return;
+            fence_proxy_async_all();  // the stage was read, and maybe patched, through the generic proxy
+            const uint32_t bar = kvfull0 + stage_of(s) * 8u;
+            mbar_expect_tx(bar, static_cast<uint32_t>(stage_bytes));
+            tma_load_4d(dst, (s < nt) ? A.kmap : A.vmap, 0, t0, kvh0 * cph, b, bar, kv_policy);
+          }
+        }
+      }
+      if (!use_tma) cp_async_commit();
+    };
+    // Tile s of the unit has landed (every thread waits: a copy's bytes are visible to the threads that saw its barrier flip).
+    auto landed = [&](int s) -> bool {
+      if (!use_tma) {
+        cp_async_wait_group<kDecStages - 2>();
+        return true;
+      }
+      return wait_mbar(cx, kvfull0 + stage_of(s) * 8u, ((gtile + s) / kDecStages) & 1, SITE_KV_TILE, s);
+    };
+#pragma unroll
+    for (int s = 0; s < kDecStages - 1; ++s) issue(s);
+
+    // --- q of every query head of the unit and the new keys (rotated if asked), and the new values
+    {
+      long long pos = 0;
+      if (A.rope) {
+        pos = p.pos[b];
+        if (pos < 0 || pos >= p.max_positions) pos = 0;  // reported by the prologue
+      }
+#pragma unroll 1
+      for (int idx = wtid; idx < (G + hpu) * half; idx += kWorkers) {
+        const int g = idx / half, i = idx - g * half;  // g < G: query head g of the unit; else new key of KV head g - G
+        const bf16* src = (g < G) ? A.q + b * A.q_bstride + (kvh0 * gs + g) * hd
+                                  : A.knew + static_cast<long long>(b) * A.new_ld + (kvh0 + g - G) * hd;
+        float first = ldcg_bf16(src + i);
+        float second = ldcg_bf16(src + i + half);
+        if (A.rope) {
+          const float c = ldg_bf16(p.cos_t + pos * hd + i);
+          const float sn = ldg_bf16(p.sin_t + pos * hd + i);
+          rope_pair(first, second, c, sn, p.rope_style, first, second);
+        }
+        if (g < G) {
+          qs[g * hd + i] = first;
+          qs[g * hd + i + half] = second;
+          qb[g * hd + i] = __float2bfloat16_rn(first);  // exact: both are bf16 values
+          qb[g * hd + i + half] = __float2bfloat16_rn(second);
+        } else {
+          kn[(g - G) * hd + i] = __float2bfloat16_rn(first);
+          kn[(g - G) * hd + i + half] = __float2bfloat16_rn(second);
+        }
+      }
+#pragma unroll 1
+      for (int i = wtid; i < hpu * hd; i += kWorkers)
+        vn[i] = __float2bfloat16_rn(ldcg_bf16(A.vnew + static_cast<long long>(b) * A.new_ld + kvh0 * hd + i));
+    }
+    named_bar_sync(1, kWorkers);
+    uint32_t qfrag[8][2];  // B fragments of this warp's KV head: q[dims][query heads], one pair per 16 dimensions
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      qfrag[ks][0] = qfrag[ks][1] = 0u;
+      if (use_mma && ks < ksteps && lg < gs) {
+        const bf16* at = qb + (my_head * gs + lg) * hd + ks * 16 + lt * 2;
+        qfrag[ks][0] = *reinterpret_cast<const uint32_t*>(at);
+        qfrag[ks][1] = *reinterpret_cast<const uint32_t*>(at + 8);
+      }
+    }
+    if (owner) {  // in-kernel KV append: the unit's heads are adjacent in the cache row
+      bf16* kd = A.k + b * A.kv_bstride + static_cast<long long>(filled) * A.kv_ld + kvh0 * hd;
+      bf16* vd = A.v + b * A.kv_bstride + static_cast<long long>(filled) * A.kv_ld + kvh0 * hd;
+#pragma unroll 1
+      for (int i = wtid; i < hpu * hd; i += kWorkers) {
+        kd[i] = kn[i];
+        vd[i] = vn[i];
+      }
+    }
+    // The new position's row joins its tile (its row was not fetched): one 16-byte piece per thread.
+    auto patch = [&](uint8_t* tile, const bf16* fresh, int local) {
+      if (wtid < hpu * lpk) {
+        const int head = wtid / lpk, piece = wtid - head * lpk;
+        uint8_t* at = use_mma ? tile + piece_at(0u, head, local, piece)
+                              : tile + head * sub_bytes + local * row_bytes + ((piece ^ (local & 7)) << 4);
+        *reinterpret_cast<uint4*>(at) = *reinterpret_cast<const uint4*>(fresh + head * hd + piece * 8);
+      }
+    };
+    bool tiles_ok = true;
+
+    // A tile is done with (this warp's share): one arrival per warp frees its stage for the copy S - 1 tiles on.
+    auto release = [&](int s) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(kvempty0 + stage_of(s) * 8u);
+    };
+    if (use_tma) {
+      // --- scores, pipelined: no block barrier per tile.  A warp waits for the tile's copy, takes the scores of
+      // its head's key blocks, releases the stage; the warp whose turn it is then issues the copy S - 1 tiles on.
+      // Only the tile that holds the new position needs the block (its row is patched in by a few threads).
+#pragma unroll 1
+      for (int s = 0; s < nt; ++s) {
+        const int t0 = j0 + s * tile_keys, t1 = min(j1, t0 + tile_keys);
+        uint8_t* tile = tiles + stage_of(s) * stage_bytes;
+        tiles_ok = landed(s) && tiles_ok;
+        if (newpos >= t0 && newpos < t1) {
+          patch(tile, kn, newpos - t0);
+          fence_proxy_async_all();
+          named_bar_sync(1, kWorkers);
+        }
+        const int tk = t1 - t0;
+        const uint32_t stage = smem_u32(tile);
+#pragma unroll 1
+        for (int blk = my_slot; blk * 16 < tk; blk += head_warps) {
+          float d[4] = {0.f, 0.f, 0.f, 0.f};
+          const int row = blk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll 2
+          for (int ks = 0; ks < ksteps; ++ks) {
+            uint32_t af[4];
+            ldmatrix_x4(af, piece_at(stage, my_head, row, ks * 2 + (lane >> 4)));
+            mma_bf16_16816(d, af, qfrag[ks][0], qfrag[ks][1]);
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int key = blk * 16 + lg + (e >> 1) * 8, n = lt * 2 + (e & 1);
+            if (n < gs && key < tk) sc[(my_head * gs + n) * chunk + (t0 - j0) + key] = bf16_round(d[e]) * A.scale;
+          }
+        }
+        release(s);
+        issue(s + kDecStages - 1);
+      }
+    }
+    // --- scores: one thread per (query head of the unit, key), a head_dim-term fp32 chain each
+#pragma unroll 1
+    for (int s = 0; s < (use_tma ? 0 : nt); ++s) {
+      const int t0 = j0 + s * tile_keys, t1 = min(j1, t0 + tile_keys);
+      uint8_t* tile = tiles + stage_of(s) * stage_bytes;
+      tiles_ok = landed(s) && tiles_ok;
+      if (newpos >= t0 && newpos < t1) patch(tile, kn, newpos - t0);
+      named_bar_sync(1, kWorkers);  // tile s is complete; every thread is done with tile s - 1
+      issue(s + kDecStages - 1);
+      const int tk = t1 - t0;
+      const int tk_shift = (tk & (tk - 1)) == 0 ? 31 - __clz(tk) : -1;  // full tiles hold a power of two of keys
+#pragma unroll 1
+      for (int item = wtid; item < G * tk; item += kWorkers) {
+        const int g = tk_shift >= 0 ? item >> tk_shift : item / tk, key = item - g * tk;
+        const uint8_t* krow = tile + (g / gs) * sub_bytes + key * row_bytes;
+        const float* qv = qs + g * hd;
+        // four partial sums (pieces 0, 4, 8, ... / 1, 5, ... / ...): the chains have to be independent
+        float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+        for (int piece0 = 0; piece0 < lpk; piece0 += 4) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int piece = piece0 + c;
+            float kf[8];
+            unpack8(*reinterpret_cast<const uint4*>(krow + ((piece ^ (key & 7)) << 4)), kf);
+            const float4 qa = *reinterpret_cast<const float4*>(qv + piece * 8);
+            const float4 qb = *reinterpret_cast<const float4*>(qv + piece * 8 + 4);
+            float acc = part[c];
+            acc = fmaf(qa.x, kf[0], acc); acc = fmaf(qa.y, kf[1], acc); acc = fmaf(qa.z, kf[2], acc); acc = fmaf(qa.w, kf[3], acc);
+            acc = fmaf(qb.x, kf[4], acc); acc = fmaf(qb.y, kf[5], acc); acc = fmaf(qb.z, kf[6], acc); acc = fmaf(qb.w, kf[7], acc);
+            part[c] = acc;
+          }
+        }
+        const float dot = (part[0] + part[1]) + (part[2] + part[3]);
+        sc[g * chunk + (t0 - j0) + key] = bf16_round(dot) * A.scale;
+      }
+    }
+    named_bar_sync(1, kWorkers);
+
+    // --- chunk max, then chunk sum of exp(score - chunk max); the first V tiles are in flight meanwhile
+#pragma unroll 1
+    for (int g = 0; g < G; ++g) {
+      float m = -INFINITY;
+#pragma unroll 1
+      for (int i = wtid; i < cl; i += kWorkers) m = fmaxf(m, sc[g * chunk + i]);
+      m = warp_max(m);
+      if (lane == 0) red[warp * 8 + g] = m;
+    }
+    named_bar_sync(1, kWorkers);
+#pragma unroll 1
+    for (int g = 0; g < G; ++g) {
+      float m = red[g];
+#pragma unroll
+      for (int w = 1; w < kWorkerWarps; ++w) m = fmaxf(m, red[w * 8 + g]);
+      float sum = 0.f;
+#pragma unroll 1
+      for (int i = wtid; i < cl; i += kWorkers) sum += expf(sc[g * chunk + i] - m);
+      sum = warp_sum(sum);
+      if (lane == 0) red[kWorkerWarps * 8 + warp * 8 + g] = sum;
+      if (wtid == 0) stat[g] = m;
+    }
+    named_bar_sync(1, kWorkers);
+    if (wtid < G) {
+      float total = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWorkerWarps; ++w) total += red[kWorkerWarps * 8 + w * 8 + wtid];
+      stat[8 + wtid] = total;
+    }
+    named_bar_sync(1, kWorkers);
+
+    if (nch > 1) {
+      // --- publish (max, sum) with this phase's stamp; wait for every chunk of the row group
+      float* mine = p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + ch) * kExchangeFloats;
+      if (wtid < 16) __stcg(mine + wtid, stat[wtid]);
+      __threadfence();
+      named_bar_sync(1, kWorkers);
+      if (wtid == 0) st_relaxed_u32(reinterpret_cast<uint32_t*>(mine + 16), A.stamp);
+      bool ok = true;
+      if (wtid < nch) {
+        const uint32_t* theirs = reinterpret_cast<const uint32_t*>(
+            p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + wtid) * kExchangeFloats + 16);
+        uint32_t spins = 0;
+        while (ld_relaxed_u32(theirs) != A.stamp) {
+          if ((++spins & 255u) == 0 && give_up(cx, SITE_ATT_EXCHANGE, rowg)) {
+            ok = false;
+            break;
+          }
+        }
+        __threadfence();
+      }
+      if (!workers_ok(cx, ok)) {
+        cp_async_wait_all();  // nothing of this CTA stays in flight past the return
+        return false;
+      }
+      if (wtid < G) {
+        const float* all = p.att_xch + static_cast<size_t>(rowg) * kMaxChunks * kExchangeFloats;
+        float m = -INFINITY;
+        for (int c = 0; c < nch; ++c) m = fmaxf(m, __ldcg(all + c * kExchangeFloats + wtid));
+        float sum = 0.f;
+        for (int c = 0; c < nch; ++c)
+          sum += __ldcg(all + c * kExchangeFloats + 8 + wtid) * expf(__ldcg(all + c * kExchangeFloats + wtid) - m);
+        stat[wtid] = m;
+        stat[8 + wtid] = sum;
+      }
+      named_bar_sync(1, kWorkers);
+    }
+
+    // --- probabilities (bf16, against the global max and sum)
+#pragma unroll 1
+    for (int g = 0; g < G; ++g) {
+      const float m = stat[g], denom = stat[8 + g];
+#pragma unroll 1
+      for (int i = wtid; i < cl; i += kWorkers) sc[g * chunk + i] = bf16_round(expf(sc[g * chunk + i] - m) / denom);
+    }
+    // --- value sums, tile by tile
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float vacc[4][4];  // tensor-core form: D[16 dims][query heads] of up to four dimension tiles of this warp's KV head
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) vacc[i][e] = 0.f;
+    if (use_tma) {
+      // --- value sums, pipelined like the scores.  The block meets once before the first tile (the
+      // probabilities are complete) and in the tiles that are written by hand (new row, zeroed tail).
+      named_bar_sync(1, kWorkers);
+#pragma unroll 1
+      for (int s = nt; s < 2 * nt; ++s) {
+        const int t0 = j0 + (s - nt) * tile_keys, t1 = min(j1, t0 + tile_keys);
+        uint8_t* tile = tiles + stage_of(s) * stage_bytes;
+        tiles_ok = landed(s) && tiles_ok;
+        const int tk = t1 - t0;
+        const bool has_new = newpos >= t0 && newpos < t1, short_tile = (tk & 15) != 0;
+        if (has_new || short_tile) {
+          if (has_new) patch(tile, vn, newpos - t0);  // the new value rows join their tile
+          if (short_tile) {
+            // the last 16-key block of a short tile: rows past the tile's keys meet zero probabilities, but what
+            // the stage holds there must be finite for that product to be zero
+            const int count = 16 - (tk & 15), per_row = hpu * lpk;
+            for (int it = wtid; it < count * per_row; it += kWorkers) {
+              const int r = tk + it / per_row, rest = it % per_row;
+              *reinterpret_cast<uint4*>(tile + piece_at(0u, rest / lpk, r, rest % lpk)) = make_uint4(0, 0, 0, 0);
+            }
+          }
+          fence_proxy_async_all();
+          named_bar_sync(1, kWorkers);
+        }
+        const uint32_t stage = smem_u32(tile);
+        const float* pr = sc + (my_head * gs + lg) * chunk + (t0 - j0);
+#pragma unroll 1
+        for (int k16 = 0; k16 * 16 < tk; ++k16) {
+          // B fragment: probabilities of query head lane / 4 for keys 2 * (lane % 4) + {0, 1} and + 8 of the block
+          const int key = k16 * 16 + lt * 2;
+          float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+          if (lg < gs) {
+            if (key < tk) p0 = pr[key];
+            if (key + 1 < tk) p1 = pr[key + 1];
+            if (key + 8 < tk) p2 = pr[key + 8];
+            if (key + 9 < tk) p3 = pr[key + 9];
+          }
+          const uint32_t b0 = pack2(p0, p1), b1 = pack2(p2, p3);
+          // A fragment: V^T, from rows (keys) of the tile: matrices (keys 0-7 | 8-15) x (dims 0-7 | 8-15) of the block
+          const int row = k16 * 16 + (lane & 7) + (lane >> 4) * 8;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int dt = my_slot + i * head_warps;
+            if (dt < dim_tiles) {
+              uint32_t af[4];
+              ldmatrix_x4_trans(af, piece_at(stage, my_head, row, dt * 2 + ((lane >> 3) & 1)));
+              mma_bf16_16816(vacc[i], af, b0, b1);
+            }
+          }
+        }
+        release(s);
+        issue(s + kDecStages - 1);
+      }
+    }
+#pragma unroll 1
+    for (int s = nt; s < (use_tma ? nt : 2 * nt); ++s) {
+      const int t0 = j0 + (s - nt) * tile_keys, t1 = min(j1, t0 + tile_keys);
+      uint8_t* tile = tiles + stage_of(s) * stage_bytes;
+      tiles_ok = landed(s) && tiles_ok;
+      if (newpos >= t0 && newpos < t1) patch(tile, vn, newpos - t0);  // the new value rows join their tile
+      named_bar_sync(1, kWorkers);  // the tile is complete and (first tile) so are the probabilities
+      issue(s + kDecStages - 1);
+      const int tk = t1 - t0;
+      if (wtid < items) {  // at most one item per thread: its sums stay in registers across the tiles
+        const float* pr = sc + item_g * chunk + (t0 - j0);
+        const uint8_t* vtile = tile + (item_g / gs) * sub_bytes;
+#pragma unroll 4
+        for (int kk = item_part; kk < tk; kk += parts) {
+          float vf[8];
+          unpack8(*reinterpret_cast<const uint4*>(vtile + kk * row_bytes + ((item_piece ^ (kk & 7)) << 4)), vf);
+          const float w = pr[kk];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] = fmaf(w, vf[e], acc[e]);
+        }
+      }
+    }
+    if (use_tma && !workers_ok(cx, tiles_ok)) {
+      // a tile never came: give the copies still in flight a bounded time to land before the CTA leaves
+      for (int st = 0; st < kDecStages; ++st)
+        for (uint32_t spins = 0; spins < (1u << 20); ++spins)
+          if (mbar_try_wait(kvfull0 + st * 8u, 0) || mbar_try_wait(kvfull0 + st * 8u, 1)) break;
+      return false;
+    }
+    if (use_mma) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int dt = my_slot + i * head_warps;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int n = lt * 2 + (e & 1), d = dt * 16 + lg + (e >> 1) * 8;
+          if (dt < dim_tiles && n < gs) red[(my_head * gs + n) * hd + d] = vacc[i][e];
+        }
+      }
+    } else if (wtid < items) {
+      float* mine = red + (item_part * G + item_g) * hd + item_piece * 8;
+      *reinterpret_cast<float4*>(mine) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      *reinterpret_cast<float4*>(mine + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+    named_bar_sync(1, kWorkers);
+    const int sum_parts = use_mma ? 1 : parts;
+#pragma unroll 1
+    for (int col = wtid; col < cols; col += kWorkers) {
+      float o = red[col];
+#pragma unroll 1
+      for (int part = 1; part < sum_parts; ++part) o += red[part * cols + col];
+      const int g = col / hd, d = col - g * hd;
+      const int head = kvh0 * gs + g;
+      if (nch == 1) {
+        A.out[b * A.out_bstride + head * A.out_hstride + d] = __float2bfloat16_rn(o);
+      } else {
+        const size_t row = static_cast<size_t>(b) * p.q_heads + head;
+        __stcg(p.att_part + (row * kMaxChunks + ch) * hd + d, o);
+      }
+    }
+    if (nch > 1 && A.combine) {
+      // There is no consumer phase that adds chunk partials: chunk 0's CTA waits for the partials of its
+      // peers (second stamp) and sums them in chunk order.
+      float* mine = p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + ch) * kExchangeFloats;
+      __threadfence();
+      named_bar_sync(1, kWorkers);
+      if (wtid == 0) st_relaxed_u32(reinterpret_cast<uint32_t*>(mine + 17), A.stamp);
+      if (ch == 0) {
+        bool ok = true;
+        if (wtid < nch) {
+          const uint32_t* theirs = reinterpret_cast<const uint32_t*>(
+              p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + wtid) * kExchangeFloats + 17);
+          uint32_t spins = 0;
+          while (ld_relaxed_u32(theirs) != A.stamp) {
+            if ((++spins & 255u) == 0 && give_up(cx, SITE_ATT_EXCHANGE, rowg)) {
+              ok = false;
+              break;
+            }
+          }
+          __threadfence();
+        }
+        if (!workers_ok(cx, ok)) {
+          cp_async_wait_all();
+          return false;
+        }
+        for (int idx = wtid; idx < cols; idx += kWorkers) {
+          const int g = idx / hd, d = idx - g * hd;
+          const int head = kvh0 * gs + g;
+          const size_t row = static_cast<size_t>(b) * p.q_heads + head;
+          float o = 0.f;
+          for (int c = 0; c < nch; ++c) o += __ldcg(p.att_part + (row * kMaxChunks + c) * hd + d);
+          A.out[b * A.out_bstride + head * A.out_hstride + d] = __float2bfloat16_rn(o);
+        }
+      }
+    }
+    gtile += 2 * nt;
+  }
+  if (wtid == 0) cx.tc->kv_seq = gtile;  // read again after the barrier that closes this phase
+  return true;
+}
+
 // Prompt attention (megabake::attention and the prefill pass) on the warp-level tensor cores.
 //
 // A unit is (sequence, query head, block of 128 query tokens); each of the eight worker warps owns 16
@@ -1466,7 +1996,8 @@ __device__ __noinline__ bool attention_prompt(const Ctx& cx, const AttnArgs& A_i
 }
 
 __device__ __forceinline__ bool attention_phase(const Ctx& cx, const AttnArgs& A, int wtid) {
-  return A.decode ? attention_decode(cx, A, wtid) : attention_prompt(cx, A, wtid);
+  if (!A.decode) return attention_prompt(cx, A, wtid);
+  return decode_stream_ok(*cx.p, A, cx.grid) ? attention_decode_stream(cx, A, wtid) : attention_decode(cx, A, wtid);
 }
 
 // Prefill: rotate q and k of every token in place in the qkv buffer.  An item is eight adjacent
@@ -1660,6 +2191,7 @@ __device__ void worker_loop(const Ctx& cx, int wtid) {
   AttnArgs A;
   A.knew = nullptr; A.vnew = nullptr; A.new_ld = 0; A.mask = nullptr;
   A.sq = 1; A.klen = 0; A.len = 0; A.lens = nullptr; A.decode = 0; A.rope = 0; A.causal = 0; A.combine = 0;
+  A.kmap = nullptr; A.vmap = nullptr;
   A.stamp = p.att_epoch + 1; A.scale = p.att_scale;
   if (p.n_gemm > 0) {
     prefetch_phase(cx, 0, wtid);
@@ -1723,6 +2255,8 @@ __device__ void worker_loop(const Ctx& cx, int wtid) {
         A.len = *p.len[layer];
       }
       A.decode = 1; A.rope = 1;
+      A.kmap = p.kv_maps ? p.kv_maps + layer : nullptr;
+      A.vmap = p.kv_maps ? p.kv_maps + p.layers + layer : nullptr;
       A.combine = 1;  // the o projection fetches a finished bf16 matrix: the first chunk's CTA sums the chunk partials
     } else {
       rope_phase(cx, wtid);
@@ -1802,6 +2336,12 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
     cx.misc->phases = p.phases;
     cx.tc->b_ready = 0;
     cx.tc->a_ready = 0;
+    cx.tc->kv_seq = 0;
+    for (int st = 0; st < 8; ++st) {
+      mbar_init(smem_u32(&cx.tc->kvfull[st]), 1);
+      mbar_init(smem_u32(&cx.tc->kvempty[st]), kWorkerWarps);
+    }
+    mbar_fence_init();
     mbar_fence_init();
   }
   // The rows of a 128-row MMA tile that a weight copy does not fill hold whatever the ring held before;

@@ -46,7 +46,7 @@ enum { EV_PHASE_ENTER = 1, EV_B_STAGED = 2, EV_FIRST_ACC = 3, EV_PHASE_DONE = 4,
 enum {
   SITE_PRODUCER_EMPTY = 1, SITE_MMA_FULL = 2, SITE_MMA_B = 3, SITE_MMA_ACC = 4, SITE_EPI_ACC = 5,
   SITE_GRID_BARRIER = 6, SITE_ATT_EXCHANGE = 7, SITE_DRAIN = 8, SITE_PROLOGUE = 9, SITE_B_EMPTY = 10,
-  SITE_TP_FLAG = 11
+  SITE_TP_FLAG = 11, SITE_KV_TILE = 12
 };
 constexpr int kMaxTp = 8;                // ranks of a tensor-parallel group (one node, NVLink peers)
 constexpr int kTpFlagBytes = 256;        // head of a rank's exchange buffer: one arrival stamp per peer
@@ -166,6 +166,7 @@ struct KParams {
   // so the call needs no upload and no synchronisation
   GemmPhase linear_phase;
   int small_ring;  // weight ring of the small-launch kernel, in 1 KiB granules
+  const CUtensorMap* kv_maps;  // decode on the tensor engine: 4-D descriptors of the key caches [layers], then of the value caches [layers]; null = plain copies
   CUtensorMap linear_wmap, linear_xmap;
   void* kc[MK_MAX_LAYERS];
   void* vc[MK_MAX_LAYERS];

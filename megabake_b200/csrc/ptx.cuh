@@ -81,6 +81,15 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, int 
       ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(bar), "l"(policy)
       : "memory");
 }
+// 4-D tiled load: w is the outermost coordinate.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, int x, int y, int z, int w, uint32_t bar,
+                                            uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%2, %3, %4, %5}], [%6], %7;"
+      ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar), "l"(policy)
+      : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
