@@ -1300,9 +1300,9 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A_i
 // head w % hpu, waits for a stage's `full` barrier, releases it on its `empty` barrier, and the warps take
 // turns issuing the copy two tiles ahead.  The block meets only around what is exchanged between warps:
 // the scores -> statistics -> probabilities hand-over and the tiles that are written by hand (new row,
-// zeroed tail).  Measured on the 1.7B shape at context 1024: chunks of 513 / 1025 keys (batch 16 / 32) 4.5 % /
-// 9 % faster per step than attention_decode, chunks of 256 keys and fewer 2-7 % slower (a short chunk never
-// fills the pipeline), hence decode_stream_ok().
+// zeroed tail).  Measured on the 1.7B shape at context 1024, per step against attention_decode: batch 8 / 16 /
+// 32 (chunks of 256 / 513 / 1025 keys) 8 % / 9 % / 12 % faster; chunks shorter than four tiles never fill
+// the pipeline and stay with attention_decode, hence decode_stream_ok().
 __device__ __forceinline__ bool decode_stream_ok(const KParams& p, const AttnArgs& A, int grid) {
   if (A.kmap == nullptr) return false;
   const int gs = p.q_heads / p.kv_heads, hd = p.head_dim;
@@ -1311,7 +1311,7 @@ __device__ __forceinline__ bool decode_stream_ok(const KParams& p, const AttnArg
   if ((hpu & (hpu - 1)) != 0 || (tile_keys & 15) != 0) return false;
   const int n_max = A.len + 1;
   const int nch = decode_chunks(n_max, p.batch * (p.kv_heads / hpu), grid, gs * hpu);
-  return (n_max + nch - 1) / nch >= 12 * tile_keys;
+  return (n_max + nch - 1) / nch >= 4 * tile_keys;
 }
 
 __device__ __noinline__ bool attention_decode_stream(const Ctx& cx, const AttnArgs& A_in, int wtid) {
