@@ -444,18 +444,11 @@ def main():
     host_ids.copy_(ids.cpu())
     host_pos = torch.empty((args.batch, 1), dtype=torch.int64).pin_memory()
     host_token = torch.empty((args.batch, 1), dtype=torch.int64).pin_memory()
-    dev_ids = torch.empty_like(host_ids, device=device)
-    dev_pos = torch.empty_like(host_pos, device=device)
     e2e_steps = args.steps
-    stream = torch.cuda.current_stream(device)
 
     def e2e_step(step):
         host_pos.fill_(args.context + step)
-        dev_ids.copy_(host_ids, non_blocking=True)
-        dev_pos.copy_(host_pos, non_blocking=True)
-        chosen = kernel.decode_steps(dev_ids, dev_pos, keys, values, lengths, steps=1)
-        host_token.copy_(chosen, non_blocking=True)
-        stream.synchronize()
+        kernel.step_from_host(host_ids, host_pos, keys, values, lengths, host_token)  # up, launch, down, synchronise
         host_ids.copy_(host_token)
 
     for step in range(args.warmup):
@@ -511,8 +504,9 @@ def main():
                      "launch_us": launch_ms * 1e3, "frac_of_8TBps_nominal": achieved / 8000.0},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": 16 * args.batch,
                 "d2h_bytes_per_step": 8 * args.batch, "us_per_call": 1e3 * e2e_ms / e2e_steps,
-                "call": "DecoderKernel.decode_steps(steps=1): ids and positions from pinned host memory, greedy token "
-                        "sampled on the device and copied back, stream synchronised every step"},
+                "call": "DecoderKernel.step_from_host (mk_decode_step_host): ids and positions copied from pinned host "
+                        "memory, one launch with the device-side sampler, the token copied back, stream synchronised, "
+                        "every step"},
         "gpu_launches": launches,
         "clocks": sampler.summary(),
     })

@@ -178,6 +178,17 @@ int mk_decode_steps(mk_handle handle, int64_t* ids, int64_t* positions, int batc
                     void* const* value_caches, int32_t* const* valid_lengths, int capacity, int steps,
                     int64_t* tokens_out, void* logits, void* stream);
 
+/* One greedy decode step driven from host memory, in one call: copies `batch` ids and positions from
+ * host_ids / host_positions (int64, pinned memory for the copies to be asynchronous) to the device,
+ * runs the step with the device-side sampler, copies the sampled tokens to host_tokens_out and
+ * SYNCHRONISES the stream before it returns.  Caches, lengths and logits as for mk_decode.  This is
+ * the serving loop's step when the next id comes from the host (a scheduler, a stop criterion): three
+ * small copies, one launch, one synchronisation, without the interpreter between them.
+ * Reference: the host loop of benchmarks/full_model.py:277-335, one iteration. */
+int mk_decode_step_host(mk_handle handle, const int64_t* host_ids, const int64_t* host_positions, int batch,
+                        void* const* key_caches, void* const* value_caches, int32_t* const* valid_lengths,
+                        int capacity, void* logits, int64_t* host_tokens_out, void* stream);
+
 /* Stateless prompt pass over [batch, sequence] tokens with causal or additive
  * attention mask (bf16 [batch, 1, sequence, sequence], NULL = causal).
  * logits: bf16 [batch, sequence, vocab].

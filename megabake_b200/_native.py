@@ -28,7 +28,7 @@ ENGINES = {"tcgen05": 0, "fma": 2, "auto": 3}
 EXPORTS = (
     "mk_workspace_bytes", "mk_create", "mk_bind_weights", "mk_decode", "mk_prefill", "mk_linear",
     "mk_kv_attention", "mk_kv_attention_static", "mk_kv_attention_static_status", "mk_attention", "mk_status", "mk_set_trace",
-    "mk_launch_info", "mk_last_error", "mk_destroy", "mk_decode_steps", "mk_set_status_mirror", "mk_debug_skew_barrier",
+    "mk_launch_info", "mk_last_error", "mk_destroy", "mk_decode_steps", "mk_decode_step_host", "mk_set_status_mirror", "mk_debug_skew_barrier",
     "mk_describe", "mk_decode_ragged", "mk_baseline_mma_gemm", "mk_tp_exchange_bytes", "mk_tp_bind", "mk_ipc_export", "mk_ipc_open", "mk_ipc_close",
 )
 
@@ -121,6 +121,11 @@ def load() -> ctypes.CDLL:
     lib.mk_decode_steps.argtypes = [
         c_void_p, c_void_p, c_void_p, c_int, POINTER(c_void_p), POINTER(c_void_p), POINTER(c_void_p),
         c_int, c_int, c_void_p, c_void_p, c_void_p,
+    ]
+    lib.mk_decode_step_host.restype = c_int
+    lib.mk_decode_step_host.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_int, POINTER(c_void_p), POINTER(c_void_p), POINTER(c_void_p),
+        c_int, c_void_p, c_void_p, c_void_p,
     ]
     lib.mk_tp_exchange_bytes.restype = c_size_t
     lib.mk_tp_exchange_bytes.argtypes = [POINTER(MkConfig)]

@@ -40,7 +40,7 @@ int fail(int code, const char* fmt, ...) {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct Carve {
-  size_t ctrl, tmaps, kvmaps, phases, hidden, hidden2, xnorm, qkv, qkv_ll, act_ll, att_ll, attn_ll, res_a, res_b, attn, act, partial, partial2, att_xch, att_part, total;
+  size_t ctrl, tmaps, kvmaps, phases, hidden, hidden2, xnorm, qkv, qkv_ll, act_ll, att_ll, attn_ll, res_a, res_b, attn, act, partial, partial2, att_xch, att_part, host_io, total;
 };
 
 int qkv_width(const mk_config& c) { return (c.q_heads + 2 * c.kv_heads) * c.head_dim; }
@@ -83,6 +83,7 @@ Carve carve(const mk_config& c) {
   v.partial2 = take(static_cast<size_t>(kMaxSplit) * kSplitTokens * c.hidden * 4);  // down-proj partials of the small-launch table
   v.att_xch = take(m * c.kv_heads * kMaxChunks * kExchangeFloats * 4);
   v.att_part = take(m * c.q_heads * kMaxChunks * c.head_dim * 4);
+  v.host_io = take(3 * m * sizeof(int64_t));  // mk_decode_step_host: ids, positions, sampled tokens
   v.total = off;
   return v;
 }
@@ -853,6 +854,27 @@ int mk_decode_steps(mk_handle h, int64_t* ids, int64_t* positions, int batch, vo
     if (int e = decode_step(h, ids, positions, batch, key_caches, value_caches, valid_lengths, capacity, logits, stream,
                             tokens_out + static_cast<size_t>(step) * batch, true))
       return e;
+  return MK_OK;
+}
+
+int mk_decode_step_host(mk_handle h, const int64_t* host_ids, const int64_t* host_positions, int batch,
+                        void* const* key_caches, void* const* value_caches, int32_t* const* valid_lengths, int capacity,
+                        void* logits, int64_t* host_tokens_out, void* stream) {
+  if (!h || !host_ids || !host_positions || !key_caches || !value_caches || !valid_lengths || !logits || !host_tokens_out)
+    return fail(MK_ERR_INVALID, "mk_decode_step_host: null argument");
+  if (batch < 1 || batch > h->cfg.max_tokens)
+    return fail(MK_ERR_INVALID, "mk_decode_step_host: batch %d outside [1, %d]", batch, h->cfg.max_tokens);
+  std::lock_guard<std::mutex> guard(h->lock);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int64_t* io = at<int64_t>(h, h->cv.host_io);
+  int64_t *ids = io, *positions = io + h->cfg.max_tokens, *tokens = io + 2 * static_cast<size_t>(h->cfg.max_tokens);
+  const size_t bytes = static_cast<size_t>(batch) * sizeof(int64_t);
+  MK_CUDA(cudaMemcpyAsync(ids, host_ids, bytes, cudaMemcpyHostToDevice, s));
+  MK_CUDA(cudaMemcpyAsync(positions, host_positions, bytes, cudaMemcpyHostToDevice, s));
+  if (int e = decode_step(h, ids, positions, batch, key_caches, value_caches, valid_lengths, capacity, logits, stream, tokens, true))
+    return e;
+  MK_CUDA(cudaMemcpyAsync(host_tokens_out, tokens, bytes, cudaMemcpyDeviceToHost, s));
+  MK_CUDA(cudaStreamSynchronize(s));
   return MK_OK;
 }
 

@@ -136,6 +136,7 @@ class DecoderKernel:
         without synchronising, so a launch that was refused (full cache, bad id) or gave up a
         wait is reported at the caller's next call instead of handing out NaN silently
         (the reference raises: src/megabake/lowering.py:229, src/megabake/compiler.py:2690)."""
+        self._host_step_logits = None
         self._mirror = torch.zeros(1, dtype=torch.int32).pin_memory()
         with torch.cuda.device(self.device):
             self._call("mk_set_status_mirror", self.lib.mk_set_status_mirror(self._handle, self._mirror.data_ptr()))
@@ -314,6 +315,36 @@ class DecoderKernel:
                 capacity, int(steps), tokens.data_ptr(), logits.data_ptr(), self._stream()), stage="input-binding")
         tokens = tokens.transpose(0, 1)
         return (tokens, logits) if return_logits else tokens
+
+    def step_from_host(
+        self,
+        host_ids: torch.Tensor,
+        host_positions: torch.Tensor,
+        key_caches: Sequence[torch.Tensor],
+        value_caches: Sequence[torch.Tensor],
+        valid_lengths: Sequence[torch.Tensor],
+        host_tokens: torch.Tensor,
+    ) -> torch.Tensor:
+        """One greedy step whose inputs and result live in host memory: ``host_ids`` and
+        ``host_positions`` ([batch, 1] int64, pinned) go up, the kernel samples on the device, the
+        chosen tokens land in ``host_tokens`` ([batch, 1] int64, pinned), and the stream is
+        synchronised: one native call.  Returns ``host_tokens``."""
+        batch = host_ids.shape[0]
+        for name, tensor in (("host_ids", host_ids), ("host_positions", host_positions), ("host_tokens", host_tokens)):
+            if tensor.device.type != "cpu" or tensor.dtype != torch.int64 or tuple(tensor.shape) != (batch, 1) \
+                    or not tensor.is_contiguous():
+                raise CompilerError(CompilerDiagnostic(
+                    "input-binding", f"{name} must be a contiguous CPU int64 tensor of shape ({batch}, 1)"))
+        keys, values, lengths, capacity = self._checked_state(batch, key_caches, value_caches, valid_lengths)
+        self.raise_if_failed()
+        if self._host_step_logits is None or self._host_step_logits.shape[0] != batch:
+            self._host_step_logits = torch.empty((batch, 1, self.config.vocab), dtype=torch.bfloat16, device=self.device)
+        with self._lock, torch.cuda.device(self.device):
+            self._call("mk_decode_step_host", self.lib.mk_decode_step_host(
+                self._handle, host_ids.data_ptr(), host_positions.data_ptr(), batch, keys, values, lengths, capacity,
+                self._host_step_logits.data_ptr(), host_tokens.data_ptr(), self._stream()), stage="input-binding")
+        self.raise_if_failed()
+        return host_tokens
 
     def prefill(self, input_ids: torch.Tensor, position_ids: torch.Tensor | None = None,
                 mask: torch.Tensor | None = None) -> torch.Tensor:

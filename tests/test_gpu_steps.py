@@ -229,3 +229,33 @@ def test_per_sequence_valid_lengths_match_the_oracle_one_sequence_at_a_time(leng
     assert all(torch.equal(length.cpu(), torch.tensor([n + 3 for n in lengths_now], dtype=torch.int32)) for length in lengths)
     for row, filled in enumerate(lengths_now):
         assert_parity(keys[-1][row:row + 1, :filled + 3], alone[row][0][-1][:, :filled + 3], f"sequence {row} key cache")
+
+
+def test_step_from_host_matches_decode_steps():
+    """The one-call host-driven step (ids and positions up, sampled token down, synchronised) walks the
+    same greedy path as the device-resident loop: same tokens, same caches, same lengths."""
+    from megabake_b200.runtime import DecoderKernel
+    from megabake_b200.synth import new_kv_state, synth_ids, synth_weights, tiny_config
+
+    device = torch.device("cuda:0")
+    config = tiny_config()
+    weights = synth_weights(config, seed=0, device=device)
+    kernel = DecoderKernel(config, weights, max_tokens=2, max_positions=32, device=device)
+    batch, steps = 2, 6
+    first = synth_ids(batch, config.vocab, seed=5, name="host-step").view(batch, 1)
+    state_a = new_kv_state(config, batch, 32, device)
+    state_b = new_kv_state(config, batch, 32, device)
+    ids = first.to(device)
+    positions = torch.zeros((batch, 1), dtype=torch.int64, device=device)
+    expected = kernel.decode_steps(ids, positions, *state_a, steps=steps).cpu()
+    host_ids, host_pos, host_tok = (torch.empty((batch, 1), dtype=torch.int64).pin_memory() for _ in range(3))
+    host_ids.copy_(first)
+    for step in range(steps):
+        host_pos.fill_(step)
+        kernel.step_from_host(host_ids, host_pos, *state_b, host_tok)
+        assert torch.equal(host_tok.view(-1), expected[:, step]), f"step {step}"
+        host_ids.copy_(host_tok)
+    kernel.check()
+    for layer in range(config.layers):
+        assert torch.equal(state_a[0][layer], state_b[0][layer]) and torch.equal(state_a[1][layer], state_b[1][layer])
+        assert int(state_a[2][layer]) == int(state_b[2][layer]) == steps
