@@ -1823,62 +1823,60 @@ __device__ __noinline__ bool attention_decode_stream(const Ctx& cx, const AttnAr
 //
 // A unit is (sequence, query head, block of 128 query tokens); each of the eight worker warps owns 16
 // of the block's query rows and keeps their q fragments in registers.  Keys and values of the unit's
-// KV head stream through the (idle) weight ring in tiles of 64 positions.  Two passes over the key
-// tiles reproduce the reference's rounding points (src/megabake/lowering.py:274-300, the Hugging
-// Face eager form): score = bf16(bf16(q.k) * scale) (+ additive mask, rounded again); softmax in fp32
-// against the row's global maximum and sum; probability rounded to bf16; fp32 value sums rounded once.
+// KV head stream through the (idle) weight ring in tiles of 64 positions, two stages deep: the copies of
+// the next tile are in flight while this one is multiplied, with one block barrier per tile.  Two passes
+// over the key tiles reproduce the reference's rounding points (src/megabake/lowering.py:274-300, the
+// Hugging Face eager form): score = bf16(bf16(q.k) * scale) (+ additive mask, rounded again); softmax in
+// fp32 against the row's global maximum and sum; probability rounded to bf16; fp32 value sums rounded once.
 //   pass 1: scores of every tile -> running row maximum and sum of exp (rescaled when the maximum grows);
 //   pass 2: the same scores again (same instructions, same bits) -> p = bf16(exp(s - max) / sum), which is
 //           already the A-fragment layout of the next product, times the V tile (ldmatrix.trans).
 // Without a mask tensor attention is causal: key j <= query token index, tiles past the block's last
 // query are skipped.  Rounded scores are bf16, so recomputing them costs tensor-core time only; no
-// score buffer limits the key count.
+// score buffer limits the key count.  One instantiation per head size: the fragment arrays then have
+// their exact extents (with the larger extents for both, ptxas spilled ~1 KB per thread inside the tile loop).
 constexpr int kPromptQueries = 16 * kWorkerWarps;  // query rows per unit
 constexpr int kPromptKeys = 64;                    // positions per K / V tile
 
 __device__ __forceinline__ uint32_t ldcg_u32(const void* ptr) { return __ldcg(reinterpret_cast<const unsigned int*>(ptr)); }
 
+template <int HD>
 __device__ __noinline__ bool attention_prompt(const Ctx& cx, const AttnArgs& A_in, int wtid) {
-  // Private copies of the arguments and of the parameters this phase reads: every poll, copy wait and block
+  // Private copies of the arguments and of the parameters this phase reads: every copy wait and block
   // barrier below is a compiler barrier for memory, behind which a value that lives behind a reference is
   // loaded again (a kernel parameter through the context: two dependent loads).
   const AttnArgs A = A_in;
-  struct {
-    int head_dim, q_heads, kv_heads, batch, max_positions, rope_style, prefill_rope_style, m;
-    const bf16 *cos_t, *sin_t;
-    float *att_xch, *att_part;
-    long long* pos;
-  } p = {cx.p->head_dim, cx.p->q_heads, cx.p->kv_heads, cx.p->batch, cx.p->max_positions, cx.p->rope_style,
-         cx.p->prefill_rope_style, cx.p->m, cx.p->cos_t, cx.p->sin_t, cx.p->att_xch, cx.p->att_part, cx.p->pos};
-  const int hd = p.head_dim;
-  const int gs = p.q_heads / p.kv_heads;
+  const int q_heads = cx.p->q_heads, kv_heads = cx.p->kv_heads, batch = cx.p->batch;
+  const int my_cta = cx.cta, grid = cx.grid;
+  constexpr int hd = HD;
+  constexpr int ksteps = HD / 16;     // k steps of the score product
+  constexpr int dtiles = HD / 8;      // 8-column tiles of the output row
+  constexpr int pitch = HD * 2 + 16;  // bytes per tile row: 16 bytes of padding keep fragment loads conflict-free
+  constexpr int pieces = HD / 8;      // 16-byte pieces per row
+  constexpr int kStage = 2 * kPromptKeys * pitch;  // a K tile and a V tile
+  static_assert(2 * kStage <= kRingBytes, "prompt attention stages exceed the weight ring");
+  const int gs = q_heads / kv_heads;
   const int warp = wtid >> 5, lane = wtid & 31, g = lane >> 2, t = lane & 3;
-  const int ksteps = hd / 16;   // k steps of the score product: 4 or 8
-  const int dtiles = hd / 8;    // 8-column tiles of the output row: 8 or 16
-  const int pitch = hd * 2 + 16;  // bytes per tile row: 16 bytes of padding keep fragment loads conflict-free
   const int qblocks = (A.sq + kPromptQueries - 1) / kPromptQueries;
-  const int units = p.batch * p.q_heads * qblocks;
-  const uint32_t ks_addr = smem_u32(cx.smem_a), vs_addr = ks_addr + kPromptKeys * pitch;
-  const int pieces = hd / 8;  // 16-byte pieces per row
+  const int units = batch * q_heads * qblocks;
+  const uint32_t ring = smem_u32(cx.smem_a);
 
 #pragma unroll 1
-  for (int u = cx.cta; u < units; u += cx.grid) {
+  for (int u = my_cta; u < units; u += grid) {
     const int qb = u % qblocks, bh = u / qblocks;
-    const int h = bh % p.q_heads, b = bh / p.q_heads, kvh = h / gs;
+    const int h = bh % q_heads, b = bh / q_heads, kvh = h / gs;
     const int q0 = qb * kPromptQueries + warp * 16;
     const int r0 = q0 + g, r1 = r0 + 8;  // this thread's two query rows
     const int r0c = min(r0, A.sq - 1), r1c = min(r1, A.sq - 1);
     const bf16* qrow0 = A.q + b * A.q_bstride + static_cast<long long>(r0c) * A.q_ld + h * hd;
     const bf16* qrow1 = A.q + b * A.q_bstride + static_cast<long long>(r1c) * A.q_ld + h * hd;
-    uint32_t qf[8][4];
+    uint32_t qf[ksteps][4];
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
-      if (ks < ksteps) {
-        qf[ks][0] = ldcg_u32(qrow0 + ks * 16 + t * 2);
-        qf[ks][1] = ldcg_u32(qrow1 + ks * 16 + t * 2);
-        qf[ks][2] = ldcg_u32(qrow0 + ks * 16 + 8 + t * 2);
-        qf[ks][3] = ldcg_u32(qrow1 + ks * 16 + 8 + t * 2);
-      }
+    for (int ks = 0; ks < ksteps; ++ks) {
+      qf[ks][0] = ldcg_u32(qrow0 + ks * 16 + t * 2);
+      qf[ks][1] = ldcg_u32(qrow1 + ks * 16 + t * 2);
+      qf[ks][2] = ldcg_u32(qrow0 + ks * 16 + 8 + t * 2);
+      qf[ks][3] = ldcg_u32(qrow1 + ks * 16 + 8 + t * 2);
     }
     const bf16* kbase = A.k + b * A.kv_bstride + kvh * hd;
     const bf16* vbase = A.v + b * A.kv_bstride + kvh * hd;
@@ -1886,117 +1884,133 @@ __device__ __noinline__ bool attention_prompt(const Ctx& cx, const AttnArgs& A_i
     const bf16* mrow1 = A.mask ? A.mask + (static_cast<long long>(b) * A.sq + r1c) * A.klen : nullptr;
     const int kend = A.causal ? min(A.klen, qb * kPromptQueries + kPromptQueries) : A.klen;
     const int ntiles = (kend + kPromptKeys - 1) / kPromptKeys;
+    const int steps = 2 * ntiles;  // pass 1 over the K tiles, then pass 2 over the K and V tiles
+    // Step s copies into stage s & 1: the K tile, and in the second pass the V tile behind it.
+    auto issue = [&](int s) {
+      const bool second = s >= ntiles;
+      const int j0 = (second ? s - ntiles : s) * kPromptKeys;
+      const uint32_t ks_addr = ring + (s & 1) * kStage, vs_addr = ks_addr + kPromptKeys * pitch;
+#pragma unroll
+      for (int it0 = 0; it0 < kPromptKeys * pieces; it0 += kWorkers) {
+        const int it = it0 + wtid;
+        const int r = it / pieces, piece = it % pieces;
+        const long long j = min(j0 + r, A.klen - 1);  // rows past the last key repeat it; they are masked below
+        cp_async16(ks_addr + r * pitch + piece * 16, reinterpret_cast<const uint4*>(kbase + j * A.kv_ld) + piece);
+        if (second) cp_async16(vs_addr + r * pitch + piece * 16, reinterpret_cast<const uint4*>(vbase + j * A.kv_ld) + piece);
+      }
+    };
+    // Wait for step s's tile, then start the next step's copies into the stage every warp has just left.
+    auto advance = [&](int s) {
+      cp_async_wait_all();
+      named_bar_sync(1, kWorkers);
+      if (s + 1 < steps) issue(s + 1);
+    };
+    // Scores of this thread's two rows against keys j0 + nt * 8 + 2t, + 1 of the tile at ks_addr.
+    auto score_tile = [&](uint32_t ks_addr, int j0, int nt, float (&out)[4]) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint32_t krow = ks_addr + (nt * 8 + g) * pitch + t * 4;
+#pragma unroll
+      for (int ks = 0; ks < ksteps; ++ks) mma_bf16_16816(acc, qf[ks], lds_u32(krow + ks * 32), lds_u32(krow + ks * 32 + 16));
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = j0 + nt * 8 + t * 2 + (e & 1);
+        const int qi = (e < 2) ? r0 : r1;
+        float v = bf16_round(bf16_round(acc[e]) * A.scale);
+        if (A.mask) v = bf16_round(v + ldg_bf16(((e < 2) ? mrow0 : mrow1) + min(j, A.klen - 1)));
+        const bool valid = j < A.klen && (!A.causal || j <= qi);
+        out[e] = valid ? v : -INFINITY;
+      }
+    };
+    named_bar_sync(1, kWorkers);  // every warp is done with the previous unit's last tile
+    issue(0);
+
+    // pass 1: row maximum and sum of exp
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-    float o[16][4];
+#pragma unroll 1
+    for (int s = 0; s < ntiles; ++s) {
+      const int j0 = s * kPromptKeys;
+      const uint32_t ks_addr = ring + (s & 1) * kStage;
+      advance(s);
+      if (A.causal && j0 > q0 + 15) continue;  // no query of this warp sees this tile (barriers stay uniform)
+      float sv[8][4];
 #pragma unroll
-    for (int d = 0; d < 16; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+      for (int nt = 0; nt < 8; ++nt) score_tile(ks_addr, j0, nt, sv[nt]);
+      float t0 = -INFINITY, t1 = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        t0 = fmaxf(t0, fmaxf(sv[nt][0], sv[nt][1]));
+        t1 = fmaxf(t1, fmaxf(sv[nt][2], sv[nt][3]));
+      }
+      t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 1)); t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 2));
+      t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 1)); t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 2));
+      const float n0 = fmaxf(m0, t0), n1 = fmaxf(m1, t1);
+      float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        if (n0 > -INFINITY) s0 += expf(sv[nt][0] - n0) + expf(sv[nt][1] - n0);
+        if (n1 > -INFINITY) s1 += expf(sv[nt][2] - n1) + expf(sv[nt][3] - n1);
+      }
+      s0 += __shfl_xor_sync(0xffffffffu, s0, 1); s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+      s1 += __shfl_xor_sync(0xffffffffu, s1, 1); s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+      if (n0 > -INFINITY) { l0 = l0 * expf(m0 - n0) + s0; m0 = n0; }
+      if (n1 > -INFINITY) { l1 = l1 * expf(m1 - n1) + s1; m1 = n1; }
+    }
 
-#pragma unroll 1
-    for (int pass = 0; pass < 2; ++pass) {
-#pragma unroll 1
-      for (int kt = 0; kt < ntiles; ++kt) {
-        const int j0 = kt * kPromptKeys;
-        named_bar_sync(1, kWorkers);  // every warp is done with the previous tile
-#pragma unroll 1
-        for (int it = wtid; it < kPromptKeys * pieces; it += kWorkers) {
-          const int r = it / pieces, piece = it - r * pieces;
-          const long long j = min(j0 + r, A.klen - 1);  // rows past the last key repeat it; they are masked below
-          cp_async16(ks_addr + r * pitch + piece * 16, reinterpret_cast<const uint4*>(kbase + j * A.kv_ld) + piece);
-          if (pass == 1) cp_async16(vs_addr + r * pitch + piece * 16, reinterpret_cast<const uint4*>(vbase + j * A.kv_ld) + piece);
-        }
-        cp_async_wait_all();
-        named_bar_sync(1, kWorkers);
-        if (A.causal && j0 > q0 + 15) continue;  // no query of this warp sees this tile (barriers stay uniform)
-
-        // scores of this warp's 16 rows against the tile's 64 keys
-        float sv[8][4];
+    // pass 2: the same scores, 16 keys at a time -> probabilities (already A fragments) x V
+    float o[dtiles][4];
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-          float acc[4] = {0.f, 0.f, 0.f, 0.f};
-          const uint32_t krow = ks_addr + (nt * 8 + g) * pitch + t * 4;
+    for (int d = 0; d < dtiles; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+#pragma unroll 1
+    for (int s = ntiles; s < steps; ++s) {
+      const int j0 = (s - ntiles) * kPromptKeys;
+      const uint32_t ks_addr = ring + (s & 1) * kStage, vs_addr = ks_addr + kPromptKeys * pitch;
+      advance(s);
+      if (A.causal && j0 > q0 + 15) continue;
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks)
-            if (ks < ksteps) mma_bf16_16816(acc, qf[ks], lds_u32(krow + ks * 32), lds_u32(krow + ks * 32 + 16));
+      for (int kk = 0; kk < 4; ++kk) {
+        float sv[2][4];
+        score_tile(ks_addr, j0, kk * 2, sv[0]);
+        score_tile(ks_addr, j0, kk * 2 + 1, sv[1]);
+        float pr[2][4];
+#pragma unroll
+        for (int half = 0; half < 2; ++half)
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const int j = j0 + nt * 8 + t * 2 + (e & 1);
-            const int qi = (e < 2) ? r0 : r1;
-            float v = bf16_round(bf16_round(acc[e]) * A.scale);
-            if (A.mask) v = bf16_round(v + ldg_bf16(((e < 2) ? mrow0 : mrow1) + min(j, A.klen - 1)));
-            const bool valid = j < A.klen && (!A.causal || j <= qi);
-            sv[nt][e] = valid ? v : -INFINITY;
+            const float sc = sv[half][e];
+            const float m = (e < 2) ? m0 : m1, l = (e < 2) ? l0 : l1;
+            pr[half][e] = (sc > -INFINITY) ? expf(sc - m) / l : 0.f;
           }
-        }
-        if (pass == 0) {
-          float t0 = -INFINITY, t1 = -INFINITY;
+        uint32_t pa[4];
+        pa[0] = pack2(pr[0][0], pr[0][1]);
+        pa[1] = pack2(pr[0][2], pr[0][3]);
+        pa[2] = pack2(pr[1][0], pr[1][1]);
+        pa[3] = pack2(pr[1][2], pr[1][3]);
 #pragma unroll
-          for (int nt = 0; nt < 8; ++nt) {
-            t0 = fmaxf(t0, fmaxf(sv[nt][0], sv[nt][1]));
-            t1 = fmaxf(t1, fmaxf(sv[nt][2], sv[nt][3]));
-          }
-          t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 1)); t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 2));
-          t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 1)); t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 2));
-          const float n0 = fmaxf(m0, t0), n1 = fmaxf(m1, t1);
-          float s0 = 0.f, s1 = 0.f;
-#pragma unroll
-          for (int nt = 0; nt < 8; ++nt) {
-            if (n0 > -INFINITY) s0 += expf(sv[nt][0] - n0) + expf(sv[nt][1] - n0);
-            if (n1 > -INFINITY) s1 += expf(sv[nt][2] - n1) + expf(sv[nt][3] - n1);
-          }
-          s0 += __shfl_xor_sync(0xffffffffu, s0, 1); s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
-          s1 += __shfl_xor_sync(0xffffffffu, s1, 1); s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
-          if (n0 > -INFINITY) { l0 = l0 * expf(m0 - n0) + s0; m0 = n0; }
-          if (n1 > -INFINITY) { l1 = l1 * expf(m1 - n1) + s1; m1 = n1; }
-        } else {
-          // probabilities, rounded to bf16, straight into A fragments: two adjacent 8-key tiles make one 16-key step
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            uint32_t pa[4];
-            float pr[2][4];
-#pragma unroll
-            for (int half = 0; half < 2; ++half)
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float s = sv[kk * 2 + half][e];
-                const float m = (e < 2) ? m0 : m1, l = (e < 2) ? l0 : l1;
-                pr[half][e] = (s > -INFINITY) ? expf(s - m) / l : 0.f;
-              }
-            pa[0] = pack2(pr[0][0], pr[0][1]);
-            pa[1] = pack2(pr[0][2], pr[0][3]);
-            pa[2] = pack2(pr[1][0], pr[1][1]);
-            pa[3] = pack2(pr[1][2], pr[1][3]);
-#pragma unroll
-            for (int d = 0; d < 16; d += 2) {
-              if (d < dtiles) {
-                uint32_t vb[4];
-                // matrices: (keys kk*16 + 0..7, dims d*8..), (keys + 8, same dims), then the same two for dims (d+1)*8..
-                ldmatrix_x4_trans(vb, vs_addr + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * pitch + (d + (lane >> 4)) * 16);
-                mma_bf16_16816(o[d], pa, vb[0], vb[1]);
-                mma_bf16_16816(o[d + 1], pa, vb[2], vb[3]);
-              }
-            }
-          }
+        for (int d = 0; d < dtiles; d += 2) {
+          uint32_t vb[4];
+          // matrices: (keys kk*16 + 0..7, dims d*8..), (keys + 8, same dims), then the same two for dims (d+1)*8..
+          ldmatrix_x4_trans(vb, vs_addr + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * pitch + (d + (lane >> 4)) * 16);
+          mma_bf16_16816(o[d], pa, vb[0], vb[1]);
+          mma_bf16_16816(o[d + 1], pa, vb[2], vb[3]);
         }
       }
     }
     // this thread's output elements: rows r0, r1; columns d * 8 + t * 2, + 1
 #pragma unroll
-    for (int d = 0; d < 16; ++d) {
-      if (d < dtiles) {
-        if (r0 < A.sq)
-          *reinterpret_cast<uint32_t*>(A.out + b * A.out_bstride + static_cast<long long>(r0) * A.out_tstride + h * A.out_hstride +
-                                       d * 8 + t * 2) = pack2(o[d][0], o[d][1]);
-        if (r1 < A.sq)
-          *reinterpret_cast<uint32_t*>(A.out + b * A.out_bstride + static_cast<long long>(r1) * A.out_tstride + h * A.out_hstride +
-                                       d * 8 + t * 2) = pack2(o[d][2], o[d][3]);
-      }
+    for (int d = 0; d < dtiles; ++d) {
+      if (r0 < A.sq)
+        *reinterpret_cast<uint32_t*>(A.out + b * A.out_bstride + static_cast<long long>(r0) * A.out_tstride + h * A.out_hstride +
+                                     d * 8 + t * 2) = pack2(o[d][0], o[d][1]);
+      if (r1 < A.sq)
+        *reinterpret_cast<uint32_t*>(A.out + b * A.out_bstride + static_cast<long long>(r1) * A.out_tstride + h * A.out_hstride +
+                                     d * 8 + t * 2) = pack2(o[d][2], o[d][3]);
     }
   }
   return true;
 }
 
 __device__ __forceinline__ bool attention_phase(const Ctx& cx, const AttnArgs& A, int wtid) {
-  if (!A.decode) return attention_prompt(cx, A, wtid);
+  if (!A.decode) return cx.p->head_dim == 64 ? attention_prompt<64>(cx, A, wtid) : attention_prompt<128>(cx, A, wtid);
   return decode_stream_ok(*cx.p, A, cx.grid) ? attention_decode_stream(cx, A, wtid) : attention_decode(cx, A, wtid);
 }
 
