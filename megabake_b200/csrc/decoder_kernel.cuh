@@ -1821,22 +1821,26 @@ __device__ __noinline__ bool attention_decode_stream(const Ctx& cx, const AttnAr
 
 // Prompt attention (megabake::attention and the prefill pass) on the warp-level tensor cores.
 //
-// A unit is (sequence, query head, block of 128 query tokens); each of the eight worker warps owns 16
-// of the block's query rows and keeps their q fragments in registers.  Keys and values of the unit's
-// KV head stream through the (idle) weight ring in tiles of 64 positions, two stages deep: the copies of
-// the next tile are in flight while this one is multiplied, with one block barrier per tile.  Two passes
-// over the key tiles reproduce the reference's rounding points (src/megabake/lowering.py:274-300, the
-// Hugging Face eager form): score = bf16(bf16(q.k) * scale) (+ additive mask, rounded again); softmax in
-// fp32 against the row's global maximum and sum; probability rounded to bf16; fp32 value sums rounded once.
+// A unit is (sequence, query head, block of 64 query tokens).  The eight worker warps are four row
+// groups of 16 query rows times two key halves: warps w and w + 4 keep the same q fragments in registers
+// and split every 64-position K / V tile between them (positions 0-31 and 32-63), which halves the
+// instruction chain of a tile; their statistics meet in shared memory after the first pass, their value
+// sums after the second.  Tiles of the unit's KV head stream through the (idle) weight ring, two stages
+// deep: the copies of the next tile are in flight while this one is multiplied, one block barrier per
+// tile.  Two passes over the key tiles reproduce the reference's rounding points
+// (src/megabake/lowering.py:274-300, the Hugging Face eager form): score = bf16(bf16(q.k) * scale)
+// (+ additive mask, rounded again); softmax in fp32 against the row's global maximum and sum; probability
+// rounded to bf16; fp32 value sums rounded once.
 //   pass 1: scores of every tile -> running row maximum and sum of exp (rescaled when the maximum grows);
 //   pass 2: the same scores again (same instructions, same bits) -> p = bf16(exp(s - max) / sum), which is
 //           already the A-fragment layout of the next product, times the V tile (ldmatrix.trans).
 // Without a mask tensor attention is causal: key j <= query token index, tiles past the block's last
-// query are skipped.  Rounded scores are bf16, so recomputing them costs tensor-core time only; no
-// score buffer limits the key count.  One instantiation per head size: the fragment arrays then have
-// their exact extents (with the larger extents for both, ptxas spilled ~1 KB per thread inside the tile loop).
-constexpr int kPromptQueries = 16 * kWorkerWarps;  // query rows per unit
-constexpr int kPromptKeys = 64;                    // positions per K / V tile
+// query are skipped, and so are the halves a warp's rows cannot see.  Causal blocks cost in proportion to
+// their index, so the units are dealt heaviest first, every second round in reverse CTA order.  Rounded
+// scores are bf16, so recomputing them costs tensor-core time only; no score buffer limits the key
+// count.  One instantiation per head size: the fragment arrays then have their exact extents.
+constexpr int kPromptQueries = 64;  // query rows per unit
+constexpr int kPromptKeys = 64;     // positions per K / V tile
 
 __device__ __forceinline__ uint32_t ldcg_u32(const void* ptr) { return __ldcg(reinterpret_cast<const unsigned int*>(ptr)); }
 
@@ -1854,18 +1858,27 @@ __device__ __noinline__ bool attention_prompt(const Ctx& cx, const AttnArgs& A_i
   constexpr int pitch = HD * 2 + 16;  // bytes per tile row: 16 bytes of padding keep fragment loads conflict-free
   constexpr int pieces = HD / 8;      // 16-byte pieces per row
   constexpr int kStage = 2 * kPromptKeys * pitch;  // a K tile and a V tile
-  static_assert(2 * kStage <= kRingBytes, "prompt attention stages exceed the weight ring");
+  constexpr int kStatFloats = 2 * 4 * 4 * 32;      // [key half][row group][m0, l0, m1, l1][lane]
+  constexpr int kSumFloats = 4 * dtiles * 4 * 32;  // [row group][output element of a lane][lane]
+  static_assert(2 * kStage + (kStatFloats + kSumFloats) * 4 <= kRingBytes, "prompt attention exceeds the weight ring");
   const int gs = q_heads / kv_heads;
   const int warp = wtid >> 5, lane = wtid & 31, g = lane >> 2, t = lane & 3;
+  const int rw = warp & 3, kh = warp >> 2;  // row group, key half
   const int qblocks = (A.sq + kPromptQueries - 1) / kPromptQueries;
-  const int units = batch * q_heads * qblocks;
+  const int heads = batch * q_heads;
+  const int units = heads * qblocks;
   const uint32_t ring = smem_u32(cx.smem_a);
+  float* const stat_x = reinterpret_cast<float*>(cx.smem_a + 2 * kStage);
+  float* const sum_x = stat_x + kStatFloats;
 
 #pragma unroll 1
-  for (int u = my_cta; u < units; u += grid) {
-    const int qb = u % qblocks, bh = u / qblocks;
+  for (int round = 0; round * grid < units; ++round) {
+    // heaviest first: sorted position i holds query block qblocks - 1 - i / heads
+    const int i = round * grid + ((round & 1) ? grid - 1 - my_cta : my_cta);
+    if (i >= units) continue;
+    const int qb = qblocks - 1 - i / heads, bh = i % heads;
     const int h = bh % q_heads, b = bh / q_heads, kvh = h / gs;
-    const int q0 = qb * kPromptQueries + warp * 16;
+    const int q0 = qb * kPromptQueries + rw * 16;
     const int r0 = q0 + g, r1 = r0 + 8;  // this thread's two query rows
     const int r0c = min(r0, A.sq - 1), r1c = min(r1, A.sq - 1);
     const bf16* qrow0 = A.q + b * A.q_bstride + static_cast<long long>(r0c) * A.q_ld + h * hd;
@@ -1885,6 +1898,7 @@ __device__ __noinline__ bool attention_prompt(const Ctx& cx, const AttnArgs& A_i
     const int kend = A.causal ? min(A.klen, qb * kPromptQueries + kPromptQueries) : A.klen;
     const int ntiles = (kend + kPromptKeys - 1) / kPromptKeys;
     const int steps = 2 * ntiles;  // pass 1 over the K tiles, then pass 2 over the K and V tiles
+
     // Step s copies into stage s & 1: the K tile, and in the second pass the V tile behind it.
     auto issue = [&](int s) {
       const bool second = s >= ntiles;
@@ -1921,23 +1935,23 @@ __device__ __noinline__ bool attention_prompt(const Ctx& cx, const AttnArgs& A_i
         out[e] = valid ? v : -INFINITY;
       }
     };
-    named_bar_sync(1, kWorkers);  // every warp is done with the previous unit's last tile
+    named_bar_sync(1, kWorkers);  // every warp is done with the previous unit's last tile and its exchange areas
     issue(0);
 
-    // pass 1: row maximum and sum of exp
+    // pass 1: row maximum and sum of exp over this warp's half of every tile
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 #pragma unroll 1
     for (int s = 0; s < ntiles; ++s) {
       const int j0 = s * kPromptKeys;
       const uint32_t ks_addr = ring + (s & 1) * kStage;
       advance(s);
-      if (A.causal && j0 > q0 + 15) continue;  // no query of this warp sees this tile (barriers stay uniform)
-      float sv[8][4];
+      if (A.causal && j0 + kh * 32 > q0 + 15) continue;  // no query of this warp sees its half (barriers stay uniform)
+      float sv[4][4];
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) score_tile(ks_addr, j0, nt, sv[nt]);
+      for (int nt = 0; nt < 4; ++nt) score_tile(ks_addr, j0, kh * 4 + nt, sv[nt]);
       float t0 = -INFINITY, t1 = -INFINITY;
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
+      for (int nt = 0; nt < 4; ++nt) {
         t0 = fmaxf(t0, fmaxf(sv[nt][0], sv[nt][1]));
         t1 = fmaxf(t1, fmaxf(sv[nt][2], sv[nt][3]));
       }
@@ -1946,7 +1960,7 @@ __device__ __noinline__ bool attention_prompt(const Ctx& cx, const AttnArgs& A_i
       const float n0 = fmaxf(m0, t0), n1 = fmaxf(m1, t1);
       float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
+      for (int nt = 0; nt < 4; ++nt) {
         if (n0 > -INFINITY) s0 += expf(sv[nt][0] - n0) + expf(sv[nt][1] - n0);
         if (n1 > -INFINITY) s1 += expf(sv[nt][2] - n1) + expf(sv[nt][3] - n1);
       }
@@ -1954,6 +1968,19 @@ __device__ __noinline__ bool attention_prompt(const Ctx& cx, const AttnArgs& A_i
       s1 += __shfl_xor_sync(0xffffffffu, s1, 1); s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
       if (n0 > -INFINITY) { l0 = l0 * expf(m0 - n0) + s0; m0 = n0; }
       if (n1 > -INFINITY) { l1 = l1 * expf(m1 - n1) + s1; m1 = n1; }
+    }
+    {  // the two key halves' statistics meet: both warps of a row group form the same (max, sum), half 0 first
+      float* mine = stat_x + (kh * 4 + rw) * 4 * 32 + lane;
+      mine[0] = m0; mine[32] = l0; mine[64] = m1; mine[96] = l1;
+      named_bar_sync(1, kWorkers);
+      const float* other = stat_x + ((kh ^ 1) * 4 + rw) * 4 * 32 + lane;
+      const float om0 = other[0], ol0 = other[32], om1 = other[64], ol1 = other[96];
+      const float am0 = kh ? om0 : m0, al0 = kh ? ol0 : l0, bm0 = kh ? m0 : om0, bl0 = kh ? l0 : ol0;
+      const float am1 = kh ? om1 : m1, al1 = kh ? ol1 : l1, bm1 = kh ? m1 : om1, bl1 = kh ? l1 : ol1;
+      m0 = fmaxf(am0, bm0);
+      m1 = fmaxf(am1, bm1);
+      l0 = (am0 > -INFINITY ? al0 * expf(am0 - m0) : 0.f) + (bm0 > -INFINITY ? bl0 * expf(bm0 - m0) : 0.f);
+      l1 = (am1 > -INFINITY ? al1 * expf(am1 - m1) : 0.f) + (bm1 > -INFINITY ? bl1 * expf(bm1 - m1) : 0.f);
     }
 
     // pass 2: the same scores, 16 keys at a time -> probabilities (already A fragments) x V
@@ -1965,9 +1992,10 @@ __device__ __noinline__ bool attention_prompt(const Ctx& cx, const AttnArgs& A_i
       const int j0 = (s - ntiles) * kPromptKeys;
       const uint32_t ks_addr = ring + (s & 1) * kStage, vs_addr = ks_addr + kPromptKeys * pitch;
       advance(s);
-      if (A.causal && j0 > q0 + 15) continue;
+      if (A.causal && j0 + kh * 32 > q0 + 15) continue;
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
+      for (int k2 = 0; k2 < 2; ++k2) {
+        const int kk = kh * 2 + k2;  // 16-key block of the tile
         float sv[2][4];
         score_tile(ks_addr, j0, kk * 2, sv[0]);
         score_tile(ks_addr, j0, kk * 2 + 1, sv[1]);
@@ -1995,15 +2023,28 @@ __device__ __noinline__ bool attention_prompt(const Ctx& cx, const AttnArgs& A_i
         }
       }
     }
-    // this thread's output elements: rows r0, r1; columns d * 8 + t * 2, + 1
+    // the second half's fp32 sums join the first half's, which rounds once and stores
+    float* sums = sum_x + rw * dtiles * 4 * 32 + lane;
+    if (kh == 1) {
 #pragma unroll
-    for (int d = 0; d < dtiles; ++d) {
-      if (r0 < A.sq)
-        *reinterpret_cast<uint32_t*>(A.out + b * A.out_bstride + static_cast<long long>(r0) * A.out_tstride + h * A.out_hstride +
-                                     d * 8 + t * 2) = pack2(o[d][0], o[d][1]);
-      if (r1 < A.sq)
-        *reinterpret_cast<uint32_t*>(A.out + b * A.out_bstride + static_cast<long long>(r1) * A.out_tstride + h * A.out_hstride +
-                                     d * 8 + t * 2) = pack2(o[d][2], o[d][3]);
+      for (int d = 0; d < dtiles; ++d)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sums[(d * 4 + e) * 32] = o[d][e];
+    }
+    named_bar_sync(1, kWorkers);
+    if (kh == 0) {
+      // this thread's output elements: rows r0, r1; columns d * 8 + t * 2, + 1
+#pragma unroll
+      for (int d = 0; d < dtiles; ++d) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[d][e] += sums[(d * 4 + e) * 32];
+        if (r0 < A.sq)
+          *reinterpret_cast<uint32_t*>(A.out + b * A.out_bstride + static_cast<long long>(r0) * A.out_tstride + h * A.out_hstride +
+                                       d * 8 + t * 2) = pack2(o[d][0], o[d][1]);
+        if (r1 < A.sq)
+          *reinterpret_cast<uint32_t*>(A.out + b * A.out_bstride + static_cast<long long>(r1) * A.out_tstride + h * A.out_hstride +
+                                       d * 8 + t * 2) = pack2(o[d][2], o[d][3]);
+      }
     }
   }
   return true;
