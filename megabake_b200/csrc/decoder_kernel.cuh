@@ -1937,6 +1937,7 @@ __device__ __noinline__ bool attention_prompt(const Ctx& cx, const AttnArgs& A_i
     };
     named_bar_sync(1, kWorkers);  // every warp is done with the previous unit's last tile and its exchange areas
     issue(0);
+    trace_event(cx, wtid, EV_ATT_INPUTS);
 
     // pass 1: row maximum and sum of exp over this warp's half of every tile
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
@@ -1969,6 +1970,7 @@ __device__ __noinline__ bool attention_prompt(const Ctx& cx, const AttnArgs& A_i
       if (n0 > -INFINITY) { l0 = l0 * expf(m0 - n0) + s0; m0 = n0; }
       if (n1 > -INFINITY) { l1 = l1 * expf(m1 - n1) + s1; m1 = n1; }
     }
+    trace_event(cx, wtid, EV_ATT_SCORES);
     {  // the two key halves' statistics meet: both warps of a row group form the same (max, sum), half 0 first
       float* mine = stat_x + (kh * 4 + rw) * 4 * 32 + lane;
       mine[0] = m0; mine[32] = l0; mine[64] = m1; mine[96] = l1;
@@ -2023,6 +2025,7 @@ __device__ __noinline__ bool attention_prompt(const Ctx& cx, const AttnArgs& A_i
         }
       }
     }
+    trace_event(cx, wtid, EV_ATT_VALUES);
     // the second half's fp32 sums join the first half's, which rounds once and stores
     float* sums = sum_x + rw * dtiles * 4 * 32 + lane;
     if (kh == 1) {
