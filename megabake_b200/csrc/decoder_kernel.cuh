@@ -62,6 +62,17 @@ struct SmemMisc {
 static_assert(sizeof(SmemMisc) <= kMiscBytes, "misc shared block too large");
 static_assert(kRingGranules < 256, "ring positions are kept in bytes");
 
+// Decode attention's cache stages in the weight ring (see attention_decode).
+#ifndef MK_DEC_STAGES
+#define MK_DEC_STAGES 3
+#endif
+#ifndef MK_DEC_TILE_KB
+#define MK_DEC_TILE_KB 32
+#endif
+constexpr int kDecStages = MK_DEC_STAGES;
+constexpr int kDecScratchBytes = 13 * 1024;  // q [8][128] fp32 and bf16, value partial sums [1024] fp32, new keys/values [2][512] bf16, statistics
+constexpr int kDecTileBytes = MK_DEC_TILE_KB * 1024;  // one stage
+
 // Tensor engine only: the activation ring's barriers and bookkeeping (behind SmemMisc).
 struct SmemMiscTc {
   uint64_t bfull[kChunkBars];
@@ -73,6 +84,14 @@ struct SmemMiscTc {
   int kv_seq;   // cache tiles fetched by TMA so far in this launch (stage and barrier parity of the next one)
   uint64_t kvfull[8];   // cache stages: the copy has landed
   uint64_t kvempty[8];  // cache stages: every worker warp is done with the tile
+  // The cache stream of one attention unit, asked for by the workers and issued by the (otherwise idle) weight
+  // producer: K tiles 0 .. nt-1, then V tiles 0 .. nt-1, of `tile_keys` positions from position t0 on.
+  int kv_req;           // units asked for so far in this launch (workers -> weight producer)
+  struct KvRequest {
+    const CUtensorMap *kmap, *vmap;
+    int t0, nt, tile_keys, chunk0, b, gtile;
+    uint32_t stage_bytes;
+  } kvr;
 };
 static_assert(sizeof(SmemMiscTc) <= kMiscTcBytes, "tensor-engine misc block too large");
 static_assert(kBBytes / kGranule < 256, "activation ring positions are kept in bytes");
@@ -274,8 +293,38 @@ __device__ __forceinline__ void ring_drain(const RingCursor& rc, uint64_t* full)
 //     [matrix 0: kb x (rows x 128 B, 128-byte swizzled)][matrix 1: ...]
 // One three-dimensional TMA box (64 elements, rows, kb chunks) brings a matrix's share, so a copy
 // carries 14-32 KB where a single chunk of a 56-row tile would carry 7 KB.
+// The cache stream of the attention unit the workers have posted (see attention_decode_stream): one tiled copy
+// per stage as soon as every worker warp has released the stage's previous tile.
+__device__ __noinline__ bool serve_cache_stream(const Ctx& cx) {
+  SmemMiscTc* tc = cx.tc;
+  __threadfence_block();
+  const volatile SmemMiscTc::KvRequest* r = &tc->kvr;
+  const CUtensorMap* const kmap = r->kmap;
+  const CUtensorMap* const vmap = r->vmap;
+  const int t0 = r->t0, nt = r->nt, tile_keys = r->tile_keys, chunk0 = r->chunk0, b = r->b, gtile = r->gtile;
+  const uint32_t stage_bytes = r->stage_bytes;
+  const uint32_t tiles = smem_u32(cx.smem_a);
+  const uint32_t kvfull0 = smem_u32(&tc->kvfull[0]), kvempty0 = smem_u32(&tc->kvempty[0]);
+  const uint64_t policy = l2_policy_evict_first();
+  int stage = gtile % kDecStages, use = gtile / kDecStages;  // earlier uses of `stage` in this launch
+#pragma unroll 1
+  for (int s = 0; s < 2 * nt; ++s) {
+    if (use > 0 && !wait_mbar(cx, kvempty0 + stage * 8u, (use - 1) & 1, SITE_KV_TILE, -s)) return false;
+    const uint32_t bar = kvfull0 + stage * 8u;
+    mbar_expect_tx(bar, stage_bytes);
+    const int t = (s < nt) ? s : s - nt;
+    tma_load_4d(tiles + stage * stage_bytes, (s < nt) ? kmap : vmap, 0, t0 + t * tile_keys, chunk0, b, bar, policy);
+    if (++stage == kDecStages) {
+      stage = 0;
+      ++use;
+    }
+  }
+  return true;
+}
+
 __device__ __noinline__ void producer_loop(const Ctx& cx) {
   const KParams& p = *cx.p;
+  int kv_served = 0;
   const uint64_t policy = p.stream_once ? l2_policy_evict_first() : l2_policy_evict_normal();
   const int ntok = token_tile(p.m);
   const int ntt = (p.m + ntok - 1) / ntok;
@@ -300,6 +349,14 @@ __device__ __noinline__ void producer_loop(const Ctx& cx) {
     if (ph->gate) {  // the attention phase before this one streams cache tiles through the ring
       uint32_t spins = 0;
       while (*reinterpret_cast<volatile int*>(&cx.tc->a_ready) <= gp) {
+        if (*reinterpret_cast<volatile int*>(&cx.tc->kv_req) != kv_served) {  // an attention unit wants its cache tiles
+          if (!serve_cache_stream(cx)) {
+            ok = false;
+            break;
+          }
+          ++kv_served;
+          continue;
+        }
         __nanosleep(64);
         if ((++spins & 255u) == 0 && give_up(cx, SITE_PRODUCER_EMPTY, -gp)) {
           ok = false;
@@ -904,9 +961,6 @@ __device__ __forceinline__ int decode_chunks(int keys, int rows, int grid, int g
 // The stages live in the weight ring, which is idle during attention (the weight producer waits at the
 // projection that follows, GemmPhase::gate): three stages of 32 KB keep two tiles, 64 KB per SM, in
 // flight.
-constexpr int kDecStages = 3;
-constexpr int kDecScratchBytes = 13 * 1024;  // q [8][128] fp32 and bf16, value partial sums [1024] fp32, new keys/values [2][512] bf16, statistics
-constexpr int kDecTileBytes = 32 * 1024;     // one stage
 static_assert(kScoreBytes + kDecScratchBytes <= kBBytes, "scores and scratch exceed their region");
 static_assert(kDecStages * kDecTileBytes <= kRingBytes, "cache stages exceed the weight ring");
 
@@ -1172,11 +1226,11 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A_i
       if (wtid < 16) __stcg(mine + wtid, stat[wtid]);
       __threadfence();
       named_bar_sync(1, kWorkers);
-      if (wtid == 0) st_relaxed_u32(reinterpret_cast<uint32_t*>(mine + 16), A.stamp);
+      if (wtid == 0) st_relaxed_u32(reinterpret_cast<uint32_t*>(mine + kXchStatsFlag), A.stamp);
       bool ok = true;
       if (wtid < nch) {
         const uint32_t* theirs = reinterpret_cast<const uint32_t*>(
-            p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + wtid) * kExchangeFloats + 16);
+            p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + wtid) * kExchangeFloats + kXchStatsFlag);
         uint32_t spins = 0;
         while (ld_relaxed_u32(theirs) != A.stamp) {
           if ((++spins & 255u) == 0 && give_up(cx, SITE_ATT_EXCHANGE, rowg)) {
@@ -1260,12 +1314,12 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A_i
       float* mine = p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + ch) * kExchangeFloats;
       __threadfence();
       named_bar_sync(1, kWorkers);
-      if (wtid == 0) st_relaxed_u32(reinterpret_cast<uint32_t*>(mine + 17), A.stamp);
+      if (wtid == 0) st_relaxed_u32(reinterpret_cast<uint32_t*>(mine + kXchPartsFlag), A.stamp);
       if (ch == 0) {
         bool ok = true;
         if (wtid < nch) {
           const uint32_t* theirs = reinterpret_cast<const uint32_t*>(
-              p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + wtid) * kExchangeFloats + 17);
+              p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + wtid) * kExchangeFloats + kXchPartsFlag);
           uint32_t spins = 0;
           while (ld_relaxed_u32(theirs) != A.stamp) {
             if ((++spins & 255u) == 0 && give_up(cx, SITE_ATT_EXCHANGE, rowg)) {
@@ -1405,27 +1459,26 @@ __device__ __noinline__ bool attention_decode_stream(const Ctx& cx, const AttnAr
     const bf16* vbase = A.v + b * A.kv_bstride + kvh0 * hd;
     named_bar_sync(1, kWorkers);  // previous unit is done with the scratch and the stages
 
-    // Element s of the stream is K tile s (s < nt) or V tile s - nt; it uses stage s % kDecStages.
-    // Every call commits one group, an empty one past the end, so that the group count is uniform.
+    // Element s of the stream is K tile s (s < nt) or V tile s - nt; it uses stage (gtile + s) % kDecStages.
+    // The copies are the weight producer's: it waits at the projection that follows this phase, takes the
+    // request below and issues a stage's next copy as soon as every worker warp has released the stage, so
+    // all the stages but the one being read stay in flight and no worker spends time on issuing.
     auto stage_of = [&](int s) -> int { return (gtile + s) % kDecStages; };
-    auto issue = [&](int s) {
-      if (s < 2 * nt) {
-        const int t = (s < nt) ? s : s - nt;
-        const int t0 = j0 + t * tile_keys, t1 = min(j1, t0 + tile_keys);
-        const uint32_t dst = tiles_addr + stage_of(s) * stage_bytes;
-        if (use_tma) {
-          if (wtid == ((s & (kWorkerWarps - 1)) << 5)) {  // the warps take turns: issuing costs its thread ~0.7 us
-            const int use = (gtile + s) / kDecStages;     // earlier uses of this stage in the launch
-            if (use > 0 && !wait_mbar(cx, kvempty0 + stage_of(s) * 8u, (use - 1) & 1, SITE_KV_TILE, -s)) return;
-            fence_proxy_async_all();  // the stage was read, and maybe patched, through the generic proxy
-            const uint32_t bar = kvfull0 + stage_of(s) * 8u;
-            mbar_expect_tx(bar, static_cast<uint32_t>(stage_bytes));
-            tma_load_4d(dst, (s < nt) ? A.kmap : A.vmap, 0, t0, kvh0 * cph, b, bar, kv_policy);
-          }
-        }
-      }
-      if (!use_tma) cp_async_commit();
-    };
+    if (wtid == 0) {
+      SmemMiscTc* tc = cx.tc;
+      tc->kvr.kmap = A.kmap;
+      tc->kvr.vmap = A.vmap;
+      tc->kvr.t0 = j0;
+      tc->kvr.nt = nt;
+      tc->kvr.tile_keys = tile_keys;
+      tc->kvr.chunk0 = kvh0 * cph;
+      tc->kvr.b = b;
+      tc->kvr.gtile = gtile;
+      tc->kvr.stage_bytes = static_cast<uint32_t>(stage_bytes);
+      __threadfence_block();
+      *reinterpret_cast<volatile int*>(&tc->kv_req) = tc->kv_req + 1;
+    }
+    auto issue = [&](int) {};
     // Tile s of the unit has landed (every thread waits: a copy's bytes are visible to the threads that saw its barrier flip).
     auto landed = [&](int s) -> bool {
       if (!use_tma) {
@@ -1434,43 +1487,43 @@ __device__ __noinline__ bool attention_decode_stream(const Ctx& cx, const AttnAr
       }
       return wait_mbar(cx, kvfull0 + stage_of(s) * 8u, ((gtile + s) / kDecStages) & 1, SITE_KV_TILE, s);
     };
-#pragma unroll
-    for (int s = 0; s < kDecStages - 1; ++s) issue(s);
 
-    // --- q of every query head of the unit and the new keys (rotated if asked), and the new values
+    // --- q of every query head of the unit and the new keys (rotated if asked), and the new values: one thread
+    // per pair of 16-byte vectors (elements i..i+7 and i+half..), every load of the phase in one round trip
     {
       long long pos = 0;
       if (A.rope) {
         pos = p.pos[b];
         if (pos < 0 || pos >= p.max_positions) pos = 0;  // reported by the prologue
       }
-#pragma unroll 1
-      for (int idx = wtid; idx < (G + hpu) * half; idx += kWorkers) {
-        const int g = idx / half, i = idx - g * half;  // g < G: query head g of the unit; else new key of KV head g - G
+      const int vecs = half / 8;
+      const int rot_items = (G + hpu) * vecs;  // <= 128
+      const int v_items = hpu * hd / 8;        // <= 64
+      if (wtid < rot_items) {
+        const int g = wtid / vecs, i = (wtid - g * vecs) * 8;  // g < G: query head g of the unit; else new key of KV head g - G
         const bf16* src = (g < G) ? A.q + b * A.q_bstride + (kvh0 * gs + g) * hd
                                   : A.knew + static_cast<long long>(b) * A.new_ld + (kvh0 + g - G) * hd;
-        float first = ldcg_bf16(src + i);
-        float second = ldcg_bf16(src + i + half);
+        float first[8], second[8];
+        unpack8(__ldcg(reinterpret_cast<const uint4*>(src + i)), first);
+        unpack8(__ldcg(reinterpret_cast<const uint4*>(src + i + half)), second);
         if (A.rope) {
-          const float c = ldg_bf16(p.cos_t + pos * hd + i);
-          const float sn = ldg_bf16(p.sin_t + pos * hd + i);
-          rope_pair(first, second, c, sn, p.rope_style, first, second);
+          float c[8], sn[8];
+          unpack8(__ldg(reinterpret_cast<const uint4*>(p.cos_t + pos * hd + i)), c);
+          unpack8(__ldg(reinterpret_cast<const uint4*>(p.sin_t + pos * hd + i)), sn);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) rope_pair(first[e], second[e], c[e], sn[e], p.rope_style, first[e], second[e]);
         }
-        if (g < G) {
-          qs[g * hd + i] = first;
-          qs[g * hd + i + half] = second;
-          qb[g * hd + i] = __float2bfloat16_rn(first);  // exact: both are bf16 values
-          qb[g * hd + i + half] = __float2bfloat16_rn(second);
-        } else {
-          kn[(g - G) * hd + i] = __float2bfloat16_rn(first);
-          kn[(g - G) * hd + i + half] = __float2bfloat16_rn(second);
-        }
+        bf16* dst = (g < G) ? qb + g * hd : kn + (g - G) * hd;  // exact: the rotated values are bf16 values
+        *reinterpret_cast<uint4*>(dst + i) = pack8(first);
+        *reinterpret_cast<uint4*>(dst + i + half) = pack8(second);
+      } else if (wtid >= 128 && wtid - 128 < v_items) {
+        const int i = (wtid - 128) * 8;
+        *reinterpret_cast<uint4*>(vn + i) =
+            __ldcg(reinterpret_cast<const uint4*>(A.vnew + static_cast<long long>(b) * A.new_ld + kvh0 * hd + i));
       }
-#pragma unroll 1
-      for (int i = wtid; i < hpu * hd; i += kWorkers)
-        vn[i] = __float2bfloat16_rn(ldcg_bf16(A.vnew + static_cast<long long>(b) * A.new_ld + kvh0 * hd + i));
     }
     named_bar_sync(1, kWorkers);
+    trace_event(cx, wtid, EV_ATT_INPUTS);
     uint32_t qfrag[8][2];  // B fragments of this warp's KV head: q[dims][query heads], one pair per 16 dimensions
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
@@ -1580,75 +1633,69 @@ __device__ __noinline__ bool attention_decode_stream(const Ctx& cx, const AttnAr
       }
     }
     named_bar_sync(1, kWorkers);
+    trace_event(cx, wtid, EV_ATT_SCORES);
 
-    // --- chunk max, then chunk sum of exp(score - chunk max); the first V tiles are in flight meanwhile
+    // --- chunk max and chunk sum of exp(score - chunk max); the first V tiles are in flight meanwhile.  Warp g
+    // owns query head g of the unit (at most eight): no block barrier until every head's numbers are in `stat`.
+    {
+      bool fresh = true;
+      if (warp < G) {
+        const float* mine = sc + warp * chunk;
+        float m = -INFINITY;
 #pragma unroll 1
-    for (int g = 0; g < G; ++g) {
-      float m = -INFINITY;
+        for (int i = lane; i < cl; i += 32) m = fmaxf(m, mine[i]);
+        m = warp_max(m);
+        float sum = 0.f;
 #pragma unroll 1
-      for (int i = wtid; i < cl; i += kWorkers) m = fmaxf(m, sc[g * chunk + i]);
-      m = warp_max(m);
-      if (lane == 0) red[warp * 8 + g] = m;
-    }
-    named_bar_sync(1, kWorkers);
-#pragma unroll 1
-    for (int g = 0; g < G; ++g) {
-      float m = red[g];
-#pragma unroll
-      for (int w = 1; w < kWorkerWarps; ++w) m = fmaxf(m, red[w * 8 + g]);
-      float sum = 0.f;
-#pragma unroll 1
-      for (int i = wtid; i < cl; i += kWorkers) sum += expf(sc[g * chunk + i] - m);
-      sum = warp_sum(sum);
-      if (lane == 0) red[kWorkerWarps * 8 + warp * 8 + g] = sum;
-      if (wtid == 0) stat[g] = m;
-    }
-    named_bar_sync(1, kWorkers);
-    if (wtid < G) {
-      float total = 0.f;
-#pragma unroll
-      for (int w = 0; w < kWorkerWarps; ++w) total += red[kWorkerWarps * 8 + w * 8 + wtid];
-      stat[8 + wtid] = total;
-    }
-    named_bar_sync(1, kWorkers);
-
-    if (nch > 1) {
-      // --- publish (max, sum) with this phase's stamp; wait for every chunk of the row group
-      float* mine = p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + ch) * kExchangeFloats;
-      if (wtid < 16) __stcg(mine + wtid, stat[wtid]);
-      __threadfence();
-      named_bar_sync(1, kWorkers);
-      if (wtid == 0) st_relaxed_u32(reinterpret_cast<uint32_t*>(mine + 16), A.stamp);
-      bool ok = true;
-      if (wtid < nch) {
-        const uint32_t* theirs = reinterpret_cast<const uint32_t*>(
-            p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + wtid) * kExchangeFloats + 16);
-        uint32_t spins = 0;
-        while (ld_relaxed_u32(theirs) != A.stamp) {
-          if ((++spins & 255u) == 0 && give_up(cx, SITE_ATT_EXCHANGE, rowg)) {
-            ok = false;
-            break;
+        for (int i = lane; i < cl; i += 32) sum += expf(mine[i] - m);
+        sum = warp_sum(sum);
+        if (nch > 1) {
+          // publish (max, sum), each with this phase's stamp in one 64-bit word (a reader that sees the stamp has
+          // the value: no fence, no flag), and wait for the same two words of every chunk of the row group
+          constexpr int kWords = kExchangeFloats / 2;
+          unsigned long long* rec = reinterpret_cast<unsigned long long*>(p.att_xch) +
+                                    static_cast<size_t>(rowg) * kMaxChunks * kWords;
+          const unsigned long long tag = static_cast<unsigned long long>(A.stamp) << 32;
+          if (lane == 0) {
+            st_relaxed_u64(rec + ch * kWords + warp, tag | __float_as_uint(m));
+            st_relaxed_u64(rec + ch * kWords + 8 + warp, tag | __float_as_uint(sum));
           }
+          float cm = -INFINITY, cs = 0.f;
+          if (lane < nch) {
+#pragma unroll
+            for (int which = 0; which < 2; ++which) {
+              const unsigned long long* word = rec + lane * kWords + which * 8 + warp;
+              unsigned long long w = ld_relaxed_u64(word);
+              uint32_t spins = 0;
+              while (static_cast<uint32_t>(w >> 32) != A.stamp) {
+                if ((++spins & 255u) == 0 && give_up(cx, SITE_ATT_EXCHANGE, rowg)) {
+                  fresh = false;
+                  break;
+                }
+                w = ld_relaxed_u64(word);
+              }
+              const float value = __uint_as_float(static_cast<uint32_t>(w));
+              if (which == 0) cm = value; else cs = value;
+            }
+          }
+          m = warp_max(cm);
+          sum = 0.f;  // in chunk order, as one thread would add them
+#pragma unroll 1
+          for (int c = 0; c < nch; ++c)
+            sum += __shfl_sync(0xffffffffu, cs, c) * expf(__shfl_sync(0xffffffffu, cm, c) - m);
         }
-        __threadfence();
+        if (lane == 0) {
+          stat[warp] = m;
+          stat[8 + warp] = sum;
+        }
       }
-      if (!workers_ok(cx, ok)) {
+      if (!workers_ok(cx, fresh)) {
         cp_async_wait_all();  // nothing of this CTA stays in flight past the return
         return false;
       }
-      if (wtid < G) {
-        const float* all = p.att_xch + static_cast<size_t>(rowg) * kMaxChunks * kExchangeFloats;
-        float m = -INFINITY;
-        for (int c = 0; c < nch; ++c) m = fmaxf(m, __ldcg(all + c * kExchangeFloats + wtid));
-        float sum = 0.f;
-        for (int c = 0; c < nch; ++c)
-          sum += __ldcg(all + c * kExchangeFloats + 8 + wtid) * expf(__ldcg(all + c * kExchangeFloats + wtid) - m);
-        stat[wtid] = m;
-        stat[8 + wtid] = sum;
-      }
-      named_bar_sync(1, kWorkers);
     }
 
+    trace_event(cx, wtid, EV_ATT_STATS);
     // --- probabilities (bf16, against the global max and sum)
 #pragma unroll 1
     for (int g = 0; g < G; ++g) {
@@ -1740,6 +1787,7 @@ __device__ __noinline__ bool attention_decode_stream(const Ctx& cx, const AttnAr
         }
       }
     }
+    trace_event(cx, wtid, EV_ATT_VALUES);
     if (use_tma && !workers_ok(cx, tiles_ok)) {
       // a tile never came: give the copies still in flight a bounded time to land before the CTA leaves
       for (int st = 0; st < kDecStages; ++st)
@@ -1778,18 +1826,19 @@ __device__ __noinline__ bool attention_decode_stream(const Ctx& cx, const AttnAr
         __stcg(p.att_part + (row * kMaxChunks + ch) * hd + d, o);
       }
     }
+    trace_event(cx, wtid, EV_ATT_PARTIAL);
     if (nch > 1 && A.combine) {
       // There is no consumer phase that adds chunk partials: chunk 0's CTA waits for the partials of its
       // peers (second stamp) and sums them in chunk order.
       float* mine = p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + ch) * kExchangeFloats;
       __threadfence();
       named_bar_sync(1, kWorkers);
-      if (wtid == 0) st_relaxed_u32(reinterpret_cast<uint32_t*>(mine + 17), A.stamp);
+      if (wtid == 0) st_relaxed_u32(reinterpret_cast<uint32_t*>(mine + kXchPartsFlag), A.stamp);
       if (ch == 0) {
         bool ok = true;
         if (wtid < nch) {
           const uint32_t* theirs = reinterpret_cast<const uint32_t*>(
-              p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + wtid) * kExchangeFloats + 17);
+              p.att_xch + (static_cast<size_t>(rowg) * kMaxChunks + wtid) * kExchangeFloats + kXchPartsFlag);
           uint32_t spins = 0;
           while (ld_relaxed_u32(theirs) != A.stamp) {
             if ((++spins & 255u) == 0 && give_up(cx, SITE_ATT_EXCHANGE, rowg)) {
@@ -2395,6 +2444,7 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
     cx.tc->b_ready = 0;
     cx.tc->a_ready = 0;
     cx.tc->kv_seq = 0;
+    cx.tc->kv_req = 0;
     for (int st = 0; st < 8; ++st) {
       mbar_init(smem_u32(&cx.tc->kvfull[st]), 1);
       mbar_init(smem_u32(&cx.tc->kvempty[st]), kWorkerWarps);

@@ -31,8 +31,10 @@ constexpr int kMiscTcBytes = 3072;       // tensor engine only: barriers of the 
 constexpr int kSmemBytes = 1024 /*alignment slack*/ + kRingBytes + kBBytes + kMiscBytes + kMiscTcBytes;
 constexpr int kMaxChunks = 16;           // split-context chunks per (sequence, kv head)
 constexpr int kScoreBytes = 40960;       // fp32 scores of one attention unit (inside the B region)
-constexpr int kExchangeFloats = 32;      // per (row group, chunk), 128 bytes: max[8], sum[8], stamps (mk::megakernel),
-                                         // or 16 values each paired with the stamp in one 64-bit word (small-launch kernel)
+constexpr int kExchangeFloats = 48;      // per (row group, chunk), 192 bytes: max[8], sum[8] as plain floats (the flag protocol) or each
+                                         // paired with the phase's stamp in one 64-bit word (16 words), then the two flags
+constexpr int kXchStatsFlag = 32;        // float index of "the statistics are out" (flag protocol)
+constexpr int kXchPartsFlag = 33;        // float index of "the chunk's partial sums are out"
 constexpr int kMaxSplit = 4;             // K slices a projection may be cut into
 constexpr int kSplitTokens = 4;          // launches with at most this many tokens use the split-K table
 
