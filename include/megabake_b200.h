@@ -302,7 +302,7 @@ int mk_launch_info(mk_handle handle, int32_t* ctas, int32_t* smem_bytes, int64_t
  * to its own pool at start and forbids later allocations; a call site where an
  * allocation would serialise the device).  This entry point has no counterpart in
  * the reference.  The exchange buffers live in a 4 MiB array inside the library
- * image: batch * 16 * (128 * kv_heads + 4 * head_dim * q_heads) bytes (+ 512) must
+ * image: batch * 16 * (192 * kv_heads + 4 * head_dim * q_heads) bytes (+ 512) must
  * fit, e.g. batch 16 x 32 heads x head_dim 64; larger shapes return
  * MK_ERR_WORKSPACE (use mk_kv_attention with a caller workspace).  `device` must be
  * the current device.  The first call on a device looks the array up, sets the
