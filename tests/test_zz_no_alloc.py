@@ -101,7 +101,7 @@ def test_static_scratch_entry_point_rejects_what_does_not_fit():
     device = torch.device("cuda:0")
     torch.cuda.set_device(device)
     lib = _native.load()
-    batch, heads, dim = 64, 32, 128  # 64 * 16 * (80 * 32 + 4 * 128 * 32) bytes = 19 MiB > 4 MiB
+    batch, heads, dim = 64, 32, 128  # 64 * 16 * (192 * 32 + 4 * 128 * 32) bytes = 22 MiB > 4 MiB
     tensor = torch.zeros(batch, 1, heads, dim, dtype=torch.bfloat16, device=device)
     cache = torch.zeros(batch, 2, heads, dim, dtype=torch.bfloat16, device=device)
     length = torch.zeros(1, dtype=torch.int32, device=device)
