@@ -1374,12 +1374,12 @@ __device__ __noinline__ bool attention_decode_stream(const Ctx& cx, const AttnAr
   // loaded again (a kernel parameter through the context: two dependent loads).
   const AttnArgs A = A_in;
   struct {
-    int head_dim, q_heads, kv_heads, batch, max_positions, rope_style, prefill_rope_style, m;
+    int head_dim, q_heads, kv_heads, batch, max_positions, rope_style;
     const bf16 *cos_t, *sin_t;
     float *att_xch, *att_part;
     long long* pos;
   } p = {cx.p->head_dim, cx.p->q_heads, cx.p->kv_heads, cx.p->batch, cx.p->max_positions, cx.p->rope_style,
-         cx.p->prefill_rope_style, cx.p->m, cx.p->cos_t, cx.p->sin_t, cx.p->att_xch, cx.p->att_part, cx.p->pos};
+         cx.p->cos_t,    cx.p->sin_t,   cx.p->att_xch,  cx.p->att_part, cx.p->pos};
   const int hd = p.head_dim, half = hd / 2;
   const int gs = p.q_heads / p.kv_heads;
   const int hpu = decode_heads_per_unit(p.kv_heads, gs, hd);  // KV heads per unit
@@ -1394,55 +1394,42 @@ __device__ __noinline__ bool attention_decode_stream(const Ctx& cx, const AttnAr
   const int units = rows * nch;
   const int row_bytes = hd * 2;
   const int tile_keys = kDecTileBytes / (row_bytes * hpu);
-  const int sub_bytes = tile_keys * row_bytes;     // one head's sub-tile
-  const int stage_bytes = sub_bytes * hpu;
+  const int stage_bytes = tile_keys * row_bytes * hpu;
 
   float* sc = reinterpret_cast<float*>(cx.smem_b);                                      // [G][chunk]
   uint8_t* tiles = cx.smem_a;                                                           // [stages][hpu][tile_keys][hd] bf16, in the weight ring
-  float* qs = reinterpret_cast<float*>(cx.smem_b + kBBytes - kDecScratchBytes);         // [G][hd]
-  float* red = qs + 8 * 128;                                                            // [worker warps][8] x 2, then [parts][G*hd]
+  float* red = reinterpret_cast<float*>(cx.smem_b + kBBytes - kDecScratchBytes) + 8 * 128;  // [G * hd] value sums (same carve-up as attention_decode)
   bf16* kn = reinterpret_cast<bf16*>(red + 1024);                                       // [hpu][hd]
   bf16* vn = kn + 512;                                                                  // [hpu][hd]
   float* stat = reinterpret_cast<float*>(vn + 512);                                     // [16]: max[8], sum[8]
   bf16* qb = reinterpret_cast<bf16*>(stat + 16);                                        // [G][hd], q again as bf16 (exact)
   const uint32_t tiles_addr = smem_u32(tiles);
-  // Both products run on the warp-level tensor cores when the unit's KV heads divide the eight worker
-  // warps: one mma.sync (m16n8k16) multiplies 16 cached positions x 16 head dimensions by the (up to
-  // eight) query heads of a KV head, where the CUDA-core loops needed 17 instructions per lane for eight
-  // elements and kept this phase, not the cache stream, bound by instruction issue.
+  // Both products run on the warp-level tensor cores (the caller checked with decode_stream_ok() that the
+  // unit's KV heads divide the eight worker warps): one mma.sync (m16n8k16) multiplies 16 cached positions x
+  // 16 head dimensions by the (up to eight) query heads of a KV head, where the CUDA-core loops of
+  // attention_decode need 17 instructions per lane for eight elements and keep that phase, not the cache
+  // stream, bound by instruction issue.
   //   scores:  D[16 keys][heads]  = K tile (ldmatrix)        x q[dims][heads]   (q fragments stay in registers)
   //   values:  D[16 dims][heads] += V tile^T (ldmatrix.trans) x p[keys][heads]
   // Warp w works for KV head w % hpu; the 8 / hpu warps of a head split the 16-key blocks (scores) and
   // the 16-dimension tiles of the output row (values).
-  constexpr bool use_mma = true;  // the caller checked decode_stream_ok()
   // Tensor-core layout of a stage: the unit's cache rows as sub-tiles of 64 dimensions, [chunk][key][128 B]
-  // with the 16-byte pieces of a row exchanged by key % 8 (the 128-byte swizzle of a tiled TMA copy, also
-  // what the cp.async path writes), chunk = head * (head_dim / 64) + dimension / 64.
+  // with the 16-byte pieces of a row exchanged by key % 8 (the 128-byte swizzle of a tiled TMA copy),
+  // chunk = head * (head_dim / 64) + dimension / 64.
   const int cph = hd / 64;                       // chunks per head
   const uint32_t csub = tile_keys * 128u;        // one chunk's sub-tile
   auto piece_at = [&](uint32_t stage, int head, int key, int piece) -> uint32_t {
     return stage + (head * cph + (piece >> 3)) * csub + key * 128u + (((piece & 7) ^ (key & 7)) << 4);
   };
-  // With descriptors of the two caches (decode through mk_decode*), one tiled TMA copy brings a whole stage
-  // (box = 64 dimensions x tile_keys positions x the unit's chunks); cp.async, 16 bytes per thread and
-  // request, measured 17 GB/s per SM on this stream, a third of an SM's share of HBM.
-  constexpr bool use_tma = true;
+  // One tiled TMA copy brings a whole stage (box = 64 dimensions x tile_keys positions x the unit's chunks);
+  // cp.async, 16 bytes per thread and request, measured 17 GB/s per SM on this stream, a third of an SM's share
+  // of HBM.
   const uint32_t kvfull0 = smem_u32(&cx.tc->kvfull[0]), kvempty0 = smem_u32(&cx.tc->kvempty[0]);
-  const uint64_t kv_policy = l2_policy_evict_first();
   int gtile = cx.tc->kv_seq;  // cache tiles issued by this CTA before this unit (same value in every thread)
   const int my_head = warp & (hpu - 1), head_warps = kWorkerWarps / hpu, my_slot = warp / hpu;
   const int ksteps = hd / 16, dim_tiles = hd / 16;
   const int lg = lane >> 2, lt = lane & 3;
-
-  // value accumulation: an item is (part of the keys, query head of the unit, 16-byte piece of the output row);
-  // part q takes keys q, q + parts, ... of every tile; the fp32 sums of an item stay in `red` between tiles
   const int cols = G * hd;
-  const int pieces = G * lpk;
-  int parts = kWorkers / pieces;
-  if (parts * cols > 1024) parts = 1024 / cols;
-  if (parts < 1) parts = 1;
-  const int items = parts * pieces;  // <= kWorkers
-  const int item_part = wtid / pieces, item_g = (wtid - item_part * pieces) / lpk, item_piece = wtid % lpk;
 
 #pragma unroll 1
   for (int u = cx.cta; u < units; u += cx.grid) {
@@ -1455,8 +1442,6 @@ __device__ __noinline__ bool attention_decode_stream(const Ctx& cx, const AttnAr
     const int newpos = filled;
     const bool owner = (filled >= j0 && filled < j1);
     const int nt = (cl + tile_keys - 1) / tile_keys;
-    const bf16* kbase = A.k + b * A.kv_bstride + kvh0 * hd;
-    const bf16* vbase = A.v + b * A.kv_bstride + kvh0 * hd;
     named_bar_sync(1, kWorkers);  // previous unit is done with the scratch and the stages
 
     // Element s of the stream is K tile s (s < nt) or V tile s - nt; it uses stage (gtile + s) % kDecStages.
@@ -1478,13 +1463,8 @@ __device__ __noinline__ bool attention_decode_stream(const Ctx& cx, const AttnAr
       __threadfence_block();
       *reinterpret_cast<volatile int*>(&tc->kv_req) = tc->kv_req + 1;
     }
-    auto issue = [&](int) {};
     // Tile s of the unit has landed (every thread waits: a copy's bytes are visible to the threads that saw its barrier flip).
     auto landed = [&](int s) -> bool {
-      if (!use_tma) {
-        cp_async_wait_group<kDecStages - 2>();
-        return true;
-      }
       return wait_mbar(cx, kvfull0 + stage_of(s) * 8u, ((gtile + s) / kDecStages) & 1, SITE_KV_TILE, s);
     };
 
@@ -1528,7 +1508,7 @@ __device__ __noinline__ bool attention_decode_stream(const Ctx& cx, const AttnAr
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
       qfrag[ks][0] = qfrag[ks][1] = 0u;
-      if (use_mma && ks < ksteps && lg < gs) {
+      if (ks < ksteps && lg < gs) {
         const bf16* at = qb + (my_head * gs + lg) * hd + ks * 16 + lt * 2;
         qfrag[ks][0] = *reinterpret_cast<const uint32_t*>(at);
         qfrag[ks][1] = *reinterpret_cast<const uint32_t*>(at + 8);
@@ -1547,8 +1527,7 @@ __device__ __noinline__ bool attention_decode_stream(const Ctx& cx, const AttnAr
     auto patch = [&](uint8_t* tile, const bf16* fresh, int local) {
       if (wtid < hpu * lpk) {
         const int head = wtid / lpk, piece = wtid - head * lpk;
-        uint8_t* at = use_mma ? tile + piece_at(0u, head, local, piece)
-                              : tile + head * sub_bytes + local * row_bytes + ((piece ^ (local & 7)) << 4);
+        uint8_t* at = tile + piece_at(0u, head, local, piece);
         *reinterpret_cast<uint4*>(at) = *reinterpret_cast<const uint4*>(fresh + head * hd + piece * 8);
       }
     };
@@ -1559,78 +1538,38 @@ __device__ __noinline__ bool attention_decode_stream(const Ctx& cx, const AttnAr
       __syncwarp();
       if (lane == 0) mbar_arrive(kvempty0 + stage_of(s) * 8u);
     };
-    if (use_tma) {
-      // --- scores, pipelined: no block barrier per tile.  A warp waits for the tile's copy, takes the scores of
-      // its head's key blocks, releases the stage; the warp whose turn it is then issues the copy S - 1 tiles on.
-      // Only the tile that holds the new position needs the block (its row is patched in by a few threads).
+    // --- scores, pipelined: no block barrier per tile.  A warp waits for the tile's copy, takes the scores of
+    // its head's key blocks and releases the stage; the weight producer refills it.
+    // Only the tile that holds the new position needs the block (its row is patched in by a few threads).
 #pragma unroll 1
-      for (int s = 0; s < nt; ++s) {
-        const int t0 = j0 + s * tile_keys, t1 = min(j1, t0 + tile_keys);
-        uint8_t* tile = tiles + stage_of(s) * stage_bytes;
-        tiles_ok = landed(s) && tiles_ok;
-        if (newpos >= t0 && newpos < t1) {
-          patch(tile, kn, newpos - t0);
-          fence_proxy_async_all();
-          named_bar_sync(1, kWorkers);
-        }
-        const int tk = t1 - t0;
-        const uint32_t stage = smem_u32(tile);
-#pragma unroll 1
-        for (int blk = my_slot; blk * 16 < tk; blk += head_warps) {
-          float d[4] = {0.f, 0.f, 0.f, 0.f};
-          const int row = blk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-#pragma unroll 2
-          for (int ks = 0; ks < ksteps; ++ks) {
-            uint32_t af[4];
-            ldmatrix_x4(af, piece_at(stage, my_head, row, ks * 2 + (lane >> 4)));
-            mma_bf16_16816(d, af, qfrag[ks][0], qfrag[ks][1]);
-          }
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int key = blk * 16 + lg + (e >> 1) * 8, n = lt * 2 + (e & 1);
-            if (n < gs && key < tk) sc[(my_head * gs + n) * chunk + (t0 - j0) + key] = bf16_round(d[e]) * A.scale;
-          }
-        }
-        release(s);
-        issue(s + kDecStages - 1);
-      }
-    }
-    // --- scores: one thread per (query head of the unit, key), a head_dim-term fp32 chain each
-#pragma unroll 1
-    for (int s = 0; s < (use_tma ? 0 : nt); ++s) {
+    for (int s = 0; s < nt; ++s) {
       const int t0 = j0 + s * tile_keys, t1 = min(j1, t0 + tile_keys);
       uint8_t* tile = tiles + stage_of(s) * stage_bytes;
       tiles_ok = landed(s) && tiles_ok;
-      if (newpos >= t0 && newpos < t1) patch(tile, kn, newpos - t0);
-      named_bar_sync(1, kWorkers);  // tile s is complete; every thread is done with tile s - 1
-      issue(s + kDecStages - 1);
-      const int tk = t1 - t0;
-      const int tk_shift = (tk & (tk - 1)) == 0 ? 31 - __clz(tk) : -1;  // full tiles hold a power of two of keys
-#pragma unroll 1
-      for (int item = wtid; item < G * tk; item += kWorkers) {
-        const int g = tk_shift >= 0 ? item >> tk_shift : item / tk, key = item - g * tk;
-        const uint8_t* krow = tile + (g / gs) * sub_bytes + key * row_bytes;
-        const float* qv = qs + g * hd;
-        // four partial sums (pieces 0, 4, 8, ... / 1, 5, ... / ...): the chains have to be independent
-        float part[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 1
-        for (int piece0 = 0; piece0 < lpk; piece0 += 4) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const int piece = piece0 + c;
-            float kf[8];
-            unpack8(*reinterpret_cast<const uint4*>(krow + ((piece ^ (key & 7)) << 4)), kf);
-            const float4 qa = *reinterpret_cast<const float4*>(qv + piece * 8);
-            const float4 qb = *reinterpret_cast<const float4*>(qv + piece * 8 + 4);
-            float acc = part[c];
-            acc = fmaf(qa.x, kf[0], acc); acc = fmaf(qa.y, kf[1], acc); acc = fmaf(qa.z, kf[2], acc); acc = fmaf(qa.w, kf[3], acc);
-            acc = fmaf(qb.x, kf[4], acc); acc = fmaf(qb.y, kf[5], acc); acc = fmaf(qb.z, kf[6], acc); acc = fmaf(qb.w, kf[7], acc);
-            part[c] = acc;
-          }
-        }
-        const float dot = (part[0] + part[1]) + (part[2] + part[3]);
-        sc[g * chunk + (t0 - j0) + key] = bf16_round(dot) * A.scale;
+      if (newpos >= t0 && newpos < t1) {
+        patch(tile, kn, newpos - t0);
+        fence_proxy_async_all();
+        named_bar_sync(1, kWorkers);
       }
+      const int tk = t1 - t0;
+      const uint32_t stage = smem_u32(tile);
+#pragma unroll 1
+      for (int blk = my_slot; blk * 16 < tk; blk += head_warps) {
+        float d[4] = {0.f, 0.f, 0.f, 0.f};
+        const int row = blk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll 2
+        for (int ks = 0; ks < ksteps; ++ks) {
+          uint32_t af[4];
+          ldmatrix_x4(af, piece_at(stage, my_head, row, ks * 2 + (lane >> 4)));
+          mma_bf16_16816(d, af, qfrag[ks][0], qfrag[ks][1]);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = blk * 16 + lg + (e >> 1) * 8, n = lt * 2 + (e & 1);
+          if (n < gs && key < tk) sc[(my_head * gs + n) * chunk + (t0 - j0) + key] = bf16_round(d[e]) * A.scale;
+        }
+      }
+      release(s);
     }
     named_bar_sync(1, kWorkers);
     trace_event(cx, wtid, EV_ATT_SCORES);
@@ -1704,119 +1643,83 @@ __device__ __noinline__ bool attention_decode_stream(const Ctx& cx, const AttnAr
       for (int i = wtid; i < cl; i += kWorkers) sc[g * chunk + i] = bf16_round(expf(sc[g * chunk + i] - m) / denom);
     }
     // --- value sums, tile by tile
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    float vacc[4][4];  // tensor-core form: D[16 dims][query heads] of up to four dimension tiles of this warp's KV head
+    float vacc[4][4];  // D[16 dims][query heads] of up to four dimension tiles of this warp's KV head
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
       for (int e = 0; e < 4; ++e) vacc[i][e] = 0.f;
-    if (use_tma) {
-      // --- value sums, pipelined like the scores.  The block meets once before the first tile (the
-      // probabilities are complete) and in the tiles that are written by hand (new row, zeroed tail).
-      named_bar_sync(1, kWorkers);
+    // --- value sums, pipelined like the scores.  The block meets once before the first tile (the
+    // probabilities are complete) and in the tiles that are written by hand (new row, zeroed tail).
+    named_bar_sync(1, kWorkers);
 #pragma unroll 1
-      for (int s = nt; s < 2 * nt; ++s) {
-        const int t0 = j0 + (s - nt) * tile_keys, t1 = min(j1, t0 + tile_keys);
-        uint8_t* tile = tiles + stage_of(s) * stage_bytes;
-        tiles_ok = landed(s) && tiles_ok;
-        const int tk = t1 - t0;
-        const bool has_new = newpos >= t0 && newpos < t1, short_tile = (tk & 15) != 0;
-        if (has_new || short_tile) {
-          if (has_new) patch(tile, vn, newpos - t0);  // the new value rows join their tile
-          if (short_tile) {
-            // the last 16-key block of a short tile: rows past the tile's keys meet zero probabilities, but what
-            // the stage holds there must be finite for that product to be zero
-            const int count = 16 - (tk & 15), per_row = hpu * lpk;
-            for (int it = wtid; it < count * per_row; it += kWorkers) {
-              const int r = tk + it / per_row, rest = it % per_row;
-              *reinterpret_cast<uint4*>(tile + piece_at(0u, rest / lpk, r, rest % lpk)) = make_uint4(0, 0, 0, 0);
-            }
-          }
-          fence_proxy_async_all();
-          named_bar_sync(1, kWorkers);
-        }
-        const uint32_t stage = smem_u32(tile);
-        const float* pr = sc + (my_head * gs + lg) * chunk + (t0 - j0);
-#pragma unroll 1
-        for (int k16 = 0; k16 * 16 < tk; ++k16) {
-          // B fragment: probabilities of query head lane / 4 for keys 2 * (lane % 4) + {0, 1} and + 8 of the block
-          const int key = k16 * 16 + lt * 2;
-          float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
-          if (lg < gs) {
-            if (key < tk) p0 = pr[key];
-            if (key + 1 < tk) p1 = pr[key + 1];
-            if (key + 8 < tk) p2 = pr[key + 8];
-            if (key + 9 < tk) p3 = pr[key + 9];
-          }
-          const uint32_t b0 = pack2(p0, p1), b1 = pack2(p2, p3);
-          // A fragment: V^T, from rows (keys) of the tile: matrices (keys 0-7 | 8-15) x (dims 0-7 | 8-15) of the block
-          const int row = k16 * 16 + (lane & 7) + (lane >> 4) * 8;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int dt = my_slot + i * head_warps;
-            if (dt < dim_tiles) {
-              uint32_t af[4];
-              ldmatrix_x4_trans(af, piece_at(stage, my_head, row, dt * 2 + ((lane >> 3) & 1)));
-              mma_bf16_16816(vacc[i], af, b0, b1);
-            }
-          }
-        }
-        release(s);
-        issue(s + kDecStages - 1);
-      }
-    }
-#pragma unroll 1
-    for (int s = nt; s < (use_tma ? nt : 2 * nt); ++s) {
+    for (int s = nt; s < 2 * nt; ++s) {
       const int t0 = j0 + (s - nt) * tile_keys, t1 = min(j1, t0 + tile_keys);
       uint8_t* tile = tiles + stage_of(s) * stage_bytes;
       tiles_ok = landed(s) && tiles_ok;
-      if (newpos >= t0 && newpos < t1) patch(tile, vn, newpos - t0);  // the new value rows join their tile
-      named_bar_sync(1, kWorkers);  // the tile is complete and (first tile) so are the probabilities
-      issue(s + kDecStages - 1);
       const int tk = t1 - t0;
-      if (wtid < items) {  // at most one item per thread: its sums stay in registers across the tiles
-        const float* pr = sc + item_g * chunk + (t0 - j0);
-        const uint8_t* vtile = tile + (item_g / gs) * sub_bytes;
-#pragma unroll 4
-        for (int kk = item_part; kk < tk; kk += parts) {
-          float vf[8];
-          unpack8(*reinterpret_cast<const uint4*>(vtile + kk * row_bytes + ((item_piece ^ (kk & 7)) << 4)), vf);
-          const float w = pr[kk];
+      const bool has_new = newpos >= t0 && newpos < t1, short_tile = (tk & 15) != 0;
+      if (has_new || short_tile) {
+        if (has_new) patch(tile, vn, newpos - t0);  // the new value rows join their tile
+        if (short_tile) {
+          // the last 16-key block of a short tile: rows past the tile's keys meet zero probabilities, but what
+          // the stage holds there must be finite for that product to be zero
+          const int count = 16 - (tk & 15), per_row = hpu * lpk;
+          for (int it = wtid; it < count * per_row; it += kWorkers) {
+            const int r = tk + it / per_row, rest = it % per_row;
+            *reinterpret_cast<uint4*>(tile + piece_at(0u, rest / lpk, r, rest % lpk)) = make_uint4(0, 0, 0, 0);
+          }
+        }
+        fence_proxy_async_all();
+        named_bar_sync(1, kWorkers);
+      }
+      const uint32_t stage = smem_u32(tile);
+      const float* pr = sc + (my_head * gs + lg) * chunk + (t0 - j0);
+#pragma unroll 1
+      for (int k16 = 0; k16 * 16 < tk; ++k16) {
+        // B fragment: probabilities of query head lane / 4 for keys 2 * (lane % 4) + {0, 1} and + 8 of the block
+        const int key = k16 * 16 + lt * 2;
+        float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+        if (lg < gs) {
+          if (key < tk) p0 = pr[key];
+          if (key + 1 < tk) p1 = pr[key + 1];
+          if (key + 8 < tk) p2 = pr[key + 8];
+          if (key + 9 < tk) p3 = pr[key + 9];
+        }
+        const uint32_t b0 = pack2(p0, p1), b1 = pack2(p2, p3);
+        // A fragment: V^T, from rows (keys) of the tile: matrices (keys 0-7 | 8-15) x (dims 0-7 | 8-15) of the block
+        const int row = k16 * 16 + (lane & 7) + (lane >> 4) * 8;
 #pragma unroll
-          for (int e = 0; e < 8; ++e) acc[e] = fmaf(w, vf[e], acc[e]);
+        for (int i = 0; i < 4; ++i) {
+          const int dt = my_slot + i * head_warps;
+          if (dt < dim_tiles) {
+            uint32_t af[4];
+            ldmatrix_x4_trans(af, piece_at(stage, my_head, row, dt * 2 + ((lane >> 3) & 1)));
+            mma_bf16_16816(vacc[i], af, b0, b1);
+          }
         }
       }
+      release(s);
     }
     trace_event(cx, wtid, EV_ATT_VALUES);
-    if (use_tma && !workers_ok(cx, tiles_ok)) {
-      // a tile never came: give the copies still in flight a bounded time to land before the CTA leaves
-      for (int st = 0; st < kDecStages; ++st)
-        for (uint32_t spins = 0; spins < (1u << 20); ++spins)
-          if (mbar_try_wait(kvfull0 + st * 8u, 0) || mbar_try_wait(kvfull0 + st * 8u, 1)) break;
+    if (!workers_ok(cx, tiles_ok)) {
+      // a tile never came (or the launch was aborted elsewhere): the producer issues nothing more once it sees the
+      // abort flag; what it had issued lands within a few microseconds, and the CTA stays for thirty
+      for (int i = 0; i < 32; ++i) __nanosleep(1000);
       return false;
     }
-    if (use_mma) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int dt = my_slot + i * head_warps;
+    for (int i = 0; i < 4; ++i) {
+      const int dt = my_slot + i * head_warps;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int n = lt * 2 + (e & 1), d = dt * 16 + lg + (e >> 1) * 8;
-          if (dt < dim_tiles && n < gs) red[(my_head * gs + n) * hd + d] = vacc[i][e];
-        }
+      for (int e = 0; e < 4; ++e) {
+        const int n = lt * 2 + (e & 1), d = dt * 16 + lg + (e >> 1) * 8;
+        if (dt < dim_tiles && n < gs) red[(my_head * gs + n) * hd + d] = vacc[i][e];
       }
-    } else if (wtid < items) {
-      float* mine = red + (item_part * G + item_g) * hd + item_piece * 8;
-      *reinterpret_cast<float4*>(mine) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-      *reinterpret_cast<float4*>(mine + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
     named_bar_sync(1, kWorkers);
-    const int sum_parts = use_mma ? 1 : parts;
 #pragma unroll 1
     for (int col = wtid; col < cols; col += kWorkers) {
-      float o = red[col];
-#pragma unroll 1
-      for (int part = 1; part < sum_parts; ++part) o += red[part * cols + col];
+      const float o = red[col];
       const int g = col / hd, d = col - g * hd;
       const int head = kvh0 * gs + g;
       if (nch == 1) {
