@@ -1351,12 +1351,13 @@ __device__ __noinline__ bool attention_decode(const Ctx& cx, const AttnArgs& A_i
 // described (AttnArgs::kmap / vmap): one tiled TMA copy brings a stage (64 dimensions x tile_keys positions x
 // the unit's 64-dimension chunks, 128-byte swizzled: [chunk][key][128 B]), both products run on mma.sync
 // (scores: D[16 keys][heads] = K tile x q; values: D[16 dims][heads] += V tile^T x p), warp w works for KV
-// head w % hpu, waits for a stage's `full` barrier, releases it on its `empty` barrier, and the warps take
-// turns issuing the copy two tiles ahead.  The block meets only around what is exchanged between warps:
-// the scores -> statistics -> probabilities hand-over and the tiles that are written by hand (new row,
-// zeroed tail).  Measured on the 1.7B shape at context 1024, per step against attention_decode: batch 8 / 16 /
-// 32 (chunks of 256 / 513 / 1025 keys) 8 % / 9 % / 12 % faster; chunks shorter than four tiles never fill
-// the pipeline and stay with attention_decode, hence decode_stream_ok().
+// head w % hpu, waits for a stage's `full` barrier and releases it on its `empty` barrier; the copies are
+// issued by the weight producer (serve_cache_stream), which refills a stage the moment its eight releases
+// are in.  The block meets only around what is exchanged between warps: the scores -> statistics ->
+// probabilities hand-over and the tiles that are written by hand (new row, zeroed tail).  Measured on the
+// 1.7B shape at context 1024, per step against attention_decode: batch 8 / 16 / 32 (chunks of 256 / 513 /
+// 1025 keys) 16 % / 18 % / 21 % faster; chunks shorter than four tiles never fill the pipeline and stay
+// with attention_decode, hence decode_stream_ok().
 __device__ __forceinline__ bool decode_stream_ok(const KParams& p, const AttnArgs& A, int grid) {
   if (A.kmap == nullptr) return false;
   const int gs = p.q_heads / p.kv_heads, hd = p.head_dim;
